@@ -1,0 +1,96 @@
+/*
+ * wuda_b200 — C ABI of the B200 (sm_100a) decode hot path.
+ *
+ * One shared library, plain pointers and sizes, no framework types.  Every pointer is a
+ * DEVICE pointer unless its name ends in `_host`.  Every call enqueues work on `stream`
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream) and returns
+ * without synchronising, except the `*_host` convenience calls, which copy from and to
+ * host buffers and synchronise the stream before returning.
+ *
+ * Return value: WUDA_OK or a wuda_status.  Arguments are validated before anything is
+ * launched; a failed call launches nothing.  The text of the last failure on the
+ * calling thread is available from wuda_last_error().  Device-side problems (a wait
+ * that ran out of time, a block-table entry outside the pool) never trap the GPU: the
+ * kernel records a code (wuda_device_status) in the caller's `status_word` and ends.
+ *
+ * File:line citations name the interface of the reference (guluguluhhhh/wuda, paths
+ * relative to dsv4_megakernel/megakernel/) that the entry point stands in for.
+ */
+#ifndef WUDA_B200_H_
+#define WUDA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum wuda_status {
+    WUDA_OK = 0,
+    WUDA_ERR_INVALID_ARGUMENT = 1, /* shape / alignment / range check failed            */
+    WUDA_ERR_UNSUPPORTED = 2,      /* valid request outside what the kernels implement   */
+    WUDA_ERR_CUDA = 3,             /* a CUDA runtime or driver call failed               */
+    WUDA_ERR_NO_DEVICE = 4,        /* no sm_100 device / driver entry point unavailable  */
+    WUDA_ERR_DEVICE_STATUS = 5     /* (host-buffer calls) the kernel reported a code     */
+} wuda_status;
+
+/* Codes a kernel may leave in `status_word` (0 = nothing to report). */
+typedef enum wuda_device_status {
+    WUDA_DEV_OK = 0,
+    WUDA_DEV_TIMEOUT_FULL_Q = 101,
+    WUDA_DEV_TIMEOUT_EMPTY_Q = 102,
+    WUDA_DEV_TIMEOUT_FULL_KV = 103,
+    WUDA_DEV_TIMEOUT_EMPTY_KV = 104,
+    WUDA_DEV_TIMEOUT_FULL_TMEM = 105,
+    WUDA_DEV_TIMEOUT_EMPTY_TMEM = 106,
+    WUDA_DEV_BAD_PAGE_INDEX = 110, /* block_table entry outside [0, num_blocks): page 0 was read instead */
+    WUDA_DEV_TIMEOUT_GEMM_FULL = 121,
+    WUDA_DEV_TIMEOUT_GEMM_EMPTY = 122,
+    WUDA_DEV_TIMEOUT_GEMM_TMEM_FULL = 123,
+    WUDA_DEV_TIMEOUT_GEMM_TMEM_EMPTY = 124,
+    WUDA_DEV_TIMEOUT_PEER_FLAG = 131
+} wuda_device_status;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int wuda_version(void);
+/* Message of the last non-OK return on this thread ("" if none). Never NULL. */
+const char* wuda_last_error(void);
+/* Number of SMs of the current device, or a negative wuda_status. */
+int wuda_num_sms(void);
+
+/* ------------------------------------------------------------------------------------
+ * Paged FP8 MQA logits (the indexer score).
+ *
+ *   logits[r, t] = scale[t] * sum_h weights[r, h] * relu( sum_d q[r, h, d] * k[t, d] )
+ *
+ * for every row r = b * next_n + j and every token t < context_lens[b, j] of request b,
+ * where token t lives in physical page block_table[b, t / entries_per_block] at slot
+ * t % entries_per_block.  Positions t >= context_lens[b, j] are NOT written.
+ *
+ * Stands in for mqa_logits_fp8_decode_out (kernels/mqa_logits_fp8.cu:388-526) without
+ * its optional compressor / query tails, and for deep_gemm.fp8_paged_mqa_logits as
+ * called at test/test_mqa_logits_fp4.py:518-522.  The reference's `schedule_meta`
+ * tensor has no counterpart: the tile schedule is computed inside the kernel.
+ *
+ *   q             e4m3  [batch * next_n, 64, 128], contiguous, 16-byte aligned
+ *   kv_pages      uint8 [num_blocks, page_stride_bytes]; a page is
+ *                 entries_per_block x 128 e4m3 key bytes followed by entries_per_block
+ *                 fp32 per-token scales (test/test_mqa_logits_fp4.py:443-474);
+ *                 16-byte aligned, page_stride_bytes % 16 == 0 and >= epb * 132
+ *   weights       fp32  [batch * next_n, 64] (per-head weight, q scale pre-folded)
+ *   context_lens  int32 [batch, next_n] (for next_n == 1 this is the reference's [B] / [B,1])
+ *   block_table   int32 [batch, block_table_stride]; rows of one request share it
+ *   logits        fp32  [batch * next_n, logits_stride]
+ *   next_n        1 or 2; entries_per_block 32, 64 or 128
+ *   status_word   int32 on the device, nullable; see wuda_device_status
+ */
+int wuda_mqa_logits_fp8(const void* q, const void* kv_pages, const float* weights,
+                        const int32_t* context_lens, const int32_t* block_table, float* logits,
+                        int batch, int next_n, int num_blocks, int entries_per_block,
+                        int64_t page_stride_bytes, int block_table_stride, int64_t logits_stride,
+                        int32_t* status_word, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WUDA_B200_H_ */

@@ -1,0 +1,221 @@
+/*
+ * TEST INFRASTRUCTURE — CPU oracle for the decode hot path.
+ *
+ * A plain-C restatement of the reference's arithmetic for each operator on the path,
+ * used only as the checker in tests/, in __graft_entry__.smoke() and as the timed CPU
+ * baseline of bench.py.  The product (wuda_b200/) never calls it.
+ *
+ * Each function names the reference file:line it restates (paths relative to the
+ * reference repository root).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define MQA_HEADS 64
+#define MQA_DIM 128
+
+/* ------------------------------------------------------------------ number formats */
+
+/* OCP e4m3 (fn variant: no infinities, 0x7f/0xff = NaN, max 448) -> fp32. */
+float oracle_e4m3_to_f32(uint8_t v) {
+    const int sign = v >> 7;
+    const int e = (v >> 3) & 0xF;
+    const int m = v & 0x7;
+    float r;
+    if (e == 0xF && m == 0x7) return NAN;
+    if (e == 0) r = ldexpf((float)m, -9); /* subnormal: m/8 * 2^-6 */
+    else r = ldexpf(1.0f + (float)m / 8.0f, e - 7);
+    return sign ? -r : r;
+}
+
+/* fp32 -> e4m3, round to nearest even, saturating to +-448 (cvt.rn.satfinite
+ * semantics, which is also what torch's .to(float8_e4m3fn) yields for |x| <= 448). */
+uint8_t oracle_f32_to_e4m3(float x) {
+    if (isnan(x)) return 0x7F;
+    const uint8_t sign = signbit(x) ? 0x80 : 0;
+    float a = fabsf(x);
+    if (a >= 448.0f) return sign | 0x7E;
+    if (a < ldexpf(1.0f, -10)) return sign; /* below half the smallest subnormal */
+    int ex;
+    frexpf(a, &ex);       /* a = f * 2^ex, f in [0.5,1) -> exponent of leading bit = ex-1 */
+    int e = ex - 1;
+    if (e < -6) e = -6;   /* subnormal range shares the exponent of 2^-6 */
+    /* quantum = 2^(e-3); value / quantum rounded to nearest even */
+    const float q = ldexpf(a, 3 - e);
+    float r = nearbyintf(q); /* default rounding mode: to nearest even */
+    int mant = (int)r;
+    int be = e + 7;
+    if (e == -6 && mant < 8) { /* subnormal */
+        return sign | (uint8_t)mant;
+    }
+    if (mant == 16) { mant = 8; be += 1; }
+    if (be > 15 || (be == 15 && mant - 8 > 6)) return sign | 0x7E;
+    return sign | (uint8_t)(be << 3) | (uint8_t)(mant - 8);
+}
+
+void oracle_e4m3_decode(const uint8_t* src, float* dst, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) dst[i] = oracle_e4m3_to_f32(src[i]);
+}
+void oracle_e4m3_encode(const float* src, uint8_t* dst, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) dst[i] = oracle_f32_to_e4m3(src[i]);
+}
+
+/* bf16 helpers (round to nearest even), used by the norm / RoPE / quant chains. */
+static inline float bf16_round(float x) {
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    if ((u & 0x7F800000u) == 0x7F800000u) return x;
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    u &= 0xFFFF0000u;
+    memcpy(&x, &u, 4);
+    return x;
+}
+static inline float bf16_to_f32(uint16_t h) {
+    uint32_t u = (uint32_t)h << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+static inline uint16_t f32_to_bf16(float x) {
+    float r = bf16_round(x);
+    uint32_t u;
+    memcpy(&u, &r, 4);
+    return (uint16_t)(u >> 16);
+}
+
+/* ------------------------------------------------------------------ paged MQA logits
+ *
+ * logits[r, t] = scale[t] * sum_h w[r, h] * relu(sum_d q[r, h, d] * k[t, d])
+ *
+ * Formula: dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py:207-218
+ * (ref_fp8_mqa_logits: fp32 einsum, relu, weighted head sum; the mask there is
+ * t < context).  Page layout: same file :443-474 (build_fp8_paged_cache: a page is
+ * epb x 128 e4m3 bytes, then epb fp32 scales; block_table maps logical to physical
+ * pages).  The per-token scale multiplies the head sum, as in
+ * dsv4_megakernel/megakernel/include/mqa_logits_fp8.cuh:722-724; the test applies it
+ * by dequantising k first, which is the same number up to fp32 rounding.
+ * Argument contract: dsv4_megakernel/megakernel/kernels/mqa_logits_fp8.cu:417-461.
+ * Rows r = b * next_n + j share request b's block table; only t < context_lens[b, j]
+ * is written.  Returns 0, or -1 if a needed block-table entry is outside the pool.
+ */
+int oracle_mqa_logits_fp8(const uint8_t* q, const uint8_t* kv_pages, const float* weights,
+                          const int32_t* context_lens, const int32_t* block_table, float* logits,
+                          int batch, int next_n, int num_blocks, int epb, int64_t page_stride,
+                          int bt_stride, int64_t logits_stride) {
+    float lut[256];
+    for (int i = 0; i < 256; ++i) lut[i] = oracle_e4m3_to_f32((uint8_t)i);
+    int bad = 0;
+    const int rows = batch * next_n;
+    /* dequantised queries, [rows][64][128] */
+    float* qf = (float*)malloc((size_t)rows * MQA_HEADS * MQA_DIM * sizeof(float));
+    if (!qf) return -2;
+    for (int64_t i = 0; i < (int64_t)rows * MQA_HEADS * MQA_DIM; ++i) qf[i] = lut[q[i]];
+
+    for (int b = 0; b < batch; ++b) {
+        int ctx_max = 0;
+        for (int j = 0; j < next_n; ++j)
+            if (context_lens[b * next_n + j] > ctx_max) ctx_max = context_lens[b * next_n + j];
+#pragma omp parallel for schedule(dynamic, 64) reduction(| : bad)
+        for (int t = 0; t < ctx_max; ++t) {
+            const int page = t / epb, slot = t % epb;
+            int phys = (page < bt_stride) ? block_table[(int64_t)b * bt_stride + page] : -1;
+            if (phys < 0 || phys >= num_blocks) {
+                bad = 1;
+                continue;
+            }
+            const uint8_t* pg = kv_pages + (int64_t)phys * page_stride;
+            float kf[MQA_DIM];
+            for (int d = 0; d < MQA_DIM; ++d) kf[d] = lut[pg[slot * MQA_DIM + d]];
+            float scale;
+            memcpy(&scale, pg + (int64_t)epb * MQA_DIM + slot * 4, 4);
+            for (int j = 0; j < next_n; ++j) {
+                const int r = b * next_n + j;
+                if (t >= context_lens[r]) continue;
+                const float* qr = qf + (int64_t)r * MQA_HEADS * MQA_DIM;
+                const float* wr = weights + (int64_t)r * MQA_HEADS;
+                float sum = 0.0f;
+                for (int h = 0; h < MQA_HEADS; ++h) {
+                    const float* qh = qr + h * MQA_DIM;
+                    float dot = 0.0f;
+                    for (int d = 0; d < MQA_DIM; ++d) dot += qh[d] * kf[d];
+                    if (dot > 0.0f) sum += wr[h] * dot;
+                }
+                logits[(int64_t)r * logits_stride + t] = sum * scale;
+            }
+        }
+    }
+    free(qf);
+    return bad ? -1 : 0;
+}
+
+/* ------------------------------------------------------------------ top-k + page transform
+ *
+ * Per row: the indices of the k largest of scores[r, 0:seq_len[r]] (ties: lower index
+ * first, i.e. torch.argsort(-scores, stable=True)[:k],
+ * dsv4_megakernel/megakernel/test/test_topk_v2.py:116), written in descending score
+ * order.  Rows with seq_len <= k give [0..n) followed by -1 (same file :108-114).
+ * page_indices = (page_table[r, i >> bits] << bits) | (i & (page_size-1)), -1 stays -1
+ * (same file :86-94).  raw (nullable) receives the untransformed indices.
+ */
+typedef struct {
+    float v;
+    int32_t i;
+} oracle_pair;
+
+static int pair_cmp(const void* a, const void* b) {
+    const oracle_pair* x = (const oracle_pair*)a;
+    const oracle_pair* y = (const oracle_pair*)b;
+    if (x->v > y->v) return -1;
+    if (x->v < y->v) return 1;
+    return (x->i > y->i) - (x->i < y->i);
+}
+
+int oracle_topk(const float* scores, const int32_t* seq_lens, const int32_t* page_table,
+                int32_t* page_indices, int32_t* raw, int rows, int64_t score_stride,
+                int64_t page_table_stride, int k, int page_size) {
+    int bits = 0;
+    while ((1 << bits) < page_size) ++bits;
+    if ((1 << bits) != page_size) return -1;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int r = 0; r < rows; ++r) {
+        const int n = seq_lens[r] > 0 ? seq_lens[r] : 0;
+        int32_t* out = (int32_t*)malloc((size_t)k * sizeof(int32_t));
+        if (n <= k) {
+            for (int i = 0; i < k; ++i) out[i] = i < n ? i : -1;
+        } else {
+            oracle_pair* p = (oracle_pair*)malloc((size_t)n * sizeof(oracle_pair));
+            for (int i = 0; i < n; ++i) {
+                p[i].v = scores[(int64_t)r * score_stride + i];
+                p[i].i = i;
+            }
+            qsort(p, (size_t)n, sizeof(oracle_pair), pair_cmp);
+            for (int i = 0; i < k; ++i) out[i] = p[i].i;
+            free(p);
+        }
+        for (int i = 0; i < k; ++i) {
+            const int32_t x = out[i];
+            if (raw) raw[(int64_t)r * k + i] = x;
+            if (page_indices)
+                page_indices[(int64_t)r * k + i] =
+                    x < 0 ? -1
+                          : (int32_t)(((uint32_t)page_table[(int64_t)r * page_table_stride + (x >> bits)] << bits) |
+                                      (uint32_t)(x & (page_size - 1)));
+        }
+        free(out);
+    }
+    return 0;
+}
+
+int oracle_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}

@@ -1,0 +1,126 @@
+"""Generates the golden fixtures in this directory by running the REFERENCE's own
+Python reference functions (imported from a checkout of guluguluhhhh/wuda) on small
+seeded inputs.  The fixtures store inputs and expected outputs, so the tests need
+neither the checkout nor this script.
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+Functions used (paths inside the reference repository):
+  dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py  ref_fp8_mqa_logits (:207-218)
+  dsv4_megakernel/megakernel/test/test_topk_v2.py         ref_page_transform (:86-94) and the
+                                                           stable-argsort rule (:116)
+Both are written for device="cuda"; they are run here on the CPU by mapping that one
+keyword to "cpu", which changes no arithmetic.
+"""
+import importlib.util
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+from wuda_b200 import workloads  # noqa: E402
+
+
+class _CpuTorch:
+    """Proxy of the torch module that sends device='cuda' factory calls to the CPU."""
+
+    def __init__(self):
+        self._t = torch
+
+    def __getattr__(self, name):
+        attr = getattr(self._t, name)
+        if callable(attr) and name in ("arange", "full", "zeros", "ones", "empty", "tensor", "randn",
+                                       "randint", "rand", "randperm", "full_like"):
+            def wrapped(*a, **k):
+                if k.get("device") == "cuda":
+                    k["device"] = "cpu"
+                return attr(*a, **k)
+            return wrapped
+        return attr
+
+
+def _load(ref_root, rel, name):
+    path = os.path.join(ref_root, rel)
+    sys.path.insert(0, os.path.dirname(path))
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.torch = _CpuTorch()
+    return mod
+
+
+def logical_keys(case, b):
+    """Dequantised keys of request b in token order: (e4m3 bytes as fp32 [T,128], scales [T])."""
+    epb, ctx = case["epb"], int(case["ctx"][b])
+    pages = case["block_table"][b, :(ctx + epb - 1) // epb]
+    pg = case["kv_pages"][pages]
+    k8 = pg[:, :epb * 128].reshape(-1, 128)[:ctx]
+    sc = pg[:, epb * 128:epb * 132].copy().view(np.float32).reshape(-1)[:ctx]
+    kf = torch.from_numpy(k8.copy()).view(torch.float8_e4m3fn).float()
+    return kf, torch.from_numpy(sc.copy())
+
+
+def golden_mqa(ref_mqa, name, **kw):
+    case = workloads.make_mqa_case(**kw)
+    rows = case["batch"] * case["next_n"]
+    expected = np.full((rows, case["logits_stride"]), -np.inf, np.float32)
+    q = torch.from_numpy(case["q"]).view(torch.float8_e4m3fn)
+    w = torch.from_numpy(case["weights"])
+    for b in range(case["batch"]):
+        kf, sc = logical_keys(case, b)
+        kv = kf * sc[:, None]                      # dequantised keys, fp32
+        r0 = b * case["next_n"]
+        qb = q[r0:r0 + case["next_n"]]
+        ke = torch.from_numpy(case["context_lens"][b].astype(np.int64))
+        ks = torch.zeros_like(ke)
+        out = ref_mqa.ref_fp8_mqa_logits(qb, kv, w[r0:r0 + case["next_n"]], ks, ke)
+        expected[r0:r0 + case["next_n"], :kv.shape[0]] = out.numpy()
+    arrays = {k: case[k] for k in ("q", "kv_pages", "weights", "context_lens", "block_table", "ctx")}
+    np.savez_compressed(os.path.join(HERE, name), expected=expected, next_n=case["next_n"], epb=case["epb"],
+                        logits_stride=case["logits_stride"], **arrays)
+    print(name, expected.shape, "finite:", int(np.isfinite(expected).sum()))
+
+
+def golden_topk(ref_topk, name, rows, length, k, lens, tie_levels, seed):
+    g = torch.Generator().manual_seed(seed)
+    scores = torch.randn(rows, length, generator=g)
+    if tie_levels > 0:
+        scores = torch.randint(0, tie_levels, (rows, length), generator=g).float()
+    for r in range(rows):
+        scores[r, lens[r]:] = float("-inf")
+    page_size = ref_topk.PAGE_SIZE
+    num_pages = (length + page_size - 1) // page_size
+    page_table = torch.randint(0, 1 << 20, (rows, max(num_pages, 1)), generator=g, dtype=torch.int32)
+    raw = torch.full((rows, k), -1, dtype=torch.int32)
+    pages = torch.full((rows, k), -1, dtype=torch.int32)
+    for r in range(rows):
+        n = lens[r]
+        if n <= k:
+            raw[r, :n] = torch.arange(n, dtype=torch.int32)
+        else:
+            raw[r] = torch.argsort(-scores[r, :n], stable=True)[:k].int()
+        pages[r] = ref_topk.ref_page_transform(page_table[r], raw[r]).int()
+    np.savez_compressed(os.path.join(HERE, name), scores=scores.numpy(), seq_lens=np.asarray(lens, np.int32),
+                        page_table=page_table.numpy(), raw=raw.numpy(), pages=pages.numpy(), k=k,
+                        page_size=page_size)
+    print(name, raw.shape)
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    tdir = "dsv4_megakernel/megakernel/test"
+    ref_mqa = _load(ref_root, tdir + "/test_mqa_logits_fp4.py", "ref_mqa")
+    golden_mqa(ref_mqa, "mqa_logits_fp8_n1.npz", batch=3, next_n=1, ctx_lo=1, ctx_hi=400, epb=64, seed=11)
+    golden_mqa(ref_mqa, "mqa_logits_fp8_n2_epb32.npz", batch=2, next_n=2, ctx_lo=60, ctx_hi=300, epb=32,
+               seed=12, page_pad=128)
+    ref_topk = _load(ref_root, tdir + "/test_topk_v2.py", "ref_topk")
+    golden_topk(ref_topk, "topk_random.npz", 3, 3000, 512, [3000, 2100, 300], 0, 21)
+    golden_topk(ref_topk, "topk_ties.npz", 2, 4096, 1024, [4096, 2500], 7, 22)
+
+
+if __name__ == "__main__":
+    main()

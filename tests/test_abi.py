@@ -1,0 +1,59 @@
+"""The C-ABI library loads without a GPU and exports every symbol the public header
+declares, and argument validation fails cleanly before any launch."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "wuda_b200.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\b(wuda_[a-z0-9_]+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_header_declares_functions():
+    names = declared_functions()
+    assert "wuda_mqa_logits_fp8" in names and "wuda_last_error" in names
+
+
+def test_library_exports_every_declared_symbol():
+    import wuda_b200._lib as L
+    for name in declared_functions():
+        assert hasattr(L.lib, name), "libwuda_b200.so does not export %s" % name
+    # and the ctypes table covers the header exactly
+    assert sorted(L.SIGNATURES) == declared_functions()
+
+
+def test_version_and_error_string():
+    import wuda_b200._lib as L
+    assert L.lib.wuda_version() >= 100
+    assert isinstance(L.lib.wuda_last_error(), bytes)
+
+
+def test_invalid_arguments_are_rejected_before_launch():
+    import wuda_b200._lib as L
+    vp = ctypes.c_void_p
+    fake = vp(0x1000)
+    # next_n = 3 is outside what the kernel implements
+    st = L.lib.wuda_mqa_logits_fp8(fake, fake, fake, fake, fake, fake, 1, 3, 4, 64, 64 * 132, 4, 256, None, None)
+    assert st == 2 and b"next_n" in L.lib.wuda_last_error()
+    # page stride too small for the payload
+    st = L.lib.wuda_mqa_logits_fp8(fake, fake, fake, fake, fake, fake, 1, 1, 4, 64, 64 * 128, 4, 256, None, None)
+    assert st == 1 and b"page_stride_bytes" in L.lib.wuda_last_error()
+    # bad page size
+    st = L.lib.wuda_mqa_logits_fp8(fake, fake, fake, fake, fake, fake, 1, 1, 4, 48, 64 * 132, 4, 256, None, None)
+    assert st == 1
+    # NULL tensors
+    st = L.lib.wuda_mqa_logits_fp8(None, fake, fake, fake, fake, fake, 1, 1, 4, 64, 64 * 132, 4, 256, None, None)
+    assert st == 1 and b"NULL" in L.lib.wuda_last_error()
+    # misaligned q
+    st = L.lib.wuda_mqa_logits_fp8(vp(0x1004), fake, fake, fake, fake, fake, 1, 1, 4, 64, 64 * 132, 4, 256, None, None)
+    assert st == 1 and b"aligned" in L.lib.wuda_last_error()
+    # empty batch is a no-op
+    assert L.lib.wuda_mqa_logits_fp8(None, None, None, None, None, None, 0, 1, 4, 64, 64 * 132, 4, 256, None, None) == 0

@@ -1,0 +1,9 @@
+"""wuda_b200 — B200 (sm_100a) implementation of the DeepSeek-V4-style decode hot path.
+
+The product is libwuda_b200.so (hand-written CUDA behind the C ABI of
+include/wuda_b200.h).  This package is the thin host-side mirror of the reference's
+Python operator interface on top of that ABI; torch is used only for device memory and
+streams.  Importing the package requires the built library (python -m wuda_b200.build).
+"""
+from ._lib import WudaError, lib, LIB_PATH  # noqa: F401
+from .ops import *  # noqa: F401,F403

@@ -1,0 +1,51 @@
+"""ctypes binding of libwuda_b200.so (the C ABI declared in include/wuda_b200.h).
+
+The library must exist: there is no fallback path.  Importing this module on a machine
+where the library has not been built raises ImportError with the build command.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libwuda_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        "wuda_b200: %s is missing. Build it with `python -m wuda_b200.build` "
+        "(needs nvcc); there is no fallback implementation." % LIB_PATH)
+
+lib = ctypes.CDLL(LIB_PATH)
+
+c_int, c_i64, c_vp, c_float = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
+
+# name -> (restype, argtypes); mirrors include/wuda_b200.h one to one.
+SIGNATURES = {
+    "wuda_version": (c_int, []),
+    "wuda_last_error": (ctypes.c_char_p, []),
+    "wuda_num_sms": (c_int, []),
+    "wuda_mqa_logits_fp8": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int,
+                                    c_i64, c_int, c_i64, c_vp, c_vp]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)  # AttributeError here = header and library disagree
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+WUDA_OK = 0
+STATUS_NAMES = {0: "WUDA_OK", 1: "WUDA_ERR_INVALID_ARGUMENT", 2: "WUDA_ERR_UNSUPPORTED",
+                3: "WUDA_ERR_CUDA", 4: "WUDA_ERR_NO_DEVICE", 5: "WUDA_ERR_DEVICE_STATUS"}
+
+
+class WudaError(RuntimeError):
+    """A C-ABI call returned a non-zero status (the reference raises RuntimeError from
+    TORCH_CHECK in the same situations)."""
+
+    def __init__(self, status, message):
+        super().__init__("%s: %s" % (STATUS_NAMES.get(status, status), message))
+        self.status = status
+
+
+def check(status):
+    if status != WUDA_OK:
+        raise WudaError(status, lib.wuda_last_error().decode())

@@ -1,0 +1,474 @@
+// Paged FP8 MQA logits for sm_100a.
+//
+//   logits[r, t] = scale[t] * sum_h w[r, h] * relu( q[r, h, :] . k[t, :] )
+//
+// Formula and page layout follow the reference's test oracle
+// (dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py:207-218 and :443-474); the
+// order "dot -> relu -> weighted head sum -> times token scale" follows the reference
+// kernel (include/mqa_logits_fp8.cuh:685-734).  The design is this library's own:
+//
+//  * persistent grid, one CTA per SM; the flat list of (request, 128-token tile) work
+//    items is cut into equal contiguous chunks inside the kernel (no host schedule);
+//  * a 128-token tile of keys is the UMMA A operand (M = 128 tokens, K = 128 dims,
+//    each token row is exactly one 128-byte swizzle span, so a page lands in shared
+//    memory with one tiled TMA copy per page and needs no repacking);
+//  * the request's next_n x 64 query heads are the B operand (N = 64 * next_n), loaded
+//    once per request, so the keys of a request are read from HBM once for all its rows;
+//  * tcgen05.mma kind::f8f6f4 accumulates into TMEM (4 accumulator stages); two math
+//    warpgroups alternate tiles: tcgen05.ld, relu, weighted head sum, token scale,
+//    coalesced fp32 stores;
+//  * every mbarrier wait is bounded and reports through the status word.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "host.h"
+#include "ptx.cuh"
+
+namespace wuda {
+namespace mqa {
+
+constexpr int kHeads = 64;
+constexpr int kDim = 128;
+constexpr int kTile = 128;          // tokens per work item (UMMA M)
+constexpr int kQStages = 2;
+constexpr int kTmemStages = 4;
+constexpr int kMaxKvStages = 12;
+constexpr int kMathWarps = 8;       // two warpgroups
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kThreads = 320;
+constexpr int kKvTileBytes = kTile * kDim;      // 16 KB
+constexpr int kScaleTileBytes = kTile * 4;      // 512 B
+
+struct Params {
+    const uint8_t* kv_pages;
+    const float* weights;
+    const int32_t* context_lens;
+    const int32_t* block_table;
+    float* logits;
+    int32_t* status;
+    int64_t page_stride;
+    int64_t logits_stride;
+    int batch;
+    int num_blocks;
+    int epb;
+    int bt_stride;
+    int kv_stages;
+};
+
+template <int NEXT_N>
+struct Smem {
+    static constexpr int kN = NEXT_N * kHeads;
+    static constexpr int kQBytes = kN * kDim;
+    static constexpr int kWBytes = kN * 4;
+    // byte offsets from the 1024-aligned base
+    static constexpr int q_off = 0;
+    static constexpr int kv_off = q_off + kQStages * kQBytes;
+    static __host__ __device__ constexpr int scale_off(int stages) { return kv_off + stages * kKvTileBytes; }
+    static __host__ __device__ constexpr int w_off(int stages) { return scale_off(stages) + stages * kScaleTileBytes; }
+    static __host__ __device__ constexpr int bar_off(int stages) { return w_off(stages) + kQStages * kWBytes; }
+    // barriers: full_q[2] empty_q[2] full_kv[12] empty_kv[12] full_tmem[4] empty_tmem[4] = 36 x 8 B
+    static __host__ __device__ constexpr int misc_off(int stages) { return bar_off(stages) + 36 * 8; }
+    static __host__ __device__ constexpr int total(int stages) { return misc_off(stages) + 16 + 1024; }
+};
+
+// Number of 128-token tiles request b needs (max context over its next_n rows).
+template <int NEXT_N>
+__device__ __forceinline__ int request_ctx(const int32_t* ctx, int b) {
+    int m = 0;
+#pragma unroll
+    for (int j = 0; j < NEXT_N; ++j) m = max(m, __ldg(ctx + b * NEXT_N + j));
+    return m;
+}
+
+// The position of one CTA in the flat tile list. Every warp keeps its own copy and
+// advances it identically, so no shared-memory broadcast is needed.
+struct TileCursor {
+    int b;         // request
+    int j;         // tile inside the request
+    int tiles_b;   // tiles of request b
+    int ctx_b;     // max context of request b
+    int count;     // tiles this CTA owns
+};
+
+template <int NEXT_N>
+__device__ __forceinline__ TileCursor make_cursor(const int32_t* ctx, int batch) {
+    const uint32_t lane = lane_id();
+    long long total = 0;
+    for (int base = 0; base < batch; base += 32) {
+        int b = base + lane;
+        int t = (b < batch) ? ((request_ctx<NEXT_N>(ctx, b) + kTile - 1) / kTile) : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        total += t;
+    }
+    const long long start = total * blockIdx.x / gridDim.x;
+    const long long end = total * (blockIdx.x + 1) / gridDim.x;
+    TileCursor c;
+    c.count = static_cast<int>(end - start);
+    c.b = batch;
+    c.j = 0;
+    c.tiles_b = 0;
+    c.ctx_b = 0;
+    if (c.count == 0) return c;
+    long long prefix = 0;
+    for (int base = 0; base < batch; base += 32) {
+        int b = base + lane;
+        int cx = (b < batch) ? request_ctx<NEXT_N>(ctx, b) : 0;
+        int t = (cx + kTile - 1) / kTile;
+        int incl = t;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        const long long incl_g = prefix + incl;
+        const unsigned hit = __ballot_sync(0xffffffffu, incl_g > start);
+        if (hit) {
+            const int src = __ffs(hit) - 1;
+            const long long incl_src = __shfl_sync(0xffffffffu, incl_g, src);
+            const int t_src = __shfl_sync(0xffffffffu, t, src);
+            c.b = base + src;
+            c.tiles_b = t_src;
+            c.ctx_b = __shfl_sync(0xffffffffu, cx, src);
+            c.j = static_cast<int>(start - (incl_src - t_src));
+            return c;
+        }
+        prefix += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    c.count = 0;  // unreachable when the two passes see the same lengths
+    return c;
+}
+
+template <int NEXT_N>
+__device__ __forceinline__ void advance(TileCursor& c, const int32_t* ctx, int batch) {
+    if (++c.j < c.tiles_b) return;
+    c.j = 0;
+    do {
+        ++c.b;
+        if (c.b >= batch) {
+            c.tiles_b = 0;
+            c.ctx_b = 0;
+            return;
+        }
+        c.ctx_b = request_ctx<NEXT_N>(ctx, c.b);
+        c.tiles_b = (c.ctx_b + kTile - 1) / kTile;
+    } while (c.tiles_b == 0);
+}
+
+template <int NEXT_N>
+__global__ void __launch_bounds__(kThreads, 1)
+mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
+                      const __grid_constant__ CUtensorMap kv_map, const Params p) {
+    using L = Smem<NEXT_N>;
+    constexpr int kN = L::kN;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw_addr);
+    const int S = p.kv_stages;
+
+    const uint32_t q_smem = base + L::q_off;
+    const uint32_t kv_smem = base + L::kv_off;
+    const uint32_t scale_smem = base + L::scale_off(S);
+    const uint32_t w_smem = base + L::w_off(S);
+    const uint32_t bars = base + L::bar_off(S);
+    const uint32_t full_q = bars, empty_q = bars + 16;
+    const uint32_t full_kv = bars + 32, empty_kv = full_kv + kMaxKvStages * 8;
+    const uint32_t full_tm = empty_kv + kMaxKvStages * 8, empty_tm = full_tm + kTmemStages * 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + L::misc_off(S));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::misc_off(S) + 4);
+    const float* scale_ptr = reinterpret_cast<const float*>(base_ptr + L::scale_off(S));
+    const float* w_ptr = reinterpret_cast<const float*>(base_ptr + L::w_off(S));
+
+    const int warp = threadIdx.x >> 5;
+    const uint32_t lane = lane_id();
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < kQStages; ++i) {
+            mbar_init(full_q + i * 8, 1);
+            mbar_init(empty_q + i * 8, 1 + kMathWarps);
+        }
+        for (int i = 0; i < S; ++i) {
+            mbar_init(full_kv + i * 8, 1);
+            mbar_init(empty_kv + i * 8, 4);
+        }
+        for (int i = 0; i < kTmemStages; ++i) {
+            mbar_init(full_tm + i * 8, 1);
+            mbar_init(empty_tm + i * 8, 4);
+        }
+        fence_mbar_init();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemStages * kN);
+        tmem_relinquish();
+    }
+    if (warp == kProducerWarp && lane == 0) {
+        prefetch_tmap(&q_map);
+        prefetch_tmap(&kv_map);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    TileCursor cur = make_cursor<NEXT_N>(p.context_lens, p.batch);
+    const int ntiles = cur.count;
+
+    if (warp == kProducerWarp) {
+        // ---------------------------------------------------------------- TMA producer
+        const uint64_t stream_policy = policy_evict_first();
+        const int ppt = kTile / p.epb;                    // pages per tile: 4, 2 or 1
+        const uint32_t page_bytes = p.epb * kDim;
+        const uint32_t page_scale_bytes = p.epb * 4;
+        int prev_b = -1, qc = 0;
+        int win_b = -1, win_base = 0, win_val = 0;        // 32 cached block-table entries
+        bool alive = true;
+        for (int n = 0; n < ntiles && alive; ++n) {
+            if (cur.b != prev_b) {
+                const int qs = qc & 1;
+                alive = mbar_wait_warp(empty_q + qs * 8, ((qc >> 1) & 1) ^ 1, abort_flag, p.status,
+                                  kDevTimeoutEmptyQ);
+                if (!alive) break;
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(full_q + qs * 8, L::kQBytes + L::kWBytes);
+                    tma_load_2d(q_smem + qs * L::kQBytes, &q_map, full_q + qs * 8, 0, cur.b * kN);
+                    bulk_load(w_smem + qs * L::kWBytes, p.weights + static_cast<int64_t>(cur.b) * kN,
+                              L::kWBytes, full_q + qs * 8);
+                }
+                prev_b = cur.b;
+                ++qc;
+            }
+            const int s = n % S;
+            alive = mbar_wait_warp(empty_kv + s * 8, ((n / S) & 1) ^ 1, abort_flag, p.status,
+                              kDevTimeoutEmptyKv);
+            if (!alive) break;
+            const int pages_b = (cur.ctx_b + p.epb - 1) / p.epb;
+            const int first_page = cur.j * ppt;
+            const int valid = min(ppt, pages_b - first_page);
+            if (win_b != cur.b || first_page < win_base || first_page + valid > win_base + 32) {
+                win_b = cur.b;
+                win_base = first_page;
+                const int pg = win_base + lane;
+                win_val = (pg < pages_b && pg < p.bt_stride)
+                              ? __ldg(p.block_table + static_cast<int64_t>(cur.b) * p.bt_stride + pg)
+                              : -1;
+            }
+            if (lane == 0)
+                mbar_arrive_expect_tx(full_kv + s * 8, valid * (page_bytes + page_scale_bytes));
+            for (int pg = 0; pg < valid; ++pg) {
+                int phys = __shfl_sync(0xffffffffu, win_val, first_page + pg - win_base);
+                if (lane == 0) {
+                    if (phys < 0 || phys >= p.num_blocks) {
+                        if (p.status) atomicCAS(p.status, 0, kDevBadPageIndex);
+                        phys = 0;
+                    }
+                    tma_load_3d_hint(kv_smem + s * kKvTileBytes + pg * page_bytes, &kv_map,
+                                     full_kv + s * 8, 0, 0, phys, stream_policy);
+                    bulk_load(scale_smem + s * kScaleTileBytes + pg * page_scale_bytes,
+                              p.kv_pages + static_cast<int64_t>(phys) * p.page_stride + page_bytes,
+                              page_scale_bytes, full_kv + s * 8);
+                }
+            }
+            advance<NEXT_N>(cur, p.context_lens, p.batch);
+        }
+    } else if (warp == kMmaWarp) {
+        // ---------------------------------------------------------------- UMMA issuer
+        constexpr uint32_t idesc = umma_idesc(kTile, kN, 0, 0);
+        int prev_b = -1, qc = 0, qs = 0;
+        bool alive = true;
+        for (int n = 0; n < ntiles && alive; ++n) {
+            if (cur.b != prev_b) {
+                if (prev_b >= 0 && lane == 0) umma_commit(empty_q + qs * 8);  // q stage free once its MMAs retire
+                qs = qc & 1;
+                alive = mbar_wait_warp(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status, kDevTimeoutFullQ);
+                if (!alive) break;
+                prev_b = cur.b;
+                ++qc;
+            }
+            const int s = n % S;
+            const int ts = n % kTmemStages;
+            alive = mbar_wait_warp(full_kv + s * 8, (n / S) & 1, abort_flag, p.status, kDevTimeoutFullKv);
+            if (!alive) break;
+            alive = mbar_wait_warp(empty_tm + ts * 8, ((n / kTmemStages) & 1) ^ 1, abort_flag, p.status,
+                              kDevTimeoutEmptyTmem);
+            if (!alive) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t a_addr = kv_smem + s * kKvTileBytes;
+                const uint32_t b_addr = q_smem + qs * L::kQBytes;
+                const uint32_t d_addr = tmem_base + ts * kN;
+#pragma unroll
+                for (int k = 0; k < kDim / 32; ++k) {
+                    umma_f8f6f4(d_addr, umma_smem_desc_sw128(a_addr + k * 32),
+                                umma_smem_desc_sw128(b_addr + k * 32), idesc, k > 0 ? 1u : 0u);
+                }
+                umma_commit(full_tm + ts * 8);
+            }
+            __syncwarp();
+            advance<NEXT_N>(cur, p.context_lens, p.batch);
+        }
+    } else {
+        // ---------------------------------------------------------------- math warps
+        const int wg = warp >> 2;                   // warpgroup 0 / 1 takes even / odd tiles
+        const int row_in_tile = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        int prev_b = -1, qc = 0, qs = 0;
+        int ctx_row[NEXT_N];
+        bool alive = true;
+        for (int n = 0; n < ntiles && alive; ++n) {
+            if (cur.b != prev_b) {
+                if (prev_b >= 0) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_q + qs * 8);
+                }
+                qs = qc & 1;
+                alive = mbar_wait_warp(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status, kDevTimeoutFullQ);
+                if (!alive) break;
+                prev_b = cur.b;
+                ++qc;
+#pragma unroll
+                for (int i = 0; i < NEXT_N; ++i) ctx_row[i] = __ldg(p.context_lens + cur.b * NEXT_N + i);
+            }
+            if ((n & 1) == wg) {
+                const int s = n % S;
+                const int ts = n % kTmemStages;
+                alive = mbar_wait_warp(full_kv + s * 8, (n / S) & 1, abort_flag, p.status, kDevTimeoutFullKv);
+                if (!alive) break;
+                const float scale = scale_ptr[s * kTile + row_in_tile];
+                alive = mbar_wait_warp(full_tm + ts * 8, (n / kTmemStages) & 1, abort_flag, p.status,
+                                  kDevTimeoutFullTmem);
+                if (!alive) break;
+                tc_fence_after();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_kv + s * 8);   // UMMA retired and scales are in registers
+                const int t = cur.j * kTile + row_in_tile;
+#pragma unroll
+                for (int i = 0; i < NEXT_N; ++i) {
+                    const float4* w4 = reinterpret_cast<const float4*>(w_ptr + qs * kN + i * kHeads);
+                    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t v[32];
+                        tmem_ld_32x32(tmem_base + lane_base + ts * kN + i * kHeads + half * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4) {
+                            const float4 w = w4[half * 8 + (c >> 2)];
+                            acc0 = fmaf(fmaxf(__uint_as_float(v[c + 0]), 0.f), w.x, acc0);
+                            acc1 = fmaf(fmaxf(__uint_as_float(v[c + 1]), 0.f), w.y, acc1);
+                            acc2 = fmaf(fmaxf(__uint_as_float(v[c + 2]), 0.f), w.z, acc2);
+                            acc3 = fmaf(fmaxf(__uint_as_float(v[c + 3]), 0.f), w.w, acc3);
+                        }
+                    }
+                    const float r = ((acc0 + acc1) + (acc2 + acc3)) * scale;
+                    if (t < ctx_row[i])
+                        p.logits[static_cast<int64_t>(cur.b * NEXT_N + i) * p.logits_stride + t] = r;
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_tm + ts * 8);
+            }
+            advance<NEXT_N>(cur, p.context_lens, p.batch);
+        }
+    }
+
+    __syncthreads();
+    if (*abort_flag) abort_drain_sleep();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemStages * kN);
+    }
+}
+
+template <int NEXT_N>
+static int launch(const CUtensorMap& q_map, const CUtensorMap& kv_map, const Params& p, int grid,
+                  cudaStream_t stream) {
+    const int smem = Smem<NEXT_N>::total(p.kv_stages);
+    auto kernel = mqa_logits_fp8_kernel<NEXT_N>;
+    WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kernel<<<grid, kThreads, smem, stream>>>(q_map, kv_map, p);
+    WUDA_CUDA(cudaGetLastError());
+    return WUDA_OK;
+}
+
+}  // namespace mqa
+}  // namespace wuda
+
+extern "C" int wuda_mqa_logits_fp8(const void* q, const void* kv_pages, const float* weights,
+                                   const int32_t* context_lens, const int32_t* block_table,
+                                   float* logits, int batch, int next_n, int num_blocks,
+                                   int entries_per_block, int64_t page_stride_bytes,
+                                   int block_table_stride, int64_t logits_stride,
+                                   int32_t* status_word, void* stream) {
+    using namespace wuda;
+    using namespace wuda::mqa;
+    clear_error();
+    WUDA_REQUIRE(batch >= 0, "batch must be >= 0 (got %d)", batch);
+    if (next_n != 1 && next_n != 2)
+        return fail(WUDA_ERR_UNSUPPORTED, "next_n must be 1 or 2 (got %d)", next_n);
+    WUDA_REQUIRE(entries_per_block == 32 || entries_per_block == 64 || entries_per_block == 128,
+                 "entries_per_block must be 32, 64 or 128 (got %d)", entries_per_block);
+    WUDA_REQUIRE(page_stride_bytes >= static_cast<int64_t>(entries_per_block) * (kDim + 4) &&
+                     page_stride_bytes % 16 == 0,
+                 "page_stride_bytes must be a multiple of 16 and >= entries_per_block * 132 (got %lld)",
+                 static_cast<long long>(page_stride_bytes));
+    WUDA_REQUIRE(num_blocks >= 1, "num_blocks must be >= 1 (got %d)", num_blocks);
+    WUDA_REQUIRE(block_table_stride >= 1, "block_table_stride must be >= 1 (got %d)", block_table_stride);
+    WUDA_REQUIRE(logits_stride >= 1, "logits_stride must be >= 1");
+    if (batch == 0) return WUDA_OK;
+    WUDA_REQUIRE(q && kv_pages && weights && context_lens && block_table && logits,
+                 "q, kv_pages, weights, context_lens, block_table and logits must not be NULL");
+    WUDA_REQUIRE(aligned16(q) && aligned16(kv_pages) && aligned16(weights),
+                 "q, kv_pages and weights must be 16-byte aligned");
+    WUDA_REQUIRE(static_cast<int64_t>(batch) * next_n * kHeads < (1ll << 31), "batch too large");
+
+    DeviceInfo dev;
+    int st = current_device_info(&dev);
+    if (st != WUDA_OK) return st;
+
+    const int kN = next_n * kHeads;
+    CUtensorMap q_map, kv_map;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(kDim), static_cast<uint64_t>(batch) * kN};
+        const uint64_t strides[1] = {static_cast<uint64_t>(kDim)};
+        const uint32_t box[2] = {static_cast<uint32_t>(kDim), static_cast<uint32_t>(kN)};
+        st = encode_tensor_map(&q_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, q, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+        if (st != WUDA_OK) return st;
+    }
+    {
+        const uint64_t dims[3] = {static_cast<uint64_t>(kDim), static_cast<uint64_t>(entries_per_block),
+                                  static_cast<uint64_t>(num_blocks)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(kDim), static_cast<uint64_t>(page_stride_bytes)};
+        const uint32_t box[3] = {static_cast<uint32_t>(kDim), static_cast<uint32_t>(entries_per_block), 1u};
+        st = encode_tensor_map(&kv_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, kv_pages, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (st != WUDA_OK) return st;
+    }
+
+    Params p;
+    p.kv_pages = static_cast<const uint8_t*>(kv_pages);
+    p.weights = weights;
+    p.context_lens = context_lens;
+    p.block_table = block_table;
+    p.logits = logits;
+    p.status = status_word;
+    p.page_stride = page_stride_bytes;
+    p.logits_stride = logits_stride;
+    p.batch = batch;
+    p.num_blocks = num_blocks;
+    p.epb = entries_per_block;
+    p.bt_stride = block_table_stride;
+    // As many key stages as shared memory allows (each stage = 128 tokens = 16.5 KB).
+    int stages = kMaxKvStages;
+    while (stages > 2 && (next_n == 1 ? Smem<1>::total(stages) : Smem<2>::total(stages)) > dev.smem_optin)
+        --stages;
+    p.kv_stages = stages;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (next_n == 1) return launch<1>(q_map, kv_map, p, dev.num_sms, s);
+    return launch<2>(q_map, kv_map, p, dev.num_sms, s);
+}

@@ -1,0 +1,329 @@
+// Exact per-row top-k index selection over fp32 scores, followed by the page-table
+// transform, for sm_100a.
+//
+// Contract (dsv4_megakernel/megakernel/kernels/topk_v2.cu:329-439 and
+// test/test_topk_v2.py:86-135): for each row r the indices of the k largest values of
+// scores[r, 0:seq_len[r]], in no particular order; rows with seq_len <= k give
+// [0..n) followed by -1; page_indices = (page_table[r, i >> bits] << bits) | (i & mask).
+// Equal values are resolved towards the LOWER index, so the selected set is exactly
+// torch.argsort(-scores, stable=True)[:k] — stricter than the reference, which leaves the
+// choice among exact duplicates unspecified.
+//
+// Algorithm: a three-level most-significant-digit radix select on an order-preserving
+// 32-bit key (12 + 12 + 8 bits), one CTA of 1024 threads per row.
+//   pass 1  histogram of the top 12 key bits over the row           (read #1)
+//   pass 2  indices whose digit is above the threshold digit are emitted at once;
+//           those inside the threshold digit are parked in shared memory (read #2)
+//   levels 2 and 3 refine the parked candidates in shared memory; when there are too
+//   many to park (heavily duplicated scores) they re-read the row instead.
+//   If more values equal the final threshold than are still needed, one ordered pass
+//   over the row takes the lowest indices among them.
+// No global scratch memory is used and nothing is allocated.
+#include <cuda_runtime.h>
+
+#include "host.h"
+
+namespace wuda {
+namespace topk {
+
+constexpr int kThreads = 1024;
+constexpr int kWarps = kThreads / 32;
+constexpr int kBins = 4096;
+constexpr int kCandCap = 6144;
+
+struct Params {
+    const float* scores;
+    const int32_t* seq_lens;
+    const int32_t* page_table;
+    int32_t* page_indices;
+    int32_t* raw;
+    int64_t score_stride;
+    int64_t pt_stride;
+    int rows;
+    int k;
+    int page_bits;
+};
+
+__device__ __forceinline__ uint32_t key_of(float x) {
+    uint32_t u = __float_as_uint(x);
+    if (u == 0x80000000u) u = 0u;  // -0 and +0 compare equal
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct Shared {
+    uint32_t hist[kBins];
+    uint32_t cand_key[kCandCap];
+    int32_t cand_idx[kCandCap];
+    uint32_t warp_tot[kWarps];
+    uint32_t warp_excl[kWarps];
+    uint32_t sel_digit, sel_above;
+    uint32_t out_count, cand_count;
+};
+
+// f(index, value) for every element of the row; 16-byte loads when the row allows.
+template <typename F>
+__device__ __forceinline__ void for_each_elem(const float* row, int n, bool vec_ok, F f) {
+    if (vec_ok) {
+        const int n4 = n >> 2;
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        for (int i = threadIdx.x; i < n4; i += kThreads) {
+            const float4 v = row4[i];
+            f(4 * i + 0, v.x);
+            f(4 * i + 1, v.y);
+            f(4 * i + 2, v.z);
+            f(4 * i + 3, v.w);
+        }
+        for (int i = (n4 << 2) + threadIdx.x; i < n; i += kThreads) f(i, row[i]);
+    } else {
+        for (int i = threadIdx.x; i < n; i += kThreads) f(i, row[i]);
+    }
+}
+
+__device__ __forceinline__ void zero_hist(Shared& s, int nbins) {
+    for (int i = threadIdx.x; i < nbins; i += kThreads) s.hist[i] = 0;
+}
+
+// Finds the digit T with  count(digit > T) < need <= count(digit >= T)  and leaves
+// T in s.sel_digit and count(digit > T) in s.sel_above.  Needs 1 <= need <= total.
+__device__ __forceinline__ void find_threshold(Shared& s, int nbins, uint32_t need) {
+    const int per = nbins >= kThreads ? nbins / kThreads : 1;
+    const int lo = threadIdx.x * per;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t local = 0;
+    if (lo < nbins)
+        for (int b = 0; b < per; ++b) local += s.hist[lo + b];
+    // suffix sums: v = sum of `local` over threads >= this one
+    uint32_t v = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_down_sync(0xffffffffu, v, o);
+        if (lane + o < 32) v += t;
+    }
+    if (lane == 0) s.warp_tot[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        const uint32_t mine = s.warp_tot[lane];
+        uint32_t w = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t t = __shfl_down_sync(0xffffffffu, w, o);
+            if (lane + o < 32) w += t;
+        }
+        s.warp_excl[lane] = w - mine;
+    }
+    __syncthreads();
+    uint32_t running = v - local + s.warp_excl[warp];  // count in digits above this thread's range
+    if (lo < nbins) {
+        for (int b = per - 1; b >= 0; --b) {
+            const uint32_t h = s.hist[lo + b];
+            if (running < need && need <= running + h) {
+                s.sel_digit = lo + b;
+                s.sel_above = running;
+            }
+            running += h;
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ void emit(const Params& p, Shared& s, int r, int idx) {
+    const uint32_t pos = atomicAdd(&s.out_count, 1u);
+    if (pos < static_cast<uint32_t>(p.k)) {
+        const int64_t o = static_cast<int64_t>(r) * p.k + pos;
+        if (p.raw) p.raw[o] = idx;
+        if (p.page_table) {
+            const int32_t page = __ldg(p.page_table + static_cast<int64_t>(r) * p.pt_stride + (idx >> p.page_bits));
+            p.page_indices[o] = static_cast<int32_t>((static_cast<uint32_t>(page) << p.page_bits) |
+                                                     static_cast<uint32_t>(idx & ((1 << p.page_bits) - 1)));
+        } else {
+            p.page_indices[o] = idx;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    Shared& s = *reinterpret_cast<Shared*>(smem_raw);
+
+    for (int r = blockIdx.x; r < p.rows; r += gridDim.x) {
+        const float* row = p.scores + static_cast<int64_t>(r) * p.score_stride;
+        int n = p.seq_lens[r];
+        n = n < 0 ? 0 : n;
+        if (static_cast<int64_t>(n) > p.score_stride) n = static_cast<int>(p.score_stride);
+        const int k = p.k;
+
+        if (n <= k) {  // everything is selected: [0..n) then -1
+            for (int i = threadIdx.x; i < k; i += kThreads) {
+                const int64_t o = static_cast<int64_t>(r) * k + i;
+                const int idx = i < n ? i : -1;
+                if (p.raw) p.raw[o] = idx;
+                int32_t out = idx;
+                if (idx >= 0 && p.page_table) {
+                    const int32_t page = __ldg(p.page_table + static_cast<int64_t>(r) * p.pt_stride + (idx >> p.page_bits));
+                    out = static_cast<int32_t>((static_cast<uint32_t>(page) << p.page_bits) |
+                                               static_cast<uint32_t>(idx & ((1 << p.page_bits) - 1)));
+                }
+                p.page_indices[o] = out;
+            }
+            continue;
+        }
+
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
+
+        // ---- level 1: top 12 bits over the whole row
+        zero_hist(s, kBins);
+        if (threadIdx.x == 0) {
+            s.out_count = 0;
+            s.cand_count = 0;
+        }
+        __syncthreads();
+        for_each_elem(row, n, vec_ok, [&](int, float x) { atomicAdd(&s.hist[key_of(x) >> 20], 1u); });
+        __syncthreads();
+        find_threshold(s, kBins, static_cast<uint32_t>(k));
+        const uint32_t d1 = s.sel_digit;
+        const uint32_t need1 = static_cast<uint32_t>(k) - s.sel_above;   // still needed from digit d1
+        const uint32_t c1 = s.hist[d1];
+        const bool parked = c1 <= static_cast<uint32_t>(kCandCap);
+        __syncthreads();
+
+        // ---- pass 2: emit everything above the digit, park the digit's members
+        for_each_elem(row, n, vec_ok, [&](int i, float x) {
+            const uint32_t key = key_of(x);
+            const uint32_t d = key >> 20;
+            if (d > d1) {
+                emit(p, s, r, i);
+            } else if (d == d1 && parked) {
+                const uint32_t slot = atomicAdd(&s.cand_count, 1u);
+                if (slot < static_cast<uint32_t>(kCandCap)) {
+                    s.cand_key[slot] = key;
+                    s.cand_idx[slot] = i;
+                }
+            }
+        });
+        zero_hist(s, kBins);
+        __syncthreads();
+        const int ncand = parked ? static_cast<int>(min(s.cand_count, static_cast<uint32_t>(kCandCap))) : 0;
+
+        // f(index, key) over the members of digit d1
+        auto for_each_member = [&](auto f) {
+            if (parked) {
+                for (int c = threadIdx.x; c < ncand; c += kThreads) f(s.cand_idx[c], s.cand_key[c]);
+            } else {
+                for_each_elem(row, n, vec_ok, [&](int i, float x) {
+                    const uint32_t key = key_of(x);
+                    if ((key >> 20) == d1) f(i, key);
+                });
+            }
+        };
+
+        // ---- level 2: next 12 bits
+        for_each_member([&](int, uint32_t key) { atomicAdd(&s.hist[(key >> 8) & 0xFFFu], 1u); });
+        __syncthreads();
+        find_threshold(s, kBins, need1);
+        const uint32_t d2 = s.sel_digit;
+        const uint32_t need2 = need1 - s.sel_above;
+        __syncthreads();
+        zero_hist(s, 256);
+        __syncthreads();
+
+        // ---- level 3: last 8 bits
+        const uint32_t prefix24 = (d1 << 12) | d2;
+        for_each_member([&](int, uint32_t key) {
+            if ((key >> 8) == prefix24) atomicAdd(&s.hist[key & 0xFFu], 1u);
+        });
+        __syncthreads();
+        find_threshold(s, 256, need2);
+        const uint32_t d3 = s.sel_digit;
+        const uint32_t need3 = need2 - s.sel_above;   // how many values equal to the threshold are taken
+        const uint32_t ceq = s.hist[d3];
+        const uint32_t thr = (prefix24 << 8) | d3;
+        const bool take_all_equal = (ceq == need3);
+        __syncthreads();
+
+        for_each_member([&](int i, uint32_t key) {
+            if (key > thr || (key == thr && take_all_equal)) emit(p, s, r, i);
+        });
+
+        if (!take_all_equal) {
+            // More duplicates of the threshold value than needed: take the lowest indices.
+            const int chunk = (n + kThreads - 1) / kThreads;
+            const int beg = min(n, static_cast<int>(threadIdx.x) * chunk);
+            const int end = min(n, beg + chunk);
+            uint32_t mine = 0;
+            for (int i = beg; i < end; ++i) mine += (key_of(row[i]) == thr);
+            // exclusive prefix over threads
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+            uint32_t v = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += t;
+            }
+            __syncthreads();
+            if (lane == 31) s.warp_tot[warp] = v;
+            __syncthreads();
+            if (warp == 0) {
+                const uint32_t tot = s.warp_tot[lane];
+                uint32_t w = tot;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t t = __shfl_up_sync(0xffffffffu, w, o);
+                    if (lane >= o) w += t;
+                }
+                s.warp_excl[lane] = w - tot;
+            }
+            __syncthreads();
+            uint32_t rank = v - mine + s.warp_excl[warp];
+            for (int i = beg; i < end && rank < need3; ++i) {
+                if (key_of(row[i]) == thr) {
+                    emit(p, s, r, i);
+                    ++rank;
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace topk
+}  // namespace wuda
+
+extern "C" int wuda_topk(const float* scores, const int32_t* seq_lens, const int32_t* page_table,
+                         int32_t* page_indices, int32_t* raw_indices, int rows, int64_t score_stride,
+                         int64_t page_table_stride, int k, int page_size, void* stream) {
+    using namespace wuda;
+    using namespace wuda::topk;
+    clear_error();
+    WUDA_REQUIRE(rows >= 0, "rows must be >= 0 (got %d)", rows);
+    WUDA_REQUIRE(k >= 1, "k must be >= 1 (got %d)", k);
+    WUDA_REQUIRE(page_size >= 1 && (page_size & (page_size - 1)) == 0, "page_size must be a power of two (got %d)",
+                 page_size);
+    WUDA_REQUIRE(score_stride >= 1, "score_stride must be >= 1");
+    if (rows == 0) return WUDA_OK;
+    WUDA_REQUIRE(scores && seq_lens && page_indices, "scores, seq_lens and page_indices must not be NULL");
+    WUDA_REQUIRE(!page_table || page_table_stride >= 1, "page_table_stride must be >= 1");
+
+    DeviceInfo dev;
+    int st = current_device_info(&dev);
+    if (st != WUDA_OK) return st;
+
+    Params p;
+    p.scores = scores;
+    p.seq_lens = seq_lens;
+    p.page_table = page_table;
+    p.page_indices = page_indices;
+    p.raw = raw_indices;
+    p.score_stride = score_stride;
+    p.pt_stride = page_table_stride;
+    p.rows = rows;
+    p.k = k;
+    p.page_bits = 0;
+    while ((1 << p.page_bits) < page_size) ++p.page_bits;
+
+    const int smem = static_cast<int>(sizeof(Shared));
+    WUDA_CUDA(cudaFuncSetAttribute(topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const int grid = rows < dev.num_sms * 2 ? rows : dev.num_sms * 2;
+    topk_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
+    WUDA_CUDA(cudaGetLastError());
+    return WUDA_OK;
+}

@@ -1,0 +1,99 @@
+"""Host-side mirror of the reference's operator interface.
+
+Each function keeps the name, argument order and argument meaning of the PyTorch
+extension function it replaces (dsv4_megakernel/megakernel/kernels/*.cu, one
+PYBIND11_MODULE per file) and forwards to the C ABI.  Arguments are validated the way
+the reference's TORCH_CHECK blocks do and failures raise RuntimeError before anything is
+launched.  Work is enqueued on torch's current CUDA stream.
+"""
+import torch
+
+from . import _lib
+from ._lib import WudaError, check, lib
+
+__all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "device_status_word", "num_sms"]
+
+NUM_INDEX_HEADS = 64
+INDEX_HEAD_DIM = 128
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require(cond, msg):
+    if not cond:
+        raise WudaError(1, msg)
+
+
+def num_sms():
+    n = lib.wuda_num_sms()
+    if n < 0:
+        check(-n)
+    return n
+
+
+def device_status_word(device=None):
+    """A zeroed int32 scalar on the device for the kernels' status reports."""
+    return torch.zeros(1, dtype=torch.int32, device=device or "cuda")
+
+
+def mqa_logits_fp8_decode_out(q, kv_cache, weights, context_lens, block_table, schedule_meta, logits,
+                              kv_entries_per_block=64, kv_block_stride_bytes=0, num_kv_stages=0,
+                              comp_eps=1e-6, *, next_n=1, status_word=None, pdl=False):
+    """Paged FP8 MQA logits written into `logits` (caller-owned, never allocates).
+
+    Mirrors mqa_logits_fp8_decode_out (kernels/mqa_logits_fp8.cu:388-526):
+      q [R,64,128] float8_e4m3fn, kv_cache uint8 [num_blocks, stride] (epb x 128 key
+      bytes then epb fp32 scales per page), weights fp32 [R,64], context_lens int32
+      [B] / [B,1] / [B,next_n], block_table int32 [B,max_pages], logits fp32 [>=R, L].
+    `schedule_meta` and `num_kv_stages` are accepted for signature compatibility and
+    ignored: tiles are scheduled inside the kernel and the stage count follows shared
+    memory.  `next_n` (keyword, default 1 as in the reference) is the number of query
+    rows per request; rows b*next_n .. b*next_n+next_n-1 share block_table[b].
+    Positions t >= context are not written.
+    """
+    _require(q.is_cuda and q.is_contiguous() and q.dtype == torch.float8_e4m3fn and q.dim() == 3
+             and q.size(1) == NUM_INDEX_HEADS and q.size(2) == INDEX_HEAD_DIM,
+             "q must be contiguous CUDA FP8 [R,64,128]")
+    rows = q.size(0)
+    _require(next_n >= 1 and rows % next_n == 0, "rows must be a multiple of next_n")
+    batch = rows // next_n
+    _require(weights.is_cuda and weights.is_contiguous() and weights.dtype == torch.float32
+             and tuple(weights.shape) == (rows, NUM_INDEX_HEADS),
+             "weights must be contiguous CUDA FP32 [R,64]")
+    _require(context_lens.is_cuda and context_lens.is_contiguous() and context_lens.dtype == torch.int32
+             and context_lens.numel() == rows,
+             "context_lens must be contiguous CUDA int32 with one entry per row")
+    _require(block_table.is_cuda and block_table.is_contiguous() and block_table.dtype == torch.int32
+             and block_table.dim() == 2 and block_table.size(0) == batch,
+             "block_table must be contiguous CUDA int32 [B,max_pages]")
+    _require(logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2
+             and logits.size(0) >= rows and logits.stride(1) == 1,
+             "logits must be CUDA FP32 [>=R, L] with unit inner stride")
+    _require(kv_cache.is_cuda and kv_cache.is_contiguous() and kv_cache.dtype == torch.uint8
+             and kv_cache.dim() == 2, "kv_cache must be contiguous CUDA uint8 physical pages")
+    if kv_block_stride_bytes == 0:
+        kv_block_stride_bytes = kv_cache.size(1)
+    _require(kv_cache.size(1) == kv_block_stride_bytes, "invalid FP8 KV page stride")
+    check(lib.wuda_mqa_logits_fp8(
+        q.data_ptr(), kv_cache.data_ptr(), weights.data_ptr(), context_lens.data_ptr(),
+        block_table.data_ptr(), logits.data_ptr(), batch, next_n, kv_cache.size(0),
+        int(kv_entries_per_block), int(kv_block_stride_bytes), block_table.size(1),
+        logits.stride(0), status_word.data_ptr() if status_word is not None else None, _stream()))
+    return logits
+
+
+def fp8_paged_mqa_logits(q, kv_cache, weights, context_lens, block_table, schedule_meta, max_context_len,
+                         kv_entries_per_block=64, status_word=None):
+    """Allocating form with deep_gemm.fp8_paged_mqa_logits' shape conventions as the
+    reference calls it (test/test_mqa_logits_fp4.py:518-522): q [B, next_n, 64, 128],
+    returns fp32 [B*next_n, max_context_len], -inf beyond each row's context."""
+    _require(q.dim() == 4, "q must be [B, next_n, 64, 128]")
+    b, next_n = q.size(0), q.size(1)
+    stride = (max_context_len + 255) // 256 * 256
+    logits = torch.full((b * next_n, stride), float("-inf"), dtype=torch.float32, device=q.device)
+    mqa_logits_fp8_decode_out(q.reshape(b * next_n, q.size(2), q.size(3)), kv_cache, weights,
+                              context_lens, block_table, schedule_meta, logits, kv_entries_per_block,
+                              next_n=next_n, status_word=status_word)
+    return logits[:, :max_context_len]
