@@ -1,0 +1,288 @@
+"""Benchmark of the indexer step: paged FP8 MQA logits + top-2048 selection.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): batch 64 x next_n 2 = 128 query rows, 64 heads x 128 dims, FP8 e4m3
+queries and keys, key pages of 64 tokens with per-token fp32 scales, context lengths
+uniform in [16384, 65536], block table = a random permutation of the physical pages,
+then the indices of the 2048 largest logits per row mapped through the block table.
+Seeded synthetic data generated on the host.  With N > 1 every rank runs its own batch
+of 64 requests (requests are independent: no collective on the data path, weak scaling).
+
+A step is one MQA-logits launch plus one top-k launch.  `value` is the algorithmic bytes
+of one step (keys and scales read once per request, fp32 logits written once and read
+once, q/weights/indices) divided by the device time of the step, inputs resident in HBM.
+`e2e` is the same number through the host-buffer C-ABI call, host<->device copies
+included.  `--impl reference` times the CPU oracle (the reference ships no CPU
+implementation of this path) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCH, NEXT_N, CTX_LO, CTX_HI, EPB, TOPK = 64, 2, 16384, 65536, 64, 2048
+SEED = 0xB201
+SAMPLE_REQUESTS = 8          # requests of the workload the CPU legs run
+WORKLOAD = "paged MQA logits fp8 + top-2048: batch 64 x next_n 2, 64 heads x 128, page 64, ctx U[16384,65536]"
+METRIC = "MQA-logits + top-k HBM GB/s"
+
+
+def step_bytes(case):
+    from wuda_b200 import workloads
+    rows = case["batch"] * case["next_n"]
+    mqa = workloads.mqa_algorithmic_bytes(case)
+    topk = int(case["context_lens"].sum()) * 4 + rows * TOPK * 4
+    return mqa, topk
+
+
+def measured_hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    clk, clk_max, power = float(f[1]), float(f[2]), float(f[3])
+                except ValueError:
+                    continue
+                if power < 250.0:      # idle sample taken before the load started
+                    continue
+                sm.append(clk)
+                mx.append(clk_max)
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def cpu_sample(case):
+    """The first SAMPLE_REQUESTS requests of the workload as a self-contained case."""
+    n = min(SAMPLE_REQUESTS, case["batch"])
+    rows = n * case["next_n"]
+    sub = dict(case)
+    sub.update(batch=n, q=case["q"][:rows], weights=case["weights"][:rows], context_lens=case["context_lens"][:n],
+               block_table=case["block_table"][:n], ctx=case["ctx"][:n])
+    return sub
+
+
+def cpu_step(sub):
+    import oracle
+    logits = oracle.mqa_logits_fp8(sub["q"], sub["kv_pages"], sub["weights"], sub["context_lens"],
+                                   sub["block_table"], sub["next_n"], sub["epb"], sub["logits_stride"])
+    pt = np.repeat(sub["block_table"], sub["next_n"], axis=0)
+    oracle.topk(logits, sub["context_lens"].reshape(-1), pt, TOPK, sub["epb"])
+
+
+def time_cpu(sub, steps, warmup):
+    import oracle
+    for _ in range(warmup):
+        cpu_step(sub)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(sub)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    mqa_b, topk_b = step_bytes(sub)
+    return (mqa_b + topk_b) / dt / 1e9, dt, oracle.num_threads()
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    from wuda_b200 import workloads
+    case = workloads.make_mqa_case(SAMPLE_REQUESTS, NEXT_N, CTX_LO, CTX_HI, epb=EPB, seed=SEED)
+    gbs, dt, cores = time_cpu(case, args.steps, min(args.warmup, 1))
+    sample = "first %d of 64 requests (same seed), every step" % SAMPLE_REQUESTS
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="wuda_b200", choices=["wuda_b200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import wuda_b200 as wuda
+    from wuda_b200 import workloads
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # every rank owns a batch of its own: request-level data parallelism, no exchange
+    case = workloads.make_mqa_case(BATCH, NEXT_N, CTX_LO, CTX_HI, epb=EPB, seed=SEED + rank)
+    rows = BATCH * NEXT_N
+    d = workloads.to_device(case)
+    logits = torch.empty((rows, case["logits_stride"]), dtype=torch.float32, device="cuda")
+    indices = torch.empty((rows, TOPK), dtype=torch.int32, device="cuda")
+    seq_lens = d["context_lens"].reshape(-1).contiguous()
+    status = wuda.device_status_word()
+
+    def step():
+        wuda.mqa_logits_fp8_decode_out(d["q"], d["kv_pages"], d["weights"], d["context_lens"], d["block_table"],
+                                       None, logits, EPB, next_n=NEXT_N, status_word=status)
+        mid.record()
+        wuda.topk_v2_transform(logits, seq_lens, d["block_table"], indices, EPB, rows_per_table_row=NEXT_N)
+
+    mid = torch.cuda.Event(enable_timing=True)
+    # The sampler runs from here to the end of the timed region: the GPU is under the
+    # same load throughout (the timed region alone is shorter than nvidia-smi's period).
+    sampler = ClockSampler(local_rank)
+    # bring the clocks up from idle before anything is measured
+    t_end = time.perf_counter() + 1.0
+    while time.perf_counter() < t_end:
+        step()
+        torch.cuda.synchronize()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps):
+        ev[i][0].record()
+        mid = ev[i][1]
+        step()
+        ev[i][2].record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = ev[0][0].elapsed_time(ev[-1][2])
+    mqa_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    topk_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    assert int(status.item()) == 0, "device status %d" % int(status.item())
+
+    t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    mqa_b, topk_b = step_bytes(case)
+    value = world * (mqa_b + topk_b) / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the host-buffer C-ABI call (pinned host inputs, results on the host)
+    host = {k: torch.from_numpy(case[k]).pin_memory() for k in ("q", "kv_pages", "weights", "context_lens", "block_table")}
+    out_host = torch.empty((rows, TOPK), dtype=torch.int32).pin_memory()
+    plan = wuda.IndexerHostPlan(BATCH, NEXT_N, case["num_blocks"], EPB, case["page_stride"],
+                                case["block_table"].shape[1], case["logits_stride"], TOPK)
+
+    def e2e_step():
+        plan.run(host["q"], host["kv_pages"], host["weights"], host["context_lens"], host["block_table"], out_host, BATCH)
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = torch.tensor([(time.perf_counter() - t0) / args.e2e_steps], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_s = float(e2e_s.item())
+    h2d = sum(int(v.numel() * v.element_size()) for v in host.values())
+    d2h = int(out_host.numel() * 4) + 4
+    same = np.array_equal(np.sort(out_host.numpy(), axis=1), np.sort(indices.cpu().numpy(), axis=1))
+    plan.close()
+
+    if rank == 0:
+        peak, peak_kind = measured_hbm_peak()
+        achieved = mqa_b / (mqa_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "l2": "inputs (%.0f MB of key pages per rank) larger than the 126 MB L2; "
+                       "no flush between iterations" % (case["kv_pages"].nbytes / 1e6),
+                       "parallelism": "request-dp%d" % world, "rows_per_s": world * rows / (ms_per_step * 1e-3)},
+            "kernels_us": {"mqa_logits_fp8": mqa_ms * 1e3, "topk": topk_ms * 1e3},
+            "roofline": {"kernel": "mqa_logits_fp8_kernel<2>", "bound": "hbm", "achieved": achieved, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "algorithmic_bytes": mqa_b},
+            "e2e": {"value": world * (mqa_b + topk_b) / e2e_s / 1e9, "unit": "GB/s", "ms_per_step": e2e_s * 1e3,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "matches_device_path": bool(same)},
+            "gpu_launches": 2 * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1:
+            gbs, dt, cores = time_cpu(cpu_sample(case), 3, 1)
+            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                                    "sample": "first %d of 64 requests, 3 timed passes of the C oracle "
+                                              "(OpenMP), %.2f s each" % (SAMPLE_REQUESTS, dt)}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

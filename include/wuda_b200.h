@@ -90,6 +90,56 @@ int wuda_mqa_logits_fp8(const void* q, const void* kv_pages, const float* weight
                         int64_t page_stride_bytes, int block_table_stride, int64_t logits_stride,
                         int32_t* status_word, void* stream);
 
+/* ------------------------------------------------------------------------------------
+ * Top-k index selection over the logits, then the page-table transform.
+ *
+ * For each row r: the indices of the k largest values of scores[r, 0 : seq_lens[r]],
+ * in no particular order; equal values are resolved towards the lower index, so the
+ * selected SET equals argsort(-scores, stable)[:k].  Rows with seq_lens[r] <= k yield
+ * 0, 1, .., n-1 followed by -1.  Each selected index i is written as
+ *     page_indices[r, j] = (page_table[r, i / page_size] * page_size) | (i % page_size)
+ * (page_size a power of two; -1 stays -1); with page_table == NULL the raw index is
+ * written.  raw_indices (nullable) receives the untransformed indices.
+ *
+ * Stands in for topk_v2 / topk_v2_transform (kernels/topk_v2.cu:329-439); the
+ * reference's `metadata` plan tensor has no counterpart (no plan kernel is needed).
+ *
+ *   scores       fp32  [rows, score_stride]
+ *   seq_lens     int32 [rows]
+ *   page_table   int32 [rows / rows_per_table_row, page_table_stride], nullable; row r
+ *                uses table row r / rows_per_table_row (1 = one table row per score
+ *                row, as in the reference; next_n when the next_n rows of a request
+ *                share the request's block table)
+ *   page_indices int32 [rows, k];  raw_indices int32 [rows, k], nullable
+ */
+int wuda_topk(const float* scores, const int32_t* seq_lens, const int32_t* page_table,
+              int32_t* page_indices, int32_t* raw_indices, int rows, int64_t score_stride,
+              int64_t page_table_stride, int rows_per_table_row, int k, int page_size,
+              void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Host-buffer form of the indexer step: paged MQA logits, then top-k with the request's
+ * block table as the page table (page_size = entries_per_block).
+ *
+ * The reference has no host-buffer call; this is the form a host program uses when its
+ * tensors live in host memory (the reference's decode_step keeps them on the device,
+ * test/test_e2e_decode.py:537-660).  A plan owns device staging buffers sized for
+ * max_batch requests; wuda_indexer_topk_host copies the *_host inputs to the device on
+ * `stream`, runs both kernels, copies page_indices [batch*next_n, k] (and the logits
+ * [batch*next_n, logits_stride] when logits_host != NULL) back, and synchronises the
+ * stream.  Host buffers should be page-locked for full copy bandwidth.  A non-zero
+ * device status is returned as WUDA_ERR_DEVICE_STATUS.
+ */
+typedef struct wuda_indexer_plan wuda_indexer_plan;
+int wuda_indexer_plan_create(wuda_indexer_plan** plan, int max_batch, int next_n, int num_blocks,
+                             int entries_per_block, int64_t page_stride_bytes,
+                             int block_table_stride, int64_t logits_stride, int k);
+int wuda_indexer_plan_destroy(wuda_indexer_plan* plan);
+int wuda_indexer_topk_host(wuda_indexer_plan* plan, const void* q_host, const void* kv_pages_host,
+                           const float* weights_host, const int32_t* context_lens_host,
+                           const int32_t* block_table_host, int32_t* page_indices_host,
+                           float* logits_host, int batch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

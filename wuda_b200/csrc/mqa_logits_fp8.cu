@@ -27,6 +27,17 @@
 namespace wuda {
 namespace mqa {
 
+#ifndef WUDA_STYLE_PROD
+#define WUDA_STYLE_PROD 1
+#endif
+#ifndef WUDA_STYLE_MMA
+#define WUDA_STYLE_MMA 1
+#endif
+#ifndef WUDA_STYLE_MATH
+#define WUDA_STYLE_MATH 1
+#endif
+
+
 constexpr int kHeads = 64;
 constexpr int kDim = 128;
 constexpr int kTile = 128;          // tokens per work item (UMMA M)
@@ -34,9 +45,11 @@ constexpr int kQStages = 2;
 constexpr int kTmemStages = 4;
 constexpr int kMaxKvStages = 12;
 constexpr int kMathWarps = 8;       // two warpgroups
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kThreads = 320;
+constexpr int kProducerWarp0 = 8;
+constexpr int kProducerWarp1 = 9;
+constexpr int kMmaWarp0 = 10;
+constexpr int kMmaWarp1 = 11;
+constexpr int kThreads = 384;
 constexpr int kKvTileBytes = kTile * kDim;      // 16 KB
 constexpr int kScaleTileBytes = kTile * 4;      // 512 B
 
@@ -156,10 +169,29 @@ __device__ __forceinline__ void advance(TileCursor& c, const int32_t* ctx, int b
     } while (c.tiles_b == 0);
 }
 
+// Ring position that advances without integer division.
+struct Ring {
+    int idx = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void step(int n, int size) {
+        idx += n;
+        while (idx >= size) {
+            idx -= size;
+            phase ^= 1u;
+        }
+    }
+};
+
+template <int NEXT_N>
+__device__ __forceinline__ void advance_thread(TileCursor& c, const int32_t* ctx, int batch) {
+    advance<NEXT_N>(c, ctx, batch);   // advance() uses no warp-level operations
+}
+
 template <int NEXT_N>
 __global__ void __launch_bounds__(kThreads, 1)
 mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
-                      const __grid_constant__ CUtensorMap kv_map, const Params p) {
+                      const __grid_constant__ CUtensorMap kv_map,
+                      const __grid_constant__ CUtensorMap sf_map, const Params p) {
     using L = Smem<NEXT_N>;
     constexpr int kN = L::kN;
     extern __shared__ uint8_t smem_raw[];
@@ -188,11 +220,11 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
         *abort_flag = 0;
         for (int i = 0; i < kQStages; ++i) {
             mbar_init(full_q + i * 8, 1);
-            mbar_init(empty_q + i * 8, 1 + kMathWarps);
+            mbar_init(empty_q + i * 8, 2 + kMathWarps);   // two UMMA issuers + eight math warps
         }
         for (int i = 0; i < S; ++i) {
             mbar_init(full_kv + i * 8, 1);
-            mbar_init(empty_kv + i * 8, 4);
+            mbar_init(empty_kv + i * 8, 4);   // the four math warps that consume the stage
         }
         for (int i = 0; i < kTmemStages; ++i) {
             mbar_init(full_tm + i * 8, 1);
@@ -200,13 +232,14 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
         }
         fence_mbar_init();
     }
-    if (warp == kMmaWarp) {
+    if (warp == kMmaWarp0) {
         tmem_alloc(smem_u32(tmem_slot), kTmemStages * kN);
         tmem_relinquish();
     }
-    if (warp == kProducerWarp && lane == 0) {
+    if (warp == kProducerWarp0 && lane == 0) {
         prefetch_tmap(&q_map);
         prefetch_tmap(&kv_map);
+        prefetch_tmap(&sf_map);
     }
     tc_fence_before();
     __syncthreads();
@@ -216,106 +249,134 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
     TileCursor cur = make_cursor<NEXT_N>(p.context_lens, p.batch);
     const int ntiles = cur.count;
 
-    if (warp == kProducerWarp) {
-        // ---------------------------------------------------------------- TMA producer
+    if (warp == kProducerWarp0 || warp == kProducerWarp1) {
+        // ------------------------------------------------------------ TMA producers
+        // Starting an asynchronous copy occupies the issuing thread for a few hundred
+        // cycles, more than a tile's share of HBM time if one thread started them all.
+        // So two warps alternate tiles, and each tile's copies (key bytes and scales of
+        // every page) go out as ONE tensor-copy instruction with one lane per copy.
+        const int me = warp - kProducerWarp0;            // takes tiles n with n % 2 == me
         const uint64_t stream_policy = policy_evict_first();
-        const int ppt = kTile / p.epb;                    // pages per tile: 4, 2 or 1
+        const int ppt = kTile / p.epb;                   // pages per tile: 4, 2 or 1
         const uint32_t page_bytes = p.epb * kDim;
         const uint32_t page_scale_bytes = p.epb * 4;
+        const int pg = static_cast<int>(lane) % ppt;     // this lane's page inside the tile
+        const bool is_scale = static_cast<int>(lane) >= ppt;
+        const bool copier = static_cast<int>(lane) < 2 * ppt;
+        const void* my_map = is_scale ? static_cast<const void*>(&sf_map) : static_cast<const void*>(&kv_map);
+        const uint32_t my_dst_off = is_scale ? pg * page_scale_bytes : pg * page_bytes;
+        const uint32_t my_dst_base = is_scale ? scale_smem : kv_smem;
+        const uint32_t my_stage_bytes = is_scale ? kScaleTileBytes : kKvTileBytes;
         int prev_b = -1, qc = 0;
-        int win_b = -1, win_base = 0, win_val = 0;        // 32 cached block-table entries
+        // block-table window: 32 entries in use, the next 32 already requested
+        int win_b = -1, win_base = 0, win_val = -1, nxt_val = -1;
+        Ring ring;
         bool alive = true;
         for (int n = 0; n < ntiles && alive; ++n) {
             if (cur.b != prev_b) {
-                const int qs = qc & 1;
-                alive = mbar_wait_warp(empty_q + qs * 8, ((qc >> 1) & 1) ^ 1, abort_flag, p.status,
-                                  kDevTimeoutEmptyQ);
-                if (!alive) break;
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(full_q + qs * 8, L::kQBytes + L::kWBytes);
-                    tma_load_2d(q_smem + qs * L::kQBytes, &q_map, full_q + qs * 8, 0, cur.b * kN);
-                    bulk_load(w_smem + qs * L::kWBytes, p.weights + static_cast<int64_t>(cur.b) * kN,
-                              L::kWBytes, full_q + qs * 8);
+                if (me == 0) {
+                    const int qs = qc & 1;
+                    alive = mbar_wait_lane0<WUDA_STYLE_PROD>(empty_q + qs * 8, ((qc >> 1) & 1) ^ 1, abort_flag, p.status,
+                                            kDevTimeoutEmptyQ);
+                    if (!alive) break;
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(full_q + qs * 8, L::kQBytes + L::kWBytes);
+                        tma_load_2d(q_smem + qs * L::kQBytes, &q_map, full_q + qs * 8, 0, cur.b * kN);
+                        bulk_load(w_smem + qs * L::kWBytes, p.weights + static_cast<int64_t>(cur.b) * kN,
+                                  L::kWBytes, full_q + qs * 8);
+                    }
                 }
                 prev_b = cur.b;
                 ++qc;
             }
-            const int s = n % S;
-            alive = mbar_wait_warp(empty_kv + s * 8, ((n / S) & 1) ^ 1, abort_flag, p.status,
-                              kDevTimeoutEmptyKv);
-            if (!alive) break;
-            const int pages_b = (cur.ctx_b + p.epb - 1) / p.epb;
-            const int first_page = cur.j * ppt;
-            const int valid = min(ppt, pages_b - first_page);
-            if (win_b != cur.b || first_page < win_base || first_page + valid > win_base + 32) {
-                win_b = cur.b;
-                win_base = first_page;
-                const int pg = win_base + lane;
-                win_val = (pg < pages_b && pg < p.bt_stride)
-                              ? __ldg(p.block_table + static_cast<int64_t>(cur.b) * p.bt_stride + pg)
-                              : -1;
-            }
-            if (lane == 0)
-                mbar_arrive_expect_tx(full_kv + s * 8, valid * (page_bytes + page_scale_bytes));
-            for (int pg = 0; pg < valid; ++pg) {
-                int phys = __shfl_sync(0xffffffffu, win_val, first_page + pg - win_base);
-                if (lane == 0) {
-                    if (phys < 0 || phys >= p.num_blocks) {
-                        if (p.status) atomicCAS(p.status, 0, kDevBadPageIndex);
-                        phys = 0;
-                    }
-                    tma_load_3d_hint(kv_smem + s * kKvTileBytes + pg * page_bytes, &kv_map,
-                                     full_kv + s * 8, 0, 0, phys, stream_policy);
-                    bulk_load(scale_smem + s * kScaleTileBytes + pg * page_scale_bytes,
-                              p.kv_pages + static_cast<int64_t>(phys) * p.page_stride + page_bytes,
-                              page_scale_bytes, full_kv + s * 8);
+            if ((n & 1) == me) {
+                const int pages_b = (cur.ctx_b + p.epb - 1) / p.epb;
+                const int first_page = cur.j * ppt;
+                const int valid = min(ppt, pages_b - first_page);
+                const int64_t bt_row = static_cast<int64_t>(cur.b) * p.bt_stride;
+                if (win_b != cur.b || first_page < win_base || first_page >= win_base + 64) {
+                    win_b = cur.b;                         // cold start of a window pair
+                    win_base = first_page;
+                    const int e0 = win_base + lane, e1 = e0 + 32;
+                    win_val = (e0 < pages_b && e0 < p.bt_stride) ? __ldg(p.block_table + bt_row + e0) : -1;
+                    nxt_val = (e1 < pages_b && e1 < p.bt_stride) ? __ldg(p.block_table + bt_row + e1) : -1;
+                } else if (first_page >= win_base + 32) {  // slide: the prefetched half becomes current
+                    win_base += 32;
+                    win_val = nxt_val;
+                    const int e1 = win_base + 32 + lane;
+                    nxt_val = (e1 < pages_b && e1 < p.bt_stride) ? __ldg(p.block_table + bt_row + e1) : -1;
                 }
+                int phys = __shfl_sync(0xffffffffu, win_val, (first_page + pg - win_base) & 31);
+                const bool mine = copier && pg < valid;
+                if (mine && (phys < 0 || phys >= p.num_blocks)) {
+                    if (p.status) atomicCAS(p.status, 0, kDevBadPageIndex);
+                    phys = 0;
+                }
+                const int s = ring.idx;
+                alive = mbar_wait_lane0<WUDA_STYLE_PROD>(empty_kv + s * 8, ring.phase ^ 1u, abort_flag, p.status,
+                                        kDevTimeoutEmptyKv);
+                if (!alive) break;
+                if (lane == 0)
+                    mbar_arrive_expect_tx(full_kv + s * 8, valid * (page_bytes + page_scale_bytes));
+                __syncwarp();
+                if (mine)
+                    tma_load_3d_hint(my_dst_base + s * my_stage_bytes + my_dst_off, my_map, full_kv + s * 8,
+                                     0, 0, phys, stream_policy);
             }
+            ring.step(1, S);
             advance<NEXT_N>(cur, p.context_lens, p.batch);
         }
-    } else if (warp == kMmaWarp) {
-        // ---------------------------------------------------------------- UMMA issuer
-        constexpr uint32_t idesc = umma_idesc(kTile, kN, 0, 0);
-        int prev_b = -1, qc = 0, qs = 0;
-        bool alive = true;
-        for (int n = 0; n < ntiles && alive; ++n) {
-            if (cur.b != prev_b) {
-                if (prev_b >= 0 && lane == 0) umma_commit(empty_q + qs * 8);  // q stage free once its MMAs retire
-                qs = qc & 1;
-                alive = mbar_wait_warp(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status, kDevTimeoutFullQ);
-                if (!alive) break;
-                prev_b = cur.b;
-                ++qc;
-            }
-            const int s = n % S;
-            const int ts = n % kTmemStages;
-            alive = mbar_wait_warp(full_kv + s * 8, (n / S) & 1, abort_flag, p.status, kDevTimeoutFullKv);
-            if (!alive) break;
-            alive = mbar_wait_warp(empty_tm + ts * 8, ((n / kTmemStages) & 1) ^ 1, abort_flag, p.status,
-                              kDevTimeoutEmptyTmem);
-            if (!alive) break;
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t a_addr = kv_smem + s * kKvTileBytes;
-                const uint32_t b_addr = q_smem + qs * L::kQBytes;
-                const uint32_t d_addr = tmem_base + ts * kN;
-#pragma unroll
-                for (int k = 0; k < kDim / 32; ++k) {
-                    umma_f8f6f4(d_addr, umma_smem_desc_sw128(a_addr + k * 32),
-                                umma_smem_desc_sw128(b_addr + k * 32), idesc, k > 0 ? 1u : 0u);
+    } else if (warp == kMmaWarp0 || warp == kMmaWarp1) {
+        // ------------------------------------------------------------ UMMA issuers
+        // One thread per warp runs the whole loop (the other lanes go straight to the
+        // final barrier, so no warp-level synchronisation sits between UMMAs).  Two
+        // issuers alternate tiles: while one is held at the tensor pipe's queue, the
+        // other does its waits and bookkeeping, which keeps the pipe fed.
+        if (lane == 0) {
+            const int me = warp - kMmaWarp0;             // takes tiles n with n % 2 == me
+            constexpr uint32_t idesc = umma_idesc(kTile, kN, 0, 0);
+            int prev_b = -1, qc = 0, qs = 0;
+            Ring ring, tring;
+            for (int n = 0; n < ntiles; ++n) {
+                if (cur.b != prev_b) {
+                    if (prev_b >= 0) umma_commit(empty_q + qs * 8);  // this issuer's UMMAs on the old q stage retired
+                    qs = qc & 1;
+                    if (!mbar_wait<WUDA_STYLE_MMA>(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status, kDevTimeoutFullQ))
+                        break;
+                    prev_b = cur.b;
+                    ++qc;
                 }
-                umma_commit(full_tm + ts * 8);
+                if ((n & 1) == me) {
+                    const int s = ring.idx, ts = tring.idx;
+                    if (!mbar_wait<WUDA_STYLE_MMA>(full_kv + s * 8, ring.phase, abort_flag, p.status, kDevTimeoutFullKv))
+                        break;
+                    if (!mbar_wait<WUDA_STYLE_MMA>(empty_tm + ts * 8, tring.phase ^ 1u, abort_flag, p.status,
+                                                   kDevTimeoutEmptyTmem))
+                        break;
+                    tc_fence_after();
+                    const uint32_t a_addr = kv_smem + s * kKvTileBytes;
+                    const uint32_t b_addr = q_smem + qs * L::kQBytes;
+                    const uint32_t d_addr = tmem_base + ts * kN;
+#pragma unroll
+                    for (int k = 0; k < kDim / 32; ++k) {
+                        umma_f8f6f4(d_addr, umma_smem_desc_sw128(a_addr + k * 32),
+                                    umma_smem_desc_sw128(b_addr + k * 32), idesc, k > 0 ? 1u : 0u);
+                    }
+                    umma_commit(full_tm + ts * 8);
+                }
+                ring.step(1, S);
+                tring.step(1, kTmemStages);
+                advance_thread<NEXT_N>(cur, p.context_lens, p.batch);
             }
-            __syncwarp();
-            advance<NEXT_N>(cur, p.context_lens, p.batch);
         }
     } else {
-        // ---------------------------------------------------------------- math warps
+        // ------------------------------------------------------------ math warps
         const int wg = warp >> 2;                   // warpgroup 0 / 1 takes even / odd tiles
         const int row_in_tile = (warp & 3) * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         int prev_b = -1, qc = 0, qs = 0;
         int ctx_row[NEXT_N];
+        Ring ring, tring;
         bool alive = true;
         for (int n = 0; n < ntiles && alive; ++n) {
             if (cur.b != prev_b) {
@@ -324,7 +385,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
                     if (lane == 0) mbar_arrive(empty_q + qs * 8);
                 }
                 qs = qc & 1;
-                alive = mbar_wait_warp(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status, kDevTimeoutFullQ);
+                alive = mbar_wait_lane0<WUDA_STYLE_MATH>(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status, kDevTimeoutFullQ);
                 if (!alive) break;
                 prev_b = cur.b;
                 ++qc;
@@ -332,17 +393,14 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
                 for (int i = 0; i < NEXT_N; ++i) ctx_row[i] = __ldg(p.context_lens + cur.b * NEXT_N + i);
             }
             if ((n & 1) == wg) {
-                const int s = n % S;
-                const int ts = n % kTmemStages;
-                alive = mbar_wait_warp(full_kv + s * 8, (n / S) & 1, abort_flag, p.status, kDevTimeoutFullKv);
+                const int s = ring.idx, ts = tring.idx;
+                alive = mbar_wait_lane0<WUDA_STYLE_MATH>(full_kv + s * 8, ring.phase, abort_flag, p.status, kDevTimeoutFullKv);
                 if (!alive) break;
                 const float scale = scale_ptr[s * kTile + row_in_tile];
-                alive = mbar_wait_warp(full_tm + ts * 8, (n / kTmemStages) & 1, abort_flag, p.status,
-                                  kDevTimeoutFullTmem);
+                alive = mbar_wait_lane0<WUDA_STYLE_MATH>(full_tm + ts * 8, tring.phase, abort_flag, p.status, kDevTimeoutFullTmem);
                 if (!alive) break;
                 tc_fence_after();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty_kv + s * 8);   // UMMA retired and scales are in registers
+                if (lane == 0) mbar_arrive(empty_kv + s * 8);   // UMMAs retired, scales in registers
                 const int t = cur.j * kTile + row_in_tile;
 #pragma unroll
                 for (int i = 0; i < NEXT_N; ++i) {
@@ -370,6 +428,8 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_tm + ts * 8);
             }
+            ring.step(1, S);
+            tring.step(1, kTmemStages);
             advance<NEXT_N>(cur, p.context_lens, p.batch);
         }
     }
@@ -377,19 +437,19 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
     __syncthreads();
     if (*abort_flag) abort_drain_sleep();
     __syncthreads();
-    if (warp == kMmaWarp) {
+    if (warp == kMmaWarp0) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemStages * kN);
     }
 }
 
 template <int NEXT_N>
-static int launch(const CUtensorMap& q_map, const CUtensorMap& kv_map, const Params& p, int grid,
+static int launch(const CUtensorMap& q_map, const CUtensorMap& kv_map, const CUtensorMap& sf_map, const Params& p, int grid,
                   cudaStream_t stream) {
     const int smem = Smem<NEXT_N>::total(p.kv_stages);
     auto kernel = mqa_logits_fp8_kernel<NEXT_N>;
     WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kernel<<<grid, kThreads, smem, stream>>>(q_map, kv_map, p);
+    kernel<<<grid, kThreads, smem, stream>>>(q_map, kv_map, sf_map, p);
     WUDA_CUDA(cudaGetLastError());
     return WUDA_OK;
 }
@@ -430,7 +490,7 @@ extern "C" int wuda_mqa_logits_fp8(const void* q, const void* kv_pages, const fl
     if (st != WUDA_OK) return st;
 
     const int kN = next_n * kHeads;
-    CUtensorMap q_map, kv_map;
+    CUtensorMap q_map, kv_map, sf_map;
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(kDim), static_cast<uint64_t>(batch) * kN};
         const uint64_t strides[1] = {static_cast<uint64_t>(kDim)};
@@ -446,6 +506,16 @@ extern "C" int wuda_mqa_logits_fp8(const void* q, const void* kv_pages, const fl
         const uint32_t box[3] = {static_cast<uint32_t>(kDim), static_cast<uint32_t>(entries_per_block), 1u};
         st = encode_tensor_map(&kv_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, kv_pages, dims, strides, box,
                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (st != WUDA_OK) return st;
+    }
+
+    {   // per-token scales: entries_per_block fp32 after the key bytes of each page
+        const uint64_t dims[3] = {static_cast<uint64_t>(entries_per_block), 1ull, static_cast<uint64_t>(num_blocks)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(page_stride_bytes), static_cast<uint64_t>(page_stride_bytes)};
+        const uint32_t box[3] = {static_cast<uint32_t>(entries_per_block), 1u, 1u};
+        st = encode_tensor_map(&sf_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                               static_cast<const uint8_t*>(kv_pages) + static_cast<int64_t>(entries_per_block) * kDim,
+                               dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE);
         if (st != WUDA_OK) return st;
     }
 
@@ -469,6 +539,6 @@ extern "C" int wuda_mqa_logits_fp8(const void* q, const void* kv_pages, const fl
     p.kv_stages = stages;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (next_n == 1) return launch<1>(q_map, kv_map, p, dev.num_sms, s);
-    return launch<2>(q_map, kv_map, p, dev.num_sms, s);
+    if (next_n == 1) return launch<1>(q_map, kv_map, sf_map, p, dev.num_sms, s);
+    return launch<2>(q_map, kv_map, sf_map, p, dev.num_sms, s);
 }

@@ -11,6 +11,9 @@
 #include <cuda_runtime.h>
 
 namespace wuda {
+#ifdef WUDA_COUNT_POLLS
+__device__ unsigned long long g_polls[64];
+#endif
 
 // ---------------------------------------------------------------- status codes
 // Written (first writer wins) to the int32 status word a kernel is given.
@@ -90,19 +93,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
+#ifdef WUDA_COUNT_POLLS
+    if (blockIdx.x == 0) atomicAdd(&g_polls[(threadIdx.x >> 5) * 2 + (ok ? 0 : 1)], 1ull);
+#endif
     return ok != 0;
 }
 
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by the whole CTA.
 // Returns true when the phase completed, false when the CTA is aborting (either this
-// wait ran out of time or another one did).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status_word, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
+// wait ran out of time or another one did).  The fast path is a bare try_wait loop
+// (the instruction itself suspends the thread for a while); the clock and the abort
+// flag are consulted only after many failed polls, because reading %globaltimer on
+// every wait adds its latency to each producer/consumer hand-off.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int* status_word, int code) {
     const unsigned long long t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 31u) == 0u) {
+        if ((++spins & 63u) == 0u) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > kWaitLimitNs) {
                 *abort_flag = 1;
@@ -113,14 +121,55 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
     return true;
 }
+#ifndef WUDA_SLEEP_NS
+#define WUDA_SLEEP_NS 200
+#endif
+template <int STYLE = 1>
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status_word, int code) {
+    if (STYLE == 0) {
+        if (mbar_try_wait(bar, parity)) return true;
+        return mbar_wait_slow(bar, parity, abort_flag, status_word, code);
+    } else if (STYLE == 3) {   // one poll, one pause, then poll hot
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(WUDA_SLEEP_NS);
+#pragma unroll 1
+        for (uint32_t spins = 0; spins < 4096u; ++spins)
+            if (mbar_try_wait(bar, parity)) return true;
+        return mbar_wait_slow(bar, parity, abort_flag, status_word, code);
+    } else if (STYLE == 4) {   // pause between all polls
+#pragma unroll 1
+        for (uint32_t spins = 0; spins < 4096u; ++spins) {
+            if (mbar_try_wait(bar, parity)) return true;
+            __nanosleep(WUDA_SLEEP_NS);
+        }
+        return mbar_wait_slow(bar, parity, abort_flag, status_word, code);
+    } else {
+#pragma unroll 1
+        for (uint32_t spins = 0; spins < 4096u; ++spins)
+            if (mbar_try_wait(bar, parity)) return true;
+        return mbar_wait_slow(bar, parity, abort_flag, status_word, code);
+    }
+}
 
-// Warp-uniform form: every lane polls, then the warp votes, so that all 32 lanes take
-// the same branch afterwards (callers use full-mask shuffles and __syncwarp).
+// Warp-uniform forms, so that all 32 lanes take the same branch afterwards (callers use
+// full-mask shuffles and __syncwarp).  `_warp`: every lane polls (each lane that later
+// reads data written by the async proxy must observe the barrier itself), then votes.
+// `_lane0`: only lane 0 polls and the result is broadcast.
+template <int STYLE = 1>
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
                                                volatile int* abort_flag, int* status_word,
                                                int code) {
-    const bool ok = mbar_wait(bar, parity, abort_flag, status_word, code);
+    const bool ok = mbar_wait<STYLE>(bar, parity, abort_flag, status_word, code);
     return __all_sync(0xffffffffu, ok);
+}
+template <int STYLE = 1>
+__device__ __forceinline__ bool mbar_wait_lane0(uint32_t bar, uint32_t parity,
+                                                volatile int* abort_flag, int* status_word,
+                                                int code) {
+    int ok = 1;
+    if (lane_id() == 0) ok = mbar_wait<STYLE>(bar, parity, abort_flag, status_word, code) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // Sleep used on the abort path so that copies and MMAs already in flight land before

@@ -42,6 +42,7 @@ struct Params {
     int rows;
     int k;
     int page_bits;
+    int rows_per_table_row;
 };
 
 __device__ __forceinline__ uint32_t key_of(float x) {
@@ -132,7 +133,7 @@ __device__ __forceinline__ void emit(const Params& p, Shared& s, int r, int idx)
         const int64_t o = static_cast<int64_t>(r) * p.k + pos;
         if (p.raw) p.raw[o] = idx;
         if (p.page_table) {
-            const int32_t page = __ldg(p.page_table + static_cast<int64_t>(r) * p.pt_stride + (idx >> p.page_bits));
+            const int32_t page = __ldg(p.page_table + static_cast<int64_t>(r / p.rows_per_table_row) * p.pt_stride + (idx >> p.page_bits));
             p.page_indices[o] = static_cast<int32_t>((static_cast<uint32_t>(page) << p.page_bits) |
                                                      static_cast<uint32_t>(idx & ((1 << p.page_bits) - 1)));
         } else {
@@ -159,7 +160,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
                 if (p.raw) p.raw[o] = idx;
                 int32_t out = idx;
                 if (idx >= 0 && p.page_table) {
-                    const int32_t page = __ldg(p.page_table + static_cast<int64_t>(r) * p.pt_stride + (idx >> p.page_bits));
+                    const int32_t page = __ldg(p.page_table + static_cast<int64_t>(r / p.rows_per_table_row) * p.pt_stride + (idx >> p.page_bits));
                     out = static_cast<int32_t>((static_cast<uint32_t>(page) << p.page_bits) |
                                                static_cast<uint32_t>(idx & ((1 << p.page_bits) - 1)));
                 }
@@ -290,7 +291,8 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
 
 extern "C" int wuda_topk(const float* scores, const int32_t* seq_lens, const int32_t* page_table,
                          int32_t* page_indices, int32_t* raw_indices, int rows, int64_t score_stride,
-                         int64_t page_table_stride, int k, int page_size, void* stream) {
+                         int64_t page_table_stride, int rows_per_table_row, int k, int page_size,
+                         void* stream) {
     using namespace wuda;
     using namespace wuda::topk;
     clear_error();
@@ -299,6 +301,7 @@ extern "C" int wuda_topk(const float* scores, const int32_t* seq_lens, const int
     WUDA_REQUIRE(page_size >= 1 && (page_size & (page_size - 1)) == 0, "page_size must be a power of two (got %d)",
                  page_size);
     WUDA_REQUIRE(score_stride >= 1, "score_stride must be >= 1");
+    WUDA_REQUIRE(rows_per_table_row >= 1, "rows_per_table_row must be >= 1 (got %d)", rows_per_table_row);
     if (rows == 0) return WUDA_OK;
     WUDA_REQUIRE(scores && seq_lens && page_indices, "scores, seq_lens and page_indices must not be NULL");
     WUDA_REQUIRE(!page_table || page_table_stride >= 1, "page_table_stride must be >= 1");
@@ -317,6 +320,7 @@ extern "C" int wuda_topk(const float* scores, const int32_t* seq_lens, const int
     p.pt_stride = page_table_stride;
     p.rows = rows;
     p.k = k;
+    p.rows_per_table_row = rows_per_table_row;
     p.page_bits = 0;
     while ((1 << p.page_bits) < page_size) ++p.page_bits;
 

@@ -11,7 +11,8 @@ import torch
 from . import _lib
 from ._lib import WudaError, check, lib
 
-__all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "device_status_word", "num_sms"]
+__all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
+           "IndexerHostPlan", "device_status_word", "num_sms"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -97,3 +98,78 @@ def fp8_paged_mqa_logits(q, kv_cache, weights, context_lens, block_table, schedu
                               context_lens, block_table, schedule_meta, logits, kv_entries_per_block,
                               next_n=next_n, status_word=status_word)
     return logits[:, :max_context_len]
+
+
+def topk_v2_transform(scores, seq_lens, page_table, page_indices, page_size=64, metadata=None,
+                      raw_indices=None, *, rows_per_table_row=1):
+    """Top-k indices of each row of `scores` written into `page_indices` [rows, k]
+    after the page-table transform (kernels/topk_v2.cu:348-423).  `metadata` (the
+    reference's plan tensor) is accepted and ignored.  Never allocates.
+    `rows_per_table_row` (keyword, default 1 as in the reference) lets the next_n score
+    rows of one request share that request's page-table row."""
+    _require(scores.is_cuda and scores.dtype == torch.float32 and scores.dim() == 2 and scores.stride(1) == 1,
+             "scores must be CUDA FP32 [rows, L] with unit inner stride")
+    rows = scores.size(0)
+    _require(seq_lens.is_cuda and seq_lens.is_contiguous() and seq_lens.dtype == torch.int32
+             and seq_lens.numel() == rows, "seq_lens must be contiguous CUDA int32 [rows]")
+    _require(page_table.is_cuda and page_table.is_contiguous() and page_table.dtype == torch.int32
+             and page_table.dim() == 2 and page_table.size(0) * rows_per_table_row == rows,
+             "page_table must be contiguous CUDA int32 [rows / rows_per_table_row, pages]")
+    _require(page_indices.is_cuda and page_indices.is_contiguous() and page_indices.dtype == torch.int32
+             and page_indices.dim() == 2 and page_indices.size(0) == rows,
+             "page_indices must be contiguous CUDA int32 [rows, k]")
+    k = page_indices.size(1)
+    if raw_indices is not None:
+        _require(raw_indices.is_cuda and raw_indices.is_contiguous() and raw_indices.dtype == torch.int32
+                 and tuple(raw_indices.shape) == (rows, k), "raw_indices must be contiguous CUDA int32 [rows, k]")
+    check(lib.wuda_topk(scores.data_ptr(), seq_lens.data_ptr(), page_table.data_ptr(), page_indices.data_ptr(),
+                        raw_indices.data_ptr() if raw_indices is not None else None, rows, scores.stride(0),
+                        page_table.stride(0), int(rows_per_table_row), k, int(page_size), _stream()))
+    return page_indices
+
+
+def topk_v2(scores, seq_lens, page_table, topk, page_size=64, raw_indices=None, *, rows_per_table_row=1):
+    """Allocating form (kernels/topk_v2.cu:428-439): returns page_indices int32 [rows, topk]."""
+    out = torch.empty((scores.size(0), int(topk)), dtype=torch.int32, device=scores.device)
+    return topk_v2_transform(scores, seq_lens, page_table, out, page_size, None, raw_indices,
+                             rows_per_table_row=rows_per_table_row)
+
+
+class IndexerHostPlan:
+    """Host-buffer indexer step (wuda_indexer_plan_* / wuda_indexer_topk_host): inputs are
+    numpy arrays or CPU torch tensors (page-locked for full copy bandwidth), the result is
+    written into a caller-owned host int32 array [rows, k]."""
+
+    def __init__(self, max_batch, next_n, num_blocks, entries_per_block, page_stride_bytes,
+                 block_table_stride, logits_stride, k):
+        import ctypes
+        self._h = ctypes.c_void_p()
+        check(lib.wuda_indexer_plan_create(ctypes.byref(self._h), max_batch, next_n, num_blocks,
+                                           entries_per_block, page_stride_bytes, block_table_stride,
+                                           logits_stride, k))
+        self.next_n, self.k = next_n, k
+
+    @staticmethod
+    def _ptr(a):
+        if a is None:
+            return None
+        return a.data_ptr() if isinstance(a, torch.Tensor) else a.ctypes.data
+
+    def run(self, q, kv_pages, weights, context_lens, block_table, page_indices_out, batch, logits_out=None,
+            stream=None):
+        check(lib.wuda_indexer_topk_host(self._h, self._ptr(q), self._ptr(kv_pages), self._ptr(weights),
+                                         self._ptr(context_lens), self._ptr(block_table),
+                                         self._ptr(page_indices_out), self._ptr(logits_out), batch,
+                                         _stream() if stream is None else stream))
+        return page_indices_out
+
+    def close(self):
+        if self._h:
+            lib.wuda_indexer_plan_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
