@@ -371,9 +371,14 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
         }
     } else {
         // ------------------------------------------------------------ math warps
-        const int wg = warp >> 2;                   // warpgroup 0 / 1 takes even / odd tiles
+        // Warpgroup g owns tiles n with n % 2 == g.  A thread is one key token: it reads
+        // its accumulator row from TMEM in 32-column chunks (the next chunk is in
+        // flight while the current one is reduced), applies relu, the per-head weight
+        // (packed fp32x2 FMAs) and the token scale, and stores one logit per query row.
+        const int wg = warp >> 2;
         const int row_in_tile = (warp & 3) * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        constexpr int kChunks = kN / 32;              // 32-column chunks per tile
         int prev_b = -1, qc = 0, qs = 0;
         int ctx_row[NEXT_N];
         Ring ring, tring;
@@ -385,7 +390,8 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
                     if (lane == 0) mbar_arrive(empty_q + qs * 8);
                 }
                 qs = qc & 1;
-                alive = mbar_wait_lane0<WUDA_STYLE_MATH>(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status, kDevTimeoutFullQ);
+                alive = mbar_wait_warp_fast<WUDA_STYLE_MATH>(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status,
+                                                             kDevTimeoutFullQ);
                 if (!alive) break;
                 prev_b = cur.b;
                 ++qc;
@@ -394,39 +400,53 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
             }
             if ((n & 1) == wg) {
                 const int s = ring.idx, ts = tring.idx;
-                alive = mbar_wait_lane0<WUDA_STYLE_MATH>(full_kv + s * 8, ring.phase, abort_flag, p.status, kDevTimeoutFullKv);
-                if (!alive) break;
-                const float scale = scale_ptr[s * kTile + row_in_tile];
-                alive = mbar_wait_lane0<WUDA_STYLE_MATH>(full_tm + ts * 8, tring.phase, abort_flag, p.status, kDevTimeoutFullTmem);
+                // full_tm completes after the UMMAs that read key stage s retired, and
+                // those were issued after the stage's copies had landed: one wait covers
+                // the accumulator and the stage's scales.
+                alive = mbar_wait_warp_fast<WUDA_STYLE_MATH>(full_tm + ts * 8, tring.phase, abort_flag, p.status,
+                                                             kDevTimeoutFullTmem);
                 if (!alive) break;
                 tc_fence_after();
-                if (lane == 0) mbar_arrive(empty_kv + s * 8);   // UMMAs retired, scales in registers
+                const uint32_t taddr = tmem_base + lane_base + ts * kN;
+                uint32_t v[2][32];
+                tmem_ld_32x32(taddr, v[0]);
+                const float scale = scale_ptr[s * kTile + row_in_tile];
                 const int t = cur.j * kTile + row_in_tile;
+                float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int i = 0; i < NEXT_N; ++i) {
-                    const float4* w4 = reinterpret_cast<const float4*>(w_ptr + qs * kN + i * kHeads);
-                    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        uint32_t v[32];
-                        tmem_ld_32x32(tmem_base + lane_base + ts * kN + i * kHeads + half * 32, v);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int c = 0; c < 32; c += 4) {
-                            const float4 w = w4[half * 8 + (c >> 2)];
-                            acc0 = fmaf(fmaxf(__uint_as_float(v[c + 0]), 0.f), w.x, acc0);
-                            acc1 = fmaf(fmaxf(__uint_as_float(v[c + 1]), 0.f), w.y, acc1);
-                            acc2 = fmaf(fmaxf(__uint_as_float(v[c + 2]), 0.f), w.z, acc2);
-                            acc3 = fmaf(fmaxf(__uint_as_float(v[c + 3]), 0.f), w.w, acc3);
+                for (int c = 0; c < kChunks; ++c) {
+                    tmem_ld_wait();
+                    if (c + 1 < kChunks) tmem_ld_32x32(taddr + (c + 1) * 32, v[(c + 1) & 1]);
+                    if (c + 1 == kChunks) {
+                        // every accumulator column is in registers, the scale too
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            mbar_arrive(empty_tm + ts * 8);
+                            mbar_arrive(empty_kv + s * 8);
                         }
                     }
-                    const float r = ((acc0 + acc1) + (acc2 + acc3)) * scale;
-                    if (t < ctx_row[i])
-                        p.logits[static_cast<int64_t>(cur.b * NEXT_N + i) * p.logits_stride + t] = r;
+                    const float4* w4 = reinterpret_cast<const float4*>(w_ptr + qs * kN + c * 32);
+                    const uint32_t* x = v[c & 1];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4) {
+                        const float4 w = w4[e >> 2];
+                        acc0 = __ffma2_rn(make_float2(fmaxf(__uint_as_float(x[e + 0]), 0.f),
+                                                      fmaxf(__uint_as_float(x[e + 1]), 0.f)),
+                                          make_float2(w.x, w.y), acc0);
+                        acc1 = __ffma2_rn(make_float2(fmaxf(__uint_as_float(x[e + 2]), 0.f),
+                                                      fmaxf(__uint_as_float(x[e + 3]), 0.f)),
+                                          make_float2(w.z, w.w), acc1);
+                    }
+                    if ((c & 1) == 1) {   // a query row (64 heads = two chunks) is complete
+                        const int i = c >> 1;
+                        const float r = ((acc0.x + acc0.y) + (acc1.x + acc1.y)) * scale;
+                        if (t < ctx_row[i])
+                            p.logits[static_cast<int64_t>(cur.b * NEXT_N + i) * p.logits_stride + t] = r;
+                        acc0 = make_float2(0.f, 0.f);
+                        acc1 = make_float2(0.f, 0.f);
+                    }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty_tm + ts * 8);
             }
             ring.step(1, S);
             tring.step(1, kTmemStages);

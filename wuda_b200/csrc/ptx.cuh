@@ -333,6 +333,17 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
         : "r"(taddr)
         : "memory");
 }
+// Warp-wide wait whose common case (phase already complete) costs one poll and one
+// vote: all lanes test the barrier together; only when that fails does lane 0 take the
+// polling loop and broadcast the outcome.
+template <int STYLE = 1>
+__device__ __forceinline__ bool mbar_wait_warp_fast(uint32_t bar, uint32_t parity,
+                                                    volatile int* abort_flag, int* status_word,
+                                                    int code) {
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    return mbar_wait_lane0<STYLE>(bar, parity, abort_flag, status_word, code);
+}
+
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
