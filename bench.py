@@ -32,7 +32,7 @@ sys.path.insert(0, ROOT)
 BATCH, NEXT_N, CTX_LO, CTX_HI, EPB, TOPK = 64, 2, 16384, 65536, 64, 2048
 SEED = 0xB201
 SAMPLE_REQUESTS = 8          # requests of the workload the CPU legs run
-WORKLOAD = "paged MQA logits fp8 + top-2048: batch 64 x next_n 2, 64 heads x 128, page 64, ctx U[16384,65536]"
+WORKLOAD = "paged MQA logits fp8 + top-2048: batch %d x next_n 2, 64 heads x 128, page 64, ctx U[16384,65536]"
 METRIC = "MQA-logits + top-k HBM GB/s"
 
 
@@ -143,7 +143,7 @@ def run_reference(args, rank):
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
+        "config": {"workload": WORKLOAD % BATCH, "sample": sample},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -156,6 +156,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="wuda_b200", choices=["wuda_b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=BATCH,
+                    help="requests per rank (default 64 = the benchmark workload; smaller values are for profiler captures)")
+    ap.add_argument("--capture", action="store_true",
+                    help="profiler capture mode: no clock pre-warm, no end-to-end leg, no CPU baseline")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -183,8 +187,9 @@ def main():
         torch.cuda.synchronize()
 
     # every rank owns a batch of its own: request-level data parallelism, no exchange
-    case = workloads.make_mqa_case(BATCH, NEXT_N, CTX_LO, CTX_HI, epb=EPB, seed=SEED + rank)
-    rows = BATCH * NEXT_N
+    batch = args.batch
+    case = workloads.make_mqa_case(batch, NEXT_N, CTX_LO, CTX_HI, epb=EPB, seed=SEED + rank)
+    rows = batch * NEXT_N
     d = workloads.to_device(case)
     logits = torch.empty((rows, case["logits_stride"]), dtype=torch.float32, device="cuda")
     indices = torch.empty((rows, TOPK), dtype=torch.int32, device="cuda")
@@ -202,7 +207,7 @@ def main():
     # same load throughout (the timed region alone is shorter than nvidia-smi's period).
     sampler = ClockSampler(local_rank)
     # bring the clocks up from idle before anything is measured
-    t_end = time.perf_counter() + 1.0
+    t_end = time.perf_counter() + (0.0 if args.capture else 1.0)
     while time.perf_counter() < t_end:
         step()
         torch.cuda.synchronize()
@@ -231,14 +236,22 @@ def main():
     mqa_b, topk_b = step_bytes(case)
     value = world * (mqa_b + topk_b) / (ms_per_step * 1e-3) / 1e9
 
+    if args.capture:
+        if rank == 0:
+            print(json.dumps({"capture": True, "batch": batch, "ms_per_step": ms_per_step,
+                              "kernels_us": {"mqa_logits_fp8": mqa_ms * 1e3, "topk": topk_ms * 1e3}}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     # ---- end to end through the host-buffer C-ABI call (pinned host inputs, results on the host)
     host = {k: torch.from_numpy(case[k]).pin_memory() for k in ("q", "kv_pages", "weights", "context_lens", "block_table")}
     out_host = torch.empty((rows, TOPK), dtype=torch.int32).pin_memory()
-    plan = wuda.IndexerHostPlan(BATCH, NEXT_N, case["num_blocks"], EPB, case["page_stride"],
+    plan = wuda.IndexerHostPlan(batch, NEXT_N, case["num_blocks"], EPB, case["page_stride"],
                                 case["block_table"].shape[1], case["logits_stride"], TOPK)
 
     def e2e_step():
-        plan.run(host["q"], host["kv_pages"], host["weights"], host["context_lens"], host["block_table"], out_host, BATCH)
+        plan.run(host["q"], host["kv_pages"], host["weights"], host["context_lens"], host["block_table"], out_host, batch)
 
     e2e_step()
     barrier()
@@ -262,7 +275,7 @@ def main():
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "l2": "inputs (%.0f MB of key pages per rank) larger than the 126 MB L2; "
+            "config": {"workload": WORKLOAD % batch, "l2": "inputs (%.0f MB of key pages per rank) larger than the 126 MB L2; "
                        "no flush between iterations" % (case["kv_pages"].nbytes / 1e6),
                        "parallelism": "request-dp%d" % world, "rows_per_s": world * rows / (ms_per_step * 1e-3)},
             "kernels_us": {"mqa_logits_fp8": mqa_ms * 1e3, "topk": topk_ms * 1e3},
@@ -277,8 +290,8 @@ def main():
         if world == 1:
             gbs, dt, cores = time_cpu(cpu_sample(case), 3, 1)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
-                                    "sample": "first %d of 64 requests, 3 timed passes of the C oracle "
-                                              "(OpenMP), %.2f s each" % (SAMPLE_REQUESTS, dt)}
+                                    "sample": "first %d of %d requests, 3 timed passes of the C oracle "
+                                              "(OpenMP), %.2f s each" % (min(SAMPLE_REQUESTS, batch), batch, dt)}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

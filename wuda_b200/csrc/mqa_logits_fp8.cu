@@ -43,13 +43,29 @@ constexpr int kDim = 128;
 constexpr int kTile = 128;          // tokens per work item (UMMA M)
 constexpr int kQStages = 2;
 constexpr int kTmemStages = 4;
+
 constexpr int kMaxKvStages = 12;
-constexpr int kMathWarps = 8;       // two warpgroups
-constexpr int kProducerWarp0 = 8;
-constexpr int kProducerWarp1 = 9;
-constexpr int kMmaWarp0 = 10;
-constexpr int kMmaWarp1 = 11;
-constexpr int kThreads = 384;
+// Math warpgroups; group g owns tiles n with n % kMathGroups == g.  The TMEM stage count
+// must be a multiple of both this and the number of UMMA issuers, so that every stage is
+// always produced by the same issuer and consumed by the same group: a parity wait may
+// not run more than one phase ahead of its barrier.
+constexpr int kMathGroups = 2;
+constexpr int kMathWarps = 4 * kMathGroups;
+static_assert(kTmemStages % kMathGroups == 0, "TMEM stages must be a multiple of the math group count");
+static_assert(kMaxKvStages % 4 == 0, "key stages come in multiples of the role counts");
+// Warp roles.  A single thread runs a dependent instruction chain at a few cycles per
+// instruction, so the bookkeeping of one tile costs a role several hundred cycles; the
+// roles are therefore replicated and take tiles round-robin: four producer warps, two
+// UMMA issuers, two math warpgroups.
+constexpr int kProducers = 4;       // warps 0..3, producer p takes tiles n with n % 4 == p
+constexpr int kIssuers = 2;         // warps 4, 5
+constexpr int kMmaWarp0 = kProducers;
+constexpr int kStageQuantum = 4;    // lcm(kProducers, kIssuers, kMathGroups)
+static_assert(kStageQuantum % kProducers == 0 && kStageQuantum % kIssuers == 0 && kStageQuantum % kMathGroups == 0,
+              "every stage must belong to one producer, one issuer and one math group");
+static_assert(kTmemStages % kIssuers == 0, "TMEM stages must be a multiple of the UMMA issuer count");
+constexpr int kFirstMathWarp = 8;   // a multiple of 4: TMEM lane quarter = warp % 4 (warps 6, 7 idle)
+constexpr int kThreads = 32 * (kFirstMathWarp + kMathWarps);
 constexpr int kKvTileBytes = kTile * kDim;      // 16 KB
 constexpr int kScaleTileBytes = kTile * 4;      // 512 B
 
@@ -153,39 +169,40 @@ __device__ __forceinline__ TileCursor make_cursor(const int32_t* ctx, int batch)
     return c;
 }
 
-template <int NEXT_N>
-__device__ __forceinline__ void advance(TileCursor& c, const int32_t* ctx, int batch) {
-    if (++c.j < c.tiles_b) return;
-    c.j = 0;
-    do {
-        ++c.b;
-        if (c.b >= batch) {
-            c.tiles_b = 0;
-            c.ctx_b = 0;
-            return;
-        }
-        c.ctx_b = request_ctx<NEXT_N>(ctx, c.b);
-        c.tiles_b = (c.ctx_b + kTile - 1) / kTile;
-    } while (c.tiles_b == 0);
+// Moves the cursor forward by k tiles.  on_enter(cursor) is called once for every
+// request entered on the way (requests without tiles are skipped by every role alike),
+// including the one the cursor lands in.  The caller never moves past the CTA's range.
+template <int NEXT_N, typename F>
+__device__ __forceinline__ void advance_by(TileCursor& c, int k, const int32_t* ctx, int batch, F&& on_enter) {
+    c.j += k;
+    while (c.j >= c.tiles_b) {
+        c.j -= c.tiles_b;
+        do {
+            ++c.b;
+            if (c.b >= batch) {      // cannot happen inside the range; keeps the loop finite
+                c.tiles_b = 0x3fffffff;
+                c.ctx_b = 0;
+                return;
+            }
+            c.ctx_b = request_ctx<NEXT_N>(ctx, c.b);
+            c.tiles_b = (c.ctx_b + kTile - 1) / kTile;
+        } while (c.tiles_b == 0);
+        on_enter(c);
+    }
 }
 
 // Ring position that advances without integer division.
 struct Ring {
     int idx = 0;
     uint32_t phase = 0;
-    __device__ __forceinline__ void step(int n, int size) {
+    __device__ __forceinline__ void step(int n, int size) {   // n <= size
         idx += n;
-        while (idx >= size) {
+        if (idx >= size) {
             idx -= size;
             phase ^= 1u;
         }
     }
 };
-
-template <int NEXT_N>
-__device__ __forceinline__ void advance_thread(TileCursor& c, const int32_t* ctx, int batch) {
-    advance<NEXT_N>(c, ctx, batch);   // advance() uses no warp-level operations
-}
 
 template <int NEXT_N>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -220,7 +237,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
         *abort_flag = 0;
         for (int i = 0; i < kQStages; ++i) {
             mbar_init(full_q + i * 8, 1);
-            mbar_init(empty_q + i * 8, 2 + kMathWarps);   // two UMMA issuers + eight math warps
+            mbar_init(empty_q + i * 8, kIssuers + kMathWarps);   // every UMMA issuer and math warp
         }
         for (int i = 0; i < S; ++i) {
             mbar_init(full_kv + i * 8, 1);
@@ -236,7 +253,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
         tmem_alloc(smem_u32(tmem_slot), kTmemStages * kN);
         tmem_relinquish();
     }
-    if (warp == kProducerWarp0 && lane == 0) {
+    if (warp == 0 && lane == 0) {
         prefetch_tmap(&q_map);
         prefetch_tmap(&kv_map);
         prefetch_tmap(&sf_map);
@@ -249,209 +266,232 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
     TileCursor cur = make_cursor<NEXT_N>(p.context_lens, p.batch);
     const int ntiles = cur.count;
 
-    if (warp == kProducerWarp0 || warp == kProducerWarp1) {
+    // Every role walks its own tiles n = r, r + R, ... of the CTA's range with a cursor
+    // that jumps R tiles at a time; entering a request runs the role's part of the
+    // query-stage protocol, and after its last tile a role walks on to the end of the
+    // range so that it enters (and thereby releases) every request in it.
+    if (warp < kProducers) {
         // ------------------------------------------------------------ TMA producers
-        // Starting an asynchronous copy occupies the issuing thread for a few hundred
-        // cycles, more than a tile's share of HBM time if one thread started them all.
-        // So two warps alternate tiles, and each tile's copies (key bytes and scales of
-        // every page) go out as ONE tensor-copy instruction with one lane per copy.
-        const int me = warp - kProducerWarp0;            // takes tiles n with n % 2 == me
+        // All copies of a tile (key bytes and scales of every page) go out as ONE
+        // tensor-copy instruction with one lane per copy.
+        const int me = warp;
         const uint64_t stream_policy = policy_evict_first();
         const int ppt = kTile / p.epb;                   // pages per tile: 4, 2 or 1
+        const int ppt_shift = ppt == 4 ? 2 : (ppt == 2 ? 1 : 0);
         const uint32_t page_bytes = p.epb * kDim;
         const uint32_t page_scale_bytes = p.epb * 4;
-        const int pg = static_cast<int>(lane) % ppt;     // this lane's page inside the tile
+        const int pg = static_cast<int>(lane) & (ppt - 1);   // this lane's page inside the tile
         const bool is_scale = static_cast<int>(lane) >= ppt;
         const bool copier = static_cast<int>(lane) < 2 * ppt;
         const void* my_map = is_scale ? static_cast<const void*>(&sf_map) : static_cast<const void*>(&kv_map);
-        const uint32_t my_dst_off = is_scale ? pg * page_scale_bytes : pg * page_bytes;
-        const uint32_t my_dst_base = is_scale ? scale_smem : kv_smem;
+        const uint32_t my_dst = (is_scale ? scale_smem + pg * page_scale_bytes : kv_smem + pg * page_bytes);
         const uint32_t my_stage_bytes = is_scale ? kScaleTileBytes : kKvTileBytes;
-        int prev_b = -1, qc = 0;
+        int qc = 0, pages_b = 0;
+        int64_t bt_row = 0;
         // block-table window: 32 entries in use, the next 32 already requested
-        int win_b = -1, win_base = 0, win_val = -1, nxt_val = -1;
-        Ring ring;
+        int win_base = 0, win_val = -1, nxt_val = -1;
+        bool win_cold = true;
         bool alive = true;
-        for (int n = 0; n < ntiles && alive; ++n) {
-            if (cur.b != prev_b) {
-                if (me == 0) {
-                    const int qs = qc & 1;
-                    alive = mbar_wait_lane0<WUDA_STYLE_PROD>(empty_q + qs * 8, ((qc >> 1) & 1) ^ 1, abort_flag, p.status,
-                                            kDevTimeoutEmptyQ);
-                    if (!alive) break;
-                    if (lane == 0) {
-                        mbar_arrive_expect_tx(full_q + qs * 8, L::kQBytes + L::kWBytes);
-                        tma_load_2d(q_smem + qs * L::kQBytes, &q_map, full_q + qs * 8, 0, cur.b * kN);
-                        bulk_load(w_smem + qs * L::kWBytes, p.weights + static_cast<int64_t>(cur.b) * kN,
-                                  L::kWBytes, full_q + qs * 8);
-                    }
+        auto on_enter = [&](const TileCursor& c) {
+            if (me == 0 && alive) {
+                const int qs = qc & 1;
+                alive = mbar_wait_lane0<WUDA_STYLE_PROD>(empty_q + qs * 8, ((qc >> 1) & 1) ^ 1, abort_flag, p.status,
+                                                         kDevTimeoutEmptyQ);
+                if (alive && lane == 0) {
+                    mbar_arrive_expect_tx(full_q + qs * 8, L::kQBytes + L::kWBytes);
+                    tma_load_2d(q_smem + qs * L::kQBytes, &q_map, full_q + qs * 8, 0, c.b * kN);
+                    bulk_load(w_smem + qs * L::kWBytes, p.weights + static_cast<int64_t>(c.b) * kN, L::kWBytes,
+                              full_q + qs * 8);
                 }
-                prev_b = cur.b;
-                ++qc;
             }
-            if ((n & 1) == me) {
-                const int pages_b = (cur.ctx_b + p.epb - 1) / p.epb;
-                const int first_page = cur.j * ppt;
-                const int valid = min(ppt, pages_b - first_page);
-                const int64_t bt_row = static_cast<int64_t>(cur.b) * p.bt_stride;
-                if (win_b != cur.b || first_page < win_base || first_page >= win_base + 64) {
-                    win_b = cur.b;                         // cold start of a window pair
-                    win_base = first_page;
-                    const int e0 = win_base + lane, e1 = e0 + 32;
-                    win_val = (e0 < pages_b && e0 < p.bt_stride) ? __ldg(p.block_table + bt_row + e0) : -1;
-                    nxt_val = (e1 < pages_b && e1 < p.bt_stride) ? __ldg(p.block_table + bt_row + e1) : -1;
-                } else if (first_page >= win_base + 32) {  // slide: the prefetched half becomes current
-                    win_base += 32;
-                    win_val = nxt_val;
-                    const int e1 = win_base + 32 + lane;
-                    nxt_val = (e1 < pages_b && e1 < p.bt_stride) ? __ldg(p.block_table + bt_row + e1) : -1;
-                }
-                int phys = __shfl_sync(0xffffffffu, win_val, (first_page + pg - win_base) & 31);
-                const bool mine = copier && pg < valid;
-                if (mine && (phys < 0 || phys >= p.num_blocks)) {
-                    if (p.status) atomicCAS(p.status, 0, kDevBadPageIndex);
-                    phys = 0;
-                }
-                const int s = ring.idx;
-                alive = mbar_wait_lane0<WUDA_STYLE_PROD>(empty_kv + s * 8, ring.phase ^ 1u, abort_flag, p.status,
-                                        kDevTimeoutEmptyKv);
-                if (!alive) break;
-                if (lane == 0)
-                    mbar_arrive_expect_tx(full_kv + s * 8, valid * (page_bytes + page_scale_bytes));
-                __syncwarp();
-                if (mine)
-                    tma_load_3d_hint(my_dst_base + s * my_stage_bytes + my_dst_off, my_map, full_kv + s * 8,
-                                     0, 0, phys, stream_policy);
+            ++qc;
+            pages_b = (c.ctx_b + p.epb - 1) / p.epb;
+            bt_row = static_cast<int64_t>(c.b) * p.bt_stride;
+            win_cold = true;
+        };
+        Ring ring;
+        int at = 0;
+        if (ntiles > 0) on_enter(cur);
+        ring.step(me, S);       // the host guarantees S >= kProducers
+        for (int n = me; n < ntiles && alive; n += kProducers) {
+            advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, on_enter);
+            at = n;
+            if (!alive) break;
+            const int first_page = cur.j << ppt_shift;
+            const int valid = min(ppt, pages_b - first_page);
+            if (win_cold || first_page < win_base || first_page >= win_base + 64) {
+                win_cold = false;
+                win_base = first_page;
+                const int e0 = win_base + lane, e1 = e0 + 32;
+                win_val = (e0 < pages_b && e0 < p.bt_stride) ? __ldg(p.block_table + bt_row + e0) : -1;
+                nxt_val = (e1 < pages_b && e1 < p.bt_stride) ? __ldg(p.block_table + bt_row + e1) : -1;
+            } else if (first_page >= win_base + 32) {    // slide: the prefetched half becomes current
+                win_base += 32;
+                win_val = nxt_val;
+                const int e1 = win_base + 32 + lane;
+                nxt_val = (e1 < pages_b && e1 < p.bt_stride) ? __ldg(p.block_table + bt_row + e1) : -1;
             }
-            ring.step(1, S);
-            advance<NEXT_N>(cur, p.context_lens, p.batch);
+            int phys = __shfl_sync(0xffffffffu, win_val, (first_page + pg - win_base) & 31);
+            const bool mine = copier && pg < valid;
+            if (mine && (phys < 0 || phys >= p.num_blocks)) {
+                if (p.status) atomicCAS(p.status, 0, kDevBadPageIndex);
+                phys = 0;
+            }
+            const int s = ring.idx;
+            alive = mbar_wait_lane0<WUDA_STYLE_PROD>(empty_kv + s * 8, ring.phase ^ 1u, abort_flag, p.status,
+                                                     kDevTimeoutEmptyKv);
+            if (!alive) break;
+            if (lane == 0) mbar_arrive_expect_tx(full_kv + s * 8, valid * (page_bytes + page_scale_bytes));
+            __syncwarp();
+            if (mine)
+                tma_load_3d_hint(my_dst + s * my_stage_bytes, my_map, full_kv + s * 8, 0, 0, phys, stream_policy);
+            ring.step(kProducers, S);
         }
-    } else if (warp == kMmaWarp0 || warp == kMmaWarp1) {
+        if (alive && ntiles > 0 && at < ntiles - 1)
+            advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, on_enter);
+    } else if (warp < kMmaWarp0 + kIssuers) {
         // ------------------------------------------------------------ UMMA issuers
         // One thread per warp runs the whole loop (the other lanes go straight to the
-        // final barrier, so no warp-level synchronisation sits between UMMAs).  Two
-        // issuers alternate tiles: while one is held at the tensor pipe's queue, the
-        // other does its waits and bookkeeping, which keeps the pipe fed.
+        // final barrier, so no warp-level synchronisation sits between UMMAs).
         if (lane == 0) {
-            const int me = warp - kMmaWarp0;             // takes tiles n with n % 2 == me
+            const int me = warp - kMmaWarp0;
             constexpr uint32_t idesc = umma_idesc(kTile, kN, 0, 0);
-            int prev_b = -1, qc = 0, qs = 0;
+            int qc = 0, qs = 0;
+            bool alive = true;
+            auto on_enter = [&](const TileCursor&) {
+                if (qc > 0) umma_commit(empty_q + qs * 8);   // this issuer's UMMAs on the old q stage retired
+                qs = qc & 1;
+                if (alive)
+                    alive = mbar_wait<WUDA_STYLE_MMA>(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status,
+                                                      kDevTimeoutFullQ);
+                ++qc;
+            };
             Ring ring, tring;
-            for (int n = 0; n < ntiles; ++n) {
-                if (cur.b != prev_b) {
-                    if (prev_b >= 0) umma_commit(empty_q + qs * 8);  // this issuer's UMMAs on the old q stage retired
-                    qs = qc & 1;
-                    if (!mbar_wait<WUDA_STYLE_MMA>(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status, kDevTimeoutFullQ))
-                        break;
-                    prev_b = cur.b;
-                    ++qc;
-                }
-                if ((n & 1) == me) {
-                    const int s = ring.idx, ts = tring.idx;
-                    if (!mbar_wait<WUDA_STYLE_MMA>(full_kv + s * 8, ring.phase, abort_flag, p.status, kDevTimeoutFullKv))
-                        break;
-                    if (!mbar_wait<WUDA_STYLE_MMA>(empty_tm + ts * 8, tring.phase ^ 1u, abort_flag, p.status,
-                                                   kDevTimeoutEmptyTmem))
-                        break;
-                    tc_fence_after();
-                    const uint32_t a_addr = kv_smem + s * kKvTileBytes;
-                    const uint32_t b_addr = q_smem + qs * L::kQBytes;
-                    const uint32_t d_addr = tmem_base + ts * kN;
+            int at = 0;
+            if (ntiles > 0) on_enter(cur);
+            ring.step(me, S);
+            tring.step(me, kTmemStages);
+            for (int n = me; n < ntiles && alive; n += kIssuers) {
+                advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, on_enter);
+                at = n;
+                if (!alive) break;
+                const int s = ring.idx, ts = tring.idx;
+                if (!mbar_wait<WUDA_STYLE_MMA>(full_kv + s * 8, ring.phase, abort_flag, p.status, kDevTimeoutFullKv))
+                    break;
+                if (!mbar_wait<WUDA_STYLE_MMA>(empty_tm + ts * 8, tring.phase ^ 1u, abort_flag, p.status,
+                                               kDevTimeoutEmptyTmem))
+                    break;
+                tc_fence_after();
+                const uint32_t a_addr = kv_smem + s * kKvTileBytes;
+                const uint32_t b_addr = q_smem + qs * L::kQBytes;
+                const uint32_t d_addr = tmem_base + ts * kN;
 #pragma unroll
-                    for (int k = 0; k < kDim / 32; ++k) {
-                        umma_f8f6f4(d_addr, umma_smem_desc_sw128(a_addr + k * 32),
-                                    umma_smem_desc_sw128(b_addr + k * 32), idesc, k > 0 ? 1u : 0u);
-                    }
-                    umma_commit(full_tm + ts * 8);
+                for (int k = 0; k < kDim / 32; ++k) {
+                    umma_f8f6f4(d_addr, umma_smem_desc_sw128(a_addr + k * 32),
+                                umma_smem_desc_sw128(b_addr + k * 32), idesc, k > 0 ? 1u : 0u);
                 }
-                ring.step(1, S);
-                tring.step(1, kTmemStages);
-                advance_thread<NEXT_N>(cur, p.context_lens, p.batch);
+                umma_commit(full_tm + ts * 8);
+                ring.step(kIssuers, S);
+                tring.step(kIssuers, kTmemStages);
             }
+            if (alive && ntiles > 0 && at < ntiles - 1)
+                advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, on_enter);
         }
-    } else {
+    } else if (warp >= kFirstMathWarp) {
         // ------------------------------------------------------------ math warps
-        // Warpgroup g owns tiles n with n % 2 == g.  A thread is one key token: it reads
+        // Warpgroup g owns tiles n with n % kMathGroups == g.  A thread is one key token: it reads
         // its accumulator row from TMEM in 32-column chunks (the next chunk is in
         // flight while the current one is reduced), applies relu, the per-head weight
         // (packed fp32x2 FMAs) and the token scale, and stores one logit per query row.
-        const int wg = warp >> 2;
+        const int wg = (warp - kFirstMathWarp) >> 2;
         const int row_in_tile = (warp & 3) * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         constexpr int kChunks = kN / 32;              // 32-column chunks per tile
-        int prev_b = -1, qc = 0, qs = 0;
+        int qc = 0, qs = 0;
         int ctx_row[NEXT_N];
-        Ring ring, tring;
         bool alive = true;
-        for (int n = 0; n < ntiles && alive; ++n) {
-            if (cur.b != prev_b) {
-                if (prev_b >= 0) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(empty_q + qs * 8);
-                }
-                qs = qc & 1;
+        auto on_enter = [&](const TileCursor& c) {
+            if (qc > 0) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_q + qs * 8);
+            }
+            qs = qc & 1;
+            if (alive)
                 alive = mbar_wait_warp_fast<WUDA_STYLE_MATH>(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status,
                                                              kDevTimeoutFullQ);
-                if (!alive) break;
-                prev_b = cur.b;
-                ++qc;
+            ++qc;
 #pragma unroll
-                for (int i = 0; i < NEXT_N; ++i) ctx_row[i] = __ldg(p.context_lens + cur.b * NEXT_N + i);
-            }
-            if ((n & 1) == wg) {
-                const int s = ring.idx, ts = tring.idx;
-                // full_tm completes after the UMMAs that read key stage s retired, and
-                // those were issued after the stage's copies had landed: one wait covers
-                // the accumulator and the stage's scales.
-                alive = mbar_wait_warp_fast<WUDA_STYLE_MATH>(full_tm + ts * 8, tring.phase, abort_flag, p.status,
-                                                             kDevTimeoutFullTmem);
-                if (!alive) break;
-                tc_fence_after();
-                const uint32_t taddr = tmem_base + lane_base + ts * kN;
-                uint32_t v[2][32];
-                tmem_ld_32x32(taddr, v[0]);
-                const float scale = scale_ptr[s * kTile + row_in_tile];
-                const int t = cur.j * kTile + row_in_tile;
-                float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+            for (int i = 0; i < NEXT_N; ++i) ctx_row[i] = __ldg(p.context_lens + c.b * NEXT_N + i);
+        };
+        Ring ring, tring;
+        int at = 0;
+        if (ntiles > 0) on_enter(cur);
+        ring.step(wg, S);
+        tring.step(wg, kTmemStages);
+        for (int n = wg; n < ntiles && alive; n += kMathGroups) {
+            advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, on_enter);
+            at = n;
+            if (!alive) break;
+            const int s = ring.idx, ts = tring.idx;
+            // full_tm completes after the UMMAs that read key stage s retired, and those
+            // were issued after the stage's copies had landed: one wait covers the
+            // accumulator and the stage's scales.
+            alive = mbar_wait_warp_fast<WUDA_STYLE_MATH>(full_tm + ts * 8, tring.phase, abort_flag, p.status,
+                                                         kDevTimeoutFullTmem);
+            if (!alive) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + lane_base + ts * kN;
+            uint32_t v[2][32];
+            tmem_ld_32x32(taddr, v[0]);
+            const float scale = scale_ptr[s * kTile + row_in_tile];
+            const int t = cur.j * kTile + row_in_tile;
+            float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+            float2 acc2 = make_float2(0.f, 0.f), acc3 = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int c = 0; c < kChunks; ++c) {
-                    tmem_ld_wait();
-                    if (c + 1 < kChunks) tmem_ld_32x32(taddr + (c + 1) * 32, v[(c + 1) & 1]);
-                    if (c + 1 == kChunks) {
-                        // every accumulator column is in registers, the scale too
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) {
-                            mbar_arrive(empty_tm + ts * 8);
-                            mbar_arrive(empty_kv + s * 8);
-                        }
-                    }
-                    const float4* w4 = reinterpret_cast<const float4*>(w_ptr + qs * kN + c * 32);
-                    const uint32_t* x = v[c & 1];
-#pragma unroll
-                    for (int e = 0; e < 32; e += 4) {
-                        const float4 w = w4[e >> 2];
-                        acc0 = __ffma2_rn(make_float2(fmaxf(__uint_as_float(x[e + 0]), 0.f),
-                                                      fmaxf(__uint_as_float(x[e + 1]), 0.f)),
-                                          make_float2(w.x, w.y), acc0);
-                        acc1 = __ffma2_rn(make_float2(fmaxf(__uint_as_float(x[e + 2]), 0.f),
-                                                      fmaxf(__uint_as_float(x[e + 3]), 0.f)),
-                                          make_float2(w.z, w.w), acc1);
-                    }
-                    if ((c & 1) == 1) {   // a query row (64 heads = two chunks) is complete
-                        const int i = c >> 1;
-                        const float r = ((acc0.x + acc0.y) + (acc1.x + acc1.y)) * scale;
-                        if (t < ctx_row[i])
-                            p.logits[static_cast<int64_t>(cur.b * NEXT_N + i) * p.logits_stride + t] = r;
-                        acc0 = make_float2(0.f, 0.f);
-                        acc1 = make_float2(0.f, 0.f);
+            for (int c = 0; c < kChunks; ++c) {
+                tmem_ld_wait();
+                if (c + 1 < kChunks) tmem_ld_32x32(taddr + (c + 1) * 32, v[(c + 1) & 1]);
+                if (c + 1 == kChunks) {
+                    // every accumulator column is in registers, the scale too
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(empty_tm + ts * 8);
+                        mbar_arrive(empty_kv + s * 8);
                     }
                 }
+                const float4* w4 = reinterpret_cast<const float4*>(w_ptr + qs * kN + c * 32);
+                const uint32_t* x = v[c & 1];
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+                    const float4 wa = w4[e >> 2], wb = w4[(e >> 2) + 1];
+                    acc0 = __ffma2_rn(make_float2(fmaxf(__uint_as_float(x[e + 0]), 0.f),
+                                                  fmaxf(__uint_as_float(x[e + 1]), 0.f)),
+                                      make_float2(wa.x, wa.y), acc0);
+                    acc1 = __ffma2_rn(make_float2(fmaxf(__uint_as_float(x[e + 2]), 0.f),
+                                                  fmaxf(__uint_as_float(x[e + 3]), 0.f)),
+                                      make_float2(wa.z, wa.w), acc1);
+                    acc2 = __ffma2_rn(make_float2(fmaxf(__uint_as_float(x[e + 4]), 0.f),
+                                                  fmaxf(__uint_as_float(x[e + 5]), 0.f)),
+                                      make_float2(wb.x, wb.y), acc2);
+                    acc3 = __ffma2_rn(make_float2(fmaxf(__uint_as_float(x[e + 6]), 0.f),
+                                                  fmaxf(__uint_as_float(x[e + 7]), 0.f)),
+                                      make_float2(wb.z, wb.w), acc3);
+                }
+                if ((c & 1) == 1) {   // a query row (64 heads = two chunks) is complete
+                    const int i = c >> 1;
+                    const float2 sum = __fadd2_rn(__fadd2_rn(acc0, acc1), __fadd2_rn(acc2, acc3));
+                    const float r = (sum.x + sum.y) * scale;
+                    if (t < ctx_row[i])
+                        p.logits[static_cast<int64_t>(cur.b * NEXT_N + i) * p.logits_stride + t] = r;
+                    acc0 = acc1 = acc2 = acc3 = make_float2(0.f, 0.f);
+                }
             }
-            ring.step(1, S);
-            tring.step(1, kTmemStages);
-            advance<NEXT_N>(cur, p.context_lens, p.batch);
+            ring.step(kMathGroups, S);
+            tring.step(kMathGroups, kTmemStages);
         }
+        if (alive && ntiles > 0 && at < ntiles - 1)
+            advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, on_enter);
     }
 
     __syncthreads();
@@ -552,10 +592,18 @@ extern "C" int wuda_mqa_logits_fp8(const void* q, const void* kv_pages, const fl
     p.num_blocks = num_blocks;
     p.epb = entries_per_block;
     p.bt_stride = block_table_stride;
-    // As many key stages as shared memory allows (each stage = 128 tokens = 16.5 KB).
+    // As many key stages as shared memory allows (a stage = 128 tokens = 16.5 KB), in
+    // multiples of kStageQuantum: a stage must always be filled by the same producer,
+    // read by the same issuer and released by the same math group, because a parity
+    // wait is only sound while its waiter is at most one phase ahead of the barrier,
+    // and only an agent's own earlier use of the stage guarantees that.
     int stages = kMaxKvStages;
-    while (stages > 2 && (next_n == 1 ? Smem<1>::total(stages) : Smem<2>::total(stages)) > dev.smem_optin)
-        --stages;
+    while (stages > kStageQuantum &&
+           (next_n == 1 ? Smem<1>::total(stages) : Smem<2>::total(stages)) > dev.smem_optin)
+        stages -= kStageQuantum;
+    if ((next_n == 1 ? Smem<1>::total(stages) : Smem<2>::total(stages)) > dev.smem_optin)
+        return fail(WUDA_ERR_UNSUPPORTED, "device offers %d bytes of shared memory per block; the kernel needs more",
+                    dev.smem_optin);
     p.kv_stages = stages;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);

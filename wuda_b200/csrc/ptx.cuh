@@ -84,6 +84,17 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
+#if defined(WUDA_TRYWAIT_HINT_NS) && WUDA_TRYWAIT_HINT_NS > 0
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(WUDA_TRYWAIT_HINT_NS))
+        : "memory");
+#else
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
@@ -93,6 +104,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
+#endif
 #ifdef WUDA_COUNT_POLLS
     if (blockIdx.x == 0) atomicAdd(&g_polls[(threadIdx.x >> 5) * 2 + (ok ? 0 : 1)], 1ull);
 #endif

@@ -9,16 +9,24 @@
 // torch.argsort(-scores, stable=True)[:k] — stricter than the reference, which leaves the
 // choice among exact duplicates unspecified.
 //
-// Algorithm: a three-level most-significant-digit radix select on an order-preserving
-// 32-bit key (12 + 12 + 8 bits), one CTA of 1024 threads per row.
-//   pass 1  histogram of the top 12 key bits over the row           (read #1)
-//   pass 2  indices whose digit is above the threshold digit are emitted at once;
-//           those inside the threshold digit are parked in shared memory (read #2)
-//   levels 2 and 3 refine the parked candidates in shared memory; when there are too
-//   many to park (heavily duplicated scores) they re-read the row instead.
-//   If more values equal the final threshold than are still needed, one ordered pass
-//   over the row takes the lowest indices among them.
-// No global scratch memory is used and nothing is allocated.
+// One CTA of 1024 threads per row.  The selection is a most-significant-digit radix
+// select on an order-preserving 32-bit key (digits of 12 + 12 + 8 bits) over a
+// CANDIDATE list held in shared memory.  The candidate list is built in one of two ways:
+//
+//   sampled path (long rows, n >= 4k): 2048 evenly spaced samples give a 12-bit digit
+//     that, with overwhelming probability, bounds the k-th value from below; ONE pass
+//     over the row then parks every element at or above that digit (a few thousand
+//     entries).  If the sample misled (fewer than k parked, or more than fit) the row
+//     falls back to the exact path.
+//   exact path: pass 1 histograms the top digit over the row, pass 2 emits everything
+//     above the threshold digit and parks the threshold digit's members; when they do
+//     not fit in shared memory (heavily duplicated scores) the two lower levels re-read
+//     the row instead.
+//
+// If more values equal the final threshold than are still needed, one ordered pass over
+// the row takes the lowest indices among them.  Shared-memory counters are bumped once
+// per warp (ballot + popcount), not once per element.  No global scratch memory is used
+// and nothing is allocated.
 #include <cuda_runtime.h>
 
 #include "host.h"
@@ -29,7 +37,8 @@ namespace topk {
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr int kBins = 4096;
-constexpr int kCandCap = 6144;
+constexpr int kCandCap = 8192;
+constexpr int kSamples = 2048;
 
 struct Params {
     const float* scores;
@@ -61,23 +70,44 @@ struct Shared {
     uint32_t out_count, cand_count;
 };
 
-// f(index, value) for every element of the row; 16-byte loads when the row allows.
+// f(index, value, valid) for every element of the row.  Every thread of the CTA makes
+// the same number of calls (valid = false past the end), so f may use full-warp votes.
 template <typename F>
 __device__ __forceinline__ void for_each_elem(const float* row, int n, bool vec_ok, F f) {
     if (vec_ok) {
         const int n4 = n >> 2;
         const float4* row4 = reinterpret_cast<const float4*>(row);
-        for (int i = threadIdx.x; i < n4; i += kThreads) {
-            const float4 v = row4[i];
-            f(4 * i + 0, v.x);
-            f(4 * i + 1, v.y);
-            f(4 * i + 2, v.z);
-            f(4 * i + 3, v.w);
+        for (int base = 0; base < n4; base += kThreads) {
+            const int i = base + threadIdx.x;
+            const bool valid = i < n4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (valid) v = row4[i];
+            f(4 * i + 0, v.x, valid);
+            f(4 * i + 1, v.y, valid);
+            f(4 * i + 2, v.z, valid);
+            f(4 * i + 3, v.w, valid);
         }
-        for (int i = (n4 << 2) + threadIdx.x; i < n; i += kThreads) f(i, row[i]);
+        const int i = (n4 << 2) + threadIdx.x;   // at most 3 leftover elements
+        if ((n & 3) != 0) f(i, i < n ? row[i] : 0.f, i < n);
     } else {
-        for (int i = threadIdx.x; i < n; i += kThreads) f(i, row[i]);
+        for (int base = 0; base < n; base += kThreads) {
+            const int i = base + threadIdx.x;
+            const bool valid = i < n;
+            f(i, valid ? row[i] : 0.f, valid);
+        }
     }
+}
+
+// Reserves one slot per lane with `pred` set by bumping `counter` once per warp.
+// Must be called by all 32 lanes of the warp.
+__device__ __forceinline__ uint32_t warp_reserve(bool pred, uint32_t* counter) {
+    const uint32_t mask = __ballot_sync(0xffffffffu, pred);
+    if (mask == 0) return 0;
+    const uint32_t lane = threadIdx.x & 31;
+    uint32_t base = 0;
+    if (lane == (__ffs(mask) - 1)) base = atomicAdd(counter, __popc(mask));
+    base = __shfl_sync(0xffffffffu, base, __ffs(mask) - 1);
+    return base + __popc(mask & ((1u << lane) - 1u));
 }
 
 __device__ __forceinline__ void zero_hist(Shared& s, int nbins) {
@@ -127,18 +157,21 @@ __device__ __forceinline__ void find_threshold(Shared& s, int nbins, uint32_t ne
     __syncthreads();
 }
 
-__device__ __forceinline__ void emit(const Params& p, Shared& s, int r, int idx) {
-    const uint32_t pos = atomicAdd(&s.out_count, 1u);
-    if (pos < static_cast<uint32_t>(p.k)) {
+__device__ __forceinline__ int32_t page_of(const Params& p, int r, int idx) {
+    if (!p.page_table) return idx;
+    const int32_t page =
+        __ldg(p.page_table + static_cast<int64_t>(r / p.rows_per_table_row) * p.pt_stride + (idx >> p.page_bits));
+    return static_cast<int32_t>((static_cast<uint32_t>(page) << p.page_bits) |
+                                static_cast<uint32_t>(idx & ((1 << p.page_bits) - 1)));
+}
+
+// Writes index `idx` to the next output slot of row r if `pred`; all 32 lanes call it.
+__device__ __forceinline__ void emit(const Params& p, Shared& s, int r, int idx, bool pred) {
+    const uint32_t pos = warp_reserve(pred, &s.out_count);
+    if (pred && pos < static_cast<uint32_t>(p.k)) {
         const int64_t o = static_cast<int64_t>(r) * p.k + pos;
         if (p.raw) p.raw[o] = idx;
-        if (p.page_table) {
-            const int32_t page = __ldg(p.page_table + static_cast<int64_t>(r / p.rows_per_table_row) * p.pt_stride + (idx >> p.page_bits));
-            p.page_indices[o] = static_cast<int32_t>((static_cast<uint32_t>(page) << p.page_bits) |
-                                                     static_cast<uint32_t>(idx & ((1 << p.page_bits) - 1)));
-        } else {
-            p.page_indices[o] = idx;
-        }
+        p.page_indices[o] = page_of(p, r, idx);
     }
 }
 
@@ -158,67 +191,123 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
                 const int64_t o = static_cast<int64_t>(r) * k + i;
                 const int idx = i < n ? i : -1;
                 if (p.raw) p.raw[o] = idx;
-                int32_t out = idx;
-                if (idx >= 0 && p.page_table) {
-                    const int32_t page = __ldg(p.page_table + static_cast<int64_t>(r / p.rows_per_table_row) * p.pt_stride + (idx >> p.page_bits));
-                    out = static_cast<int32_t>((static_cast<uint32_t>(page) << p.page_bits) |
-                                               static_cast<uint32_t>(idx & ((1 << p.page_bits) - 1)));
-                }
-                p.page_indices[o] = out;
+                p.page_indices[o] = idx >= 0 ? page_of(p, r, idx) : -1;
             }
             continue;
         }
 
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
-
-        // ---- level 1: top 12 bits over the whole row
         zero_hist(s, kBins);
         if (threadIdx.x == 0) {
             s.out_count = 0;
             s.cand_count = 0;
         }
         __syncthreads();
-        for_each_elem(row, n, vec_ok, [&](int, float x) { atomicAdd(&s.hist[key_of(x) >> 20], 1u); });
-        __syncthreads();
-        find_threshold(s, kBins, static_cast<uint32_t>(k));
-        const uint32_t d1 = s.sel_digit;
-        const uint32_t need1 = static_cast<uint32_t>(k) - s.sel_above;   // still needed from digit d1
-        const uint32_t c1 = s.hist[d1];
-        const bool parked = c1 <= static_cast<uint32_t>(kCandCap);
-        __syncthreads();
 
-        // ---- pass 2: emit everything above the digit, park the digit's members
-        for_each_elem(row, n, vec_ok, [&](int i, float x) {
-            const uint32_t key = key_of(x);
-            const uint32_t d = key >> 20;
-            if (d > d1) {
-                emit(p, s, r, i);
-            } else if (d == d1 && parked) {
-                const uint32_t slot = atomicAdd(&s.cand_count, 1u);
-                if (slot < static_cast<uint32_t>(kCandCap)) {
+        // ------------------------------------------------ sampled path: build the candidate list
+        bool have_all = false;      // candidate list holds EVERY element at or above some digit
+        int ncand = 0;
+        if (n >= 4 * k && k <= kCandCap / 2) {
+            for (int t = threadIdx.x; t < kSamples; t += kThreads) {
+                const int i = static_cast<int>(static_cast<long long>(t) * n / kSamples);
+                atomicAdd(&s.hist[key_of(row[i]) >> 20], 1u);
+            }
+            __syncthreads();
+            // expected sample rank of the k-th value, plus a 5-sigma margin
+            const float expect = static_cast<float>(kSamples) * static_cast<float>(k) / static_cast<float>(n);
+            uint32_t rank = static_cast<uint32_t>(expect + 5.f * sqrtf(expect) + 8.f);
+            if (rank > static_cast<uint32_t>(kSamples)) rank = kSamples;
+            find_threshold(s, kBins, rank);
+            const uint32_t d_lo = s.sel_digit;
+            __syncthreads();
+            for_each_elem(row, n, vec_ok, [&](int i, float x, bool valid) {
+                const uint32_t key = key_of(x);
+                const bool take = valid && (key >> 20) >= d_lo;
+                const uint32_t slot = warp_reserve(take, &s.cand_count);
+                if (take && slot < static_cast<uint32_t>(kCandCap)) {
                     s.cand_key[slot] = key;
                     s.cand_idx[slot] = i;
                 }
-            }
-        });
-        zero_hist(s, kBins);
-        __syncthreads();
-        const int ncand = parked ? static_cast<int>(min(s.cand_count, static_cast<uint32_t>(kCandCap))) : 0;
+            });
+            zero_hist(s, kBins);
+            __syncthreads();
+            const uint32_t total = s.cand_count;
+            have_all = total >= static_cast<uint32_t>(k) && total <= static_cast<uint32_t>(kCandCap);
+            ncand = have_all ? static_cast<int>(total) : 0;
+            __syncthreads();
+            if (!have_all && threadIdx.x == 0) s.cand_count = 0;
+            __syncthreads();
+        }
 
-        // f(index, key) over the members of digit d1
+        // ------------------------------------------------ level 1: the top 12 bits
+        uint32_t d1, need1;
+        bool parked;                // the threshold digit's members are in the candidate list
+        const int ncand_pad = (ncand + kThreads - 1) / kThreads * kThreads;
+        if (have_all) {
+            for (int c = threadIdx.x; c < ncand; c += kThreads) atomicAdd(&s.hist[s.cand_key[c] >> 20], 1u);
+            __syncthreads();
+            find_threshold(s, kBins, static_cast<uint32_t>(k));
+            d1 = s.sel_digit;
+            need1 = static_cast<uint32_t>(k) - s.sel_above;
+            parked = true;
+            __syncthreads();
+            for (int c = threadIdx.x; c < ncand_pad; c += kThreads) {
+                const bool ok = c < ncand && (s.cand_key[c] >> 20) > d1;
+                emit(p, s, r, ok ? s.cand_idx[c] : 0, ok);
+            }
+            zero_hist(s, kBins);
+            __syncthreads();
+        } else {
+            for_each_elem(row, n, vec_ok, [&](int, float x, bool valid) {
+                if (valid) atomicAdd(&s.hist[key_of(x) >> 20], 1u);
+            });
+            __syncthreads();
+            find_threshold(s, kBins, static_cast<uint32_t>(k));
+            d1 = s.sel_digit;
+            need1 = static_cast<uint32_t>(k) - s.sel_above;   // still needed from digit d1
+            parked = s.hist[d1] <= static_cast<uint32_t>(kCandCap);
+            __syncthreads();
+            // pass 2: emit everything above the digit, park the digit's members
+            for_each_elem(row, n, vec_ok, [&](int i, float x, bool valid) {
+                const uint32_t key = key_of(x);
+                const uint32_t d = key >> 20;
+                emit(p, s, r, i, valid && d > d1);
+                if (parked) {
+                    const bool take = valid && d == d1;
+                    const uint32_t slot = warp_reserve(take, &s.cand_count);
+                    if (take && slot < static_cast<uint32_t>(kCandCap)) {
+                        s.cand_key[slot] = key;
+                        s.cand_idx[slot] = i;
+                    }
+                }
+            });
+            zero_hist(s, kBins);
+            __syncthreads();
+            ncand = parked ? static_cast<int>(min(s.cand_count, static_cast<uint32_t>(kCandCap))) : 0;
+        }
+        const int nmem_pad = (ncand + kThreads - 1) / kThreads * kThreads;
+
+        // f(index, key, is_member) over the members of digit d1, with a uniform call
+        // count across the CTA (is_member = false on padding calls)
         auto for_each_member = [&](auto f) {
             if (parked) {
-                for (int c = threadIdx.x; c < ncand; c += kThreads) f(s.cand_idx[c], s.cand_key[c]);
+                for (int c = threadIdx.x; c < nmem_pad; c += kThreads) {
+                    const bool in = c < ncand;
+                    const uint32_t key = in ? s.cand_key[c] : 0u;
+                    f(in ? s.cand_idx[c] : 0, key, in && (key >> 20) == d1);
+                }
             } else {
-                for_each_elem(row, n, vec_ok, [&](int i, float x) {
+                for_each_elem(row, n, vec_ok, [&](int i, float x, bool valid) {
                     const uint32_t key = key_of(x);
-                    if ((key >> 20) == d1) f(i, key);
+                    f(i, key, valid && (key >> 20) == d1);
                 });
             }
         };
 
-        // ---- level 2: next 12 bits
-        for_each_member([&](int, uint32_t key) { atomicAdd(&s.hist[(key >> 8) & 0xFFFu], 1u); });
+        // ------------------------------------------------ level 2: the next 12 bits
+        for_each_member([&](int, uint32_t key, bool in) {
+            if (in) atomicAdd(&s.hist[(key >> 8) & 0xFFFu], 1u);
+        });
         __syncthreads();
         find_threshold(s, kBins, need1);
         const uint32_t d2 = s.sel_digit;
@@ -227,10 +316,10 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
         zero_hist(s, 256);
         __syncthreads();
 
-        // ---- level 3: last 8 bits
+        // ------------------------------------------------ level 3: the last 8 bits
         const uint32_t prefix24 = (d1 << 12) | d2;
-        for_each_member([&](int, uint32_t key) {
-            if ((key >> 8) == prefix24) atomicAdd(&s.hist[key & 0xFFu], 1u);
+        for_each_member([&](int, uint32_t key, bool in) {
+            if (in && (key >> 8) == prefix24) atomicAdd(&s.hist[key & 0xFFu], 1u);
         });
         __syncthreads();
         find_threshold(s, 256, need2);
@@ -241,8 +330,8 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
         const bool take_all_equal = (ceq == need3);
         __syncthreads();
 
-        for_each_member([&](int i, uint32_t key) {
-            if (key > thr || (key == thr && take_all_equal)) emit(p, s, r, i);
+        for_each_member([&](int i, uint32_t key, bool in) {
+            emit(p, s, r, i, in && (key > thr || (key == thr && take_all_equal)));
         });
 
         if (!take_all_equal) {
@@ -276,8 +365,13 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
             __syncthreads();
             uint32_t rank = v - mine + s.warp_excl[warp];
             for (int i = beg; i < end && rank < need3; ++i) {
-                if (key_of(row[i]) == thr) {
-                    emit(p, s, r, i);
+                if (key_of(row[i]) == thr) {   // few and scattered: one counter bump each
+                    const uint32_t pos = atomicAdd(&s.out_count, 1u);
+                    if (pos < static_cast<uint32_t>(k)) {
+                        const int64_t o = static_cast<int64_t>(r) * k + pos;
+                        if (p.raw) p.raw[o] = i;
+                        p.page_indices[o] = page_of(p, r, i);
+                    }
                     ++rank;
                 }
             }
