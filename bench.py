@@ -196,36 +196,67 @@ def main():
     seq_lens = d["context_lens"].reshape(-1).contiguous()
     status = wuda.device_status_word()
 
-    def step():
+    def mqa():
         wuda.mqa_logits_fp8_decode_out(d["q"], d["kv_pages"], d["weights"], d["context_lens"], d["block_table"],
                                        None, logits, EPB, next_n=NEXT_N, status_word=status)
-        mid.record()
+
+    def topk():
         wuda.topk_v2_transform(logits, seq_lens, d["block_table"], indices, EPB, rows_per_table_row=NEXT_N)
 
-    mid = torch.cuda.Event(enable_timing=True)
+    def step():
+        mqa()
+        topk()
+
+    # One step = one CUDA graph of the two launches, replayed: the host-side cost of a
+    # launch (argument checks, tensor-map encoding, ~25 us) would otherwise leave the GPU
+    # idle between the kernels.  A decode engine replays the layer as a graph too.
+    step()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        step_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(step_graph, stream=side):
+            step()
+        topk_graph = torch.cuda.CUDAGraph()     # ten top-k launches, for the per-kernel split
+        with torch.cuda.graph(topk_graph, stream=side):
+            for _ in range(10):
+                topk()
+    torch.cuda.synchronize()
+
     # The sampler runs from here to the end of the timed region: the GPU is under the
     # same load throughout (the timed region alone is shorter than nvidia-smi's period).
     sampler = ClockSampler(local_rank)
     # bring the clocks up from idle before anything is measured
     t_end = time.perf_counter() + (0.0 if args.capture else 1.0)
     while time.perf_counter() < t_end:
-        step()
+        for _ in range(20):
+            step_graph.replay()
         torch.cuda.synchronize()
     for _ in range(args.warmup):
-        step()
+        step_graph.replay()
     barrier()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    e0, e1, e2, e3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
     barrier()
-    for i in range(args.steps):
-        ev[i][0].record()
-        mid = ev[i][1]
-        step()
-        ev[i][2].record()
+    e0.record()
+    for _ in range(args.steps):
+        step_graph.replay()
+    e1.record()
     barrier()
+    total_ms = e0.elapsed_time(e1)
+    # per-kernel durations, same stream, right after the timed region: the MQA kernel
+    # launched back to back (the host is faster than the kernel), top-k as graphs of ten
+    e1.record()
+    for _ in range(args.steps):
+        mqa()
+    e2.record()
+    reps = max(args.steps // 10, 1)
+    for _ in range(reps):
+        topk_graph.replay()
+    e3.record()
+    torch.cuda.synchronize()
     clocks = sampler.stop()
-    total_ms = ev[0][0].elapsed_time(ev[-1][2])
-    mqa_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
-    topk_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    mqa_ms = e1.elapsed_time(e2) / args.steps
+    topk_ms = e2.elapsed_time(e3) / (reps * 10)
     assert int(status.item()) == 0, "device status %d" % int(status.item())
 
     t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
@@ -284,7 +315,7 @@ def main():
                          "traffic": None, "algorithmic_bytes": mqa_b},
             "e2e": {"value": world * (mqa_b + topk_b) / e2e_s / 1e9, "unit": "GB/s", "ms_per_step": e2e_s * 1e3,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "matches_device_path": bool(same)},
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": 2 * args.steps, "launch": "one CUDA graph replay per step",
             "clocks": clocks,
         }
         if world == 1:

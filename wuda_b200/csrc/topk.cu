@@ -27,6 +27,7 @@
 // the row takes the lowest indices among them.  Shared-memory counters are bumped once
 // per warp (ballot + popcount), not once per element.  No global scratch memory is used
 // and nothing is allocated.
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 
 #include "host.h"
@@ -39,6 +40,7 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kBins = 4096;
 constexpr int kCandCap = 8192;
 constexpr int kSamples = 2048;
+constexpr int kMaxCluster = 4;  // CTAs that may share one row's scan (thread-block cluster, distributed shared memory)
 
 struct Params {
     const float* scores;
@@ -60,6 +62,10 @@ __device__ __forceinline__ uint32_t key_of(float x) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+__device__ __forceinline__ float float_of_key(uint32_t key) {   // inverse of key_of
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7FFFFFFFu) : ~key);
+}
+
 struct Shared {
     uint32_t hist[kBins];
     uint32_t cand_key[kCandCap];
@@ -72,28 +78,47 @@ struct Shared {
 
 // f(index, value, valid) for every element of the row.  Every thread of the CTA makes
 // the same number of calls (valid = false past the end), so f may use full-warp votes.
+// Loads are issued kBatch at a time before any is consumed: the row comes from L2 (the
+// logits kernel has just written it) and a dependent load-use chain per 16 bytes would
+// leave the pass bound by L2 latency.
+constexpr int kBatch = 4;
 template <typename F>
 __device__ __forceinline__ void for_each_elem(const float* row, int n, bool vec_ok, F f) {
     if (vec_ok) {
         const int n4 = n >> 2;
         const float4* row4 = reinterpret_cast<const float4*>(row);
-        for (int base = 0; base < n4; base += kThreads) {
-            const int i = base + threadIdx.x;
-            const bool valid = i < n4;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (valid) v = row4[i];
-            f(4 * i + 0, v.x, valid);
-            f(4 * i + 1, v.y, valid);
-            f(4 * i + 2, v.z, valid);
-            f(4 * i + 3, v.w, valid);
+        for (int base = 0; base < n4; base += kThreads * kBatch) {
+            float4 v[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int i = base + u * kThreads + threadIdx.x;
+                v[u] = i < n4 ? __ldcg(row4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int i = base + u * kThreads + threadIdx.x;
+                const bool valid = i < n4;
+                f(4 * i + 0, v[u].x, valid);
+                f(4 * i + 1, v[u].y, valid);
+                f(4 * i + 2, v[u].z, valid);
+                f(4 * i + 3, v[u].w, valid);
+            }
         }
         const int i = (n4 << 2) + threadIdx.x;   // at most 3 leftover elements
         if ((n & 3) != 0) f(i, i < n ? row[i] : 0.f, i < n);
     } else {
-        for (int base = 0; base < n; base += kThreads) {
-            const int i = base + threadIdx.x;
-            const bool valid = i < n;
-            f(i, valid ? row[i] : 0.f, valid);
+        for (int base = 0; base < n; base += kThreads * kBatch) {
+            float v[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int i = base + u * kThreads + threadIdx.x;
+                v[u] = i < n ? row[i] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int i = base + u * kThreads + threadIdx.x;
+                f(i, v[u], i < n);
+            }
         }
     }
 }
@@ -175,17 +200,132 @@ __device__ __forceinline__ void emit(const Params& p, Shared& s, int r, int idx,
     }
 }
 
+// One pass over the row that sorts every element into "emit now", "park as candidate"
+// or "drop" (cls(key) = 2 / 1 / 0).  A thread classifies a whole batch of its elements
+// into two bit masks first; slots in the output and in the candidate list are then
+// reserved once per warp and batch (a warp scan of the per-thread counts and ONE counter
+// bump), instead of a vote and a shared-memory atomic round trip per element.
+constexpr int kClsBatch = 4;   // 16 elements per thread and batch: fits the 64-register budget of a 1024-thread CTA
+// The pass covers elements [lo, hi) of the row (lo a multiple of 4); candidates go to
+// `dst`, which may be another CTA's shared memory within the cluster; emitted indices
+// are counted in `dst` as well.
+template <typename Cls>
+__device__ __forceinline__ void classify_pass(const float* row, int lo, int hi, bool vec_ok, const Params& p,
+                                              Shared& dst, int r, Cls cls) {
+    Shared& s = dst;
+    const int n = hi;
+    const uint32_t lane = threadIdx.x & 31;
+    auto reserve = [&](uint32_t count, uint32_t* counter) -> uint32_t {   // exclusive offset for this lane
+        uint32_t incl = count;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= static_cast<uint32_t>(o)) incl += t;
+        }
+        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+        uint32_t base = 0;
+        if (total != 0) {
+            if (lane == 31) base = atomicAdd(counter, total);
+            base = __shfl_sync(0xffffffffu, base, 31);
+        }
+        return base + incl - count;
+    };
+    auto put_emit = [&](uint32_t pos, int idx) {
+        if (pos < static_cast<uint32_t>(p.k)) {
+            const int64_t o = static_cast<int64_t>(r) * p.k + pos;
+            if (p.raw) p.raw[o] = idx;
+            p.page_indices[o] = page_of(p, r, idx);
+        }
+    };
+    auto put_park = [&](uint32_t slot, int idx, uint32_t key) {
+        if (slot < static_cast<uint32_t>(kCandCap)) {
+            s.cand_key[slot] = key;
+            s.cand_idx[slot] = idx;
+        }
+    };
+    if (vec_ok) {
+        const int n4 = n >> 2;
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        for (int base = lo >> 2; base < n4; base += kThreads * kClsBatch) {
+            float4 v[kClsBatch];
+#pragma unroll
+            for (int u = 0; u < kClsBatch; ++u) {
+                const int i = base + u * kThreads + threadIdx.x;
+                v[u] = i < n4 ? __ldcg(row4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            uint32_t park = 0, emit_m = 0;
+#pragma unroll
+            for (int u = 0; u < kClsBatch; ++u) {
+                const bool valid = base + u * kThreads + static_cast<int>(threadIdx.x) < n4;
+                const float x[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int cl = valid ? cls(x[c]) : 0;
+                    park |= static_cast<uint32_t>(cl == 1) << (u * 4 + c);
+                    emit_m |= static_cast<uint32_t>(cl == 2) << (u * 4 + c);
+                }
+            }
+            uint32_t park_at = reserve(__popc(park), &s.cand_count);
+            uint32_t emit_at = reserve(__popc(emit_m), &s.out_count);
+            if ((park | emit_m) != 0) {
+#pragma unroll
+                for (int u = 0; u < kClsBatch; ++u) {
+                    const int i = base + u * kThreads + threadIdx.x;
+                    const float x[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        if ((park >> (u * 4 + c)) & 1u) put_park(park_at++, 4 * i + c, key_of(x[c]));
+                        if ((emit_m >> (u * 4 + c)) & 1u) put_emit(emit_at++, 4 * i + c);
+                    }
+                }
+            }
+        }
+        if ((n & 3) != 0) {   // at most 3 leftover elements
+            const int i = (n4 << 2) + threadIdx.x;
+            const float x = i < n ? row[i] : 0.f;
+            const uint32_t key = key_of(x);
+            const int cl = (i < n && lo < hi) ? cls(x) : 0;
+            const uint32_t slot = warp_reserve(cl == 1, &s.cand_count);
+            if (cl == 1) put_park(slot, i, key);
+            const uint32_t pos = warp_reserve(cl == 2, &s.out_count);
+            if (cl == 2) put_emit(pos, i);
+        }
+    } else {
+        for (int base = lo; base < n; base += kThreads) {
+            const int i = base + threadIdx.x;
+            const float x = i < n ? row[i] : 0.f;
+            const uint32_t key = key_of(x);
+            const int cl = i < n ? cls(x) : 0;
+            const uint32_t slot = warp_reserve(cl == 1, &s.cand_count);
+            if (cl == 1) put_park(slot, i, key);
+            const uint32_t pos = warp_reserve(cl == 2, &s.out_count);
+            if (cl == 2) put_emit(pos, i);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     Shared& s = *reinterpret_cast<Shared*>(smem_raw);
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int crank = static_cast<int>(cluster.block_rank());
+    const int csize = static_cast<int>(cluster.num_blocks());
+    Shared& lead = *cluster.map_shared_rank(&s, 0);   // the cluster leader's shared memory
 
-    for (int r = blockIdx.x; r < p.rows; r += gridDim.x) {
+    // A cluster of csize CTAs (1, 2 or 4: the host uses the SMs that rows alone would leave
+    // idle) takes one row at a time.  Only the scan of a long row
+    // is shared (every CTA classifies its slice and parks candidates in the leader's
+    // shared memory); the selection among the candidates runs in the leader alone.
+    for (int r = blockIdx.x / csize; r < p.rows; r += gridDim.x / csize) {
         const float* row = p.scores + static_cast<int64_t>(r) * p.score_stride;
         int n = p.seq_lens[r];
         n = n < 0 ? 0 : n;
         if (static_cast<int64_t>(n) > p.score_stride) n = static_cast<int>(p.score_stride);
         const int k = p.k;
 
+        const bool sampled = n >= 4 * k && k <= kCandCap / 2;
+        if (crank != 0 && !sampled) continue;   // short rows are the leader's alone
         if (n <= k) {  // everything is selected: [0..n) then -1
             for (int i = threadIdx.x; i < k; i += kThreads) {
                 const int64_t o = static_cast<int64_t>(r) * k + i;
@@ -207,7 +347,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
         // ------------------------------------------------ sampled path: build the candidate list
         bool have_all = false;      // candidate list holds EVERY element at or above some digit
         int ncand = 0;
-        if (n >= 4 * k && k <= kCandCap / 2) {
+        uint32_t key_lo = 0;        // lower bound of the sampled scan's candidate keys
+        if (sampled) {
+            cluster.sync();   // the leader's counters are zeroed before anyone parks into them
             for (int t = threadIdx.x; t < kSamples; t += kThreads) {
                 const int i = static_cast<int>(static_cast<long long>(t) * n / kSamples);
                 atomicAdd(&s.hist[key_of(row[i]) >> 20], 1u);
@@ -220,17 +362,17 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
             find_threshold(s, kBins, rank);
             const uint32_t d_lo = s.sel_digit;
             __syncthreads();
-            for_each_elem(row, n, vec_ok, [&](int i, float x, bool valid) {
-                const uint32_t key = key_of(x);
-                const bool take = valid && (key >> 20) >= d_lo;
-                const uint32_t slot = warp_reserve(take, &s.cand_count);
-                if (take && slot < static_cast<uint32_t>(kCandCap)) {
-                    s.cand_key[slot] = key;
-                    s.cand_idx[slot] = i;
-                }
-            });
+            // every CTA of the cluster found the same d_lo (same samples); each scans a slice
+            const int slice = ((n + csize - 1) / csize + 3) & ~3;
+            const int lo = min(n, crank * slice), hi = min(n, lo + slice);
+            // digit >= d_lo  <=>  key >= d_lo << 20  <=>  x >= the float with that key: one
+            // compare per element (an unordered bound selects nothing and the row falls back)
+            key_lo = d_lo << 20;
+            const float x_lo = float_of_key(key_lo);
+            classify_pass(row, lo, hi, vec_ok, p, lead, r, [&](float x) { return x >= x_lo ? 1 : 0; });
             zero_hist(s, kBins);
-            __syncthreads();
+            cluster.sync();   // all slices are parked
+            if (crank != 0) continue;
             const uint32_t total = s.cand_count;
             have_all = total >= static_cast<uint32_t>(k) && total <= static_cast<uint32_t>(kCandCap);
             ncand = have_all ? static_cast<int>(total) : 0;
@@ -239,10 +381,51 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
             __syncthreads();
         }
 
+        uint32_t thr, need3;        // threshold key; how many values equal to it are still taken
+        bool take_all_equal;
+        bool done = false;
+        const int ncand_pad = (ncand + kThreads - 1) / kThreads * kThreads;
+        if (have_all) {
+            // ------------------------------------------------ candidates from the sampled scan
+            // Their keys start at key_lo = d_lo << 20.  A 4096-bin histogram of
+            // (key - key_lo) >> 12 resolves 20 key bits at once with little contention (the
+            // candidates spread over many bins); one more level on the low 12 bits finishes.
+            // Keys beyond the window share the last bin; if the threshold lands there
+            // (never for ordinary data) the generic three-level path below takes over.
+            for (int c = threadIdx.x; c < ncand; c += kThreads)
+                atomicAdd(&s.hist[min((s.cand_key[c] - key_lo) >> 12, static_cast<uint32_t>(kBins - 1))], 1u);
+            __syncthreads();
+            find_threshold(s, kBins, static_cast<uint32_t>(k));
+            const uint32_t bin_a = s.sel_digit;
+            const uint32_t need_a = static_cast<uint32_t>(k) - s.sel_above;
+            __syncthreads();
+            zero_hist(s, kBins);
+            __syncthreads();
+            if (bin_a != static_cast<uint32_t>(kBins - 1)) {
+                const uint32_t prefix20 = (key_lo >> 12) + bin_a;
+                for (int c = threadIdx.x; c < ncand; c += kThreads) {
+                    const uint32_t key = s.cand_key[c];
+                    if ((key >> 12) == prefix20) atomicAdd(&s.hist[key & 0xFFFu], 1u);
+                }
+                __syncthreads();
+                find_threshold(s, kBins, need_a);
+                const uint32_t d_b = s.sel_digit;
+                need3 = need_a - s.sel_above;
+                take_all_equal = (s.hist[d_b] == need3);
+                thr = (prefix20 << 12) | d_b;
+                __syncthreads();
+                for (int c = threadIdx.x; c < ncand_pad; c += kThreads) {
+                    const uint32_t key = c < ncand ? s.cand_key[c] : 0u;
+                    const bool ok = c < ncand && (key > thr || (key == thr && take_all_equal));
+                    emit(p, s, r, ok ? s.cand_idx[c] : 0, ok);
+                }
+                done = true;
+            }
+        }
+        if (!done) {
         // ------------------------------------------------ level 1: the top 12 bits
         uint32_t d1, need1;
         bool parked;                // the threshold digit's members are in the candidate list
-        const int ncand_pad = (ncand + kThreads - 1) / kThreads * kThreads;
         if (have_all) {
             for (int c = threadIdx.x; c < ncand; c += kThreads) atomicAdd(&s.hist[s.cand_key[c] >> 20], 1u);
             __syncthreads();
@@ -268,18 +451,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
             parked = s.hist[d1] <= static_cast<uint32_t>(kCandCap);
             __syncthreads();
             // pass 2: emit everything above the digit, park the digit's members
-            for_each_elem(row, n, vec_ok, [&](int i, float x, bool valid) {
-                const uint32_t key = key_of(x);
-                const uint32_t d = key >> 20;
-                emit(p, s, r, i, valid && d > d1);
-                if (parked) {
-                    const bool take = valid && d == d1;
-                    const uint32_t slot = warp_reserve(take, &s.cand_count);
-                    if (take && slot < static_cast<uint32_t>(kCandCap)) {
-                        s.cand_key[slot] = key;
-                        s.cand_idx[slot] = i;
-                    }
-                }
+            classify_pass(row, 0, n, vec_ok, p, s, r, [&](float x) {
+                const uint32_t d = key_of(x) >> 20;
+                return d > d1 ? 2 : ((d == d1 && parked) ? 1 : 0);
             });
             zero_hist(s, kBins);
             __syncthreads();
@@ -324,15 +498,16 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
         __syncthreads();
         find_threshold(s, 256, need2);
         const uint32_t d3 = s.sel_digit;
-        const uint32_t need3 = need2 - s.sel_above;   // how many values equal to the threshold are taken
+        need3 = need2 - s.sel_above;
         const uint32_t ceq = s.hist[d3];
-        const uint32_t thr = (prefix24 << 8) | d3;
-        const bool take_all_equal = (ceq == need3);
+        thr = (prefix24 << 8) | d3;
+        take_all_equal = (ceq == need3);
         __syncthreads();
 
         for_each_member([&](int i, uint32_t key, bool in) {
             emit(p, s, r, i, in && (key > thr || (key == thr && take_all_equal)));
         });
+        }
 
         if (!take_all_equal) {
             // More duplicates of the threshold value than needed: take the lowest indices.
@@ -420,8 +595,23 @@ extern "C" int wuda_topk(const float* scores, const int32_t* seq_lens, const int
 
     const int smem = static_cast<int>(sizeof(Shared));
     WUDA_CUDA(cudaFuncSetAttribute(topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    const int grid = rows < dev.num_sms * 2 ? rows : dev.num_sms * 2;
-    topk_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    // One 1024-thread CTA fills an SM; when there are fewer rows than SMs the spare SMs
+    // join the rows' clusters.
+    int kCluster = 1;
+    while (kCluster < kMaxCluster && rows * kCluster * 2 <= dev.num_sms) kCluster *= 2;
+    const int clusters = rows * kCluster <= dev.num_sms ? rows : dev.num_sms / kCluster;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(clusters * kCluster), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kCluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    WUDA_CUDA(cudaLaunchKernelEx(&cfg, topk_kernel, p));
     return WUDA_OK;
 }
