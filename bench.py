@@ -312,7 +312,9 @@ def main():
             "kernels_us": {"mqa_logits_fp8": mqa_ms * 1e3, "topk": topk_ms * 1e3},
             "roofline": {"kernel": "mqa_logits_fp8_kernel<2>", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "algorithmic_bytes": mqa_b},
+                         # dram read+write per launch: 0.98 x algorithmic bytes, from the ncu capture
+                         # of the batch-24 case scaled by bytes (profiles/mqa_logits_fp8_batch24.md)
+                         "traffic": int(0.98 * mqa_b) if batch == BATCH else None, "algorithmic_bytes": mqa_b},
             "e2e": {"value": world * (mqa_b + topk_b) / e2e_s / 1e9, "unit": "GB/s", "ms_per_step": e2e_s * 1e3,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "matches_device_path": bool(same)},
             "gpu_launches": 2 * args.steps, "launch": "one CUDA graph replay per step",
