@@ -118,6 +118,45 @@ int wuda_topk(const float* scores, const int32_t* seq_lens, const int32_t* page_
               void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * RMSNorm + 1x128 FP8 quantisation in one pass over a bf16 row.
+ *
+ *   y = bf16( gamma * (x * rsqrt(mean(x^2) + eps)) )           (gamma == NULL: y = x)
+ *   per 128 elements of y: amax = max(|y|, 1e-4); scale = amax / 448 (scale_mode 0) or
+ *   2^ceil(log2(amax / 448)) (scale_mode 1); y_fp8 = e4m3(clamp(y / scale, +-448))
+ *
+ * Numerics: origin/model.py:191-196 (RMSNorm) and origin/kernel.py:40-125 (act_quant).
+ * Stands in for qnorm_quant_kernel (kernels/wq_b_fp8_gemm.cu:139-183) and for the
+ * attn_norm + FP8 tail of hc_reduce_fuse_out (kernels/hc_fused_kernel_tc.cu:319-335).
+ *
+ *   x_bf16   bf16 [rows, x_row_stride] (first `dim` of each row are used; 16-byte aligned)
+ *   gamma    fp32 or bf16 [dim] (gamma_is_bf16), nullable
+ *   y_bf16   bf16 [rows, dim], nullable;  y_fp8 e4m3 [rows, dim], nullable
+ *   y_scales fp32 [rows, dim/128], required with y_fp8;  dim % 128 == 0, dim <= 24576
+ */
+int wuda_rmsnorm_quant_fp8(const void* x_bf16, int64_t x_row_stride, const void* gamma, int gamma_is_bf16,
+                           float eps, void* y_bf16, void* y_fp8, float* y_scales, int rows, int dim,
+                           int scale_mode, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Partial RoPE + 1x128 FP8 quantisation in one pass.
+ *
+ * x is bf16 [tokens, heads, head_dim]; the LAST rope_dim dims of every head are rotated in
+ * interleaved pairs by the angle of positions[t] (cos/sin tables fp32 [max_pos, rope_dim/2];
+ * inverse != 0 rotates backwards), rounded to bf16, and the flat row of heads*head_dim
+ * values is quantised per 128 consecutive elements as above.
+ *
+ * Numerics: origin/model.py:232-244 (apply_rotary_emb) and origin/kernel.py:40-125.
+ * Stands in for the FP8 indexer-q post (include/idx_post_fp4.cuh:229-283, rope tail +
+ * per-row e4m3), inv_rope_quant (kernels/mla_o_inv_rope_quant.cu:43-157, inverse = 1) and,
+ * with y_fp8 == NULL, for the RoPE half of rmsnorm_rope_out (kernels/rmsnorm_prod.cu:91-158).
+ * Positions outside [0, max_pos) are clamped.
+ */
+int wuda_rope_quant_fp8(const void* x_bf16, const int64_t* positions, const float* cos_table,
+                        const float* sin_table, void* y_bf16, void* y_fp8, float* y_scales, int tokens,
+                        int heads, int head_dim, int rope_dim, int max_pos, int inverse, int scale_mode,
+                        void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Host-buffer form of the indexer step: paged MQA logits, then top-k with the request's
  * block table as the page table (page_size = entries_per_block).
  *

@@ -212,6 +212,145 @@ int oracle_topk(const float* scores, const int32_t* seq_lens, const int32_t* pag
     return 0;
 }
 
+/* ------------------------------------------------------------------ RMSNorm
+ *
+ * y = bf16( gamma * (x * rsqrt(mean(x^2) + eps)) ), x bf16, fp32 math:
+ * dsv4_megakernel/origin/model.py:191-196 (RMSNorm.forward).  gamma is fp32 there (the
+ * checkpoint stores it in bf16, :188); both forms are accepted here (gamma_is_bf16).
+ */
+void oracle_rmsnorm_bf16(const uint16_t* x, const void* gamma, int gamma_is_bf16, float eps, uint16_t* y,
+                         int rows, int dim) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const uint16_t* xr = x + (int64_t)r * dim;
+        double ss = 0.0;
+        for (int i = 0; i < dim; ++i) {
+            const float v = bf16_to_f32(xr[i]);
+            ss += (double)v * v;
+        }
+        const float var = (float)(ss / dim);
+        const float rs = 1.0f / sqrtf(var + eps);
+        for (int i = 0; i < dim; ++i) {
+            const float g = gamma_is_bf16 ? bf16_to_f32(((const uint16_t*)gamma)[i]) : ((const float*)gamma)[i];
+            y[(int64_t)r * dim + i] = f32_to_bf16(g * (bf16_to_f32(xr[i]) * rs));
+        }
+    }
+}
+
+/* ------------------------------------------------------------------ block-wise FP8 quantisation
+ *
+ * Per `block` consecutive elements of a row: amax = max(|x|, 1e-4); scale = amax / 448,
+ * or (round_scale) 2^ceil(log2(amax / 448)); y = e4m3(clamp(x / scale, +-448)).
+ * dsv4_megakernel/origin/kernel.py:40-125 (act_quant_kernel; fast_round_scale :22-37).
+ * x is bf16, arithmetic in fp32; scales are returned as fp32.
+ */
+static float round_scale_pow2(float v) { /* kernel.py:22-37: 2^ceil(log2(v)) by bit manipulation */
+    uint32_t bits;
+    memcpy(&bits, &v, 4);
+    int e = (int)((bits >> 23) & 0xFF) - 127 + ((bits & 0x7FFFFFu) != 0 ? 1 : 0);
+    uint32_t out = (uint32_t)(e + 127) << 23;
+    float r;
+    memcpy(&r, &out, 4);
+    return r;
+}
+
+void oracle_act_quant_fp8(const uint16_t* x, uint8_t* y, float* scales, int rows, int dim, int block,
+                          int round_scale) {
+    const float fp8_max_inv = 1.0f / 448.0f;
+    const int groups = dim / block;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        for (int g = 0; g < groups; ++g) {
+            const uint16_t* xg = x + (int64_t)r * dim + (int64_t)g * block;
+            float amax = 0.0f;
+            for (int i = 0; i < block; ++i) {
+                const float a = fabsf(bf16_to_f32(xg[i]));
+                if (a > amax) amax = a;
+            }
+            if (amax < 1e-4f) amax = 1e-4f;
+            const float sc = round_scale ? round_scale_pow2(amax * fp8_max_inv) : amax * fp8_max_inv;
+            scales[(int64_t)r * groups + g] = sc;
+            for (int i = 0; i < block; ++i) {
+                float q = bf16_to_f32(xg[i]) / sc;
+                if (q > 448.0f) q = 448.0f;
+                if (q < -448.0f) q = -448.0f;
+                y[(int64_t)r * dim + (int64_t)g * block + i] = oracle_f32_to_e4m3(q);
+            }
+        }
+    }
+}
+
+/* ------------------------------------------------------------------ partial RoPE
+ *
+ * Rotates the LAST rope_dim dims of every head of x [tokens, heads, head_dim] (bf16) in
+ * interleaved pairs: (re, im) -> (re*c - im*s, re*s + im*c), conjugate when inverse, fp32
+ * math, result rounded back to bf16 in place of the input:
+ * dsv4_megakernel/origin/model.py:232-244 (apply_rotary_emb: view_as_complex of
+ * unflatten(-1, (-1, 2)), multiply by freqs_cis, copy back in the input dtype).
+ * cos/sin are fp32 [max_pos, rope_dim/2] tables, as the reference kernels take them
+ * (dsv4_megakernel/megakernel/kernels/rmsnorm_prod.cu:91-158).
+ */
+/* compiled without FMA contraction: a complex multiply is four products, one difference and
+ * one sum, each rounded to fp32 */
+__attribute__((optimize("fp-contract=off")))
+void oracle_rope_bf16(uint16_t* x, const int64_t* positions, const float* cos_t, const float* sin_t, int tokens,
+                      int heads, int head_dim, int rope_dim, int inverse) {
+    const int half = rope_dim / 2;
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < tokens; ++t) {
+        const float* c = cos_t + positions[t] * half;
+        const float* s = sin_t + positions[t] * half;
+        for (int h = 0; h < heads; ++h) {
+            uint16_t* v = x + ((int64_t)t * heads + h) * head_dim + (head_dim - rope_dim);
+            for (int i = 0; i < half; ++i) {
+                const float re = bf16_to_f32(v[2 * i]), im = bf16_to_f32(v[2 * i + 1]);
+                const float sn = inverse ? -s[i] : s[i];
+                v[2 * i] = f32_to_bf16(re * c[i] - im * sn);
+                v[2 * i + 1] = f32_to_bf16(re * sn + im * c[i]);
+            }
+        }
+    }
+}
+
+/* ------------------------------------------------------------------ block-scaled FP8 GEMM
+ *
+ * C[M,N] = A[M,K] @ B[N,K]^T, A and B e4m3, scales fp32: a_s [M, K/128] (1x128 blocks),
+ * b_s [N/128, K/128] (128x128 blocks).  Each 128-wide K block is accumulated in fp32 and
+ * then added, times a_s[m,kb] * b_s[n/128,kb], into a second fp32 accumulator:
+ * dsv4_megakernel/origin/kernel.py:203-273 (fp8_gemm_kernel, lines 246-250).  Output
+ * bf16 (out_bf16) or fp32.
+ */
+void oracle_gemm_fp8_blockscaled(const uint8_t* a, const float* a_s, const uint8_t* b, const float* b_s, void* c,
+                                 int M, int N, int K, int out_bf16) {
+    float lut[256];
+    for (int i = 0; i < 256; ++i) lut[i] = oracle_e4m3_to_f32((uint8_t)i);
+    const int kb_n = (K + 127) / 128;
+    float* af = (float*)malloc((size_t)M * K * sizeof(float));
+    for (int64_t i = 0; i < (int64_t)M * K; ++i) af[i] = lut[a[i]];
+#pragma omp parallel for schedule(dynamic, 16)
+    for (int n = 0; n < N; ++n) {
+        float bf[128];
+        float* acc = (float*)calloc((size_t)M, sizeof(float));
+        for (int kb = 0; kb < kb_n; ++kb) {
+            const int k0 = kb * 128, kl = (K - k0) < 128 ? (K - k0) : 128;
+            for (int k = 0; k < kl; ++k) bf[k] = lut[b[(int64_t)n * K + k0 + k]];
+            const float sb = b_s[(int64_t)(n / 128) * kb_n + kb];
+            for (int m = 0; m < M; ++m) {
+                const float* am = af + (int64_t)m * K + k0;
+                float part = 0.0f;
+                for (int k = 0; k < kl; ++k) part += am[k] * bf[k];
+                acc[m] += part * (a_s[(int64_t)m * kb_n + kb] * sb);
+            }
+        }
+        for (int m = 0; m < M; ++m) {
+            if (out_bf16) ((uint16_t*)c)[(int64_t)m * N + n] = f32_to_bf16(acc[m]);
+            else ((float*)c)[(int64_t)m * N + n] = acc[m];
+        }
+        free(acc);
+    }
+    free(af);
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -48,6 +48,12 @@ def _declare(l):
     l.oracle_topk.argtypes = [c.c_void_p] * 5 + [c.c_int, c.c_int64, c.c_int64, c.c_int, c.c_int]
     l.oracle_topk.restype = c.c_int
     l.oracle_num_threads.restype = c.c_int
+    l.oracle_rmsnorm_bf16.argtypes = [c.c_void_p, c.c_void_p, c.c_int, c.c_float, c.c_void_p, c.c_int, c.c_int]
+    l.oracle_act_quant_fp8.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int]
+    l.oracle_rope_bf16.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int,
+                                   c.c_int, c.c_int]
+    l.oracle_gemm_fp8_blockscaled.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
+                                              c.c_int, c.c_int, c.c_int, c.c_int]
 
 
 def _p(a):
@@ -113,3 +119,48 @@ def topk(scores, seq_lens, page_table, k, page_size=64):
     if rc != 0:
         raise ValueError("oracle_topk: page_size must be a power of two")
     return out, raw
+
+
+def rmsnorm_bf16(x_bf16, gamma, eps=1e-6):
+    """x: uint16 view of bf16 [rows, dim]; gamma fp32 [dim] or uint16 (bf16) [dim]. Returns uint16 (bf16)."""
+    x = _c(x_bf16, np.uint16)
+    is_bf16 = np.asarray(gamma).dtype == np.uint16
+    g = _c(gamma, np.uint16 if is_bf16 else np.float32)
+    y = np.empty_like(x)
+    lib().oracle_rmsnorm_bf16(_p(x), _p(g), int(is_bf16), eps, _p(y), x.shape[0], x.shape[1])
+    return y
+
+
+def act_quant_fp8(x_bf16, block=128, round_scale=False):
+    """x: uint16 view of bf16 [rows, dim]. Returns (e4m3 bytes [rows, dim], fp32 scales [rows, dim/block])."""
+    x = _c(x_bf16, np.uint16)
+    y = np.empty(x.shape, np.uint8)
+    s = np.empty((x.shape[0], x.shape[1] // block), np.float32)
+    lib().oracle_act_quant_fp8(_p(x), _p(y), _p(s), x.shape[0], x.shape[1], block, int(round_scale))
+    return y, s
+
+
+def rope_bf16(x_bf16, positions, cos_t, sin_t, rope_dim, inverse=False):
+    """x: uint16 view of bf16 [tokens, heads, head_dim]; rotates the last rope_dim dims. Returns a copy."""
+    x = _c(x_bf16, np.uint16).copy()
+    pos = _c(positions, np.int64)
+    cos_t, sin_t = _c(cos_t, np.float32), _c(sin_t, np.float32)
+    lib().oracle_rope_bf16(_p(x), _p(pos), _p(cos_t), _p(sin_t), x.shape[0], x.shape[1], x.shape[2], rope_dim,
+                           int(inverse))
+    return x
+
+
+def gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=True):
+    """a e4m3 bytes [M,K], a_s fp32 [M,K/128], b e4m3 bytes [N,K], b_s fp32 [N/128,K/128].
+    Returns uint16 (bf16) or fp32 [M,N]."""
+    a, b = _c(a, np.uint8), _c(b, np.uint8)
+    a_s, b_s = _c(a_s, np.float32), _c(b_s, np.float32)
+    m, k = a.shape
+    n = b.shape[0]
+    c = np.empty((m, n), np.uint16 if out_bf16 else np.float32)
+    lib().oracle_gemm_fp8_blockscaled(_p(a), _p(a_s), _p(b), _p(b_s), _p(c), m, n, k, int(out_bf16))
+    return c
+
+
+def bf16_to_f32(u16):
+    return (np.asarray(u16, np.uint16).astype(np.uint32) << 16).view(np.float32)

@@ -110,6 +110,50 @@ def golden_topk(ref_topk, name, rows, length, k, lens, tie_levels, seed):
     print(name, raw.shape)
 
 
+def _u16(t):
+    return t.view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def golden_norm_rope_quant(ref_root):
+    """RMSNorm and RoPE from the origin model (dsv4_megakernel/origin/model.py:183-196,
+    232-244), power-of-two 1x128 FP8 quantisation from the reference's torch twin
+    quant_act_fp8 (dsv4_megakernel/megakernel/test/test_front_mixed_gemm.py:75-83)."""
+    model = _load(ref_root, "dsv4_megakernel/origin/model.py", "ref_origin_model")
+    model.torch = torch          # the origin model needs the real module (nn.Module subclasses)
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(5, 7168, generator=g).bfloat16()
+    gamma = (1 + 0.1 * torch.randn(7168, generator=g)).bfloat16()
+    norm = model.RMSNorm(7168, 1e-6)
+    norm.weight.data = gamma.float()
+    y = norm(x)
+    np.savez_compressed(os.path.join(HERE, "rmsnorm_7168.npz"), x=_u16(x), gamma=_u16(gamma), eps=1e-6, y=_u16(y))
+    print("rmsnorm_7168.npz", tuple(y.shape))
+
+    tokens, heads, head_dim, rope_dim = 4, 8, 192, 64
+    xr = torch.randn(tokens, heads, head_dim, generator=g).bfloat16()
+    pos = torch.tensor([0, 3, 4097, 65535])
+    freqs = 1.0 / (10000 ** (torch.arange(0, rope_dim, 2, dtype=torch.float32) / rope_dim))
+    ang = torch.outer(torch.arange(65536).float(), freqs)
+    cis = torch.polar(torch.ones_like(ang), ang)
+    fwd = xr.clone()
+    model.apply_rotary_emb(fwd.view(1, tokens, heads, head_dim)[..., -rope_dim:], cis[pos])
+    inv = xr.clone()
+    model.apply_rotary_emb(inv.view(1, tokens, heads, head_dim)[..., -rope_dim:], cis[pos], inverse=True)
+    np.savez_compressed(os.path.join(HERE, "rope_192.npz"), x=_u16(xr), positions=pos.numpy(),
+                        cos=ang.cos()[pos.unique()].numpy(), sin=ang.sin()[pos.unique()].numpy(),
+                        table_rows=pos.unique().numpy(), rope_dim=rope_dim, y=_u16(fwd), y_inverse=_u16(inv))
+    print("rope_192.npz", tuple(fwd.shape))
+
+    front = _load(ref_root, "dsv4_megakernel/megakernel/test/test_front_mixed_gemm.py", "ref_front")
+    front.torch = torch
+    xq = (torch.randn(6, front.K, generator=g) * 0.1).bfloat16()
+    xq[0, :128] = 0                                   # an all-zero group: amax clamps at 1e-4
+    q, exp = front.quant_act_fp8(xq)
+    np.savez_compressed(os.path.join(HERE, "act_quant_pow2_7168.npz"), x=_u16(xq), q=q.view(torch.uint8).numpy(),
+                        scale=torch.pow(2.0, exp.float() - 127.0).numpy())
+    print("act_quant_pow2_7168.npz", tuple(q.shape))
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     tdir = "dsv4_megakernel/megakernel/test"
@@ -120,6 +164,7 @@ def main():
     ref_topk = _load(ref_root, tdir + "/test_topk_v2.py", "ref_topk")
     golden_topk(ref_topk, "topk_random.npz", 3, 3000, 512, [3000, 2100, 300], 0, 21)
     golden_topk(ref_topk, "topk_ties.npz", 2, 4096, 1024, [4096, 2500], 7, 22)
+    golden_norm_rope_quant(ref_root)
 
 
 if __name__ == "__main__":

@@ -75,3 +75,53 @@ def test_topk_oracle_trivial_rows():
     assert raw[0].tolist() == [0, 1, 2, 3, 4] + [-1] * 11
     assert raw[1].tolist() == [-1] * 16
     assert pages[0, :5].tolist() == [(100 << 6) + i for i in range(5)] and (pages[0, 5:] == -1).all()
+
+
+def test_rmsnorm_oracle_matches_origin_model():
+    g = load_golden("rmsnorm_7168.npz")
+    got = oracle.rmsnorm_bf16(g["x"], g["gamma"], float(g["eps"]))
+    assert np.array_equal(got, g["y"])
+
+
+def test_rope_oracle_matches_origin_model_forward_and_inverse():
+    g = load_golden("rope_192.npz")
+    rows = {int(p): i for i, p in enumerate(g["table_rows"])}
+    local_pos = np.array([rows[int(p)] for p in g["positions"]], np.int64)   # fixture stores only the used table rows
+    fwd = oracle.rope_bf16(g["x"], local_pos, g["cos"], g["sin"], int(g["rope_dim"]))
+    inv = oracle.rope_bf16(g["x"], local_pos, g["cos"], g["sin"], int(g["rope_dim"]), inverse=True)
+    assert np.array_equal(fwd, g["y"]) and np.array_equal(inv, g["y_inverse"])
+    # the first 128 dims of each head are untouched
+    assert np.array_equal(fwd[..., :128], g["x"][..., :128])
+
+
+def test_act_quant_oracle_matches_reference_pow2_twin():
+    g = load_golden("act_quant_pow2_7168.npz")
+    q, s = oracle.act_quant_fp8(g["x"], 128, round_scale=True)
+    assert np.array_equal(s, g["scale"])
+    assert np.array_equal(q, g["q"])
+
+
+def test_act_quant_oracle_fp32_scales_round_trip():
+    g = load_golden("act_quant_pow2_7168.npz")
+    q, s = oracle.act_quant_fp8(g["x"], 128, round_scale=False)
+    x = oracle.bf16_to_f32(g["x"]).reshape(6, -1, 128)
+    amax = np.maximum(np.abs(x).max(-1), 1e-4).astype(np.float32)
+    assert np.array_equal(s, amax * np.float32(1.0 / 448.0))
+    deq = oracle.e4m3_decode(q).reshape(6, -1, 128) * s[..., None]
+    assert np.max(np.abs(deq - x)) <= np.max(amax) / 448.0 * 16 * 1.01     # half a step of the top binade (step = 32 * scale)
+    # every group's largest element maps to +-448 exactly
+    assert np.all(np.abs(oracle.e4m3_decode(q).reshape(6, -1, 128)).max(-1)[amax > 1e-4] == 448.0)
+
+
+def test_gemm_fp8_oracle_equals_dequantised_matmul():
+    rng = np.random.default_rng(3)
+    m, n, k = 5, 256, 384
+    a = oracle.e4m3_encode(np.clip(rng.normal(size=(m, k)) * 100, -448, 448).astype(np.float32))
+    b = oracle.e4m3_encode(np.clip(rng.normal(size=(n, k)) * 100, -448, 448).astype(np.float32))
+    a_s = rng.uniform(0.5, 2, size=(m, k // 128)).astype(np.float32)
+    b_s = rng.uniform(0.5, 2, size=(n // 128, k // 128)).astype(np.float32)
+    got = oracle.gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=False)
+    ad = oracle.e4m3_decode(a).astype(np.float64) * np.repeat(a_s, 128, axis=1)
+    bd = oracle.e4m3_decode(b).astype(np.float64) * np.repeat(np.repeat(b_s, 128, axis=0), 128, axis=1)
+    ref = ad @ bd.T
+    assert np.max(np.abs(got - ref)) <= 1e-5 * np.max(np.abs(ref))

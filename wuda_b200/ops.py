@@ -12,7 +12,8 @@ from . import _lib
 from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
-           "IndexerHostPlan", "device_status_word", "num_sms"]
+           "IndexerHostPlan", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
+           "rmsnorm_rope_out"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -173,3 +174,76 @@ class IndexerHostPlan:
             self.close()
         except Exception:
             pass
+
+
+def rmsnorm_quant(x, gamma, eps=1e-6, *, quant=True, scale_fmt=None, return_bf16=True):
+    """RMSNorm(gamma, eps) of a bf16 [rows, dim] tensor and, in the same pass, its 1x128
+    FP8 quantisation.  Returns (y_bf16 or None, y_fp8 or None, scales or None).
+    scale_fmt: None = fp32 amax/448 scales, anything else = power-of-two scales, as the
+    origin's act_quant (origin/kernel.py:105-125).  gamma None = no normalisation."""
+    _require(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1,
+             "x must be CUDA bf16 [rows, dim] with unit inner stride")
+    rows, dim = x.shape
+    if gamma is not None:
+        _require(gamma.is_cuda and gamma.is_contiguous() and gamma.numel() == dim
+                 and gamma.dtype in (torch.float32, torch.bfloat16), "gamma must be CUDA fp32 or bf16 [dim]")
+    y16 = torch.empty((rows, dim), dtype=torch.bfloat16, device=x.device) if return_bf16 else None
+    y8 = torch.empty((rows, dim), dtype=torch.float8_e4m3fn, device=x.device) if quant else None
+    sc = torch.empty((rows, dim // 128), dtype=torch.float32, device=x.device) if quant else None
+    check(lib.wuda_rmsnorm_quant_fp8(x.data_ptr(), x.stride(0), gamma.data_ptr() if gamma is not None else None,
+                                     int(gamma is not None and gamma.dtype == torch.bfloat16), float(eps),
+                                     y16.data_ptr() if y16 is not None else None,
+                                     y8.data_ptr() if y8 is not None else None,
+                                     sc.data_ptr() if sc is not None else None, rows, dim,
+                                     0 if scale_fmt is None else 1, _stream()))
+    return y16, y8, sc
+
+
+def act_quant(x, block_size=128, scale_fmt=None):
+    """Block-wise FP8 quantisation with the origin's signature (origin/kernel.py:105):
+    returns (y float8_e4m3fn, scales fp32 [..., N/128])."""
+    _require(block_size == 128, "block_size must be 128")
+    shape = x.shape
+    _, y8, sc = rmsnorm_quant(x.reshape(-1, shape[-1]), None, quant=True, scale_fmt=scale_fmt, return_bf16=False)
+    return y8.view(shape), sc.view(*shape[:-1], shape[-1] // 128)
+
+
+def rope_quant(x, positions, cos_table, sin_table, rope_dim, *, inverse=False, quant=True, scale_fmt=None,
+               return_bf16=False):
+    """Partial RoPE of bf16 [tokens, heads, head_dim] (last rope_dim dims of each head) and,
+    in the same pass, 1x128 FP8 quantisation of the flat row.  Returns (y_bf16 or None,
+    y_fp8 [tokens, heads*head_dim] or None, scales or None)."""
+    _require(x.is_cuda and x.is_contiguous() and x.dtype == torch.bfloat16 and x.dim() == 3,
+             "x must be contiguous CUDA bf16 [tokens, heads, head_dim]")
+    tokens, heads, head_dim = x.shape
+    _require(positions.is_cuda and positions.is_contiguous() and positions.dtype == torch.int64
+             and positions.numel() == tokens, "positions must be contiguous CUDA int64 [tokens]")
+    _require(cos_table.is_cuda and cos_table.is_contiguous() and cos_table.dtype == torch.float32
+             and cos_table.dim() == 2 and cos_table.size(1) == rope_dim // 2 and sin_table.shape == cos_table.shape
+             and sin_table.is_cuda and sin_table.is_contiguous() and sin_table.dtype == torch.float32,
+             "cos/sin tables must be contiguous CUDA fp32 [max_pos, rope_dim/2]")
+    width = heads * head_dim
+    y16 = torch.empty_like(x) if return_bf16 else None
+    y8 = torch.empty((tokens, width), dtype=torch.float8_e4m3fn, device=x.device) if quant else None
+    sc = torch.empty((tokens, width // 128), dtype=torch.float32, device=x.device) if quant else None
+    check(lib.wuda_rope_quant_fp8(x.data_ptr(), positions.data_ptr(), cos_table.data_ptr(), sin_table.data_ptr(),
+                                  y16.data_ptr() if y16 is not None else None,
+                                  y8.data_ptr() if y8 is not None else None,
+                                  sc.data_ptr() if sc is not None else None, tokens, heads, head_dim, rope_dim,
+                                  cos_table.size(0), int(inverse), 0 if scale_fmt is None else 1, _stream()))
+    return y16, y8, sc
+
+
+def rmsnorm_rope_out(x, positions, cos_table, sin_table, out, input_heads=None, eps=1e-6, pdl=False, max_blocks=0):
+    """Per-head RMSNorm (no gamma) + RoPE on the last 64 dims, bf16 -> bf16, with the
+    reference's signature (kernels/rmsnorm_prod.cu:160-167); `out` is caller-owned."""
+    _require(x.is_cuda and x.is_contiguous() and x.dtype == torch.bfloat16 and x.dim() == 3,
+             "x must be contiguous CUDA bf16 [B, heads, 512]")
+    b, heads, d = x.shape
+    ones = torch.ones(d, dtype=torch.float32, device=x.device)
+    normed, _, _ = rmsnorm_quant(x.view(b * heads, d), ones, eps, quant=False)
+    rope_dim = cos_table.size(1) * 2
+    y16, _, _ = rope_quant(normed.view(b, heads, d), positions, cos_table, sin_table, rope_dim, quant=False,
+                           return_bf16=True)
+    out.copy_(y16 if out.shape == y16.shape else y16.repeat(1, out.size(1) // heads, 1))
+    return out
