@@ -157,6 +157,31 @@ int wuda_rope_quant_fp8(const void* x_bf16, const int64_t* positions, const floa
                         void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Block-scaled FP8 GEMM for decode-sized M:
+ *
+ *   c[m, n] = bf16( sum_kb a_s[m, kb] * w_s[n / 128, kb] * sum_{k in block kb} a[m, k] * w[n, k] )
+ *
+ * Each 128-wide K block is accumulated in fp32 and promoted with its scales into a second
+ * fp32 accumulator, as the origin's fp8_gemm does (origin/kernel.py:203-273; Python
+ * signature fp8_gemm(a, a_s, b, b_s) at :257).  It is the generic form of the reference's
+ * fixed-shape wq_b / wo_b projections (kernels/wq_b_fp8_gemm.cu:849-1365,
+ * test/o_proj_csa.py:454-480).
+ *
+ *   a         e4m3 [m, k], 16-byte aligned;   a_scales fp32 [m, k/128]
+ *   w         e4m3 [n, k], 16-byte aligned;   w_scales fp32 [ceil(n/128), k/128]
+ *   c_bf16    bf16 [m, n];   1 <= m <= 256, k % 128 == 0
+ *   scratch   device memory of at least wuda_gemm_fp8_scratch_bytes(m, n) bytes, 256-byte
+ *             aligned, ZERO before the first call; the kernel leaves it zero again, so the
+ *             same scratch can serve call after call (calls that share it must not overlap
+ *             on the GPU).  It holds the fp32 partial tiles of weight tiles whose K range is
+ *             split across SMs.
+ */
+int64_t wuda_gemm_fp8_scratch_bytes(int m, int n);
+int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* w, const float* w_scales,
+                              void* c_bf16, int m, int n, int k, void* scratch, int64_t scratch_bytes,
+                              int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Host-buffer form of the indexer step: paged MQA logits, then top-k with the request's
  * block table as the page table (page_size = entries_per_block).
  *

@@ -1,0 +1,429 @@
+// Block-scaled FP8 GEMM for decode-sized M on sm_100a:
+//
+//   C[M, N] (bf16) = A[M, K] (e4m3, fp32 scale per 1x128) x W[N, K]^T (e4m3, fp32 scale per 128x128)
+//
+// Numerics contract (dsv4_megakernel/origin/kernel.py:203-273, fp8_gemm_kernel): every
+// 128-wide K block is accumulated in fp32 on its own and then added, multiplied by
+// a_s[m, kb] * w_s[n / 128, kb], to a second fp32 accumulator (lines 246-250).  This is
+// the generic form of the reference's wq_b / wo_b projections
+// (dsv4_megakernel/megakernel/kernels/wq_b_fp8_gemm.cu:189-780, test/o_proj_csa.py:454-480),
+// which use power-of-two UE8M0 scales; fp32 scales cannot ride the tensor core's
+// block-scale path, so the promotion happens in registers.
+//
+// Design: decode GEMMs are bound by the weight stream (N*K bytes once from HBM), so
+//  * swap-AB: the UMMA M dimension (128) is a tile of weight rows, the UMMA N dimension
+//    is the padded activation count (16..256); the activations (a few MB at most) are
+//    re-read from L2 for every weight tile;
+//  * stream-K: the flat list of (weight tile, K block) units is cut into one equal
+//    contiguous range per SM, so every SM streams the same number of bytes whatever N is;
+//    a range that covers only part of a tile's K adds its fp32 partial to a scratch tile
+//    in global memory, and the last contributor converts the sum to bf16 and clears the
+//    scratch for the next call;
+//  * per unit: one TMA instruction fetches the weight tile (128 x 128 B) and the
+//    activation tile (M_PAD x 128 B), four tcgen05.mma kind::f8f6f4 fill a fresh TMEM
+//    stage, and two epilogue warpgroups (half the columns each) add the stage, times the
+//    unit's scales, to their register accumulators;
+//  * roles are replicated (2 producers, 2 issuers) and take units round-robin; stage
+//    counts are multiples of the role counts; every wait is bounded and reports through
+//    the status word.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "host.h"
+#include "ptx.cuh"
+
+namespace wuda {
+namespace gemm8 {
+
+constexpr int kTileN = 128;          // weight rows per tile (UMMA M)
+constexpr int kBlockK = 128;         // K per unit
+constexpr int kProducers = 2;        // warps 0, 1
+constexpr int kIssuers = 2;          // warps 2, 3
+constexpr int kFirstEpiWarp = 4;     // warps 4..11: two warpgroups, half the columns each
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
+constexpr int kWBytes = kTileN * kBlockK;   // 16 KB
+
+struct Params {
+    const float* a_scales;     // [M, K/128]
+    const float* w_scales;     // [ceil(N/128), K/128]
+    __nv_bfloat16* c;          // [M, N]
+    float* scratch;            // [n_tiles * 128, M_PAD] fp32, zero between calls
+    int32_t* counters;         // [n_tiles], zero between calls
+    int32_t* status;
+    int M, N, K, kb;           // kb = K / 128
+    int n_tiles;
+    int stages;
+};
+
+template <int M_PAD>
+struct Smem {
+    static constexpr int kABytes = M_PAD * kBlockK;
+    static constexpr int kStageBytes = kWBytes + kABytes;
+    static constexpr int kTmemStages = M_PAD <= 128 ? 4 : 2;
+    static constexpr int kTmemCols = kTmemStages * M_PAD < 32 ? 32 : kTmemStages * M_PAD;
+    static __host__ __device__ constexpr int scale_off(int stages) { return stages * kStageBytes; }
+    // scale ring: 4 slots x M_PAD floats
+    static __host__ __device__ constexpr int bar_off(int stages) { return scale_off(stages) + 4 * M_PAD * 4; }
+    // barriers: full[16] empty[16] full_tm[4] empty_tm[4]
+    static __host__ __device__ constexpr int misc_off(int stages) { return bar_off(stages) + 40 * 8; }
+    static __host__ __device__ constexpr int total(int stages) { return misc_off(stages) + 32 + 1024; }
+};
+
+struct Ring {
+    int idx = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void step(int n, int size) {   // n <= size
+        idx += n;
+        if (idx >= size) {
+            idx -= size;
+            phase ^= 1u;
+        }
+    }
+};
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// Range boundary of CTA c in the flat unit list.
+__device__ __forceinline__ long long range_begin(long long units, int c, int grid) { return units * c / grid; }
+// The CTA whose range holds unit u.
+__device__ __forceinline__ int cta_of(long long units, long long u, int grid) {
+    int c = static_cast<int>(u * grid / units);
+    while (c + 1 < grid && range_begin(units, c + 1, grid) <= u) ++c;
+    while (c > 0 && range_begin(units, c, grid) > u) --c;
+    return c;
+}
+
+template <int M_PAD>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap a_map,
+                const Params p) {
+    using L = Smem<M_PAD>;
+    constexpr int kTS = L::kTmemStages;
+    constexpr int kHalf = M_PAD / 2;                 // columns per epilogue warpgroup
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw_addr);
+    const int S = p.stages;
+    const uint32_t bars = base + L::bar_off(S);
+    const uint32_t full = bars, empty = bars + 16 * 8, full_tm = bars + 32 * 8, empty_tm = bars + 36 * 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + L::misc_off(S));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::misc_off(S) + 4);
+    int* last_flag = reinterpret_cast<int*>(base_ptr + L::misc_off(S) + 8);
+    float* scale_ring = reinterpret_cast<float*>(base_ptr + L::scale_off(S));
+
+    const int warp = threadIdx.x >> 5;
+    const uint32_t lane = lane_id();
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < S; ++i) {
+            mbar_init(full + i * 8, 1);
+            mbar_init(empty + i * 8, 1);          // released by the UMMA commit
+        }
+        for (int i = 0; i < kTS; ++i) {
+            mbar_init(full_tm + i * 8, 1);
+            mbar_init(empty_tm + i * 8, kEpiWarps);
+        }
+        fence_mbar_init();
+    }
+    if (warp == kProducers) {   // first issuer warp owns the TMEM allocation
+        tmem_alloc(smem_u32(tmem_slot), L::kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == 0 && lane == 0) {
+        prefetch_tmap(&w_map);
+        prefetch_tmap(&a_map);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const long long units = static_cast<long long>(p.n_tiles) * p.kb;
+    const long long u0 = range_begin(units, blockIdx.x, gridDim.x);
+    const long long u1 = range_begin(units, blockIdx.x + 1, gridDim.x);
+    const int count = static_cast<int>(u1 - u0);
+
+    if (warp < kProducers) {
+        // ------------------------------------------------------------ TMA producers
+        const int me = warp;
+        const uint64_t stream_policy = policy_evict_first();
+        const uint64_t keep_policy = policy_evict_last();
+        Ring ring;
+        ring.step(me, S);
+        int tile = static_cast<int>((u0 + me) / p.kb), kb = static_cast<int>((u0 + me) % p.kb);
+        bool alive = true;
+        for (int n = me; n < count && alive; n += kProducers) {
+            const int s = ring.idx;
+            alive = mbar_wait_lane0(empty + s * 8, ring.phase ^ 1u, abort_flag, p.status, kDevTimeoutGemmEmpty);
+            if (!alive) break;
+            if (lane == 0) mbar_arrive_expect_tx(full + s * 8, L::kStageBytes);
+            __syncwarp();
+            // one instruction, two lanes: lane 0 fetches the weight tile, lane 1 the activations
+            const uint32_t dst = base + s * L::kStageBytes + (lane == 1 ? kWBytes : 0);
+            const void* map = lane == 1 ? static_cast<const void*>(&a_map) : static_cast<const void*>(&w_map);
+            if (lane < 2)
+                tma_load_2d_hint(dst, map, full + s * 8, kb * kBlockK, lane == 1 ? 0 : tile * kTileN,
+                                 lane == 1 ? keep_policy : stream_policy);
+            ring.step(kProducers, S);
+            kb += kProducers;
+            while (kb >= p.kb) {
+                kb -= p.kb;
+                ++tile;
+            }
+        }
+    } else if (warp < kProducers + kIssuers) {
+        // ------------------------------------------------------------ UMMA issuers (one thread each)
+        if (lane == 0) {
+            const int me = warp - kProducers;
+            constexpr uint32_t idesc = umma_idesc(kTileN, M_PAD, 0, 0);
+            Ring ring, tring;
+            ring.step(me, S);
+            tring.step(me, kTS);
+            for (int n = me; n < count; n += kIssuers) {
+                const int s = ring.idx, ts = tring.idx;
+                if (!mbar_wait(full + s * 8, ring.phase, abort_flag, p.status, kDevTimeoutGemmFull)) break;
+                if (!mbar_wait(empty_tm + ts * 8, tring.phase ^ 1u, abort_flag, p.status, kDevTimeoutGemmTmemEmpty)) break;
+                tc_fence_after();
+                const uint32_t w_addr = base + s * L::kStageBytes;
+                const uint32_t a_addr = w_addr + kWBytes;
+                const uint32_t d_addr = tmem_base + ts * M_PAD;
+#pragma unroll
+                for (int k = 0; k < kBlockK / 32; ++k)
+                    umma_f8f6f4(d_addr, umma_smem_desc_sw128(w_addr + k * 32), umma_smem_desc_sw128(a_addr + k * 32),
+                                idesc, k > 0 ? 1u : 0u);
+                umma_commit(full_tm + ts * 8);
+                umma_commit(empty + s * 8);      // the stage's bytes are consumed once the UMMAs retire
+                ring.step(kIssuers, S);
+                tring.step(kIssuers, kTS);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps
+        // Thread = one weight row (TMEM lane) x half of the activation columns.
+        const int ew = warp - kFirstEpiWarp;            // 0..7
+        const int half = ew >> 2;                       // which half of the columns
+        const int et = (ew * 32 + lane);                // 0..255 among epilogue threads
+        const int row_in_tile = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        float acc[kHalf];
+#pragma unroll
+        for (int i = 0; i < kHalf; ++i) acc[i] = 0.f;
+        Ring tring;
+        bool alive = true;
+        int tile = static_cast<int>(u0 / p.kb), kb = static_cast<int>(u0 % p.kb);
+        int seg_kb0 = kb;                               // first K block of the running segment
+        // scale of unit n for activation row et: a_s[et, kb] * w_s[tile, kb]; slot n % 4 of the ring
+        auto load_scale = [&](int t, int k) -> float {
+            if (et >= p.M || t >= p.n_tiles) return 0.f;
+            return __ldg(p.a_scales + static_cast<int64_t>(et) * p.kb + k) *
+                   __ldg(p.w_scales + static_cast<int64_t>(t) * p.kb + k);
+        };
+        if (et < M_PAD && count > 0) scale_ring[et] = load_scale(tile, kb);
+        // An aborting CTA keeps walking the loop (every wait then fails at once) so that all
+        // 256 epilogue threads reach every named barrier; it only skips the arithmetic.
+        for (int n = 0; n < count; ++n) {
+            // stage the next unit's scales while this unit's accumulator is awaited
+            int ntile = tile, nkb = kb + 1;
+            if (nkb == p.kb) {
+                nkb = 0;
+                ++ntile;
+            }
+            float next_scale = 0.f;
+            if (et < M_PAD && n + 1 < count) next_scale = load_scale(ntile, nkb);
+            epi_bar_sync();                              // unit n's scales are visible to all epilogue threads
+            if (et < M_PAD && n + 1 < count) scale_ring[((n + 1) & 3) * M_PAD + et] = next_scale;
+            const int ts = tring.idx;
+            if (alive)
+                alive = mbar_wait_warp_fast(full_tm + ts * 8, tring.phase, abort_flag, p.status, kDevTimeoutGemmTmemFull);
+            if (alive) {
+            tc_fence_after();
+            const float* sc = scale_ring + (n & 3) * M_PAD + half * kHalf;
+            const uint32_t taddr = tmem_base + lane_base + ts * M_PAD + half * kHalf;
+            if constexpr (kHalf >= 32) {
+#pragma unroll
+                for (int c = 0; c < kHalf; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(taddr + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(__uint_as_float(v[i]), sc[c + i], acc[c + i]);
+                }
+            } else if constexpr (kHalf == 16) {
+                uint32_t v[16];
+                tmem_ld_32x16(taddr, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[i] = fmaf(__uint_as_float(v[i]), sc[i], acc[i]);
+            } else {
+                uint32_t v[8];
+                tmem_ld_32x8(taddr, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = fmaf(__uint_as_float(v[i]), sc[i], acc[i]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_tm + ts * 8);
+            }
+            tring.step(1, kTS);
+
+            // ---- end of a segment: the tile's K range ended, or this CTA's range did
+            const bool seg_end = (kb + 1 == p.kb) || (n + 1 == count);
+            if (seg_end) {
+                const int nrow = tile * kTileN + row_in_tile;
+                const bool whole = (seg_kb0 == 0) && (kb + 1 == p.kb);
+                if (!alive) {
+                    // nothing is published by an aborting CTA
+                } else if (whole) {
+                    if (nrow < p.N) {
+#pragma unroll
+                        for (int i = 0; i < kHalf; ++i) {
+                            const int m = half * kHalf + i;
+                            if (m < p.M) p.c[static_cast<int64_t>(m) * p.N + nrow] = __float2bfloat16_rn(acc[i]);
+                        }
+                    }
+                } else {
+                    float* sp = p.scratch + (static_cast<int64_t>(tile) * kTileN + row_in_tile) * M_PAD + half * kHalf;
+#pragma unroll
+                    for (int i = 0; i < kHalf; ++i) atomicAdd(sp + i, acc[i]);
+                    __threadfence();
+                    epi_bar_sync();
+                    if (et == 0) {
+                        const long long t0 = static_cast<long long>(tile) * p.kb;
+                        const int contributors = cta_of(units, t0 + p.kb - 1, gridDim.x) - cta_of(units, t0, gridDim.x) + 1;
+                        const int old = atomicAdd(p.counters + tile, 1);
+                        *last_flag = (old == contributors - 1) ? 1 : 0;
+                        if (old == contributors - 1) p.counters[tile] = 0;
+                    }
+                    epi_bar_sync();
+                    if (*last_flag) {
+                        __threadfence();
+#pragma unroll
+                        for (int i = 0; i < kHalf; ++i) {
+                            const float v = __ldcg(sp + i);
+                            __stcg(sp + i, 0.f);          // leave the scratch tile clear for the next call
+                            const int m = half * kHalf + i;
+                            if (nrow < p.N && m < p.M) p.c[static_cast<int64_t>(m) * p.N + nrow] = __float2bfloat16_rn(v);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kHalf; ++i) acc[i] = 0.f;
+                seg_kb0 = 0;
+            }
+            if (++kb == p.kb) {
+                kb = 0;
+                ++tile;
+            }
+        }
+    }
+
+    __syncthreads();
+    if (*abort_flag) abort_drain_sleep();
+    __syncthreads();
+    if (warp == kProducers) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, L::kTmemCols);
+    }
+}
+
+template <int M_PAD>
+static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p, const DeviceInfo& dev,
+                  cudaStream_t stream) {
+    using L = Smem<M_PAD>;
+    int stages = 16;
+    while (stages > 2 && L::total(stages) > dev.smem_optin) stages -= 2;
+    if (L::total(stages) > dev.smem_optin)
+        return fail(WUDA_ERR_UNSUPPORTED, "device offers %d bytes of shared memory per block; the kernel needs more",
+                    dev.smem_optin);
+    p.stages = stages;
+    auto kernel = gemm_fp8_kernel<M_PAD>;
+    WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total(stages)));
+    const long long units = static_cast<long long>(p.n_tiles) * p.kb;
+    const int grid = units < dev.num_sms ? static_cast<int>(units) : dev.num_sms;
+    kernel<<<grid, kThreads, L::total(stages), stream>>>(w_map, a_map, p);
+    WUDA_CUDA(cudaGetLastError());
+    return WUDA_OK;
+}
+
+}  // namespace gemm8
+}  // namespace wuda
+
+extern "C" int64_t wuda_gemm_fp8_scratch_bytes(int m, int n) {
+    if (m < 1 || n < 1 || m > 256) return -1;
+    int m_pad = 16;
+    while (m_pad < m) m_pad *= 2;
+    const int64_t n_tiles = (n + 127) / 128;
+    // fp32 partial tiles, then one counter per tile (kept 256-byte aligned)
+    return n_tiles * 128 * m_pad * 4 + ((n_tiles * 4 + 255) / 256) * 256;
+}
+
+extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* w, const float* w_scales,
+                                         void* c_bf16, int m, int n, int k, void* scratch, int64_t scratch_bytes,
+                                         int32_t* status_word, void* stream) {
+    using namespace wuda;
+    using namespace wuda::gemm8;
+    clear_error();
+    WUDA_REQUIRE(m >= 0 && m <= 256, "m must be in [0, 256] (got %d)", m);
+    WUDA_REQUIRE(n >= 1, "n must be >= 1 (got %d)", n);
+    WUDA_REQUIRE(k >= 128 && k % 128 == 0, "k must be a positive multiple of 128 (got %d)", k);
+    if (m == 0) return WUDA_OK;
+    WUDA_REQUIRE(a && a_scales && w && w_scales && c_bf16 && scratch,
+                 "a, a_scales, w, w_scales, c and scratch must not be NULL");
+    WUDA_REQUIRE(aligned16(a) && aligned16(w), "a and w must be 16-byte aligned");
+    WUDA_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "scratch must be 256-byte aligned");
+    const int64_t need = wuda_gemm_fp8_scratch_bytes(m, n);
+    WUDA_REQUIRE(scratch_bytes >= need, "scratch holds %lld bytes; %lld are needed (wuda_gemm_fp8_scratch_bytes)",
+                 static_cast<long long>(scratch_bytes), static_cast<long long>(need));
+
+    DeviceInfo dev;
+    int st = current_device_info(&dev);
+    if (st != WUDA_OK) return st;
+
+    int m_pad = 16;
+    while (m_pad < m) m_pad *= 2;
+    Params p;
+    p.a_scales = a_scales;
+    p.w_scales = w_scales;
+    p.c = static_cast<__nv_bfloat16*>(c_bf16);
+    p.status = status_word;
+    p.M = m;
+    p.N = n;
+    p.K = k;
+    p.kb = k / 128;
+    p.n_tiles = (n + 127) / 128;
+    p.scratch = static_cast<float*>(scratch);
+    p.counters = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) +
+                                            static_cast<int64_t>(p.n_tiles) * 128 * m_pad * 4);
+    p.stages = 0;
+
+    CUtensorMap w_map, a_map;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+        const uint32_t box[2] = {128u, 128u};
+        st = encode_tensor_map(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (st != WUDA_OK) return st;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+        const uint32_t box[2] = {128u, static_cast<uint32_t>(m_pad)};
+        st = encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+        if (st != WUDA_OK) return st;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (m_pad) {
+        case 16: return launch<16>(w_map, a_map, p, dev, s);
+        case 32: return launch<32>(w_map, a_map, p, dev, s);
+        case 64: return launch<64>(w_map, a_map, p, dev, s);
+        case 128: return launch<128>(w_map, a_map, p, dev, s);
+        default: return launch<256>(w_map, a_map, p, dev, s);
+    }
+}

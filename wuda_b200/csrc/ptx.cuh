@@ -117,7 +117,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // (the instruction itself suspends the thread for a while); the clock and the abort
 // flag are consulted only after many failed polls, because reading %globaltimer on
 // every wait adds its latency to each producer/consumer hand-off.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                             int* status_word, int code) {
     const unsigned long long t0 = globaltimer_ns();
     uint32_t spins = 0;
@@ -345,6 +345,14 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr)
+        : "memory");
+}
+
 // Warp-wide wait whose common case (phase already complete) costs one poll and one
 // vote: all lanes test the barrier together; only when that fails does lane 0 take the
 // polling loop and broadcast the outcome.

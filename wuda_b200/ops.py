@@ -13,7 +13,7 @@ from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
-           "rmsnorm_rope_out"]
+           "rmsnorm_rope_out", "fp8_gemm"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -246,4 +246,42 @@ def rmsnorm_rope_out(x, positions, cos_table, sin_table, out, input_heads=None, 
     y16, _, _ = rope_quant(normed.view(b, heads, d), positions, cos_table, sin_table, rope_dim, quant=False,
                            return_bf16=True)
     out.copy_(y16 if out.shape == y16.shape else y16.repeat(1, out.size(1) // heads, 1))
+    return out
+
+
+_gemm_scratch = {}
+
+
+def _scratch_for(device, nbytes):
+    """A zeroed scratch buffer per device, grown on demand (the GEMM leaves it zero)."""
+    buf = _gemm_scratch.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _gemm_scratch[device] = buf
+    return buf
+
+
+def fp8_gemm(a, a_s, b, b_s, scale_dtype=torch.float32, *, out=None, status_word=None):
+    """C[M,N] = A[M,K] @ B[N,K]^T with 1x128 (A) and 128x128 (B) fp32 block scales, bf16
+    output: the origin's fp8_gemm(a, a_s, b, b_s) (origin/kernel.py:257-273)."""
+    _require(scale_dtype == torch.float32, "only fp32 scales are implemented")
+    _require(a.is_cuda and a.is_contiguous() and a.dtype == torch.float8_e4m3fn, "a must be contiguous CUDA e4m3")
+    _require(b.is_cuda and b.is_contiguous() and b.dtype == torch.float8_e4m3fn and b.dim() == 2,
+             "b must be contiguous CUDA e4m3 [N, K]")
+    k = a.size(-1)
+    m = a.numel() // k
+    n = b.size(0)
+    _require(b.size(1) == k, "a and b disagree on K")
+    _require(a_s.is_cuda and a_s.is_contiguous() and a_s.dtype == torch.float32 and a_s.numel() == m * (k // 128),
+             "a_s must be contiguous CUDA fp32 [M, K/128]")
+    _require(b_s.is_cuda and b_s.is_contiguous() and b_s.dtype == torch.float32
+             and tuple(b_s.shape) == ((n + 127) // 128, k // 128), "b_s must be contiguous CUDA fp32 [ceil(N/128), K/128]")
+    if out is None:
+        out = torch.empty(*a.shape[:-1], n, dtype=torch.bfloat16, device=a.device)
+    need = lib.wuda_gemm_fp8_scratch_bytes(m, n)
+    _require(need >= 0, "m must be in [1, 256]")
+    scratch = _scratch_for(a.device, need)
+    check(lib.wuda_gemm_fp8_blockscaled(a.data_ptr(), a_s.data_ptr(), b.data_ptr(), b_s.data_ptr(), out.data_ptr(),
+                                        m, n, k, scratch.data_ptr(), scratch.numel(),
+                                        status_word.data_ptr() if status_word is not None else None, _stream()))
     return out

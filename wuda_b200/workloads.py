@@ -76,3 +76,38 @@ def to_device(case, device="cuda"):
     for k in ("kv_pages", "weights", "context_lens", "block_table"):
         out[k] = torch.from_numpy(case[k]).to(device)
     return out
+
+
+def quantize_fp8_1x128(x):
+    """fp32 [M, K] -> (e4m3 bytes [M, K], fp32 scales [M, K/128]); scale = max(amax, 1e-4) / 448
+    (origin/kernel.py:79-83)."""
+    m, k = x.shape
+    v = torch.as_tensor(x, dtype=torch.float32).view(m, k // 128, 128)
+    s = v.abs().amax(-1).clamp_min(1e-4) * (1.0 / 448.0)
+    q = (v / s.unsqueeze(-1)).clamp(-448, 448).view(m, k)
+    return _e4m3_bytes(q), s.numpy().astype(np.float32)
+
+
+def quantize_fp8_128x128(w):
+    """fp32 [N, K] -> (e4m3 bytes [N, K], fp32 scales [ceil(N/128), K/128])."""
+    n, k = w.shape
+    nt = (n + 127) // 128
+    wp = torch.zeros(nt * 128, k)
+    wp[:n] = torch.as_tensor(w, dtype=torch.float32)
+    v = wp.view(nt, 128, k // 128, 128)
+    s = v.abs().amax(dim=(1, 3)).clamp_min(1e-4) * (1.0 / 448.0)
+    q = (v / s[:, None, :, None]).clamp(-448, 448).view(nt * 128, k)[:n]
+    return _e4m3_bytes(q.contiguous()), s.numpy().astype(np.float32)
+
+
+def make_gemm_fp8_case(m, n, k, seed=0xB202):
+    """Activations ~ N(0,1), weights ~ N(0, 0.02), quantised to e4m3 with 1x128 / 128x128 fp32 scales."""
+    g = torch.Generator().manual_seed(int(seed))
+    a, a_s = quantize_fp8_1x128(torch.randn(m, k, generator=g))
+    w, w_s = quantize_fp8_128x128(torch.randn(n, k, generator=g) * 0.02)
+    return dict(a=a, a_s=a_s, w=w, w_s=w_s, m=m, n=n, k=k)
+
+
+def gemm_fp8_algorithmic_bytes(m, n, k):
+    """N*K weights + their scales + M*K activations + their scales + M*N bf16 output."""
+    return n * k + ((n + 127) // 128) * (k // 128) * 4 + m * k + m * (k // 128) * 4 + m * n * 2
