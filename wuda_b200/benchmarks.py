@@ -1,0 +1,104 @@
+"""Per-operator timing tables for the rows of the hot path that bench.py (the indexer
+step) does not cover.  Device time with CUDA events over CUDA-graph replays, cold L2
+between launches is not forced: weights (>= 15 MB) are re-streamed from HBM every launch
+because consecutive launches use different weight buffers that together exceed L2.
+
+    python -m wuda_b200.benchmarks gemm_fp8
+    python -m wuda_b200.benchmarks norm_rope_quant
+"""
+import json
+import os
+import sys
+
+import torch
+
+import wuda_b200 as wuda
+from wuda_b200 import workloads
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def time_graph(fn, reps=20, inner=10):
+    """Mean device time (us) of one call of fn, from graphs of `inner` calls."""
+    fn()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(inner):
+                fn()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * inner)
+
+
+def gemm_fp8():
+    hbm, tf, kind = peaks()
+    print("block-scaled FP8 GEMM, bf16 out; peaks (%s): %.0f GB/s HBM, %.0f TFLOP/s dense bf16 (fp8 nominal = 2x)" % (kind, hbm, tf))
+    print("%6s %6s %6s %9s %9s %8s %9s %8s" % ("M", "N", "K", "us", "GB/s", "of HBM", "TFLOP/s", "of 2xbf16"))
+    for n, k in ((24576, 7168), (7168, 16384), (2112, 7168), (4096, 7168)):
+        for m in (1, 8, 32, 64, 128, 256):
+            # enough distinct weight buffers that a launch never finds its weights in the 126 MB L2
+            copies = max(2, int(300e6 // (n * k)) + 1)
+            cases = [workloads.make_gemm_fp8_case(m, n, k, seed=7)]
+            a = torch.from_numpy(cases[0]["a"]).cuda().view(torch.float8_e4m3fn)
+            a_s = torch.from_numpy(cases[0]["a_s"]).cuda()
+            w0 = torch.from_numpy(cases[0]["w"]).cuda()
+            ws = [w0.clone().view(torch.float8_e4m3fn) for _ in range(copies)]
+            w_s = torch.from_numpy(cases[0]["w_s"]).cuda()
+            out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            state = {"i": 0}
+
+            def fn():
+                wuda.fp8_gemm(a, a_s, ws[state["i"] % copies], w_s, out=out)
+                state["i"] += 1
+
+            us = time_graph(fn, reps=10, inner=copies * 2)
+            by = workloads.gemm_fp8_algorithmic_bytes(m, n, k)
+            gbs = by / us / 1e3
+            tfl = 2.0 * m * n * k / us / 1e6
+            print("%6d %6d %6d %9.1f %9.0f %7.1f%% %9.1f %7.1f%%" % (m, n, k, us, gbs, 100 * gbs / hbm, tfl, 100 * tfl / (2 * tf)))
+            del ws
+
+
+def norm_rope_quant():
+    hbm, _, kind = peaks()
+    print("fused RMSNorm+quant and RoPE+quant; HBM peak (%s) %.0f GB/s" % (kind, hbm))
+    for tokens in (1, 64, 256):
+        g = torch.Generator().manual_seed(1)
+        x = torch.randn(tokens, 7168, generator=g).bfloat16().cuda()
+        gamma = torch.ones(7168).bfloat16().cuda()
+        us = time_graph(lambda: wuda.rmsnorm_quant(x, gamma, 1e-6))
+        by = tokens * 7168 * 2 + 14336 + tokens * 7168 * 3 + tokens * 56 * 4
+        print("rmsnorm_quant tokens %4d: %7.2f us %7.0f GB/s" % (tokens, us, by / us / 1e3))
+        proj = torch.randn(tokens, 128, 192, generator=g).bfloat16().cuda()
+        pos = torch.randint(0, 65536, (tokens,), generator=g).cuda()
+        freqs = 1.0 / (10000 ** (torch.arange(0, 64, 2, dtype=torch.float32) / 64))
+        ang = torch.outer(torch.arange(65536).float(), freqs)
+        cos, sin = ang.cos().cuda().contiguous(), ang.sin().cuda().contiguous()
+        us = time_graph(lambda: wuda.rope_quant(proj, pos, cos, sin, 64))
+        by = tokens * 24576 * 2 + tokens * 8 + tokens * 24576 + tokens * 192 * 4
+        print("rope_quant    tokens %4d: %7.2f us %7.0f GB/s" % (tokens, us, by / us / 1e3))
+
+
+if __name__ == "__main__":
+    which = sys.argv[1] if len(sys.argv) > 1 else "gemm_fp8"
+    {"gemm_fp8": gemm_fp8, "norm_rope_quant": norm_rope_quant}[which]()

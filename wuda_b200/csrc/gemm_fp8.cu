@@ -16,9 +16,9 @@
 //    re-read from L2 for every weight tile;
 //  * stream-K: the flat list of (weight tile, K block) units is cut into one equal
 //    contiguous range per SM, so every SM streams the same number of bytes whatever N is;
-//    a range that covers only part of a tile's K adds its fp32 partial to a scratch tile
-//    in global memory, and the last contributor converts the sum to bf16 and clears the
-//    scratch for the next call;
+//    a range that does not start a tile's K range writes its fp32 partial to the CTA's own
+//    scratch slot in global memory and raises a flag; the CTA holding the start of the
+//    range adds the partials in CTA order (deterministic) and writes the bf16 tile;
 //  * per unit: one TMA instruction fetches the weight tile (128 x 128 B) and the
 //    activation tile (M_PAD x 128 B), four tcgen05.mma kind::f8f6f4 fill a fresh TMEM
 //    stage, and two epilogue warpgroups (half the columns each) add the stage, times the
@@ -44,13 +44,15 @@ constexpr int kFirstEpiWarp = 4;     // warps 4..11: two warpgroups, half the co
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
 constexpr int kWBytes = kTileN * kBlockK;   // 16 KB
+constexpr int kScaleSlots = 8;       // scale ring depth
+constexpr int kScaleAhead = 6;       // units of look-ahead of the scale fetch (< kScaleSlots - 1)
 
 struct Params {
     const float* a_scales;     // [M, K/128]
     const float* w_scales;     // [ceil(N/128), K/128]
     __nv_bfloat16* c;          // [M, N]
-    float* scratch;            // [n_tiles * 128, M_PAD] fp32, zero between calls
-    int32_t* counters;         // [n_tiles], zero between calls
+    float* scratch;            // [grid][M_PAD][128] fp32: one partial-tile slot per CTA
+    int32_t* flags;            // [grid]: slot c is published; zero between calls
     int32_t* status;
     int M, N, K, kb;           // kb = K / 128
     int n_tiles;
@@ -64,8 +66,10 @@ struct Smem {
     static constexpr int kTmemStages = M_PAD <= 128 ? 4 : 2;
     static constexpr int kTmemCols = kTmemStages * M_PAD < 32 ? 32 : kTmemStages * M_PAD;
     static __host__ __device__ constexpr int scale_off(int stages) { return stages * kStageBytes; }
-    // scale ring: 4 slots x M_PAD floats
-    static __host__ __device__ constexpr int bar_off(int stages) { return scale_off(stages) + 4 * M_PAD * 4; }
+    // scale rings: kScaleSlots x (M_PAD activation scales) + kScaleSlots weight scales
+    static __host__ __device__ constexpr int bar_off(int stages) {
+        return scale_off(stages) + kScaleSlots * M_PAD * 4 + kScaleSlots * 4;
+    }
     // barriers: full[16] empty[16] full_tm[4] empty_tm[4]
     static __host__ __device__ constexpr int misc_off(int stages) { return bar_off(stages) + 40 * 8; }
     static __host__ __device__ constexpr int total(int stages) { return misc_off(stages) + 32 + 1024; }
@@ -84,6 +88,22 @@ struct Ring {
 };
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void st_release_gpu(int32_t* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int32_t* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 // Range boundary of CTA c in the flat unit list.
 __device__ __forceinline__ long long range_begin(long long units, int c, int grid) { return units * c / grid; }
@@ -111,8 +131,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     const uint32_t full = bars, empty = bars + 16 * 8, full_tm = bars + 32 * 8, empty_tm = bars + 36 * 8;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + L::misc_off(S));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::misc_off(S) + 4);
-    int* last_flag = reinterpret_cast<int*>(base_ptr + L::misc_off(S) + 8);
-    float* scale_ring = reinterpret_cast<float*>(base_ptr + L::scale_off(S));
+    float* a_ring = reinterpret_cast<float*>(base_ptr + L::scale_off(S));
+    float* w_ring = a_ring + kScaleSlots * M_PAD;
 
     const int warp = threadIdx.x >> 5;
     const uint32_t lane = lane_id();
@@ -216,58 +236,68 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         bool alive = true;
         int tile = static_cast<int>(u0 / p.kb), kb = static_cast<int>(u0 % p.kb);
         int seg_kb0 = kb;                               // first K block of the running segment
-        // scale of unit n for activation row et: a_s[et, kb] * w_s[tile, kb]; slot n % 4 of the ring
-        auto load_scale = [&](int t, int k) -> float {
-            if (et >= p.M || t >= p.n_tiles) return 0.f;
-            return __ldg(p.a_scales + static_cast<int64_t>(et) * p.kb + k) *
-                   __ldg(p.w_scales + static_cast<int64_t>(t) * p.kb + k);
+
+        // Scales of unit n (activation scales a_s[:, kb], weight scale w_s[tile, kb]) are
+        // fetched kScaleAhead units early with 4-byte asynchronous copies into rings of
+        // kScaleSlots slots, so their L2 latency never sits between two units.
+        int ftile = tile, fkb = kb;                     // the unit the next fetch is for
+        auto fetch_scales = [&](int n_fetch) {
+            if (n_fetch < count) {
+                const int slot = n_fetch & (kScaleSlots - 1);
+                if (et < p.M)
+                    cp_async4(smem_u32(a_ring + slot * M_PAD + et), p.a_scales + static_cast<int64_t>(et) * p.kb + fkb);
+                if (et == 255)
+                    cp_async4(smem_u32(w_ring + slot), p.w_scales + static_cast<int64_t>(ftile) * p.kb + fkb);
+                if (++fkb == p.kb) {
+                    fkb = 0;
+                    ++ftile;
+                }
+            }
+            cp_async_commit();                           // one group per unit, empty or not
         };
-        if (et < M_PAD && count > 0) scale_ring[et] = load_scale(tile, kb);
+        for (int n = 0; n < kScaleAhead; ++n) fetch_scales(n);
+
         // An aborting CTA keeps walking the loop (every wait then fails at once) so that all
         // 256 epilogue threads reach every named barrier; it only skips the arithmetic.
         for (int n = 0; n < count; ++n) {
-            // stage the next unit's scales while this unit's accumulator is awaited
-            int ntile = tile, nkb = kb + 1;
-            if (nkb == p.kb) {
-                nkb = 0;
-                ++ntile;
-            }
-            float next_scale = 0.f;
-            if (et < M_PAD && n + 1 < count) next_scale = load_scale(ntile, nkb);
-            epi_bar_sync();                              // unit n's scales are visible to all epilogue threads
-            if (et < M_PAD && n + 1 < count) scale_ring[((n + 1) & 3) * M_PAD + et] = next_scale;
+            fetch_scales(n + kScaleAhead);
+            cp_async_wait<kScaleAhead>();                // this thread's copies for unit n have landed
+            epi_bar_sync();                              // ... and so have everybody else's
             const int ts = tring.idx;
             if (alive)
                 alive = mbar_wait_warp_fast(full_tm + ts * 8, tring.phase, abort_flag, p.status, kDevTimeoutGemmTmemFull);
             if (alive) {
-            tc_fence_after();
-            const float* sc = scale_ring + (n & 3) * M_PAD + half * kHalf;
-            const uint32_t taddr = tmem_base + lane_base + ts * M_PAD + half * kHalf;
-            if constexpr (kHalf >= 32) {
+                tc_fence_after();
+                const int slot = n & (kScaleSlots - 1);
+                const float wsc = w_ring[slot];
+                const float* sc = a_ring + slot * M_PAD + half * kHalf;
+                const uint32_t taddr = tmem_base + lane_base + ts * M_PAD + half * kHalf;
+                if constexpr (kHalf >= 32) {
 #pragma unroll
-                for (int c = 0; c < kHalf; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(taddr + c, v);
+                    for (int c = 0; c < kHalf; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld_32x32(taddr + c, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            acc[c + i] = fmaf(__uint_as_float(v[i]), sc[c + i] * wsc, acc[c + i]);
+                    }
+                } else if constexpr (kHalf == 16) {
+                    uint32_t v[16];
+                    tmem_ld_32x16(taddr, v);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(__uint_as_float(v[i]), sc[c + i], acc[c + i]);
+                    for (int i = 0; i < 16; ++i) acc[i] = fmaf(__uint_as_float(v[i]), sc[i] * wsc, acc[i]);
+                } else {
+                    uint32_t v[8];
+                    tmem_ld_32x8(taddr, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] = fmaf(__uint_as_float(v[i]), sc[i] * wsc, acc[i]);
                 }
-            } else if constexpr (kHalf == 16) {
-                uint32_t v[16];
-                tmem_ld_32x16(taddr, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 16; ++i) acc[i] = fmaf(__uint_as_float(v[i]), sc[i], acc[i]);
-            } else {
-                uint32_t v[8];
-                tmem_ld_32x8(taddr, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[i] = fmaf(__uint_as_float(v[i]), sc[i], acc[i]);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty_tm + ts * 8);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_tm + ts * 8);
             }
             tring.step(1, kTS);
 
@@ -275,39 +305,55 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
             const bool seg_end = (kb + 1 == p.kb) || (n + 1 == count);
             if (seg_end) {
                 const int nrow = tile * kTileN + row_in_tile;
-                const bool whole = (seg_kb0 == 0) && (kb + 1 == p.kb);
-                if (!alive) {
-                    // nothing is published by an aborting CTA
-                } else if (whole) {
-                    if (nrow < p.N) {
+                const bool from_zero = (seg_kb0 == 0), to_end = (kb + 1 == p.kb);
+                if (!from_zero) {
+                    // A partial that does not start the tile's K range goes to this CTA's slot;
+                    // the CTA that holds the start of the range collects it.  Layout
+                    // [column][row]: a warp's 32 rows are contiguous.
+                    float* slot = p.scratch + static_cast<int64_t>(blockIdx.x) * (M_PAD * kTileN) + row_in_tile;
+                    if (alive) {
+#pragma unroll
+                        for (int i = 0; i < kHalf; ++i) __stcg(slot + (half * kHalf + i) * kTileN, acc[i]);
+                    }
+                    __threadfence();
+                    epi_bar_sync();
+                    if (et == 0 && alive) st_release_gpu(p.flags + blockIdx.x, 1);
+                } else {
+                    if (!to_end) {
+                        // This CTA holds the start of the tile's K range and the range continues in
+                        // the following CTAs (all resident: the grid is one CTA per SM).  Add their
+                        // partials in CTA order, so the sum does not depend on timing.
+                        const long long t_end = static_cast<long long>(tile + 1) * p.kb - 1;
+                        const int last = cta_of(units, t_end, gridDim.x);
+                        for (int c = blockIdx.x + 1; c <= last; ++c) {
+                            if (et == 0 && alive) {
+                                const unsigned long long start = globaltimer_ns();
+                                uint32_t spins = 0;
+                                while (ld_acquire_gpu(p.flags + c) == 0) {
+                                    if ((++spins & 255u) == 0u && (*abort_flag || globaltimer_ns() - start > kWaitLimitNs)) {
+                                        *abort_flag = 1;
+                                        if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeerFlag);
+                                        break;
+                                    }
+                                    __nanosleep(64);
+                                }
+                            }
+                            epi_bar_sync();
+                            alive = alive && !*abort_flag;
+                            if (alive) {
+                                const float* peer = p.scratch + static_cast<int64_t>(c) * (M_PAD * kTileN) + row_in_tile;
+#pragma unroll
+                                for (int i = 0; i < kHalf; ++i) acc[i] += __ldcg(peer + (half * kHalf + i) * kTileN);
+                            }
+                            epi_bar_sync();
+                            if (et == 0 && alive) p.flags[c] = 0;     // the slot is free for the next call
+                        }
+                    }
+                    if (alive && nrow < p.N) {
 #pragma unroll
                         for (int i = 0; i < kHalf; ++i) {
                             const int m = half * kHalf + i;
                             if (m < p.M) p.c[static_cast<int64_t>(m) * p.N + nrow] = __float2bfloat16_rn(acc[i]);
-                        }
-                    }
-                } else {
-                    float* sp = p.scratch + (static_cast<int64_t>(tile) * kTileN + row_in_tile) * M_PAD + half * kHalf;
-#pragma unroll
-                    for (int i = 0; i < kHalf; ++i) atomicAdd(sp + i, acc[i]);
-                    __threadfence();
-                    epi_bar_sync();
-                    if (et == 0) {
-                        const long long t0 = static_cast<long long>(tile) * p.kb;
-                        const int contributors = cta_of(units, t0 + p.kb - 1, gridDim.x) - cta_of(units, t0, gridDim.x) + 1;
-                        const int old = atomicAdd(p.counters + tile, 1);
-                        *last_flag = (old == contributors - 1) ? 1 : 0;
-                        if (old == contributors - 1) p.counters[tile] = 0;
-                    }
-                    epi_bar_sync();
-                    if (*last_flag) {
-                        __threadfence();
-#pragma unroll
-                        for (int i = 0; i < kHalf; ++i) {
-                            const float v = __ldcg(sp + i);
-                            __stcg(sp + i, 0.f);          // leave the scratch tile clear for the next call
-                            const int m = half * kHalf + i;
-                            if (nrow < p.N && m < p.M) p.c[static_cast<int64_t>(m) * p.N + nrow] = __float2bfloat16_rn(v);
                         }
                     }
                 }
@@ -320,6 +366,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
                 ++tile;
             }
         }
+        cp_async_wait<0>();
     }
 
     __syncthreads();
@@ -353,13 +400,15 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p,
 }  // namespace gemm8
 }  // namespace wuda
 
+// Scratch = one fp32 partial tile [M_PAD][128] per CTA, then one flag per CTA.  The grid
+// never exceeds kMaxGrid CTAs (one per SM).
+constexpr int kMaxGrid = 192;
+
 extern "C" int64_t wuda_gemm_fp8_scratch_bytes(int m, int n) {
     if (m < 1 || n < 1 || m > 256) return -1;
     int m_pad = 16;
     while (m_pad < m) m_pad *= 2;
-    const int64_t n_tiles = (n + 127) / 128;
-    // fp32 partial tiles, then one counter per tile (kept 256-byte aligned)
-    return n_tiles * 128 * m_pad * 4 + ((n_tiles * 4 + 255) / 256) * 256;
+    return static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4 + kMaxGrid * 4;
 }
 
 extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* w, const float* w_scales,
@@ -397,8 +446,8 @@ extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, c
     p.kb = k / 128;
     p.n_tiles = (n + 127) / 128;
     p.scratch = static_cast<float*>(scratch);
-    p.counters = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) +
-                                            static_cast<int64_t>(p.n_tiles) * 128 * m_pad * 4);
+    p.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
+    WUDA_REQUIRE(dev.num_sms <= kMaxGrid, "device has %d SMs; at most %d are supported", dev.num_sms, kMaxGrid);
     p.stages = 0;
 
     CUtensorMap w_map, a_map;
