@@ -181,6 +181,21 @@ int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* 
                               void* c_bf16, int m, int n, int k, void* scratch, int64_t scratch_bytes,
                               int32_t* status_word, void* stream);
 
+/* The same GEMM for callers that cannot provide scratch memory and must not trigger a device
+ * allocation (a process that has handed all device memory to its own pool, a loop in which
+ * cudaMalloc would stall the device).  No counterpart in the reference.  The scratch is a fixed
+ * 6,292,224-byte array inside the library's device image, present on every GPU that loads the
+ * library until the process exits; the entry point allocates nothing and frees nothing.
+ * Limits and rules: m <= 64 (larger m is refused with WUDA_ERR_UNSUPPORTED); calls on one
+ * device share the array, so they must not overlap on the GPU (issue them on one stream, or
+ * order the streams); the first call on each device looks the array's address up and should
+ * therefore be made once before any stream capture begins.  Results are identical to
+ * wuda_gemm_fp8_blockscaled.
+ */
+int wuda_gemm_fp8_blockscaled_noalloc(const void* a, const float* a_scales, const void* w,
+                                      const float* w_scales, void* c_bf16, int m, int n, int k,
+                                      int32_t* status_word, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Host-buffer form of the indexer step: paged MQA logits, then top-k with the request's
  * block table as the page table (page_size = entries_per_block).

@@ -30,6 +30,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "host.h"
 #include "ptx.cuh"
 
@@ -474,5 +476,118 @@ extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, c
         case 64: return launch<64>(w_map, a_map, p, dev, s);
         case 128: return launch<128>(w_map, a_map, p, dev, s);
         default: return launch<256>(w_map, a_map, p, dev, s);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free entry point.
+//
+// Some hosts must never see a device allocation from a library they call: a serving process
+// that carved up all device memory at start-up and hands it out through its own pool (a stray
+// cudaMalloc can fail there, or fragment what is left), and latency-critical loops in which
+// cudaMalloc / cudaFree would synchronise the whole device and stall every other stream.  The
+// regular entry point leaves the scratch to the caller; this one needs no scratch argument at
+// all: the partial-tile slots and flags of the stream-K fix-up live in a fixed array inside the
+// library's device image.  The price is a limit on m (kNoAllocMaxM) and kNoAllocScratchBytes of
+// device memory held by every GPU that loads the library, until the process exits.
+//
+// The array is shared by every call on a device and keeps what the last call left in it.  The
+// partial tiles are always written before they are read, so only the flags have to start at
+// zero; the kernel resets each flag after use, and the entry point clears all of them again
+// before every launch in case an earlier call ended abnormally.  Two calls that overlap on the
+// GPU (different streams) would race on the slots: calls through this entry point must be
+// ordered one after another on the device.
+constexpr int kNoAllocMaxM = 64;
+constexpr int64_t kNoAllocSlotBytes = static_cast<int64_t>(kMaxGrid) * kNoAllocMaxM * 128 * 4;
+constexpr int64_t kNoAllocScratchBytes = kNoAllocSlotBytes + kMaxGrid * 4;   // 6,292,224 bytes
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// The array's name is only a handle in host code; the device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static int noalloc_scratch_address(int device, void** out) {
+    static std::mutex mu;
+    static void* cached[64] = {};
+    if (device < 0 || device >= 64) return wuda::fail(WUDA_ERR_UNSUPPORTED, "device ordinal %d out of range", device);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[device]) {
+        void* ptr = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (err != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return wuda::fail(WUDA_ERR_CUDA, "cudaGetSymbolAddress(no-alloc scratch) failed: %s", cudaGetErrorString(err));
+        }
+        cached[device] = ptr;
+    }
+    *out = cached[device];
+    return WUDA_OK;
+}
+
+extern "C" int wuda_gemm_fp8_blockscaled_noalloc(const void* a, const float* a_scales, const void* w,
+                                                 const float* w_scales, void* c_bf16, int m, int n, int k,
+                                                 int32_t* status_word, void* stream) {
+    using namespace wuda;
+    using namespace wuda::gemm8;
+    clear_error();
+    WUDA_REQUIRE(m >= 0, "m must be >= 0 (got %d)", m);
+    if (m > kNoAllocMaxM)
+        return fail(WUDA_ERR_UNSUPPORTED,
+                    "the allocation-free entry point handles m <= %d (got %d): its built-in scratch is %lld bytes; "
+                    "use wuda_gemm_fp8_blockscaled with caller-provided scratch for larger m",
+                    kNoAllocMaxM, m, static_cast<long long>(kNoAllocScratchBytes));
+    WUDA_REQUIRE(n >= 1, "n must be >= 1 (got %d)", n);
+    WUDA_REQUIRE(k >= 128 && k % 128 == 0, "k must be a positive multiple of 128 (got %d)", k);
+    if (m == 0) return WUDA_OK;
+    WUDA_REQUIRE(a && a_scales && w && w_scales && c_bf16, "a, a_scales, w, w_scales and c must not be NULL");
+    WUDA_REQUIRE(aligned16(a) && aligned16(w), "a and w must be 16-byte aligned");
+
+    DeviceInfo dev;
+    int st = current_device_info(&dev);
+    if (st != WUDA_OK) return st;
+    WUDA_REQUIRE(dev.num_sms <= kMaxGrid, "device has %d SMs; at most %d are supported", dev.num_sms, kMaxGrid);
+    void* scratch = nullptr;
+    st = noalloc_scratch_address(dev.device, &scratch);   // first call on a device: symbol lookup
+    if (st != WUDA_OK) return st;
+
+    int m_pad = 16;
+    while (m_pad < m) m_pad *= 2;
+    Params p;
+    p.a_scales = a_scales;
+    p.w_scales = w_scales;
+    p.c = static_cast<__nv_bfloat16*>(c_bf16);
+    p.status = status_word;
+    p.M = m;
+    p.N = n;
+    p.K = k;
+    p.kb = k / 128;
+    p.n_tiles = (n + 127) / 128;
+    p.scratch = static_cast<float*>(scratch);
+    p.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + kNoAllocSlotBytes);
+    p.stages = 0;
+
+    CUtensorMap w_map, a_map;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+        const uint32_t box[2] = {128u, 128u};
+        st = encode_tensor_map(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (st != WUDA_OK) return st;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+        const uint32_t box[2] = {128u, static_cast<uint32_t>(m_pad)};
+        st = encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+        if (st != WUDA_OK) return st;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the flags must start at zero whatever the previous call left behind
+    WUDA_CUDA(cudaMemsetAsync(p.flags, 0, kMaxGrid * sizeof(int32_t), s));
+    switch (m_pad) {
+        case 16: return launch<16>(w_map, a_map, p, dev, s);
+        case 32: return launch<32>(w_map, a_map, p, dev, s);
+        default: return launch<64>(w_map, a_map, p, dev, s);
     }
 }
