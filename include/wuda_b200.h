@@ -181,6 +181,33 @@ int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* 
                               void* c_bf16, int m, int n, int k, void* scratch, int64_t scratch_bytes,
                               int32_t* status_word, void* stream);
 
+/* ------------------------------------------------------------------------------------
+ * Two-rank tensor-parallel FP8 GEMM with the all-reduce fused into its epilogue.
+ *
+ * The K dimension is split across two GPUs (a row-parallel linear, origin/model.py:166-180:
+ * per-rank partial products summed in fp32, then cast).  Each rank calls this function with
+ * its K slice; finished fp32 tiles are stored directly into the peer GPU's inbox over NVLink
+ * and the peer's tiles are added from the local inbox, so both ranks end with the same bf16
+ * c = bf16(partial_0 + partial_1).  No NCCL call is involved.  The reference's megakernel has
+ * no such collective (it fabricates the sum, test/test_e2e_decode.py:186-194).
+ *
+ * An inbox is device memory of wuda_tp2_inbox_bytes(m, n) bytes created by wuda_tp2_alloc,
+ * which also returns a 64-byte CUDA IPC handle; the peer process maps it with wuda_tp2_open
+ * (the handles travel by any host-side channel).  `epoch` is the call's sequence number: it
+ * must start at 1 and grow by one per call, identically on both ranks.  A wait for the peer
+ * that exceeds peer_wait_ms ends the kernel with WUDA_DEV_TIMEOUT_PEER_FLAG in status_word
+ * (c is then not fully written); nothing traps or hangs.
+ */
+int64_t wuda_tp2_inbox_bytes(int m, int n);
+int wuda_tp2_alloc(int64_t bytes, void** local_base, unsigned char* ipc_handle_64);
+int wuda_tp2_open(const unsigned char* ipc_handle_64, void** peer_base);
+int wuda_tp2_close(void* peer_base);
+int wuda_tp2_free(void* local_base);
+int wuda_gemm_fp8_blockscaled_tp2(const void* a, const float* a_scales, const void* w,
+                                  const float* w_scales, void* c_bf16, int m, int n, int k_local,
+                                  void* scratch, int64_t scratch_bytes, void* my_inbox, void* peer_inbox,
+                                  int epoch, int peer_wait_ms, int32_t* status_word, void* stream);
+
 /* The same GEMM for callers that cannot provide scratch memory and must not trigger a device
  * allocation (a process that has handed all device memory to its own pool, a loop in which
  * cudaMalloc would stall the device).  No counterpart in the reference.  The scratch is a fixed

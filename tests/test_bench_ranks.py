@@ -56,3 +56,34 @@ def test_reference_arm_prints_one_json_line():
     res = json.loads(out.stdout.strip().splitlines()[-1])
     assert res["impl"] == "reference" and res["cpu_baseline"]["kind"] == "port" and res["value"] > 0
     assert res["e2e"]["h2d_bytes_per_step"] == 0
+
+
+HANDLE_WORKER = textwrap.dedent("""
+    import os, sys, json
+    sys.path.insert(0, %r)
+    import torch.distributed as dist
+    dist.init_process_group("gloo")
+    from wuda_b200.ops import exchange_handles
+    rank = dist.get_rank()
+    mine = bytes([rank + 1] * 64)
+    peer = exchange_handles(mine)
+    ok = peer == bytes([2 - rank] * 64)
+    flags = [None, None]
+    dist.all_gather_object(flags, ok)
+    if rank == 0:
+        print(json.dumps({"ok": all(flags)}))
+    dist.destroy_process_group()
+""") % ROOT
+
+
+def test_tp2_handle_exchange_over_gloo(tmp_path):
+    """Host-side bootstrap of the two-rank link: each rank ends up with the other's 64-byte handle."""
+    script = tmp_path / "handles.py"
+    script.write_text(HANDLE_WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29593", str(script)],
+                         capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    import json
+    assert json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1]) == {"ok": True}

@@ -34,6 +34,13 @@ SIGNATURES = {
     "wuda_gemm_fp8_scratch_bytes": (c_i64, [c_int, c_int]),
     "wuda_gemm_fp8_blockscaled": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
     "wuda_gemm_fp8_blockscaled_noalloc": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp]),
+    "wuda_tp2_inbox_bytes": (c_i64, [c_int, c_int]),
+    "wuda_tp2_alloc": (c_int, [c_i64, ctypes.POINTER(c_vp), c_vp]),
+    "wuda_tp2_open": (c_int, [c_vp, ctypes.POINTER(c_vp)]),
+    "wuda_tp2_close": (c_int, [c_vp]),
+    "wuda_tp2_free": (c_int, [c_vp]),
+    "wuda_gemm_fp8_blockscaled_tp2": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp,
+                                              c_vp, c_int, c_int, c_vp, c_vp]),
     "wuda_topk": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_int, c_int, c_int, c_vp]),
 }
 

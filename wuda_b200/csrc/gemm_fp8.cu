@@ -30,6 +30,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstring>
 #include <mutex>
 
 #include "host.h"
@@ -59,6 +60,13 @@ struct Params {
     int M, N, K, kb;           // kb = K / 128
     int n_tiles;
     int stages;
+    // two-rank tensor parallelism (K split across two GPUs): peer exchange of fp32 tiles
+    float* tp_my_inbox = nullptr;      // [2 sets][n_tiles][M_PAD][128] fp32 in THIS GPU's memory
+    float* tp_peer_inbox = nullptr;    // the same buffer of the peer, mapped into this process
+    int32_t* tp_my_flags = nullptr;    // [2 sets][n_tiles]: sequence number of the last tile received
+    int32_t* tp_peer_flags = nullptr;
+    int tp_epoch = 0;                  // sequence number of this call (> 0, same on both ranks)
+    unsigned long long tp_wait_ns = 0; // limit of one wait for the peer
 };
 
 template <int M_PAD>
@@ -100,6 +108,19 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 __device__ __forceinline__ void st_release_gpu(int32_t* p, int v) {
     asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_volatile_f32(const float* p) {   // written by the peer GPU: bypass L1
+    float v;
+    asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
 }
 __device__ __forceinline__ int ld_acquire_gpu(const int32_t* p) {
     int v;
@@ -351,6 +372,44 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
                             if (et == 0 && alive) p.flags[c] = 0;     // the slot is free for the next call
                         }
                     }
+                    if (p.tp_peer_inbox) {
+                        // Two-rank all-reduce fused into the epilogue: the finished fp32 tile goes
+                        // straight into the peer GPU's inbox over NVLink (plain stores through the
+                        // peer mapping, then a system-scope release of the tile's flag), and the
+                        // peer's tile is awaited in this GPU's own inbox and added.  a + b == b + a
+                        // in fp32, so both ranks hold bit-identical sums.  Inbox sets alternate
+                        // with the call's sequence number: a rank can be one call ahead of its
+                        // peer's reads, never two.
+                        const int64_t set = static_cast<int64_t>(p.tp_epoch & 1) * p.n_tiles;
+                        const int64_t tile_off = (set + tile) * (M_PAD * kTileN) + row_in_tile;
+                        if (alive) {
+#pragma unroll
+                            for (int i = 0; i < kHalf; ++i)
+                                p.tp_peer_inbox[tile_off + (half * kHalf + i) * kTileN] = acc[i];
+                        }
+                        __threadfence_system();
+                        epi_bar_sync();
+                        if (et == 0 && alive) {
+                            st_release_sys(p.tp_peer_flags + set + tile, p.tp_epoch);
+                            const unsigned long long start = globaltimer_ns();
+                            uint32_t spins = 0;
+                            while (ld_acquire_sys(p.tp_my_flags + set + tile) != p.tp_epoch) {
+                                if ((++spins & 63u) == 0u && (*abort_flag || globaltimer_ns() - start > p.tp_wait_ns)) {
+                                    *abort_flag = 1;
+                                    if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeerFlag);
+                                    break;
+                                }
+                                __nanosleep(100);
+                            }
+                        }
+                        epi_bar_sync();
+                        alive = alive && !*abort_flag;
+                        if (alive) {
+#pragma unroll
+                            for (int i = 0; i < kHalf; ++i)
+                                acc[i] += ld_volatile_f32(p.tp_my_inbox + tile_off + (half * kHalf + i) * kTileN);
+                        }
+                    }
                     if (alive && nrow < p.N) {
 #pragma unroll
                         for (int i = 0; i < kHalf; ++i) {
@@ -589,5 +648,149 @@ extern "C" int wuda_gemm_fp8_blockscaled_noalloc(const void* a, const float* a_s
         case 16: return launch<16>(w_map, a_map, p, dev, s);
         case 32: return launch<32>(w_map, a_map, p, dev, s);
         default: return launch<64>(w_map, a_map, p, dev, s);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Two-rank tensor-parallel form: the K dimension is split across two GPUs (row-parallel
+// linear, dsv4_megakernel/origin/model.py:166-180: y = x_r W_r^T summed over ranks in fp32,
+// then cast; the reference's megakernel only fabricates this sum,
+// dsv4_megakernel/megakernel/test/test_e2e_decode.py:186-194).  Each rank runs the same GEMM on
+// its K slice; the all-reduce happens tile by tile inside the epilogue through peer memory.
+//
+// The exchange buffer of a rank ("inbox") is ordinary device memory made visible to the peer
+// process with CUDA IPC.  Layout: 2 sets x n_tiles flags (int32, padded to 4 KB), then
+// 2 sets x n_tiles x [M_PAD][128] fp32 tiles.
+namespace {
+constexpr int64_t kTpFlagBytes = 4096;
+
+int64_t tp_bytes(int m, int n) {
+    if (m < 1 || m > 256 || n < 1) return -1;
+    int m_pad = 16;
+    while (m_pad < m) m_pad *= 2;
+    const int64_t n_tiles = (n + 127) / 128;
+    if (2 * n_tiles * 4 > kTpFlagBytes) return -1;
+    return kTpFlagBytes + 2 * n_tiles * m_pad * 128 * 4;
+}
+}  // namespace
+
+extern "C" int64_t wuda_tp2_inbox_bytes(int m, int n) { return tp_bytes(m, n); }
+
+extern "C" int wuda_tp2_alloc(int64_t bytes, void** local_base, unsigned char* ipc_handle_64) {
+    using namespace wuda;
+    clear_error();
+    WUDA_REQUIRE(bytes > 0 && local_base && ipc_handle_64, "bytes must be > 0 and the outputs must not be NULL");
+    void* ptr = nullptr;
+    WUDA_CUDA(cudaMalloc(&ptr, static_cast<size_t>(bytes)));
+    cudaError_t err = cudaMemset(ptr, 0, static_cast<size_t>(bytes));
+    cudaIpcMemHandle_t h;
+    if (err == cudaSuccess) err = cudaIpcGetMemHandle(&h, ptr);
+    if (err != cudaSuccess) {
+        cudaFree(ptr);
+        cudaGetLastError();
+        return fail(WUDA_ERR_CUDA, "preparing the exchange buffer failed: %s", cudaGetErrorString(err));
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+    memcpy(ipc_handle_64, &h, 64);
+    *local_base = ptr;
+    return WUDA_OK;
+}
+
+extern "C" int wuda_tp2_open(const unsigned char* ipc_handle_64, void** peer_base) {
+    using namespace wuda;
+    clear_error();
+    WUDA_REQUIRE(ipc_handle_64 && peer_base, "handle and output must not be NULL");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, ipc_handle_64, 64);
+    WUDA_CUDA(cudaIpcOpenMemHandle(peer_base, h, cudaIpcMemLazyEnablePeerAccess));
+    return WUDA_OK;
+}
+
+extern "C" int wuda_tp2_close(void* peer_base) {
+    using namespace wuda;
+    clear_error();
+    if (peer_base) WUDA_CUDA(cudaIpcCloseMemHandle(peer_base));
+    return WUDA_OK;
+}
+
+extern "C" int wuda_tp2_free(void* local_base) {
+    using namespace wuda;
+    clear_error();
+    if (local_base) WUDA_CUDA(cudaFree(local_base));
+    return WUDA_OK;
+}
+
+extern "C" int wuda_gemm_fp8_blockscaled_tp2(const void* a, const float* a_scales, const void* w,
+                                             const float* w_scales, void* c_bf16, int m, int n, int k_local,
+                                             void* scratch, int64_t scratch_bytes, void* my_inbox, void* peer_inbox,
+                                             int epoch, int peer_wait_ms, int32_t* status_word, void* stream) {
+    using namespace wuda;
+    using namespace wuda::gemm8;
+    clear_error();
+    WUDA_REQUIRE(m >= 1 && m <= 256, "m must be in [1, 256] (got %d)", m);
+    WUDA_REQUIRE(n >= 1, "n must be >= 1 (got %d)", n);
+    WUDA_REQUIRE(k_local >= 128 && k_local % 128 == 0, "k_local must be a positive multiple of 128 (got %d)", k_local);
+    WUDA_REQUIRE(a && a_scales && w && w_scales && c_bf16 && scratch && my_inbox && peer_inbox,
+                 "a, a_scales, w, w_scales, c, scratch and both inboxes must not be NULL");
+    WUDA_REQUIRE(epoch >= 1, "epoch must be >= 1 and grow by one per call on both ranks (got %d)", epoch);
+    WUDA_REQUIRE(peer_wait_ms >= 1 && peer_wait_ms <= 10000, "peer_wait_ms must be in [1, 10000] (got %d)", peer_wait_ms);
+    WUDA_REQUIRE(aligned16(a) && aligned16(w), "a and w must be 16-byte aligned");
+    WUDA_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "scratch must be 256-byte aligned");
+    const int64_t need = wuda_gemm_fp8_scratch_bytes(m, n);
+    WUDA_REQUIRE(scratch_bytes >= need, "scratch holds %lld bytes; %lld are needed (wuda_gemm_fp8_scratch_bytes)",
+                 static_cast<long long>(scratch_bytes), static_cast<long long>(need));
+    WUDA_REQUIRE(tp_bytes(m, n) > 0, "n is too large for the exchange buffer's flag block");
+
+    DeviceInfo dev;
+    int st = current_device_info(&dev);
+    if (st != WUDA_OK) return st;
+    WUDA_REQUIRE(dev.num_sms <= kMaxGrid, "device has %d SMs; at most %d are supported", dev.num_sms, kMaxGrid);
+
+    int m_pad = 16;
+    while (m_pad < m) m_pad *= 2;
+    Params p;
+    p.a_scales = a_scales;
+    p.w_scales = w_scales;
+    p.c = static_cast<__nv_bfloat16*>(c_bf16);
+    p.status = status_word;
+    p.M = m;
+    p.N = n;
+    p.K = k_local;
+    p.kb = k_local / 128;
+    p.n_tiles = (n + 127) / 128;
+    p.scratch = static_cast<float*>(scratch);
+    p.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
+    p.stages = 0;
+    p.tp_my_flags = static_cast<int32_t*>(my_inbox);
+    p.tp_peer_flags = static_cast<int32_t*>(peer_inbox);
+    p.tp_my_inbox = reinterpret_cast<float*>(static_cast<uint8_t*>(my_inbox) + kTpFlagBytes);
+    p.tp_peer_inbox = reinterpret_cast<float*>(static_cast<uint8_t*>(peer_inbox) + kTpFlagBytes);
+    p.tp_epoch = epoch;
+    p.tp_wait_ns = static_cast<unsigned long long>(peer_wait_ms) * 1000ull * 1000ull;
+
+    CUtensorMap w_map, a_map;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(k_local), static_cast<uint64_t>(n)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(k_local)};
+        const uint32_t box[2] = {128u, 128u};
+        st = encode_tensor_map(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (st != WUDA_OK) return st;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(k_local), static_cast<uint64_t>(m)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(k_local)};
+        const uint32_t box[2] = {128u, static_cast<uint32_t>(m_pad)};
+        st = encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+        if (st != WUDA_OK) return st;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (m_pad) {
+        case 16: return launch<16>(w_map, a_map, p, dev, s);
+        case 32: return launch<32>(w_map, a_map, p, dev, s);
+        case 64: return launch<64>(w_map, a_map, p, dev, s);
+        case 128: return launch<128>(w_map, a_map, p, dev, s);
+        default: return launch<256>(w_map, a_map, p, dev, s);
     }
 }

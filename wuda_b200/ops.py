@@ -13,7 +13,7 @@ from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
-           "rmsnorm_rope_out", "fp8_gemm"]
+           "rmsnorm_rope_out", "fp8_gemm", "TP2Link", "exchange_handles"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -285,3 +285,84 @@ def fp8_gemm(a, a_s, b, b_s, scale_dtype=torch.float32, *, out=None, status_word
                                         m, n, k, scratch.data_ptr(), scratch.numel(),
                                         status_word.data_ptr() if status_word is not None else None, _stream()))
     return out
+
+
+def exchange_handles(my_handle, group=None):
+    """Host-side bootstrap of the two-rank link: all-gathers the ranks' 64-byte IPC handles
+    over torch.distributed (any backend) and returns the peer's.  Not on the hot path."""
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    _require(world == 2, "the link joins exactly two ranks")
+    backend = dist.get_backend(group)
+    device = "cuda" if backend == "nccl" else "cpu"
+    mine = torch.tensor(list(my_handle), dtype=torch.uint8, device=device)
+    both = [torch.zeros(64, dtype=torch.uint8, device=device) for _ in range(2)]
+    dist.all_gather(both, mine, group=group)
+    return bytes(both[1 - rank].cpu().tolist())
+
+
+class TP2Link:
+    """Exchange buffers of a two-rank tensor-parallel pair for fp8_gemm's fused all-reduce.
+
+    link = TP2Link(max_m, n)           # allocates this rank's inbox, exchanges IPC handles
+    y = link.fp8_gemm(a_local, a_s, w_local, w_s)   # == bf16(sum over ranks), on both ranks
+    """
+
+    def __init__(self, m, n, group=None, peer_handle=None, loopback=False):
+        import ctypes
+        self.m, self.n = m, n
+        self.nbytes = lib.wuda_tp2_inbox_bytes(m, n)
+        _require(self.nbytes > 0, "unsupported (m, n) for the exchange buffer")
+        self._local, self._peer = ctypes.c_void_p(), ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        check(lib.wuda_tp2_alloc(self.nbytes, ctypes.byref(self._local), handle))
+        self.handle = bytes(handle)
+        self.epoch = 0
+        self._mute = None
+        if loopback:
+            # a peer that never answers: a second buffer on this GPU receives the pushes and
+            # nothing ever raises the flags of the real inbox (tests of the time-out path)
+            self._mute = ctypes.c_void_p()
+            check(lib.wuda_tp2_alloc(self.nbytes, ctypes.byref(self._mute), (ctypes.c_ubyte * 64)()))
+            self._peer = self._mute
+            self._own_peer = False
+        else:
+            if peer_handle is None:
+                peer_handle = exchange_handles(self.handle, group)
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(peer_handle)
+            check(lib.wuda_tp2_open(buf, ctypes.byref(self._peer)))
+            self._own_peer = True
+
+    def fp8_gemm(self, a, a_s, b, b_s, *, out=None, status_word=None, peer_wait_ms=2000):
+        k = a.size(-1)
+        m = a.numel() // k
+        n = b.size(0)
+        _require(m <= self.m and n == self.n, "shape outside what the link was created for")
+        if out is None:
+            out = torch.empty(*a.shape[:-1], n, dtype=torch.bfloat16, device=a.device)
+        need = lib.wuda_gemm_fp8_scratch_bytes(m, n)
+        scratch = _scratch_for(a.device, need)
+        self.epoch += 1
+        check(lib.wuda_gemm_fp8_blockscaled_tp2(a.data_ptr(), a_s.data_ptr(), b.data_ptr(), b_s.data_ptr(),
+                                                out.data_ptr(), m, n, k, scratch.data_ptr(), scratch.numel(),
+                                                self._local, self._peer, self.epoch, int(peer_wait_ms),
+                                                status_word.data_ptr() if status_word is not None else None,
+                                                _stream()))
+        return out
+
+    def close(self):
+        if getattr(self, "_own_peer", False) and self._peer:
+            lib.wuda_tp2_close(self._peer)
+        self._peer = None
+        if getattr(self, "_mute", None):
+            lib.wuda_tp2_free(self._mute)
+            self._mute = None
+        if getattr(self, "_local", None):
+            lib.wuda_tp2_free(self._local)
+            self._local = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
