@@ -5,6 +5,7 @@ because consecutive launches use different weight buffers that together exceed L
 
     python -m wuda_b200.benchmarks gemm_fp8
     python -m wuda_b200.benchmarks norm_rope_quant
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks tp2
 """
 import json
 import os
@@ -99,6 +100,64 @@ def norm_rope_quant():
         print("rope_quant    tokens %4d: %7.2f us %7.0f GB/s" % (tokens, us, by / us / 1e3))
 
 
+def tp2():
+    """Run under torch.distributed.run with two ranks: wo_b-shaped GEMM (N 7168, K 16384 split in two)
+    with the fused all-reduce, next to the same local GEMM without any exchange."""
+    import torch.distributed as dist
+    rank = int(os.environ["RANK"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("gloo")
+    hbm, _, kind = peaks()
+    for m in (1, 32, 64, 128):
+        n, k = 7168, 16384
+        case = workloads.make_gemm_fp8_case(m, n, k // 2, seed=11 + rank)
+        a = torch.from_numpy(case["a"]).cuda().view(torch.float8_e4m3fn)
+        a_s, w_s = torch.from_numpy(case["a_s"]).cuda(), torch.from_numpy(case["w_s"]).cuda()
+        copies = 6
+        ws = [torch.from_numpy(case["w"]).cuda().view(torch.float8_e4m3fn).clone() for _ in range(copies)]
+        out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        link = wuda.TP2Link(m, n)
+        status = wuda.device_status_word()
+        state = {"i": 0}
+
+        def fused():
+            link.fp8_gemm(a, a_s, ws[state["i"] % copies], w_s, out=out, status_word=status)
+            state["i"] += 1
+
+        def local():
+            wuda.fp8_gemm(a, a_s, ws[state["i"] % copies], w_s, out=out)
+            state["i"] += 1
+
+        def timed(fn, iters=60):
+            for _ in range(5):
+                fn()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        t_local = timed(local)
+        t_fused = timed(fused)
+        by = workloads.gemm_fp8_algorithmic_bytes(m, n, k // 2)
+        link_bytes = m * n * 4
+        bound = max(by / (hbm * 1e3), link_bytes / (770.0 * 1e3))
+        if rank == 0:
+            print("M %4d: local GEMM %6.1f us, fused GEMM+all-reduce %6.1f us (status %d); roofline max(HBM %.1f us, NVLink %.1f us) "
+                  "-> %.0f%% of it; %.1f MB over the link per rank" %
+                  (m, t_local, t_fused, int(status.item()), by / (hbm * 1e3), link_bytes / 770e3, 100 * bound / t_fused,
+                   link_bytes / 1e6))
+        dist.barrier()
+        link.close()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm_fp8"
-    {"gemm_fp8": gemm_fp8, "norm_rope_quant": norm_rope_quant}[which]()
+    {"gemm_fp8": gemm_fp8, "norm_rope_quant": norm_rope_quant, "tp2": tp2}[which]()
