@@ -182,6 +182,29 @@ int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* 
                               int32_t* status_word, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * NVFP4 block-scaled GEMM for decode-sized M:
+ *
+ *   c[m, n] = bf16( a_global_scale * w_global_scale *
+ *                   sum_k (e2m1 a[m,k] * ue4m3 a_sf[m,k/16]) * (e2m1 w[n,k] * ue4m3 w_sf[n,k/16]) )
+ *
+ * Operands are packed e2m1 (two per byte, low nibble = even k; value table and rounding as the
+ * reference's FP4 helpers, origin/convert.py:11-14, test/test_mqa_logits_fp4.py:69-115).  The
+ * reference has no NVFP4 GEMM: its fp4_gemm (origin/kernel.py:441-536) is FP8-activation x
+ * FP4-weight with 1x32 e8m0 scales; this entry is the 16-element-ue4m3 + per-tensor-fp32 form.
+ *
+ *   a  uint8 [m, k/2];  w  uint8 [n, k/2];  1 <= m <= 128, k % 256 == 0; 16-byte aligned
+ *   a_sf_packed, w_sf_packed: the ue4m3 scale bytes in tensor-core order: per 128 rows x 256 K one
+ *      2048-byte block [K/64 step (4)][row % 32 (32)][row / 32 (4)][scale of the step (4)],
+ *      blocks ordered [row tile][k / 256]; rows beyond m / n are zero-padded to a multiple of 128
+ *   scratch: wuda_gemm_nvfp4_scratch_bytes(m, n) bytes, 256-byte aligned, zero before the first
+ *      call; left zero by the kernel
+ */
+int64_t wuda_gemm_nvfp4_scratch_bytes(int m, int n);
+int wuda_gemm_nvfp4(const void* a, const void* a_sf_packed, float a_global_scale, const void* w,
+                    const void* w_sf_packed, float w_global_scale, void* c_bf16, int m, int n, int k,
+                    void* scratch, int64_t scratch_bytes, int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Two-rank tensor-parallel FP8 GEMM with the all-reduce fused into its epilogue.
  *
  * The K dimension is split across two GPUs (a row-parallel linear, origin/model.py:166-180:

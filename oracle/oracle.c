@@ -351,6 +351,52 @@ void oracle_gemm_fp8_blockscaled(const uint8_t* a, const float* a_s, const uint8
     free(af);
 }
 
+/* ------------------------------------------------------------------ NVFP4 block-scaled GEMM
+ *
+ * C[M,N] = gs_a * gs_w * sum_k (e2m1(a[m,k]) * ue4m3(a_sf[m,k/16])) * (e2m1(w[n,k]) * ue4m3(w_sf[n,k/16]))
+ *
+ * e2m1 value table 0, .5, 1, 1.5, 2, 3, 4, 6 with a sign bit, two codes per byte, low nibble =
+ * even element: dsv4_megakernel/origin/convert.py:11-14 and
+ * dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py:69-115.  The reference's FP4 GEMM
+ * (dsv4_megakernel/origin/kernel.py:441-536) pairs FP4 weights with FP8 activations and 1x32 e8m0
+ * scales; the 16-element ue4m3 scales plus a per-tensor fp32 scale of this function are the NVFP4
+ * form named by the benchmark configuration, not pinned by any reference test.  fp32 accumulation.
+ */
+static const float kE2M1[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+static inline float e2m1_value(uint8_t code) {
+    const float v = kE2M1[code & 7];
+    return (code & 8) ? -v : v;
+}
+
+void oracle_gemm_nvfp4(const uint8_t* a, const uint8_t* a_sf, float a_gs, const uint8_t* w, const uint8_t* w_sf,
+                       float w_gs, void* c, int M, int N, int K, int out_bf16) {
+    float* af = (float*)malloc((size_t)M * K * sizeof(float));
+    for (int m = 0; m < M; ++m)
+        for (int k = 0; k < K; ++k) {
+            const uint8_t byte = a[(int64_t)m * (K / 2) + k / 2];
+            af[(int64_t)m * K + k] = e2m1_value((k & 1) ? (byte >> 4) : (byte & 15)) *
+                                     oracle_e4m3_to_f32(a_sf[(int64_t)m * (K / 16) + k / 16]);
+        }
+#pragma omp parallel for schedule(dynamic, 16)
+    for (int n = 0; n < N; ++n) {
+        float* wf = (float*)malloc((size_t)K * sizeof(float));
+        for (int k = 0; k < K; ++k) {
+            const uint8_t byte = w[(int64_t)n * (K / 2) + k / 2];
+            wf[k] = e2m1_value((k & 1) ? (byte >> 4) : (byte & 15)) * oracle_e4m3_to_f32(w_sf[(int64_t)n * (K / 16) + k / 16]);
+        }
+        for (int m = 0; m < M; ++m) {
+            const float* am = af + (int64_t)m * K;
+            float acc = 0.0f;
+            for (int k = 0; k < K; ++k) acc += am[k] * wf[k];
+            acc *= a_gs * w_gs;
+            if (out_bf16) ((uint16_t*)c)[(int64_t)m * N + n] = f32_to_bf16(acc);
+            else ((float*)c)[(int64_t)m * N + n] = acc;
+        }
+        free(wf);
+    }
+    free(af);
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -52,6 +52,8 @@ def _declare(l):
     l.oracle_act_quant_fp8.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int]
     l.oracle_rope_bf16.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int,
                                    c.c_int, c.c_int]
+    l.oracle_gemm_nvfp4.argtypes = [c.c_void_p, c.c_void_p, c.c_float, c.c_void_p, c.c_void_p, c.c_float, c.c_void_p,
+                                    c.c_int, c.c_int, c.c_int, c.c_int]
     l.oracle_gemm_fp8_blockscaled.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
                                               c.c_int, c.c_int, c.c_int, c.c_int]
 
@@ -164,3 +166,15 @@ def gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=True):
 
 def bf16_to_f32(u16):
     return (np.asarray(u16, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def gemm_nvfp4(a, a_sf, a_gs, w, w_sf, w_gs, out_bf16=True):
+    """a packed e2m1 [M,K/2], a_sf ue4m3 bytes [M,K/16], a_gs fp32; w [N,K/2], w_sf [N,K/16], w_gs.
+    Returns uint16 (bf16) or fp32 [M,N]."""
+    a, w = _c(a, np.uint8), _c(w, np.uint8)
+    a_sf, w_sf = _c(a_sf, np.uint8), _c(w_sf, np.uint8)
+    m, k = a.shape[0], a.shape[1] * 2
+    n = w.shape[0]
+    c = np.empty((m, n), np.uint16 if out_bf16 else np.float32)
+    lib().oracle_gemm_nvfp4(_p(a), _p(a_sf), float(a_gs), _p(w), _p(w_sf), float(w_gs), _p(c), m, n, k, int(out_bf16))
+    return c

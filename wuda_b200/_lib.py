@@ -41,6 +41,9 @@ SIGNATURES = {
     "wuda_tp2_free": (c_int, [c_vp]),
     "wuda_gemm_fp8_blockscaled_tp2": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp,
                                               c_vp, c_int, c_int, c_vp, c_vp]),
+    "wuda_gemm_nvfp4_scratch_bytes": (c_i64, [c_int, c_int]),
+    "wuda_gemm_nvfp4": (c_int, [c_vp, c_vp, c_float, c_vp, c_vp, c_float, c_vp, c_int, c_int, c_int, c_vp, c_i64,
+                                c_vp, c_vp]),
     "wuda_topk": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_int, c_int, c_int, c_vp]),
 }
 

@@ -252,7 +252,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         const int et = (ew * 32 + lane);                // 0..255 among epilogue threads
         const int row_in_tile = (warp & 3) * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        float acc[kHalf];
+        __align__(8) float acc[kHalf];
 #pragma unroll
         for (int i = 0; i < kHalf; ++i) acc[i] = 0.f;
         Ring tring;
@@ -295,15 +295,30 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
                 const float wsc = w_ring[slot];
                 const float* sc = a_ring + slot * M_PAD + half * kHalf;
                 const uint32_t taddr = tmem_base + lane_base + ts * M_PAD + half * kHalf;
+                // acc[c] += v[c] * (a_s[c] * w_s): scales come as 16-byte shared-memory loads, the
+                // products and sums as packed fp32x2 operations (one instruction per two columns)
+                float2* acc2 = reinterpret_cast<float2*>(acc);
+                const float2 w2 = make_float2(wsc, wsc);
                 if constexpr (kHalf >= 32) {
+                    uint32_t v[2][32];
+                    tmem_ld_32x32(taddr, v[0]);
 #pragma unroll
                     for (int c = 0; c < kHalf; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld_32x32(taddr + c, v);
                         tmem_ld_wait();
+                        if (c + 32 < kHalf) tmem_ld_32x32(taddr + c + 32, v[((c >> 5) + 1) & 1]);
+                        const uint32_t* x = v[(c >> 5) & 1];
+                        const float4* s4 = reinterpret_cast<const float4*>(sc + c);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            acc[c + i] = fmaf(__uint_as_float(v[i]), sc[c + i] * wsc, acc[c + i]);
+                        for (int i = 0; i < 32; i += 4) {
+                            const float4 sv = s4[i >> 2];
+                            const float2 s01 = __fmul2_rn(make_float2(sv.x, sv.y), w2);
+                            const float2 s23 = __fmul2_rn(make_float2(sv.z, sv.w), w2);
+                            acc2[(c + i) >> 1] = __ffma2_rn(make_float2(__uint_as_float(x[i]), __uint_as_float(x[i + 1])),
+                                                            s01, acc2[(c + i) >> 1]);
+                            acc2[((c + i) >> 1) + 1] = __ffma2_rn(
+                                make_float2(__uint_as_float(x[i + 2]), __uint_as_float(x[i + 3])), s23,
+                                acc2[((c + i) >> 1) + 1]);
+                        }
                     }
                 } else if constexpr (kHalf == 16) {
                     uint32_t v[16];
@@ -489,6 +504,17 @@ extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, c
     const int64_t need = wuda_gemm_fp8_scratch_bytes(m, n);
     WUDA_REQUIRE(scratch_bytes >= need, "scratch holds %lld bytes; %lld are needed (wuda_gemm_fp8_scratch_bytes)",
                  static_cast<long long>(scratch_bytes), static_cast<long long>(need));
+    if (m > 128) {
+        // Above 128 rows a warpgroup's 128 accumulator columns no longer fit the register file;
+        // two passes of <= 128 rows (the weights stream twice) are faster than one that spills.
+        int st2 = wuda_gemm_fp8_blockscaled(a, a_scales, w, w_scales, c_bf16, 128, n, k, scratch, scratch_bytes,
+                                            status_word, stream);
+        if (st2 != WUDA_OK) return st2;
+        return wuda_gemm_fp8_blockscaled(static_cast<const uint8_t*>(a) + static_cast<int64_t>(128) * k,
+                                         a_scales + static_cast<int64_t>(128) * (k / 128), w, w_scales,
+                                         static_cast<__nv_bfloat16*>(c_bf16) + static_cast<int64_t>(128) * n, m - 128,
+                                         n, k, scratch, scratch_bytes, status_word, stream);
+    }
 
     DeviceInfo dev;
     int st = current_device_info(&dev);

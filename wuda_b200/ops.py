@@ -13,7 +13,7 @@ from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
-           "rmsnorm_rope_out", "fp8_gemm", "TP2Link", "exchange_handles"]
+           "rmsnorm_rope_out", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -366,3 +366,28 @@ class TP2Link:
             self.close()
         except Exception:
             pass
+
+
+def nvfp4_gemm(a, a_sf_packed, a_global_scale, w, w_sf_packed, w_global_scale, *, out=None, status_word=None):
+    """bf16 C[M,N] = NVFP4 A[M,K] @ W[N,K]^T: a, w packed e2m1 uint8 [rows, K/2]; *_sf_packed the
+    ue4m3 block scales in tensor-core order (wuda_b200.workloads.pack_nvfp4_scales); one fp32
+    scale per tensor."""
+    _require(a.is_cuda and a.is_contiguous() and a.dtype == torch.uint8 and a.dim() == 2, "a must be CUDA uint8 [M, K/2]")
+    _require(w.is_cuda and w.is_contiguous() and w.dtype == torch.uint8 and w.dim() == 2 and w.size(1) == a.size(1),
+             "w must be CUDA uint8 [N, K/2]")
+    m, k = a.size(0), a.size(1) * 2
+    n = w.size(0)
+    _require(a_sf_packed.is_cuda and a_sf_packed.dtype == torch.uint8
+             and a_sf_packed.numel() == ((m + 127) // 128) * 128 * (k // 16), "a_sf_packed has the wrong size")
+    _require(w_sf_packed.is_cuda and w_sf_packed.dtype == torch.uint8
+             and w_sf_packed.numel() == ((n + 127) // 128) * 128 * (k // 16), "w_sf_packed has the wrong size")
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    need = lib.wuda_gemm_nvfp4_scratch_bytes(m, n)
+    _require(need >= 0, "m must be in [1, 128]")
+    scratch = _scratch_for(a.device, need)
+    check(lib.wuda_gemm_nvfp4(a.data_ptr(), a_sf_packed.data_ptr(), float(a_global_scale), w.data_ptr(),
+                              w_sf_packed.data_ptr(), float(w_global_scale), out.data_ptr(), m, n, k,
+                              scratch.data_ptr(), scratch.numel(),
+                              status_word.data_ptr() if status_word is not None else None, _stream()))
+    return out

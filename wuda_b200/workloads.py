@@ -111,3 +111,49 @@ def make_gemm_fp8_case(m, n, k, seed=0xB202):
 def gemm_fp8_algorithmic_bytes(m, n, k):
     """N*K weights + their scales + M*K activations + their scales + M*N bf16 output."""
     return n * k + ((n + 127) // 128) * (k // 128) * 4 + m * k + m * (k // 128) * 4 + m * n * 2
+
+
+E2M1_BOUNDS = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+
+
+def quantize_nvfp4(x):
+    """fp32 [R, K] -> (packed e2m1 uint8 [R, K/2], ue4m3 scale bytes [R, K/16], per-tensor fp32 scale).
+    x ~= e2m1 * ue4m3(scale of its 16-element block) * tensor scale, tensor scale = amax / (448 * 6)."""
+    x = torch.as_tensor(x, dtype=torch.float32)
+    r, k = x.shape
+    amax = float(x.abs().max())
+    gs = amax / (448.0 * 6.0) if amax > 0 else 1.0
+    v = x.view(r, k // 16, 16)
+    sf = (v.abs().amax(-1) / 6.0 / gs).clamp(max=448.0).to(torch.float8_e4m3fn)
+    sf_dec = sf.float()
+    scaled = torch.where(sf_dec.unsqueeze(-1) > 0, v / (sf_dec.unsqueeze(-1) * gs), torch.zeros_like(v))
+    ax = scaled.abs().clamp_max(6.0)
+    idx = torch.bucketize(ax, E2M1_BOUNDS)                     # ties go to the smaller magnitude
+    code = idx.to(torch.uint8) | (((scaled < 0) & (idx != 0)).to(torch.uint8) << 3)
+    code = code.view(r, k // 2, 2)
+    packed = (code[:, :, 0] & 15) | (code[:, :, 1] << 4)
+    return packed.contiguous().numpy(), sf.view(torch.uint8).numpy().copy(), np.float32(gs)
+
+
+def pack_nvfp4_scales(sf, rows_pad=128):
+    """Scale bytes [R, K/16] -> the layout the tensor core's scale copy expects, per 128 rows x 256 K:
+    [row tile][K/256][4 (K/64 step)][32 (row % 32)][4 (row / 32)][4 (scale within the step)] bytes."""
+    r, g = sf.shape
+    assert g % 16 == 0
+    rt = (r + rows_pad - 1) // rows_pad
+    buf = np.zeros((rt * rows_pad, g), np.uint8)
+    buf[:r] = sf
+    v = buf.reshape(rt, 4, 32, g // 16, 4, 4)          # [tile][row/32][row%32][kb][step][byte]
+    return np.ascontiguousarray(v.transpose(0, 3, 4, 2, 1, 5)).reshape(-1)
+
+
+def make_gemm_nvfp4_case(m, n, k, seed=0xB203):
+    g = torch.Generator().manual_seed(int(seed))
+    a, a_sf, a_gs = quantize_nvfp4(torch.randn(m, k, generator=g))
+    w, w_sf, w_gs = quantize_nvfp4(torch.randn(n, k, generator=g) * 0.02)
+    return dict(a=a, a_sf=a_sf, a_gs=a_gs, w=w, w_sf=w_sf, w_gs=w_gs, m=m, n=n, k=k,
+                a_sf_packed=pack_nvfp4_scales(a_sf), w_sf_packed=pack_nvfp4_scales(w_sf))
+
+
+def gemm_nvfp4_algorithmic_bytes(m, n, k):
+    return n * k // 2 + n * k // 16 + 4 + m * k // 2 + m * k // 16 + 4 + m * n * 2
