@@ -4,13 +4,16 @@ between launches is not forced: weights (>= 15 MB) are re-streamed from HBM ever
 because consecutive launches use different weight buffers that together exceed L2.
 
     python -m wuda_b200.benchmarks gemm_fp8
+    python -m wuda_b200.benchmarks gemm_nvfp4
     python -m wuda_b200.benchmarks norm_rope_quant
+    python -m wuda_b200.benchmarks one gemm_fp8 64 24576 7168      (a few launches of one shape, for ncu)
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks tp2
 """
 import json
 import os
 import sys
 
+import numpy as np
 import torch
 
 import wuda_b200 as wuda
@@ -78,6 +81,34 @@ def gemm_fp8():
             tfl = 2.0 * m * n * k / us / 1e6
             print("%6d %6d %6d %9.1f %9.0f %7.1f%% %9.1f %7.1f%%" % (m, n, k, us, gbs, 100 * gbs / hbm, tfl, 100 * tfl / (2 * tf)))
             del ws
+
+
+def gemm_nvfp4():
+    hbm, tf, kind = peaks()
+    print("NVFP4 block-scaled GEMM, bf16 out; peaks (%s): %.0f GB/s HBM, %.0f TFLOP/s dense bf16 (fp4 nominal = 4x)" % (kind, hbm, tf))
+    print("%6s %6s %6s %9s %9s %8s %9s %8s" % ("M", "N", "K", "us", "GB/s", "of HBM", "TFLOP/s", "of 4xbf16"))
+    for n, k in ((24576, 7168), (7168, 16384), (2112, 7168), (4096, 7168)):
+        base = workloads.make_gemm_nvfp4_case(128, n, k, seed=7)
+        t = lambda x: torch.from_numpy(x).cuda()
+        copies = max(2, int(300e6 // (n * k // 2)) + 1)
+        ws = [t(base["w"]).clone() for _ in range(copies)]
+        w_sf = t(base["w_sf_packed"])
+        for m in (1, 8, 32, 64, 128):
+            a = t(np.ascontiguousarray(base["a"][:m]))
+            a_sf = t(workloads.pack_nvfp4_scales(base["a_sf"][:m]))
+            out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            state = {"i": 0}
+
+            def fn():
+                wuda.nvfp4_gemm(a, a_sf, base["a_gs"], ws[state["i"] % copies], w_sf, base["w_gs"], out=out)
+                state["i"] += 1
+
+            us = time_graph(fn, reps=10, inner=copies * 2)
+            by = workloads.gemm_nvfp4_algorithmic_bytes(m, n, k)
+            gbs = by / us / 1e3
+            tfl = 2.0 * m * n * k / us / 1e6
+            print("%6d %6d %6d %9.1f %9.0f %7.1f%% %9.1f %7.1f%%" % (m, n, k, us, gbs, 100 * gbs / hbm, tfl, 100 * tfl / (4 * tf)))
+        del ws
 
 
 def norm_rope_quant():
@@ -158,6 +189,27 @@ def tp2():
     dist.destroy_process_group()
 
 
+def one(kind, m, n, k, launches=5):
+    """A few eager launches of one GEMM shape (profiler captures)."""
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    if kind == "gemm_fp8":
+        c = workloads.make_gemm_fp8_case(m, n, k, seed=7)
+        a, w = t(c["a"]).view(torch.float8_e4m3fn), t(c["w"]).view(torch.float8_e4m3fn)
+        a_s, w_s = t(c["a_s"]), t(c["w_s"])
+        fn = lambda: wuda.fp8_gemm(a, a_s, w, w_s)
+    else:
+        c = workloads.make_gemm_nvfp4_case(m, n, k, seed=7)
+        a, w, a_sf, w_sf = t(c["a"]), t(c["w"]), t(c["a_sf_packed"]), t(c["w_sf_packed"])
+        fn = lambda: wuda.nvfp4_gemm(a, a_sf, c["a_gs"], w, w_sf, c["w_gs"])
+    for _ in range(launches):
+        fn()
+    torch.cuda.synchronize()
+    print("ran %d launches of %s M=%d N=%d K=%d" % (launches, kind, m, n, k))
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm_fp8"
-    {"gemm_fp8": gemm_fp8, "norm_rope_quant": norm_rope_quant, "tp2": tp2}[which]()
+    if which == "one":
+        one(sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]))
+        sys.exit(0)
+    {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2}[which]()
