@@ -157,6 +157,24 @@ int wuda_rope_quant_fp8(const void* x_bf16, const int64_t* positions, const floa
                         void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * mHC post mix, the last op of an attention half-layer:
+ *   output[t, j, d] = post[t, j] * attention_out[t, d] + sum_i comb[t, i, j] * residual[t, i, d]
+ *
+ * Replaces mhc_post_out / mhc_post_run (kernels/mhc_post.cu:41-99 kernel, :102-137 validate
+ * and run; include/mhc_post.cuh:16-33 argument block).  fp32 arithmetic in the reference
+ * kernel's order: one rounded product, then fused multiply-adds over i = 0..3, then bf16
+ * round-to-nearest-even - results are bit-identical to that kernel.
+ *
+ *   attention_out bf16 [m, hidden];  residual bf16 [m, 4, hidden];  post fp32 [m, 4]
+ *   comb fp32 [m, 4, 4] indexed [input stream i][output stream j];  output bf16 [m, 4, hidden]
+ * m >= 1, hidden % 8 == 0 (7168 in the model), every buffer 16-byte aligned, output must not
+ * overlap any input (checked, as the reference checks it).  The reference also refuses
+ * m > 128, its decode batch limit; this entry takes any m.
+ */
+int wuda_mhc_post(const void* attention_out, const void* residual, const float* post, const float* comb,
+                  void* output, int m, int hidden, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Block-scaled FP8 GEMM for decode-sized M:
  *
  *   c[m, n] = bf16( sum_kb a_s[m, kb] * w_s[n / 128, kb] * sum_{k in block kb} a[m, k] * w[n, k] )

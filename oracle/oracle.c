@@ -312,6 +312,28 @@ void oracle_rope_bf16(uint16_t* x, const int64_t* positions, const float* cos_t,
     }
 }
 
+/* ------------------------------------------------------------------ mHC post mix
+ *
+ * out[m,j,d] = post[m,j] * x[m,d] + sum_i comb[m,i,j] * res[m,i,d], bf16 in and out, in the
+ * arithmetic order of dsv4_megakernel/megakernel/kernels/mhc_post.cu:74-81: a rounded fp32
+ * product, then fmaf over i = 0..3, then round-to-nearest-even to bf16.  The reference's torch
+ * twin (dsv4_megakernel/megakernel/test/test_e2e_decode.py:423-426) sums in another order; the
+ * golden fixture made from it is met to within one bf16 step.
+ */
+__attribute__((optimize("fp-contract=off")))
+void oracle_mhc_post(const uint16_t* x, const uint16_t* res, const float* post, const float* comb, uint16_t* out,
+                     int m, int hidden) {
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < m; ++t)
+        for (int j = 0; j < 4; ++j)
+            for (int d = 0; d < hidden; ++d) {
+                float v = post[t * 4 + j] * bf16_to_f32(x[(int64_t)t * hidden + d]);
+                for (int i = 0; i < 4; ++i)
+                    v = fmaf(comb[t * 16 + i * 4 + j], bf16_to_f32(res[((int64_t)t * 4 + i) * hidden + d]), v);
+                out[((int64_t)t * 4 + j) * hidden + d] = f32_to_bf16(v);
+            }
+}
+
 /* ------------------------------------------------------------------ block-scaled FP8 GEMM
  *
  * C[M,N] = A[M,K] @ B[N,K]^T, A and B e4m3, scales fp32: a_s [M, K/128] (1x128 blocks),

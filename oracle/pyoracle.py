@@ -52,6 +52,7 @@ def _declare(l):
     l.oracle_act_quant_fp8.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int]
     l.oracle_rope_bf16.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int,
                                    c.c_int, c.c_int]
+    l.oracle_mhc_post.argtypes = [c.c_void_p] * 5 + [c.c_int, c.c_int]
     l.oracle_gemm_nvfp4.argtypes = [c.c_void_p, c.c_void_p, c.c_float, c.c_void_p, c.c_void_p, c.c_float, c.c_void_p,
                                     c.c_int, c.c_int, c.c_int, c.c_int]
     l.oracle_gemm_fp8_blockscaled.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
@@ -150,6 +151,15 @@ def rope_bf16(x_bf16, positions, cos_t, sin_t, rope_dim, inverse=False):
     lib().oracle_rope_bf16(_p(x), _p(pos), _p(cos_t), _p(sin_t), x.shape[0], x.shape[1], x.shape[2], rope_dim,
                            int(inverse))
     return x
+
+
+def mhc_post(x_bf16, res_bf16, post, comb):
+    """x uint16 (bf16) [M,H], res uint16 [M,4,H], post fp32 [M,4], comb fp32 [M,4,4] -> uint16 [M,4,H]."""
+    x, res = _c(x_bf16, np.uint16), _c(res_bf16, np.uint16)
+    post, comb = _c(post, np.float32), _c(comb, np.float32)
+    out = np.empty_like(res)
+    lib().oracle_mhc_post(_p(x), _p(res), _p(post), _p(comb), _p(out), x.shape[0], x.shape[1])
+    return out
 
 
 def gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=True):

@@ -9,7 +9,9 @@ Functions used (paths inside the reference repository):
   dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py  ref_fp8_mqa_logits (:207-218)
   dsv4_megakernel/megakernel/test/test_topk_v2.py         ref_page_transform (:86-94) and the
                                                            stable-argsort rule (:116)
-Both are written for device="cuda"; they are run here on the CPU by mapping that one
+  dsv4_megakernel/megakernel/test/test_e2e_decode.py      ref_mhc_post (:423-426)
+  dsv4_megakernel/megakernel/test/kv_cache_manager.py     KVCacheManager (:53-257), run on the CPU
+The first two are written for device="cuda"; they are run here on the CPU by mapping that one
 keyword to "cpu", which changes no arithmetic.
 """
 import importlib.util
@@ -154,6 +156,96 @@ def golden_norm_rope_quant(ref_root):
     print("act_quant_pow2_7168.npz", tuple(q.shape))
 
 
+def golden_mhc_post(ref_root):
+    """The torch twin of the mHC post mix on seeded inputs of the model's width."""
+    e2e = _load(ref_root, "dsv4_megakernel/megakernel/test/test_e2e_decode.py", "ref_e2e")
+    e2e.torch = torch
+    g = torch.Generator().manual_seed(41)
+    m, hidden = 3, 7168
+    x = torch.randn(m, hidden, generator=g).bfloat16()
+    res = torch.randn(m, 4, hidden, generator=g).bfloat16()
+    post = torch.rand(m, 4, generator=g) * 2
+    comb = torch.softmax(torch.randn(m, 4, 4, generator=g), dim=-1)
+    out = e2e.ref_mhc_post(x, res, post, comb)
+    np.savez_compressed(os.path.join(HERE, "mhc_post_7168.npz"), x=_u16(x), residual=_u16(res), post=post.numpy(),
+                        comb=comb.numpy(), out=_u16(out))
+    print("mhc_post_7168.npz", tuple(out.shape))
+
+
+KV_TRACE_CONFIGS = [
+    dict(capacity=5, pages_per_pool=96, max_pages_per_req=12),
+    dict(capacity=5, pages_per_pool=96, max_pages_per_req=12, state_ring_entries=16),
+    dict(capacity=4, pages_per_pool=400, max_pages_per_req=40, swa_entries_per_block=64,
+         cmp_entries_per_block=32, idx_entries_per_block=16),
+]
+
+
+def kv_trace(manager_cls, config, ops):
+    """Replays a scripted request lifecycle on a cache manager and records everything it hands
+    out.  `ops` is a list of ("alloc",), ("free", live index) and ("step", [live indices])."""
+    m = manager_cls(device="cpu", **config)
+    live, out = [], []
+    for op in ops:
+        if op[0] == "alloc":
+            live.append(m.alloc_request())
+            out.append(["alloc", live[-1]])
+        elif op[0] == "free":
+            slot = live.pop(op[1])
+            m.free_request(slot)
+            out.append(["free", slot])
+        else:
+            slots = [live[i] for i in op[1]]
+            st = m.step_begin(slots)
+            pos = st["pos"].tolist()
+            swa, swa_len = m.swa_indices(slots, pos, 128)
+            out.append(["step", {
+                "slots": slots, "pos": pos, "q_pos": st["q_pos"].tolist(),
+                "main_state_row": st["main_state_row"].tolist(), "idx_state_row": st["idx_state_row"].tolist(),
+                "idx_dst": st["idx_dst"].tolist(), "cmp_dst": st["cmp_dst"].tolist(), "swa_dst": st["swa_dst"].tolist(),
+                "block_table": {n: m.block_table(n, slots).tolist() for n in ("swa", "cmp", "idx")},
+                "swa_indices": swa.tolist(), "swa_lens": swa_len.tolist(),
+                "n_compressed": m.n_compressed(slots, pos).tolist()}])
+    geometry = {n: m.geometry(n) for n in ("swa", "cmp", "idx")}
+    shapes = {"main_state": list(m.main_state.shape), "idx_state": list(m.idx_state.shape),
+              "swa_pool": list(m.swa_pool.shape), "cmp_pool": list(m.cmp_pool.shape), "idx_pool": list(m.idx_pool.shape),
+              "cmp_view": [list(m.model1_cache_view("cmp").shape), list(m.model1_cache_view("cmp").stride())],
+              "idx_view": [list(m.indexer_cache_view().shape), list(m.indexer_cache_view().stride())]}
+    return {"events": out, "geometry": geometry, "shapes": shapes}
+
+
+def kv_script(seed, capacity, steps):
+    import random
+    rnd = random.Random(seed)
+    live, ops = 0, []
+    for _ in range(steps):
+        r = rnd.random()
+        if live == 0 or (r < 0.05 and live < capacity):
+            ops.append(("alloc",))
+            live += 1
+        elif r < 0.07:
+            ops.append(("free", rnd.randrange(live)))
+            live -= 1
+            if live == 0:
+                continue
+        chosen = [i for i in range(live) if rnd.random() < 0.9] or [0]
+        ops.append(("step", chosen))
+    return ops
+
+
+def golden_kv_cache(ref_root):
+    import gzip
+    import json
+    ref = _load(ref_root, "dsv4_megakernel/megakernel/test/kv_cache_manager.py", "ref_kv_cache")
+    ref.torch = torch
+    traces = []
+    for n, config in enumerate(KV_TRACE_CONFIGS):
+        ops = kv_script(50 + n, config["capacity"], 420)
+        traces.append({"config": config, "ops": ops, "expect": kv_trace(ref.KVCacheManager, config, ops)})
+    with gzip.open(os.path.join(HERE, "kv_cache_trace.json.gz"), "wt") as f:
+        json.dump(traces, f)
+    print("kv_cache_trace.json.gz", sum(len(t["ops"]) for t in traces), "ops")
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     tdir = "dsv4_megakernel/megakernel/test"
@@ -165,6 +257,8 @@ def main():
     golden_topk(ref_topk, "topk_random.npz", 3, 3000, 512, [3000, 2100, 300], 0, 21)
     golden_topk(ref_topk, "topk_ties.npz", 2, 4096, 1024, [4096, 2500], 7, 22)
     golden_norm_rope_quant(ref_root)
+    golden_mhc_post(ref_root)
+    golden_kv_cache(ref_root)
 
 
 if __name__ == "__main__":

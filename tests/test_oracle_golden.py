@@ -125,3 +125,19 @@ def test_gemm_fp8_oracle_equals_dequantised_matmul():
     bd = oracle.e4m3_decode(b).astype(np.float64) * np.repeat(np.repeat(b_s, 128, axis=0), 128, axis=1)
     ref = ad @ bd.T
     assert np.max(np.abs(got - ref)) <= 1e-5 * np.max(np.abs(ref))
+
+
+def test_mhc_post_oracle_matches_reference_formula():
+    """The reference's torch twin sums comb·residual first and adds post·x last; the oracle
+    follows the reference kernel (product first, then four fmaf).  Both round once to bf16,
+    so they agree to one bf16 step and are identical almost everywhere."""
+    g = load_golden("mhc_post_7168.npz")
+    got = oracle.mhc_post(g["x"], g["residual"], g["post"], g["comb"])
+    d = np.abs(got.astype(np.int32) - g["out"].astype(np.int32))
+    assert d.max() <= 1
+    assert (d == 0).mean() >= 0.99
+    # exact against a float64 evaluation rounded once, wherever that is not a near-tie
+    x, res = oracle.bf16_to_f32(g["x"]).astype(np.float64), oracle.bf16_to_f32(g["residual"]).astype(np.float64)
+    exact = np.einsum("mij,mih->mjh", g["comb"].astype(np.float64), res) + g["post"][..., None] * x[:, None, :]
+    err = np.abs(oracle.bf16_to_f32(got) - exact)
+    assert np.all(err <= np.abs(exact) * 2.0 ** -8 + 1e-6)

@@ -31,6 +31,7 @@ SIGNATURES = {
     "wuda_rmsnorm_quant_fp8": (c_int, [c_vp, c_i64, c_vp, c_int, c_float, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp]),
     "wuda_rope_quant_fp8": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_vp]),
+    "wuda_mhc_post": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
     "wuda_gemm_fp8_scratch_bytes": (c_i64, [c_int, c_int]),
     "wuda_gemm_fp8_blockscaled": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
     "wuda_gemm_fp8_blockscaled_noalloc": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp]),

@@ -13,7 +13,7 @@ from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
-           "rmsnorm_rope_out", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
+           "rmsnorm_rope_out", "mhc_post_out", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -232,6 +232,24 @@ def rope_quant(x, positions, cos_table, sin_table, rope_dim, *, inverse=False, q
                                   sc.data_ptr() if sc is not None else None, tokens, heads, head_dim, rope_dim,
                                   cos_table.size(0), int(inverse), 0 if scale_fmt is None else 1, _stream()))
     return y16, y8, sc
+
+
+def mhc_post_out(attention_out, residual, post, comb, output):
+    """output[m,j,:] = post[m,j] * attention_out[m,:] + sum_i comb[m,i,j] * residual[m,i,:], with
+    the reference's signature and checks (kernels/mhc_post.cu:139-177): bf16 [M,7168] and
+    [M,4,7168], fp32 [M,4] and [M,4,4], caller-owned bf16 output [M,4,7168], 1 <= M <= 128."""
+    _require(attention_out.is_cuda and attention_out.is_contiguous() and attention_out.dtype == torch.bfloat16
+             and attention_out.dim() == 2, "attention_out must be contiguous CUDA bf16 [M, hidden]")
+    m, hidden = attention_out.shape
+    _require(1 <= m <= 128, "M must be in [1, 128]")
+    for name, t, dtype, shape in (("residual", residual, torch.bfloat16, (m, 4, hidden)),
+                                  ("post", post, torch.float32, (m, 4)), ("comb", comb, torch.float32, (m, 4, 4)),
+                                  ("output", output, torch.bfloat16, (m, 4, hidden))):
+        _require(t.is_cuda and t.is_contiguous() and t.dtype == dtype and tuple(t.shape) == shape,
+                 f"{name} must be contiguous CUDA {dtype} {list(shape)}")
+    check(lib.wuda_mhc_post(attention_out.data_ptr(), residual.data_ptr(), post.data_ptr(), comb.data_ptr(),
+                            output.data_ptr(), m, hidden, _stream()))
+    return output
 
 
 def rmsnorm_rope_out(x, positions, cos_table, sin_table, out, input_heads=None, eps=1e-6, pdl=False, max_blocks=0):
