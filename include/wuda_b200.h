@@ -48,7 +48,9 @@ typedef enum wuda_device_status {
     WUDA_DEV_TIMEOUT_GEMM_EMPTY = 122,
     WUDA_DEV_TIMEOUT_GEMM_TMEM_FULL = 123,
     WUDA_DEV_TIMEOUT_GEMM_TMEM_EMPTY = 124,
-    WUDA_DEV_TIMEOUT_PEER_FLAG = 131
+    WUDA_DEV_TIMEOUT_PEER_FLAG = 131,
+    WUDA_DEV_BAD_DESTINATION = 141, /* cache destination outside the pool: that record was not written */
+    WUDA_DEV_BAD_STATE_ROW = 142    /* state_row outside the state rings: that row was skipped         */
 } wuda_device_status;
 
 /* Library version (major*10000 + minor*100 + patch). */
@@ -155,6 +157,84 @@ int wuda_rope_quant_fp8(const void* x_bf16, const int64_t* positions, const floa
                         const float* sin_table, void* y_bf16, void* y_fp8, float* y_scales, int tokens,
                         int heads, int head_dim, int rope_dim, int max_pos, int inverse, int scale_mode,
                         void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * The cache writers of a decode step, all in one launch: the indexer compressor, the MAIN
+ * compressor and the window-KV writer.  Each fills the paged pool its consumer reads and,
+ * optionally, compact per-row copies of what it wrote.
+ *
+ * Replaces the writers the reference runs in idle warps of other kernels and their
+ * stand-alone forms: idx_comp::process_row<true> and process_win_row
+ * (include/idx_comp_fp4.cuh:97-201, :282-383; bundle of wq_b_proj_gemm_merged,
+ * kernels/wq_b_fp8_gemm.cu:849-1365) and run_main_compressor_row / MainCompressorArgs
+ * (include/mqa_logits_fp8.cuh:29-45, :133-284; mqa_compressor_fp8_standalone,
+ * kernels/mqa_logits_fp8.cu:542-599).  Numerics follow their torch twins
+ * (test/test_wq_b_fp8_gemm.py:550-586 with fp8=True, :646-665; test/test_mqa_logits_fp4.py:769-789):
+ * IEEE division, 1/sqrt and expf where the reference kernels use the fast-math forms.
+ *
+ * A compressor bundle works on rows with (pos[r] + 1) % 4 == 0 and state_row[r] >= 0:
+ *   state      fp32 [state_rows_total, 4*H]: entry = [kv 2H | score 2H], H = 128 (indexer) or
+ *              512 (MAIN); state_row[r] = block * ring_entries + (pos % ring_entries)
+ *   the 8 entries ending at state_row (walking back inside the block, modulo ring_entries) are
+ *   combined per column by softmax(score) * kv - entries 0..3 use columns [0,H), 4..7 use [H,2H) -
+ *   -> bf16 -> RMSNorm(H, norm_w fp32 [H]) -> bf16 -> RoPE on the last 64 at position pos - 3 -> bf16
+ *   indexer: scale = max(amax / 448, 1e-12); 128 e4m3 bytes at page + off*128 and the fp32
+ *            scale at page + entries_per_block*128 + off*4 (the kv_pages format of
+ *            wuda_mqa_logits_fp8); compact q8 [rows,128], s8 fp32 [rows]
+ *   MAIN:    a MODEL1 record: columns [0,448) e4m3 with one power-of-two scale per 64
+ *            (2^ceil(log2(max(amax/448, 1e-4)))), columns [448,512) bf16; body at
+ *            page + off*576, 7 biased-exponent bytes at page + entries_per_block*576 + off*8;
+ *            compact q8 [rows,448], s8 fp32 [rows,7], rope bf16 [rows,64]
+ * The window bundle works on every row: y fp32 [rows,512] -> RMSNorm from the raw row ->
+ * [0,448) rounded to bf16 and quantised as above, [448,512) rotated in fp32 at pos[r] -> bf16,
+ * written as a MODEL1 record like MAIN.
+ * dst[r] = page * entries_per_block + off; dst[r] < 0 writes no record (compact outputs are
+ * still written).  A bundle with state (or y) == NULL is skipped; pool, q8, s8, rope are each
+ * optional.  Rows that do not compress leave their compact outputs untouched.  Out-of-range
+ * destinations or state rows are skipped and reported in status_word (nullable).
+ */
+typedef struct wuda_compressor_bundle {
+    const float* state;
+    const int64_t* state_row;
+    const float* norm_w;
+    int64_t state_rows_total;
+    int ring_entries;
+    int entries_per_block;
+    int num_blocks;
+    int reserved;
+    int64_t block_stride_bytes;
+    uint8_t* pool;
+    const int64_t* dst;
+    uint8_t* q8;
+    float* s8;
+    void* rope; /* MAIN only */
+} wuda_compressor_bundle;
+
+typedef struct wuda_window_bundle {
+    const float* y;
+    const float* norm_w;
+    int entries_per_block;
+    int num_blocks;
+    int64_t block_stride_bytes;
+    uint8_t* pool;
+    const int64_t* dst;
+    uint8_t* q8;
+    float* s8;
+    void* rope;
+} wuda_window_bundle;
+
+typedef struct wuda_cache_writers {
+    const int64_t* pos;     /* [rows] token positions                               */
+    const float* cos_table; /* fp32 [max_pos, 32]                                    */
+    const float* sin_table;
+    int max_pos;            /* rotation positions are clamped into [0, max_pos)      */
+    float eps;
+    wuda_compressor_bundle indexer;
+    wuda_compressor_bundle main;
+    wuda_window_bundle window;
+} wuda_cache_writers;
+
+int wuda_cache_writers_fp8(const wuda_cache_writers* args, int rows, int32_t* status_word, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * mHC post mix, the last op of an attention half-layer:

@@ -312,6 +312,170 @@ void oracle_rope_bf16(uint16_t* x, const int64_t* positions, const float* cos_t,
     }
 }
 
+/* ------------------------------------------------------------------ cache writers
+ *
+ * The indexer compressor, the MAIN compressor and the window-KV writer of a decode step, after
+ * the reference's torch twins: dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py:550-586
+ * (ref_comp_step, fp8 form), :646-665 (ref_win_step) and test_mqa_logits_fp4.py:769-789 (MAIN,
+ * inline).  Where the twins leave the fp32 evaluation order open, this follows the order of the
+ * reference's device code (include/idx_comp_fp4.cuh:113-160, include/mqa_logits_fp8.cuh:152-206):
+ * softmax as sum(e*kv) / sum(e) accumulated over entries 0..7, the sum of squares as 4 columns per
+ * thread, a 32-lane butterfly, then warps in order.  Division, 1/sqrt and expf are the C library's.
+ */
+__attribute__((optimize("fp-contract=off"), noinline))
+static float sumsq_tree(const float* v, int width) {
+    /* width is 128 (one warp) or 512 (four warps); lane l of warp w holds columns 4*(32w+l) .. +3 */
+    float total = 0.0f;
+    for (int w = 0; w < width / 128; ++w) {
+        float lane[32];
+        for (int l = 0; l < 32; ++l) {
+            const float* c = v + (w * 32 + l) * 4;
+            float s = 0.0f;
+            for (int e = 0; e < 4; ++e) s += c[e] * c[e];
+            lane[l] = s;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            float next[32];
+            for (int l = 0; l < 32; ++l) next[l] = lane[l] + lane[l ^ o];
+            memcpy(lane, next, sizeof lane);
+        }
+        total = w == 0 ? lane[0] : total + lane[0];
+    }
+    return total;
+}
+
+static int log2_ceil_f32(float x) {
+    uint32_t bits;
+    memcpy(&bits, &x, 4);
+    return (int)((bits >> 23) & 0xff) - 127 + ((bits & 0x7fffffu) ? 1 : 0);
+}
+
+__attribute__((optimize("fp-contract=off"), noinline))
+static void rotate_tail(float* v64, const float* c, const float* s, int round_bf16) {
+    for (int i = 0; i < 32; ++i) {
+        const float re = v64[2 * i], im = v64[2 * i + 1];
+        const float a = re * c[i] - im * s[i], b = re * s[i] + im * c[i];
+        v64[2 * i] = round_bf16 ? bf16_to_f32(f32_to_bf16(a)) : a;
+        v64[2 * i + 1] = round_bf16 ? bf16_to_f32(f32_to_bf16(b)) : b;
+    }
+}
+
+/* softmax-weighted window sum -> bf16 -> RMSNorm(norm_w) -> bf16 -> RoPE(last 64, position p-3) -> bf16 */
+__attribute__((optimize("fp-contract=off"), noinline))
+static void compress_row(const float* state, int64_t state_row, int ring, int half, const float* norm_w,
+                         const float* cos_t, const float* sin_t, int max_pos, int64_t p, float eps, float* v) {
+    const int entry = 4 * half;
+    const int current = (int)(state_row % ring);
+    const float* base = state + (state_row - current) * entry;
+    int first = current - 7;
+    if (first < 0) first += ring;
+    for (int c = 0; c < half; ++c) {
+        float sc[8], kv[8];
+        for (int r = 0; r < 8; ++r) {
+            const float* e = base + (int64_t)((first + r) % ring) * entry + (r < 4 ? c : half + c);
+            kv[r] = e[0];
+            sc[r] = e[2 * half];
+        }
+        float mx = sc[0];
+        for (int r = 1; r < 8; ++r) mx = fmaxf(mx, sc[r]);
+        float den = 0.0f, num = 0.0f;
+        for (int r = 0; r < 8; ++r) {
+            const float w = expf(sc[r] - mx);
+            den += w;
+            num += w * kv[r];
+        }
+        v[c] = bf16_to_f32(f32_to_bf16(num / den));
+    }
+    const float rms = 1.0f / sqrtf(sumsq_tree(v, half) / (float)half + eps);
+    for (int c = 0; c < half; ++c) v[c] = bf16_to_f32(f32_to_bf16(v[c] * rms * norm_w[c]));
+    int64_t rp = p - 3;
+    if (rp < 0) rp = 0;
+    if (rp >= max_pos) rp = max_pos - 1;
+    rotate_tail(v + half - 64, cos_t + rp * 32, sin_t + rp * 32, 1);
+}
+
+/* 448 values -> e4m3 with a power-of-two scale per 64; 64 values -> bf16; compact outputs and record */
+__attribute__((optimize("fp-contract=off"), noinline))
+static void write_model1(const float* v, int row, uint8_t* q8, float* s8, uint16_t* rope, uint8_t* pool,
+                         const int64_t* dst, int epb, int64_t stride) {
+    uint8_t body[576], sb[7];
+    for (int g = 0; g < 7; ++g) {
+        float amax = 0.0f;
+        for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(v[g * 64 + i]));
+        const int e = log2_ceil_f32(fmaxf(amax / 448.0f, 1e-4f));
+        const float scale = ldexpf(1.0f, e);
+        for (int i = 0; i < 64; ++i) body[g * 64 + i] = oracle_f32_to_e4m3(v[g * 64 + i] / scale);
+        sb[g] = (uint8_t)(e + 127);
+        if (s8) s8[(int64_t)row * 7 + g] = scale;
+    }
+    for (int i = 0; i < 64; ++i) {
+        const uint16_t h = f32_to_bf16(v[448 + i]);
+        memcpy(body + 448 + 2 * i, &h, 2);
+    }
+    if (q8) memcpy(q8 + (int64_t)row * 448, body, 448);
+    if (rope) memcpy(rope + (int64_t)row * 64, body + 448, 128);
+    if (pool && dst && dst[row] >= 0) {
+        uint8_t* page = pool + dst[row] / epb * stride;
+        const int off = (int)(dst[row] % epb);
+        memcpy(page + (int64_t)off * 576, body, 576);
+        memcpy(page + (int64_t)epb * 576 + off * 8, sb, 7);
+    }
+}
+
+__attribute__((optimize("fp-contract=off")))
+void oracle_indexer_compressor_fp8(const float* state, const int64_t* state_row, int ring, const int64_t* pos,
+                                   const float* norm_w, const float* cos_t, const float* sin_t, int max_pos,
+                                   float eps, uint8_t* pool, const int64_t* dst, int epb, int64_t stride, uint8_t* q8,
+                                   float* s8, int rows) {
+    for (int r = 0; r < rows; ++r) {
+        if ((pos[r] + 1) % 4 != 0 || state_row[r] < 0) continue;
+        float v[128];
+        compress_row(state, state_row[r], ring, 128, norm_w, cos_t, sin_t, max_pos, pos[r], eps, v);
+        float amax = 0.0f;
+        for (int c = 0; c < 128; ++c) amax = fmaxf(amax, fabsf(v[c]));
+        const float scale = fmaxf(amax / 448.0f, 1e-12f);
+        uint8_t q[128];
+        for (int c = 0; c < 128; ++c) q[c] = oracle_f32_to_e4m3(v[c] / scale);
+        if (q8) memcpy(q8 + (int64_t)r * 128, q, 128);
+        if (s8) s8[r] = scale;
+        if (pool && dst && dst[r] >= 0) {
+            uint8_t* page = pool + dst[r] / epb * stride;
+            const int off = (int)(dst[r] % epb);
+            memcpy(page + (int64_t)off * 128, q, 128);
+            memcpy(page + (int64_t)epb * 128 + off * 4, &scale, 4);
+        }
+    }
+}
+
+__attribute__((optimize("fp-contract=off")))
+void oracle_main_compressor_fp8(const float* state, const int64_t* state_row, int ring, const int64_t* pos,
+                                const float* norm_w, const float* cos_t, const float* sin_t, int max_pos, float eps,
+                                uint8_t* pool, const int64_t* dst, int epb, int64_t stride, uint8_t* q8, float* s8,
+                                uint16_t* rope, int rows) {
+    for (int r = 0; r < rows; ++r) {
+        if ((pos[r] + 1) % 4 != 0 || state_row[r] < 0) continue;
+        float v[512];
+        compress_row(state, state_row[r], ring, 512, norm_w, cos_t, sin_t, max_pos, pos[r], eps, v);
+        write_model1(v, r, q8, s8, rope, pool, dst, epb, stride);
+    }
+}
+
+__attribute__((optimize("fp-contract=off")))
+void oracle_window_kv_fp8(const float* y, const int64_t* pos, const float* norm_w, const float* cos_t,
+                          const float* sin_t, int max_pos, float eps, uint8_t* pool, const int64_t* dst, int epb,
+                          int64_t stride, uint8_t* q8, float* s8, uint16_t* rope, int rows) {
+    for (int r = 0; r < rows; ++r) {
+        float v[512];
+        memcpy(v, y + (int64_t)r * 512, sizeof v);
+        const float rms = 1.0f / sqrtf(sumsq_tree(v, 512) / 512.0f + eps);
+        for (int c = 0; c < 512; ++c) v[c] = v[c] * rms * norm_w[c];
+        for (int c = 0; c < 448; ++c) v[c] = bf16_to_f32(f32_to_bf16(v[c]));
+        int64_t rp = pos[r] < 0 ? 0 : (pos[r] >= max_pos ? max_pos - 1 : pos[r]);
+        rotate_tail(v + 448, cos_t + rp * 32, sin_t + rp * 32, 0);
+        write_model1(v, r, q8, s8, rope, pool, dst, epb, stride);
+    }
+}
+
 /* ------------------------------------------------------------------ mHC post mix
  *
  * out[m,j,d] = post[m,j] * x[m,d] + sum_i comb[m,i,j] * res[m,i,d], bf16 in and out, in the

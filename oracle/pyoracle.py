@@ -53,6 +53,13 @@ def _declare(l):
     l.oracle_rope_bf16.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int,
                                    c.c_int, c.c_int]
     l.oracle_mhc_post.argtypes = [c.c_void_p] * 5 + [c.c_int, c.c_int]
+    vp, i64 = c.c_void_p, c.c_int64
+    l.oracle_indexer_compressor_fp8.argtypes = [vp, vp, c.c_int, vp, vp, vp, vp, c.c_int, c.c_float, vp, vp, c.c_int,
+                                                i64, vp, vp, c.c_int]
+    l.oracle_main_compressor_fp8.argtypes = [vp, vp, c.c_int, vp, vp, vp, vp, c.c_int, c.c_float, vp, vp, c.c_int,
+                                             i64, vp, vp, vp, c.c_int]
+    l.oracle_window_kv_fp8.argtypes = [vp, vp, vp, vp, vp, c.c_int, c.c_float, vp, vp, c.c_int, i64, vp, vp, vp,
+                                       c.c_int]
     l.oracle_gemm_nvfp4.argtypes = [c.c_void_p, c.c_void_p, c.c_float, c.c_void_p, c.c_void_p, c.c_float, c.c_void_p,
                                     c.c_int, c.c_int, c.c_int, c.c_int]
     l.oracle_gemm_fp8_blockscaled.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
@@ -160,6 +167,55 @@ def mhc_post(x_bf16, res_bf16, post, comb):
     out = np.empty_like(res)
     lib().oracle_mhc_post(_p(x), _p(res), _p(post), _p(comb), _p(out), x.shape[0], x.shape[1])
     return out
+
+
+def _pool_args(pool, dst, epb):
+    if pool is None:
+        return None, None, 1, 0
+    assert pool.dtype == np.uint8 and pool.ndim == 2 and pool.flags.c_contiguous
+    return pool, _c(dst, np.int64), int(epb), pool.shape[1]
+
+
+def indexer_compressor_fp8(state, state_row, pos, norm_w, cos_t, sin_t, eps=1e-6, pool=None, dst=None, epb=64):
+    """state fp32 [blocks, ring, 512].  Returns (q8 [rows,128] uint8, scale [rows] fp32); rows that do not
+    compress keep the fill (0xAB / -1).  `pool` (uint8 [pages, stride]) is written in place."""
+    state = _c(state, np.float32)
+    rows = len(pos)
+    q8, s8 = np.full((rows, 128), 0xAB, np.uint8), np.full(rows, -1.0, np.float32)
+    pool, dst, epb, stride = _pool_args(pool, dst, epb)
+    sr, ps = _c(state_row, np.int64), _c(pos, np.int64)
+    nw, ct, st = _c(norm_w, np.float32), _c(cos_t, np.float32), _c(sin_t, np.float32)
+    lib().oracle_indexer_compressor_fp8(_p(state), _p(sr), state.shape[1], _p(ps), _p(nw), _p(ct), _p(st), ct.shape[0],
+                                        eps, _p(pool), _p(dst), epb, stride, _p(q8), _p(s8), rows)
+    return q8, s8
+
+
+def main_compressor_fp8(state, state_row, pos, norm_w, cos_t, sin_t, eps=1e-6, pool=None, dst=None, epb=64):
+    """state fp32 [blocks, ring, 2048].  Returns (q8 [rows,448], s8 [rows,7], rope uint16 [rows,64])."""
+    state = _c(state, np.float32)
+    rows = len(pos)
+    q8, s8 = np.full((rows, 448), 0xAB, np.uint8), np.full((rows, 7), -1.0, np.float32)
+    rope = np.zeros((rows, 64), np.uint16)
+    pool, dst, epb, stride = _pool_args(pool, dst, epb)
+    sr, ps = _c(state_row, np.int64), _c(pos, np.int64)
+    nw, ct, st = _c(norm_w, np.float32), _c(cos_t, np.float32), _c(sin_t, np.float32)
+    lib().oracle_main_compressor_fp8(_p(state), _p(sr), state.shape[1], _p(ps), _p(nw), _p(ct), _p(st), ct.shape[0], eps,
+                                     _p(pool), _p(dst), epb, stride, _p(q8), _p(s8), _p(rope), rows)
+    return q8, s8, rope
+
+
+def window_kv_fp8(y, pos, norm_w, cos_t, sin_t, eps=1e-6, pool=None, dst=None, epb=256):
+    """y fp32 [rows,512].  Returns (q8 [rows,448], s8 [rows,7], rope uint16 [rows,64])."""
+    y = _c(y, np.float32)
+    rows = y.shape[0]
+    q8, s8 = np.empty((rows, 448), np.uint8), np.empty((rows, 7), np.float32)
+    rope = np.empty((rows, 64), np.uint16)
+    pool, dst, epb, stride = _pool_args(pool, dst, epb)
+    ps = _c(pos, np.int64)
+    nw, ct, st = _c(norm_w, np.float32), _c(cos_t, np.float32), _c(sin_t, np.float32)
+    lib().oracle_window_kv_fp8(_p(y), _p(ps), _p(nw), _p(ct), _p(st), ct.shape[0], eps, _p(pool), _p(dst), epb, stride,
+                               _p(q8), _p(s8), _p(rope), rows)
+    return q8, s8, rope
 
 
 def gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=True):

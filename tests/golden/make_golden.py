@@ -10,6 +10,8 @@ Functions used (paths inside the reference repository):
   dsv4_megakernel/megakernel/test/test_topk_v2.py         ref_page_transform (:86-94) and the
                                                            stable-argsort rule (:116)
   dsv4_megakernel/megakernel/test/test_e2e_decode.py      ref_mhc_post (:423-426)
+  dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py   ref_comp_step (:550-586, fp8 form) and
+                                                           ref_win_step (:646-665)
   dsv4_megakernel/megakernel/test/kv_cache_manager.py     KVCacheManager (:53-257), run on the CPU
 The first two are written for device="cuda"; they are run here on the CPU by mapping that one
 keyword to "cpu", which changes no arithmetic.
@@ -172,6 +174,39 @@ def golden_mhc_post(ref_root):
     print("mhc_post_7168.npz", tuple(out.shape))
 
 
+def golden_cache_writers(ref_root):
+    """Indexer compressor (FP8 form) and window-KV torch twins on seeded state rings."""
+    wqb = _load(ref_root, "dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py", "ref_wqb")
+    wqb.torch = torch
+    g = torch.Generator().manual_seed(61)
+    max_pos = 64
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float32), 1.0 / (10000.0 ** (torch.arange(32) / 32.0)))
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+
+    rows = 12
+    pos = torch.tensor([3, 7, 11, 12, 15, 19, 23, 30, 31, 35, 47, 59])
+    state = torch.randn(rows, 8, 512, generator=g)
+    state[0, 4:, :256], state[0, 4:, 256:] = 0.0, float("-inf")     # a fresh request: entries 4..7 never written
+    state[1, :, 256:] *= 8.0                                        # peaked softmax
+    state_row = torch.arange(rows) * 8 + pos % 8
+    norm_w = torch.rand(128, generator=g) + 0.5
+    q, scale, mask = wqb.ref_comp_step(state, state_row, pos, norm_w, cos, sin, fp8=True)
+    np.savez_compressed(os.path.join(HERE, "indexer_compressor_fp8.npz"), state=state.numpy(), pos=pos.numpy(),
+                        state_row=state_row.numpy(), norm_w=norm_w.numpy(), cos=cos.numpy(), sin=sin.numpy(),
+                        q8=q.view(torch.uint8).numpy(), scale=scale.numpy(), compress=mask.numpy())
+    print("indexer_compressor_fp8.npz", int(mask.sum()), "compress rows of", rows)
+
+    rows = 6
+    y = torch.randn(rows, 512, generator=g) * torch.tensor([1.0, 0.01, 30.0, 1.0, 1e-4, 3.0]).view(rows, 1)
+    wpos = torch.tensor([0, 1, 17, 33, 62, 63])
+    wnorm = torch.rand(512, generator=g) + 0.5
+    q8, s8, rope = wqb.ref_win_step(y, wpos, wnorm, cos, sin)
+    np.savez_compressed(os.path.join(HERE, "window_kv_fp8.npz"), y=y.numpy(), pos=wpos.numpy(), norm_w=wnorm.numpy(),
+                        cos=cos.numpy(), sin=sin.numpy(), q8=q8.view(torch.uint8).numpy(), s8=s8.numpy(),
+                        rope=_u16(rope))
+    print("window_kv_fp8.npz", tuple(q8.shape))
+
+
 KV_TRACE_CONFIGS = [
     dict(capacity=5, pages_per_pool=96, max_pages_per_req=12),
     dict(capacity=5, pages_per_pool=96, max_pages_per_req=12, state_ring_entries=16),
@@ -259,6 +294,7 @@ def main():
     golden_norm_rope_quant(ref_root)
     golden_mhc_post(ref_root)
     golden_kv_cache(ref_root)
+    golden_cache_writers(ref_root)
 
 
 if __name__ == "__main__":

@@ -141,3 +141,67 @@ def test_mhc_post_oracle_matches_reference_formula():
     exact = np.einsum("mij,mih->mjh", g["comb"].astype(np.float64), res) + g["post"][..., None] * x[:, None, :]
     err = np.abs(oracle.bf16_to_f32(got) - exact)
     assert np.all(err <= np.abs(exact) * 2.0 ** -8 + 1e-6)
+
+
+def test_indexer_compressor_oracle_matches_reference_twin():
+    g = load_golden("indexer_compressor_fp8.npz")
+    q8, scale = oracle.indexer_compressor_fp8(g["state"], g["state_row"], g["pos"], g["norm_w"], g["cos"], g["sin"])
+    m = g["compress"]
+    assert np.array_equal(m, (g["pos"] + 1) % 4 == 0) and m.sum() >= 8
+    assert (q8[~m] == 0xAB).all() and (scale[~m] == -1).all()          # other rows are not touched
+    # the twin forms softmax(score) * kv and sums; the oracle divides two running sums: the bf16
+    # rounding that follows hides the difference almost always
+    assert np.mean(q8[m] == g["q8"][m]) >= 0.995
+    assert np.allclose(scale[m], g["scale"][m], rtol=2 ** -7)
+    assert np.mean(scale[m] == g["scale"][m]) >= 0.9
+
+
+def test_window_kv_oracle_matches_reference_twin():
+    g = load_golden("window_kv_fp8.npz")
+    q8, s8, rope = oracle.window_kv_fp8(g["y"], g["pos"], g["norm_w"], g["cos"], g["sin"])
+    assert np.array_equal(s8, g["s8"])                                  # power-of-two scales: exact
+    assert np.mean(q8 == g["q8"]) >= 0.995
+    assert np.mean(rope == g["rope"]) >= 0.995
+    assert np.abs(rope.astype(np.int32) - g["rope"].astype(np.int32)).max() <= 1
+
+
+def test_main_compressor_oracle_structure():
+    """No callable twin exists for the MAIN compressor (the reference checks it inline,
+    test_mqa_logits_fp4.py:769-789); its two halves are the code pinned above: the window
+    sum / norm / rotation of the indexer compressor at width 512 and the MODEL1 quantiser of
+    the window writer.  Here: a float64 evaluation of the same formula, and the record layout."""
+    rng = np.random.default_rng(9)
+    rows, ring, epb = 8, 8, 4
+    pos = np.arange(rows, dtype=np.int64)
+    state = rng.normal(size=(rows, ring, 2048)).astype(np.float32)
+    state_row = np.arange(rows) * ring + pos % ring
+    norm = (rng.random(512) + 0.5).astype(np.float32)
+    ang = np.outer(np.arange(16, dtype=np.float32), 1.0 / (10000.0 ** (np.arange(32) / 32.0))).astype(np.float32)
+    cos, sin = np.cos(ang), np.sin(ang)
+    stride = epb * 584 + 128
+    pool = np.full((2, stride), 0xA5, np.uint8)
+    q8, s8, rope = oracle.main_compressor_fp8(state, state_row, pos, norm, cos, sin, pool=pool,
+                                              dst=np.arange(rows), epb=epb)
+    for r in range(rows):
+        page, off = pool[r // epb], r % epb
+        body, sb = page[off * 576:(off + 1) * 576], page[epb * 576 + off * 8:epb * 576 + off * 8 + 8]
+        if (pos[r] + 1) % 4:
+            assert (q8[r] == 0xAB).all() and (s8[r] == -1).all() and (body == 0xA5).all() and (sb == 0xA5).all()
+            continue
+        assert np.array_equal(body[:448], q8[r]) and np.array_equal(body[448:].view(np.uint16), rope[r])
+        assert np.array_equal(sb[:7], (np.log2(s8[r]) + 127).astype(np.uint8)) and sb[7] == 0xA5
+        cur = int(state_row[r]) % ring
+        perm = [(cur - 7 + k) % ring for k in range(8)]
+        kv = np.stack([state[r, perm[k], (0 if k < 4 else 512):(512 if k < 4 else 1024)] for k in range(8)]).astype(np.float64)
+        sc = np.stack([state[r, perm[k], 1024 + (0 if k < 4 else 512):1024 + (512 if k < 4 else 1024)] for k in range(8)]).astype(np.float64)
+        e = np.exp(sc - sc.max(0))
+        agg = (e * kv).sum(0) / e.sum(0)
+        ro = agg / np.sqrt((agg * agg).mean() + 1e-6) * norm
+        p = pos[r] - 3
+        ev, od = ro[448::2].copy(), ro[449::2].copy()
+        ro[448::2], ro[449::2] = ev * cos[p] - od * sin[p], ev * sin[p] + od * cos[p]
+        deq = oracle.e4m3_decode(q8[r]).reshape(7, 64) * s8[r][:, None]
+        assert np.all(np.abs(deq - ro[:448].reshape(7, 64)) <= s8[r][:, None] * 16 * 1.01 + np.abs(ro[:448].reshape(7, 64)) * 2 ** -6)
+        mag = np.repeat(np.abs(ev) + np.abs(od), 2)                  # three bf16 roundings of the pair
+        assert np.all(np.abs(oracle.bf16_to_f32(rope[r]) - ro[448:]) <= mag * 2 ** -6 + 1e-3)
+    assert (pool[:, epb * 584:] == 0xA5).all()

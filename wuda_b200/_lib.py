@@ -18,6 +18,29 @@ lib = ctypes.CDLL(LIB_PATH)
 
 c_int, c_i64, c_vp, c_float = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
 
+
+
+class CompressorBundle(ctypes.Structure):
+    """wuda_compressor_bundle"""
+    _fields_ = [("state", c_vp), ("state_row", c_vp), ("norm_w", c_vp), ("state_rows_total", c_i64),
+                ("ring_entries", c_int), ("entries_per_block", c_int), ("num_blocks", c_int), ("reserved", c_int),
+                ("block_stride_bytes", c_i64), ("pool", c_vp), ("dst", c_vp), ("q8", c_vp), ("s8", c_vp),
+                ("rope", c_vp)]
+
+
+class WindowBundle(ctypes.Structure):
+    """wuda_window_bundle"""
+    _fields_ = [("y", c_vp), ("norm_w", c_vp), ("entries_per_block", c_int), ("num_blocks", c_int),
+                ("block_stride_bytes", c_i64), ("pool", c_vp), ("dst", c_vp), ("q8", c_vp), ("s8", c_vp),
+                ("rope", c_vp)]
+
+
+class CacheWriters(ctypes.Structure):
+    """wuda_cache_writers"""
+    _fields_ = [("pos", c_vp), ("cos_table", c_vp), ("sin_table", c_vp), ("max_pos", c_int), ("eps", c_float),
+                ("indexer", CompressorBundle), ("main", CompressorBundle), ("window", WindowBundle)]
+
+
 # name -> (restype, argtypes); mirrors include/wuda_b200.h one to one.
 SIGNATURES = {
     "wuda_version": (c_int, []),
@@ -31,6 +54,7 @@ SIGNATURES = {
     "wuda_rmsnorm_quant_fp8": (c_int, [c_vp, c_i64, c_vp, c_int, c_float, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp]),
     "wuda_rope_quant_fp8": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_vp]),
+    "wuda_cache_writers_fp8": (c_int, [ctypes.POINTER(CacheWriters), c_int, c_vp, c_vp]),
     "wuda_mhc_post": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
     "wuda_gemm_fp8_scratch_bytes": (c_i64, [c_int, c_int]),
     "wuda_gemm_fp8_blockscaled": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),

@@ -6,6 +6,8 @@ PYBIND11_MODULE per file) and forwards to the C ABI.  Arguments are validated th
 the reference's TORCH_CHECK blocks do and failures raise RuntimeError before anything is
 launched.  Work is enqueued on torch's current CUDA stream.
 """
+import ctypes
+
 import torch
 
 from . import _lib
@@ -13,7 +15,7 @@ from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
-           "rmsnorm_rope_out", "mhc_post_out", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
+           "rmsnorm_rope_out", "mhc_post_out", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -250,6 +252,95 @@ def mhc_post_out(attention_out, residual, post, comb, output):
     check(lib.wuda_mhc_post(attention_out.data_ptr(), residual.data_ptr(), post.data_ptr(), comb.data_ptr(),
                             output.data_ptr(), m, hidden, _stream()))
     return output
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+def _f32(t, name, last=None):
+    _require(t.is_cuda and t.is_contiguous() and t.dtype == torch.float32 and (last is None or t.size(-1) == last),
+             f"{name} must be contiguous CUDA fp32" + (f" [..., {last}]" if last else ""))
+    return t
+
+
+def _pool_fields(bundle, rows, name):
+    pool, dst = bundle.get("pool"), bundle.get("dst")
+    if pool is None:
+        return dict(entries_per_block=1, num_blocks=1, block_stride_bytes=0, pool=None, dst=None)
+    _require(pool.is_cuda and pool.dtype == torch.uint8 and pool.dim() == 2 and pool.stride(1) == 1,
+             f"{name}: pool must be CUDA uint8 [pages, stride]")
+    _require(dst is not None and dst.is_cuda and dst.is_contiguous() and dst.dtype == torch.int64
+             and dst.numel() == rows, f"{name}: dst must be contiguous CUDA int64 [rows]")
+    return dict(entries_per_block=int(bundle["entries_per_block"]), num_blocks=pool.size(0),
+                block_stride_bytes=pool.stride(0), pool=pool.data_ptr(), dst=dst.data_ptr())
+
+
+def _compact_fields(bundle, rows, name, nq, ns, with_rope):
+    q8, s8, rope = bundle.get("q8"), bundle.get("s8"), bundle.get("rope")
+    if q8 is not None:
+        _require(q8.is_cuda and q8.is_contiguous() and q8.element_size() == 1 and q8.numel() == rows * nq,
+                 f"{name}: q8 must be contiguous CUDA 1-byte [rows, {nq}]")
+    if s8 is not None:
+        _require(s8.is_cuda and s8.is_contiguous() and s8.dtype == torch.float32 and s8.numel() == rows * ns,
+                 f"{name}: s8 must be contiguous CUDA fp32 with {ns} per row")
+    if rope is not None:
+        _require(with_rope and rope.is_cuda and rope.is_contiguous() and rope.dtype == torch.bfloat16
+                 and rope.numel() == rows * 64, f"{name}: rope must be contiguous CUDA bf16 [rows, 64]")
+    return dict(q8=_ptr(q8), s8=_ptr(s8), rope=_ptr(rope))
+
+
+def _compressor_bundle(bundle, rows, name, half):
+    if bundle is None:
+        return _lib.CompressorBundle()
+    state = _f32(bundle["state"], name + ".state", 4 * half)
+    ring = int(bundle.get("ring_entries", state.size(-2) if state.dim() == 3 else 8))
+    row = bundle["state_row"]
+    _require(row.is_cuda and row.is_contiguous() and row.dtype == torch.int64 and row.numel() == rows,
+             f"{name}: state_row must be contiguous CUDA int64 [rows]")
+    norm = _f32(bundle["norm_w"], name + ".norm_w", half)
+    fields = dict(state=state.data_ptr(), state_row=row.data_ptr(), norm_w=norm.data_ptr(),
+                  state_rows_total=state.numel() // (4 * half), ring_entries=ring)
+    fields.update(_pool_fields(bundle, rows, name))
+    fields.update(_compact_fields(bundle, rows, name, 128 if half == 128 else 448, 1 if half == 128 else 7, half == 512))
+    return _lib.CompressorBundle(**fields)
+
+
+def cache_writers_fp8(pos, cos_table, sin_table, *, indexer=None, main=None, window=None, eps=1e-6, status_word=None):
+    """The indexer compressor, the MAIN compressor and the window-KV writer of one decode step in one
+    launch (wuda_cache_writers_fp8).  Each writer is a dict or None:
+      indexer / main: state fp32 [blocks, ring, 512 | 2048], state_row int64 [rows], norm_w fp32 [128 | 512],
+                      optional pool uint8 [pages, stride] + dst int64 [rows] + entries_per_block,
+                      optional compact outputs q8, s8 (and rope bf16 [rows,64] for main)
+      window:         y fp32 [rows, 512], norm_w fp32 [512], the same optional pool and compact outputs
+    Everything is caller-owned; nothing is allocated."""
+    _require(pos.is_cuda and pos.is_contiguous() and pos.dtype == torch.int64 and pos.dim() == 1,
+             "pos must be contiguous CUDA int64 [rows]")
+    rows = pos.numel()
+    _f32(cos_table, "cos_table", 32)
+    _f32(sin_table, "sin_table", 32)
+    _require(cos_table.shape == sin_table.shape and cos_table.dim() == 2, "cos/sin tables must both be [max_pos, 32]")
+    args = _lib.CacheWriters(pos=pos.data_ptr(), cos_table=cos_table.data_ptr(), sin_table=sin_table.data_ptr(),
+                             max_pos=cos_table.size(0), eps=float(eps))
+    args.indexer = _compressor_bundle(indexer, rows, "indexer", 128)
+    args.main = _compressor_bundle(main, rows, "main", 512)
+    if window is not None:
+        y = _f32(window["y"], "window.y", 512)
+        _require(y.numel() == rows * 512, "window.y must be [rows, 512]")
+        fields = dict(y=y.data_ptr(), norm_w=_f32(window["norm_w"], "window.norm_w", 512).data_ptr())
+        fields.update(_pool_fields(window, rows, "window"))
+        fields.update(_compact_fields(window, rows, "window", 448, 7, True))
+        args.window = _lib.WindowBundle(**fields)
+    check(lib.wuda_cache_writers_fp8(ctypes.byref(args), rows, _ptr(status_word), _stream()))
+
+
+def mqa_compressor_fp8_standalone(cmp_pos, comp_norm, cos_tab, sin_tab, comp_state, comp_state_row,
+                                  comp_state_ring_entries, comp_q8, comp_s8, comp_rope, comp_eps=1e-6):
+    """The MAIN compressor on its own, with the reference's argument list
+    (kernels/mqa_logits_fp8.cu:542-599): compact outputs only."""
+    cache_writers_fp8(cmp_pos, cos_tab, sin_tab, eps=comp_eps,
+                      main=dict(state=comp_state, state_row=comp_state_row, norm_w=comp_norm,
+                                ring_entries=comp_state_ring_entries, q8=comp_q8, s8=comp_s8, rope=comp_rope))
 
 
 def rmsnorm_rope_out(x, positions, cos_table, sin_table, out, input_heads=None, eps=1e-6, pdl=False, max_blocks=0):
