@@ -159,6 +159,40 @@ int wuda_rope_quant_fp8(const void* x_bf16, const int64_t* positions, const floa
                         void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Indexer-q post (FP8 form): every (token, index head) row of 128 bf16 values gets RoPE on its
+ * last 64 dims (rounded to bf16), one scale = max(amax / 448, 1e-12), e4m3 payload, and the
+ * head weight multiplied by that scale - what wuda_mqa_logits_fp8 takes as q and weights.
+ *
+ * Replaces idx_postprocess_fp8_standalone and the idx-post tail of wq_b_proj_gemm_merged
+ * (include/idx_post_fp4.cuh:229-283, kernels/wq_b_fp8_gemm.cu:1368-1567); numerics as the
+ * torch twin test/test_wq_b_fp8_gemm.py:184-196.
+ *
+ *   iq_bf16   bf16, row t starts at t * row_stride elements and holds heads * 128 values
+ *             (so the projection's output is read in place); row_stride % 8 == 0
+ *   q_pos     int32 [tokens], clamped into [0, max_pos);  tables fp32 [max_pos, 32]
+ *   weights   fp32 [tokens, heads], nullable (then weights_out receives the bare scales)
+ *   q_fp8     e4m3 [tokens, heads, 128];  weights_out fp32 [tokens, heads]
+ */
+int wuda_index_q_post_fp8(const void* iq_bf16, int64_t row_stride, const int32_t* q_pos, const float* cos_table,
+                          const float* sin_table, int max_pos, const float* weights, void* q_fp8,
+                          float* weights_out, int tokens, int heads, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Query RMSNorm (no weight) + RoPE on the last 64 of every 512-wide head, bf16 -> bf16, in
+ * one pass with one rounding.  Output head h reads input head h % input_heads.
+ *
+ * Replaces rmsnorm_rope_out (kernels/rmsnorm_prod.cu:91-167) and the query tail of
+ * mqa_logits_fp8_decode_out (QueryRmsRopeArgs, include/mqa_logits_fp8.cuh:47-116;
+ * include/query_rms_rope.cuh:20-61).
+ *
+ *   x_bf16    bf16, row t at t * row_stride elements, input_heads * 512 values
+ *   positions int64 [tokens];  out_bf16 bf16 [tokens, output_heads, 512]
+ */
+int wuda_query_rms_rope(const void* x_bf16, int64_t row_stride, const int64_t* positions, const float* cos_table,
+                        const float* sin_table, int max_pos, void* out_bf16, int tokens, int input_heads,
+                        int output_heads, float eps, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * The cache writers of a decode step, all in one launch: the indexer compressor, the MAIN
  * compressor and the window-KV writer.  Each fills the paged pool its consumer reads and,
  * optionally, compact per-row copies of what it wrote.

@@ -476,6 +476,67 @@ void oracle_window_kv_fp8(const float* y, const int64_t* pos, const float* norm_
     }
 }
 
+/* ------------------------------------------------------------------ query-side tails
+ *
+ * Indexer-q post after dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py:184-196
+ * (ref_idx_fp8_chain): bf16 head of 128 -> RoPE on the last 64 (bf16 round) -> scale =
+ * max(amax/448, 1e-12) -> e4m3(x / scale); the head weight is multiplied by the scale.
+ */
+__attribute__((optimize("fp-contract=off")))
+void oracle_index_q_post_fp8(const uint16_t* x, int64_t row_stride, const int32_t* q_pos, const float* cos_t,
+                             const float* sin_t, int max_pos, const float* weights, uint8_t* q8, float* w_out,
+                             int tokens, int heads) {
+    for (int t = 0; t < tokens; ++t) {
+        int pos = q_pos[t] < 0 ? 0 : (q_pos[t] >= max_pos ? max_pos - 1 : q_pos[t]);
+        for (int h = 0; h < heads; ++h) {
+            float v[128];
+            for (int i = 0; i < 128; ++i) v[i] = bf16_to_f32(x[t * row_stride + h * 128 + i]);
+            rotate_tail(v + 64, cos_t + (int64_t)pos * 32, sin_t + (int64_t)pos * 32, 1);
+            float amax = 0.0f;
+            for (int i = 0; i < 128; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            const float scale = fmaxf(amax / 448.0f, 1e-12f);
+            const int64_t g = (int64_t)t * heads + h;
+            for (int i = 0; i < 128; ++i) q8[g * 128 + i] = oracle_f32_to_e4m3(v[i] / scale);
+            w_out[g] = weights ? weights[g] * scale : scale;
+        }
+    }
+}
+
+/* Query RMSNorm (no weight) + RoPE on the last 64 of 512, one rounding to bf16, after
+ * dsv4_megakernel/megakernel/include/query_rms_rope.cuh:20-61: the sum of squares runs as fused
+ * multiply-adds over the 16 values a lane holds (columns [8l, 8l+8) then [256+8l, 256+8l+8)) and a
+ * 32-lane butterfly.  1/sqrt is the C library's (the reference kernel uses the approximate rsqrtf).
+ */
+__attribute__((optimize("fp-contract=off")))
+void oracle_query_rms_rope(const uint16_t* x, int64_t row_stride, const int64_t* positions, const float* cos_t,
+                           const float* sin_t, int max_pos, uint16_t* out, int tokens, int in_heads, int out_heads,
+                           float eps) {
+    for (int t = 0; t < tokens; ++t) {
+        int64_t pos = positions[t] < 0 ? 0 : (positions[t] >= max_pos ? max_pos - 1 : positions[t]);
+        for (int h = 0; h < out_heads; ++h) {
+            float v[512], lane[32];
+            const uint16_t* src = x + t * row_stride + (h % in_heads) * 512;
+            for (int i = 0; i < 512; ++i) v[i] = bf16_to_f32(src[i]);
+            for (int l = 0; l < 32; ++l) {
+                float ss = 0.0f;
+                for (int i = 0; i < 8; ++i) ss = fmaf(v[8 * l + i], v[8 * l + i], ss);
+                for (int i = 0; i < 8; ++i) ss = fmaf(v[256 + 8 * l + i], v[256 + 8 * l + i], ss);
+                lane[l] = ss;
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                float next[32];
+                for (int l = 0; l < 32; ++l) next[l] = lane[l] + lane[l ^ o];
+                memcpy(lane, next, sizeof lane);
+            }
+            const float scale = 1.0f / sqrtf(lane[0] / 512.0f + eps);
+            for (int i = 0; i < 512; ++i) v[i] = v[i] * scale;
+            rotate_tail(v + 448, cos_t + pos * 32, sin_t + pos * 32, 0);
+            uint16_t* dst = out + ((int64_t)t * out_heads + h) * 512;
+            for (int i = 0; i < 512; ++i) dst[i] = f32_to_bf16(v[i]);
+        }
+    }
+}
+
 /* ------------------------------------------------------------------ mHC post mix
  *
  * out[m,j,d] = post[m,j] * x[m,d] + sum_i comb[m,i,j] * res[m,i,d], bf16 in and out, in the

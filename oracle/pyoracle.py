@@ -60,6 +60,8 @@ def _declare(l):
                                              i64, vp, vp, vp, c.c_int]
     l.oracle_window_kv_fp8.argtypes = [vp, vp, vp, vp, vp, c.c_int, c.c_float, vp, vp, c.c_int, i64, vp, vp, vp,
                                        c.c_int]
+    l.oracle_index_q_post_fp8.argtypes = [vp, i64, vp, vp, vp, c.c_int, vp, vp, vp, c.c_int, c.c_int]
+    l.oracle_query_rms_rope.argtypes = [vp, i64, vp, vp, vp, c.c_int, vp, c.c_int, c.c_int, c.c_int, c.c_float]
     l.oracle_gemm_nvfp4.argtypes = [c.c_void_p, c.c_void_p, c.c_float, c.c_void_p, c.c_void_p, c.c_float, c.c_void_p,
                                     c.c_int, c.c_int, c.c_int, c.c_int]
     l.oracle_gemm_fp8_blockscaled.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
@@ -218,6 +220,30 @@ def window_kv_fp8(y, pos, norm_w, cos_t, sin_t, eps=1e-6, pool=None, dst=None, e
     return q8, s8, rope
 
 
+def index_q_post_fp8(x_bf16, q_pos, cos_t, sin_t, weights=None):
+    """x uint16 (bf16) [tokens, heads, 128] -> (q8 uint8 [tokens, heads, 128], weights * scale [tokens, heads])."""
+    x = _c(x_bf16, np.uint16)
+    tokens, heads = x.shape[0], x.shape[1]
+    ct, st = _c(cos_t, np.float32), _c(sin_t, np.float32)
+    q8, w = np.empty((tokens, heads, 128), np.uint8), np.empty((tokens, heads), np.float32)
+    wt = None if weights is None else _c(weights, np.float32)
+    lib().oracle_index_q_post_fp8(_p(x), heads * 128, _p(_c(q_pos, np.int32)), _p(ct), _p(st), ct.shape[0], _p(wt),
+                                  _p(q8), _p(w), tokens, heads)
+    return q8, w
+
+
+def query_rms_rope(x_bf16, positions, cos_t, sin_t, out_heads=None, eps=1e-6):
+    """x uint16 (bf16) [tokens, heads, 512] -> uint16 [tokens, out_heads, 512]."""
+    x = _c(x_bf16, np.uint16)
+    tokens, heads = x.shape[0], x.shape[1]
+    out_heads = out_heads or heads
+    ct, st = _c(cos_t, np.float32), _c(sin_t, np.float32)
+    out = np.empty((tokens, out_heads, 512), np.uint16)
+    lib().oracle_query_rms_rope(_p(x), heads * 512, _p(_c(positions, np.int64)), _p(ct), _p(st), ct.shape[0], _p(out),
+                                tokens, heads, out_heads, eps)
+    return out
+
+
 def gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=True):
     """a e4m3 bytes [M,K], a_s fp32 [M,K/128], b e4m3 bytes [N,K], b_s fp32 [N/128,K/128].
     Returns uint16 (bf16) or fp32 [M,N]."""
@@ -232,6 +258,12 @@ def gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=True):
 
 def bf16_to_f32(u16):
     return (np.asarray(u16, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(x):
+    """Round-to-nearest-even fp32 -> bf16 bit patterns (finite inputs)."""
+    b = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
 
 
 def gemm_nvfp4(a, a_sf, a_gs, w, w_sf, w_gs, out_bf16=True):

@@ -196,6 +196,16 @@ def golden_cache_writers(ref_root):
                         q8=q.view(torch.uint8).numpy(), scale=scale.numpy(), compress=mask.numpy())
     print("indexer_compressor_fp8.npz", int(mask.sum()), "compress rows of", rows)
 
+    tokens, heads = 5, 64
+    iq = (torch.randn(tokens, heads, 128, generator=g) * torch.rand(tokens, heads, 1, generator=g) * 4).bfloat16()
+    iq[0, 0] = 0                                                      # an all-zero head: the 1e-12 clamp
+    w = torch.randn(tokens, heads, generator=g) / 8
+    qpos = torch.tensor([0, 1, 13, 40, 63], dtype=torch.int32)
+    q, wf = wqb.ref_idx_fp8_chain(iq, w, qpos.long(), cos, sin)
+    np.savez_compressed(os.path.join(HERE, "index_q_post_fp8.npz"), iq=_u16(iq), weights=w.numpy(), q_pos=qpos.numpy(),
+                        cos=cos.numpy(), sin=sin.numpy(), q8=q.view(torch.uint8).numpy(), w_folded=wf.numpy())
+    print("index_q_post_fp8.npz", tuple(q.shape))
+
     rows = 6
     y = torch.randn(rows, 512, generator=g) * torch.tensor([1.0, 0.01, 30.0, 1.0, 1e-4, 3.0]).view(rows, 1)
     wpos = torch.tensor([0, 1, 17, 33, 62, 63])

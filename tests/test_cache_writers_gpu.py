@@ -80,7 +80,7 @@ def test_window_kv_golden(wuda):
 def make_step(rows, ring, seed, epb_idx=64, epb_cmp=64, epb_swa=256, pad=0):
     rng = np.random.default_rng(seed)
     pos = rng.integers(3, 4000, size=rows).astype(np.int64)
-    pos[: rows // 2] |= 3                                   # at least half the rows compress
+    pos[: (rows + 1) // 2] |= 3                                   # at least half the rows compress
     cos, sin = rope_tables(4096)
     case = dict(pos=pos, cos=cos, sin=sin, ring=ring)
     case["idx_state"] = rng.normal(size=(rows, ring, 512)).astype(np.float32)

@@ -138,9 +138,50 @@ def test_query_rmsnorm_rope_reference_signature(wuda):
     out = torch.empty(3, 64, 512, dtype=torch.bfloat16, device="cuda")
     wuda.rmsnorm_rope_out(x.cuda(), pos.cuda(), ang.cos().cuda().contiguous(), ang.sin().cuda().contiguous(), out, 64, 1e-6)
     torch.cuda.synchronize()
+    ref = oracle.query_rms_rope(u16(x), pos.numpy(), ang.cos().numpy(), ang.sin().numpy())
+    assert np.array_equal(u16(out), ref)              # same operations in the same order: bit-exact
+    # against the two-pass form (norm -> bf16 -> rotate -> bf16) only the 64 rotated dims may move a step
     normed = oracle.rmsnorm_bf16(u16(x).reshape(-1, 512), np.ones(512, np.float32), 1e-6).reshape(3, 64, 512)
-    ref = oracle.rope_bf16(normed, pos.numpy(), ang.cos().numpy(), ang.sin().numpy(), 64)
-    bf16_close(u16(out), ref, min_equal=0.995)
+    two_pass = oracle.rope_bf16(normed, pos.numpy(), ang.cos().numpy(), ang.sin().numpy(), 64)
+    bf16_close(u16(out)[..., :448], two_pass[..., :448], min_equal=0.995)
+    bf16_close(u16(out), two_pass, min_equal=0.95)
+
+
+def test_query_rmsnorm_rope_strided_input_and_head_duplication(wuda):
+    """x is read in place from a wider projection output; out head h reads head h % heads."""
+    gen = torch.Generator().manual_seed(8)
+    wide = torch.randn(5, 8192 + 4 * 512, generator=gen).bfloat16().cuda()
+    x = wide[:, 8192:].unflatten(-1, (4, 512))
+    pos = torch.tensor([0, 1, 100, 4095, 9999], device="cuda")     # the last one is clamped to the table
+    freqs = 1.0 / (10000 ** (torch.arange(0, 64, 2, dtype=torch.float32) / 64))
+    ang = torch.outer(torch.arange(4096).float(), freqs)
+    out = torch.empty(5, 8, 512, dtype=torch.bfloat16, device="cuda")
+    wuda.rmsnorm_rope_out(x, pos, ang.cos().cuda().contiguous(), ang.sin().cuda().contiguous(), out, 4, 1e-6)
+    torch.cuda.synchronize()
+    ref = oracle.query_rms_rope(u16(x.contiguous()), pos.cpu().numpy(), ang.cos().numpy(), ang.sin().numpy(), out_heads=8)
+    assert np.array_equal(u16(out), ref)
+    assert torch.equal(out[:, :4], out[:, 4:])
+
+
+def test_index_q_post_golden_and_oracle(wuda):
+    g = load_golden("index_q_post_fp8.npz")
+    iq = from_u16(g["iq"])
+    q, w = wuda.idx_postprocess_fp8(iq, torch.from_numpy(g["weights"]).cuda(), torch.from_numpy(g["q_pos"]).cuda(),
+                                    torch.from_numpy(g["cos"]).cuda(), torch.from_numpy(g["sin"]).cuda())
+    torch.cuda.synchronize()
+    oq, ow = oracle.index_q_post_fp8(g["iq"], g["q_pos"], g["cos"], g["sin"], g["weights"])
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), oq)    # correctly rounded operations only: exact
+    assert np.array_equal(w.cpu().numpy(), ow)
+    assert np.mean(oq == g["q8"]) >= 0.999 and np.allclose(ow, g["w_folded"], rtol=1e-6)
+    # strided input (a slice of the projection output), no weights -> bare scales
+    wide = torch.zeros(iq.size(0), 4096 + iq.size(1) * 128, dtype=torch.bfloat16, device="cuda")
+    wide[:, :iq.size(1) * 128] = iq.flatten(1)
+    q2, s2 = wuda.idx_postprocess_fp8(wide[:, :iq.size(1) * 128].unflatten(-1, (iq.size(1), 128)), None,
+                                      torch.from_numpy(g["q_pos"]).cuda(), torch.from_numpy(g["cos"]).cuda(),
+                                      torch.from_numpy(g["sin"]).cuda())
+    torch.cuda.synchronize()
+    assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8))
+    assert np.array_equal(s2.cpu().numpy() * g["weights"], ow)
 
 
 def test_bad_arguments(wuda):

@@ -205,3 +205,32 @@ def test_main_compressor_oracle_structure():
         mag = np.repeat(np.abs(ev) + np.abs(od), 2)                  # three bf16 roundings of the pair
         assert np.all(np.abs(oracle.bf16_to_f32(rope[r]) - ro[448:]) <= mag * 2 ** -6 + 1e-3)
     assert (pool[:, epb * 584:] == 0xA5).all()
+
+
+def test_index_q_post_oracle_matches_reference_twin():
+    g = load_golden("index_q_post_fp8.npz")
+    q8, w = oracle.index_q_post_fp8(g["iq"], g["q_pos"], g["cos"], g["sin"], g["weights"])
+    assert np.array_equal(q8, g["q8"])
+    assert np.array_equal(w, g["w_folded"])
+    assert (q8[0, 0] == 0).all() and w[0, 0] == g["weights"][0, 0] * np.float32(1e-12)
+
+
+def test_query_rms_rope_oracle_against_the_two_pass_fixtures():
+    """No twin of the fused query tail exists in the reference's tests; the oracle is held against
+    the origin model's RMSNorm (fixture rmsnorm_7168) re-used on 512-wide rows: unit weight, so
+    the not-rotated 448 columns must be the rounded x * rsqrt(mean x^2 + eps)."""
+    rng = np.random.default_rng(4)
+    x = oracle.f32_to_bf16(rng.normal(size=(3, 2, 512)).astype(np.float32))
+    ang = np.outer(np.arange(32, dtype=np.float32), 1.0 / (10000.0 ** (np.arange(32) / 32.0))).astype(np.float32)
+    out = oracle.query_rms_rope(x, [0, 7, 31], np.cos(ang), np.sin(ang), out_heads=4)
+    assert np.array_equal(out[:, :2], out[:, 2:])
+    normed = oracle.rmsnorm_bf16(x.reshape(-1, 512), np.ones(512, np.float32), 1e-6).reshape(3, 2, 512)
+    d = np.abs(out[:, :2, :448].astype(np.int32) - normed[..., :448].astype(np.int32))
+    assert d.max() <= 1 and np.mean(d == 0) >= 0.995
+    assert np.array_equal(out[0, :, 448:], normed[0, :, 448:]) or d.max() <= 1   # position 0: no rotation
+    xf = oracle.bf16_to_f32(x).astype(np.float64)
+    y = xf / np.sqrt((xf * xf).mean(-1, keepdims=True) + 1e-6)
+    ev, od = y[..., 448::2].copy(), y[..., 449::2].copy()
+    c, s = np.cos(ang.astype(np.float64))[[0, 7, 31]][:, None], np.sin(ang.astype(np.float64))[[0, 7, 31]][:, None]
+    y[..., 448::2], y[..., 449::2] = ev * c - od * s, ev * s + od * c
+    assert np.all(np.abs(oracle.bf16_to_f32(out[:, :2]) - y) <= np.abs(y) * 2.0 ** -8 + 1e-6)

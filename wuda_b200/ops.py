@@ -15,7 +15,7 @@ from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
-           "rmsnorm_rope_out", "mhc_post_out", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
+           "rmsnorm_rope_out", "mhc_post_out", "idx_postprocess_fp8", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -344,18 +344,53 @@ def mqa_compressor_fp8_standalone(cmp_pos, comp_norm, cos_tab, sin_tab, comp_sta
 
 
 def rmsnorm_rope_out(x, positions, cos_table, sin_table, out, input_heads=None, eps=1e-6, pdl=False, max_blocks=0):
-    """Per-head RMSNorm (no gamma) + RoPE on the last 64 dims, bf16 -> bf16, with the
-    reference's signature (kernels/rmsnorm_prod.cu:160-167); `out` is caller-owned."""
-    _require(x.is_cuda and x.is_contiguous() and x.dtype == torch.bfloat16 and x.dim() == 3,
-             "x must be contiguous CUDA bf16 [B, heads, 512]")
-    b, heads, d = x.shape
-    ones = torch.ones(d, dtype=torch.float32, device=x.device)
-    normed, _, _ = rmsnorm_quant(x.view(b * heads, d), ones, eps, quant=False)
-    rope_dim = cos_table.size(1) * 2
-    y16, _, _ = rope_quant(normed.view(b, heads, d), positions, cos_table, sin_table, rope_dim, quant=False,
-                           return_bf16=True)
-    out.copy_(y16 if out.shape == y16.shape else y16.repeat(1, out.size(1) // heads, 1))
+    """Per-head RMSNorm (no gamma) + RoPE on the last 64 dims, bf16 -> bf16 in one pass with one
+    rounding, with the reference's signature (kernels/rmsnorm_prod.cu:160-167).  `x` is
+    [B, heads, 512] and may be a column slice of a wider projection output (row stride taken from
+    the tensor); `out` is caller-owned [B, out_heads, 512], out head h reads head h % heads."""
+    _require(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3 and x.size(2) == 512
+             and x.stride(2) == 1 and x.stride(1) == 512, "x must be CUDA bf16 [B, heads, 512] with dense heads")
+    b, heads, _ = x.shape
+    _require(input_heads in (None, 0, heads), "input_heads must equal x.size(1)")
+    _require(out.is_cuda and out.is_contiguous() and out.dtype == torch.bfloat16 and out.dim() == 3
+             and out.size(0) == b and out.size(2) == 512 and out.size(1) % heads == 0,
+             "out must be contiguous CUDA bf16 [B, k * heads, 512]")
+    _require(positions.is_cuda and positions.is_contiguous() and positions.dtype == torch.int64
+             and positions.numel() == b, "positions must be contiguous CUDA int64 [B]")
+    _f32(cos_table, "cos_table", 32)
+    _f32(sin_table, "sin_table", 32)
+    check(lib.wuda_query_rms_rope(x.data_ptr(), x.stride(0), positions.data_ptr(), cos_table.data_ptr(),
+                                  sin_table.data_ptr(), cos_table.size(0), out.data_ptr(), b, heads, out.size(1),
+                                  float(eps), _stream()))
     return out
+
+
+def idx_postprocess_fp8(iq, weights, q_pos, rope_cos, rope_sin, q_fp8=None, weights_out=None):
+    """Indexer-q post, FP8 form (the reference's idx_postprocess_fp8_standalone,
+    kernels/wq_b_fp8_gemm.cu:1368-1567): iq bf16 [M, heads, 128] (may be a column slice of the
+    projection output), weights fp32 [M, heads] or None, q_pos int32 [M].  Returns
+    (q e4m3 [M, heads, 128], weights * scale fp32 [M, heads])."""
+    _require(iq.is_cuda and iq.dtype == torch.bfloat16 and iq.dim() == 3 and iq.size(2) == 128
+             and iq.stride(2) == 1 and iq.stride(1) == 128, "iq must be CUDA bf16 [M, heads, 128] with dense heads")
+    m, heads, _ = iq.shape
+    _require(q_pos.is_cuda and q_pos.is_contiguous() and q_pos.dtype == torch.int32 and q_pos.numel() == m,
+             "q_pos must be contiguous CUDA int32 [M]")
+    if weights is not None:
+        _require(weights.is_cuda and weights.is_contiguous() and weights.dtype == torch.float32
+                 and weights.numel() == m * heads, "weights must be contiguous CUDA fp32 [M, heads]")
+    _f32(rope_cos, "rope_cos", 32)
+    _f32(rope_sin, "rope_sin", 32)
+    if q_fp8 is None:
+        q_fp8 = torch.empty((m, heads, 128), dtype=torch.float8_e4m3fn, device=iq.device)
+    if weights_out is None:
+        weights_out = torch.empty((m, heads), dtype=torch.float32, device=iq.device)
+    _require(q_fp8.is_contiguous() and q_fp8.element_size() == 1 and q_fp8.numel() == m * heads * 128
+             and weights_out.is_contiguous() and weights_out.dtype == torch.float32
+             and weights_out.numel() == m * heads, "outputs must be contiguous [M, heads, 128] / fp32 [M, heads]")
+    check(lib.wuda_index_q_post_fp8(iq.data_ptr(), iq.stride(0), q_pos.data_ptr(), rope_cos.data_ptr(),
+                                    rope_sin.data_ptr(), rope_cos.size(0), _ptr(weights), q_fp8.data_ptr(),
+                                    weights_out.data_ptr(), m, heads, _stream()))
+    return q_fp8, weights_out
 
 
 _gemm_scratch = {}
