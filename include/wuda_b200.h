@@ -271,6 +271,93 @@ typedef struct wuda_cache_writers {
 int wuda_cache_writers_fp8(const wuda_cache_writers* args, int rows, int32_t* status_word, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Layer launch of the indexer half of one decode step: q RMSNorm + quantisation, the merged
+ * q projection, query RMSNorm + RoPE of the main heads, indexer-q post, the three cache
+ * writers, paged MQA logits and top-k - seven launches enqueued on `stream`, nothing
+ * allocated, no host synchronisation, so the call can be captured into a CUDA graph.
+ *
+ * Replaces the part of decode_step (test/test_e2e_decode.py:475-800) between the front GEMM
+ * and the sparse attention: qnorm_quant + wq_b_proj_gemm_merged, mqa_logits_fp8_decode_out
+ * with its compressor and query bundles, and topk_v2.  Its inputs are what the front GEMM
+ * publishes (q_raw, w64, win_y2, the fresh state-ring rows), its outputs what the sparse
+ * attention consumes (top-k page indices, normalised and rotated queries, the three caches).
+ *
+ * The merged weight holds the index heads first: rows [0, index_heads*128) then
+ * [.., + main_heads*512), K = q_lora, with fp32 128x128 block scales.  All pointers are
+ * device pointers; row arrays (pos, rows, dst) have m entries and the meaning they have in
+ * wuda_cache_writers_fp8.  n_compressed[r] is the number of indexer entries of request r
+ * INCLUDING the one written this step; block_table maps its logical indexer pages.
+ * 1 <= m <= 128.  status_word collects the device status of every kernel of the step.
+ */
+typedef struct wuda_csa_weights {
+    const void* wq_b;          /* e4m3 [index_heads*128 + main_heads*512, q_lora]            */
+    const float* wq_b_scales;  /* fp32 [ceil(rows/128), q_lora/128]                           */
+    const float* q_norm;       /* fp32 [q_lora]                                               */
+    const float* idx_norm;     /* fp32 [128]                                                  */
+    const float* main_norm;    /* fp32 [512]                                                  */
+    const float* win_norm;     /* fp32 [512]                                                  */
+    const float* cos_table;    /* fp32 [max_pos, 32]                                          */
+    const float* sin_table;
+    int max_pos;
+    int q_lora;
+    int index_heads;
+    int main_heads;            /* heads of 512 in the weight                                  */
+    int out_heads;             /* heads of q_main_out (a multiple of main_heads)              */
+    float eps;
+} wuda_csa_weights;
+
+typedef struct wuda_csa_caches {
+    float* idx_state;          /* fp32 [state_rows_total, 512]; NULL skips the writer          */
+    float* main_state;         /* fp32 [state_rows_total, 2048]; NULL skips the writer         */
+    int64_t state_rows_total;
+    int ring_entries;
+    int idx_entries_per_block, cmp_entries_per_block, swa_entries_per_block;
+    int idx_num_blocks, cmp_num_blocks, swa_num_blocks;
+    int reserved;
+    int64_t idx_block_stride_bytes, cmp_block_stride_bytes, swa_block_stride_bytes;
+    uint8_t* idx_pool;
+    uint8_t* cmp_pool;
+    uint8_t* swa_pool;
+} wuda_csa_caches;
+
+typedef struct wuda_csa_step {
+    const void* q_raw;         /* bf16, row r at r * q_raw_stride elements, q_lora values      */
+    int64_t q_raw_stride;
+    const float* w64;          /* fp32 [m, index_heads] head weights                           */
+    const float* win_y2;       /* fp32 [m, 512]; NULL skips the window writer                  */
+    const int64_t* pos;
+    const int32_t* q_pos;
+    const int64_t* main_state_row;
+    const int64_t* idx_state_row;
+    const int64_t* idx_dst;
+    const int64_t* cmp_dst;
+    const int64_t* swa_dst;
+    const int32_t* idx_block_table; /* int32 [m, block_table_stride]                           */
+    const int32_t* n_compressed;    /* int32 [m]                                               */
+    int block_table_stride;
+    int topk;
+    int64_t logits_stride;
+    float* logits;             /* fp32 [m, logits_stride], caller pre-fills -inf if it reads it */
+    int32_t* topk_indices;     /* int32 [m, topk] page-transformed                             */
+    int32_t* topk_raw;         /* int32 [m, topk] or NULL                                      */
+    void* q_main_out;          /* bf16 [m, out_heads, 512] or NULL                             */
+} wuda_csa_step;
+
+typedef struct wuda_csa_workspace {
+    void* q_fp8;               /* e4m3 [m, q_lora]                                             */
+    float* q_scales;           /* fp32 [m, q_lora/128]                                         */
+    void* y;                   /* bf16 [m, index_heads*128 + main_heads*512]                   */
+    void* iq_fp8;              /* e4m3 [m, index_heads, 128]                                   */
+    float* w_folded;           /* fp32 [m, index_heads]                                        */
+    void* gemm_scratch;        /* wuda_gemm_fp8_scratch_bytes(m, rows of wq_b), zeroed once    */
+    int64_t gemm_scratch_bytes;
+    int32_t* status_word;
+} wuda_csa_workspace;
+
+int wuda_csa_decode_step(const wuda_csa_weights* weights, const wuda_csa_caches* caches, const wuda_csa_step* step,
+                         const wuda_csa_workspace* workspace, int m, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * mHC post mix, the last op of an attention half-layer:
  *   output[t, j, d] = post[t, j] * attention_out[t, d] + sum_i comb[t, i, j] * residual[t, i, d]
  *

@@ -57,3 +57,28 @@ def test_invalid_arguments_are_rejected_before_launch():
     assert st == 1 and b"aligned" in L.lib.wuda_last_error()
     # empty batch is a no-op
     assert L.lib.wuda_mqa_logits_fp8(None, None, None, None, None, None, 0, 1, 4, 64, 64 * 132, 4, 256, None, None) == 0
+
+
+def test_struct_layouts_match_the_header(tmp_path):
+    """The ctypes mirrors of the argument structs have the size and field offsets the C compiler
+    gives the declarations in the header."""
+    import subprocess
+    import wuda_b200._lib as L
+    structs = {"wuda_compressor_bundle": L.CompressorBundle, "wuda_window_bundle": L.WindowBundle,
+               "wuda_cache_writers": L.CacheWriters, "wuda_csa_weights": L.CsaWeights, "wuda_csa_caches": L.CsaCaches,
+               "wuda_csa_step": L.CsaStep, "wuda_csa_workspace": L.CsaWorkspace}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "%s"' % HEADER, 'int main(void) {']
+    for cname, cls in structs.items():
+        lines.append('printf("%s %%zu\\n", sizeof(%s));' % (cname, cname))
+        for field, _ in cls._fields_:
+            lines.append('printf("%s.%s %%zu\\n", offsetof(%s, %s));' % (cname, field, cname, field))
+    lines += ['return 0; }']
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.check_call(["gcc", "-o", str(exe), str(src)])
+    out = dict(line.split() for line in subprocess.check_output([str(exe)], text=True).splitlines())
+    for cname, cls in structs.items():
+        assert int(out[cname]) == ctypes.sizeof(cls), cname
+        for field, _ in cls._fields_:
+            assert int(out["%s.%s" % (cname, field)]) == getattr(cls, field).offset, "%s.%s" % (cname, field)

@@ -200,7 +200,7 @@ def test_compressed_indexer_entries_feed_the_logits_kernel(wuda):
     wuda.cache_writers_fp8(cu(c["pos"]), cu(c["cos"]), cu(c["sin"]),
                            indexer=dict(state=cu(c["idx_state"]), state_row=cu(c["state_row"]),
                                         norm_w=cu(c["idx_norm"]), pool=pool, dst=cu(dst), entries_per_block=epb))
-    q = torch.randn(1, 1, 64, 128, device="cuda").clamp(-448, 448).to(torch.float8_e4m3fn)
+    q = torch.randn(1, 64, 128, device="cuda").clamp(-448, 448).to(torch.float8_e4m3fn)
     w = torch.randn(1, 64, device="cuda") / 8
     ctx = torch.tensor([[tokens]], dtype=torch.int32, device="cuda")
     bt = cu(table[None, :])

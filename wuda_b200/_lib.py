@@ -41,6 +41,37 @@ class CacheWriters(ctypes.Structure):
                 ("indexer", CompressorBundle), ("main", CompressorBundle), ("window", WindowBundle)]
 
 
+class CsaWeights(ctypes.Structure):
+    """wuda_csa_weights"""
+    _fields_ = [("wq_b", c_vp), ("wq_b_scales", c_vp), ("q_norm", c_vp), ("idx_norm", c_vp), ("main_norm", c_vp),
+                ("win_norm", c_vp), ("cos_table", c_vp), ("sin_table", c_vp), ("max_pos", c_int), ("q_lora", c_int),
+                ("index_heads", c_int), ("main_heads", c_int), ("out_heads", c_int), ("eps", c_float)]
+
+
+class CsaCaches(ctypes.Structure):
+    """wuda_csa_caches"""
+    _fields_ = [("idx_state", c_vp), ("main_state", c_vp), ("state_rows_total", c_i64), ("ring_entries", c_int),
+                ("idx_entries_per_block", c_int), ("cmp_entries_per_block", c_int), ("swa_entries_per_block", c_int),
+                ("idx_num_blocks", c_int), ("cmp_num_blocks", c_int), ("swa_num_blocks", c_int), ("reserved", c_int),
+                ("idx_block_stride_bytes", c_i64), ("cmp_block_stride_bytes", c_i64), ("swa_block_stride_bytes", c_i64),
+                ("idx_pool", c_vp), ("cmp_pool", c_vp), ("swa_pool", c_vp)]
+
+
+class CsaStep(ctypes.Structure):
+    """wuda_csa_step"""
+    _fields_ = [("q_raw", c_vp), ("q_raw_stride", c_i64), ("w64", c_vp), ("win_y2", c_vp), ("pos", c_vp),
+                ("q_pos", c_vp), ("main_state_row", c_vp), ("idx_state_row", c_vp), ("idx_dst", c_vp), ("cmp_dst", c_vp),
+                ("swa_dst", c_vp), ("idx_block_table", c_vp), ("n_compressed", c_vp), ("block_table_stride", c_int),
+                ("topk", c_int), ("logits_stride", c_i64), ("logits", c_vp), ("topk_indices", c_vp), ("topk_raw", c_vp),
+                ("q_main_out", c_vp)]
+
+
+class CsaWorkspace(ctypes.Structure):
+    """wuda_csa_workspace"""
+    _fields_ = [("q_fp8", c_vp), ("q_scales", c_vp), ("y", c_vp), ("iq_fp8", c_vp), ("w_folded", c_vp),
+                ("gemm_scratch", c_vp), ("gemm_scratch_bytes", c_i64), ("status_word", c_vp)]
+
+
 # name -> (restype, argtypes); mirrors include/wuda_b200.h one to one.
 SIGNATURES = {
     "wuda_version": (c_int, []),
@@ -57,6 +88,8 @@ SIGNATURES = {
     "wuda_cache_writers_fp8": (c_int, [ctypes.POINTER(CacheWriters), c_int, c_vp, c_vp]),
     "wuda_index_q_post_fp8": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
     "wuda_query_rms_rope": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_int, c_vp, c_int, c_int, c_int, c_float, c_vp]),
+    "wuda_csa_decode_step": (c_int, [ctypes.POINTER(CsaWeights), ctypes.POINTER(CsaCaches), ctypes.POINTER(CsaStep),
+                                     ctypes.POINTER(CsaWorkspace), c_int, c_vp]),
     "wuda_mhc_post": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
     "wuda_gemm_fp8_scratch_bytes": (c_i64, [c_int, c_int]),
     "wuda_gemm_fp8_blockscaled": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),

@@ -1,0 +1,90 @@
+// Layer launch of the indexer half of a decode step: the reference's three consecutive stages
+//   qnorm_quant + wq_b_proj_gemm_merged  (q RMSNorm + quant, q projection, indexer-q post,
+//                                          indexer compressor, window KV)
+//   mqa_logits_fp8_decode_out            (paged MQA logits, MAIN compressor, query RMSNorm + RoPE)
+//   topk_v2                              (top-k + page-table transform)
+// as they are called from decode_step (dsv4_megakernel/megakernel/test/test_e2e_decode.py:560-640),
+// enqueued on one stream with no host synchronisation and no allocation, so a caller can capture
+// the whole step into a CUDA graph once and replay it.  Everything here is host code: the step is
+// seven launches of this library's kernels in dependency order
+//   1 q RMSNorm + power-of-two 1x128 FP8 quantisation of q_raw
+//   2 block-scaled FP8 GEMM with the merged [indexer heads | main heads] weight
+//   3 query RMSNorm + RoPE of the main heads (reads the GEMM output in place)
+//   4 indexer-q post (reads the GEMM output in place) -> FP8 q + folded head weights
+//   5 cache writers: the indexer entry of this step must be in the pool before 6 scores it
+//   6 paged MQA logits over the indexer pool
+//   7 top-k + page transform
+#include "host.h"
+
+extern "C" int wuda_csa_decode_step(const wuda_csa_weights* w, const wuda_csa_caches* c, const wuda_csa_step* s,
+                                    const wuda_csa_workspace* ws, int m, void* stream) {
+    using namespace wuda;
+    clear_error();
+    WUDA_REQUIRE(w && c && s && ws, "weights, caches, step and workspace must not be NULL");
+    WUDA_REQUIRE(m >= 1 && m <= 128, "m must be in [1, 128] (got %d)", m);
+    WUDA_REQUIRE(w->q_lora >= 128 && w->q_lora % 128 == 0, "q_lora must be a positive multiple of 128");
+    WUDA_REQUIRE(w->index_heads >= 1 && w->main_heads >= 1 && w->out_heads >= w->main_heads,
+                 "index_heads, main_heads >= 1 and out_heads >= main_heads are required");
+    WUDA_REQUIRE(ws->q_fp8 && ws->q_scales && ws->y && ws->iq_fp8 && ws->w_folded && ws->gemm_scratch,
+                 "every workspace buffer is required");
+    const int n_index = w->index_heads * 128, n_main = w->main_heads * 512;
+    const int n_total = n_index + n_main;
+    const char* y = static_cast<const char*>(ws->y);
+
+    int st = wuda_rmsnorm_quant_fp8(s->q_raw, s->q_raw_stride, w->q_norm, 0, w->eps, nullptr, ws->q_fp8, ws->q_scales, m,
+                                    w->q_lora, 1, stream);
+    if (st != WUDA_OK) return st;
+    st = wuda_gemm_fp8_blockscaled(ws->q_fp8, ws->q_scales, w->wq_b, w->wq_b_scales, ws->y, m, n_total, w->q_lora,
+                                   ws->gemm_scratch, ws->gemm_scratch_bytes, ws->status_word, stream);
+    if (st != WUDA_OK) return st;
+    if (s->q_main_out) {
+        st = wuda_query_rms_rope(y + static_cast<int64_t>(n_index) * 2, n_total, s->pos, w->cos_table, w->sin_table,
+                                 w->max_pos, s->q_main_out, m, w->main_heads, w->out_heads, w->eps, stream);
+        if (st != WUDA_OK) return st;
+    }
+    st = wuda_index_q_post_fp8(y, n_total, s->q_pos, w->cos_table, w->sin_table, w->max_pos, s->w64, ws->iq_fp8,
+                               ws->w_folded, m, w->index_heads, stream);
+    if (st != WUDA_OK) return st;
+
+    wuda_cache_writers cw = {};
+    cw.pos = s->pos;
+    cw.cos_table = w->cos_table;
+    cw.sin_table = w->sin_table;
+    cw.max_pos = w->max_pos;
+    cw.eps = w->eps;
+    cw.indexer.state = c->idx_state;
+    cw.indexer.state_row = s->idx_state_row;
+    cw.indexer.norm_w = w->idx_norm;
+    cw.indexer.state_rows_total = c->state_rows_total;
+    cw.indexer.ring_entries = c->ring_entries;
+    cw.indexer.entries_per_block = c->idx_entries_per_block;
+    cw.indexer.num_blocks = c->idx_num_blocks;
+    cw.indexer.block_stride_bytes = c->idx_block_stride_bytes;
+    cw.indexer.pool = c->idx_pool;
+    cw.indexer.dst = s->idx_dst;
+    cw.main = cw.indexer;
+    cw.main.state = c->main_state;
+    cw.main.state_row = s->main_state_row;
+    cw.main.norm_w = w->main_norm;
+    cw.main.entries_per_block = c->cmp_entries_per_block;
+    cw.main.num_blocks = c->cmp_num_blocks;
+    cw.main.block_stride_bytes = c->cmp_block_stride_bytes;
+    cw.main.pool = c->cmp_pool;
+    cw.main.dst = s->cmp_dst;
+    cw.window.y = s->win_y2;
+    cw.window.norm_w = w->win_norm;
+    cw.window.entries_per_block = c->swa_entries_per_block;
+    cw.window.num_blocks = c->swa_num_blocks;
+    cw.window.block_stride_bytes = c->swa_block_stride_bytes;
+    cw.window.pool = c->swa_pool;
+    cw.window.dst = s->swa_dst;
+    st = wuda_cache_writers_fp8(&cw, m, ws->status_word, stream);
+    if (st != WUDA_OK) return st;
+
+    st = wuda_mqa_logits_fp8(ws->iq_fp8, c->idx_pool, ws->w_folded, s->n_compressed, s->idx_block_table, s->logits, m, 1,
+                             c->idx_num_blocks, c->idx_entries_per_block, c->idx_block_stride_bytes,
+                             s->block_table_stride, s->logits_stride, ws->status_word, stream);
+    if (st != WUDA_OK) return st;
+    return wuda_topk(s->logits, s->n_compressed, s->idx_block_table, s->topk_indices, s->topk_raw, m, s->logits_stride,
+                     s->block_table_stride, 1, s->topk, c->idx_entries_per_block, stream);
+}
