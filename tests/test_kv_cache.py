@@ -83,3 +83,18 @@ def test_argument_errors():
     m.alloc_request()
     with pytest.raises(IndexError):
         m.alloc_request()                              # no free slot
+
+
+def test_advance_equals_stepping():
+    a = KVCacheManager(2, 64, 8, device="cpu")
+    b = KVCacheManager(2, 64, 8, device="cpu")
+    sa, sb = a.alloc_request(), b.alloc_request()
+    for _ in range(1000):
+        a.step_begin([sa])
+    b.advance(sb, 1000)
+    for _ in range(9):
+        x, y = a.step_begin([sa]), b.step_begin([sb])
+        for key in ("pos", "main_state_row", "idx_dst", "cmp_dst", "swa_dst"):
+            assert x[key].tolist() == y[key].tolist()
+        for name in ("swa", "cmp", "idx"):
+            assert a.block_table(name, [sa]).tolist() == b.block_table(name, [sb]).tolist()

@@ -6,6 +6,8 @@ because consecutive launches use different weight buffers that together exceed L
     python -m wuda_b200.benchmarks gemm_fp8
     python -m wuda_b200.benchmarks gemm_nvfp4
     python -m wuda_b200.benchmarks norm_rope_quant
+    python -m wuda_b200.benchmarks csa_chain                       (layer launch of the indexer half-step)
+    python -m wuda_b200.benchmarks csa_chain_launches              (three eager steps, for an ncu launch list)
     python -m wuda_b200.benchmarks one gemm_fp8 64 24576 7168      (a few launches of one shape, for ncu)
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks tp2
 """
@@ -189,6 +191,72 @@ def tp2():
     dist.destroy_process_group()
 
 
+def csa_chain(batch=64, context=32768, topk=2048, reps=30, launches_only=0):
+    """The layer launch of the indexer half of a decode step (wuda_csa_decode_step, seven kernels in
+    one CUDA graph) at the model's geometry: q_lora 1536, 64 index heads, 128 main heads, `batch`
+    requests at `context` tokens.  L2 is flushed before every timed replay."""
+    from wuda_b200.decode import CsaDecodeStage, CsaWeights
+    from wuda_b200.kv_cache import KVCacheManager
+    hbm, tf, kind = peaks()
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(7)
+    q_lora, ih, mh = 1536, 64, 128
+    n_total = ih * 128 + mh * 512
+    w8 = torch.randint(0, 0x7E, (n_total, q_lora), generator=g, dtype=torch.uint8, device=dev)
+    ws = torch.rand((n_total // 128, q_lora // 128), generator=g, device=dev) * 1e-3 + 1e-4
+    ang = torch.outer(torch.arange(65536, dtype=torch.float32), 1.0 / (10000.0 ** (torch.arange(32) / 32.0))).to(dev)
+    weights = CsaWeights(w8, ws, torch.rand(q_lora, generator=g, device=dev) + 0.5,
+                         torch.rand(128, generator=g, device=dev) + 0.5, torch.rand(512, generator=g, device=dev) + 0.5,
+                         torch.rand(512, generator=g, device=dev) + 0.5, torch.cos(ang).contiguous(),
+                         torch.sin(ang).contiguous(), index_heads=ih, main_heads=mh)
+    pages_per_req = (context // 4 + 63) // 64 + 1
+    cache = KVCacheManager(batch, batch * pages_per_req + batch, pages_per_req, device=dev)
+    stage = CsaDecodeStage(weights, cache, batch, topk=topk)
+    slots = [cache.alloc_request() for _ in range(batch)]
+    for s in slots:
+        cache.advance(s, context - 1)               # the timed token is the one at position context - 1
+    epb = cache.entries_per_block["idx"]
+    pool = cache.idx_pool
+    pool[:, :epb * 128] = torch.randint(0, 0x7E, (pool.size(0), epb * 128), generator=g, dtype=torch.uint8, device=dev)
+    pool[:, epb * 128:epb * 132] = (torch.rand(pool.size(0), epb, generator=g, device=dev) * 0.09 + 0.01).view(torch.uint8)
+    cache.main_state.normal_(generator=g)
+    cache.idx_state.normal_(generator=g)
+    st = stage.prepare(slots)
+    assert int(st["pos"][0]) == context - 1 and int(st["idx_dst"][0]) >= 0
+    stage.q_raw.normal_(generator=g)
+    stage.w64.normal_(generator=g)
+    stage.win_y2.normal_(generator=g)
+    if launches_only:
+        for _ in range(launches_only):
+            stage.launch(batch)
+        torch.cuda.synchronize()
+        stage.check_status()
+        print("csa_chain: %d eager steps done" % launches_only)
+        return
+    stage.capture(batch)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    total = 0.0
+    for i in range(reps + 3):
+        flush.fill_(i & 0xff)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        stage.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            total += e0.elapsed_time(e1) * 1e3
+    stage.check_status()
+    us = total / reps
+    ncmp = int(stage.n_compressed[0])
+    bytes_step = (n_total * q_lora + batch * ncmp * 132 + 2 * batch * ncmp * 4 + batch * n_total * 2 * 2
+                  + batch * mh * 512 * 2)
+    print("indexer half of a decode step: batch %d, context %d (%d indexer entries / request), top-%d" %
+          (batch, context, ncmp, topk))
+    print("  %.1f us per step (L2 flushed before each) = %.0f tokens/s for this stage chain; %.1f MB algorithmic "
+          "-> %.0f GB/s = %.2f of %s HBM peak" % (us, batch / us * 1e6, bytes_step / 1e6, bytes_step / us / 1e3,
+                                                   bytes_step / us / 1e3 / hbm, kind))
+
+
 def one(kind, m, n, k, launches=5):
     """A few eager launches of one GEMM shape (profiler captures)."""
     t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
@@ -212,4 +280,5 @@ if __name__ == "__main__":
     if which == "one":
         one(sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]))
         sys.exit(0)
-    {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2}[which]()
+    {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2,
+     "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3)}[which]()

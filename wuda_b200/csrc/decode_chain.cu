@@ -6,7 +6,7 @@
 // as they are called from decode_step (dsv4_megakernel/megakernel/test/test_e2e_decode.py:560-640),
 // enqueued on one stream with no host synchronisation and no allocation, so a caller can capture
 // the whole step into a CUDA graph once and replay it.  Everything here is host code: the step is
-// seven launches of this library's kernels in dependency order
+// seven launches of this library's kernels:
 //   1 q RMSNorm + power-of-two 1x128 FP8 quantisation of q_raw
 //   2 block-scaled FP8 GEMM with the merged [indexer heads | main heads] weight
 //   3 query RMSNorm + RoPE of the main heads (reads the GEMM output in place)
@@ -14,7 +14,40 @@
 //   5 cache writers: the indexer entry of this step must be in the pool before 6 scores it
 //   6 paged MQA logits over the indexer pool
 //   7 top-k + page transform
+// Only 1 -> 2 -> 4 -> 6 -> 7 is a chain.  5 needs nothing from 1-4 and 3 feeds nothing in 4-7, so
+// they run on two side streams forked from and joined back into the caller's stream with events
+// (5 joins before 6, 3 at the end).  Under stream capture the forks become parallel branches of the
+// graph.  The side streams and events are created once per device and never destroyed.
 #include "host.h"
+
+namespace wuda {
+namespace chain {
+
+struct Side {
+    bool ready = false;
+    cudaStream_t writers = nullptr, query = nullptr;
+    cudaEvent_t fork = nullptr, forked_gemm = nullptr, writers_done = nullptr, query_done = nullptr;
+};
+
+int side_of_current_device(Side** out) {
+    static Side sides[16];
+    int dev = 0;
+    WUDA_CUDA(cudaGetDevice(&dev));
+    WUDA_REQUIRE(dev >= 0 && dev < 16, "device ordinal %d is outside the 16 this library keeps state for", dev);
+    Side& s = sides[dev];
+    if (!s.ready) {
+        WUDA_CUDA(cudaStreamCreateWithFlags(&s.writers, cudaStreamNonBlocking));
+        WUDA_CUDA(cudaStreamCreateWithFlags(&s.query, cudaStreamNonBlocking));
+        for (cudaEvent_t* e : {&s.fork, &s.forked_gemm, &s.writers_done, &s.query_done})
+            WUDA_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+        s.ready = true;
+    }
+    *out = &s;
+    return WUDA_OK;
+}
+
+}  // namespace chain
+}  // namespace wuda
 
 extern "C" int wuda_csa_decode_step(const wuda_csa_weights* w, const wuda_csa_caches* c, const wuda_csa_step* s,
                                     const wuda_csa_workspace* ws, int m, void* stream) {
@@ -30,22 +63,14 @@ extern "C" int wuda_csa_decode_step(const wuda_csa_weights* w, const wuda_csa_ca
     const int n_index = w->index_heads * 128, n_main = w->main_heads * 512;
     const int n_total = n_index + n_main;
     const char* y = static_cast<const char*>(ws->y);
-
-    int st = wuda_rmsnorm_quant_fp8(s->q_raw, s->q_raw_stride, w->q_norm, 0, w->eps, nullptr, ws->q_fp8, ws->q_scales, m,
-                                    w->q_lora, 1, stream);
-    if (st != WUDA_OK) return st;
-    st = wuda_gemm_fp8_blockscaled(ws->q_fp8, ws->q_scales, w->wq_b, w->wq_b_scales, ws->y, m, n_total, w->q_lora,
-                                   ws->gemm_scratch, ws->gemm_scratch_bytes, ws->status_word, stream);
-    if (st != WUDA_OK) return st;
-    if (s->q_main_out) {
-        st = wuda_query_rms_rope(y + static_cast<int64_t>(n_index) * 2, n_total, s->pos, w->cos_table, w->sin_table,
-                                 w->max_pos, s->q_main_out, m, w->main_heads, w->out_heads, w->eps, stream);
-        if (st != WUDA_OK) return st;
-    }
-    st = wuda_index_q_post_fp8(y, n_total, s->q_pos, w->cos_table, w->sin_table, w->max_pos, s->w64, ws->iq_fp8,
-                               ws->w_folded, m, w->index_heads, stream);
+    cudaStream_t main_stream = static_cast<cudaStream_t>(stream);
+    chain::Side* side = nullptr;
+    int st = chain::side_of_current_device(&side);
     if (st != WUDA_OK) return st;
 
+    // ---- branch A (side stream): the cache writers, independent of the projection
+    WUDA_CUDA(cudaEventRecord(side->fork, main_stream));
+    WUDA_CUDA(cudaStreamWaitEvent(side->writers, side->fork, 0));
     wuda_cache_writers cw = {};
     cw.pos = s->pos;
     cw.cos_table = w->cos_table;
@@ -78,13 +103,38 @@ extern "C" int wuda_csa_decode_step(const wuda_csa_weights* w, const wuda_csa_ca
     cw.window.block_stride_bytes = c->swa_block_stride_bytes;
     cw.window.pool = c->swa_pool;
     cw.window.dst = s->swa_dst;
-    st = wuda_cache_writers_fp8(&cw, m, ws->status_word, stream);
-    if (st != WUDA_OK) return st;
+    int status = wuda_cache_writers_fp8(&cw, m, ws->status_word, side->writers);
+    WUDA_CUDA(cudaEventRecord(side->writers_done, side->writers));
 
-    st = wuda_mqa_logits_fp8(ws->iq_fp8, c->idx_pool, ws->w_folded, s->n_compressed, s->idx_block_table, s->logits, m, 1,
-                             c->idx_num_blocks, c->idx_entries_per_block, c->idx_block_stride_bytes,
-                             s->block_table_stride, s->logits_stride, ws->status_word, stream);
-    if (st != WUDA_OK) return st;
-    return wuda_topk(s->logits, s->n_compressed, s->idx_block_table, s->topk_indices, s->topk_raw, m, s->logits_stride,
-                     s->block_table_stride, 1, s->topk, c->idx_entries_per_block, stream);
+    // ---- the chain on the caller's stream.  Every fork is joined on every path out of this function,
+    // also after a refused launch, so that a stream capture in progress stays well formed.
+    if (status == WUDA_OK)
+        status = wuda_rmsnorm_quant_fp8(s->q_raw, s->q_raw_stride, w->q_norm, 0, w->eps, nullptr, ws->q_fp8, ws->q_scales,
+                                        m, w->q_lora, 1, stream);
+    if (status == WUDA_OK)
+        status = wuda_gemm_fp8_blockscaled(ws->q_fp8, ws->q_scales, w->wq_b, w->wq_b_scales, ws->y, m, n_total, w->q_lora,
+                                           ws->gemm_scratch, ws->gemm_scratch_bytes, ws->status_word, stream);
+    // ---- branch B (side stream): the main heads' query tail, needed only by the attention that follows
+    bool query_forked = false;
+    if (status == WUDA_OK && s->q_main_out) {
+        WUDA_CUDA(cudaEventRecord(side->forked_gemm, main_stream));
+        WUDA_CUDA(cudaStreamWaitEvent(side->query, side->forked_gemm, 0));
+        query_forked = true;
+        status = wuda_query_rms_rope(y + static_cast<int64_t>(n_index) * 2, n_total, s->pos, w->cos_table, w->sin_table,
+                                     w->max_pos, s->q_main_out, m, w->main_heads, w->out_heads, w->eps, side->query);
+        WUDA_CUDA(cudaEventRecord(side->query_done, side->query));
+    }
+    if (status == WUDA_OK)
+        status = wuda_index_q_post_fp8(y, n_total, s->q_pos, w->cos_table, w->sin_table, w->max_pos, s->w64, ws->iq_fp8,
+                                       ws->w_folded, m, w->index_heads, stream);
+    WUDA_CUDA(cudaStreamWaitEvent(main_stream, side->writers_done, 0));     // join A: the pool is written
+    if (status == WUDA_OK)
+        status = wuda_mqa_logits_fp8(ws->iq_fp8, c->idx_pool, ws->w_folded, s->n_compressed, s->idx_block_table, s->logits,
+                                     m, 1, c->idx_num_blocks, c->idx_entries_per_block, c->idx_block_stride_bytes,
+                                     s->block_table_stride, s->logits_stride, ws->status_word, stream);
+    if (status == WUDA_OK)
+        status = wuda_topk(s->logits, s->n_compressed, s->idx_block_table, s->topk_indices, s->topk_raw, m,
+                           s->logits_stride, s->block_table_stride, 1, s->topk, c->idx_entries_per_block, stream);
+    if (query_forked) WUDA_CUDA(cudaStreamWaitEvent(main_stream, side->query_done, 0));   // join B
+    return status;
 }

@@ -100,6 +100,17 @@ class KVCacheManager:
         self.reqs[slot] = {"pos": -1, "cmp": [], "idx": [], "swa": [swa.take() for _ in range(window_pages)]}
         return slot
 
+    def advance(self, slot, tokens):
+        """Bookkeeping of a prefill of `tokens` tokens (not in the reference's manager): moves the
+        request's position forward and takes the pages its compressed entries occupy, without
+        producing per-token destinations.  The caches themselves are filled by whoever prefills."""
+        req = self.reqs[slot]
+        req["pos"] += int(tokens)
+        entries = (req["pos"] + 1) // RATIO
+        if entries:
+            for name in ("idx", "cmp"):
+                self._pools[name].entry(req[name], entries - 1)
+
     def free_request(self, slot):
         req = self.reqs.pop(slot)
         for name in ("swa", "cmp", "idx"):
