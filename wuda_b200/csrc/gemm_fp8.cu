@@ -21,8 +21,11 @@
 //    range adds the partials in CTA order (deterministic) and writes the bf16 tile;
 //  * per unit: one TMA instruction fetches the weight tile (128 x 128 B) and the
 //    activation tile (M_PAD x 128 B), four tcgen05.mma kind::f8f6f4 fill a fresh TMEM
-//    stage, and two epilogue warpgroups (half the columns each) add the stage, times the
-//    unit's scales, to their register accumulators;
+//    stage, and an epilogue warpgroup adds the stage, times the unit's scales, to its register
+//    accumulators.  One unit's epilogue is a chain of waits (scales, TMEM stage, tcgen05.ld), so
+//    the two epilogue warpgroups take units alternately and their chains overlap; the two
+//    accumulator sets are added when a tile's segment ends.  (Above 64 activation rows a thread
+//    cannot hold all columns; the groups then split the columns and both take every unit.);
 //  * roles are replicated (2 producers, 2 issuers) and take units round-robin; stage
 //    counts are multiples of the role counts; every wait is bounded and reports through
 //    the status word.
@@ -60,6 +63,7 @@ struct Params {
     int M, N, K, kb;           // kb = K / 128
     int n_tiles;
     int stages;
+    int a_resident = 0;        // the whole activation matrix stays in shared memory (see Smem)
     // two-rank tensor parallelism (K split across two GPUs): peer exchange of fp32 tiles
     float* tp_my_inbox = nullptr;      // [2 sets][n_tiles][M_PAD][128] fp32 in THIS GPU's memory
     float* tp_peer_inbox = nullptr;    // the same buffer of the peer, mapped into this process
@@ -75,14 +79,36 @@ struct Smem {
     static constexpr int kStageBytes = kWBytes + kABytes;
     static constexpr int kTmemStages = M_PAD <= 128 ? 4 : 2;
     static constexpr int kTmemCols = kTmemStages * M_PAD < 32 ? 32 : kTmemStages * M_PAD;
-    static __host__ __device__ constexpr int scale_off(int stages) { return stages * kStageBytes; }
-    // scale rings: kScaleSlots x (M_PAD activation scales) + kScaleSlots weight scales
-    static __host__ __device__ constexpr int bar_off(int stages) {
-        return scale_off(stages) + kScaleSlots * M_PAD * 4 + kScaleSlots * 4;
+    // Two layouts.  Streaming: every stage holds a weight tile and the matching activation tile.
+    // Resident: when the padded activation matrix (kb tiles of kABytes) fits beside at least six
+    // weight stages it is loaded once per CTA and the stages hold weight tiles only - a CTA then
+    // ingests 16 KB per unit instead of 16 KB + kABytes, which is what bounds decode shapes with
+    // many rows and a short K.
+    static __host__ __device__ constexpr int stage_bytes(bool resident) { return resident ? kWBytes : kStageBytes; }
+    static __host__ __device__ constexpr int scale_off(int stages, int resident_kb = 0) {
+        return stages * stage_bytes(resident_kb > 0) + resident_kb * kABytes;
     }
-    // barriers: full[16] empty[16] full_tm[4] empty_tm[4]
-    static __host__ __device__ constexpr int misc_off(int stages) { return bar_off(stages) + 40 * 8; }
-    static __host__ __device__ constexpr int total(int stages) { return misc_off(stages) + 32 + 1024; }
+    // Up to M_PAD = 64 the two epilogue warpgroups take units alternately (all columns each) and add
+    // their accumulators through a [M_PAD][128] fp32 buffer when a tile's segment ends; above that a
+    // thread cannot hold M_PAD accumulators and the groups split the columns instead.
+    static constexpr bool kAlternate = M_PAD <= 64;
+    static constexpr int kCombineBytes = kAlternate ? M_PAD * kTileN * 4 : 0;
+    // scale rings, one set per epilogue group: kScaleSlots x (M_PAD activation scales) + kScaleSlots
+    // weight scales
+    static constexpr int kRingFloats = kScaleSlots * M_PAD + kScaleSlots;
+    static __host__ __device__ constexpr int comb_off(int stages, int resident_kb = 0) {
+        return scale_off(stages, resident_kb) + 2 * kRingFloats * 4;
+    }
+    static __host__ __device__ constexpr int bar_off(int stages, int resident_kb = 0) {
+        return comb_off(stages, resident_kb) + kCombineBytes;
+    }
+    // barriers: full[16] empty[16] full_tm[4] empty_tm[4] a_full[1]
+    static __host__ __device__ constexpr int misc_off(int stages, int resident_kb = 0) {
+        return bar_off(stages, resident_kb) + 48 * 8;
+    }
+    static __host__ __device__ constexpr int total(int stages, int resident_kb = 0) {
+        return misc_off(stages, resident_kb) + 32 + 1024;
+    }
 };
 
 struct Ring {
@@ -150,12 +176,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - raw_addr);
     const int S = p.stages;
-    const uint32_t bars = base + L::bar_off(S);
+    const bool resident = p.a_resident != 0;
+    const int rkb = resident ? p.kb : 0;
+    const int stage_bytes = L::stage_bytes(resident);
+    const uint32_t a_res = base + S * stage_bytes;      // resident activations: kb tiles of kABytes
+    const uint32_t bars = base + L::bar_off(S, rkb);
     const uint32_t full = bars, empty = bars + 16 * 8, full_tm = bars + 32 * 8, empty_tm = bars + 36 * 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + L::misc_off(S));
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::misc_off(S) + 4);
-    float* a_ring = reinterpret_cast<float*>(base_ptr + L::scale_off(S));
-    float* w_ring = a_ring + kScaleSlots * M_PAD;
+    const uint32_t a_full = bars + 40 * 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + L::misc_off(S, rkb));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::misc_off(S, rkb) + 4);
+    float* rings = reinterpret_cast<float*>(base_ptr + L::scale_off(S, rkb));
+    float* comb = reinterpret_cast<float*>(base_ptr + L::comb_off(S, rkb));
+    constexpr bool kAlt = L::kAlternate;
 
     const int warp = threadIdx.x >> 5;
     const uint32_t lane = lane_id();
@@ -168,8 +200,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         }
         for (int i = 0; i < kTS; ++i) {
             mbar_init(full_tm + i * 8, 1);
-            mbar_init(empty_tm + i * 8, kEpiWarps);
+            mbar_init(empty_tm + i * 8, kAlt ? kEpiWarps / 2 : kEpiWarps);   // the warps that read a stage
         }
+        mbar_init(a_full, kProducers);
         fence_mbar_init();
     }
     if (warp == kProducers) {   // first issuer warp owns the TMEM allocation
@@ -199,16 +232,32 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         ring.step(me, S);
         int tile = static_cast<int>((u0 + me) / p.kb), kb = static_cast<int>((u0 + me) % p.kb);
         bool alive = true;
+        if (resident && count > 0) {
+            // this producer's share of the activation tiles (K blocks me, me + kProducers, ..), one lane
+            // per tile in a single instruction
+            const int mine = me < p.kb ? (p.kb - me + kProducers - 1) / kProducers : 0;
+            if (lane == 0) {
+                if (mine > 0) mbar_arrive_expect_tx(a_full, static_cast<uint32_t>(mine) * L::kABytes);
+                else mbar_arrive(a_full);
+            }
+            __syncwarp();
+            for (int j0 = 0; j0 < mine; j0 += 32) {
+                const int j = j0 + static_cast<int>(lane);
+                const int kbj = me + j * kProducers;
+                if (j < mine) tma_load_2d_hint(a_res + kbj * L::kABytes, &a_map, a_full, kbj * kBlockK, 0, keep_policy);
+            }
+        }
+        const uint32_t lanes_loading = resident ? 1u : 2u;
         for (int n = me; n < count && alive; n += kProducers) {
             const int s = ring.idx;
             alive = mbar_wait_lane0(empty + s * 8, ring.phase ^ 1u, abort_flag, p.status, kDevTimeoutGemmEmpty);
             if (!alive) break;
-            if (lane == 0) mbar_arrive_expect_tx(full + s * 8, L::kStageBytes);
+            if (lane == 0) mbar_arrive_expect_tx(full + s * 8, stage_bytes);
             __syncwarp();
             // one instruction, two lanes: lane 0 fetches the weight tile, lane 1 the activations
-            const uint32_t dst = base + s * L::kStageBytes + (lane == 1 ? kWBytes : 0);
+            const uint32_t dst = base + s * stage_bytes + (lane == 1 ? kWBytes : 0);
             const void* map = lane == 1 ? static_cast<const void*>(&a_map) : static_cast<const void*>(&w_map);
-            if (lane < 2)
+            if (lane < lanes_loading)
                 tma_load_2d_hint(dst, map, full + s * 8, kb * kBlockK, lane == 1 ? 0 : tile * kTileN,
                                  lane == 1 ? keep_policy : stream_policy);
             ring.step(kProducers, S);
@@ -226,13 +275,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
             Ring ring, tring;
             ring.step(me, S);
             tring.step(me, kTS);
-            for (int n = me; n < count; n += kIssuers) {
+            int kbi = static_cast<int>((u0 + me) % p.kb);   // K block of this issuer's next unit
+            bool a_ready = !resident || count <= me ||
+                           mbar_wait(a_full, 0u, abort_flag, p.status, kDevTimeoutGemmFull);
+            for (int n = me; n < count && a_ready; n += kIssuers) {
                 const int s = ring.idx, ts = tring.idx;
                 if (!mbar_wait(full + s * 8, ring.phase, abort_flag, p.status, kDevTimeoutGemmFull)) break;
                 if (!mbar_wait(empty_tm + ts * 8, tring.phase ^ 1u, abort_flag, p.status, kDevTimeoutGemmTmemEmpty)) break;
                 tc_fence_after();
-                const uint32_t w_addr = base + s * L::kStageBytes;
-                const uint32_t a_addr = w_addr + kWBytes;
+                const uint32_t w_addr = base + s * stage_bytes;
+                const uint32_t a_addr = resident ? a_res + kbi * L::kABytes : w_addr + kWBytes;
+                kbi += kIssuers;
+                while (kbi >= p.kb) kbi -= p.kb;
                 const uint32_t d_addr = tmem_base + ts * M_PAD;
 #pragma unroll
                 for (int k = 0; k < kBlockK / 32; ++k)
@@ -248,64 +302,88 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         // ------------------------------------------------------------ epilogue warps
         // Thread = one weight row (TMEM lane) x half of the activation columns.
         const int ew = warp - kFirstEpiWarp;            // 0..7
-        const int half = ew >> 2;                       // which half of the columns
+        const int grp = ew >> 2;                        // epilogue warpgroup
+        const int half = grp;                           // the half of the columns this group finishes
         const int et = (ew * 32 + lane);                // 0..255 among epilogue threads
+        const int gt = et & 127;                        // 0..127 inside the group
         const int row_in_tile = (warp & 3) * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        __align__(8) float acc[kHalf];
+        // kAlt: this group takes the units with (n & 1) == grp and accumulates every column;
+        // otherwise both groups take every unit and half of the columns each.
+        constexpr int kCols = kAlt ? M_PAD : kHalf;
+        const int col0 = kAlt ? 0 : half * kHalf;
+        constexpr int kStep = kAlt ? 2 : 1;
+        const int first = kAlt ? grp : 0;               // this group's first unit
+        __align__(8) float acc[kCols];
 #pragma unroll
-        for (int i = 0; i < kHalf; ++i) acc[i] = 0.f;
+        for (int i = 0; i < kCols; ++i) acc[i] = 0.f;
         Ring tring;
+        tring.step(first, kTS);
         bool alive = true;
         int tile = static_cast<int>(u0 / p.kb), kb = static_cast<int>(u0 % p.kb);
         int seg_kb0 = kb;                               // first K block of the running segment
 
-        // Scales of unit n (activation scales a_s[:, kb], weight scale w_s[tile, kb]) are
-        // fetched kScaleAhead units early with 4-byte asynchronous copies into rings of
-        // kScaleSlots slots, so their L2 latency never sits between two units.
-        int ftile = tile, fkb = kb;                     // the unit the next fetch is for
-        auto fetch_scales = [&](int n_fetch) {
-            if (n_fetch < count) {
-                const int slot = n_fetch & (kScaleSlots - 1);
-                if (et < p.M)
-                    cp_async4(smem_u32(a_ring + slot * M_PAD + et), p.a_scales + static_cast<int64_t>(et) * p.kb + fkb);
-                if (et == 255)
+        // Scales of a unit (activation scales a_s[:, kb], weight scale w_s[tile, kb]) are fetched
+        // kScaleAhead of the group's units early with 4-byte asynchronous copies into the group's rings
+        // of kScaleSlots slots, so their L2 latency never sits between two units.
+        float* a_ring = rings + (kAlt ? grp * L::kRingFloats : 0);   // one ring per group, or one shared
+        float* w_ring = a_ring + kScaleSlots * M_PAD;
+        const int fetcher = kAlt ? gt : et;             // thread index among those that share the rings
+        const int fetchers = kAlt ? 128 : 256;
+        int ftile = static_cast<int>((u0 + first) / p.kb), fkb = static_cast<int>((u0 + first) % p.kb);
+        auto fetch_scales = [&](int j) {                // j-th unit of this group
+            if (first + j * kStep < count) {
+                const int slot = j & (kScaleSlots - 1);
+                for (int r = fetcher; r < p.M; r += fetchers)
+                    cp_async4(smem_u32(a_ring + slot * M_PAD + r), p.a_scales + static_cast<int64_t>(r) * p.kb + fkb);
+                if (fetcher == fetchers - 1)
                     cp_async4(smem_u32(w_ring + slot), p.w_scales + static_cast<int64_t>(ftile) * p.kb + fkb);
-                if (++fkb == p.kb) {
-                    fkb = 0;
+                fkb += kStep;
+                while (fkb >= p.kb) {
+                    fkb -= p.kb;
                     ++ftile;
                 }
             }
             cp_async_commit();                           // one group per unit, empty or not
         };
-        for (int n = 0; n < kScaleAhead; ++n) fetch_scales(n);
+        for (int j = 0; j < kScaleAhead; ++j) fetch_scales(j);
+        auto ring_sync = [&]() {                         // the threads that share this group's rings
+            if constexpr (kAlt) {
+                if (grp == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
+                else asm volatile("bar.sync 3, 128;" ::: "memory");
+            } else {
+                epi_bar_sync();
+            }
+        };
 
         // An aborting CTA keeps walking the loop (every wait then fails at once) so that all
         // 256 epilogue threads reach every named barrier; it only skips the arithmetic.
+        int j = 0;                                       // units this group has taken
         for (int n = 0; n < count; ++n) {
-            fetch_scales(n + kScaleAhead);
-            cp_async_wait<kScaleAhead>();                // this thread's copies for unit n have landed
-            epi_bar_sync();                              // ... and so have everybody else's
+            if (!kAlt || (n & 1) == grp) {
+            fetch_scales(j + kScaleAhead);
+            cp_async_wait<kScaleAhead>();                // this thread's copies for the unit have landed
+            ring_sync();                                 // ... and so have everybody else's
             const int ts = tring.idx;
             if (alive)
                 alive = mbar_wait_warp_fast(full_tm + ts * 8, tring.phase, abort_flag, p.status, kDevTimeoutGemmTmemFull);
             if (alive) {
                 tc_fence_after();
-                const int slot = n & (kScaleSlots - 1);
+                const int slot = j & (kScaleSlots - 1);
                 const float wsc = w_ring[slot];
-                const float* sc = a_ring + slot * M_PAD + half * kHalf;
-                const uint32_t taddr = tmem_base + lane_base + ts * M_PAD + half * kHalf;
+                const float* sc = a_ring + slot * M_PAD + col0;
+                const uint32_t taddr = tmem_base + lane_base + ts * M_PAD + col0;
                 // acc[c] += v[c] * (a_s[c] * w_s): scales come as 16-byte shared-memory loads, the
                 // products and sums as packed fp32x2 operations (one instruction per two columns)
                 float2* acc2 = reinterpret_cast<float2*>(acc);
                 const float2 w2 = make_float2(wsc, wsc);
-                if constexpr (kHalf >= 32) {
+                if constexpr (kCols >= 32) {
                     uint32_t v[2][32];
                     tmem_ld_32x32(taddr, v[0]);
 #pragma unroll
-                    for (int c = 0; c < kHalf; c += 32) {
+                    for (int c = 0; c < kCols; c += 32) {
                         tmem_ld_wait();
-                        if (c + 32 < kHalf) tmem_ld_32x32(taddr + c + 32, v[((c >> 5) + 1) & 1]);
+                        if (c + 32 < kCols) tmem_ld_32x32(taddr + c + 32, v[((c >> 5) + 1) & 1]);
                         const uint32_t* x = v[(c >> 5) & 1];
                         const float4* s4 = reinterpret_cast<const float4*>(sc + c);
 #pragma unroll
@@ -320,7 +398,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
                                 acc2[((c + i) >> 1) + 1]);
                         }
                     }
-                } else if constexpr (kHalf == 16) {
+                } else if constexpr (kCols == 16) {
                     uint32_t v[16];
                     tmem_ld_32x16(taddr, v);
                     tmem_ld_wait();
@@ -337,11 +415,35 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_tm + ts * 8);
             }
-            tring.step(1, kTS);
+            tring.step(kStep, kTS);
+            ++j;
+            }
 
             // ---- end of a segment: the tile's K range ended, or this CTA's range did
             const bool seg_end = (kb + 1 == p.kb) || (n + 1 == count);
             if (seg_end) {
+                if constexpr (kAlt) {
+                    // Each group hands the other the columns that one finishes and adds what it gets
+                    // to its own half; the sums land in acc[0, kHalf).  x + y == y + x, so the result
+                    // does not depend on which group held which units.
+                    // (constant register indices in both branches: the accumulators stay in registers)
+                    if (half == 0) {
+#pragma unroll
+                        for (int i = 0; i < kHalf; ++i) comb[(kHalf + i) * kTileN + row_in_tile] = acc[kHalf + i];
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < kHalf; ++i) comb[i * kTileN + row_in_tile] = acc[i];
+                    }
+                    epi_bar_sync();
+                    if (half == 0) {
+#pragma unroll
+                        for (int i = 0; i < kHalf; ++i) acc[i] = acc[i] + comb[i * kTileN + row_in_tile];
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < kHalf; ++i) acc[i] = acc[kHalf + i] + comb[(kHalf + i) * kTileN + row_in_tile];
+                    }
+                    epi_bar_sync();                      // the buffer is free for the next segment
+                }
                 const int nrow = tile * kTileN + row_in_tile;
                 const bool from_zero = (seg_kb0 == 0), to_end = (kb + 1 == p.kb);
                 if (!from_zero) {
@@ -434,7 +536,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
                     }
                 }
 #pragma unroll
-                for (int i = 0; i < kHalf; ++i) acc[i] = 0.f;
+                for (int i = 0; i < kCols; ++i) acc[i] = 0.f;
                 seg_kb0 = 0;
             }
             if (++kb == p.kb) {
@@ -458,17 +560,25 @@ template <int M_PAD>
 static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p, const DeviceInfo& dev,
                   cudaStream_t stream) {
     using L = Smem<M_PAD>;
-    int stages = 16;
-    while (stages > 2 && L::total(stages) > dev.smem_optin) stages -= 2;
-    if (L::total(stages) > dev.smem_optin)
+    // resident activations if they leave room for six or more weight stages (96 KB in flight)
+    int stages = 16, rkb = p.kb;
+    while (stages > 6 && L::total(stages, rkb) > dev.smem_optin) stages -= 2;
+    if (L::total(stages, rkb) > dev.smem_optin) {
+        rkb = 0;
+        stages = 16;
+        while (stages > 2 && L::total(stages) > dev.smem_optin) stages -= 2;
+    }
+    const int smem = L::total(stages, rkb);
+    if (smem > dev.smem_optin)
         return fail(WUDA_ERR_UNSUPPORTED, "device offers %d bytes of shared memory per block; the kernel needs more",
                     dev.smem_optin);
     p.stages = stages;
+    p.a_resident = rkb > 0;
     auto kernel = gemm_fp8_kernel<M_PAD>;
-    WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total(stages)));
+    WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.smem_optin));
     const long long units = static_cast<long long>(p.n_tiles) * p.kb;
     const int grid = units < dev.num_sms ? static_cast<int>(units) : dev.num_sms;
-    kernel<<<grid, kThreads, L::total(stages), stream>>>(w_map, a_map, p);
+    kernel<<<grid, kThreads, smem, stream>>>(w_map, a_map, p);
     WUDA_CUDA(cudaGetLastError());
     return WUDA_OK;
 }
