@@ -358,6 +358,35 @@ int wuda_csa_decode_step(const wuda_csa_weights* weights, const wuda_csa_caches*
                          const wuda_csa_workspace* workspace, int m, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * mHC pre, the head of a half-layer: from the 4 residual streams of each token
+ *   r = 1/sqrt(mean(x^2) + rms_eps) over the 4*hidden values;  mix = (x . weight^T) * r   [24]
+ *   pre  = sigmoid(mix[0:4] * scale[0] + base[0:4]) + hc_eps
+ *   post = 2 * sigmoid(mix[4:8] * scale[1] + base[4:8])
+ *   comb = 20 Sinkhorn iterations on softmax_rows(mix[8:24] * scale[2] + base[8:24]) + hc_eps
+ *   collapsed = bf16(sum_h pre[h] * x[h, :])
+ *   normed    = bf16((collapsed * 1/sqrt(mean collapsed^2 + norm_eps)) * gamma)
+ *   x_fp8, x_scales = power-of-two 1x128 quantisation of normed (amax / 448 clamped at 1e-4)
+ *
+ * Replaces the reference's pair tf32_hc_prenorm_gemm (third party) + hc_reduce_fuse_out
+ * (kernels/hc_fused_kernel_tc.cu:420-540) with its Sinkhorn tail (include/front_mixed_gemm.cuh:
+ * 438-489); numerics as the torch twin test/test_hc_fused_tc.py:115-136 and origin/model.py:673-681,
+ * with fp32 products where the reference's GEMM rounds its operands to TF32.
+ *
+ *   hidden_states bf16 [m, 4, hidden];  weight fp32 [24, 4*hidden];  base fp32 [24];  scale fp32 [3]
+ *   attn_norm_gamma bf16 [hidden], required with normed / x_fp8
+ *   pre, post fp32 [m, 4];  comb fp32 [m, 4, 4] ([row][column]);  each nullable
+ *   collapsed_bf16, normed_bf16 bf16 [m, hidden];  x_fp8 e4m3 [m, hidden] with x_scales fp32
+ *   [m, hidden/128];  each nullable
+ *   workspace: wuda_mhc_pre_workspace_bytes(m, hidden) bytes, contents irrelevant
+ * hidden % 128 == 0, hidden <= 16384.
+ */
+int64_t wuda_mhc_pre_workspace_bytes(int m, int hidden);
+int wuda_mhc_pre(const void* hidden_states, const float* weight, const float* base, const float* scale,
+                 const void* attn_norm_gamma, float hc_eps, float rms_eps, float norm_eps, float* pre, float* post,
+                 float* comb, void* collapsed_bf16, void* normed_bf16, void* x_fp8, float* x_scales,
+                 void* workspace, int64_t workspace_bytes, int m, int hidden, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * mHC post mix, the last op of an attention half-layer:
  *   output[t, j, d] = post[t, j] * attention_out[t, d] + sum_i comb[t, i, j] * residual[t, i, d]
  *

@@ -537,6 +537,97 @@ void oracle_query_rms_rope(const uint16_t* x, int64_t row_stride, const int64_t*
     }
 }
 
+/* ------------------------------------------------------------------ mHC pre
+ *
+ * After dsv4_megakernel/megakernel/test/test_hc_fused_tc.py:115-136 (hc_reference) and
+ * dsv4_megakernel/origin/model.py:673-681: the 24 mixes of a token are dot products of its
+ * 4*hidden values with the fp32 weight, times 1/sqrt(mean x^2 + eps) (accumulated in double here:
+ * the twin leaves the order to the BLAS); gates, 20 Sinkhorn iterations, the collapsed stream in
+ * bf16, and the attention RMSNorm + power-of-two 1x128 FP8 quantisation that the reference fuses
+ * behind it (dsv4_megakernel/megakernel/kernels/hc_fused_kernel_tc.cu:300-340).
+ */
+__attribute__((optimize("fp-contract=off")))
+void oracle_mhc_pre(const uint16_t* x, const float* weight, const float* base, const float* scale,
+                    const uint16_t* gamma, float hc_eps, float rms_eps, float norm_eps, float* pre, float* post,
+                    float* comb, uint16_t* collapsed, uint16_t* normed, uint8_t* x_fp8, float* x_scales, int m,
+                    int hidden) {
+    const int K = 4 * hidden;
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < m; ++t) {
+        const uint16_t* xt = x + (int64_t)t * K;
+        double ss = 0.0, dot[24];
+        for (int j = 0; j < 24; ++j) dot[j] = 0.0;
+        for (int k = 0; k < K; ++k) {
+            const double v = bf16_to_f32(xt[k]);
+            ss += v * v;
+            for (int j = 0; j < 24; ++j) dot[j] += v * (double)weight[(int64_t)j * K + k];
+        }
+        const float r = 1.0f / sqrtf((float)(ss / K) + rms_eps);
+        float mix[24], p4[4];
+        for (int j = 0; j < 24; ++j) mix[j] = (float)dot[j] * r;
+        for (int h = 0; h < 4; ++h) {
+            p4[h] = 1.0f / (1.0f + expf(-(mix[h] * scale[0] + base[h]))) + hc_eps;
+            if (pre) pre[t * 4 + h] = p4[h];
+            if (post) post[t * 4 + h] = 2.0f * (1.0f / (1.0f + expf(-(mix[4 + h] * scale[1] + base[4 + h]))));
+        }
+        float c[4][4];
+        for (int i = 0; i < 4; ++i) {
+            float mx = -INFINITY, sum = 0.0f;
+            for (int j = 0; j < 4; ++j) {
+                c[i][j] = mix[8 + i * 4 + j] * scale[2] + base[8 + i * 4 + j];
+                mx = fmaxf(mx, c[i][j]);
+            }
+            for (int j = 0; j < 4; ++j) {
+                c[i][j] = expf(c[i][j] - mx);
+                sum += c[i][j];
+            }
+            for (int j = 0; j < 4; ++j) c[i][j] = c[i][j] / sum + hc_eps;
+        }
+        for (int it = 0; it < 20; ++it) {
+            if (it > 0)
+                for (int i = 0; i < 4; ++i) {
+                    const float sum = ((c[i][0] + c[i][1]) + c[i][2]) + c[i][3];
+                    for (int j = 0; j < 4; ++j) c[i][j] = c[i][j] / (sum + hc_eps);
+                }
+            for (int j = 0; j < 4; ++j) {
+                const float sum = ((c[0][j] + c[1][j]) + c[2][j]) + c[3][j];
+                for (int i = 0; i < 4; ++i) c[i][j] = c[i][j] / (sum + hc_eps);
+            }
+        }
+        if (comb) memcpy(comb + t * 16, c, sizeof c);
+        if (!collapsed && !normed && !x_fp8) continue;
+        float* y = (float*)malloc(sizeof(float) * hidden);
+        double ys = 0.0;
+        for (int d = 0; d < hidden; ++d) {
+            float a = p4[0] * bf16_to_f32(xt[d]);
+            for (int h = 1; h < 4; ++h) a = a + p4[h] * bf16_to_f32(xt[(int64_t)h * hidden + d]);
+            const uint16_t b = f32_to_bf16(a);
+            if (collapsed) collapsed[(int64_t)t * hidden + d] = b;
+            y[d] = bf16_to_f32(b);
+            ys += (double)y[d] * y[d];
+        }
+        if (normed || x_fp8) {
+            const float rn = 1.0f / sqrtf((float)(ys / hidden) + norm_eps);
+            for (int d = 0; d < hidden; ++d) {
+                const uint16_t b = f32_to_bf16(y[d] * rn * bf16_to_f32(gamma[d]));
+                if (normed) normed[(int64_t)t * hidden + d] = b;
+                y[d] = bf16_to_f32(b);
+            }
+            if (x_fp8)
+                for (int g = 0; g < hidden / 128; ++g) {
+                    float amax = 0.0f;
+                    for (int i = 0; i < 128; ++i) amax = fmaxf(amax, fabsf(y[g * 128 + i]));
+                    const int e = log2_ceil_f32(fmaxf(amax / 448.0f, 1e-4f));
+                    const float sc = ldexpf(1.0f, e);
+                    x_scales[(int64_t)t * (hidden / 128) + g] = sc;
+                    for (int i = 0; i < 128; ++i)
+                        x_fp8[(int64_t)t * hidden + g * 128 + i] = oracle_f32_to_e4m3(y[g * 128 + i] / sc);
+                }
+        }
+        free(y);
+    }
+}
+
 /* ------------------------------------------------------------------ mHC post mix
  *
  * out[m,j,d] = post[m,j] * x[m,d] + sum_i comb[m,i,j] * res[m,i,d], bf16 in and out, in the

@@ -62,6 +62,8 @@ def _declare(l):
                                        c.c_int]
     l.oracle_index_q_post_fp8.argtypes = [vp, i64, vp, vp, vp, c.c_int, vp, vp, vp, c.c_int, c.c_int]
     l.oracle_query_rms_rope.argtypes = [vp, i64, vp, vp, vp, c.c_int, vp, c.c_int, c.c_int, c.c_int, c.c_float]
+    l.oracle_mhc_pre.argtypes = [vp, vp, vp, vp, vp, c.c_float, c.c_float, c.c_float, vp, vp, vp, vp, vp, vp, vp,
+                                 c.c_int, c.c_int]
     l.oracle_gemm_nvfp4.argtypes = [c.c_void_p, c.c_void_p, c.c_float, c.c_void_p, c.c_void_p, c.c_float, c.c_void_p,
                                     c.c_int, c.c_int, c.c_int, c.c_int]
     l.oracle_gemm_fp8_blockscaled.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
@@ -241,6 +243,25 @@ def query_rms_rope(x_bf16, positions, cos_t, sin_t, out_heads=None, eps=1e-6):
     out = np.empty((tokens, out_heads, 512), np.uint16)
     lib().oracle_query_rms_rope(_p(x), heads * 512, _p(_c(positions, np.int64)), _p(ct), _p(st), ct.shape[0], _p(out),
                                 tokens, heads, out_heads, eps)
+    return out
+
+
+def mhc_pre(hidden_bf16, weight, base, scale, gamma_bf16=None, hc_eps=1e-6, rms_eps=1e-6, norm_eps=1e-6):
+    """hidden uint16 (bf16) [M,4,D], weight fp32 [24,4D].  Returns a dict: pre, post [M,4], comb [M,4,4],
+    collapsed uint16 [M,D] and, with gamma, normed uint16 [M,D], xq uint8 [M,D], xsf fp32 [M,D/128]."""
+    x = _c(hidden_bf16, np.uint16)
+    m, _, d = x.shape
+    w, b, sc = _c(weight, np.float32), _c(base, np.float32), _c(scale, np.float32)
+    out = dict(pre=np.empty((m, 4), np.float32), post=np.empty((m, 4), np.float32),
+               comb=np.empty((m, 4, 4), np.float32), collapsed=np.empty((m, d), np.uint16))
+    g = None
+    if gamma_bf16 is not None:
+        g = _c(gamma_bf16, np.uint16)
+        out.update(normed=np.empty((m, d), np.uint16), xq=np.empty((m, d), np.uint8),
+                   xsf=np.empty((m, d // 128), np.float32))
+    lib().oracle_mhc_pre(_p(x), _p(w), _p(b), _p(sc), _p(g), hc_eps, rms_eps, norm_eps, _p(out["pre"]), _p(out["post"]),
+                         _p(out["comb"]), _p(out["collapsed"]), _p(out.get("normed")), _p(out.get("xq")),
+                         _p(out.get("xsf")), m, d)
     return out
 
 

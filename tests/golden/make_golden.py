@@ -12,6 +12,7 @@ Functions used (paths inside the reference repository):
   dsv4_megakernel/megakernel/test/test_e2e_decode.py      ref_mhc_post (:423-426)
   dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py   ref_comp_step (:550-586, fp8 form) and
                                                            ref_win_step (:646-665)
+  dsv4_megakernel/megakernel/test/test_hc_fused_tc.py     hc_reference (:115-136)
   dsv4_megakernel/megakernel/test/kv_cache_manager.py     KVCacheManager (:53-257), run on the CPU
 The first two are written for device="cuda"; they are run here on the CPU by mapping that one
 keyword to "cpu", which changes no arithmetic.
@@ -217,6 +218,29 @@ def golden_cache_writers(ref_root):
     print("window_kv_fp8.npz", tuple(q8.shape))
 
 
+def mhc_pre_inputs(seed=71, m=3, hidden=7168):
+    """Seeded inputs of the mHC-pre fixture (regenerated by the tests: 2.75 MB of weights are not
+    stored).  numpy's PCG64 stream is stable across versions; the fixture carries a checksum."""
+    rng = np.random.default_rng(seed)
+    x = torch.from_numpy(rng.standard_normal((m, 4, hidden), dtype=np.float32)).bfloat16()
+    weight = rng.standard_normal((24, 4 * hidden), dtype=np.float32) * np.float32(0.01)
+    base = rng.standard_normal(24, dtype=np.float32) * np.float32(0.1)
+    scale = np.array([1.0, 0.7, 1.3], np.float32)
+    return x, weight, base, scale
+
+
+def golden_mhc_pre(ref_root):
+    hc = _load(ref_root, "dsv4_megakernel/megakernel/test/test_hc_fused_tc.py", "ref_hc")
+    hc.torch = torch
+    x, weight, base, scale = mhc_pre_inputs()
+    collapsed, pre, post, comb = hc.hc_reference(x, torch.from_numpy(weight), torch.from_numpy(base),
+                                                 torch.from_numpy(scale))
+    check = float(np.abs(weight).sum() + np.abs(_u16(x).astype(np.float64)).sum() % 1e6)
+    np.savez_compressed(os.path.join(HERE, "mhc_pre_7168.npz"), collapsed=_u16(collapsed), pre=pre.numpy(),
+                        post=post.numpy(), comb=comb.numpy(), input_checksum=check)
+    print("mhc_pre_7168.npz", tuple(collapsed.shape))
+
+
 KV_TRACE_CONFIGS = [
     dict(capacity=5, pages_per_pool=96, max_pages_per_req=12),
     dict(capacity=5, pages_per_pool=96, max_pages_per_req=12, state_ring_entries=16),
@@ -305,6 +329,7 @@ def main():
     golden_mhc_post(ref_root)
     golden_kv_cache(ref_root)
     golden_cache_writers(ref_root)
+    golden_mhc_pre(ref_root)
 
 
 if __name__ == "__main__":

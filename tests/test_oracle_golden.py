@@ -234,3 +234,30 @@ def test_query_rms_rope_oracle_against_the_two_pass_fixtures():
     c, s = np.cos(ang.astype(np.float64))[[0, 7, 31]][:, None], np.sin(ang.astype(np.float64))[[0, 7, 31]][:, None]
     y[..., 448::2], y[..., 449::2] = ev * c - od * s, ev * s + od * c
     assert np.all(np.abs(oracle.bf16_to_f32(out[:, :2]) - y) <= np.abs(y) * 2.0 ** -8 + 1e-6)
+
+
+def test_mhc_pre_oracle_matches_reference_twin():
+    import sys, os
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+    from make_golden import mhc_pre_inputs
+    g = load_golden("mhc_pre_7168.npz")
+    x, weight, base, scale = mhc_pre_inputs()
+    xu = x.view(torch.int16).numpy().view(np.uint16)
+    assert abs(float(np.abs(weight).sum() + np.abs(xu.astype(np.float64)).sum() % 1e6) - float(g["input_checksum"])) < 1e-3
+    o = oracle.mhc_pre(xu, weight, base, scale, np.full(7168, 0x3F80, np.uint16))
+    # the reference's own gates (test_hc_fused_tc.py:172-177) are 2e-3 / 2e-3 / 5e-4; fp32 twins agree far closer
+    for key, tol in (("pre", 2e-6), ("post", 2e-6), ("comb", 2e-6)):
+        assert np.abs(o[key] - g[key]).max() <= tol, key
+    got, ref = oracle.bf16_to_f32(o["collapsed"]), oracle.bf16_to_f32(g["collapsed"])
+    assert np.mean(o["collapsed"] == g["collapsed"]) >= 0.999
+    assert np.all(np.abs(got - ref) <= np.abs(ref) * 2.0 ** -7 + 1e-6)
+    # doubly stochastic after the Sinkhorn iterations
+    assert np.allclose(o["comb"].sum(1), 1, atol=1e-4) and np.allclose(o["comb"].sum(2), 1, atol=1e-4)
+    # unit gamma: normed = collapsed * rsqrt(mean^2), and the quantised copy decodes back to it
+    y = oracle.bf16_to_f32(o["collapsed"]).astype(np.float64)
+    n = y / np.sqrt((y * y).mean(-1, keepdims=True) + 1e-6)
+    assert np.all(np.abs(oracle.bf16_to_f32(o["normed"]) - n) <= np.abs(n) * 2.0 ** -8 + 1e-6)
+    deq = oracle.e4m3_decode(o["xq"]).reshape(3, 56, 128) * o["xsf"][..., None]
+    nb = oracle.bf16_to_f32(o["normed"]).reshape(3, 56, 128)
+    assert np.all(np.abs(deq - nb) <= o["xsf"][..., None] * 16 * 1.01 + np.abs(nb) * 2.0 ** -4)
+    assert np.all(np.log2(o["xsf"]) == np.round(np.log2(o["xsf"])))

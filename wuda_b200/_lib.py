@@ -90,6 +90,9 @@ SIGNATURES = {
     "wuda_query_rms_rope": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_int, c_vp, c_int, c_int, c_int, c_float, c_vp]),
     "wuda_csa_decode_step": (c_int, [ctypes.POINTER(CsaWeights), ctypes.POINTER(CsaCaches), ctypes.POINTER(CsaStep),
                                      ctypes.POINTER(CsaWorkspace), c_int, c_vp]),
+    "wuda_mhc_pre_workspace_bytes": (c_i64, [c_int, c_int]),
+    "wuda_mhc_pre": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_float, c_float, c_vp, c_vp, c_vp, c_vp, c_vp,
+                             c_vp, c_vp, c_vp, c_i64, c_int, c_int, c_vp]),
     "wuda_mhc_post": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
     "wuda_gemm_fp8_scratch_bytes": (c_i64, [c_int, c_int]),
     "wuda_gemm_fp8_blockscaled": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),

@@ -1,0 +1,311 @@
+// mHC pre: the head of an attention (or FFN) half-layer.  From the 4 residual streams of a token,
+//   x      = the 4 x hidden values as one row of K = 4 * hidden,  r = 1/sqrt(mean x^2 + eps)
+//   mix    = (x . W^T) * r                    W fp32 [24, K]:  pre[0,4) | post[4,8) | comb[8,24)
+//   pre    = sigmoid(mix_pre  * scale[0] + base_pre) + hc_eps
+//   post   = 2 * sigmoid(mix_post * scale[1] + base_post)
+//   comb   = Sinkhorn(softmax_rows(mix_comb * scale[2] + base_comb) + hc_eps), 20 iterations
+//   y      = bf16(sum_h pre[h] * x[h, :])                      the collapsed stream
+//   normed = bf16((y * 1/sqrt(mean y^2 + eps)) * gamma)        attention RMSNorm, bf16 gamma
+//   x_fp8, x_scale = 1x128 power-of-two FP8 quantisation of normed (amax/448 clamped at 1e-4)
+// Torch twin: dsv4_megakernel/megakernel/test/test_hc_fused_tc.py:115-136 (hc_reference); origin
+// dsv4_megakernel/origin/model.py:673-681 (hc_pre).  Device counterparts: a TF32 tensor-core GEMM
+// of a third-party library plus kernels/hc_fused_kernel_tc.cu:420-520 (hc_reduce_fuse_out, fused
+// norm + quant at :300-340) and the Sinkhorn tail include/front_mixed_gemm.cuh:438-489.
+//
+// Two kernels.  (1) The 24 dot products are 1.4 MFLOP per token against 2.75 MB of weights: CUDA
+// cores in fp32 (exact products, unlike TF32), K cut into 56 slices of 512 so that 56 x ceil(M/8)
+// CTAs share the work; a thread keeps its 24 x 4 weights in registers across the CTA's 8 tokens.
+// Partials go to a workspace [slice][token][25] (24 dots + the sum of squares).  (2) One CTA per
+// token adds the slices in order (deterministic), runs the gates and the Sinkhorn in one warp, and
+// streams the 4 residual rows once for collapse + norm + quantisation.
+#include <cuda_bf16.h>
+
+#include "host.h"
+
+namespace wuda {
+namespace mhcpre {
+
+constexpr int kStreams = 4;
+constexpr int kMix = 24;                 // pre 4 | post 4 | comb 16
+constexpr int kPart = kMix + 1;          // + sum of squares
+constexpr int kSlice = 512;              // K elements per slice
+constexpr int kMixThreads = 128;         // 4 elements per thread
+constexpr int kTokensPerCta = 8;
+constexpr int kFinishThreads = 256;
+constexpr int kSinkhornIters = 20;
+
+struct Params {
+    const __nv_bfloat16* x;        // [m, 4, hidden]
+    const float* weight;           // [24, 4 * hidden]
+    const float* base;             // [24]
+    const float* scale;            // [3]
+    const __nv_bfloat16* gamma;    // [hidden] or nullptr
+    float* ws;                     // [slices, m, 25]
+    float* pre;                    // [m, 4] or nullptr
+    float* post;                   // [m, 4]
+    float* comb;                   // [m, 4, 4]
+    __nv_bfloat16* collapsed;      // [m, hidden] or nullptr
+    __nv_bfloat16* normed;         // [m, hidden] or nullptr
+    uint8_t* x_fp8;                // [m, hidden] or nullptr
+    float* x_scales;               // [m, hidden / 128]
+    int m, hidden, slices;
+    float hc_eps, rms_eps, norm_eps;
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__global__ void __launch_bounds__(kMixThreads) mhc_pre_mix_kernel(Params p) {
+    __shared__ float warp_part[kMixThreads / 32][kPart];
+    const int slice = blockIdx.x;
+    const int k0 = slice * kSlice + threadIdx.x * 4;
+    const int K = kStreams * p.hidden;
+    const bool in = k0 < K;                         // the last slice may be ragged (K % 512 != 0)
+    float4 w[kMix];
+#pragma unroll
+    for (int j = 0; j < kMix; ++j)
+        w[j] = in ? __ldg(reinterpret_cast<const float4*>(p.weight + static_cast<int64_t>(j) * K + k0))
+                  : make_float4(0.f, 0.f, 0.f, 0.f);
+    const int t0 = blockIdx.y * kTokensPerCta;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int t = t0; t < min(t0 + kTokensPerCta, p.m); ++t) {
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        if (in) {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.x + static_cast<int64_t>(t) * K + k0));
+            x[0] = __uint_as_float(raw.x << 16);
+            x[1] = __uint_as_float(raw.x & 0xffff0000u);
+            x[2] = __uint_as_float(raw.y << 16);
+            x[3] = __uint_as_float(raw.y & 0xffff0000u);
+        }
+        float part[kPart];
+#pragma unroll
+        for (int j = 0; j < kMix; ++j)
+            part[j] = fmaf(x[3], w[j].w, fmaf(x[2], w[j].z, fmaf(x[1], w[j].y, x[0] * w[j].x)));
+        part[kMix] = fmaf(x[3], x[3], fmaf(x[2], x[2], fmaf(x[1], x[1], x[0] * x[0])));
+#pragma unroll
+        for (int j = 0; j < kPart; ++j) part[j] = warp_sum(part[j]);
+        __syncthreads();                            // the previous token's partials have been read
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < kPart; ++j) warp_part[warp][j] = part[j];
+        }
+        __syncthreads();
+        if (threadIdx.x < kPart) {
+            const int j = threadIdx.x;
+            p.ws[(static_cast<int64_t>(slice) * p.m + t) * kPart + j] =
+                ((warp_part[0][j] + warp_part[1][j]) + warp_part[2][j]) + warp_part[3][j];
+        }
+    }
+}
+
+__device__ __forceinline__ float sigmoid(float x) { return __fdiv_rn(1.0f, 1.0f + expf(-x)); }
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+__global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p) {
+    __shared__ float mix[kPart];
+    __shared__ float pre_s[kStreams];
+    __shared__ float warp_ss[kFinishThreads / 32];
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    if (threadIdx.x < kPart) {
+        float s = 0.f;
+        for (int sl = 0; sl < p.slices; ++sl) s += p.ws[(static_cast<int64_t>(sl) * p.m + t) * kPart + threadIdx.x];
+        mix[threadIdx.x] = s;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(mix[kMix], static_cast<float>(kStreams * p.hidden)) + p.rms_eps));
+        if (lane < kStreams) {
+            const float v = sigmoid(mix[lane] * r * p.scale[0] + p.base[lane]) + p.hc_eps;
+            pre_s[lane] = v;
+            if (p.pre) p.pre[t * kStreams + lane] = v;
+            if (p.post)
+                p.post[t * kStreams + lane] = 2.0f * sigmoid(mix[kStreams + lane] * r * p.scale[1] + p.base[kStreams + lane]);
+        }
+        // Sinkhorn on the 4 x 4 comb in lanes 0..15 (row = lane / 4, column = lane % 4): row sums by
+        // xor 1, 2; column sums by xor 4, 8.  Lanes 16..31 compute on zeros and are ignored.
+        const bool live = lane < kStreams * kStreams;
+        float v = live ? mix[2 * kStreams + lane] * r * p.scale[2] + p.base[2 * kStreams + lane] : 0.f;
+        float mx = v;
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float e = expf(v - mx);
+        float rs = e;
+        rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+        rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+        v = __fdiv_rn(e, rs) + p.hc_eps;
+        float cs = v;
+        cs += __shfl_xor_sync(0xffffffffu, cs, 4);
+        cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+        v = __fdiv_rn(v, cs + p.hc_eps);
+        for (int it = 0; it < kSinkhornIters - 1; ++it) {
+            rs = v;
+            rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+            rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+            v = __fdiv_rn(v, rs + p.hc_eps);
+            cs = v;
+            cs += __shfl_xor_sync(0xffffffffu, cs, 4);
+            cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+            v = __fdiv_rn(v, cs + p.hc_eps);
+        }
+        if (live && p.comb) p.comb[t * kStreams * kStreams + lane] = v;
+    }
+    __syncthreads();
+    if (!p.collapsed && !p.normed && !p.x_fp8) return;
+
+    // collapse: a thread owns the 8-value vectors tid, tid + 256, ..; a 128-block of the row is 16
+    // consecutive vectors, i.e. 16 consecutive threads
+    constexpr int kMaxVec = 8;                       // hidden <= 8 * 256 * 8 = 16384
+    const int vectors = p.hidden / 8;
+    const float pr[kStreams] = {pre_s[0], pre_s[1], pre_s[2], pre_s[3]};
+    float y[kMaxVec][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMaxVec; ++k) {
+        const int vi = threadIdx.x + k * kFinishThreads;
+        if (vi < vectors) {
+            float acc[8];
+#pragma unroll
+            for (int h = 0; h < kStreams; ++h) {
+                const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p.x + (static_cast<int64_t>(t) * kStreams + h) * p.hidden) + vi);
+                const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float lo = __fmul_rn(pr[h], __uint_as_float(wv[i] << 16));
+                    const float hi = __fmul_rn(pr[h], __uint_as_float(wv[i] & 0xffff0000u));
+                    acc[2 * i] = h == 0 ? lo : __fadd_rn(acc[2 * i], lo);
+                    acc[2 * i + 1] = h == 0 ? hi : __fadd_rn(acc[2 * i + 1], hi);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                y[k][i] = __bfloat162float(__float2bfloat16_rn(acc[i]));
+                ss = fmaf(y[k][i], y[k][i], ss);
+            }
+            if (p.collapsed) {
+                uint4 o;
+                uint32_t* ow = &o.x;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    __nv_bfloat162 b = __floats2bfloat162_rn(y[k][2 * i], y[k][2 * i + 1]);
+                    ow[i] = *reinterpret_cast<uint32_t*>(&b);
+                }
+                *(reinterpret_cast<uint4*>(p.collapsed + static_cast<int64_t>(t) * p.hidden) + vi) = o;
+            }
+        }
+    }
+    if (!p.normed && !p.x_fp8) return;
+    ss = warp_sum(ss);
+    if (lane == 0) warp_ss[warp] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < kFinishThreads / 32; ++i) total += warp_ss[i];
+    const float rn = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(total, static_cast<float>(p.hidden)) + p.norm_eps));
+#pragma unroll
+    for (int k = 0; k < kMaxVec; ++k) {
+        const int vi = threadIdx.x + k * kFinishThreads;
+        const bool on = vi < vectors;              // uniform over every group of 16 threads (vectors % 16 == 0)
+        float v[8];
+        float amax = 0.f;
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (on) {
+            const uint4 graw = __ldg(reinterpret_cast<const uint4*>(p.gamma) + vi);
+            const uint32_t gw[4] = {graw.x, graw.y, graw.z, graw.w};
+            uint32_t* ow = &o.x;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float a = __fmul_rn(__fmul_rn(y[k][2 * i], rn), __uint_as_float(gw[i] << 16));
+                const float b = __fmul_rn(__fmul_rn(y[k][2 * i + 1], rn), __uint_as_float(gw[i] & 0xffff0000u));
+                __nv_bfloat162 bb = __floats2bfloat162_rn(a, b);
+                ow[i] = *reinterpret_cast<uint32_t*>(&bb);
+                v[2 * i] = __uint_as_float(ow[i] << 16);
+                v[2 * i + 1] = __uint_as_float(ow[i] & 0xffff0000u);
+                amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+            }
+            if (p.normed) *(reinterpret_cast<uint4*>(p.normed + static_cast<int64_t>(t) * p.hidden) + vi) = o;
+        }
+        if (p.x_fp8) {
+#pragma unroll
+            for (int s = 8; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+            if (on) {
+                const uint32_t bits = __float_as_uint(fmaxf(__fdiv_rn(amax, 448.f), 1e-4f));
+                const int e = static_cast<int>((bits >> 23) & 0xff) - 127 + ((bits & 0x7fffffu) ? 1 : 0);
+                const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+                const uint2 q = make_uint2(pack_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                                           pack_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
+                *(reinterpret_cast<uint2*>(p.x_fp8 + static_cast<int64_t>(t) * p.hidden) + vi) = q;
+                if ((threadIdx.x & 15) == 0)
+                    p.x_scales[static_cast<int64_t>(t) * (p.hidden / 128) + vi / 16] =
+                        __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
+            }
+        }
+    }
+}
+
+}  // namespace mhcpre
+}  // namespace wuda
+
+extern "C" int64_t wuda_mhc_pre_workspace_bytes(int m, int hidden) {
+    if (m < 1 || hidden < 8) return -1;
+    const int64_t slices = (4LL * hidden + wuda::mhcpre::kSlice - 1) / wuda::mhcpre::kSlice;
+    return slices * m * wuda::mhcpre::kPart * 4;
+}
+
+extern "C" int wuda_mhc_pre(const void* hidden_states, const float* weight, const float* base, const float* scale,
+                            const void* attn_norm_gamma, float hc_eps, float rms_eps, float norm_eps, float* pre,
+                            float* post, float* comb, void* collapsed_bf16, void* normed_bf16, void* x_fp8,
+                            float* x_scales, void* workspace, int64_t workspace_bytes, int m, int hidden,
+                            void* stream) {
+    using namespace wuda;
+    using namespace wuda::mhcpre;
+    clear_error();
+    WUDA_REQUIRE(m >= 1, "m must be >= 1 (got %d)", m);
+    WUDA_REQUIRE(hidden >= 128 && hidden % 128 == 0 && hidden <= 16384,
+                 "hidden must be a multiple of 128 in [128, 16384] (got %d)", hidden);
+    WUDA_REQUIRE(hidden_states && weight && base && scale && workspace, "hidden, weight, base, scale and workspace are required");
+    WUDA_REQUIRE((!normed_bf16 && !x_fp8) || attn_norm_gamma, "the norm weight is required with normed or x_fp8");
+    WUDA_REQUIRE(!x_fp8 || x_scales, "x_scales is required with x_fp8");
+    WUDA_REQUIRE(aligned16(hidden_states) && aligned16(weight) && aligned16(attn_norm_gamma) && aligned16(collapsed_bf16) &&
+                     aligned16(normed_bf16) && aligned16(x_fp8),
+                 "hidden, weight, gamma and the row outputs must be 16-byte aligned");
+    const int64_t need = wuda_mhc_pre_workspace_bytes(m, hidden);
+    WUDA_REQUIRE(workspace_bytes >= need, "workspace holds %lld bytes; %lld are needed (wuda_mhc_pre_workspace_bytes)",
+                 static_cast<long long>(workspace_bytes), static_cast<long long>(need));
+    Params p;
+    p.x = static_cast<const __nv_bfloat16*>(hidden_states);
+    p.weight = weight;
+    p.base = base;
+    p.scale = scale;
+    p.gamma = static_cast<const __nv_bfloat16*>(attn_norm_gamma);
+    p.ws = static_cast<float*>(workspace);
+    p.pre = pre;
+    p.post = post;
+    p.comb = comb;
+    p.collapsed = static_cast<__nv_bfloat16*>(collapsed_bf16);
+    p.normed = static_cast<__nv_bfloat16*>(normed_bf16);
+    p.x_fp8 = static_cast<uint8_t*>(x_fp8);
+    p.x_scales = x_scales;
+    p.m = m;
+    p.hidden = hidden;
+    p.slices = (kStreams * hidden + kSlice - 1) / kSlice;
+    p.hc_eps = hc_eps;
+    p.rms_eps = rms_eps;
+    p.norm_eps = norm_eps;
+    const dim3 grid_mix(p.slices, (m + kTokensPerCta - 1) / kTokensPerCta);
+    mhc_pre_mix_kernel<<<grid_mix, kMixThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    WUDA_CUDA(cudaGetLastError());
+    mhc_pre_finish_kernel<<<m, kFinishThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    WUDA_CUDA(cudaGetLastError());
+    return WUDA_OK;
+}

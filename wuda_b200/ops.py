@@ -15,7 +15,7 @@ from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
-           "rmsnorm_rope_out", "mhc_post_out", "idx_postprocess_fp8", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
+           "rmsnorm_rope_out", "mhc_post_out", "mhc_pre", "idx_postprocess_fp8", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -234,6 +234,40 @@ def rope_quant(x, positions, cos_table, sin_table, rope_dim, *, inverse=False, q
                                   sc.data_ptr() if sc is not None else None, tokens, heads, head_dim, rope_dim,
                                   cos_table.size(0), int(inverse), 0 if scale_fmt is None else 1, _stream()))
     return y16, y8, sc
+
+
+def mhc_pre(hidden, weight, base, scale, attn_norm_w=None, hc_eps=1e-6, rms_eps=1e-6, attn_norm_eps=1e-6,
+            quant=True, workspace=None):
+    """mHC pre of a half-layer (the reference's tf32_hc_prenorm_gemm + hc_reduce_fuse_out pair,
+    test/test_hc_fused_tc.py:85-112): hidden bf16 [M, 4, D], weight fp32 [24, 4*D], base fp32 [24],
+    scale fp32 [3], attn_norm_w bf16 [D] or None.  Returns a dict with pre, post [M,4], comb [M,4,4],
+    collapsed bf16 [M,D] and, with attn_norm_w, normed bf16 [M,D] (+ xq e4m3 [M,D], xsf fp32 [M,D/128]
+    when quant)."""
+    _require(hidden.is_cuda and hidden.is_contiguous() and hidden.dtype == torch.bfloat16 and hidden.dim() == 3
+             and hidden.size(1) == 4, "hidden must be contiguous CUDA bf16 [M, 4, D]")
+    m, _, d = hidden.shape
+    _require(_f32(weight, "weight").shape == (24, 4 * d), "weight must be fp32 [24, 4*D]")
+    _require(_f32(base, "base").numel() == 24 and _f32(scale, "scale").numel() == 3, "base [24] and scale [3] are fp32")
+    dev = hidden.device
+    out = dict(pre=torch.empty(m, 4, device=dev), post=torch.empty(m, 4, device=dev), comb=torch.empty(m, 4, 4, device=dev),
+               collapsed=torch.empty(m, d, dtype=torch.bfloat16, device=dev))
+    if attn_norm_w is not None:
+        _require(attn_norm_w.is_cuda and attn_norm_w.is_contiguous() and attn_norm_w.dtype == torch.bfloat16
+                 and attn_norm_w.numel() == d, "attn_norm_w must be contiguous CUDA bf16 [D]")
+        out["normed"] = torch.empty(m, d, dtype=torch.bfloat16, device=dev)
+        if quant:
+            out["xq"] = torch.empty(m, d, dtype=torch.float8_e4m3fn, device=dev)
+            out["xsf"] = torch.empty(m, d // 128, device=dev)
+    need = lib.wuda_mhc_pre_workspace_bytes(m, d)
+    _require(need > 0, "unsupported M or D")
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+    check(lib.wuda_mhc_pre(hidden.data_ptr(), weight.data_ptr(), base.data_ptr(), scale.data_ptr(), _ptr(attn_norm_w),
+                           hc_eps, rms_eps, attn_norm_eps, out["pre"].data_ptr(), out["post"].data_ptr(),
+                           out["comb"].data_ptr(), out["collapsed"].data_ptr(), _ptr(out.get("normed")),
+                           _ptr(out.get("xq")), _ptr(out.get("xsf")), workspace.data_ptr(), workspace.numel(), m, d,
+                           _stream()))
+    return out
 
 
 def mhc_post_out(attention_out, residual, post, comb, output):
