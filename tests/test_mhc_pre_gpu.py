@@ -21,10 +21,12 @@ def u16(t):
     return t.cpu().view(torch.int16).numpy().view(np.uint16)
 
 
-def bf16_near(got, ref, frac=0.999):
+def bf16_near(got, ref, frac=0.999, steps=1):
     g, r = oracle.bf16_to_f32(got), oracle.bf16_to_f32(ref)
     assert np.mean(got == ref) >= frac, np.mean(got == ref)
-    assert np.all(np.abs(g - r) <= np.abs(r) * 2.0 ** -7 + 1e-5)
+    # `steps` bf16 steps, or the fp32 noise of a sum whose terms cancel (terms are O(1))
+    bad = np.abs(g - r) > np.abs(r) * steps * 2.0 ** -7 + 2e-4
+    assert not bad.any(), (g[bad][:4], r[bad][:4])
 
 
 def test_golden(wuda):
@@ -53,7 +55,8 @@ def test_against_oracle(wuda, m, hidden):
     for key in ("pre", "post", "comb"):
         assert np.abs(out[key].cpu().numpy() - ref[key]).max() <= 5e-6, key
     bf16_near(u16(out["collapsed"]), ref["collapsed"])
-    bf16_near(u16(out["normed"]), ref["normed"], 0.995)
+    # a one-step difference of the collapsed value moves the normalised one by up to two steps
+    bf16_near(u16(out["normed"]), ref["normed"], 0.995, steps=2)
     xq, xsf = out["xq"].view(torch.uint8).cpu().numpy(), out["xsf"].cpu().numpy()
     assert np.mean(xsf == ref["xsf"]) >= 0.99 and np.mean(xq == ref["xq"]) >= 0.99
     # self-consistency, exact: the FP8 copy is the power-of-two quantisation of the GPU's own normed row
