@@ -430,6 +430,45 @@ int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* 
                               int32_t* status_word, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * BF16 GEMM for decode-sized M:  c[m, n] = sum_k a[m, k] * w[n, k], fp32 accumulation, written
+ * as bf16 or (c_is_fp32 != 0) as fp32.
+ *
+ * Carries the projections the reference keeps in BF16: the BF16 segment of the front mixed GEMM
+ * (kernels/front_mixed_gemm_csa_swapab.cu:10-258), whose outputs feed fp32 state, and the
+ * origin's `linear` on bf16 weights (origin/model.py:108-120).
+ *
+ *   a_bf16 bf16 [m, k];  w_bf16 bf16 [n, k];  c bf16 or fp32 [m, n];  1 <= m <= 128, k % 64 == 0
+ *   scratch: wuda_gemm_bf16_scratch_bytes(m, n) bytes, 256-byte aligned, zero before the first
+ *   call (left zero again), not shared by calls that overlap on the GPU.
+ */
+int64_t wuda_gemm_bf16_scratch_bytes(int m, int n);
+int wuda_gemm_bf16(const void* a_bf16, const void* w_bf16, void* c, int c_is_fp32, int m, int n, int k,
+                   void* scratch, int64_t scratch_bytes, int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * FRONT-EMIT: scatters the front projection's outputs of a decode step.  The front GEMM yields
+ * per token [q 1536 | win 512] (FP8 segment, bf16 out) and [main 2048 | idx 512 | w64 64] (BF16
+ * segment, fp32 out of wuda_gemm_bf16):
+ *   win_y2[t]  = fp32 of y8[t, 1536:2048]
+ *   main_state[main_state_row[t]] = y16[t, 0:2048],    + ape[pos % 4] on its second half
+ *   idx_state[idx_state_row[t]]   = y16[t, 2048:2560], + idx_ape[pos % 4] on its second half
+ *   w64[t]     = fp32(bf16(y16[t, 2560:2624]))
+ *
+ * Replaces the side-channel epilogue of front_mixed_gemm_csa_swapab (FrontEmitArgs,
+ * include/front_mixed_gemm.cuh:390-425; its test stand-in publish_fresh,
+ * test/test_wq_b_fp8_gemm.py:539-547).  Rows < 0 are skipped, rows >= state_rows_total are
+ * skipped and reported in status_word.  Each output group is optional (NULL).
+ *
+ *   y8_bf16 bf16 [m, 2048];  y16_f32 fp32 [m, 2624];  pos int64 [m]
+ *   main_state fp32 [state_rows_total, 2048], ape fp32 [4, 1024];  idx_state fp32
+ *   [state_rows_total, 512], idx_ape fp32 [4, 256];  win_y2 fp32 [m, 512];  w64 fp32 [m, 64]
+ */
+int wuda_front_emit(const void* y8_bf16, const float* y16_f32, const int64_t* pos, float* main_state,
+                    const float* ape, const int64_t* main_state_row, float* idx_state, const float* idx_ape,
+                    const int64_t* idx_state_row, float* win_y2, float* w64, int64_t state_rows_total, int m,
+                    int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * NVFP4 block-scaled GEMM for decode-sized M:
  *
  *   c[m, n] = bf16( a_global_scale * w_global_scale *

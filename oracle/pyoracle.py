@@ -265,6 +265,33 @@ def mhc_pre(hidden_bf16, weight, base, scale, gamma_bf16=None, hc_eps=1e-6, rms_
     return out
 
 
+def gemm_bf16(a_bf16, w_bf16):
+    """a uint16 (bf16) [M,K], w uint16 [N,K] -> float64 [M,N] (products of bf16 values are exact in
+    fp32; the sum is taken in double so that any fp32 summation order can be held against it)."""
+    a = bf16_to_f32(_c(a_bf16, np.uint16)).astype(np.float64)
+    w = bf16_to_f32(_c(w_bf16, np.uint16)).astype(np.float64)
+    return a @ w.T
+
+
+def front_emit(y8_bf16, y16, pos, main_state, ape, main_row, idx_state, idx_ape, idx_row):
+    """FRONT-EMIT scatter after dsv4_megakernel/megakernel/include/front_mixed_gemm.cuh:390-425 and
+    test/test_wq_b_fp8_gemm.py:539-547.  States are modified in place; returns (win_y2, w64)."""
+    y16 = _c(y16, np.float32)
+    pos = np.asarray(pos, np.int64)
+    win = bf16_to_f32(_c(y8_bf16, np.uint16)[:, 1536:2048]).copy()
+    w64 = bf16_to_f32(f32_to_bf16(y16[:, 2560:2624]))
+    ms, isr = main_state.reshape(-1, 2048), idx_state.reshape(-1, 512)
+    for t in range(len(pos)):
+        ph = int(pos[t]) % 4
+        if main_row[t] >= 0:
+            ms[main_row[t], :1024] = y16[t, :1024]
+            ms[main_row[t], 1024:] = y16[t, 1024:2048] + ape[ph]
+        if idx_row[t] >= 0:
+            isr[idx_row[t], :256] = y16[t, 2048:2304]
+            isr[idx_row[t], 256:] = y16[t, 2304:2560] + idx_ape[ph]
+    return win, w64
+
+
 def gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=True):
     """a e4m3 bytes [M,K], a_s fp32 [M,K/128], b e4m3 bytes [N,K], b_s fp32 [N/128,K/128].
     Returns uint16 (bf16) or fp32 [M,N]."""

@@ -93,6 +93,10 @@ SIGNATURES = {
     "wuda_mhc_pre_workspace_bytes": (c_i64, [c_int, c_int]),
     "wuda_mhc_pre": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_float, c_float, c_vp, c_vp, c_vp, c_vp, c_vp,
                              c_vp, c_vp, c_vp, c_i64, c_int, c_int, c_vp]),
+    "wuda_gemm_bf16_scratch_bytes": (c_i64, [c_int, c_int]),
+    "wuda_gemm_bf16": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
+    "wuda_front_emit": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_int, c_vp,
+                                c_vp]),
     "wuda_mhc_post": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
     "wuda_gemm_fp8_scratch_bytes": (c_i64, [c_int, c_int]),
     "wuda_gemm_fp8_blockscaled": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),

@@ -15,7 +15,7 @@ from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
-           "rmsnorm_rope_out", "mhc_post_out", "mhc_pre", "idx_postprocess_fp8", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
+           "rmsnorm_rope_out", "mhc_post_out", "mhc_pre", "bf16_gemm", "front_mixed_gemm", "idx_postprocess_fp8", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -463,6 +463,70 @@ def fp8_gemm(a, a_s, b, b_s, scale_dtype=torch.float32, *, out=None, status_word
                                         m, n, k, scratch.data_ptr(), scratch.numel(),
                                         status_word.data_ptr() if status_word is not None else None, _stream()))
     return out
+
+
+def bf16_gemm(a, w, *, out=None, out_dtype=torch.bfloat16, status_word=None):
+    """C[M,N] = A[M,K] @ W[N,K]^T on bf16 operands with fp32 accumulation; bf16 or fp32 output
+    (the origin's `linear` on bf16 weights, origin/model.py:108-120)."""
+    _require(a.is_cuda and a.is_contiguous() and a.dtype == torch.bfloat16, "a must be contiguous CUDA bf16")
+    _require(w.is_cuda and w.is_contiguous() and w.dtype == torch.bfloat16 and w.dim() == 2,
+             "w must be contiguous CUDA bf16 [N, K]")
+    k = a.size(-1)
+    m, n = a.numel() // k, w.size(0)
+    _require(w.size(1) == k, "a and w disagree on K")
+    if out is None:
+        out = torch.empty(*a.shape[:-1], n, dtype=out_dtype, device=a.device)
+    _require(out.is_contiguous() and out.dtype in (torch.bfloat16, torch.float32) and out.numel() == m * n,
+             "out must be contiguous bf16 or fp32 [M, N]")
+    need = lib.wuda_gemm_bf16_scratch_bytes(m, n)
+    _require(need >= 0, "m must be in [1, 128]")
+    scratch = _scratch_for(a.device, need)
+    check(lib.wuda_gemm_bf16(a.data_ptr(), w.data_ptr(), out.data_ptr(), int(out.dtype == torch.float32), m, n, k,
+                             scratch.data_ptr(), scratch.numel(), _ptr(status_word), _stream()))
+    return out
+
+
+def front_mixed_gemm(x, x_fp8, x_sf, w_bf16, w_fp8, w_sf, out, *, pos=None, main_state=None, ape=None,
+                     main_state_row=None, idx_state=None, idx_state_row=None, idx_ape=None, win_y2=None, w64=None,
+                     y16=None, status_word=None):
+    """The front projection of a decode step with its side-channel outputs, after the reference's
+    front_mixed_gemm_csa_swapab (kernels/front_mixed_gemm_csa_swapab.cu:262-279):
+    y[M, 4672] = x . [W8 (2048 rows, FP8 1x128 / 128x128 scales) | W16 (2624 rows, BF16)]^T.
+    `out` bf16 [M, 2048] receives the FP8 segment (q_raw | win); the BF16 segment is produced in fp32
+    (`y16` [M, 2624], allocated if not given) and scattered into the state rings, win_y2 and w64 when
+    those are passed (all-or-none with pos).  Three launches: two GEMMs and the scatter."""
+    m = x.size(0)
+    _require(tuple(w_fp8.shape) == (2048, x.size(1)) and tuple(w_bf16.shape) == (2624, x.size(1)),
+             "w_fp8 must be [2048, K] and w_bf16 [2624, K]")
+    _require(out.is_cuda and out.is_contiguous() and out.dtype == torch.bfloat16 and tuple(out.shape) == (m, 2048),
+             "out must be contiguous CUDA bf16 [M, 2048]")
+    fp8_gemm(x_fp8, x_sf, w_fp8, w_sf, out=out, status_word=status_word)
+    if y16 is None:
+        y16 = torch.empty(m, 2624, dtype=torch.float32, device=x.device)
+    bf16_gemm(x, w_bf16, out=y16, status_word=status_word)
+    if pos is not None:
+        _require(pos.is_cuda and pos.is_contiguous() and pos.dtype == torch.int64 and pos.numel() == m,
+                 "pos must be contiguous CUDA int64 [M]")
+        rows_total = 0
+        for state, width, row, table, tw in ((main_state, 2048, main_state_row, ape, 1024),
+                                             (idx_state, 512, idx_state_row, idx_ape, 256)):
+            if state is None:
+                continue
+            _f32(state, "state", width)
+            _require(row is not None and row.is_cuda and row.is_contiguous() and row.dtype == torch.int64
+                     and row.numel() == m, "state rows must be contiguous CUDA int64 [M]")
+            _require(_f32(table, "ape").shape == (4, tw), "ape must be fp32 [4, %d]" % tw)
+            total = state.numel() // width
+            _require(rows_total in (0, total), "the two state rings must have the same number of rows")
+            rows_total = total
+        if win_y2 is not None:
+            _require(_f32(win_y2, "win_y2", 512).numel() == m * 512, "win_y2 must be fp32 [M, 512]")
+        if w64 is not None:
+            _require(_f32(w64, "w64", 64).numel() == m * 64, "w64 must be fp32 [M, 64]")
+        check(lib.wuda_front_emit(out.data_ptr(), y16.data_ptr(), pos.data_ptr(), _ptr(main_state), _ptr(ape),
+                                  _ptr(main_state_row), _ptr(idx_state), _ptr(idx_ape), _ptr(idx_state_row),
+                                  _ptr(win_y2), _ptr(w64), max(rows_total, 1), m, _ptr(status_word), _stream()))
+    return out, y16
 
 
 def exchange_handles(my_handle, group=None):
