@@ -430,6 +430,22 @@ int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* 
                               int32_t* status_word, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Grouped block-scaled FP8 GEMM: `groups` independent projections in one launch,
+ *   c[m, g * n_per_group + j] = sum_k a[m, g * k + kk] * w[g * n_per_group + j, kk]   (scaled as above)
+ * i.e. group g multiplies its own k columns of the activation row by its own n_per_group weight
+ * rows - the low-rank output projection wo_a of the reference ([groups, 1024, 4096] applied to the
+ * attention output viewed as [M, groups, 4096]; test/o_proj_csa.py:319-494, origin/model.py:520-540).
+ *
+ *   a e4m3 [m, groups * k];  a_scales fp32 [m, groups * k / 128]
+ *   w e4m3 [groups * n_per_group, k];  w_scales fp32 [groups * n_per_group / 128, k / 128]
+ *   c_bf16 bf16 [m, groups * n_per_group];  n_per_group % 128 == 0;  scratch as for
+ *   wuda_gemm_fp8_blockscaled with n = groups * n_per_group.
+ */
+int wuda_gemm_fp8_grouped(const void* a, const float* a_scales, const void* w, const float* w_scales, void* c_bf16,
+                          int m, int n_per_group, int k, int groups, void* scratch, int64_t scratch_bytes,
+                          int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * BF16 GEMM for decode-sized M:  c[m, n] = sum_k a[m, k] * w[n, k], fp32 accumulation, written
  * as bf16 or (c_is_fp32 != 0) as fp32.
  *

@@ -64,6 +64,10 @@ struct Params {
     int n_tiles;
     int stages;
     int a_resident = 0;        // the whole activation matrix stays in shared memory (see Smem)
+    // grouped form: weight tile t belongs to group t / group_tiles and reads the activations'
+    // columns [group * K, (group + 1) * K); a_kb_total = K blocks in an activation row (0: kb)
+    int group_tiles = 0;
+    int a_kb_total = 0;
     // two-rank tensor parallelism (K split across two GPUs): peer exchange of fp32 tiles
     float* tp_my_inbox = nullptr;      // [2 sets][n_tiles][M_PAD][128] fp32 in THIS GPU's memory
     float* tp_peer_inbox = nullptr;    // the same buffer of the peer, mapped into this process
@@ -257,8 +261,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
             // one instruction, two lanes: lane 0 fetches the weight tile, lane 1 the activations
             const uint32_t dst = base + s * stage_bytes + (lane == 1 ? kWBytes : 0);
             const void* map = lane == 1 ? static_cast<const void*>(&a_map) : static_cast<const void*>(&w_map);
+            const int a_x = kb * kBlockK + (p.group_tiles ? (tile / p.group_tiles) * p.K : 0);
             if (lane < lanes_loading)
-                tma_load_2d_hint(dst, map, full + s * 8, kb * kBlockK, lane == 1 ? 0 : tile * kTileN,
+                tma_load_2d_hint(dst, map, full + s * 8, lane == 1 ? a_x : kb * kBlockK, lane == 1 ? 0 : tile * kTileN,
                                  lane == 1 ? keep_policy : stream_policy);
             ring.step(kProducers, S);
             kb += kProducers;
@@ -334,8 +339,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         auto fetch_scales = [&](int j) {                // j-th unit of this group
             if (first + j * kStep < count) {
                 const int slot = j & (kScaleSlots - 1);
+                const int a_stride = p.a_kb_total ? p.a_kb_total : p.kb;
+                const int a_col = fkb + (p.group_tiles ? (ftile / p.group_tiles) * p.kb : 0);
                 for (int r = fetcher; r < p.M; r += fetchers)
-                    cp_async4(smem_u32(a_ring + slot * M_PAD + r), p.a_scales + static_cast<int64_t>(r) * p.kb + fkb);
+                    cp_async4(smem_u32(a_ring + slot * M_PAD + r), p.a_scales + static_cast<int64_t>(r) * a_stride + a_col);
                 if (fetcher == fetchers - 1)
                     cp_async4(smem_u32(w_ring + slot), p.w_scales + static_cast<int64_t>(ftile) * p.kb + fkb);
                 fkb += kStep;
@@ -566,7 +573,7 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p,
     // resident activations if they leave room for six or more weight stages (96 KB in flight)
     int stages = 16, rkb = p.kb;
     while (stages > 6 && L::total(stages, rkb) > dev.smem_optin) stages -= 2;
-    if (L::total(stages, rkb) > dev.smem_optin) {
+    if (p.group_tiles || L::total(stages, rkb) > dev.smem_optin) {   // groups read different activation columns
         rkb = 0;
         stages = 16;
         while (stages > 2 && L::total(stages) > dev.smem_optin) stages -= 2;
@@ -600,12 +607,17 @@ extern "C" int64_t wuda_gemm_fp8_scratch_bytes(int m, int n) {
     return static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4 + kMaxGrid * 4;
 }
 
-extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* w, const float* w_scales,
-                                         void* c_bf16, int m, int n, int k, void* scratch, int64_t scratch_bytes,
-                                         int32_t* status_word, void* stream) {
+// groups == 1: the plain GEMM.  groups > 1: `n` rows per group, group g multiplies the activations'
+// columns [g * k, (g + 1) * k) by the weight rows [g * n, (g + 1) * n).
+static int gemm_fp8_entry(const void* a, const float* a_scales, const void* w, const float* w_scales, void* c_bf16,
+                          int m, int n, int k, int groups, void* scratch, int64_t scratch_bytes,
+                          int32_t* status_word, void* stream) {
     using namespace wuda;
     using namespace wuda::gemm8;
     clear_error();
+    WUDA_REQUIRE(groups >= 1, "groups must be >= 1 (got %d)", groups);
+    WUDA_REQUIRE(groups == 1 || n % 128 == 0, "with groups the rows per group must be a multiple of 128 (got %d)", n);
+    const int n_all = n * groups;
     WUDA_REQUIRE(m >= 0 && m <= 256, "m must be in [0, 256] (got %d)", m);
     WUDA_REQUIRE(n >= 1, "n must be >= 1 (got %d)", n);
     WUDA_REQUIRE(k >= 128 && k % 128 == 0, "k must be a positive multiple of 128 (got %d)", k);
@@ -614,19 +626,19 @@ extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, c
                  "a, a_scales, w, w_scales, c and scratch must not be NULL");
     WUDA_REQUIRE(aligned16(a) && aligned16(w), "a and w must be 16-byte aligned");
     WUDA_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "scratch must be 256-byte aligned");
-    const int64_t need = wuda_gemm_fp8_scratch_bytes(m, n);
+    const int64_t need = wuda_gemm_fp8_scratch_bytes(m, n_all);
     WUDA_REQUIRE(scratch_bytes >= need, "scratch holds %lld bytes; %lld are needed (wuda_gemm_fp8_scratch_bytes)",
                  static_cast<long long>(scratch_bytes), static_cast<long long>(need));
     if (m > 128) {
         // Above 128 rows a warpgroup's 128 accumulator columns no longer fit the register file;
         // two passes of <= 128 rows (the weights stream twice) are faster than one that spills.
-        int st2 = wuda_gemm_fp8_blockscaled(a, a_scales, w, w_scales, c_bf16, 128, n, k, scratch, scratch_bytes,
-                                            status_word, stream);
+        int st2 = gemm_fp8_entry(a, a_scales, w, w_scales, c_bf16, 128, n, k, groups, scratch, scratch_bytes, status_word,
+                                 stream);
         if (st2 != WUDA_OK) return st2;
-        return wuda_gemm_fp8_blockscaled(static_cast<const uint8_t*>(a) + static_cast<int64_t>(128) * k,
-                                         a_scales + static_cast<int64_t>(128) * (k / 128), w, w_scales,
-                                         static_cast<__nv_bfloat16*>(c_bf16) + static_cast<int64_t>(128) * n, m - 128,
-                                         n, k, scratch, scratch_bytes, status_word, stream);
+        return gemm_fp8_entry(static_cast<const uint8_t*>(a) + static_cast<int64_t>(128) * k * groups,
+                              a_scales + static_cast<int64_t>(128) * (k / 128) * groups, w, w_scales,
+                              static_cast<__nv_bfloat16*>(c_bf16) + static_cast<int64_t>(128) * n_all, m - 128, n, k,
+                              groups, scratch, scratch_bytes, status_word, stream);
     }
 
     DeviceInfo dev;
@@ -641,10 +653,12 @@ extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, c
     p.c = static_cast<__nv_bfloat16*>(c_bf16);
     p.status = status_word;
     p.M = m;
-    p.N = n;
+    p.N = n_all;
     p.K = k;
     p.kb = k / 128;
-    p.n_tiles = (n + 127) / 128;
+    p.n_tiles = (n_all + 127) / 128;
+    p.group_tiles = groups > 1 ? n / 128 : 0;
+    p.a_kb_total = groups * (k / 128);
     p.scratch = static_cast<float*>(scratch);
     p.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
     WUDA_REQUIRE(dev.num_sms <= kMaxGrid, "device has %d SMs; at most %d are supported", dev.num_sms, kMaxGrid);
@@ -652,7 +666,7 @@ extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, c
 
     CUtensorMap w_map, a_map;
     {
-        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n_all)};
         const uint64_t strides[1] = {static_cast<uint64_t>(k)};
         const uint32_t box[2] = {128u, 128u};
         st = encode_tensor_map(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box,
@@ -660,8 +674,8 @@ extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, c
         if (st != WUDA_OK) return st;
     }
     {
-        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+        const uint64_t dims[2] = {static_cast<uint64_t>(k) * groups, static_cast<uint64_t>(m)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(k) * groups};
         const uint32_t box[2] = {128u, static_cast<uint32_t>(m_pad)};
         st = encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box,
                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
@@ -675,6 +689,19 @@ extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, c
         case 128: return launch<128>(w_map, a_map, p, dev, s);
         default: return launch<256>(w_map, a_map, p, dev, s);
     }
+}
+
+extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* w, const float* w_scales,
+                                         void* c_bf16, int m, int n, int k, void* scratch, int64_t scratch_bytes,
+                                         int32_t* status_word, void* stream) {
+    return gemm_fp8_entry(a, a_scales, w, w_scales, c_bf16, m, n, k, 1, scratch, scratch_bytes, status_word, stream);
+}
+
+extern "C" int wuda_gemm_fp8_grouped(const void* a, const float* a_scales, const void* w, const float* w_scales,
+                                     void* c_bf16, int m, int n_per_group, int k, int groups, void* scratch,
+                                     int64_t scratch_bytes, int32_t* status_word, void* stream) {
+    return gemm_fp8_entry(a, a_scales, w, w_scales, c_bf16, m, n_per_group, k, groups, scratch, scratch_bytes,
+                          status_word, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
