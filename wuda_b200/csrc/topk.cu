@@ -200,6 +200,65 @@ __device__ __forceinline__ void emit(const Params& p, Shared& s, int r, int idx,
     }
 }
 
+// Exclusive prefix sum of `count` over the CTA's threads (thread order) and the CTA total.
+// Two barriers; uses warp_tot / warp_excl.
+__device__ __forceinline__ uint32_t block_exclusive_scan(Shared& s, uint32_t count, uint32_t* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t v = count;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+    }
+    if (lane == 31) s.warp_tot[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        const uint32_t tot = s.warp_tot[lane];
+        uint32_t w = tot;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += t;
+        }
+        s.warp_excl[lane] = w - tot;
+        if (lane == 31) s.sel_above = w;             // the total (sel_above is free between selections)
+    }
+    __syncthreads();
+    *total = s.sel_above;
+    return v - count + s.warp_excl[warp];
+}
+
+// Writes the selected candidates (sel(key) true) to the row's output, after the `s.out_count` already
+// written, without atomics: every thread counts its candidates c = tid, tid + 1024, .. (at most 8),
+// one block scan hands out the positions.  All threads must call it; ends with a barrier.
+template <typename Sel>
+__device__ __forceinline__ void emit_candidates(const Params& p, Shared& s, int r, int ncand, Sel sel) {
+    uint32_t mask = 0;
+#pragma unroll
+    for (int j = 0; j < kCandCap / kThreads; ++j) {
+        const int c = threadIdx.x + j * kThreads;
+        if (c < ncand && sel(s.cand_key[c])) mask |= 1u << j;
+    }
+    uint32_t total;
+    const uint32_t base = s.out_count;               // stable: the caller's last barrier is behind us
+    uint32_t pos = base + block_exclusive_scan(s, __popc(mask), &total);
+#pragma unroll
+    for (int j = 0; j < kCandCap / kThreads; ++j) {
+        if ((mask >> j) & 1u) {
+            if (pos < static_cast<uint32_t>(p.k)) {
+                const int idx = s.cand_idx[threadIdx.x + j * kThreads];
+                const int64_t o = static_cast<int64_t>(r) * p.k + pos;
+                if (p.raw) p.raw[o] = idx;
+                p.page_indices[o] = page_of(p, r, idx);
+            }
+            ++pos;
+        }
+    }
+    __syncthreads();                                 // everybody has read out_count and sel_above
+    if (threadIdx.x == 0) s.out_count = base + total;
+    __syncthreads();
+}
+
 // One pass over the row that sorts every element into "emit now", "park as candidate"
 // or "drop" (cls(key) = 2 / 1 / 0).  A thread classifies a whole batch of its elements
 // into two bit masks first; slots in the output and in the candidate list are then
@@ -304,6 +363,17 @@ __device__ __forceinline__ void classify_pass(const float* row, int lo, int hi, 
     }
 }
 
+#ifdef WUDA_TOPK_TIMING
+// Development aid, compiled only on request: cycle stamps of the phases of CTA 0's first row.
+__device__ long long g_phase_clock[16];
+#define WUDA_STAMP(i)                                                    \
+    do {                                                                 \
+        if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[i] = clock64(); \
+    } while (0)
+#else
+#define WUDA_STAMP(i) ((void)0)
+#endif
+
 __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     Shared& s = *reinterpret_cast<Shared*>(smem_raw);
@@ -324,7 +394,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
         if (static_cast<int64_t>(n) > p.score_stride) n = static_cast<int>(p.score_stride);
         const int k = p.k;
 
-        const bool sampled = n >= 4 * k && k <= kCandCap / 2;
+        // A row that fits the candidate list whole needs neither sampling nor classification.
+        const bool small = n <= kCandCap;
+        const bool sampled = !small && n >= 4 * k && k <= kCandCap / 2;
         if (crank != 0 && !sampled) continue;   // short rows are the leader's alone
         if (n <= k) {  // everything is selected: [0..n) then -1
             for (int i = threadIdx.x; i < k; i += kThreads) {
@@ -337,6 +409,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
         }
 
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
+        WUDA_STAMP(0);
         zero_hist(s, kBins);
         if (threadIdx.x == 0) {
             s.out_count = 0;
@@ -348,6 +421,91 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
         bool have_all = false;      // candidate list holds EVERY element at or above some digit
         int ncand = 0;
         uint32_t key_lo = 0;        // lower bound of the sampled scan's candidate keys
+        uint32_t thr = 0, need3 = 0;   // threshold key; how many values equal to it are still taken
+        bool take_all_equal = true;
+        bool done = false;
+        if (small) {
+            // ---------------------------------------------------------- short rows: keys stay in registers
+            // Thread t holds elements 4 (t + 1024 j) + c, j < 2, c < 4.  Three histogram levels
+            // (12 + 12 + 8 key bits) find the threshold, one scan hands out the output positions.
+            uint32_t key[8];
+            uint32_t valid = 0;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int e0 = 4 * (threadIdx.x + j * kThreads);
+                if (vec_ok && e0 + 3 < n) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(row + e0));
+                    key[4 * j] = key_of(v.x), key[4 * j + 1] = key_of(v.y), key[4 * j + 2] = key_of(v.z), key[4 * j + 3] = key_of(v.w);
+                    valid |= 0xFu << (4 * j);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const bool in = e0 + c < n;
+                        key[4 * j + c] = in ? key_of(row[e0 + c]) : 0u;
+                        valid |= static_cast<uint32_t>(in) << (4 * j + c);
+                    }
+                }
+            }
+            WUDA_STAMP(1);
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if ((valid >> e) & 1u) atomicAdd(&s.hist[key[e] >> 20], 1u);
+            __syncthreads();
+            WUDA_STAMP(2);
+            find_threshold(s, kBins, static_cast<uint32_t>(k));
+            const uint32_t d1 = s.sel_digit;
+            const uint32_t need1 = static_cast<uint32_t>(k) - s.sel_above;
+            __syncthreads();
+            WUDA_STAMP(3);
+            zero_hist(s, kBins);
+            __syncthreads();
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (((valid >> e) & 1u) && (key[e] >> 20) == d1) atomicAdd(&s.hist[(key[e] >> 8) & 0xFFFu], 1u);
+            __syncthreads();
+            WUDA_STAMP(4);
+            find_threshold(s, kBins, need1);
+            const uint32_t d2 = s.sel_digit;
+            const uint32_t need2 = need1 - s.sel_above;
+            __syncthreads();
+            WUDA_STAMP(5);
+            zero_hist(s, 256);
+            __syncthreads();
+            const uint32_t prefix24 = (d1 << 12) | d2;
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (((valid >> e) & 1u) && (key[e] >> 8) == prefix24) atomicAdd(&s.hist[key[e] & 0xFFu], 1u);
+            __syncthreads();
+            WUDA_STAMP(6);
+            find_threshold(s, 256, need2);
+            const uint32_t d3 = s.sel_digit;
+            need3 = need2 - s.sel_above;
+            thr = (prefix24 << 8) | d3;
+            take_all_equal = (s.hist[d3] == need3);
+            __syncthreads();
+            WUDA_STAMP(7);
+            uint32_t mask = 0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (((valid >> e) & 1u) && (key[e] > thr || (key[e] == thr && take_all_equal))) mask |= 1u << e;
+            uint32_t total;
+            uint32_t pos = block_exclusive_scan(s, __popc(mask), &total);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                if ((mask >> e) & 1u) {
+                    const int idx = 4 * (threadIdx.x + (e >> 2) * kThreads) + (e & 3);
+                    const int64_t o = static_cast<int64_t>(r) * k + pos;
+                    if (p.raw) p.raw[o] = idx;
+                    p.page_indices[o] = page_of(p, r, idx);
+                    ++pos;
+                }
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) s.out_count = total;
+            __syncthreads();
+            WUDA_STAMP(8);
+            done = true;
+        }
         if (sampled) {
             cluster.sync();   // the leader's counters are zeroed before anyone parks into them
             for (int t = threadIdx.x; t < kSamples; t += kThreads) {
@@ -381,11 +539,8 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
             __syncthreads();
         }
 
-        uint32_t thr, need3;        // threshold key; how many values equal to it are still taken
-        bool take_all_equal;
-        bool done = false;
         const int ncand_pad = (ncand + kThreads - 1) / kThreads * kThreads;
-        if (have_all) {
+        if (have_all && !small) {
             // ------------------------------------------------ candidates from the sampled scan
             // Their keys start at key_lo = d_lo << 20.  A 4096-bin histogram of
             // (key - key_lo) >> 12 resolves 20 key bits at once with little contention (the
@@ -414,10 +569,10 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
                 take_all_equal = (s.hist[d_b] == need3);
                 thr = (prefix20 << 12) | d_b;
                 __syncthreads();
-                for (int c = threadIdx.x; c < ncand_pad; c += kThreads) {
-                    const uint32_t key = c < ncand ? s.cand_key[c] : 0u;
-                    const bool ok = c < ncand && (key > thr || (key == thr && take_all_equal));
-                    emit(p, s, r, ok ? s.cand_idx[c] : 0, ok);
+                {
+                    const uint32_t t = thr;
+                    const bool eq = take_all_equal;
+                    emit_candidates(p, s, r, ncand, [&](uint32_t key) { return key > t || (key == t && eq); });
                 }
                 done = true;
             }
@@ -434,10 +589,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
             need1 = static_cast<uint32_t>(k) - s.sel_above;
             parked = true;
             __syncthreads();
-            for (int c = threadIdx.x; c < ncand_pad; c += kThreads) {
-                const bool ok = c < ncand && (s.cand_key[c] >> 20) > d1;
-                emit(p, s, r, ok ? s.cand_idx[c] : 0, ok);
-            }
+            emit_candidates(p, s, r, ncand, [&](uint32_t key) { return (key >> 20) > d1; });
             zero_hist(s, kBins);
             __syncthreads();
         } else {
@@ -552,6 +704,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
             }
         }
         __syncthreads();
+        WUDA_STAMP(10);
     }
 }
 
@@ -597,8 +750,9 @@ extern "C" int wuda_topk(const float* scores, const int32_t* seq_lens, const int
     WUDA_CUDA(cudaFuncSetAttribute(topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     // One 1024-thread CTA fills an SM; when there are fewer rows than SMs the spare SMs
     // join the rows' clusters.
+    // (rows of at most 16 K scores are not worth a cluster barrier: one CTA scans them in a few passes)
     int kCluster = 1;
-    while (kCluster < kMaxCluster && rows * kCluster * 2 <= dev.num_sms) kCluster *= 2;
+    while (score_stride > 16384 && kCluster < kMaxCluster && rows * kCluster * 2 <= dev.num_sms) kCluster *= 2;
     const int clusters = rows * kCluster <= dev.num_sms ? rows : dev.num_sms / kCluster;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(clusters * kCluster), 1, 1);
@@ -615,3 +769,9 @@ extern "C" int wuda_topk(const float* scores, const int32_t* seq_lens, const int
     WUDA_CUDA(cudaLaunchKernelEx(&cfg, topk_kernel, p));
     return WUDA_OK;
 }
+
+#ifdef WUDA_TOPK_TIMING
+extern "C" int wuda_topk_phase_clocks(long long* out16) {
+    return cudaMemcpyFromSymbol(out16, wuda::topk::g_phase_clock, sizeof(long long) * 16) == cudaSuccess ? 0 : 3;
+}
+#endif
