@@ -14,8 +14,8 @@
 //    memory with one tiled TMA copy per page and needs no repacking);
 //  * the request's next_n x 64 query heads are the B operand (N = 64 * next_n), loaded
 //    once per request, so the keys of a request are read from HBM once for all its rows;
-//  * tcgen05.mma kind::f8f6f4 accumulates into TMEM (4 accumulator stages); two math
-//    warpgroups alternate tiles: tcgen05.ld, relu, weighted head sum, token scale,
+//  * tcgen05.mma kind::f8f6f4 accumulates into TMEM (4 accumulator stages); four math
+//    warpgroups, one per stage, take tiles in turn: tcgen05.ld, relu, weighted head sum, token scale,
 //    coalesced fp32 stores;
 //  * every mbarrier wait is bounded and reports through the status word.
 #include <cuda.h>
@@ -49,14 +49,16 @@ constexpr int kMaxKvStages = 12;
 // must be a multiple of both this and the number of UMMA issuers, so that every stage is
 // always produced by the same issuer and consumed by the same group: a parity wait may
 // not run more than one phase ahead of its barrier.
-constexpr int kMathGroups = 2;
+constexpr int kMathGroups = 4;
 constexpr int kMathWarps = 4 * kMathGroups;
 static_assert(kTmemStages % kMathGroups == 0, "TMEM stages must be a multiple of the math group count");
 static_assert(kMaxKvStages % 4 == 0, "key stages come in multiples of the role counts");
 // Warp roles.  A single thread runs a dependent instruction chain at a few cycles per
 // instruction, so the bookkeeping of one tile costs a role several hundred cycles; the
 // roles are therefore replicated and take tiles round-robin: four producer warps, two
-// UMMA issuers, two math warpgroups.
+// UMMA issuers, four math warpgroups (a tile's reduction is a chain of tcgen05.ld latencies of about
+// 2000 cycles against a tile period of about 700 at HBM speed, so it takes three or more groups in
+// flight to keep up; 768 threads leave each 80 registers, which the reduction fits without spills).
 constexpr int kProducers = 4;       // warps 0..3, producer p takes tiles n with n % 4 == p
 constexpr int kIssuers = 2;         // warps 4, 5
 constexpr int kMmaWarp0 = kProducers;
