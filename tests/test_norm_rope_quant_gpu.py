@@ -144,7 +144,8 @@ def test_query_rmsnorm_rope_reference_signature(wuda):
     normed = oracle.rmsnorm_bf16(u16(x).reshape(-1, 512), np.ones(512, np.float32), 1e-6).reshape(3, 64, 512)
     two_pass = oracle.rope_bf16(normed, pos.numpy(), ang.cos().numpy(), ang.sin().numpy(), 64)
     bf16_close(u16(out)[..., :448], two_pass[..., :448], min_equal=0.995)
-    bf16_close(u16(out), two_pass, min_equal=0.95)
+    # the rotated dims are differences of products: compare them by value (normalised inputs are O(1))
+    assert np.allclose(oracle.bf16_to_f32(u16(out)), oracle.bf16_to_f32(two_pass), rtol=2 ** -6, atol=3e-2)
 
 
 def test_query_rmsnorm_rope_strided_input_and_head_duplication(wuda):

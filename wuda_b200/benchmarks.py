@@ -8,6 +8,8 @@ because consecutive launches use different weight buffers that together exceed L
     python -m wuda_b200.benchmarks norm_rope_quant
     python -m wuda_b200.benchmarks csa_chain                       (layer launch of the indexer half-step)
     python -m wuda_b200.benchmarks csa_chain_launches              (three eager steps, for an ncu launch list)
+    python -m wuda_b200.benchmarks attention_half_layer            (every built stage of the half-layer, one graph)
+    python -m wuda_b200.benchmarks attention_half_layer_launches   (three eager passes, for an ncu launch list)
     python -m wuda_b200.benchmarks one gemm_fp8 64 24576 7168      (a few launches of one shape, for ncu)
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks tp2
 """
@@ -257,6 +259,98 @@ def csa_chain(batch=64, context=32768, topk=2048, reps=30, launches_only=0):
                                                    bytes_step / us / 1e3 / hbm, kind))
 
 
+def attention_half_layer(batch=64, context=32768, topk=2048, reps=30, launches_only=0):
+    """Every built stage of the attention half-layer in order, one CUDA graph: mHC pre -> front mixed
+    GEMM + FRONT-EMIT -> indexer half-step (q norm/quant, q projection, tails, cache writers, MQA
+    logits, top-k) -> [sparse attention: not built; its output is a constant stand-in tensor] ->
+    inverse RoPE + quant, grouped wo_a, quant, wo_b -> mHC post.  Model geometry (hidden 7168,
+    128 heads of 512, 16 output groups), random weights, L2 flushed before every timed replay."""
+    from wuda_b200 import o_proj
+    from wuda_b200.decode import CsaDecodeStage, CsaWeights
+    from wuda_b200.kv_cache import KVCacheManager
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(11)
+    hidden, q_lora, ih, mh = 7168, 1536, 64, 128
+    rnd8 = lambda *s: torch.randint(0, 0x7E, s, generator=g, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    sc = lambda *s: torch.rand(s, generator=g, device=dev) * 1e-3 + 1e-4
+    n_total = ih * 128 + mh * 512
+    ang = torch.outer(torch.arange(65536, dtype=torch.float32), 1.0 / (10000.0 ** (torch.arange(32) / 32.0))).to(dev)
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    weights = CsaWeights(rnd8(n_total, q_lora), sc(n_total // 128, q_lora // 128),
+                         torch.rand(q_lora, generator=g, device=dev) + 0.5, torch.rand(128, generator=g, device=dev) + 0.5,
+                         torch.rand(512, generator=g, device=dev) + 0.5, torch.rand(512, generator=g, device=dev) + 0.5,
+                         cos, sin, index_heads=ih, main_heads=mh)
+    pages_per_req = (context // 4 + 63) // 64 + 1
+    cache = KVCacheManager(batch, batch * pages_per_req + batch, pages_per_req, device=dev)
+    stage = CsaDecodeStage(weights, cache, batch, topk=topk)
+    slots = [cache.alloc_request() for _ in range(batch)]
+    for s_ in slots:
+        cache.advance(s_, context - 1)
+    epb = cache.entries_per_block["idx"]
+    pool = cache.idx_pool
+    pool[:, :epb * 128] = torch.randint(0, 0x7E, (pool.size(0), epb * 128), generator=g, dtype=torch.uint8, device=dev)
+    pool[:, epb * 128:epb * 132] = (torch.rand(pool.size(0), epb, generator=g, device=dev) * 0.09 + 0.01).view(torch.uint8)
+    cache.main_state.normal_(generator=g)
+    cache.idx_state.normal_(generator=g)
+    stage.prepare(slots)
+    # weights of the other stages
+    hc_w = torch.randn(24, 4 * hidden, generator=g, device=dev) * 0.01
+    hc_base, hc_scale = torch.zeros(24, device=dev), torch.ones(3, device=dev)
+    gamma = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
+    w8, w8s = rnd8(2048, hidden), sc(16, hidden // 128)
+    w16 = (torch.randn(2624, hidden, generator=g, device=dev) * 0.02).bfloat16()
+    ape, idx_ape = torch.randn(4, 1024, generator=g, device=dev), torch.randn(4, 256, generator=g, device=dev)
+    oproj = o_proj.OProjWeights(rnd8(16, 1024, 4096), sc(16 * 8, 32), rnd8(hidden, 16384), sc(56, 128))
+    x_hidden = torch.randn(batch, 4, hidden, generator=g, device=dev).bfloat16()
+    mla_out = torch.randn(batch, mh, 512, generator=g, device=dev).bfloat16()      # stand-in for the sparse attention
+    front_out = torch.empty(batch, 2048, dtype=torch.bfloat16, device=dev)
+    y16 = torch.empty(batch, 2624, dtype=torch.float32, device=dev)
+    ws = torch.empty(wuda.lib.wuda_mhc_pre_workspace_bytes(batch, hidden), dtype=torch.uint8, device=dev)
+    stage.q_raw = front_out[:, :q_lora]                                            # read in place by the chain
+    result = {}
+
+    def layer():
+        pre = wuda.mhc_pre(x_hidden, hc_w, hc_base, hc_scale, gamma, workspace=ws)
+        wuda.front_mixed_gemm(pre["normed"], pre["xq"], pre["xsf"], w16, w8, w8s, front_out, pos=stage.pos,
+                              main_state=cache.main_state, ape=ape, main_state_row=stage.main_state_row,
+                              idx_state=cache.idx_state, idx_state_row=stage.idx_state_row, idx_ape=idx_ape,
+                              win_y2=stage.win_y2, w64=stage.w64, y16=y16, status_word=stage.status)
+        stage.launch(batch)
+        result["out"] = o_proj.run_o_proj_mhc_post(mla_out, stage.pos, cos, sin, x_hidden, pre["post"], pre["comb"], oproj,
+                                                   status_word=stage.status)
+
+    if launches_only:
+        for _ in range(launches_only):
+            layer()
+        torch.cuda.synchronize()
+        stage.check_status()
+        print("attention_half_layer: %d eager passes done" % launches_only)
+        return
+    layer()
+    torch.cuda.synchronize()
+    stage.check_status()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        layer()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    total = 0.0
+    for i in range(reps + 3):
+        flush.fill_(i & 0xff)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            total += e0.elapsed_time(e1) * 1e3
+    stage.check_status()
+    us = total / reps
+    wbytes = 24 * 4 * hidden * 4 + 2048 * hidden + 2624 * hidden * 2 + n_total * q_lora + 16 * 1024 * 4096 + hidden * 16384
+    print("attention half-layer without its sparse attention: batch %d, context %d" % (batch, context))
+    print("  %.1f us per pass (one graph, L2 flushed before each); weights streamed %.1f MB + %.1f MB of indexer keys"
+          % (us, wbytes / 1e6, batch * (context // 4) * 132 / 1e6))
+
+
 def one(kind, m, n, k, launches=5):
     """A few eager launches of one GEMM shape (profiler captures)."""
     t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
@@ -281,4 +375,6 @@ if __name__ == "__main__":
         one(sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]))
         sys.exit(0)
     {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2,
-     "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3)}[which]()
+     "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
+     "attention_half_layer": attention_half_layer,
+     "attention_half_layer_launches": lambda: attention_half_layer(launches_only=3)}[which]()

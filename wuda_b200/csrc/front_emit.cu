@@ -39,26 +39,36 @@ struct Params {
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 __global__ void __launch_bounds__(kThreads) front_emit_kernel(Params p) {
+    // grid (tokens, 4): blockIdx.y = 0, 1 the two halves of the MAIN entry, 2 the indexer entry, 3 win_y2 + w64
     const int t = blockIdx.x;
+    const int part = blockIdx.y;
     const int phase = static_cast<int>(p.pos[t] & 3);
     const float* y16 = p.y16 + static_cast<int64_t>(t) * kN16;
-    if (p.win_y2)
-        for (int c = threadIdx.x; c < kWin; c += kThreads)
-            p.win_y2[static_cast<int64_t>(t) * kWin + c] = __bfloat162float(p.y8[static_cast<int64_t>(t) * kN8 + kQ + c]);
-    if (p.w64)
-        for (int c = threadIdx.x; c < kW64; c += kThreads)
-            p.w64[static_cast<int64_t>(t) * kW64 + c] = bf16_round(y16[kMain + kIdx + c]);
-    if (p.main_state) {
+    if (part == 3) {
+        if (p.win_y2)
+            for (int c = threadIdx.x; c < kWin; c += kThreads)
+                p.win_y2[static_cast<int64_t>(t) * kWin + c] = __bfloat162float(p.y8[static_cast<int64_t>(t) * kN8 + kQ + c]);
+        if (p.w64 && threadIdx.x < kW64)
+            p.w64[static_cast<int64_t>(t) * kW64 + threadIdx.x] = bf16_round(y16[kMain + kIdx + threadIdx.x]);
+    } else if (part < 2) {
+        if (!p.main_state) return;
         const int64_t row = p.main_row[t];
         if (row >= p.state_rows_total) {
             if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, WUDA_DEV_BAD_STATE_ROW);
         } else if (row >= 0) {
-            float* dst = p.main_state + row * kMain;
-            for (int c = threadIdx.x; c < kMain; c += kThreads)
-                dst[c] = c < kMain / 2 ? y16[c] : __fadd_rn(y16[c], __ldg(p.ape + phase * (kMain / 2) + c - kMain / 2));
+            // 1024 values as float4: the kv half is copied, the score half gets + ape
+            const float4* src = reinterpret_cast<const float4*>(y16 + part * (kMain / 2));
+            float4* dst = reinterpret_cast<float4*>(p.main_state + row * kMain + part * (kMain / 2));
+            const float4* add = reinterpret_cast<const float4*>(p.ape + phase * (kMain / 2));
+            float4 v = src[threadIdx.x];
+            if (part == 1) {
+                const float4 a = __ldg(add + threadIdx.x);
+                v = make_float4(__fadd_rn(v.x, a.x), __fadd_rn(v.y, a.y), __fadd_rn(v.z, a.z), __fadd_rn(v.w, a.w));
+            }
+            dst[threadIdx.x] = v;
         }
-    }
-    if (p.idx_state) {
+    } else {
+        if (!p.idx_state) return;
         const int64_t row = p.idx_row[t];
         if (row >= p.state_rows_total) {
             if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, WUDA_DEV_BAD_STATE_ROW);
@@ -86,6 +96,7 @@ extern "C" int wuda_front_emit(const void* y8_bf16, const float* y16_f32, const 
     WUDA_REQUIRE(y16_f32 && pos, "the BF16 segment's output and pos are required");
     WUDA_REQUIRE(!win_y2 || y8_bf16, "win_y2 needs the FP8 segment's output");
     WUDA_REQUIRE(!main_state || (ape && main_state_row), "main_state needs ape and main_state_row");
+    WUDA_REQUIRE(aligned16(y16_f32) && aligned16(main_state) && aligned16(ape), "y16, main_state and ape must be 16-byte aligned");
     WUDA_REQUIRE(!idx_state || (idx_ape && idx_state_row), "idx_state needs idx_ape and idx_state_row");
     WUDA_REQUIRE((!main_state && !idx_state) || state_rows_total >= 1, "state_rows_total must be >= 1");
     Params p;
@@ -102,7 +113,7 @@ extern "C" int wuda_front_emit(const void* y8_bf16, const float* y16_f32, const 
     p.w64 = w64;
     p.state_rows_total = state_rows_total;
     p.status = status_word;
-    front_emit_kernel<<<m, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    front_emit_kernel<<<dim3(m, 4), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
     WUDA_CUDA(cudaGetLastError());
     return WUDA_OK;
 }

@@ -71,15 +71,21 @@ __global__ void __launch_bounds__(kMixThreads) mhc_pre_mix_kernel(Params p) {
                   : make_float4(0.f, 0.f, 0.f, 0.f);
     const int t0 = blockIdx.y * kTokensPerCta;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int t = t0; t < min(t0 + kTokensPerCta, p.m); ++t) {
-        float x[4] = {0.f, 0.f, 0.f, 0.f};
-        if (in) {
-            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.x + static_cast<int64_t>(t) * K + k0));
-            x[0] = __uint_as_float(raw.x << 16);
-            x[1] = __uint_as_float(raw.x & 0xffff0000u);
-            x[2] = __uint_as_float(raw.y << 16);
-            x[3] = __uint_as_float(raw.y & 0xffff0000u);
-        }
+    // all of the CTA's activation loads go out before the first is used
+    uint2 raw[kTokensPerCta];
+#pragma unroll
+    for (int i = 0; i < kTokensPerCta; ++i)
+        raw[i] = (in && t0 + i < p.m) ? __ldg(reinterpret_cast<const uint2*>(p.x + static_cast<int64_t>(t0 + i) * K + k0))
+                                      : make_uint2(0u, 0u);
+#pragma unroll
+    for (int i = 0; i < kTokensPerCta; ++i) {
+        const int t = t0 + i;
+        if (t >= p.m) break;                        // uniform over the CTA
+        float x[4];
+        x[0] = __uint_as_float(raw[i].x << 16);
+        x[1] = __uint_as_float(raw[i].x & 0xffff0000u);
+        x[2] = __uint_as_float(raw[i].y << 16);
+        x[3] = __uint_as_float(raw[i].y & 0xffff0000u);
         float part[kPart];
 #pragma unroll
         for (int j = 0; j < kMix; ++j)
@@ -117,9 +123,20 @@ __global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
-    if (threadIdx.x < kPart) {
+    // 25 sums over the slices: 8 groups of threads take every eighth slice each (independent loads), then
+    // the 8 group sums are added in order - a fixed tree, so the result does not depend on timing
+    __shared__ float group_sum[8][kPart];
+    if (threadIdx.x < 8 * kPart) {
+        const int j = threadIdx.x % kPart, grp = threadIdx.x / kPart;
         float s = 0.f;
-        for (int sl = 0; sl < p.slices; ++sl) s += p.ws[(static_cast<int64_t>(sl) * p.m + t) * kPart + threadIdx.x];
+        for (int sl = grp; sl < p.slices; sl += 8) s += p.ws[(static_cast<int64_t>(sl) * p.m + t) * kPart + j];
+        group_sum[grp][j] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x < kPart) {
+        float s = group_sum[0][threadIdx.x];
+#pragma unroll
+        for (int grp = 1; grp < 8; ++grp) s += group_sum[grp][threadIdx.x];
         mix[threadIdx.x] = s;
     }
     __syncthreads();

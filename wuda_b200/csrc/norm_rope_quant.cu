@@ -176,7 +176,8 @@ __global__ void __launch_bounds__(1024, 1) rope_quant_kernel(const RopeParams p)
     const __nv_bfloat16* x = p.x + static_cast<int64_t>(t) * width;
     // every thread of a 16-thread quantisation group runs the same number of iterations
     // (width is a multiple of 128), so the shuffles inside quant_store8 are convergent
-    for (int ch = threadIdx.x; ch < chunks; ch += blockDim.x) {
+    // (blockIdx.y splits a token's chunks over several CTAs when there are few tokens)
+    for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < chunks; ch += blockDim.x * gridDim.y) {
         float v[8];
         unpack8(*reinterpret_cast<const uint4*>(x + 8 * ch), v);
         const int in_head = (8 * ch) % p.head_dim;
@@ -277,7 +278,12 @@ extern "C" int wuda_rope_quant_fp8(const void* x_bf16, const int64_t* positions,
     const int chunks = heads * head_dim / 8;
     int threads = chunks < 1024 ? (chunks + 31) / 32 * 32 : 1024;
     // keep whole 16-thread groups in step: the per-thread iteration count must be equal inside a group
-    rope_quant_kernel<<<tokens, threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    // few tokens: cut each token's row over several CTAs (a quantisation group is 16 consecutive threads, so any
+    // multiple of the block size is a valid cut)
+    int splits = 1;
+    const int passes = (chunks + threads - 1) / threads;
+    while (splits < passes && tokens * splits < 296) splits *= 2;
+    rope_quant_kernel<<<dim3(tokens, splits), threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
     WUDA_CUDA(cudaGetLastError());
     return WUDA_OK;
 }
