@@ -378,7 +378,7 @@ int wuda_csa_decode_step(const wuda_csa_weights* weights, const wuda_csa_caches*
  *   collapsed_bf16, normed_bf16 bf16 [m, hidden];  x_fp8 e4m3 [m, hidden] with x_scales fp32
  *   [m, hidden/128];  each nullable
  *   workspace: wuda_mhc_pre_workspace_bytes(m, hidden) bytes, contents irrelevant
- * hidden % 128 == 0, hidden <= 16384.
+ * hidden % 128 == 0, hidden <= 8192.
  */
 int64_t wuda_mhc_pre_workspace_bytes(int m, int hidden);
 int wuda_mhc_pre(const void* hidden_states, const float* weight, const float* base, const float* scale,

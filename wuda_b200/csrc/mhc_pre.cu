@@ -13,8 +13,8 @@
 // norm + quant at :300-340) and the Sinkhorn tail include/front_mixed_gemm.cuh:438-489.
 //
 // Two kernels.  (1) The 24 dot products are 1.4 MFLOP per token against 2.75 MB of weights: CUDA
-// cores in fp32 (exact products, unlike TF32), K cut into 56 slices of 512 so that 56 x ceil(M/8)
-// CTAs share the work; a thread keeps its 24 x 4 weights in registers across the CTA's 8 tokens.
+// cores in fp32 (exact products, unlike TF32), K cut into 56 slices of 512 so that 56 x ceil(M/4)
+// CTAs share the work; a thread keeps its 24 x 4 weights in registers across the CTA's 4 tokens.
 // Partials go to a workspace [slice][token][25] (24 dots + the sum of squares).  (2) One CTA per
 // token adds the slices in order (deterministic), runs the gates and the Sinkhorn in one warp, and
 // streams the 4 residual rows once for collapse + norm + quantisation.
@@ -30,7 +30,7 @@ constexpr int kMix = 24;                 // pre 4 | post 4 | comb 16
 constexpr int kPart = kMix + 1;          // + sum of squares
 constexpr int kSlice = 512;              // K elements per slice
 constexpr int kMixThreads = 128;         // 4 elements per thread
-constexpr int kTokensPerCta = 8;
+constexpr int kTokensPerCta = 4;
 constexpr int kFinishThreads = 256;
 constexpr int kSinkhornIters = 20;
 
@@ -59,7 +59,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 __global__ void __launch_bounds__(kMixThreads) mhc_pre_mix_kernel(Params p) {
-    __shared__ float warp_part[kMixThreads / 32][kPart];
+    __shared__ float warp_part[2][kMixThreads / 32][kPart];   // two buffers: one barrier per token
     const int slice = blockIdx.x;
     const int k0 = slice * kSlice + threadIdx.x * 4;
     const int K = kStreams * p.hidden;
@@ -93,16 +93,15 @@ __global__ void __launch_bounds__(kMixThreads) mhc_pre_mix_kernel(Params p) {
         part[kMix] = fmaf(x[3], x[3], fmaf(x[2], x[2], fmaf(x[1], x[1], x[0] * x[0])));
 #pragma unroll
         for (int j = 0; j < kPart; ++j) part[j] = warp_sum(part[j]);
-        __syncthreads();                            // the previous token's partials have been read
+        float (*buf)[kPart] = warp_part[i & 1];
         if (lane == 0) {
 #pragma unroll
-            for (int j = 0; j < kPart; ++j) warp_part[warp][j] = part[j];
+            for (int j = 0; j < kPart; ++j) buf[warp][j] = part[j];
         }
-        __syncthreads();
+        __syncthreads();                            // (buffer i & 1 is next written two tokens later, after another barrier)
         if (threadIdx.x < kPart) {
             const int j = threadIdx.x;
-            p.ws[(static_cast<int64_t>(slice) * p.m + t) * kPart + j] =
-                ((warp_part[0][j] + warp_part[1][j]) + warp_part[2][j]) + warp_part[3][j];
+            p.ws[(static_cast<int64_t>(slice) * p.m + t) * kPart + j] = ((buf[0][j] + buf[1][j]) + buf[2][j]) + buf[3][j];
         }
     }
 }
@@ -122,6 +121,19 @@ __global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p
     __shared__ float warp_ss[kFinishThreads / 32];
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int kMaxVec = 4;                       // hidden <= 4 * 256 * 8 = 8192
+    const int vectors = (p.collapsed || p.normed || p.x_fp8) ? p.hidden / 8 : 0;
+    // the token's four rows are requested first: their latency hides behind the slice sums, the gates and the
+    // Sinkhorn iterations, none of which needs them
+    uint4 raw[kMaxVec][kStreams];
+#pragma unroll
+    for (int k = 0; k < kMaxVec; ++k) {
+        const int vi = threadIdx.x + k * kFinishThreads;
+#pragma unroll
+        for (int h = 0; h < kStreams; ++h)
+            raw[k][h] = vi < vectors ? __ldcs(reinterpret_cast<const uint4*>(p.x + (static_cast<int64_t>(t) * kStreams + h) * p.hidden) + vi)
+                                     : make_uint4(0u, 0u, 0u, 0u);
+    }
 
     // 25 sums over the slices: 8 groups of threads take every eighth slice each (independent loads), then
     // the 8 group sums are added in order - a fixed tree, so the result does not depend on timing
@@ -182,8 +194,6 @@ __global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p
 
     // collapse: a thread owns the 8-value vectors tid, tid + 256, ..; a 128-block of the row is 16
     // consecutive vectors, i.e. 16 consecutive threads
-    constexpr int kMaxVec = 8;                       // hidden <= 8 * 256 * 8 = 16384
-    const int vectors = p.hidden / 8;
     const float pr[kStreams] = {pre_s[0], pre_s[1], pre_s[2], pre_s[3]};
     float y[kMaxVec][8];
     float ss = 0.f;
@@ -194,8 +204,7 @@ __global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p
             float acc[8];
 #pragma unroll
             for (int h = 0; h < kStreams; ++h) {
-                const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p.x + (static_cast<int64_t>(t) * kStreams + h) * p.hidden) + vi);
-                const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+                const uint32_t wv[4] = {raw[k][h].x, raw[k][h].y, raw[k][h].z, raw[k][h].w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float lo = __fmul_rn(pr[h], __uint_as_float(wv[i] << 16));
@@ -288,8 +297,8 @@ extern "C" int wuda_mhc_pre(const void* hidden_states, const float* weight, cons
     using namespace wuda::mhcpre;
     clear_error();
     WUDA_REQUIRE(m >= 1, "m must be >= 1 (got %d)", m);
-    WUDA_REQUIRE(hidden >= 128 && hidden % 128 == 0 && hidden <= 16384,
-                 "hidden must be a multiple of 128 in [128, 16384] (got %d)", hidden);
+    WUDA_REQUIRE(hidden >= 128 && hidden % 128 == 0 && hidden <= 8192,
+                 "hidden must be a multiple of 128 in [128, 8192] (got %d)", hidden);
     WUDA_REQUIRE(hidden_states && weight && base && scale && workspace, "hidden, weight, base, scale and workspace are required");
     WUDA_REQUIRE((!normed_bf16 && !x_fp8) || attn_norm_gamma, "the norm weight is required with normed or x_fp8");
     WUDA_REQUIRE(!x_fp8 || x_scales, "x_scales is required with x_fp8");
