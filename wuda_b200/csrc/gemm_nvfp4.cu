@@ -304,29 +304,32 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 if (!to_end) {
                     const long long t_end = static_cast<long long>(tile + 1) * p.kb - 1;
                     const int last = cta_of(units, t_end, gridDim.x);
-                    for (int c = blockIdx.x + 1; c <= last; ++c) {
-                        if (et == 0 && alive) {
-                            const unsigned long long start = globaltimer_ns();
-                            uint32_t spins = 0;
-                            while (ld_acquire_gpu(p.flags + c) == 0) {
-                                if ((++spins & 255u) == 0u && (*abort_flag || globaltimer_ns() - start > kWaitLimitNs)) {
-                                    *abort_flag = 1;
-                                    if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeerFlag);
-                                    break;
-                                }
-                                __nanosleep(64);
+                    // every contributor's flag is awaited by a thread of its own, then the partials are added in
+                    // CTA order (the loads of different partials overlap)
+                    for (int c = blockIdx.x + 1 + et; c <= last && alive; c += 32 * kEpiWarps) {
+                        const unsigned long long start = globaltimer_ns();
+                        uint32_t spins = 0;
+                        while (ld_acquire_gpu(p.flags + c) == 0) {
+                            if ((++spins & 255u) == 0u && (*abort_flag || globaltimer_ns() - start > kWaitLimitNs)) {
+                                *abort_flag = 1;
+                                if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeerFlag);
+                                break;
                             }
+                            __nanosleep(64);
                         }
-                        epi_bar_sync();
-                        alive = alive && !*abort_flag;
-                        if (alive) {
+                    }
+                    epi_bar_sync();
+                    alive = alive && !*abort_flag;
+                    if (alive) {
+                        for (int c = blockIdx.x + 1; c <= last; ++c) {
                             const float* peer = p.scratch + static_cast<int64_t>(c) * (M_PAD * kTileN) + et;
 #pragma unroll
                             for (int i = 0; i < M_PAD; ++i) acc[i] += __ldcg(peer + i * kTileN);
                         }
-                        epi_bar_sync();
-                        if (et == 0 && alive) p.flags[c] = 0;
                     }
+                    epi_bar_sync();
+                    if (alive)
+                        for (int c = blockIdx.x + 1 + et; c <= last; c += 32 * kEpiWarps) p.flags[c] = 0;
                 }
                 if (alive && nrow < p.N) {
 #pragma unroll
