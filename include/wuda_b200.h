@@ -387,6 +387,22 @@ int wuda_mhc_pre(const void* hidden_states, const float* weight, const float* ba
                  void* workspace, int64_t workspace_bytes, int m, int hidden, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * MoE router: expert logits -> top-k experts and routing weights.
+ *   score = softmax (0) | sigmoid (1) | sqrt(softplus) (2) of the logits; the k largest of
+ *   score + bias are selected (ties to the lower expert, listed in descending order);
+ *   weights = score[selected], divided by their sum unless softmax, times route_scale.
+ *
+ * Replaces Gate.forward of the origin (origin/model.py:563-584) behind its projection, which is
+ * wuda_gemm_bf16 with fp32 output (x bf16 [tokens, dim] x gate weight bf16 [experts, dim]).  The
+ * hash-routed form of the first layers (a table lookup by token id) needs no kernel.
+ *
+ *   logits fp32 [tokens, experts];  bias fp32 [experts], nullable
+ *   weights fp32 [tokens, k];  indices int32 [tokens, k];  experts <= 512, k <= 32
+ */
+int wuda_moe_route(const float* logits, const float* bias, float* weights, int32_t* indices, int tokens, int experts,
+                   int k, int score_func, float route_scale, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * mHC post mix, the last op of an attention half-layer:
  *   output[t, j, d] = post[t, j] * attention_out[t, d] + sum_i comb[t, i, j] * residual[t, i, d]
  *

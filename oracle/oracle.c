@@ -628,6 +628,49 @@ void oracle_mhc_pre(const uint16_t* x, const float* weight, const float* base, c
     }
 }
 
+/* ------------------------------------------------------------------ MoE router
+ *
+ * After Gate.forward, dsv4_megakernel/origin/model.py:563-584: scores from the logits (softmax,
+ * sigmoid or sqrt(softplus)), selection of the k largest of score + bias (ties to the lower
+ * expert, descending order), weights = the selected scores without the bias, normalised unless
+ * softmax, times route_scale.
+ */
+void oracle_moe_route(const float* logits, const float* bias, float* weights, int32_t* indices, int tokens,
+                      int experts, int k, int score_func, float route_scale) {
+    float* score = (float*)malloc(sizeof(float) * experts * 2);
+    float* pick = score + experts;
+    for (int t = 0; t < tokens; ++t) {
+        const float* row = logits + (int64_t)t * experts;
+        if (score_func == 0) {
+            float mx = -INFINITY, sum = 0.0f;
+            for (int e = 0; e < experts; ++e) mx = fmaxf(mx, row[e]);
+            for (int e = 0; e < experts; ++e) sum += (score[e] = expf(row[e] - mx));
+            for (int e = 0; e < experts; ++e) score[e] /= sum;
+        } else {
+            for (int e = 0; e < experts; ++e)
+                score[e] = score_func == 1 ? 1.0f / (1.0f + expf(-row[e]))
+                                           : sqrtf(row[e] > 20.0f ? row[e] : log1pf(expf(row[e])));
+        }
+        for (int e = 0; e < experts; ++e) pick[e] = bias ? score[e] + bias[e] : score[e];
+        float wsum = 0.0f;
+        for (int r = 0; r < k; ++r) {
+            int best = 0;
+            for (int e = 1; e < experts; ++e)
+                if (pick[e] > pick[best]) best = e;
+            indices[(int64_t)t * k + r] = best;
+            weights[(int64_t)t * k + r] = score[best];
+            wsum += score[best];
+            pick[best] = -INFINITY;
+        }
+        for (int r = 0; r < k; ++r) {
+            float w = weights[(int64_t)t * k + r];
+            if (score_func != 0) w /= wsum;
+            weights[(int64_t)t * k + r] = w * route_scale;
+        }
+    }
+    free(score);
+}
+
 /* ------------------------------------------------------------------ mHC post mix
  *
  * out[m,j,d] = post[m,j] * x[m,d] + sum_i comb[m,i,j] * res[m,i,d], bf16 in and out, in the

@@ -64,6 +64,7 @@ def _declare(l):
     l.oracle_query_rms_rope.argtypes = [vp, i64, vp, vp, vp, c.c_int, vp, c.c_int, c.c_int, c.c_int, c.c_float]
     l.oracle_mhc_pre.argtypes = [vp, vp, vp, vp, vp, c.c_float, c.c_float, c.c_float, vp, vp, vp, vp, vp, vp, vp,
                                  c.c_int, c.c_int]
+    l.oracle_moe_route.argtypes = [vp, vp, vp, vp, c.c_int, c.c_int, c.c_int, c.c_int, c.c_float]
     l.oracle_gemm_nvfp4.argtypes = [c.c_void_p, c.c_void_p, c.c_float, c.c_void_p, c.c_void_p, c.c_float, c.c_void_p,
                                     c.c_int, c.c_int, c.c_int, c.c_int]
     l.oracle_gemm_fp8_blockscaled.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
@@ -290,6 +291,17 @@ def front_emit(y8_bf16, y16, pos, main_state, ape, main_row, idx_state, idx_ape,
             isr[idx_row[t], :256] = y16[t, 2048:2304]
             isr[idx_row[t], 256:] = y16[t, 2304:2560] + idx_ape[ph]
     return win, w64
+
+
+def moe_route(logits, bias, k, score_func, route_scale=1.0):
+    """logits fp32 [tokens, experts] -> (weights fp32 [tokens, k], indices int32 [tokens, k]);
+    score_func 0 softmax, 1 sigmoid, 2 sqrt(softplus)."""
+    lg = _c(logits, np.float32)
+    b = None if bias is None else _c(bias, np.float32)
+    w = np.empty((lg.shape[0], k), np.float32)
+    idx = np.empty((lg.shape[0], k), np.int32)
+    lib().oracle_moe_route(_p(lg), _p(b), _p(w), _p(idx), lg.shape[0], lg.shape[1], k, score_func, route_scale)
+    return w, idx
 
 
 def gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=True):

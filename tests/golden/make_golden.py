@@ -13,6 +13,7 @@ Functions used (paths inside the reference repository):
   dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py   ref_comp_step (:550-586, fp8 form) and
                                                            ref_win_step (:646-665)
   dsv4_megakernel/megakernel/test/test_hc_fused_tc.py     hc_reference (:115-136)
+  dsv4_megakernel/origin/model.py                         Gate.forward (:563-584)
   dsv4_megakernel/megakernel/test/kv_cache_manager.py     KVCacheManager (:53-257), run on the CPU
 The first two are written for device="cuda"; they are run here on the CPU by mapping that one
 keyword to "cpu", which changes no arithmetic.
@@ -241,6 +242,29 @@ def golden_mhc_pre(ref_root):
     print("mhc_pre_7168.npz", tuple(collapsed.shape))
 
 
+def golden_moe_gate(ref_root):
+    """The origin's Gate on seeded inputs, once per score function, with and without a bias."""
+    import types
+    model = _load(ref_root, "dsv4_megakernel/origin/model.py", "ref_origin_model_gate")
+    model.torch = torch
+    g = torch.Generator().manual_seed(81)
+    tokens, dim, experts, topk = 7, 256, 256, 8
+    x = torch.randn(tokens, dim, generator=g).bfloat16()
+    w = (torch.randn(experts, dim, generator=g) * 0.08).bfloat16()
+    bias = torch.randn(experts, generator=g) * 0.05
+    out = dict(x=_u16(x), weight=_u16(w), bias=bias.numpy(), route_scale=2.5, topk=topk)
+    for name in ("softmax", "sigmoid", "sqrtsoftplus"):
+        args = types.SimpleNamespace(dim=dim, n_activated_experts=topk, score_func=name, route_scale=2.5,
+                                     n_hash_layers=0, n_routed_experts=experts, vocab_size=16)
+        gate = model.Gate(1, args)
+        gate.weight.data = w.float()
+        gate.bias.data = bias.clone()
+        weights, indices = gate(x.float())
+        out["weights_" + name], out["indices_" + name] = weights.detach().numpy(), indices.numpy().astype(np.int32)
+    np.savez_compressed(os.path.join(HERE, "moe_gate_256.npz"), **out)
+    print("moe_gate_256.npz", tuple(weights.shape))
+
+
 KV_TRACE_CONFIGS = [
     dict(capacity=5, pages_per_pool=96, max_pages_per_req=12),
     dict(capacity=5, pages_per_pool=96, max_pages_per_req=12, state_ring_entries=16),
@@ -330,6 +354,7 @@ def main():
     golden_kv_cache(ref_root)
     golden_cache_writers(ref_root)
     golden_mhc_pre(ref_root)
+    golden_moe_gate(ref_root)
 
 
 if __name__ == "__main__":

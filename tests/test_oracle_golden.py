@@ -261,3 +261,20 @@ def test_mhc_pre_oracle_matches_reference_twin():
     nb = oracle.bf16_to_f32(o["normed"]).reshape(3, 56, 128)
     assert np.all(np.abs(deq - nb) <= o["xsf"][..., None] * 16 * 1.01 + np.abs(nb) * 2.0 ** -4)
     assert np.all(np.log2(o["xsf"]) == np.round(np.log2(o["xsf"])))
+
+
+def test_moe_route_oracle_matches_origin_gate():
+    g = load_golden("moe_gate_256.npz")
+    x, w = oracle.bf16_to_f32(g["x"]).astype(np.float64), oracle.bf16_to_f32(g["weight"]).astype(np.float64)
+    logits = (x @ w.T).astype(np.float32)
+    for code, name in enumerate(("softmax", "sigmoid", "sqrtsoftplus")):
+        weights, indices = oracle.moe_route(logits, g["bias"], int(g["topk"]), code, float(g["route_scale"]))
+        assert np.array_equal(indices, g["indices_" + name]), name
+        assert np.abs(weights - g["weights_" + name]).max() <= 1e-6, name
+        if code:
+            assert np.allclose(weights.sum(1), float(g["route_scale"]), rtol=1e-5)
+    # ties go to the lower expert; without a bias the choice follows the score itself
+    flat = np.zeros((1, 40), np.float32)
+    flat[0, [7, 3, 30]] = 1.0
+    weights, indices = oracle.moe_route(flat, None, 5, 1, 1.0)
+    assert indices[0].tolist() == [3, 7, 30, 0, 1]

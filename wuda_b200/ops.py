@@ -15,7 +15,7 @@ from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
-           "rmsnorm_rope_out", "mhc_post_out", "mhc_pre", "bf16_gemm", "front_mixed_gemm", "idx_postprocess_fp8", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
+           "rmsnorm_rope_out", "mhc_post_out", "mhc_pre", "moe_gate", "bf16_gemm", "front_mixed_gemm", "idx_postprocess_fp8", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -527,6 +527,27 @@ def front_mixed_gemm(x, x_fp8, x_sf, w_bf16, w_fp8, w_sf, out, *, pos=None, main
                                   _ptr(main_state_row), _ptr(idx_state), _ptr(idx_ape), _ptr(idx_state_row),
                                   _ptr(win_y2), _ptr(w64), max(rows_total, 1), m, _ptr(status_word), _stream()))
     return out, y16
+
+
+SCORE_FUNCS = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}
+
+
+def moe_gate(x, weight, bias=None, score_func="sqrtsoftplus", route_scale=1.0, topk=8, *, logits=None):
+    """The origin's Gate.forward (origin/model.py:563-584) for score-routed layers: x bf16 [M, dim],
+    gate weight bf16 [experts, dim], bias fp32 [experts] or None.  Returns (weights fp32 [M, topk],
+    indices int32 [M, topk]).  Two launches: the projection (fp32 logits) and the router."""
+    _require(score_func in SCORE_FUNCS, "score_func must be one of %s" % sorted(SCORE_FUNCS))
+    m, experts = x.size(0), weight.size(0)
+    if logits is None:
+        logits = torch.empty(m, experts, dtype=torch.float32, device=x.device)
+    bf16_gemm(x, weight, out=logits)
+    if bias is not None:
+        _require(_f32(bias, "bias").numel() == experts, "bias must be fp32 [experts]")
+    w = torch.empty(m, topk, dtype=torch.float32, device=x.device)
+    idx = torch.empty(m, topk, dtype=torch.int32, device=x.device)
+    check(lib.wuda_moe_route(logits.data_ptr(), _ptr(bias), w.data_ptr(), idx.data_ptr(), m, experts, topk,
+                             SCORE_FUNCS[score_func], float(route_scale), _stream()))
+    return w, idx
 
 
 def exchange_handles(my_handle, group=None):
