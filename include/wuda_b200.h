@@ -50,7 +50,8 @@ typedef enum wuda_device_status {
     WUDA_DEV_TIMEOUT_GEMM_TMEM_EMPTY = 124,
     WUDA_DEV_TIMEOUT_PEER_FLAG = 131,
     WUDA_DEV_BAD_DESTINATION = 141, /* cache destination outside the pool: that record was not written */
-    WUDA_DEV_BAD_STATE_ROW = 142    /* state_row outside the state rings: that row was skipped         */
+    WUDA_DEV_BAD_STATE_ROW = 142,   /* state_row outside the state rings: that row was skipped         */
+    WUDA_DEV_BAD_EXPERT = 143       /* expert index outside [0, experts): that pair was dropped        */
 } wuda_device_status;
 
 /* Library version (major*10000 + minor*100 + patch). */
@@ -401,6 +402,49 @@ int wuda_mhc_pre(const void* hidden_states, const float* weight, const float* ba
  */
 int wuda_moe_route(const float* logits, const float* bias, float* weights, int32_t* indices, int tokens, int experts,
                    int k, int score_func, float route_scale, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Routed experts of the MoE block (origin/model.py:587-644, MoE.forward / Expert.forward), as five
+ * calls that never synchronise with the host: the number of row groups stays on the device.
+ *
+ *   wuda_moe_dispatch            (token, expert) pairs -> rows sorted by expert, each expert's rows
+ *                                padded to groups of 16 (a GEMM row tile), stable in token order
+ *   wuda_moe_gather_quant_nvfp4  row r <- activation of row_token[r], quantised to NVFP4
+ *   wuda_gemm_nvfp4_grouped      c[group rows] = a[group rows] . w[expert of the group]^T
+ *   wuda_moe_swiglu_quant_nvfp4  silu(min(gate, L)) * clamp(up, +-L) * routing weight -> bf16 -> NVFP4
+ *   wuda_moe_combine             y[t] = bf16(sum_j out[pair_row[t, j]] (+ shared[t])), slot order
+ * The reference has no kernel for this block (its MoE runs through the origin's TileLang GEMMs,
+ * which are W4A8 with e8m0 scales); NVFP4 (e2m1, one ue4m3 scale per 16 values, one fp32 scale per
+ * tensor) on both operands is the form the benchmark configuration names.
+ *
+ * Arrays (all device memory): max_groups >= wuda_moe_max_groups(tokens, k, experts);
+ *   group_expert int32 [max_groups] (-1 = unused);  num_groups int32 [1]
+ *   row_token int32 [max_groups*16] (-1 = padding);  row_weight fp32 [max_groups*16]
+ *   pair_row int32 [tokens, k] (row of each pair; -1 for an invalid expert index)
+ *   a_fp4 uint8 [max_groups*16, K/2] (two e2m1 per byte, low nibble first)
+ *   a_sf_packed uint8 [max_groups, K/256, 2048]: scale of row r, values [16j, 16j+16) of K block kb at
+ *       ((g*K/256 + kb)*2048) + ((j/4)%4)*512 + (r%16)*16 + j%4, g = r/16; ZERO before the first call
+ *       (only rows 0..15 of each 128-row image are ever written)
+ *   expert weights: w uint8 [experts*n, K/2]; w_sf_packed per expert in the layout of wuda_gemm_nvfp4,
+ *       experts concatenated; w_global_scales fp32 [experts]
+ * NVFP4 quantisation of 16 values with tensor scale gs: sf = e4m3(min(amax/6/gs, 448)),
+ * q = e2m1(x / (sf*gs)) to the nearest code, ties to the smaller magnitude.
+ */
+int wuda_moe_max_groups(int tokens, int k, int experts);
+int wuda_moe_dispatch(const int32_t* indices, const float* weights, int32_t* group_expert, int32_t* num_groups,
+                      int32_t* row_token, float* row_weight, int32_t* pair_row, int tokens, int k, int experts,
+                      int max_groups, int32_t* status_word, void* stream);
+int wuda_moe_gather_quant_nvfp4(const void* x_bf16, const int32_t* row_token, const int32_t* num_groups, void* a_fp4,
+                                void* a_sf_packed, float global_scale, int max_groups, int k, void* stream);
+int wuda_gemm_nvfp4_grouped(const void* a, const void* a_sf_packed, float a_global_scale, const void* w,
+                            const void* w_sf_packed, const float* w_global_scales, const int32_t* group_expert,
+                            const int32_t* num_groups, void* c_bf16, int max_groups, int experts, int n, int k,
+                            void* scratch, int64_t scratch_bytes, int32_t* status_word, void* stream);
+int wuda_moe_swiglu_quant_nvfp4(const void* h_bf16, const int32_t* row_token, const float* row_weight,
+                                const int32_t* num_groups, void* a_fp4, void* a_sf_packed, float global_scale,
+                                float swiglu_limit, int max_groups, int inter, void* stream);
+int wuda_moe_combine(const void* expert_out_bf16, const int32_t* pair_row, const void* shared_bf16, void* y_bf16,
+                     int tokens, int k, int dim, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * mHC post mix, the last op of an attention half-layer:

@@ -304,6 +304,59 @@ def moe_route(logits, bias, k, score_func, route_scale=1.0):
     return w, idx
 
 
+E2M1_BOUNDS = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], np.float32)
+
+
+def quantize_nvfp4_rows(x, gs):
+    """fp32 [R, K] -> (packed e2m1 uint8 [R, K/2], ue4m3 scale bytes [R, K/16]) with a GIVEN tensor scale:
+    sf = e4m3(min(amax/6/gs, 448)), q = e2m1(x / (sf*gs)), ties to the smaller magnitude (the rule of
+    dsv4_megakernel/origin/convert.py:11-14 and megakernel/test/test_mqa_logits_fp4.py:69-115)."""
+    x = np.ascontiguousarray(x, np.float32)
+    r, k = x.shape
+    v = x.reshape(r, k // 16, 16)
+    gs = np.float32(gs)
+    want = np.minimum(np.abs(v).max(-1) / np.float32(6.0) / gs, np.float32(448.0)).astype(np.float32)
+    sf = e4m3_encode(want)
+    d = e4m3_decode(sf).astype(np.float32)
+    denom = (d * gs).astype(np.float32)[..., None]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        scaled = np.where(d[..., None] > 0, v / denom, np.float32(0)).astype(np.float32)
+    idx = np.searchsorted(E2M1_BOUNDS, np.minimum(np.abs(scaled), np.float32(6.0)), side="left").astype(np.uint8)
+    code = idx | (((scaled < 0) & (idx != 0)).astype(np.uint8) << 3)
+    code = code.reshape(r, k // 2, 2)
+    return ((code[:, :, 0] & 15) | (code[:, :, 1] << 4)).astype(np.uint8), sf.reshape(r, k // 16)
+
+
+def moe_dispatch(indices, experts):
+    """indices int32 [tokens, k] -> (group_expert list, row_token [groups*16], pair_row [tokens, k]): pairs sorted
+    by expert, stable in flat order, every expert padded to groups of 16 rows."""
+    idx = np.asarray(indices, np.int32)
+    flat = idx.reshape(-1)
+    group_expert, row_token, pair_row = [], [], np.full(flat.shape, -1, np.int32)
+    for e in range(experts):
+        members = np.nonzero(flat == e)[0]
+        if len(members) == 0:
+            continue
+        base = len(row_token)
+        groups = (len(members) + 15) // 16
+        group_expert += [e] * groups
+        row_token += [int(p) // idx.shape[1] for p in members] + [-1] * (groups * 16 - len(members))
+        pair_row[members] = base + np.arange(len(members))
+    return np.array(group_expert, np.int32), np.array(row_token, np.int32), pair_row.reshape(idx.shape)
+
+
+def moe_swiglu(h_bf16, row_weight, limit):
+    """h uint16 (bf16) [R, 2I] = gate | up -> uint16 (bf16) [R, I] of weight * silu(min(gate, L)) * clamp(up, +-L)."""
+    h = bf16_to_f32(_c(h_bf16, np.uint16))
+    inter = h.shape[1] // 2
+    gate, up = h[:, :inter].copy(), h[:, inter:].copy()
+    if limit > 0:
+        up = np.clip(up, -np.float32(limit), np.float32(limit))
+        gate = np.minimum(gate, np.float32(limit))
+    silu = (gate / (np.float32(1) + np.exp(-gate, dtype=np.float32))).astype(np.float32)
+    return f32_to_bf16((np.asarray(row_weight, np.float32)[:, None] * (silu * up).astype(np.float32)).astype(np.float32))
+
+
 def gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=True):
     """a e4m3 bytes [M,K], a_s fp32 [M,K/128], b e4m3 bytes [N,K], b_s fp32 [N/128,K/128].
     Returns uint16 (bf16) or fp32 [M,N]."""

@@ -1,0 +1,133 @@
+"""GPU parity of the routed-expert block (dispatch, NVFP4 gather-quantisation, grouped NVFP4 GEMMs,
+SwiGLU + quantisation, combine; all through the C ABI) against the CPU oracle, stage by stage: every
+stage's GPU output is compared with the oracle applied to that stage's GPU inputs."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from wuda_b200 import moe
+
+pytestmark = pytest.mark.gpu
+
+
+def u16(t):
+    return t.cpu().view(torch.int16).numpy().view(np.uint16)
+
+
+def unpack_sf(packed, groups, kb):
+    """[groups, kb, 2048] image -> scale bytes [groups*16, kb*16] (rows 0..15 of every 128-row image)."""
+    v = packed.reshape(groups, kb, 4, 32, 4, 4)            # [g][kb][step][row%32][row/32][byte]
+    rows = v[:, :, :, :16, 0, :]                           # [g][kb][step][r][byte]
+    return np.ascontiguousarray(rows.transpose(0, 3, 1, 2, 4)).reshape(groups * 16, kb * 16)
+
+
+def close_bf16(got, ref, rel=1e-2):
+    g, r = oracle.bf16_to_f32(got), oracle.bf16_to_f32(ref)
+    assert np.all(np.abs(g - r) <= rel * np.abs(r) + 2e-3 * np.abs(r).max())
+
+
+@pytest.mark.parametrize("tokens,experts,k,dim,inter,limit", [(20, 6, 3, 512, 256, 0.0), (64, 16, 4, 768, 512, 7.0),
+                                                              (1, 4, 2, 256, 256, 0.0)])
+def test_routed_experts_stagewise(wuda, tokens, experts, k, dim, inter, limit):
+    g = torch.Generator().manual_seed(tokens * 13 + experts)
+    w1 = torch.randn(experts, inter, dim, generator=g) * 0.05
+    w3 = torch.randn(experts, inter, dim, generator=g) * 0.05
+    w2 = torch.randn(experts, dim, inter, generator=g) * 0.05
+    weights = moe.RoutedExperts(w1, w3, w2, act_scale_in=4.0 / (448 * 6), act_scale_mid=3.0 / (448 * 6), swiglu_limit=limit)
+    runner = moe.MoERunner(weights, tokens, k)
+    x = torch.randn(tokens, dim, generator=g).bfloat16()
+    # a skewed routing: expert 0 takes more than one group of 16 when there are enough tokens
+    idx = torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(tokens)]).int()
+    if tokens >= 20:
+        idx[:18, 0] = 0
+        for t in range(18):                                # keep the k experts of a token distinct
+            for j in range(1, k):
+                if idx[t, j] == 0:
+                    idx[t, j] = experts - 1 if (experts - 1) not in idx[t].tolist() else experts - 2
+    rw = torch.rand(tokens, k, generator=g) + 0.1
+    shared = torch.randn(tokens, dim, generator=g).bfloat16()
+    y = runner.forward(x.cuda(), rw.cuda(), idx.cuda(), shared=shared.cuda())
+    torch.cuda.synchronize()
+    assert int(runner.status.item()) == 0
+
+    # 1 dispatch: identical
+    ge, rt, pr = oracle.moe_dispatch(idx.numpy(), experts)
+    groups = len(ge)
+    assert int(runner.num_groups.item()) == groups
+    assert np.array_equal(runner.group_expert.cpu().numpy()[:groups], ge)
+    assert np.array_equal(runner.row_token.cpu().numpy()[:groups * 16], rt)
+    assert np.array_equal(runner.pair_row.cpu().numpy()[:tokens], pr)
+    rows = groups * 16
+    live = rt >= 0
+    row_w = np.zeros(rows, np.float32)
+    row_w[pr.reshape(-1)] = rw.numpy().reshape(-1)
+    assert np.array_equal(runner.row_weight.cpu().numpy()[:rows], row_w)
+    # 2 gather + quantise: bit-exact
+    xr = np.zeros((rows, dim), np.float32)
+    xr[live] = oracle.bf16_to_f32(u16(x))[rt[live]]
+    q, sf = oracle.quantize_nvfp4_rows(xr, weights.act_scale_in)
+    assert np.array_equal(runner.a1.cpu().numpy()[:rows], q)
+    a1_sf = unpack_sf(runner.a1_sf.cpu().numpy()[:groups], groups, dim // 256)
+    assert np.array_equal(a1_sf, sf)
+    # 3 grouped w1|w3 GEMM on the GPU's own quantised rows
+    h = u16(runner.h)[:rows]
+    for gi, e in enumerate(ge):
+        sl = slice(gi * 16, gi * 16 + 16)
+        ref = oracle.gemm_nvfp4(q[sl], sf[sl], weights.act_scale_in, weights.host["w13"][e], weights.raw_scales["w13"][e],
+                                weights.host["w13_gs"][e])
+        close_bf16(h[sl], ref)
+    # 4 SwiGLU + routing weight + quantise, from the GPU's h
+    act = oracle.moe_swiglu(h, row_w, limit)
+    act[~live] = 0
+    q2, sf2 = oracle.quantize_nvfp4_rows(oracle.bf16_to_f32(act), weights.act_scale_mid)
+    a2 = runner.a2.cpu().numpy()[:rows]
+    a2_sf = unpack_sf(runner.a2_sf.cpu().numpy()[:groups], groups, inter // 256)
+    assert np.mean(a2 == q2) >= 0.995 and np.mean(a2_sf == sf2) >= 0.995     # expf differs in the last bit
+    # 5 grouped w2 GEMM on the GPU's own a2
+    out = u16(runner.out)[:rows]
+    for gi, e in enumerate(ge):
+        sl = slice(gi * 16, gi * 16 + 16)
+        ref = oracle.gemm_nvfp4(a2[sl], a2_sf[sl], weights.act_scale_mid, weights.host["w2"][e],
+                                weights.raw_scales["w2"][e], weights.host["w2_gs"][e])
+        close_bf16(out[sl], ref)
+    # 6 combine: exact, pairs in slot order, then the shared expert's row
+    of = oracle.bf16_to_f32(out)
+    acc = np.zeros((tokens, dim), np.float32)
+    for j in range(k):
+        acc = (acc + of[pr[:, j]]).astype(np.float32)
+    acc = (acc + oracle.bf16_to_f32(u16(shared))).astype(np.float32)
+    assert np.array_equal(u16(y), oracle.f32_to_bf16(acc))
+
+
+def test_end_to_end_against_a_float_reference(wuda):
+    """The whole block against an fp32 evaluation of the origin's formula on the dequantised weights:
+    NVFP4 on both operands leaves a few per cent of error, no more."""
+    g = torch.Generator().manual_seed(5)
+    tokens, experts, k, dim, inter = 32, 8, 2, 512, 256
+    w1 = torch.randn(experts, inter, dim, generator=g) * 0.05
+    w3 = torch.randn(experts, inter, dim, generator=g) * 0.05
+    w2 = torch.randn(experts, dim, inter, generator=g) * 0.05
+    weights = moe.RoutedExperts(w1, w3, w2, act_scale_in=4.5 / (448 * 6), act_scale_mid=2.0 / (448 * 6))
+    runner = moe.MoERunner(weights, tokens, k)
+    x = torch.randn(tokens, dim, generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(tokens)]).int()
+    rw = torch.rand(tokens, k, generator=g) + 0.1
+    y = runner.forward(x.cuda(), rw.cuda(), idx.cuda()).float().cpu()
+    ref = torch.zeros(tokens, dim)
+    for t in range(tokens):
+        for j in range(k):
+            e = int(idx[t, j])
+            hgate, hup = w1[e] @ x[t].float(), w3[e] @ x[t].float()
+            ref[t] += w2[e] @ (rw[t, j] * torch.nn.functional.silu(hgate) * hup)
+    err = (y - ref).norm() / ref.norm()
+    assert err < 0.15, float(err)
+
+
+def test_rejects_bad_arguments(wuda):
+    from wuda_b200._lib import check
+    with pytest.raises(wuda.WudaError, match="max_groups"):
+        z = torch.zeros(64, dtype=torch.int32, device="cuda")
+        check(wuda.lib.wuda_moe_dispatch(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(),
+                                         z.data_ptr(), 8, 2, 4, 1, None, None))
+    assert wuda.lib.wuda_moe_max_groups(64, 8, 256) == 288 and wuda.lib.wuda_moe_max_groups(1, 2, 256) == 2

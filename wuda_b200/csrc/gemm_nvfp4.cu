@@ -52,6 +52,12 @@ struct Params {
     int M, N, kb;              // kb = K / 256
     int n_tiles;
     int stages;
+    // grouped form (routed experts): row group g (16 activation rows) belongs to expert
+    // group_expert[g]; flat tile T = g * n_tiles + tile of the expert's N rows.  The number of groups
+    // is read on the device, so nothing is synchronised with the host between routing and the GEMM.
+    const int32_t* group_expert = nullptr;   // [num_groups]
+    const int32_t* num_groups = nullptr;     // [1]
+    const float* expert_scale = nullptr;     // [experts] per-expert weight tensor scale (times out_scale)
 };
 
 template <int M_PAD>
@@ -141,7 +147,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const long long units = static_cast<long long>(p.n_tiles) * p.kb;
+    const bool grouped = p.group_expert != nullptr;
+    const int groups = grouped ? *p.num_groups : 1;
+    const long long units = static_cast<long long>(groups) * p.n_tiles * p.kb;
     const long long u0 = range_begin(units, blockIdx.x, gridDim.x);
     const long long u1 = range_begin(units, blockIdx.x + 1, gridDim.x);
     const int count = static_cast<int>(u1 - u0);
@@ -165,23 +173,26 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             const uint32_t stage = base + s * L::kStageBytes;
             uint32_t dst = stage;
             const void* map = &w_map;
-            int c0 = kb * kRowBytes, c1 = tile * kTileN;
+            // grouped: `tile` is the flat index; the weight tile is the expert's, the activations the group's
+            const int grp = grouped ? tile / p.n_tiles : 0;
+            const int wtile = grouped ? __ldg(p.group_expert + grp) * p.n_tiles + (tile - grp * p.n_tiles) : tile;
+            int c0 = kb * kRowBytes, c1 = wtile * kTileN;
             uint64_t policy = stream_policy;
             if (lane == 1) {
                 dst = stage + kWBytes;
                 map = &a_map;
-                c1 = 0;
+                c1 = grp * M_PAD;
                 policy = keep_policy;
             } else if (lane == 2) {
                 dst = stage + kWBytes + L::kABytes;
                 map = &wsf_map;
                 c0 = 0;
-                c1 = (tile * p.kb + kb) * 4;
+                c1 = (wtile * p.kb + kb) * 4;
             } else if (lane == 3) {
                 dst = stage + kWBytes + L::kABytes + kSfBytes;
                 map = &asf_map;
                 c0 = 0;
-                c1 = kb * 4;
+                c1 = (grp * p.kb + kb) * 4;
                 policy = keep_policy;
             }
             if (lane < 4) tma_load_2d_hint(dst, map, full + s * 8, c0, c1, policy);
@@ -290,7 +301,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_tm);
 
-            const int nrow = tile * kTileN + et;
+            const int grp = grouped ? tile / p.n_tiles : 0;
+            const int nrow = (tile - grp * p.n_tiles) * kTileN + et;
             if (!from_zero) {
                 float* slot = p.scratch + static_cast<int64_t>(blockIdx.x) * (M_PAD * kTileN) + et;
                 if (alive) {
@@ -332,9 +344,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                         for (int c = blockIdx.x + 1 + et; c <= last; c += 32 * kEpiWarps) p.flags[c] = 0;
                 }
                 if (alive && nrow < p.N) {
+                    const float scale = grouped ? p.out_scale * __ldg(p.expert_scale + __ldg(p.group_expert + grp)) : p.out_scale;
+                    __nv_bfloat16* c = p.c + static_cast<int64_t>(grp) * M_PAD * p.N;
 #pragma unroll
                     for (int i = 0; i < M_PAD; ++i)
-                        if (i < p.M) p.c[static_cast<int64_t>(i) * p.N + nrow] = __float2bfloat16_rn(acc[i] * p.out_scale);
+                        if (i < p.M) c[static_cast<int64_t>(i) * p.N + nrow] = __float2bfloat16_rn(acc[i] * scale);
                 }
             }
             n += seg_len;
@@ -368,7 +382,8 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, const CUte
     auto kernel = gemm_nvfp4_kernel<M_PAD>;
     WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total(stages)));
     const long long units = static_cast<long long>(p.n_tiles) * p.kb;
-    const int grid = units < dev.num_sms ? static_cast<int>(units) : dev.num_sms;
+    // (grouped: the number of groups is only known on the device; one CTA per SM, idle ones return at once)
+    const int grid = (!p.group_expert && units < dev.num_sms) ? static_cast<int>(units) : dev.num_sms;
     kernel<<<grid, kThreads, L::total(stages), stream>>>(w_map, a_map, wsf_map, asf_map, p);
     WUDA_CUDA(cudaGetLastError());
     return WUDA_OK;
@@ -463,4 +478,83 @@ extern "C" int wuda_gemm_nvfp4(const void* a, const void* a_sf_packed, float a_g
         case 64: return launch<64>(w_map, a_map, wsf_map, asf_map, p, dev, s);
         default: return launch<128>(w_map, a_map, wsf_map, asf_map, p, dev, s);
     }
+}
+
+// Grouped form for the routed experts: activations [max_groups * 16, k] quantised per group (see
+// moe.cu), expert weights stacked [experts * n, k / 2] with their packed scales stacked per expert.
+extern "C" int wuda_gemm_nvfp4_grouped(const void* a, const void* a_sf_packed, float a_global_scale, const void* w,
+                                       const void* w_sf_packed, const float* w_global_scales,
+                                       const int32_t* group_expert, const int32_t* num_groups, void* c_bf16,
+                                       int max_groups, int experts, int n, int k, void* scratch, int64_t scratch_bytes,
+                                       int32_t* status_word, void* stream) {
+    using namespace wuda;
+    using namespace wuda::gemm4;
+    clear_error();
+    WUDA_REQUIRE(max_groups >= 1 && experts >= 1, "max_groups and experts must be >= 1");
+    WUDA_REQUIRE(n >= 128 && n % 128 == 0, "n (rows per expert) must be a positive multiple of 128 (got %d)", n);
+    WUDA_REQUIRE(k >= 256 && k % 256 == 0, "k must be a positive multiple of 256 (got %d)", k);
+    WUDA_REQUIRE(a && a_sf_packed && w && w_sf_packed && w_global_scales && group_expert && num_groups && c_bf16 && scratch,
+                 "no array may be NULL");
+    WUDA_REQUIRE(aligned16(a) && aligned16(w) && aligned16(a_sf_packed) && aligned16(w_sf_packed),
+                 "operands and packed scales must be 16-byte aligned");
+    WUDA_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "scratch must be 256-byte aligned");
+    const int64_t need = wuda_gemm_nvfp4_scratch_bytes(16, n);
+    WUDA_REQUIRE(scratch_bytes >= need, "scratch holds %lld bytes; %lld are needed (wuda_gemm_nvfp4_scratch_bytes(16, n))",
+                 static_cast<long long>(scratch_bytes), static_cast<long long>(need));
+    DeviceInfo dev;
+    int st = current_device_info(&dev);
+    if (st != WUDA_OK) return st;
+    WUDA_REQUIRE(dev.num_sms <= kMaxGrid, "device has %d SMs; at most %d are supported", dev.num_sms, kMaxGrid);
+
+    constexpr int m_pad = 16;
+    Params p;
+    p.c = static_cast<__nv_bfloat16*>(c_bf16);
+    p.status = status_word;
+    p.out_scale = a_global_scale;
+    p.M = m_pad;
+    p.N = n;
+    p.kb = k / 256;
+    p.n_tiles = n / 128;
+    p.scratch = static_cast<float*>(scratch);
+    p.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
+    p.stages = 0;
+    p.group_expert = group_expert;
+    p.num_groups = num_groups;
+    p.expert_scale = w_global_scales;
+
+    CUtensorMap w_map, a_map, wsf_map, asf_map;
+    const uint64_t row_bytes = static_cast<uint64_t>(k) / 2;
+    {
+        const uint64_t dims[2] = {row_bytes, static_cast<uint64_t>(experts) * n};
+        const uint64_t strides[1] = {row_bytes};
+        const uint32_t box[2] = {128u, 128u};
+        st = encode_tensor_map(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (st != WUDA_OK) return st;
+    }
+    {
+        const uint64_t dims[2] = {row_bytes, static_cast<uint64_t>(max_groups) * m_pad};
+        const uint64_t strides[1] = {row_bytes};
+        const uint32_t box[2] = {128u, static_cast<uint32_t>(m_pad)};
+        st = encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+        if (st != WUDA_OK) return st;
+    }
+    {
+        const uint64_t dims[2] = {128ull, static_cast<uint64_t>(experts) * p.n_tiles * p.kb * 4};
+        const uint64_t strides[1] = {512ull};
+        const uint32_t box[2] = {128u, 4u};
+        st = encode_tensor_map(&wsf_map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, w_sf_packed, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+        if (st != WUDA_OK) return st;
+    }
+    {
+        const uint64_t dims[2] = {128ull, static_cast<uint64_t>(max_groups) * p.kb * 4};
+        const uint64_t strides[1] = {512ull};
+        const uint32_t box[2] = {128u, 4u};
+        st = encode_tensor_map(&asf_map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a_sf_packed, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+        if (st != WUDA_OK) return st;
+    }
+    return launch<16>(w_map, a_map, wsf_map, asf_map, p, dev, static_cast<cudaStream_t>(stream));
 }

@@ -1,0 +1,368 @@
+// The pieces of the routed-expert block around its two grouped NVFP4 GEMMs
+// (dsv4_megakernel/origin/model.py:587-644, MoE.forward and Expert.forward):
+//   dispatch      (token, expert) pairs -> rows sorted by expert, every expert's rows padded to
+//                 groups of 16 (one GEMM row tile), stable in token order
+//   gather_quant  row r = activation of its token -> NVFP4 (e2m1 + one ue4m3 scale per 16 values +
+//                 a given per-tensor scale), scales written in the layout the tensor core reads
+//   swiglu_quant  h = silu(min(gate, L)) * clamp(up, +-L) * routing weight, rounded to bf16, -> NVFP4
+//   combine       y[t] = bf16( sum_j out[row(t, j)] (+ shared[t]) ), pairs added in slot order
+// Everything is deterministic: no floating-point atomics, fixed summation orders.
+//
+// NVFP4 quantisation of a block of 16 values with tensor scale gs:
+//   sf  = e4m3(min(amax / 6 / gs, 448))  (round to nearest even);  d = decoded sf
+//   q_i = e2m1(x_i / (d * gs)), nearest value of {0, .5, 1, 1.5, 2, 3, 4, 6}, ties to the smaller
+//         magnitude, saturating at 6; an all-zero block has sf = 0 and q = 0
+// Two values per byte, low nibble first.  Scale bytes of group g (16 rows), K block kb (256 values):
+//   ((g * K/256 + kb) * 2048) + step * 512 + row * 16 + byte,  step = (k / 64) % 4, byte = (k / 16) % 4
+// which is rows 0..15 of the 128-row image tcgen05.cp.32x128b.warpx4 copies (rows 16..127 stay zero).
+#include <cuda_bf16.h>
+
+#include "host.h"
+
+namespace wuda {
+namespace moe {
+
+constexpr int kGroupRows = 16;
+
+// ---------------------------------------------------------------- dispatch (one CTA)
+struct DispatchParams {
+    const int32_t* indices;   // [tokens, k]
+    const float* weights;     // [tokens, k]
+    int32_t* group_expert;    // [max_groups]
+    int32_t* num_groups;      // [1]
+    int32_t* row_token;       // [max_groups * 16]
+    float* row_weight;        // [max_groups * 16]
+    int32_t* pair_row;        // [tokens, k]
+    int tokens, k, experts, max_groups;
+    int32_t* status;
+};
+
+constexpr int kDispatchThreads = 1024;
+constexpr int kMaxExperts = 512;
+
+__global__ void __launch_bounds__(kDispatchThreads) moe_dispatch_kernel(DispatchParams p) {
+    __shared__ int count[kMaxExperts];
+    __shared__ int base[kMaxExperts];       // first group of the expert
+    __shared__ int total_groups;
+    const int pairs = p.tokens * p.k;
+    for (int e = threadIdx.x; e < p.experts; e += kDispatchThreads) count[e] = 0;
+    for (int r = threadIdx.x; r < p.max_groups * kGroupRows; r += kDispatchThreads) {
+        p.row_token[r] = -1;
+        p.row_weight[r] = 0.f;
+    }
+    for (int g = threadIdx.x; g < p.max_groups; g += kDispatchThreads) p.group_expert[g] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += kDispatchThreads) {
+        const int e = p.indices[i];
+        if (e >= 0 && e < p.experts) atomicAdd(&count[e], 1);
+        else if (p.status) atomicCAS(p.status, 0, WUDA_DEV_BAD_EXPERT);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {                 // experts <= 512: a serial scan is a few hundred steps
+        int g = 0;
+        for (int e = 0; e < p.experts; ++e) {
+            base[e] = g;
+            g += (count[e] + kGroupRows - 1) / kGroupRows;
+        }
+        total_groups = g;
+        *p.num_groups = g <= p.max_groups ? g : 0;
+        if (g > p.max_groups && p.status) atomicCAS(p.status, 0, WUDA_DEV_BAD_DESTINATION);
+    }
+    __syncthreads();
+    if (total_groups > p.max_groups) return;
+    for (int e = threadIdx.x; e < p.experts; e += kDispatchThreads) {
+        const int groups = (count[e] + kGroupRows - 1) / kGroupRows;
+        for (int g = 0; g < groups; ++g) p.group_expert[base[e] + g] = e;
+    }
+    // stable placement: the rank of a pair among the earlier pairs of the same expert
+    for (int i = threadIdx.x; i < pairs; i += kDispatchThreads) {
+        const int e = p.indices[i];
+        if (e < 0 || e >= p.experts) {
+            p.pair_row[i] = -1;
+            continue;
+        }
+        int rank = 0;
+        for (int j = 0; j < i; ++j) rank += (p.indices[j] == e);
+        const int row = base[e] * kGroupRows + rank;
+        p.pair_row[i] = row;
+        p.row_token[row] = i / p.k;
+        p.row_weight[row] = p.weights[i];
+    }
+}
+
+// ---------------------------------------------------------------- NVFP4 quantisation of 16 values
+__device__ __forceinline__ uint32_t e2m1_code(float x) {
+    const float a = fminf(fabsf(x), 6.0f);
+    // bucket boundaries are the midpoints; a value on a boundary takes the smaller magnitude
+    uint32_t idx = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+    return idx | ((x < 0.f && idx != 0) ? 8u : 0u);
+}
+
+__device__ __forceinline__ float e4m3_decode(uint32_t b) {
+    const uint32_t e = (b >> 3) & 15u, m = b & 7u;
+    return e == 0 ? static_cast<float>(m) * 0.001953125f : __uint_as_float(((e + 120u) << 23) | (m << 20));
+}
+
+// v: 16 values.  Returns the 8 packed bytes (as two words) and the scale byte.
+__device__ __forceinline__ void quant16(const float (&v)[16], float gs, uint32_t (&packed)[2], uint32_t* sf_byte) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const float want = fminf(__fdiv_rn(__fdiv_rn(amax, 6.0f), gs), 448.0f);
+    uint16_t pair;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.f), "f"(want));
+    const uint32_t sf = pair & 0xffu;
+    const float d = e4m3_decode(sf);
+    const float denom = __fmul_rn(d, gs);
+    packed[0] = packed[1] = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t code = d > 0.f ? e2m1_code(__fdiv_rn(v[i], denom)) : 0u;
+        packed[i >> 3] |= code << (4 * (i & 7));
+    }
+    *sf_byte = sf;
+}
+
+__device__ __forceinline__ int64_t sf_offset(int row, int k16, int kb_per_row) {
+    // k16 = index of the 16-value block along K
+    const int group = row / kGroupRows, r = row % kGroupRows;
+    const int kb = k16 >> 4, within = k16 & 15;
+    return (static_cast<int64_t>(group) * kb_per_row + kb) * 2048 + (within >> 2) * 512 + r * 16 + (within & 3);
+}
+
+// ---------------------------------------------------------------- gather + quantise
+struct GatherParams {
+    const __nv_bfloat16* x;      // [tokens, K]
+    const int32_t* row_token;
+    const int32_t* num_groups;
+    uint8_t* a4;                 // [rows, K / 2]
+    uint8_t* a_sf;               // packed scales
+    float gs;
+    int K;
+};
+
+__global__ void __launch_bounds__(256) moe_gather_quant_kernel(GatherParams p) {
+    const int row = blockIdx.x;
+    if (row >= *p.num_groups * kGroupRows) return;
+    const int tok = p.row_token[row];
+    const int blocks = p.K / 16;
+    for (int b = threadIdx.x; b < blocks; b += blockDim.x) {
+        uint32_t packed[2] = {0u, 0u}, sf = 0u;
+        if (tok >= 0) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(tok) * p.K + b * 16);
+            const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+            const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            }
+            quant16(v, p.gs, packed, &sf);
+        }
+        *reinterpret_cast<uint2*>(p.a4 + static_cast<int64_t>(row) * (p.K / 2) + b * 8) = make_uint2(packed[0], packed[1]);
+        p.a_sf[sf_offset(row, b, p.K / 256)] = static_cast<uint8_t>(sf);
+    }
+}
+
+// ---------------------------------------------------------------- SwiGLU + routing weight + quantise
+struct SwigluParams {
+    const __nv_bfloat16* h;      // [rows, 2 * I]: gate | up
+    const int32_t* row_token;
+    const float* row_weight;
+    const int32_t* num_groups;
+    uint8_t* a4;                 // [rows, I / 2]
+    uint8_t* a_sf;
+    float gs, limit;
+    int I;
+};
+
+__global__ void __launch_bounds__(128) moe_swiglu_quant_kernel(SwigluParams p) {
+    const int row = blockIdx.x;
+    if (row >= *p.num_groups * kGroupRows) return;
+    const bool live = p.row_token[row] >= 0;
+    const float rw = p.row_weight[row];
+    const int blocks = p.I / 16;
+    for (int b = threadIdx.x; b < blocks; b += blockDim.x) {
+        uint32_t packed[2] = {0u, 0u}, sf = 0u;
+        if (live) {
+            const __nv_bfloat16* g = p.h + static_cast<int64_t>(row) * (2 * p.I) + b * 16;
+            const uint4 g0 = *reinterpret_cast<const uint4*>(g), g1 = *reinterpret_cast<const uint4*>(g + 8);
+            const uint4 u0 = *reinterpret_cast<const uint4*>(g + p.I), u1 = *reinterpret_cast<const uint4*>(g + p.I + 8);
+            const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            const uint32_t uw[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                float gate = __uint_as_float((i & 1) ? (gw[i >> 1] & 0xffff0000u) : (gw[i >> 1] << 16));
+                float up = __uint_as_float((i & 1) ? (uw[i >> 1] & 0xffff0000u) : (uw[i >> 1] << 16));
+                if (p.limit > 0.f) {
+                    up = fminf(fmaxf(up, -p.limit), p.limit);
+                    gate = fminf(gate, p.limit);
+                }
+                const float silu = __fdiv_rn(gate, 1.0f + expf(-gate));
+                v[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(rw, __fmul_rn(silu, up))));
+            }
+            quant16(v, p.gs, packed, &sf);
+        }
+        *reinterpret_cast<uint2*>(p.a4 + static_cast<int64_t>(row) * (p.I / 2) + b * 8) = make_uint2(packed[0], packed[1]);
+        p.a_sf[sf_offset(row, b, p.I / 256)] = static_cast<uint8_t>(sf);
+    }
+}
+
+// ---------------------------------------------------------------- combine
+struct CombineParams {
+    const __nv_bfloat16* out;    // [rows, dim]
+    const int32_t* pair_row;     // [tokens, k]
+    const __nv_bfloat16* shared; // [tokens, dim] or nullptr
+    __nv_bfloat16* y;            // [tokens, dim]
+    int k, dim;
+};
+
+__global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < p.dim / 8; c += blockDim.x) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < p.k; ++j) {
+            const int row = p.pair_row[t * p.k + j];
+            if (row < 0) continue;
+            const uint4 raw = *(reinterpret_cast<const uint4*>(p.out + static_cast<int64_t>(row) * p.dim) + c);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] = __fadd_rn(acc[2 * i], __uint_as_float(w[i] << 16));
+                acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
+            }
+        }
+        if (p.shared) {
+            const uint4 raw = *(reinterpret_cast<const uint4*>(p.shared + static_cast<int64_t>(t) * p.dim) + c);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] = __fadd_rn(acc[2 * i], __uint_as_float(w[i] << 16));
+                acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
+            }
+        }
+        uint4 o;
+        uint32_t* ow = &o.x;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+            ow[i] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        *(reinterpret_cast<uint4*>(p.y + static_cast<int64_t>(t) * p.dim) + c) = o;
+    }
+}
+
+}  // namespace moe
+}  // namespace wuda
+
+extern "C" int wuda_moe_max_groups(int tokens, int k, int experts) {
+    if (tokens < 1 || k < 1 || experts < 1) return -1;
+    // every expert can end in one partly filled group
+    const long long g = (static_cast<long long>(tokens) * k + 15) / 16 + experts;
+    const long long cap = static_cast<long long>(tokens) * k < experts ? static_cast<long long>(tokens) * k : g;
+    return static_cast<int>(cap < g ? cap : g);
+}
+
+extern "C" int wuda_moe_dispatch(const int32_t* indices, const float* weights, int32_t* group_expert, int32_t* num_groups,
+                                 int32_t* row_token, float* row_weight, int32_t* pair_row, int tokens, int k, int experts,
+                                 int max_groups, int32_t* status_word, void* stream) {
+    using namespace wuda;
+    using namespace wuda::moe;
+    clear_error();
+    WUDA_REQUIRE(tokens >= 1 && k >= 1, "tokens and k must be >= 1");
+    WUDA_REQUIRE(experts >= 1 && experts <= kMaxExperts, "experts must be in [1, %d] (got %d)", kMaxExperts, experts);
+    WUDA_REQUIRE(static_cast<long long>(tokens) * k <= 65536, "at most 65536 (token, expert) pairs per call");
+    WUDA_REQUIRE(max_groups >= wuda_moe_max_groups(tokens, k, experts),
+                 "max_groups must be at least wuda_moe_max_groups(tokens, k, experts) = %d (got %d)",
+                 wuda_moe_max_groups(tokens, k, experts), max_groups);
+    WUDA_REQUIRE(indices && weights && group_expert && num_groups && row_token && row_weight && pair_row,
+                 "no array may be NULL");
+    DispatchParams p;
+    p.indices = indices;
+    p.weights = weights;
+    p.group_expert = group_expert;
+    p.num_groups = num_groups;
+    p.row_token = row_token;
+    p.row_weight = row_weight;
+    p.pair_row = pair_row;
+    p.tokens = tokens;
+    p.k = k;
+    p.experts = experts;
+    p.max_groups = max_groups;
+    p.status = status_word;
+    moe_dispatch_kernel<<<1, kDispatchThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    WUDA_CUDA(cudaGetLastError());
+    return WUDA_OK;
+}
+
+extern "C" int wuda_moe_gather_quant_nvfp4(const void* x_bf16, const int32_t* row_token, const int32_t* num_groups,
+                                           void* a_fp4, void* a_sf_packed, float global_scale, int max_groups, int k,
+                                           void* stream) {
+    using namespace wuda;
+    using namespace wuda::moe;
+    clear_error();
+    WUDA_REQUIRE(max_groups >= 1, "max_groups must be >= 1");
+    WUDA_REQUIRE(k >= 256 && k % 256 == 0, "k must be a positive multiple of 256 (got %d)", k);
+    WUDA_REQUIRE(global_scale > 0.f, "global_scale must be positive");
+    WUDA_REQUIRE(x_bf16 && row_token && num_groups && a_fp4 && a_sf_packed, "no array may be NULL");
+    WUDA_REQUIRE(aligned16(x_bf16) && aligned16(a_fp4) && aligned16(a_sf_packed), "x, a_fp4 and a_sf must be 16-byte aligned");
+    GatherParams p;
+    p.x = static_cast<const __nv_bfloat16*>(x_bf16);
+    p.row_token = row_token;
+    p.num_groups = num_groups;
+    p.a4 = static_cast<uint8_t*>(a_fp4);
+    p.a_sf = static_cast<uint8_t*>(a_sf_packed);
+    p.gs = global_scale;
+    p.K = k;
+    moe_gather_quant_kernel<<<max_groups * kGroupRows, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    WUDA_CUDA(cudaGetLastError());
+    return WUDA_OK;
+}
+
+extern "C" int wuda_moe_swiglu_quant_nvfp4(const void* h_bf16, const int32_t* row_token, const float* row_weight,
+                                           const int32_t* num_groups, void* a_fp4, void* a_sf_packed, float global_scale,
+                                           float swiglu_limit, int max_groups, int inter, void* stream) {
+    using namespace wuda;
+    using namespace wuda::moe;
+    clear_error();
+    WUDA_REQUIRE(max_groups >= 1, "max_groups must be >= 1");
+    WUDA_REQUIRE(inter >= 256 && inter % 256 == 0, "inter must be a positive multiple of 256 (got %d)", inter);
+    WUDA_REQUIRE(global_scale > 0.f, "global_scale must be positive");
+    WUDA_REQUIRE(h_bf16 && row_token && row_weight && num_groups && a_fp4 && a_sf_packed, "no array may be NULL");
+    WUDA_REQUIRE(aligned16(h_bf16) && aligned16(a_fp4) && aligned16(a_sf_packed), "h, a_fp4 and a_sf must be 16-byte aligned");
+    SwigluParams p;
+    p.h = static_cast<const __nv_bfloat16*>(h_bf16);
+    p.row_token = row_token;
+    p.row_weight = row_weight;
+    p.num_groups = num_groups;
+    p.a4 = static_cast<uint8_t*>(a_fp4);
+    p.a_sf = static_cast<uint8_t*>(a_sf_packed);
+    p.gs = global_scale;
+    p.limit = swiglu_limit;
+    p.I = inter;
+    moe_swiglu_quant_kernel<<<max_groups * kGroupRows, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    WUDA_CUDA(cudaGetLastError());
+    return WUDA_OK;
+}
+
+extern "C" int wuda_moe_combine(const void* expert_out_bf16, const int32_t* pair_row, const void* shared_bf16,
+                                void* y_bf16, int tokens, int k, int dim, void* stream) {
+    using namespace wuda;
+    using namespace wuda::moe;
+    clear_error();
+    WUDA_REQUIRE(tokens >= 1 && k >= 1 && dim >= 8 && dim % 8 == 0, "tokens, k >= 1 and dim a positive multiple of 8");
+    WUDA_REQUIRE(expert_out_bf16 && pair_row && y_bf16, "expert_out, pair_row and y must not be NULL");
+    WUDA_REQUIRE(aligned16(expert_out_bf16) && aligned16(shared_bf16) && aligned16(y_bf16), "rows must be 16-byte aligned");
+    CombineParams p;
+    p.out = static_cast<const __nv_bfloat16*>(expert_out_bf16);
+    p.pair_row = pair_row;
+    p.shared = static_cast<const __nv_bfloat16*>(shared_bf16);
+    p.y = static_cast<__nv_bfloat16*>(y_bf16);
+    p.k = k;
+    p.dim = dim;
+    moe_combine_kernel<<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    WUDA_CUDA(cudaGetLastError());
+    return WUDA_OK;
+}

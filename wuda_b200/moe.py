@@ -1,0 +1,84 @@
+"""Host-side driver of the routed experts of the MoE block (the origin's MoE / Expert modules,
+dsv4_megakernel/origin/model.py:587-644): routing -> dispatch -> NVFP4 quantisation of the gathered
+rows -> grouped w1|w3 GEMM -> SwiGLU + quantisation -> grouped w2 GEMM -> combine.  Every buffer is
+allocated once; a forward pass is eight launches with no host synchronisation in between (the number
+of row groups stays on the device), so it can be captured into a CUDA graph.
+"""
+import numpy as np
+import torch
+
+from . import ops, workloads
+from ._lib import check, lib
+
+
+class RoutedExperts:
+    """NVFP4 weights of `experts` SwiGLU experts: w13 = [w1; w3] stacked ([2*inter, dim]) and w2
+    ([dim, inter]) per expert, quantised here from fp32/bf16 tensors (set-up, not the hot path)."""
+
+    def __init__(self, w1, w3, w2, act_scale_in, act_scale_mid, swiglu_limit=0.0, device="cuda"):
+        experts, inter, dim = w1.shape
+        if w3.shape != w1.shape or tuple(w2.shape) != (experts, dim, inter) or dim % 256 or inter % 256:
+            raise ValueError("w1, w3 must be [E, inter, dim], w2 [E, dim, inter], dims multiples of 256")
+        self.experts, self.inter, self.dim = experts, inter, dim
+        self.act_scale_in, self.act_scale_mid, self.swiglu_limit = float(act_scale_in), float(act_scale_mid), float(swiglu_limit)
+        q13, s13, g13, q2, s2, g2, raw13, raw2 = [], [], [], [], [], [], [], []
+        for e in range(experts):
+            q, sf, gs = workloads.quantize_nvfp4(torch.cat([w1[e], w3[e]]).float())
+            q13.append(q), s13.append(workloads.pack_nvfp4_scales(sf)), g13.append(gs), raw13.append(sf)
+            q, sf, gs = workloads.quantize_nvfp4(w2[e].float())
+            q2.append(q), s2.append(workloads.pack_nvfp4_scales(sf)), g2.append(gs), raw2.append(sf)
+        self.host = dict(w13=np.stack(q13), w13_sf=np.stack(s13), w13_gs=np.array(g13, np.float32), w2=np.stack(q2),
+                         w2_sf=np.stack(s2), w2_gs=np.array(g2, np.float32))
+        self.raw_scales = dict(w13=raw13, w2=raw2)          # unpacked scale bytes, kept for checks on the host
+        self.dev = {k: torch.from_numpy(v).to(device) for k, v in self.host.items()}
+
+
+class MoERunner:
+    def __init__(self, weights, max_tokens, topk, device="cuda"):
+        self.w, self.max_tokens, self.topk = weights, max_tokens, topk
+        self.max_groups = lib.wuda_moe_max_groups(max_tokens, topk, weights.experts)
+        rows = self.max_groups * 16
+        dev = device
+        z = lambda *s, dtype=torch.uint8: torch.zeros(*s, dtype=dtype, device=dev)
+        self.group_expert, self.num_groups = z(self.max_groups, dtype=torch.int32), z(1, dtype=torch.int32)
+        self.row_token, self.row_weight = z(rows, dtype=torch.int32), z(rows, dtype=torch.float32)
+        self.pair_row = z(max_tokens, topk, dtype=torch.int32)
+        self.a1, self.a1_sf = z(rows, weights.dim // 2), z(self.max_groups, weights.dim // 256, 2048)
+        self.h = z(rows, 2 * weights.inter, dtype=torch.bfloat16)
+        self.a2, self.a2_sf = z(rows, weights.inter // 2), z(self.max_groups, weights.inter // 256, 2048)
+        self.out = z(rows, weights.dim, dtype=torch.bfloat16)
+        need = max(lib.wuda_gemm_nvfp4_scratch_bytes(16, 2 * weights.inter), lib.wuda_gemm_nvfp4_scratch_bytes(16, weights.dim))
+        self.scratch = z(need)
+        self.status = z(1, dtype=torch.int32)
+
+    def forward(self, x, weights, indices, shared=None, y=None):
+        """x bf16 [M, dim]; routing weights fp32 [M, k] and indices int32 [M, k] (ops.moe_gate);
+        shared bf16 [M, dim] or None.  Returns y bf16 [M, dim]."""
+        w, m = self.w, x.size(0)
+        if m > self.max_tokens or indices.shape != (m, self.topk):
+            raise ValueError("batch does not fit this runner")
+        s = torch.cuda.current_stream().cuda_stream
+        st = self.status.data_ptr()
+        check(lib.wuda_moe_dispatch(indices.data_ptr(), weights.data_ptr(), self.group_expert.data_ptr(),
+                                    self.num_groups.data_ptr(), self.row_token.data_ptr(), self.row_weight.data_ptr(),
+                                    self.pair_row.data_ptr(), m, self.topk, w.experts, self.max_groups, st, s))
+        check(lib.wuda_moe_gather_quant_nvfp4(x.data_ptr(), self.row_token.data_ptr(), self.num_groups.data_ptr(),
+                                              self.a1.data_ptr(), self.a1_sf.data_ptr(), w.act_scale_in, self.max_groups,
+                                              w.dim, s))
+        d = w.dev
+        check(lib.wuda_gemm_nvfp4_grouped(self.a1.data_ptr(), self.a1_sf.data_ptr(), w.act_scale_in, d["w13"].data_ptr(),
+                                          d["w13_sf"].data_ptr(), d["w13_gs"].data_ptr(), self.group_expert.data_ptr(),
+                                          self.num_groups.data_ptr(), self.h.data_ptr(), self.max_groups, w.experts,
+                                          2 * w.inter, w.dim, self.scratch.data_ptr(), self.scratch.numel(), st, s))
+        check(lib.wuda_moe_swiglu_quant_nvfp4(self.h.data_ptr(), self.row_token.data_ptr(), self.row_weight.data_ptr(),
+                                              self.num_groups.data_ptr(), self.a2.data_ptr(), self.a2_sf.data_ptr(),
+                                              w.act_scale_mid, w.swiglu_limit, self.max_groups, w.inter, s))
+        check(lib.wuda_gemm_nvfp4_grouped(self.a2.data_ptr(), self.a2_sf.data_ptr(), w.act_scale_mid, d["w2"].data_ptr(),
+                                          d["w2_sf"].data_ptr(), d["w2_gs"].data_ptr(), self.group_expert.data_ptr(),
+                                          self.num_groups.data_ptr(), self.out.data_ptr(), self.max_groups, w.experts,
+                                          w.dim, w.inter, self.scratch.data_ptr(), self.scratch.numel(), st, s))
+        if y is None:
+            y = torch.empty(m, w.dim, dtype=torch.bfloat16, device=x.device)
+        check(lib.wuda_moe_combine(self.out.data_ptr(), self.pair_row.data_ptr(), shared.data_ptr() if shared is not None else None,
+                                   y.data_ptr(), m, self.topk, w.dim, s))
+        return y
