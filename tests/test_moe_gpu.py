@@ -108,7 +108,7 @@ def test_end_to_end_against_a_float_reference(wuda):
     w1 = torch.randn(experts, inter, dim, generator=g) * 0.05
     w3 = torch.randn(experts, inter, dim, generator=g) * 0.05
     w2 = torch.randn(experts, dim, inter, generator=g) * 0.05
-    weights = moe.RoutedExperts(w1, w3, w2, act_scale_in=4.5 / (448 * 6), act_scale_mid=2.0 / (448 * 6))
+    weights = moe.RoutedExperts(w1, w3, w2, act_scale_in=5.0 / (448 * 6), act_scale_mid=24.0 / (448 * 6))
     runner = moe.MoERunner(weights, tokens, k)
     x = torch.randn(tokens, dim, generator=g).bfloat16()
     idx = torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(tokens)]).int()

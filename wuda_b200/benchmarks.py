@@ -10,6 +10,7 @@ because consecutive launches use different weight buffers that together exceed L
     python -m wuda_b200.benchmarks csa_chain_launches              (three eager steps, for an ncu launch list)
     python -m wuda_b200.benchmarks attention_half_layer            (every built stage of the half-layer, one graph)
     python -m wuda_b200.benchmarks attention_half_layer_launches   (three eager passes, for an ncu launch list)
+    python -m wuda_b200.benchmarks moe_experts                     (router + routed NVFP4 experts of one MoE block)
     python -m wuda_b200.benchmarks one gemm_fp8 64 24576 7168      (a few launches of one shape, for ncu)
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks tp2
 """
@@ -351,6 +352,42 @@ def attention_half_layer(batch=64, context=32768, topk=2048, reps=30, launches_o
           % (us, wbytes / 1e6, batch * (context // 4) * 132 / 1e6))
 
 
+def moe_experts(tokens=64, topk=8, experts=256, dim=7168, inter=2048, reps=10):
+    """Router + routed experts of one MoE block at the model's geometry (256 NVFP4 experts, top-8,
+    intermediate 2048): gate projection, routing, dispatch, gather-quantisation, grouped w1|w3 GEMM,
+    SwiGLU + quantisation, grouped w2 GEMM, combine - nine launches in one CUDA graph.  The weights of
+    the active experts (about 220 of 256 at batch 64) are far larger than L2, so no flush is needed."""
+    from wuda_b200 import moe
+    hbm, tf, kind = peaks()
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(3)
+    w = moe.RandomRoutedExperts(experts, inter, dim)
+    runner = moe.MoERunner(w, tokens, topk)
+    x = torch.randn(tokens, dim, generator=g, device=dev).bfloat16()
+    gate_w = (torch.randn(experts, dim, generator=g, device=dev) * 0.05).bfloat16()
+    bias = torch.zeros(experts, device=dev)
+    logits = torch.empty(tokens, experts, device=dev)
+    y = torch.empty(tokens, dim, dtype=torch.bfloat16, device=dev)
+
+    def step():
+        rw, idx = wuda.moe_gate(x, gate_w, bias, "sqrtsoftplus", 2.5, topk, logits=logits)
+        runner.forward(x, rw, idx, y=y)
+        return idx
+
+    idx = step()
+    torch.cuda.synchronize()
+    assert int(runner.status.item()) == 0
+    active = int(torch.unique(idx).numel())
+    groups = int(runner.num_groups.item())
+    us = time_graph(step, reps=reps, inner=1)
+    per_expert = 2 * inter * dim // 2 + 2 * inter * dim // 16 + dim * inter // 2 + dim * inter // 16
+    wbytes = active * per_expert
+    print("MoE router + routed experts: %d tokens x top-%d of %d experts (%d active, %d row groups)" %
+          (tokens, topk, experts, active, groups))
+    print("  %.1f us per block; %.2f GB of expert weights streamed -> %.0f GB/s = %.2f of %s HBM peak" %
+          (us, wbytes / 1e9, wbytes / us / 1e3, wbytes / us / 1e3 / hbm, kind))
+
+
 def one(kind, m, n, k, launches=5):
     """A few eager launches of one GEMM shape (profiler captures)."""
     t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
@@ -376,5 +413,5 @@ if __name__ == "__main__":
         sys.exit(0)
     {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2,
      "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
-     "attention_half_layer": attention_half_layer,
+     "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,
      "attention_half_layer_launches": lambda: attention_half_layer(launches_only=3)}[which]()

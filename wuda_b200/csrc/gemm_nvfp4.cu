@@ -150,8 +150,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     const bool grouped = p.group_expert != nullptr;
     const int groups = grouped ? *p.num_groups : 1;
     const long long units = static_cast<long long>(groups) * p.n_tiles * p.kb;
-    const long long u0 = range_begin(units, blockIdx.x, gridDim.x);
-    const long long u1 = range_begin(units, blockIdx.x + 1, gridDim.x);
+    // Only the first min(grid, units) CTAs take part (the grouped form is launched with one CTA per SM
+    // before the number of groups is known): every participating CTA then owns at least one unit, which
+    // the fix-up relies on when it waits for the CTAs that share a tile.
+    const int grid = units < static_cast<long long>(gridDim.x) ? static_cast<int>(units) : static_cast<int>(gridDim.x);
+    const bool taking_part = static_cast<int>(blockIdx.x) < grid;
+    const long long u0 = taking_part ? range_begin(units, blockIdx.x, grid) : 0;
+    const long long u1 = taking_part ? range_begin(units, blockIdx.x + 1, grid) : 0;
     const int count = static_cast<int>(u1 - u0);
 
     if (warp < kProducers) {
@@ -315,7 +320,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             } else {
                 if (!to_end) {
                     const long long t_end = static_cast<long long>(tile + 1) * p.kb - 1;
-                    const int last = cta_of(units, t_end, gridDim.x);
+                    const int last = cta_of(units, t_end, grid);
                     // every contributor's flag is awaited by a thread of its own, then the partials are added in
                     // CTA order (the loads of different partials overlap)
                     for (int c = blockIdx.x + 1 + et; c <= last && alive; c += 32 * kEpiWarps) {

@@ -33,6 +33,23 @@ class RoutedExperts:
         self.dev = {k: torch.from_numpy(v).to(device) for k, v in self.host.items()}
 
 
+class RandomRoutedExperts:
+    """Random NVFP4 expert weights created on the device (benchmarks): packed e2m1 codes, ue4m3 scale
+    bytes in a sane range, unit tensor scales.  Same attributes as RoutedExperts minus the host copies."""
+
+    def __init__(self, experts, inter, dim, act_scale_in=1.0 / 448, act_scale_mid=1.0 / 448, swiglu_limit=0.0,
+                 device="cuda", seed=1):
+        self.experts, self.inter, self.dim = experts, inter, dim
+        self.act_scale_in, self.act_scale_mid, self.swiglu_limit = act_scale_in, act_scale_mid, swiglu_limit
+        g = torch.Generator(device=device).manual_seed(seed)
+        rnd = lambda *s, hi=256: torch.randint(0, hi, s, generator=g, dtype=torch.uint8, device=device)
+        self.dev = dict(
+            w13=rnd(experts, 2 * inter, dim // 2), w13_sf=rnd(experts, (2 * inter // 128) * (dim // 256) * 2048, hi=0x30),
+            w13_gs=torch.full((experts,), 1e-3, device=device),
+            w2=rnd(experts, dim, inter // 2), w2_sf=rnd(experts, (dim // 128) * (inter // 256) * 2048, hi=0x30),
+            w2_gs=torch.full((experts,), 1e-3, device=device))
+
+
 class MoERunner:
     def __init__(self, weights, max_tokens, topk, device="cuda"):
         self.w, self.max_tokens, self.topk = weights, max_tokens, topk
