@@ -465,6 +465,15 @@ int wuda_mhc_post(const void* attention_out, const void* residual, const float* 
                   void* output, int m, int hidden, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * SwiGLU of a dense (shared) expert + 1x128 FP8 quantisation in one pass:
+ *   y = bf16(silu(min(gate, L)) * clamp(up, -L, L)),  h = [gate | up] bf16 [rows, 2*inter];  L = 0: no clamp
+ * Expert.forward of the origin (origin/model.py:596-606) between its w1|w3 and w2 projections,
+ * which are wuda_gemm_fp8_blockscaled calls.  Outputs as wuda_rmsnorm_quant_fp8; inter % 128 == 0.
+ */
+int wuda_swiglu_quant_fp8(const void* h_bf16, void* y_bf16, void* y_fp8, float* y_scales, int rows, int inter,
+                          float swiglu_limit, int scale_mode, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Block-scaled FP8 GEMM for decode-sized M:
  *
  *   c[m, n] = bf16( sum_kb a_s[m, kb] * w_s[n / 128, kb] * sum_{k in block kb} a[m, k] * w[n, k] )

@@ -131,3 +131,51 @@ def test_rejects_bad_arguments(wuda):
         check(wuda.lib.wuda_moe_dispatch(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(),
                                          z.data_ptr(), 8, 2, 4, 1, None, None))
     assert wuda.lib.wuda_moe_max_groups(64, 8, 256) == 288 and wuda.lib.wuda_moe_max_groups(1, 2, 256) == 2
+
+
+def test_shared_expert_and_block(wuda):
+    """Dense shared expert: SwiGLU + FP8 quantisation against numpy on the GPU's own projection, and the
+    whole block (router + routed + shared) against its parts."""
+    from wuda_b200 import workloads
+    from wuda_b200._lib import check
+    g = torch.Generator().manual_seed(21)
+    tokens, experts, k, dim, inter = 12, 8, 2, 512, 256
+    h = (torch.randn(tokens, 2 * inter, generator=g) * 3).bfloat16()
+    a8 = torch.empty(tokens, inter, dtype=torch.float8_e4m3fn, device="cuda")
+    a_s = torch.empty(tokens, inter // 128, device="cuda")
+    y16 = torch.empty(tokens, inter, dtype=torch.bfloat16, device="cuda")
+    hc = h.cuda()
+    check(wuda.lib.wuda_swiglu_quant_fp8(hc.data_ptr(), y16.data_ptr(), a8.data_ptr(), a_s.data_ptr(), tokens, inter, 5.0, 1, None))
+    torch.cuda.synchronize()
+    ref = oracle.moe_swiglu(u16(h), np.ones(tokens, np.float32), 5.0)
+    got = u16(y16)
+    assert np.mean(got == ref) >= 0.995 and np.abs(got.astype(np.int32) - ref.astype(np.int32)).max() <= 1
+    q, s = oracle.act_quant_fp8(got, 128, round_scale=True)          # exact on the GPU's own bf16 values
+    assert np.array_equal(a8.view(torch.uint8).cpu().numpy(), q) and np.array_equal(a_s.cpu().numpy(), s)
+
+    mk = lambda n, kk: workloads.quantize_fp8_128x128(torch.randn(n, kk, generator=g) * 0.05)
+    t8 = lambda a: torch.from_numpy(a).cuda().view(torch.float8_e4m3fn)
+    w13, w13s = mk(2 * inter, dim)
+    w2, w2s = mk(dim, inter)
+    shared = moe.SharedExpert(t8(w13), torch.from_numpy(w13s).cuda(), t8(w2), torch.from_numpy(w2s).cuda())
+    routed_w = moe.RoutedExperts(torch.randn(experts, inter, dim, generator=g) * 0.05, torch.randn(experts, inter, dim, generator=g) * 0.05,
+                                 torch.randn(experts, dim, inter, generator=g) * 0.05, 5.0 / 2688, 24.0 / 2688)
+    runner = moe.MoERunner(routed_w, tokens, k)
+    x = torch.randn(tokens, dim, generator=g).bfloat16().cuda()
+    gate_w = (torch.randn(experts, dim, generator=g) * 0.05).bfloat16().cuda()
+    y = moe.moe_block(x, gate_w, None, runner, shared, "sigmoid", 1.5)
+    rw, idx = wuda.moe_gate(x, gate_w, None, "sigmoid", 1.5, k)
+    sh = shared.forward(x)
+    y_parts = runner.forward(x, rw, idx, shared=sh)
+    y_routed = runner.forward(x, rw, idx)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y_parts)                                    # deterministic
+    assert torch.allclose(y.float(), y_routed.float() + sh.float(), rtol=2 ** -7, atol=1e-2)
+    # the shared expert against the FP8 oracle chain on its own activations
+    x8, xs = oracle.act_quant_fp8(u16(x), 128, round_scale=True)
+    hh = oracle.gemm_fp8_blockscaled(x8, xs, w13, w13s)
+    act = oracle.moe_swiglu(hh, np.ones(tokens, np.float32), 0.0)
+    q2, s2 = oracle.act_quant_fp8(act, 128, round_scale=True)
+    ref_sh = oracle.bf16_to_f32(oracle.gemm_fp8_blockscaled(q2, s2, w2, w2s))
+    got_sh = sh.float().cpu().numpy()
+    assert np.all(np.abs(got_sh - ref_sh) <= 3e-2 * np.abs(ref_sh) + 1e-2 * np.abs(ref_sh).max())

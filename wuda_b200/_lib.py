@@ -106,6 +106,7 @@ SIGNATURES = {
                                         c_int, c_vp, c_i64, c_vp, c_vp]),
     "wuda_moe_swiglu_quant_nvfp4": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_float, c_int, c_int, c_vp]),
     "wuda_moe_combine": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp]),
+    "wuda_swiglu_quant_fp8": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_float, c_int, c_vp]),
     "wuda_mhc_post": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
     "wuda_gemm_fp8_scratch_bytes": (c_i64, [c_int, c_int]),
     "wuda_gemm_fp8_blockscaled": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),

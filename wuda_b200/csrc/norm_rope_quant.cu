@@ -202,6 +202,43 @@ __global__ void __launch_bounds__(1024, 1) rope_quant_kernel(const RopeParams p)
     }
 }
 
+struct SwigluParams {
+    const __nv_bfloat16* h;   // [rows, 2 * inter]: gate | up
+    __nv_bfloat16* y_bf16;    // nullable
+    uint8_t* y_fp8;           // nullable
+    float* y_scales;
+    int rows, inter, pow2;
+    float limit;
+};
+
+// SwiGLU of a dense expert: y = bf16(silu(min(gate, L)) * clamp(up, +-L)), then 1x128 FP8 quantisation
+// (dsv4_megakernel/origin/model.py:596-606; L = 0 disables the clamps).
+__global__ void __launch_bounds__(1024, 1) swiglu_quant_kernel(const SwigluParams p) {
+    const int r = blockIdx.x;
+    const int chunks = p.inter >> 3;
+    const __nv_bfloat16* g = p.h + static_cast<int64_t>(r) * (2 * p.inter);
+    for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < chunks; ch += blockDim.x * gridDim.y) {
+        float gate[8], up[8], v[8];
+        unpack8(*reinterpret_cast<const uint4*>(g + 8 * ch), gate);
+        unpack8(*reinterpret_cast<const uint4*>(g + p.inter + 8 * ch), up);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float a = gate[i], b = up[i];
+            if (p.limit > 0.f) {
+                b = fminf(fmaxf(b, -p.limit), p.limit);
+                a = fminf(a, p.limit);
+            }
+            v[i] = bf16_round(__fmul_rn(__fdiv_rn(a, 1.0f + expf(-a)), b));
+        }
+        const int64_t o = static_cast<int64_t>(r) * p.inter + 8 * ch;
+        if (p.y_bf16) *reinterpret_cast<uint4*>(p.y_bf16 + o) = pack8(v);
+        if (p.y_fp8)
+            quant_store8(v, p.pow2, p.y_fp8 + o,
+                         p.y_scales ? p.y_scales + static_cast<int64_t>(r) * (p.inter >> 7) + (ch >> 4) : nullptr,
+                         (ch & 15) == 0);
+    }
+}
+
 }  // namespace nrq
 }  // namespace wuda
 
@@ -284,6 +321,37 @@ extern "C" int wuda_rope_quant_fp8(const void* x_bf16, const int64_t* positions,
     const int passes = (chunks + threads - 1) / threads;
     while (splits < passes && tokens * splits < 296) splits *= 2;
     rope_quant_kernel<<<dim3(tokens, splits), threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    WUDA_CUDA(cudaGetLastError());
+    return WUDA_OK;
+}
+
+extern "C" int wuda_swiglu_quant_fp8(const void* h_bf16, void* y_bf16, void* y_fp8, float* y_scales, int rows, int inter,
+                                     float swiglu_limit, int scale_mode, void* stream) {
+    using namespace wuda;
+    using namespace wuda::nrq;
+    clear_error();
+    WUDA_REQUIRE(rows >= 0, "rows must be >= 0 (got %d)", rows);
+    WUDA_REQUIRE(inter >= 128 && inter % 128 == 0, "inter must be a positive multiple of 128 (got %d)", inter);
+    WUDA_REQUIRE(scale_mode == 0 || scale_mode == 1, "scale_mode must be 0 (amax/448) or 1 (power of two)");
+    if (rows == 0) return WUDA_OK;
+    WUDA_REQUIRE(h_bf16 && (y_bf16 || y_fp8), "h and at least one output must not be NULL");
+    WUDA_REQUIRE(!y_fp8 || y_scales, "y_scales is required with y_fp8");
+    WUDA_REQUIRE(aligned16(h_bf16) && aligned16(y_bf16) && aligned16(y_fp8), "h and the outputs must be 16-byte aligned");
+    SwigluParams p;
+    p.h = static_cast<const __nv_bfloat16*>(h_bf16);
+    p.y_bf16 = static_cast<__nv_bfloat16*>(y_bf16);
+    p.y_fp8 = static_cast<uint8_t*>(y_fp8);
+    p.y_scales = y_scales;
+    p.rows = rows;
+    p.inter = inter;
+    p.pow2 = scale_mode;
+    p.limit = swiglu_limit;
+    const int chunks = inter / 8;
+    const int threads = chunks < 1024 ? (chunks + 31) / 32 * 32 : 1024;
+    int splits = 1;
+    const int passes = (chunks + threads - 1) / threads;
+    while (splits < passes && rows * splits < 296) splits *= 2;
+    swiglu_quant_kernel<<<dim3(rows, splits), threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
     WUDA_CUDA(cudaGetLastError());
     return WUDA_OK;
 }

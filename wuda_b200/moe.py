@@ -99,3 +99,30 @@ class MoERunner:
         check(lib.wuda_moe_combine(self.out.data_ptr(), self.pair_row.data_ptr(), shared.data_ptr() if shared is not None else None,
                                    y.data_ptr(), m, self.topk, w.dim, s))
         return y
+
+
+class SharedExpert:
+    """The dense shared expert (Expert.forward, origin/model.py:587-606) on FP8 weights: w13 = [w1; w3]
+    e4m3 [2*inter, dim] and w2 e4m3 [dim, inter] with fp32 128x128 block scales."""
+
+    def __init__(self, w13, w13_scale, w2, w2_scale, swiglu_limit=0.0):
+        self.w13, self.w13_scale, self.w2, self.w2_scale, self.limit = w13, w13_scale, w2, w2_scale, float(swiglu_limit)
+        self.inter = w2.size(1)
+
+    def forward(self, x):
+        """x bf16 [M, dim] -> bf16 [M, dim]: quantise, w1|w3 GEMM, SwiGLU + quantise, w2 GEMM (four launches)."""
+        x8, xs = ops.act_quant(x, 128, "ue8m0")
+        h = ops.fp8_gemm(x8, xs, self.w13, self.w13_scale)
+        m = x.size(0)
+        a8 = torch.empty(m, self.inter, dtype=torch.float8_e4m3fn, device=x.device)
+        a_s = torch.empty(m, self.inter // 128, dtype=torch.float32, device=x.device)
+        check(lib.wuda_swiglu_quant_fp8(h.data_ptr(), None, a8.data_ptr(), a_s.data_ptr(), m, self.inter, self.limit, 1,
+                                        torch.cuda.current_stream().cuda_stream))
+        return ops.fp8_gemm(a8, a_s, self.w2, self.w2_scale)
+
+
+def moe_block(x, gate_weight, gate_bias, routed, shared, score_func="sqrtsoftplus", route_scale=1.0):
+    """One MoE block of the origin (MoE.forward, origin/model.py:620-644) on one rank: router, routed
+    NVFP4 experts (a MoERunner), dense shared expert (a SharedExpert or None), sum in bf16."""
+    w, idx = ops.moe_gate(x, gate_weight, gate_bias, score_func, route_scale, routed.topk)
+    return routed.forward(x, w, idx, shared=shared.forward(x) if shared is not None else None)
