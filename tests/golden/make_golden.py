@@ -3,7 +3,7 @@ Python reference functions (imported from a checkout of guluguluhhhh/wuda) on sm
 seeded inputs.  The fixtures store inputs and expected outputs, so the tests need
 neither the checkout nor this script.
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 Functions used (paths inside the reference repository):
   dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py  ref_fp8_mqa_logits (:207-218)
@@ -340,7 +340,9 @@ def golden_kv_cache(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2 and "WUDA_REFERENCE_ROOT" not in os.environ:
+        sys.exit("usage: make_golden.py <path to a checkout of the reference>  (or set WUDA_REFERENCE_ROOT)")
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ["WUDA_REFERENCE_ROOT"]
     tdir = "dsv4_megakernel/megakernel/test"
     ref_mqa = _load(ref_root, tdir + "/test_mqa_logits_fp4.py", "ref_mqa")
     golden_mqa(ref_mqa, "mqa_logits_fp8_n1.npz", batch=3, next_n=1, ctx_lo=1, ctx_hi=400, epb=64, seed=11)

@@ -264,7 +264,7 @@ __device__ __forceinline__ void emit_candidates(const Params& p, Shared& s, int 
 // into two bit masks first; slots in the output and in the candidate list are then
 // reserved once per warp and batch (a warp scan of the per-thread counts and ONE counter
 // bump), instead of a vote and a shared-memory atomic round trip per element.
-constexpr int kClsBatch = 4;   // 16 elements per thread and batch: fits the 64-register budget of a 1024-thread CTA
+constexpr int kClsBatch = 4;   // 16 elements per thread and batch: fits the 64 registers a thread of a 1024-thread CTA can have
 // The pass covers elements [lo, hi) of the row (lo a multiple of 4); candidates go to
 // `dst`, which may be another CTA's shared memory within the cluster; emitted indices
 // are counted in `dst` as well.
