@@ -11,6 +11,7 @@ because consecutive launches use different weight buffers that together exceed L
     python -m wuda_b200.benchmarks attention_half_layer            (every built stage of the half-layer, one graph)
     python -m wuda_b200.benchmarks attention_half_layer_launches   (three eager passes, for an ncu launch list)
     python -m wuda_b200.benchmarks moe_experts                     (router + routed NVFP4 experts of one MoE block)
+    python -m wuda_b200.benchmarks moe_experts_launches            (two eager passes, for an ncu launch list)
     python -m wuda_b200.benchmarks one gemm_fp8 64 24576 7168      (a few launches of one shape, for ncu)
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks tp2
 """
@@ -352,7 +353,7 @@ def attention_half_layer(batch=64, context=32768, topk=2048, reps=30, launches_o
           % (us, wbytes / 1e6, batch * (context // 4) * 132 / 1e6))
 
 
-def moe_experts(tokens=64, topk=8, experts=256, dim=7168, inter=2048, reps=10):
+def moe_experts(tokens=64, topk=8, experts=256, dim=7168, inter=2048, reps=10, launches_only=0):
     """Router + routed experts of one MoE block at the model's geometry (256 NVFP4 experts, top-8,
     intermediate 2048): gate projection, routing, dispatch, gather-quantisation, grouped w1|w3 GEMM,
     SwiGLU + quantisation, grouped w2 GEMM, combine - nine launches in one CUDA graph.  The weights of
@@ -377,6 +378,12 @@ def moe_experts(tokens=64, topk=8, experts=256, dim=7168, inter=2048, reps=10):
     idx = step()
     torch.cuda.synchronize()
     assert int(runner.status.item()) == 0
+    if launches_only:
+        for _ in range(launches_only - 1):
+            step()
+        torch.cuda.synchronize()
+        print("moe_experts: %d eager passes done" % launches_only)
+        return
     active = int(torch.unique(idx).numel())
     groups = int(runner.num_groups.item())
     us = time_graph(step, reps=reps, inner=1)
@@ -414,4 +421,5 @@ if __name__ == "__main__":
     {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2,
      "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
      "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,
+     "moe_experts_launches": lambda: moe_experts(launches_only=2),
      "attention_half_layer_launches": lambda: attention_half_layer(launches_only=3)}[which]()

@@ -587,7 +587,11 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p,
     auto kernel = gemm_fp8_kernel<M_PAD>;
     WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.smem_optin));
     const long long units = static_cast<long long>(p.n_tiles) * p.kb;
-    const int grid = units < dev.num_sms ? static_cast<int>(units) : dev.num_sms;
+    // at most kMaxSplit CTAs share one weight tile: the tile's owner adds the others' partials one after
+    // the other, which costs more than it saves when a few tiles are cut into a hundred pieces
+    constexpr int kMaxSplit = 16;
+    int grid = units < dev.num_sms ? static_cast<int>(units) : dev.num_sms;
+    if (static_cast<long long>(p.n_tiles) * kMaxSplit < grid) grid = p.n_tiles * kMaxSplit;
     kernel<<<grid, kThreads, smem, stream>>>(w_map, a_map, p);
     WUDA_CUDA(cudaGetLastError());
     return WUDA_OK;

@@ -400,7 +400,9 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, const CUte
     WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total(stages)));
     const long long units = static_cast<long long>(p.n_tiles) * p.kb;
     // (grouped: the number of groups is only known on the device; one CTA per SM, idle ones return at once)
-    const int grid = (!p.group_expert && units < dev.num_sms) ? static_cast<int>(units) : dev.num_sms;
+    constexpr int kMaxSplit = 16;   // CTAs that may share one weight tile (the owner adds their partials serially)
+    int grid = (!p.group_expert && units < dev.num_sms) ? static_cast<int>(units) : dev.num_sms;
+    if (!p.group_expert && static_cast<long long>(p.n_tiles) * kMaxSplit < grid) grid = p.n_tiles * kMaxSplit;
     kernel<<<grid, kThreads, L::total(stages), stream>>>(w_map, a_map, wsf_map, asf_map, p);
     WUDA_CUDA(cudaGetLastError());
     return WUDA_OK;
