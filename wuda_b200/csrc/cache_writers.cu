@@ -300,6 +300,8 @@ __device__ void window_row(const Params& P, float* warp_ssq) {
 }
 
 __global__ void __launch_bounds__(kThreads) cache_writers_kernel(const __grid_constant__ Params P) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     __shared__ float warp_ssq[4];
     if (blockIdx.y == 0) {
         if (P.a.main.state) main_row(P, warp_ssq);
@@ -366,7 +368,6 @@ extern "C" int wuda_cache_writers_fp8(const wuda_cache_writers* args, int rows, 
     p.rows = rows;
     p.status = status_word;
     const dim3 grid(rows, 3);
-    cache_writers_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(cache_writers_kernel, dim3(grid), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }

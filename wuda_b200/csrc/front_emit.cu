@@ -39,6 +39,8 @@ struct Params {
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 __global__ void __launch_bounds__(kThreads) front_emit_kernel(Params p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     // grid (tokens, 4): blockIdx.y = 0, 1 the two halves of the MAIN entry, 2 the indexer entry, 3 win_y2 + w64
     const int t = blockIdx.x;
     const int part = blockIdx.y;
@@ -113,7 +115,6 @@ extern "C" int wuda_front_emit(const void* y8_bf16, const float* y16_f32, const 
     p.w64 = w64;
     p.state_rows_total = state_rows_total;
     p.status = status_word;
-    front_emit_kernel<<<dim3(m, 4), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(front_emit_kernel, dim3(dim3(m, 4)), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }

@@ -221,6 +221,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // the prologue above ran while the kernel ahead was still finishing; global memory from here on
+    pdl_launch_dependents();
+    pdl_wait();
 
     const long long units = static_cast<long long>(p.n_tiles) * p.kb;
     const long long u0 = range_begin(units, blockIdx.x, gridDim.x);
@@ -592,8 +595,7 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p,
     constexpr int kMaxSplit = 16;
     int grid = units < dev.num_sms ? static_cast<int>(units) : dev.num_sms;
     if (static_cast<long long>(p.n_tiles) * kMaxSplit < grid) grid = p.n_tiles * kMaxSplit;
-    kernel<<<grid, kThreads, smem, stream>>>(w_map, a_map, p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(kThreads), smem, stream, w_map, a_map, p));
     return WUDA_OK;
 }
 

@@ -146,6 +146,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // the prologue above ran while the kernel ahead was still finishing; global memory from here on
+    pdl_launch_dependents();
+    pdl_wait();
 
     const bool grouped = p.group_expert != nullptr;
     const int groups = grouped ? *p.num_groups : 1;
@@ -403,8 +406,7 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, const CUte
     constexpr int kMaxSplit = 16;   // CTAs that may share one weight tile (the owner adds their partials serially)
     int grid = (!p.group_expert && units < dev.num_sms) ? static_cast<int>(units) : dev.num_sms;
     if (!p.group_expert && static_cast<long long>(p.n_tiles) * kMaxSplit < grid) grid = p.n_tiles * kMaxSplit;
-    kernel<<<grid, kThreads, L::total(stages), stream>>>(w_map, a_map, wsf_map, asf_map, p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(kThreads), L::total(stages), stream, w_map, a_map, wsf_map, asf_map, p));
     return WUDA_OK;
 }
 

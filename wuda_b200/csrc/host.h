@@ -44,4 +44,30 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, con
                       const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                       CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promo);
 
+// ---- programmatic dependent launch.  Every kernel of the library is launched with the attribute
+// that lets it start while the kernel before it in the stream is still running; it then runs its
+// prologue (barrier set-up, TMEM allocation, descriptor prefetch) and stops at pdl_wait() until
+// the earlier kernel has completed and its writes are visible, before its first access to global memory.
+// pdl_launch_dependents() is called at the start, so the next kernel gets the same head start.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 }  // namespace wuda

@@ -38,6 +38,8 @@ __device__ __forceinline__ uint32_t f2_to_bf2(float lo, float hi) {
 }
 
 __global__ void __launch_bounds__(kThreads) mhc_post_kernel(Params p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
     if (t >= p.total) return;
     const int64_t row = t / p.vectors;
@@ -114,7 +116,6 @@ extern "C" int wuda_mhc_post(const void* attention_out, const void* residual, co
     p.total = static_cast<int64_t>(m) * p.vectors;
     const int64_t blocks = (p.total + kThreads - 1) / kThreads;
     WUDA_REQUIRE(blocks <= 0x7fffffffLL, "m * hidden is too large for one launch");
-    mhc_post_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(mhc_post_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }

@@ -59,6 +59,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 __global__ void __launch_bounds__(kMixThreads) mhc_pre_mix_kernel(Params p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     __shared__ float warp_part[2][kMixThreads / 32][kPart];   // two buffers: one barrier per token
     const int slice = blockIdx.x;
     const int k0 = slice * kSlice + threadIdx.x * 4;
@@ -116,6 +118,8 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 }
 
 __global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     __shared__ float mix[kPart];
     __shared__ float pre_s[kStreams];
     __shared__ float warp_ss[kFinishThreads / 32];
@@ -329,9 +333,7 @@ extern "C" int wuda_mhc_pre(const void* hidden_states, const float* weight, cons
     p.rms_eps = rms_eps;
     p.norm_eps = norm_eps;
     const dim3 grid_mix(p.slices, (m + kTokensPerCta - 1) / kTokensPerCta);
-    mhc_pre_mix_kernel<<<grid_mix, kMixThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
-    mhc_pre_finish_kernel<<<m, kFinishThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(mhc_pre_mix_kernel, dim3(grid_mix), dim3(kMixThreads), 0, static_cast<cudaStream_t>(stream), p));
+    WUDA_CUDA(launch_pdl(mhc_pre_finish_kernel, dim3(m), dim3(kFinishThreads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }

@@ -41,6 +41,8 @@ constexpr int kDispatchThreads = 1024;
 constexpr int kMaxExperts = 512;
 
 __global__ void __launch_bounds__(kDispatchThreads) moe_dispatch_kernel(DispatchParams p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     __shared__ int count[kMaxExperts];
     __shared__ int base[kMaxExperts];       // first group of the expert
     __shared__ int total_groups;
@@ -142,6 +144,8 @@ struct GatherParams {
 };
 
 __global__ void __launch_bounds__(256) moe_gather_quant_kernel(GatherParams p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     const int row = blockIdx.x;
     if (row >= *p.num_groups * kGroupRows) return;
     const int tok = p.row_token[row];
@@ -178,6 +182,8 @@ struct SwigluParams {
 };
 
 __global__ void __launch_bounds__(128) moe_swiglu_quant_kernel(SwigluParams p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     const int row = blockIdx.x;
     if (row >= *p.num_groups * kGroupRows) return;
     const bool live = p.row_token[row] >= 0;
@@ -220,6 +226,8 @@ struct CombineParams {
 };
 
 __global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < p.dim / 8; c += blockDim.x) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -292,8 +300,7 @@ extern "C" int wuda_moe_dispatch(const int32_t* indices, const float* weights, i
     p.experts = experts;
     p.max_groups = max_groups;
     p.status = status_word;
-    moe_dispatch_kernel<<<1, kDispatchThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(moe_dispatch_kernel, dim3(1), dim3(kDispatchThreads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 
@@ -316,8 +323,7 @@ extern "C" int wuda_moe_gather_quant_nvfp4(const void* x_bf16, const int32_t* ro
     p.a_sf = static_cast<uint8_t*>(a_sf_packed);
     p.gs = global_scale;
     p.K = k;
-    moe_gather_quant_kernel<<<max_groups * kGroupRows, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(moe_gather_quant_kernel, dim3(max_groups * kGroupRows), dim3(256), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 
@@ -342,8 +348,7 @@ extern "C" int wuda_moe_swiglu_quant_nvfp4(const void* h_bf16, const int32_t* ro
     p.gs = global_scale;
     p.limit = swiglu_limit;
     p.I = inter;
-    moe_swiglu_quant_kernel<<<max_groups * kGroupRows, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(moe_swiglu_quant_kernel, dim3(max_groups * kGroupRows), dim3(128), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 
@@ -362,7 +367,6 @@ extern "C" int wuda_moe_combine(const void* expert_out_bf16, const int32_t* pair
     p.y = static_cast<__nv_bfloat16*>(y_bf16);
     p.k = k;
     p.dim = dim;
-    moe_combine_kernel<<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(moe_combine_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }

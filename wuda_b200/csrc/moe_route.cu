@@ -24,6 +24,8 @@ struct Params {
 };
 
 __global__ void __launch_bounds__(32 * kWarpsPerCta) moe_route_kernel(Params p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     if (t >= p.tokens) return;                         // whole warps
@@ -138,7 +140,6 @@ extern "C" int wuda_moe_route(const float* logits, const float* bias, float* wei
     p.k = k;
     p.score_func = score_func;
     p.route_scale = route_scale;
-    moe_route_kernel<<<(tokens + kWarpsPerCta - 1) / kWarpsPerCta, 32 * kWarpsPerCta, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(moe_route_kernel, dim3((tokens + kWarpsPerCta - 1) / kWarpsPerCta), dim3(32 * kWarpsPerCta), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }

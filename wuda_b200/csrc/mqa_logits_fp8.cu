@@ -264,6 +264,9 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // the prologue above ran while the kernel ahead was still finishing; global memory from here on
+    pdl_launch_dependents();
+    pdl_wait();
 
     TileCursor cur = make_cursor<NEXT_N>(p.context_lens, p.batch);
     const int ntiles = cur.count;
@@ -511,8 +514,7 @@ static int launch(const CUtensorMap& q_map, const CUtensorMap& kv_map, const CUt
     const int smem = Smem<NEXT_N>::total(p.kv_stages);
     auto kernel = mqa_logits_fp8_kernel<NEXT_N>;
     WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kernel<<<grid, kThreads, smem, stream>>>(q_map, kv_map, sf_map, p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(kThreads), smem, stream, q_map, kv_map, sf_map, p));
     return WUDA_OK;
 }
 

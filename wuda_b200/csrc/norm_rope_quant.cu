@@ -95,6 +95,8 @@ struct NormParams {
 };
 
 __global__ void __launch_bounds__(1024, 1) rmsnorm_quant_kernel(const NormParams p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     __shared__ float warp_part[32];
     __shared__ float total;
     const int row = blockIdx.x;
@@ -165,6 +167,8 @@ struct RopeParams {
 };
 
 __global__ void __launch_bounds__(1024, 1) rope_quant_kernel(const RopeParams p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     const int t = blockIdx.x;
     const int width = p.heads * p.head_dim;
     const int chunks = width >> 3;
@@ -214,6 +218,8 @@ struct SwigluParams {
 // SwiGLU of a dense expert: y = bf16(silu(min(gate, L)) * clamp(up, +-L)), then 1x128 FP8 quantisation
 // (dsv4_megakernel/origin/model.py:596-606; L = 0 disables the clamps).
 __global__ void __launch_bounds__(1024, 1) swiglu_quant_kernel(const SwigluParams p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     const int r = blockIdx.x;
     const int chunks = p.inter >> 3;
     const __nv_bfloat16* g = p.h + static_cast<int64_t>(r) * (2 * p.inter);
@@ -274,8 +280,7 @@ extern "C" int wuda_rmsnorm_quant_fp8(const void* x_bf16, int64_t x_row_stride, 
     int threads = (chunks + kMaxChunks - 1) / kMaxChunks;
     threads = (threads + 31) / 32 * 32;
     if (threads > 1024) threads = 1024;
-    rmsnorm_quant_kernel<<<rows, threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(rmsnorm_quant_kernel, dim3(rows), dim3(threads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 
@@ -320,8 +325,7 @@ extern "C" int wuda_rope_quant_fp8(const void* x_bf16, const int64_t* positions,
     int splits = 1;
     const int passes = (chunks + threads - 1) / threads;
     while (splits < passes && tokens * splits < 296) splits *= 2;
-    rope_quant_kernel<<<dim3(tokens, splits), threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(rope_quant_kernel, dim3(dim3(tokens, splits)), dim3(threads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 
@@ -351,7 +355,6 @@ extern "C" int wuda_swiglu_quant_fp8(const void* h_bf16, void* y_bf16, void* y_f
     int splits = 1;
     const int passes = (chunks + threads - 1) / threads;
     while (splits < passes && rows * splits < 296) splits *= 2;
-    swiglu_quant_kernel<<<dim3(rows, splits), threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(swiglu_quant_kernel, dim3(dim3(rows, splits)), dim3(threads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }

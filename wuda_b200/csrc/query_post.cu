@@ -72,6 +72,8 @@ struct IndexParams {
 };
 
 __global__ void __launch_bounds__(kThreads) index_q_post_kernel(IndexParams p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     const int64_t g = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 4;   // (token, head)
     const int sub = threadIdx.x & 15;
     const bool live = g < p.groups;            // whole 16-lane groups are live or not
@@ -116,6 +118,8 @@ struct QueryParams {
 };
 
 __global__ void __launch_bounds__(kThreads) query_rms_rope_kernel(QueryParams p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     const int64_t r = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;   // (token, out head)
     if (r >= p.rows) return;                   // whole warps
     const int lane = threadIdx.x & 31;
@@ -181,8 +185,7 @@ extern "C" int wuda_index_q_post_fp8(const void* iq_bf16, int64_t row_stride, co
     p.groups = static_cast<int64_t>(tokens) * heads;
     p.heads = heads;
     const int64_t blocks = (p.groups * 16 + kThreads - 1) / kThreads;
-    index_q_post_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(index_q_post_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 
@@ -214,7 +217,6 @@ extern "C" int wuda_query_rms_rope(const void* x_bf16, int64_t row_stride, const
     p.out_heads = output_heads;
     p.eps = eps;
     const int64_t blocks = (p.rows * 32 + kThreads - 1) / kThreads;
-    query_rms_rope_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    WUDA_CUDA(cudaGetLastError());
+    WUDA_CUDA(launch_pdl(query_rms_rope_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }

@@ -375,6 +375,8 @@ __device__ long long g_phase_clock[16];
 #endif
 
 __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     extern __shared__ uint8_t smem_raw[];
     Shared& s = *reinterpret_cast<Shared*>(smem_raw);
     namespace cg = cooperative_groups;
@@ -759,13 +761,15 @@ extern "C" int wuda_topk(const float* scores, const int32_t* seq_lens, const int
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = kCluster;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     WUDA_CUDA(cudaLaunchKernelEx(&cfg, topk_kernel, p));
     return WUDA_OK;
 }
