@@ -34,9 +34,9 @@ namespace gemm4 {
 constexpr int kTileN = 128;          // weight rows per tile (UMMA M)
 constexpr int kBlockK = 256;         // K elements per unit = 128 bytes per row
 constexpr int kRowBytes = 128;
-constexpr int kProducers = 2;        // warps 0, 1
+constexpr int kProducers = 4;        // warps 0..3: a warp needs ~1000 cycles to start a unit's four copies, a unit lasts ~800
 constexpr int kIssuers = 2;          // warps 2, 3: each accumulates its own units into its own TMEM tile
-constexpr int kFirstEpiWarp = 4;     // warps 4..7
+constexpr int kFirstEpiWarp = 8;     // warps 8..11 (6 and 7 idle: the TMEM lane quarter of a warp is warp % 4)
 constexpr int kEpiWarps = 4;
 constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
 constexpr int kWBytes = kTileN * kRowBytes;   // 16 KB
@@ -283,7 +283,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 ++seg;
             }
         }
-    } else {
+    } else if (warp >= kFirstEpiWarp) {
         // ------------------------------------------------------------ epilogue warps
         const int et = (warp - kFirstEpiWarp) * 32 + lane;       // 0..127 = weight row inside the tile
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -393,8 +393,10 @@ template <int M_PAD>
 static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, const CUtensorMap& wsf_map,
                   const CUtensorMap& asf_map, Params& p, const DeviceInfo& dev, cudaStream_t stream) {
     using L = Smem<M_PAD>;
+    // stage counts are multiples of the producer and issuer counts (a stage always belongs to the same
+    // producer and the same issuer)
     int stages = 16;
-    while (stages > 2 && L::total(stages) > dev.smem_optin) stages -= 2;
+    while (stages > 4 && L::total(stages) > dev.smem_optin) stages -= 4;
     if (L::total(stages) > dev.smem_optin)
         return fail(WUDA_ERR_UNSUPPORTED, "device offers %d bytes of shared memory per block; the kernel needs more",
                     dev.smem_optin);
