@@ -29,9 +29,9 @@ namespace gemm16 {
 constexpr int kTileN = 128;          // weight rows per tile (UMMA M)
 constexpr int kBlockK = 64;          // K elements per unit = 128 bytes per row
 constexpr int kRowBytes = 128;
-constexpr int kProducers = 2;        // warps 0, 1
+constexpr int kProducers = 4;        // warps 0..3: starting a unit's copies costs a warp several hundred cycles
 constexpr int kIssuers = 2;          // warps 2, 3: each accumulates its own units into its own TMEM tile
-constexpr int kFirstEpiWarp = 4;     // warps 4..7
+constexpr int kFirstEpiWarp = 8;     // warps 8..11 (6 and 7 idle: the TMEM lane quarter of a warp is warp % 4)
 constexpr int kEpiWarps = 4;
 constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
 constexpr int kWBytes = kTileN * kRowBytes;   // 16 KB
@@ -220,7 +220,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
                 ++seg;
             }
         }
-    } else {
+    } else if (warp >= kFirstEpiWarp) {
         // ------------------------------------------------------------ epilogue warps
         const int et = (warp - kFirstEpiWarp) * 32 + lane;       // 0..127 = weight row inside the tile
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -334,7 +334,7 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p,
                   cudaStream_t stream) {
     using L = Smem<M_PAD>;
     int stages = 16;
-    while (stages > 2 && L::total(stages) > dev.smem_optin) stages -= 2;
+    while (stages > 4 && L::total(stages) > dev.smem_optin) stages -= 4;   // multiples of the producer and issuer counts
     if (L::total(stages) > dev.smem_optin)
         return fail(WUDA_ERR_UNSUPPORTED, "device offers %d bytes of shared memory per block; the kernel needs more",
                     dev.smem_optin);
@@ -344,7 +344,8 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p,
     const long long units = static_cast<long long>(p.n_tiles) * p.kb;
     // at most kMaxSplit CTAs share one weight tile: the tile's owner adds the others' partials one after
     // the other, which costs more than it saves when a few tiles are cut into a hundred pieces
-    constexpr int kMaxSplit = 16;
+    // (adding one partial costs the owner about as much as streaming M_PAD / 64 units, so wide tiles split less)
+    constexpr int kMaxSplit = M_PAD <= 16 ? 16 : (M_PAD == 32 ? 12 : (M_PAD == 64 ? 8 : 6));
     int grid = units < dev.num_sms ? static_cast<int>(units) : dev.num_sms;
     if (static_cast<long long>(p.n_tiles) * kMaxSplit < grid) grid = p.n_tiles * kMaxSplit;
     WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(kThreads), L::total(stages), stream, w_map, a_map, p));
