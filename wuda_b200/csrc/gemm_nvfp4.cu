@@ -39,6 +39,12 @@ constexpr int kIssuers = 2;          // warps 2, 3: each accumulates its own uni
 constexpr int kFirstEpiWarp = 8;     // warps 8..11 (6 and 7 idle: the TMEM lane quarter of a warp is warp % 4)
 constexpr int kEpiWarps = 4;
 constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
+// Role layout by tile width.  Up to 64 activation rows: four producers (warps 0..3), two issuers (4, 5), epilogue
+// warps 8..11.  128 rows: the epilogue holds 128 accumulators per thread and needs the registers of a 256-thread
+// CTA, and the wide stages leave room for few of them: two producers (0, 1), issuers 2, 3, epilogue 4..7.
+__host__ __device__ constexpr int producers_for(int m_pad) { return m_pad >= 128 ? 2 : kProducers; }
+__host__ __device__ constexpr int first_epi_warp_for(int m_pad) { return (producers_for(m_pad) + kIssuers + 3) / 4 * 4; }
+__host__ __device__ constexpr int threads_for(int m_pad) { return 32 * (first_epi_warp_for(m_pad) + kEpiWarps); }
 constexpr int kWBytes = kTileN * kRowBytes;   // 16 KB
 constexpr int kSfBytes = 2048;                // one packed scale block
 constexpr int kMaxGrid = 192;
@@ -104,7 +110,7 @@ __device__ __forceinline__ int cta_of(long long units, long long u, int grid) {
 }
 
 template <int M_PAD>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(threads_for(M_PAD), 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap a_map,
                   const __grid_constant__ CUtensorMap wsf_map, const __grid_constant__ CUtensorMap asf_map,
                   const Params p) {
@@ -132,7 +138,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
         mbar_init(empty_tm, kEpiWarps);    // the epilogue has read them
         fence_mbar_init();
     }
-    if (warp == kProducers) {
+    if (warp == producers_for(M_PAD)) {
         tmem_alloc(smem_u32(tmem_slot), L::kTmemCols);
         tmem_relinquish();
     }
@@ -162,7 +168,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     const long long u1 = taking_part ? range_begin(units, blockIdx.x + 1, grid) : 0;
     const int count = static_cast<int>(u1 - u0);
 
-    if (warp < kProducers) {
+    // wide activation tiles leave room for few stages; they keep two producers so that the stage count can be
+    // any even number (a stage always belongs to one producer and one issuer)
+    constexpr int kProd = producers_for(M_PAD);
+    constexpr int kIssuer0 = kProd;                       // first issuer warp (it owns the TMEM allocation)
+    constexpr int kEpi0 = first_epi_warp_for(M_PAD);
+    if (warp < kProd) {
         // ------------------------------------------------------------ TMA producers
         const int me = warp;
         const uint64_t stream_policy = policy_evict_first();
@@ -172,7 +183,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
         int tile = static_cast<int>((u0 + me) / p.kb), kb = static_cast<int>((u0 + me) % p.kb);
         int seen_tile = -1, grp = grouped ? -1 : 0, expert = 0, wtile = 0;
         bool alive = true;
-        for (int n = me; n < count && alive; n += kProducers) {
+        for (int n = me; n < count && alive; n += kProd) {
             const int s = ring.idx;
             alive = mbar_wait_lane0(empty + s * 8, ring.phase ^ 1u, abort_flag, p.status, kDevTimeoutGemmEmpty);
             if (!alive) break;
@@ -216,20 +227,20 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 policy = keep_policy;
             }
             if (lane < 4) tma_load_2d_hint(dst, map, full + s * 8, c0, c1, policy);
-            ring.step(kProducers, S);
-            kb += kProducers;
+            ring.step(kProd, S);
+            kb += kProd;
             while (kb >= p.kb) {
                 kb -= p.kb;
                 ++tile;
             }
         }
-    } else if (warp < kProducers + kIssuers) {
+    } else if (warp >= kIssuer0 && warp < kIssuer0 + kIssuers) {
         // ------------------------------------------------------------ UMMA issuers (one thread each)
         // Issuer i takes units n with n % 2 == i and accumulates them into its own TMEM tile; the
         // epilogue adds the two tiles.  (Two threads must not chain accumulations into one tile:
         // only operations of one thread are ordered.)
         if (lane == 0) {
-            const int me = warp - kProducers;
+            const int me = warp - kIssuer0;
             // kind::mxf4nvf4: formats e2m1 (1), scale format ue4m3 (0), both operands K-major
             constexpr uint32_t idesc = umma_idesc_block_scaled(kTileN, M_PAD, 1, 1, 0, 0, 0);
             const uint32_t d_addr = tmem_base + me * M_PAD;
@@ -283,9 +294,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 ++seg;
             }
         }
-    } else if (warp >= kFirstEpiWarp) {
+    } else if (warp >= kEpi0) {
         // ------------------------------------------------------------ epilogue warps
-        const int et = (warp - kFirstEpiWarp) * 32 + lane;       // 0..127 = weight row inside the tile
+        const int et = (warp - kEpi0) * 32 + lane;       // 0..127 = weight row inside the tile
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         bool alive = true;
         int tile = static_cast<int>(u0 / p.kb), kb = static_cast<int>(u0 % p.kb);
@@ -383,7 +394,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     __syncthreads();
     if (*abort_flag) abort_drain_sleep();
     __syncthreads();
-    if (warp == kProducers) {
+    if (warp == producers_for(M_PAD)) {
         tc_fence_after();
         tmem_dealloc(tmem_base, L::kTmemCols);
     }
@@ -396,7 +407,8 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, const CUte
     // stage counts are multiples of the producer and issuer counts (a stage always belongs to the same
     // producer and the same issuer)
     int stages = 16;
-    while (stages > 4 && L::total(stages) > dev.smem_optin) stages -= 4;
+    constexpr int kStep = M_PAD >= 128 ? 2 : 4;   // lcm of the producer and issuer counts
+    while (stages > kStep && L::total(stages) > dev.smem_optin) stages -= kStep;
     if (L::total(stages) > dev.smem_optin)
         return fail(WUDA_ERR_UNSUPPORTED, "device offers %d bytes of shared memory per block; the kernel needs more",
                     dev.smem_optin);
@@ -410,7 +422,7 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, const CUte
     constexpr int kMaxSplit = M_PAD <= 16 ? 16 : (M_PAD == 32 ? 12 : (M_PAD == 64 ? 8 : 6));
     int grid = (!p.group_expert && units < dev.num_sms) ? static_cast<int>(units) : dev.num_sms;
     if (!p.group_expert && static_cast<long long>(p.n_tiles) * kMaxSplit < grid) grid = p.n_tiles * kMaxSplit;
-    WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(kThreads), L::total(stages), stream, w_map, a_map, wsf_map, asf_map, p));
+    WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(threads_for(M_PAD)), L::total(stages), stream, w_map, a_map, wsf_map, asf_map, p));
     return WUDA_OK;
 }
 
