@@ -192,6 +192,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     float* rings = reinterpret_cast<float*>(base_ptr + L::scale_off(S, rkb));
     float* comb = reinterpret_cast<float*>(base_ptr + L::comb_off(S, rkb));
     constexpr bool kAlt = L::kAlternate;
+    constexpr bool kPreScale = M_PAD >= 64;   // multiply activation and weight scales once per column, not per thread
 
     const int warp = threadIdx.x >> 5;
     const uint32_t lane = lane_id();
@@ -374,17 +375,22 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
             fetch_scales(j + kScaleAhead);
             cp_async_wait<kScaleAhead>();                // this thread's copies for the unit have landed
             ring_sync();                                 // ... and so have everybody else's
+            if constexpr (kPreScale) {   // the unit's scale products a_s[c] * w_s, once per column
+                const int slot = j & (kScaleSlots - 1);
+                if (fetcher < M_PAD) a_ring[slot * M_PAD + fetcher] = __fmul_rn(a_ring[slot * M_PAD + fetcher], w_ring[slot]);
+                ring_sync();
+            }
             const int ts = tring.idx;
             if (alive)
                 alive = mbar_wait_warp_fast(full_tm + ts * 8, tring.phase, abort_flag, p.status, kDevTimeoutGemmTmemFull);
             if (alive) {
                 tc_fence_after();
                 const int slot = j & (kScaleSlots - 1);
-                const float wsc = w_ring[slot];
+                const float wsc = kPreScale ? 1.0f : w_ring[slot];   // wide tiles hold a_s[c] * w_s already
                 const float* sc = a_ring + slot * M_PAD + col0;
                 const uint32_t taddr = tmem_base + lane_base + ts * M_PAD + col0;
-                // acc[c] += v[c] * (a_s[c] * w_s): scales come as 16-byte shared-memory loads, the
-                // products and sums as packed fp32x2 operations (one instruction per two columns)
+                // acc[c] += v[c] * (a_s[c] * w_s): the products come as 16-byte shared-memory loads, the
+                // sums as packed fp32x2 operations (one instruction per two columns)
                 float2* acc2 = reinterpret_cast<float2*>(acc);
                 const float2 w2 = make_float2(wsc, wsc);
                 if constexpr (kCols >= 32) {
@@ -399,8 +405,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
                             const float4 sv = s4[i >> 2];
-                            const float2 s01 = __fmul2_rn(make_float2(sv.x, sv.y), w2);
-                            const float2 s23 = __fmul2_rn(make_float2(sv.z, sv.w), w2);
+                            const float2 s01 = kPreScale ? make_float2(sv.x, sv.y) : __fmul2_rn(make_float2(sv.x, sv.y), w2);
+                            const float2 s23 = kPreScale ? make_float2(sv.z, sv.w) : __fmul2_rn(make_float2(sv.z, sv.w), w2);
                             acc2[(c + i) >> 1] = __ffma2_rn(make_float2(__uint_as_float(x[i]), __uint_as_float(x[i + 1])),
                                                             s01, acc2[(c + i) >> 1]);
                             acc2[((c + i) >> 1) + 1] = __ffma2_rn(
