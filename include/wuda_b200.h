@@ -51,7 +51,12 @@ typedef enum wuda_device_status {
     WUDA_DEV_TIMEOUT_PEER_FLAG = 131,
     WUDA_DEV_BAD_DESTINATION = 141, /* cache destination outside the pool: that record was not written */
     WUDA_DEV_BAD_STATE_ROW = 142,   /* state_row outside the state rings: that row was skipped         */
-    WUDA_DEV_BAD_EXPERT = 143       /* expert index outside [0, experts): that pair was dropped        */
+    WUDA_DEV_BAD_EXPERT = 143,      /* expert index outside [0, experts): that pair was dropped        */
+    WUDA_DEV_TIMEOUT_MLA_KEYS = 151,
+    WUDA_DEV_TIMEOUT_MLA_SCORES = 152,
+    WUDA_DEV_TIMEOUT_MLA_SCORES_READ = 153,
+    WUDA_DEV_TIMEOUT_MLA_PROBS = 154,
+    WUDA_DEV_TIMEOUT_MLA_OUTPUT = 155
 } wuda_device_status;
 
 /* Library version (major*10000 + minor*100 + patch). */
@@ -357,6 +362,47 @@ typedef struct wuda_csa_workspace {
 
 int wuda_csa_decode_step(const wuda_csa_weights* weights, const wuda_csa_caches* caches, const wuda_csa_step* step,
                          const wuda_csa_workspace* workspace, int m, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Sparse MLA decode attention over gathered FP8 cache records: per request one query token
+ * with `heads` heads of 512 dims attends to swa_lengths[b] sliding-window entries and then
+ * cmp_lengths[b] top-k compressed entries, each named by a pool entry index
+ * (page * entries_per_block + offset; a negative index is skipped).  A pool page holds
+ * entries_per_block records of 576 bytes (448 e4m3, then 64 bf16), then entries_per_block
+ * groups of 8 scale bytes (7 power-of-two exponents + 1 pad): the record format
+ * wuda_cache_writers_fp8 writes.  The value vector of a key is the key itself.
+ *   logit[h, t] = softmax_scale * q[h, :] . k[t, :]
+ *   out[h, :]   = sum_t exp(logit[h, t]) k[t, :] / (sum_t exp(logit[h, t]) + exp(attn_sink[h]))
+ * A request without a valid key gives a zero row.  fp32 logits and sums; the probabilities
+ * are rounded to bf16 before they meet the values.
+ *
+ * Replaces the third-party call at test/test_e2e_decode.py:719-728 (flash_mla_with_kvcache
+ * with indices / extra_indices_in_kvcache / attn_sink); arithmetic as the torch twin
+ * ref_flash_attn (test/test_e2e_decode.py:377-392) over deq_model1_row (:346-356) and as
+ * origin/kernel.py:276-352.
+ *
+ * An index at or beyond pages * entries_per_block is skipped and reported as
+ * WUDA_DEV_BAD_PAGE_INDEX.  Either pool may be absent (capacity 0).
+ */
+typedef struct wuda_sparse_mla_args {
+    const void* q;               /* bf16 [batch, heads, 512], after RMSNorm and RoPE        */
+    const void* swa_pool;        /* uint8 [swa_pages, swa_stride]                           */
+    int64_t swa_stride;
+    const int32_t* swa_indices;  /* int32 [batch, swa_capacity]                             */
+    const int32_t* swa_lengths;  /* int32 [batch], clamped to [0, swa_capacity]             */
+    const void* cmp_pool;        /* uint8 [cmp_pages, cmp_stride]                           */
+    int64_t cmp_stride;
+    const int32_t* cmp_indices;  /* int32 [batch, cmp_capacity]                             */
+    const int32_t* cmp_lengths;  /* int32 [batch]                                           */
+    const float* attn_sink;      /* fp32 [heads] or NULL                                    */
+    void* out;                   /* bf16 [batch, heads, 512]                                */
+    int32_t swa_pages, swa_entries_per_block, swa_capacity;
+    int32_t cmp_pages, cmp_entries_per_block, cmp_capacity;
+    int32_t batch, heads;
+    float softmax_scale;
+} wuda_sparse_mla_args;
+
+int wuda_sparse_mla_decode(const wuda_sparse_mla_args* args, int32_t* status_word, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * mHC pre, the head of a half-layer: from the 4 residual streams of each token

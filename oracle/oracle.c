@@ -785,3 +785,68 @@ int oracle_num_threads(void) {
     return 1;
 #endif
 }
+
+/* ------------------------------------------------------------------ sparse MLA decode attention
+ *
+ * Softmax attention of one query token per request over gathered cache records, after
+ * dsv4_megakernel/megakernel/test/test_e2e_decode.py:377-392 (ref_flash_attn: softmax over the
+ * logits and the sink, the sink's column dropped from the weighted sum; value = key) with the
+ * keys dequantised as :346-356 (deq_model1_row: 448 e4m3 * 2^(byte-127) per 64, then 64 bf16).
+ * Keys: the first swa_len[b] entries of swa_idx, then the first cmp_len[b] of cmp_idx; a
+ * negative entry is skipped.  Sums run in double so that the result stands for the exact value.
+ */
+static void model1_row(const uint8_t* pool, int64_t stride, int epb, int idx, float* k) {
+    const uint8_t* page = pool + (int64_t)(idx / epb) * stride;
+    const int off = idx % epb;
+    const uint8_t* body = page + (int64_t)off * 576;
+    const uint8_t* sb = page + (int64_t)epb * 576 + off * 8;
+    for (int g = 0; g < 7; ++g) {
+        const float scale = sb[g] == 0 ? ldexpf(1.0f, -127) : ldexpf(1.0f, (int)sb[g] - 127);
+        for (int i = 0; i < 64; ++i) k[g * 64 + i] = oracle_e4m3_to_f32(body[g * 64 + i]) * scale;
+    }
+    for (int i = 0; i < 64; ++i) {
+        uint16_t h;
+        memcpy(&h, body + 448 + 2 * i, 2);
+        k[448 + i] = bf16_to_f32(h);
+    }
+}
+
+void oracle_sparse_mla(const uint16_t* q, const uint8_t* swa_pool, int64_t swa_stride, int swa_epb,
+                       const int32_t* swa_idx, const int32_t* swa_len, int swa_cap, const uint8_t* cmp_pool,
+                       int64_t cmp_stride, int cmp_epb, const int32_t* cmp_idx, const int32_t* cmp_len, int cmp_cap,
+                       const float* sink, float scale, float* out, int batch, int heads) {
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int b = 0; b < batch; ++b) {
+        const int ns = swa_cap > 0 ? (swa_len[b] < swa_cap ? swa_len[b] : swa_cap) : 0;
+        const int nc = cmp_cap > 0 ? (cmp_len[b] < cmp_cap ? cmp_len[b] : cmp_cap) : 0;
+        float* keys = (float*)malloc(sizeof(float) * 512 * (size_t)(ns + nc + 1));
+        int n = 0;
+        for (int t = 0; t < ns; ++t)
+            if (swa_idx[(int64_t)b * swa_cap + t] >= 0)
+                model1_row(swa_pool, swa_stride, swa_epb, swa_idx[(int64_t)b * swa_cap + t], keys + 512 * (size_t)n++);
+        for (int t = 0; t < nc; ++t)
+            if (cmp_idx[(int64_t)b * cmp_cap + t] >= 0)
+                model1_row(cmp_pool, cmp_stride, cmp_epb, cmp_idx[(int64_t)b * cmp_cap + t], keys + 512 * (size_t)n++);
+        double* lg = (double*)malloc(sizeof(double) * (size_t)(n + 1));
+        for (int h = 0; h < heads; ++h) {
+            const uint16_t* qh = q + ((int64_t)b * heads + h) * 512;
+            float* o = out + ((int64_t)b * heads + h) * 512;
+            double mx = sink ? (double)sink[h] : -INFINITY;
+            for (int t = 0; t < n; ++t) {
+                double acc = 0.0;
+                for (int d = 0; d < 512; ++d) acc += (double)bf16_to_f32(qh[d]) * (double)keys[512 * (size_t)t + d];
+                lg[t] = (double)((float)acc * scale);
+                if (lg[t] > mx) mx = lg[t];
+            }
+            double den = sink ? exp((double)sink[h] - mx) : 0.0;
+            for (int t = 0; t < n; ++t) den += (lg[t] = exp(lg[t] - mx));
+            for (int d = 0; d < 512; ++d) {
+                double acc = 0.0;
+                for (int t = 0; t < n; ++t) acc += lg[t] * (double)keys[512 * (size_t)t + d];
+                o[d] = (n > 0 && den > 0.0) ? (float)(acc / den) : 0.0f;
+            }
+        }
+        free(lg);
+        free(keys);
+    }
+}

@@ -64,6 +64,8 @@ def _declare(l):
     l.oracle_query_rms_rope.argtypes = [vp, i64, vp, vp, vp, c.c_int, vp, c.c_int, c.c_int, c.c_int, c.c_float]
     l.oracle_mhc_pre.argtypes = [vp, vp, vp, vp, vp, c.c_float, c.c_float, c.c_float, vp, vp, vp, vp, vp, vp, vp,
                                  c.c_int, c.c_int]
+    l.oracle_sparse_mla.argtypes = [vp, vp, i64, c.c_int, vp, vp, c.c_int, vp, i64, c.c_int, vp, vp, c.c_int, vp,
+                                    c.c_float, vp, c.c_int, c.c_int]
     l.oracle_moe_route.argtypes = [vp, vp, vp, vp, c.c_int, c.c_int, c.c_int, c.c_int, c.c_float]
     l.oracle_gemm_nvfp4.argtypes = [c.c_void_p, c.c_void_p, c.c_float, c.c_void_p, c.c_void_p, c.c_float, c.c_void_p,
                                     c.c_int, c.c_int, c.c_int, c.c_int]
@@ -263,6 +265,29 @@ def mhc_pre(hidden_bf16, weight, base, scale, gamma_bf16=None, hc_eps=1e-6, rms_
     lib().oracle_mhc_pre(_p(x), _p(w), _p(b), _p(sc), _p(g), hc_eps, rms_eps, norm_eps, _p(out["pre"]), _p(out["post"]),
                          _p(out["comb"]), _p(out["collapsed"]), _p(out.get("normed")), _p(out.get("xq")),
                          _p(out.get("xsf")), m, d)
+    return out
+
+
+def sparse_mla(q_bf16, swa, cmp, sink, scale):
+    """q uint16 [batch, heads, 512]; swa / cmp = None or (pool uint8 [pages, stride], entries_per_block,
+    indices int32 [batch, capacity], lengths int32 [batch]).  Returns fp32 [batch, heads, 512]."""
+    q = _c(q_bf16, np.uint16)
+    batch, heads = q.shape[0], q.shape[1]
+
+    def unpack(t):
+        if t is None:
+            return None, 0, 1, None, None, 0
+        pool, epb, idx, lens = t
+        assert pool.dtype == np.uint8 and pool.ndim == 2 and pool.flags.c_contiguous
+        idx = _c(idx, np.int32).reshape(batch, -1)
+        return pool, pool.shape[1], int(epb), idx, _c(lens, np.int32), idx.shape[1]
+
+    sp, ss, se, si, sl, sc = unpack(swa)
+    cp, cs, ce, ci, cl, cc = unpack(cmp)
+    sink = _c(sink, np.float32) if sink is not None else None
+    out = np.zeros((batch, heads, 512), np.float32)
+    lib().oracle_sparse_mla(_p(q), _p(sp), ss, se, _p(si), _p(sl), sc, _p(cp), cs, ce, _p(ci), _p(cl), cc, _p(sink),
+                            float(scale), _p(out), batch, heads)
     return out
 
 

@@ -9,7 +9,8 @@ Functions used (paths inside the reference repository):
   dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py  ref_fp8_mqa_logits (:207-218)
   dsv4_megakernel/megakernel/test/test_topk_v2.py         ref_page_transform (:86-94) and the
                                                            stable-argsort rule (:116)
-  dsv4_megakernel/megakernel/test/test_e2e_decode.py      ref_mhc_post (:423-426)
+  dsv4_megakernel/megakernel/test/test_e2e_decode.py      ref_mhc_post (:423-426), ref_flash_attn
+                                                           (:377-392) over deq_model1_row (:346-356)
   dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py   ref_comp_step (:550-586, fp8 form) and
                                                            ref_win_step (:646-665)
   dsv4_megakernel/megakernel/test/test_hc_fused_tc.py     hc_reference (:115-136)
@@ -174,6 +175,54 @@ def golden_mhc_post(ref_root):
     np.savez_compressed(os.path.join(HERE, "mhc_post_7168.npz"), x=_u16(x), residual=_u16(res), post=post.numpy(),
                         comb=comb.numpy(), out=_u16(out))
     print("mhc_post_7168.npz", tuple(out.shape))
+
+
+def model1_pool(g, pages, epb):
+    """A pool of random MODEL1 records: finite e4m3 bytes, scale exponents near 0, bf16 rotary values."""
+    stride = -(-epb * 584 // 576) * 576
+    pool = torch.zeros(pages, stride, dtype=torch.uint8)
+    body = torch.randint(0, 256, (pages, epb, 448), generator=g, dtype=torch.int64)
+    body = torch.where((body & 0x7f) == 0x7f, body & 0x80, body).to(torch.uint8)   # no NaN patterns
+    rope = (torch.randn(pages, epb, 64, generator=g) * 0.7).bfloat16().view(torch.uint8).view(pages, epb, 128)
+    pool[:, :epb * 576] = torch.cat([body, rope], dim=-1).reshape(pages, epb * 576)
+    sb = torch.zeros(pages, epb, 8, dtype=torch.uint8)
+    sb[..., :7] = torch.randint(115, 122, (pages, epb, 7), generator=g).to(torch.uint8)
+    pool[:, epb * 576:epb * 584] = sb.reshape(pages, epb * 8)
+    return pool
+
+
+def golden_sparse_mla(ref_root):
+    """ref_flash_attn over records dequantised by deq_model1_row: window entries, then top-k entries."""
+    e2e = _load(ref_root, "dsv4_megakernel/megakernel/test/test_e2e_decode.py", "ref_e2e")
+    e2e.torch = torch
+    e2e.DEV = "cpu"
+    g = torch.Generator().manual_seed(83)
+    batch, heads = 3, 16
+    swa_epb, cmp_epb, swa_cap, cmp_cap = 256, 64, 128, 160
+    swa_pool, cmp_pool = model1_pool(g, 2, swa_epb), model1_pool(g, 5, cmp_epb)
+    swa_len, cmp_len = [128, 37, 0], [160, 75, 9]
+    swa_idx = torch.full((batch, swa_cap), -1, dtype=torch.int32)
+    cmp_idx = torch.full((batch, cmp_cap), -1, dtype=torch.int32)
+    for b in range(batch):
+        swa_idx[b, :swa_len[b]] = torch.randperm(2 * swa_epb, generator=g)[:swa_len[b]].int()
+        cmp_idx[b, :cmp_len[b]] = torch.randperm(5 * cmp_epb, generator=g)[:cmp_len[b]].int()
+    q = (torch.randn(batch, heads, 512, generator=g) * 1.5).bfloat16()
+    sink = torch.randn(heads, generator=g)
+    scale = 512 ** -0.5
+    outs = []
+    for b in range(batch):
+        sw = [e2e.deq_model1_row(swa_pool, int(i) // swa_epb, int(i) % swa_epb, swa_epb) for i in swa_idx[b, :swa_len[b]]]
+        cm = [e2e.deq_model1_row(cmp_pool, int(i) // cmp_epb, int(i) % cmp_epb, cmp_epb) for i in cmp_idx[b, :cmp_len[b]]]
+        sw = torch.stack(sw) if sw else torch.zeros(0, 512)
+        cm = torch.stack(cm) if cm else torch.zeros(0, 512)
+        outs.append(e2e.ref_flash_attn(q[b].float(), sw, cm, scale, sink))
+    out = torch.stack(outs)
+    np.savez_compressed(os.path.join(HERE, "sparse_mla_h16.npz"), q=_u16(q), swa_pool=swa_pool.numpy(),
+                        cmp_pool=cmp_pool.numpy(), swa_idx=swa_idx.numpy(), cmp_idx=cmp_idx.numpy(),
+                        swa_len=np.asarray(swa_len, np.int32), cmp_len=np.asarray(cmp_len, np.int32),
+                        sink=sink.numpy(), scale=np.float32(scale), swa_epb=np.int32(swa_epb), cmp_epb=np.int32(cmp_epb),
+                        out=out.numpy())
+    print("sparse_mla_h16.npz", tuple(out.shape))
 
 
 def golden_cache_writers(ref_root):
@@ -357,6 +406,7 @@ def main():
     golden_cache_writers(ref_root)
     golden_mhc_pre(ref_root)
     golden_moe_gate(ref_root)
+    golden_sparse_mla(ref_root)
 
 
 if __name__ == "__main__":

@@ -278,3 +278,12 @@ def test_moe_route_oracle_matches_origin_gate():
     flat[0, [7, 3, 30]] = 1.0
     weights, indices = oracle.moe_route(flat, None, 5, 1, 1.0)
     assert indices[0].tolist() == [3, 7, 30, 0, 1]
+
+
+def test_sparse_mla_oracle_matches_reference_twin():
+    """ref_flash_attn over deq_model1_row records (window entries, then top-k entries, with the
+    attention sink): the oracle sums in double, the twin in fp32."""
+    g = load_golden("sparse_mla_h16.npz")
+    got = oracle.sparse_mla(g["q"], (g["swa_pool"], int(g["swa_epb"]), g["swa_idx"], g["swa_len"]),
+                            (g["cmp_pool"], int(g["cmp_epb"]), g["cmp_idx"], g["cmp_len"]), g["sink"], float(g["scale"]))
+    assert np.max(np.abs(got - g["out"])) <= 2e-5 * np.max(np.abs(g["out"]))

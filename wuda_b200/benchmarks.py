@@ -12,6 +12,8 @@ because consecutive launches use different weight buffers that together exceed L
     python -m wuda_b200.benchmarks attention_half_layer_launches   (three eager passes, for an ncu launch list)
     python -m wuda_b200.benchmarks moe_experts                     (router + routed NVFP4 experts of one MoE block)
     python -m wuda_b200.benchmarks moe_experts_launches            (two eager passes, for an ncu launch list)
+    python -m wuda_b200.benchmarks sparse_mla                      (sparse MLA decode attention, window 128 + top-2048)
+    python -m wuda_b200.benchmarks sparse_mla_launches             (three eager launches of a small case, for ncu)
     python -m wuda_b200.benchmarks one gemm_fp8 64 24576 7168      (a few launches of one shape, for ncu)
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks tp2
 """
@@ -395,6 +397,60 @@ def moe_experts(tokens=64, topk=8, experts=256, dim=7168, inter=2048, reps=10, l
           (us, wbytes / 1e9, wbytes / us / 1e3, wbytes / us / 1e3 / hbm, kind))
 
 
+def model1_pool(pages, epb, seed):
+    """uint8 [pages, stride] pool of random MODEL1 records (finite e4m3, exponents near 0, small bf16)."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    stride = -(-epb * 584 // 576) * 576
+    pool = torch.zeros(pages, stride, dtype=torch.uint8, device="cuda")
+    body = torch.randint(0, 256, (pages, epb, 576), generator=g, device="cuda", dtype=torch.int32)
+    body = torch.where((body & 0x7f) == 0x7f, body & 0x80, body)
+    body[..., 449::2] = (body[..., 449::2] & 0x80) | 0x3e | (body[..., 449::2] & 1)   # bf16 high bytes: |x| in [0.1, 0.6)
+    pool[:, :epb * 576] = body.to(torch.uint8).reshape(pages, epb * 576)
+    sb = torch.zeros(pages, epb, 8, dtype=torch.uint8, device="cuda")
+    sb[..., :7] = torch.randint(115, 122, (pages, epb, 7), generator=g, device="cuda").to(torch.uint8)
+    pool[:, epb * 576:epb * 584] = sb.reshape(pages, epb * 8)
+    return pool
+
+
+def sparse_mla(batches=(4, 16, 64, 128), heads=128, window=128, topk=2048, context=32768, launches_only=0):
+    """Sparse MLA decode attention: per request `window` sliding-window records and `topk` of the
+    context / 4 compressed records, gathered by index from pools that exceed L2."""
+    hbm, tf, kind = peaks()
+    print("sparse MLA decode, heads %d, window %d + top-%d of %d compressed; peaks (%s) %.0f GB/s, %.0f TFLOP/s bf16"
+          % (heads, window, topk, context // 4, kind, hbm, tf))
+    print("%6s %9s %11s %9s %12s %9s" % ("batch", "us", "TFLOP/s", "of peak", "gather GB/s", "of peak"))
+    for batch in batches:
+        ncmp = context // 4
+        cmp_pages = batch * ncmp // 64
+        swa = model1_pool(batch, 256, 1)
+        cmp = model1_pool(cmp_pages, 64, 2)
+        view = lambda t, epb: t.as_strided((t.size(0), epb, 1, 584), (t.size(1), 584, 584, 1))
+        g = torch.Generator().manual_seed(batch)
+        swa_idx = torch.stack([torch.randperm(256, generator=g)[:window] + 256 * b for b in range(batch)]).int().cuda()
+        cmp_idx = torch.stack([torch.randperm(ncmp, generator=g)[:topk] + ncmp * b for b in range(batch)]).int().cuda()
+        swa_len = torch.full((batch,), window, dtype=torch.int32).cuda()
+        cmp_len = torch.full((batch,), topk, dtype=torch.int32).cuda()
+        q = torch.randn(batch, heads, 512, generator=g).bfloat16().cuda()
+        sink = torch.randn(heads, generator=g).cuda()
+        out = torch.empty_like(q)
+        status = wuda.device_status_word()
+        fn = lambda: wuda.sparse_mla_decode(q, view(swa, 256), swa_idx, swa_len, view(cmp, 64), cmp_idx, cmp_len, sink,
+                                            512 ** -0.5, out=out, status_word=status)
+        if launches_only:
+            for _ in range(launches_only):
+                fn()
+            torch.cuda.synchronize()
+            print("ran %d launches at batch %d (status %d)" % (launches_only, batch, int(status.item())))
+            continue
+        us = time_graph(fn, reps=10, inner=5)
+        assert int(status.item()) == 0
+        keys = batch * (window + topk)
+        flops = keys * heads * 512 * 2 * 2            # Q K^T and P V, each once
+        gathered = keys * 584
+        print("%6d %9.1f %11.1f %8.1f%% %12.0f %8.1f%%" % (batch, us, flops / us / 1e6, flops / us / 1e6 / tf * 100,
+                                                         gathered / us / 1e3, gathered / us / 1e3 / hbm * 100))
+
+
 def one(kind, m, n, k, launches=5):
     """A few eager launches of one GEMM shape (profiler captures)."""
     t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
@@ -419,6 +475,7 @@ if __name__ == "__main__":
         one(sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]))
         sys.exit(0)
     {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2,
+     "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(16,), launches_only=3),
      "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
      "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,
      "moe_experts_launches": lambda: moe_experts(launches_only=2),

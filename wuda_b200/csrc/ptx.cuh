@@ -31,6 +31,11 @@ enum DeviceStatus : int {
     kDevTimeoutGemmTmemFull = 123,
     kDevTimeoutGemmTmemEmpty = 124,
     kDevTimeoutPeerFlag = 131,
+    kDevTimeoutMlaKeys = 151,       // sparse attention: a key block never arrived
+    kDevTimeoutMlaScores = 152,     // ... its scores never completed
+    kDevTimeoutMlaScoresRead = 153, // ... the softmax never released a score buffer
+    kDevTimeoutMlaProbs = 154,      // ... its probabilities never arrived
+    kDevTimeoutMlaOutput = 155,     // ... its weighted sum never completed
 };
 
 // Wall-clock limit of one device-side wait.  Generous next to any real pipeline
@@ -368,6 +373,23 @@ __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// The store twin of tmem_ld_32x32: thread i of the warp writes lane (warp%4)*32+i,
+// columns [col, col+32).
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor for a K-major operand whose rows are exactly one
 // 128-byte swizzle span (TMA SWIZZLE_128B layout): 8-row groups 1024 bytes apart.
@@ -390,11 +412,25 @@ __host__ __device__ constexpr uint64_t umma_smem_desc_noswz(uint32_t addr, uint3
            (static_cast<uint64_t>(1) << 46);
 }
 
+// MN-major operand in the 128-byte swizzle: 64 consecutive M/N elements of 16 bits form one
+// 128-byte row, 8 rows (8 steps of K) form a 1024-byte group.  `lbo` = byte distance between
+// blocks of 64 M/N elements, the groups of 8 K steps are 1024 bytes apart.  The bytes are
+// arranged exactly as in the K-major form with the roles of the two dimensions exchanged.
+__host__ __device__ constexpr uint64_t umma_smem_desc_mn_sw128(uint32_t addr, uint32_t lbo) {
+    return (static_cast<uint64_t>((addr & 0x3FFFFu) >> 4)) | (static_cast<uint64_t>(lbo >> 4) << 16) |
+           (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) |
+           (static_cast<uint64_t>(2) << 61);
+}
+
 // Instruction descriptor, dense, fp32 accumulate, both operands K-major.
 // fmt: kind::f8f6f4 -> 0 e4m3, 1 e5m2, 5 e2m1; kind::f16 -> 0 f16, 1 bf16.
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t m, uint32_t n, uint32_t a_fmt,
                                                   uint32_t b_fmt) {
     return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// The same with operand B MN-major (its N dimension contiguous in shared memory).
+__host__ __device__ constexpr uint32_t umma_idesc_b_mn(uint32_t m, uint32_t n, uint32_t a_fmt, uint32_t b_fmt) {
+    return umma_idesc(m, n, a_fmt, b_fmt) | (1u << 16);
 }
 // Block-scaled variant (kind::mxf4nvf4): scale format bit 23 (0 ue4m3, 1 ue8m0), scale
 // ids select which byte column of the TMEM scale words is used.

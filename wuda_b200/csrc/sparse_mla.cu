@@ -1,0 +1,479 @@
+// Sparse MLA decode attention over gathered FP8 cache records.
+//
+// Per request, one query token with `heads` heads of 512 dims attends to a list of keys named
+// by index: first the sliding-window entries of one pool, then the top-k compressed entries of
+// a second pool.  A key is a 584-byte "MODEL1" record (448 e4m3 values with one power-of-two
+// scale byte per 64, then 64 bf16 rotary values); the value vector of a key is the key itself.
+//   logit[h, t] = softmax_scale * sum_d q[h, d] * k[t, d]
+//   out[h, :]   = sum_t exp(logit[h, t]) * k[t, :] / (sum_t exp(logit[h, t]) + exp(sink[h]))
+// This is the role the reference gives to a third-party kernel at
+// dsv4_megakernel/megakernel/test/test_e2e_decode.py:719-728; the arithmetic is the torch twin
+// ref_flash_attn (:377-392) over records dequantised as deq_model1_row (:346-356), the same
+// online-softmax form as dsv4_megakernel/origin/kernel.py:276-352.
+//
+// One CTA owns one request and one 256-dim half of the output (the 512 fp32 accumulator
+// columns of a full row do not fit beside the scores in tensor memory); both halves compute
+// the full scores.  Roles:
+//   warps 0-3   softmax: thread = head row = tensor-memory lane.  Scores of a 32-key block are
+//               read from tensor memory, scaled, masked, exponentiated against a running
+//               reference maximum and written to shared memory as bf16 probabilities.  The
+//               accumulator is rescaled only when the maximum grows by more than 2^8 (the final
+//               division uses the same reference, so the result does not depend on when).
+//   warps 4-11  key producers: gather records with plain loads (8 lanes per key), expand e4m3 *
+//               2^E to bf16 (exact) and store the block in the 128-byte-swizzled operand layout.
+//               The same bytes serve as the K-major operand of Q K^T and as the MN-major
+//               operand of P V.
+//   warp 12     issues the tcgen05 MMAs: Q K^T of block j ahead of P V of block j-1.
+// Every wait is bounded; a wait that runs out leaves a code in the status word and the CTA
+// exits normally.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "host.h"
+#include "ptx.cuh"
+
+namespace wuda {
+namespace mla {
+
+constexpr int kDim = 512;          // key / query / value dims
+constexpr int kNope = 448;         // e4m3 part
+constexpr int kBody = 576;         // 448 + 64 * 2 bytes
+constexpr int kScaleRec = 8;       // 7 scale bytes + 1 pad
+constexpr int kRows = 128;         // UMMA M: head rows, zero-padded
+constexpr int kBlock = 32;         // keys per block
+constexpr int kHalf = 256;         // output dims per CTA
+constexpr int kSoftmaxWarps = 4;
+constexpr int kProducerWarps = 8;
+constexpr int kIssuerWarp = kSoftmaxWarps + kProducerWarps;
+constexpr int kThreads = (kIssuerWarp + 1) * 32;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleStep = 8.0f;   // log2 units the block maximum may exceed the reference by
+
+// shared memory, offsets from a 1024-byte aligned base
+constexpr uint32_t kQBytes = kRows * kDim * 2;          // 8 chunks of [128 rows][128 B]
+constexpr uint32_t kQChunk = kRows * 128;
+constexpr uint32_t kStageBytes = kBlock * kDim * 2;     // 8 chunks of [32 keys][128 B]
+constexpr uint32_t kKChunk = kBlock * 128;
+constexpr uint32_t kPBytes = kRows * kBlock * 2;        // 4 pieces of [128 rows][16 B]
+constexpr uint32_t kPPiece = kRows * 16;
+constexpr uint32_t kOffQ = 0;
+constexpr uint32_t kOffK = kOffQ + kQBytes;
+constexpr uint32_t kOffP = kOffK + 2 * kStageBytes;
+constexpr uint32_t kOffValid = kOffP + 2 * kPBytes;     // 2 x 8 bytes: per producer warp, 4 valid bits
+constexpr uint32_t kOffBars = kOffValid + 16;
+constexpr uint32_t kNumBars = 10;
+constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
+constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
+
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColO = 0, kColS = 256;
+
+struct Pool {
+    const uint8_t* data;
+    int64_t stride;
+    int pages, epb;
+    const int32_t* indices;   // [batch, capacity]
+    const int32_t* lengths;   // [batch]
+    int capacity;
+};
+
+struct Params {
+    const __nv_bfloat16* q;   // [batch, heads, 512]
+    Pool swa, cmp;
+    const float* sink;        // [heads] or nullptr
+    float scale_log2;         // softmax_scale * log2(e)
+    __nv_bfloat16* out;       // [batch, heads, 512]
+    int heads;
+    int* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// 2^(e - 127) of a scale byte, as torch's float8_e8m0fnu reads it
+__device__ __forceinline__ float ue8m0(uint32_t e) {
+    return __uint_as_float(e == 0 ? 0x00400000u : (e == 255u ? 0x7fc00000u : e << 23));
+}
+
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t pair, float scale) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<unsigned short>(pair)));
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+    const __nv_bfloat162 b = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+    return *reinterpret_cast<const uint32_t*>(&b);
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+// One key's share of a lane: 8 e4m3 of each of the 7 scaled tiles, 8 rotary bf16, the scale bytes.
+struct KeyRegs {
+    uint2 nope[7];
+    uint4 rope;
+    uint2 scales;
+    int valid;
+};
+
+__device__ __forceinline__ void fetch_key(const Params& p, int b, int g, int n_swa, int n_total, int piece,
+                                          KeyRegs& r, bool* bad) {
+    r.valid = 0;
+    if (g >= n_total) return;
+    const bool window = g < n_swa;
+    const Pool& pool = window ? p.swa : p.cmp;
+    const int idx = __ldg(pool.indices + static_cast<int64_t>(b) * pool.capacity + (window ? g : g - n_swa));
+    if (idx < 0) return;
+    const int page = idx / pool.epb, off = idx - page * pool.epb;
+    if (page >= pool.pages) {
+        *bad = true;
+        return;
+    }
+    const uint8_t* base = pool.data + static_cast<int64_t>(page) * pool.stride;
+    const uint8_t* rec = base + static_cast<int64_t>(off) * kBody;
+#pragma unroll
+    for (int c = 0; c < 7; ++c) r.nope[c] = __ldg(reinterpret_cast<const uint2*>(rec + c * 64) + piece);
+    r.rope = __ldg(reinterpret_cast<const uint4*>(rec + kNope) + piece);
+    r.scales = __ldg(reinterpret_cast<const uint2*>(base + static_cast<int64_t>(pool.epb) * kBody + off * kScaleRec));
+    r.valid = 1;
+}
+
+__device__ __forceinline__ void store_key(uint32_t stage_addr, int row, int piece, const KeyRegs& r) {
+    const uint32_t at = stage_addr + row * 128 + ((piece ^ (row & 7)) << 4);
+    if (!r.valid) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) st_shared_v4(at + c * kKChunk, make_uint4(0, 0, 0, 0));
+        return;
+    }
+#pragma unroll
+    for (int c = 0; c < 7; ++c) {
+        const uint32_t byte = ((c < 4 ? r.scales.x : r.scales.y) >> ((c & 3) * 8)) & 0xffu;
+        const float s = ue8m0(byte);
+        uint4 v;
+        v.x = e4m3x2_to_bf16x2(r.nope[c].x & 0xffffu, s);
+        v.y = e4m3x2_to_bf16x2(r.nope[c].x >> 16, s);
+        v.z = e4m3x2_to_bf16x2(r.nope[c].y & 0xffffu, s);
+        v.w = e4m3x2_to_bf16x2(r.nope[c].y >> 16, s);
+        st_shared_v4(at + c * kKChunk, v);
+    }
+    st_shared_v4(at + 7 * kKChunk, r.rope);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw_addr);
+    const uint32_t bars = base + kOffBars;
+    // per buffer b in {0, 1}: key block stored, scores complete, scores read, probabilities stored,
+    // weighted sum complete
+    const uint32_t k_full = bars, s_full = bars + 16, s_empty = bars + 32, p_full = bars + 48, pv_done = bars + 64;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + kOffMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kOffMisc + 4);
+    volatile uint8_t* valid_bytes = base_ptr + kOffValid;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = static_cast<int>(lane_id());
+    const int half = blockIdx.x, b = blockIdx.y;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full + i * 8, kProducerWarps);
+            mbar_init(s_full + i * 8, 1);
+            mbar_init(s_empty + i * 8, kSoftmaxWarps);
+            mbar_init(p_full + i * 8, kSoftmaxWarps);
+            mbar_init(pv_done + i * 8, 1);
+        }
+        fence_mbar_init();
+    }
+    if (warp == kIssuerWarp) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
+
+    const int n_swa = p.swa.capacity > 0 ? min(max(__ldg(p.swa.lengths + b), 0), p.swa.capacity) : 0;
+    const int n_cmp = p.cmp.capacity > 0 ? min(max(__ldg(p.cmp.lengths + b), 0), p.cmp.capacity) : 0;
+    const int n_total = n_swa + n_cmp;
+    const int blocks = (n_total + kBlock - 1) / kBlock;
+
+    // the query rows, zero-padded to 128, in the swizzled K-major operand layout
+    for (int i = threadIdx.x; i < kRows * 64; i += kThreads) {
+        const int row = i >> 6, piece = i & 63;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < p.heads)
+            v = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim) + piece);
+        st_shared_v4(base + kOffQ + (piece >> 3) * kQChunk + row * 128 + (((piece & 7) ^ (row & 7)) << 4), v);
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp >= kSoftmaxWarps && warp < kIssuerWarp) {
+        // ------------------------------------------------------------ key producers
+        const int pw = warp - kSoftmaxWarps;
+        const int row = pw * 4 + (lane >> 3), piece = lane & 7;
+        bool bad = false;
+        KeyRegs cur, nxt;
+        fetch_key(p, b, row, n_swa, n_total, piece, cur, &bad);
+        bool alive = true;
+        for (int j = 0; j < blocks && alive; ++j) {
+            const int s = j & 1;
+            nxt.valid = 0;
+            if (j + 1 < blocks) fetch_key(p, b, (j + 1) * kBlock + row, n_swa, n_total, piece, nxt, &bad);
+            if (j >= 2)
+                alive = mbar_wait_warp(pv_done + s * 8, ((j >> 1) - 1) & 1u, abort_flag, p.status, kDevTimeoutMlaOutput);
+            if (!alive) break;
+            store_key(base + kOffK + s * kStageBytes, row, piece, cur);
+            const uint32_t bits = __ballot_sync(0xffffffffu, cur.valid != 0);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                valid_bytes[s * 8 + pw] = static_cast<uint8_t>((bits & 1u) | ((bits >> 7) & 2u) | ((bits >> 14) & 4u) |
+                                                               ((bits >> 21) & 8u));
+                mbar_arrive(k_full + s * 8);
+            }
+            cur = nxt;
+        }
+        if (bad && p.status) atomicCAS(p.status, 0, static_cast<int>(kDevBadPageIndex));
+    } else if (warp == kIssuerWarp) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc_qk = umma_idesc(kRows, kBlock, 1, 1);
+        constexpr uint32_t idesc_pv = umma_idesc_b_mn(kRows, kHalf, 1, 1);
+        bool alive = true;
+        for (int j = 0; j <= blocks && alive; ++j) {
+            if (j < blocks) {
+                const int s = j & 1;
+                alive = mbar_wait_lane0(k_full + s * 8, (j >> 1) & 1u, abort_flag, p.status, kDevTimeoutMlaKeys);
+                if (alive && j >= 2)
+                    alive = mbar_wait_lane0(s_empty + s * 8, ((j >> 1) - 1) & 1u, abort_flag, p.status,
+                                            kDevTimeoutMlaScoresRead);
+                if (!alive) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t q_addr = base + kOffQ, k_addr = base + kOffK + s * kStageBytes;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma_f16(tmem_base + kColS + s * kBlock, umma_smem_desc_sw128(q_addr + c * kQChunk + k * 32),
+                                     umma_smem_desc_sw128(k_addr + c * kKChunk + k * 32), idesc_qk, (c | k) != 0);
+                    umma_commit(s_full + s * 8);
+                }
+                __syncwarp();
+            }
+            if (j >= 1) {
+                const int t = (j - 1) & 1;
+                alive = mbar_wait_lane0(p_full + t * 8, ((j - 1) >> 1) & 1u, abort_flag, p.status, kDevTimeoutMlaProbs);
+                if (!alive) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t p_addr = base + kOffP + t * kPBytes;
+                    const uint32_t v_addr = base + kOffK + t * kStageBytes + half * 4 * kKChunk;
+#pragma unroll
+                    for (int k = 0; k < 2; ++k)   // 16 keys each
+                        umma_f16(tmem_base + kColO, umma_smem_desc_noswz(p_addr + k * 2 * kPPiece, kPPiece, 128),
+                                 umma_smem_desc_mn_sw128(v_addr + k * 16 * 128, kKChunk), idesc_pv, (j - 1 > 0) || k > 0);
+                    umma_commit(pv_done + t * 8);
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax and output
+        const int row = warp * 32 + lane;
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+        float m_ref = -INFINITY, l = 0.0f;
+        bool alive = true;
+        for (int j = 0; j < blocks && alive; ++j) {
+            const int s = j & 1;
+            alive = mbar_wait_warp(s_full + s * 8, (j >> 1) & 1u, abort_flag, p.status, kDevTimeoutMlaScores);
+            if (!alive) break;
+            tc_fence_after();
+            uint32_t v[32];
+            tmem_ld_32x32(lane_addr + kColS + s * kBlock, v);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty + s * 8);
+            // the block's valid bits were published before its keys were announced, and its stage is
+            // not refilled before this block's weighted sum has run
+            const volatile uint32_t* vw = reinterpret_cast<const volatile uint32_t*>(valid_bytes + s * 8);
+            const uint2 vb = make_uint2(vw[0], vw[1]);
+            uint32_t mask = 0;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                mask |= ((vb.x >> (8 * w)) & 0xfu) << (4 * w);
+                mask |= ((vb.y >> (8 * w)) & 0xfu) << (16 + 4 * w);
+            }
+            float x[32], bmax = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                x[i] = (mask >> i) & 1u ? __uint_as_float(v[i]) * p.scale_log2 : -INFINITY;
+                bmax = fmaxf(bmax, x[i]);
+            }
+            const bool grow = bmax > m_ref + kRescaleStep;   // also the first finite maximum
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = grow ? bmax : m_ref;
+                const float f = grow ? ex2(m_ref - m_new) : 1.0f;   // 0 on the first finite maximum
+                if (j > 0) {
+                    alive = mbar_wait_warp(pv_done + ((j - 1) & 1) * 8, ((j - 1) >> 1) & 1u, abort_flag, p.status,
+                                           kDevTimeoutMlaOutput);
+                    if (!alive) break;
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < kHalf; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld_32x32(lane_addr + kColO + c, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                        tmem_st_32x32(lane_addr + kColO + c, o);
+                    }
+                    tmem_st_wait();
+                    tc_fence_before();
+                }
+                l *= f;
+                m_ref = m_new;
+            }
+            float sum = 0.0f;
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const float e0 = m_ref == -INFINITY ? 0.0f : ex2(x[i] - m_ref);
+                const float e1 = m_ref == -INFINITY ? 0.0f : ex2(x[i + 1] - m_ref);
+                sum += e0 + e1;
+                const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+                pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            l += sum;
+            if (j >= 2) {   // the weighted sum of block j-2 has read this probability buffer
+                alive = mbar_wait_warp(pv_done + s * 8, ((j >> 1) - 1) & 1u, abort_flag, p.status, kDevTimeoutMlaOutput);
+                if (!alive) break;
+            }
+            const uint32_t p_addr = base + kOffP + s * kPBytes + row * 16;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                st_shared_v4(p_addr + c * kPPiece, make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]));
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full + s * 8);
+        }
+        if (alive && blocks > 0)
+            alive = mbar_wait_warp(pv_done + ((blocks - 1) & 1) * 8, ((blocks - 1) >> 1) & 1u, abort_flag, p.status,
+                                   kDevTimeoutMlaOutput);
+        if (alive) {
+            tc_fence_after();
+            const bool any = blocks > 0 && m_ref != -INFINITY;
+            float inv = 0.0f;
+            if (any) {
+                const float sink = (p.sink && row < p.heads) ? ex2(__ldg(p.sink + row) * kLog2e - m_ref) : 0.0f;
+                inv = 1.0f / (l + sink);   // an overwhelming sink gives 1 / inf = 0
+            }
+            __nv_bfloat16* dst = p.out + (static_cast<int64_t>(b) * p.heads + row) * kDim + half * kHalf;
+#pragma unroll 1
+            for (int c = 0; c < kHalf; c += 32) {
+                uint32_t o[32];
+                if (blocks > 0) {   // warp-uniform: without a block the accumulator was never written
+                    tmem_ld_32x32(lane_addr + kColO + c, o);
+                    tmem_ld_wait();
+                }
+                if (row < p.heads) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float lo = any ? __uint_as_float(o[i + 2 * k]) * inv : 0.0f;
+                            const float hi = any ? __uint_as_float(o[i + 2 * k + 1]) * inv : 0.0f;
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                            w[k] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    }
+
+    __syncthreads();
+    if (*abort_flag) abort_drain_sleep();
+    __syncthreads();
+    if (warp == kIssuerWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+static int check_pool(const char* name, const void* data, int64_t stride, int pages, int epb, const int32_t* indices,
+                      const int32_t* lengths, int capacity, Pool* out) {
+    WUDA_REQUIRE(capacity >= 0, "%s_capacity must be >= 0 (got %d)", name, capacity);
+    out->capacity = capacity;
+    if (capacity == 0) {
+        out->data = nullptr, out->indices = nullptr, out->lengths = nullptr;
+        out->stride = 0, out->pages = 0, out->epb = 1;
+        return WUDA_OK;
+    }
+    WUDA_REQUIRE(data && indices && lengths, "%s pool, indices and lengths must not be NULL when its capacity is > 0", name);
+    WUDA_REQUIRE(pages >= 1 && epb >= 1, "%s pages and entries_per_block must be >= 1", name);
+    WUDA_REQUIRE(aligned16(data) && stride % 16 == 0, "%s pool base and page stride must be multiples of 16 bytes", name);
+    WUDA_REQUIRE(stride >= static_cast<int64_t>(epb) * (kBody + kScaleRec),
+                 "%s page stride %lld is smaller than %d records of 584 bytes", name, static_cast<long long>(stride), epb);
+    WUDA_REQUIRE((static_cast<int64_t>(epb) * kBody) % 8 == 0, "%s scale records must start on an 8-byte boundary", name);
+    out->data = static_cast<const uint8_t*>(data);
+    out->stride = stride;
+    out->pages = pages;
+    out->epb = epb;
+    out->indices = indices;
+    out->lengths = lengths;
+    return WUDA_OK;
+}
+
+}  // namespace mla
+}  // namespace wuda
+
+extern "C" int wuda_sparse_mla_decode(const wuda_sparse_mla_args* a, int32_t* status_word, void* stream) {
+    using namespace wuda;
+    using namespace wuda::mla;
+    clear_error();
+    WUDA_REQUIRE(a != nullptr, "args must not be NULL");
+    WUDA_REQUIRE(a->batch >= 0, "batch must be >= 0 (got %d)", a->batch);
+    WUDA_REQUIRE(a->heads >= 1 && a->heads <= kRows, "heads must be in [1, 128] (got %d)", a->heads);
+    if (a->batch == 0) return WUDA_OK;
+    WUDA_REQUIRE(a->batch <= 65535, "batch must be <= 65535 (got %d)", a->batch);
+    WUDA_REQUIRE(a->q && a->out, "q and out must not be NULL");
+    WUDA_REQUIRE(aligned16(a->q) && aligned16(a->out), "q and out must be 16-byte aligned");
+    WUDA_REQUIRE(a->softmax_scale > 0.0f && a->softmax_scale < 1e30f, "softmax_scale must be positive and finite");
+    Params p;
+    int st = check_pool("swa", a->swa_pool, a->swa_stride, a->swa_pages, a->swa_entries_per_block, a->swa_indices,
+                        a->swa_lengths, a->swa_capacity, &p.swa);
+    if (st != WUDA_OK) return st;
+    st = check_pool("cmp", a->cmp_pool, a->cmp_stride, a->cmp_pages, a->cmp_entries_per_block, a->cmp_indices,
+                    a->cmp_lengths, a->cmp_capacity, &p.cmp);
+    if (st != WUDA_OK) return st;
+    p.q = static_cast<const __nv_bfloat16*>(a->q);
+    p.sink = a->attn_sink;
+    p.scale_log2 = a->softmax_scale * kLog2e;
+    p.out = static_cast<__nv_bfloat16*>(a->out);
+    p.heads = a->heads;
+    p.status = status_word;
+
+    DeviceInfo dev;
+    st = current_device_info(&dev);
+    if (st != WUDA_OK) return st;
+    if (static_cast<int>(kSmemBytes) > dev.smem_optin)
+        return fail(WUDA_ERR_UNSUPPORTED, "device offers %d bytes of shared memory per block; the kernel needs %u",
+                    dev.smem_optin, kSmemBytes);
+    WUDA_CUDA(cudaFuncSetAttribute(sparse_mla_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    WUDA_CUDA(launch_pdl(sparse_mla_kernel, dim3(2, a->batch), dim3(kThreads), kSmemBytes,
+                         static_cast<cudaStream_t>(stream), p));
+    return WUDA_OK;
+}

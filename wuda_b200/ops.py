@@ -14,7 +14,7 @@ from . import _lib
 from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
-           "IndexerHostPlan", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
+           "IndexerHostPlan", "sparse_mla_decode", "flash_mla_with_kvcache", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
            "rmsnorm_rope_out", "mhc_post_out", "mhc_pre", "moe_gate", "bf16_gemm", "front_mixed_gemm", "idx_postprocess_fp8", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
 
 NUM_INDEX_HEADS = 64
@@ -290,6 +290,80 @@ def mhc_post_out(attention_out, residual, post, comb, output):
 
 def _ptr(t):
     return t.data_ptr() if t is not None else None
+
+
+def _model1_pool(cache, name):
+    """(pointer, page stride, pages, entries) of a MODEL1 pool given either as uint8 [pages, stride]
+    with an explicit entry count, or as the strided [pages, entries, 1, 584] view the cache manager hands
+    to the attention (kv_cache.KVCacheManager.model1_cache_view)."""
+    _require(cache.is_cuda and cache.element_size() == 1 and cache.dim() == 4 and cache.size(3) == 584
+             and cache.stride(3) == 1 and cache.stride(1) == 584,
+             f"{name} must be a CUDA 1-byte [pages, entries, 1, 584] view of a MODEL1 pool")
+    return cache.data_ptr(), cache.stride(0), cache.size(0), cache.size(1)
+
+
+def sparse_mla_decode(q, swa_cache, swa_indices, swa_lengths, cmp_cache=None, cmp_indices=None, cmp_lengths=None,
+                      attn_sink=None, softmax_scale=None, *, out=None, status_word=None):
+    """Decode attention of q bf16 [batch, heads, 512] over gathered MODEL1 records: swa_lengths[b] entries of
+    swa_indices[b] in swa_cache, then cmp_lengths[b] entries of cmp_indices[b] in cmp_cache (pool entry
+    indices, negative = skipped), with the attention sink in the denominator.  Returns bf16
+    [batch, heads, 512]."""
+    _require(q.is_cuda and q.is_contiguous() and q.dtype == torch.bfloat16 and q.dim() == 3 and q.size(2) == 512,
+             "q must be contiguous CUDA bf16 [batch, heads, 512]")
+    batch, heads = q.size(0), q.size(1)
+    a = _lib.SparseMlaArgs()
+    a.q, a.batch, a.heads = q.data_ptr(), batch, heads
+    a.softmax_scale = float(softmax_scale if softmax_scale is not None else 512 ** -0.5)
+    for name, cache, idx, lens in (("swa", swa_cache, swa_indices, swa_lengths), ("cmp", cmp_cache, cmp_indices, cmp_lengths)):
+        if cache is None:
+            setattr(a, name + "_capacity", 0)
+            continue
+        ptr, stride, pages, entries = _model1_pool(cache, name + "_cache")
+        _require(idx.is_cuda and idx.is_contiguous() and idx.dtype == torch.int32 and idx.numel() % max(batch, 1) == 0,
+                 f"{name}_indices must be contiguous CUDA int32 [batch, capacity]")
+        _require(lens.is_cuda and lens.is_contiguous() and lens.dtype == torch.int32 and lens.numel() == batch,
+                 f"{name}_lengths must be contiguous CUDA int32 [batch]")
+        setattr(a, name + "_pool", ptr)
+        setattr(a, name + "_stride", stride)
+        setattr(a, name + "_pages", pages)
+        setattr(a, name + "_entries_per_block", entries)
+        setattr(a, name + "_indices", idx.data_ptr())
+        setattr(a, name + "_lengths", lens.data_ptr())
+        setattr(a, name + "_capacity", idx.numel() // max(batch, 1))
+    if attn_sink is not None:
+        _require(attn_sink.is_cuda and attn_sink.is_contiguous() and attn_sink.dtype == torch.float32
+                 and attn_sink.numel() == heads, "attn_sink must be contiguous CUDA fp32 [heads]")
+        a.attn_sink = attn_sink.data_ptr()
+    if out is None:
+        out = torch.empty_like(q)
+    _require(out.is_cuda and out.is_contiguous() and out.dtype == torch.bfloat16 and out.shape == q.shape,
+             "out must be contiguous CUDA bf16 shaped like q")
+    a.out = out.data_ptr()
+    check(lib.wuda_sparse_mla_decode(ctypes.byref(a), _ptr(status_word), _stream()))
+    return out
+
+
+def flash_mla_with_kvcache(q, k_cache, block_table=None, cache_seqlens=None, head_dim_v=512,
+                           tile_scheduler_metadata=None, num_splits=None, softmax_scale=None, causal=False,
+                           is_fp8_kvcache=True, indices=None, topk_length=None, extra_k_cache=None,
+                           extra_indices_in_kvcache=None, extra_topk_length=None, attn_sink=None):
+    """The sparse FP8 decode call of the layer step with the keyword list it is made with at
+    test/test_e2e_decode.py:719-728: q bf16 [batch, 1, heads, 512]; k_cache / extra_k_cache MODEL1 views;
+    indices [batch, 1, topk] with topk_length [batch] for the first pool, extra_* for the second.  Only this
+    form (sparse indices, FP8 records, one query token, value = key) is implemented; the scheduler metadata
+    is accepted and ignored.  Returns (out bf16 [batch, 1, heads, 512], None)."""
+    _require(is_fp8_kvcache and indices is not None and block_table is None and cache_seqlens is None and not causal,
+             "only the sparse FP8 form (indices given, no block table, not causal) is implemented")
+    _require(head_dim_v == 512 and q.dim() == 4 and q.size(1) == 1, "q must be [batch, 1, heads, 512] with head_dim_v 512")
+    batch, heads = q.size(0), q.size(2)
+    if topk_length is None:
+        topk_length = torch.full((batch,), indices.size(-1), dtype=torch.int32, device=q.device)
+    if extra_k_cache is not None and extra_topk_length is None:
+        extra_topk_length = torch.full((batch,), extra_indices_in_kvcache.size(-1), dtype=torch.int32, device=q.device)
+    out = sparse_mla_decode(q.view(batch, heads, 512), k_cache, indices.reshape(batch, -1), topk_length, extra_k_cache,
+                            None if extra_k_cache is None else extra_indices_in_kvcache.reshape(batch, -1),
+                            extra_topk_length, attn_sink, softmax_scale)
+    return out.view(batch, 1, heads, 512), None
 
 
 def _f32(t, name, last=None):
