@@ -396,12 +396,19 @@ typedef struct wuda_sparse_mla_args {
     const int32_t* cmp_lengths;  /* int32 [batch]                                           */
     const float* attn_sink;      /* fp32 [heads] or NULL                                    */
     void* out;                   /* bf16 [batch, heads, 512]                                */
+    void* workspace;             /* wuda_sparse_mla_workspace_bytes(...) bytes, or NULL      */
+    int64_t workspace_bytes;
     int32_t swa_pages, swa_entries_per_block, swa_capacity;
     int32_t cmp_pages, cmp_entries_per_block, cmp_capacity;
     int32_t batch, heads;
     float softmax_scale;
 } wuda_sparse_mla_args;
 
+/* With a workspace, a small batch is spread over the whole device: several CTAs take runs of a
+ * request's keys and a second launch merges their partial sums (same arithmetic, another order of
+ * the fp32 additions).  Bytes needed for key_capacity = swa_capacity + cmp_capacity; 0 when the batch
+ * fills the device by itself; -1 on bad arguments.  Without a workspace (NULL) requests are never split. */
+int64_t wuda_sparse_mla_workspace_bytes(int batch, int heads, int key_capacity);
 int wuda_sparse_mla_decode(const wuda_sparse_mla_args* args, int32_t* status_word, void* stream);
 
 /* ------------------------------------------------------------------------------------

@@ -67,7 +67,7 @@ def check_close(got_u16, ref):
     assert np.all(got[~live] == 0)
 
 
-def run(wuda, q, swa, cmp, sink, scale=SCALE):
+def run(wuda, q, swa, cmp, sink, scale=SCALE, split=True):
     """swa / cmp = None or (pool, epb, idx, lens) in numpy; q uint16 [batch, heads, 512]."""
     status = wuda.device_status_word()
     status.zero_()
@@ -78,7 +78,7 @@ def run(wuda, q, swa, cmp, sink, scale=SCALE):
         else:
             args += [view4(t[0], t[1]), torch.from_numpy(t[2]).cuda(), torch.from_numpy(np.asarray(t[3], np.int32)).cuda()]
     out = wuda.sparse_mla_decode(from_u16(q), *args, None if sink is None else torch.from_numpy(sink).cuda(), scale,
-                                 status_word=status)
+                                 status_word=status, split=split)
     torch.cuda.synchronize()
     return u16(out), int(status.item())
 
@@ -100,7 +100,8 @@ def test_golden(wuda):
     (2, 128, [128, 40], [1024, 700], 0, True, 8.0),       # peaked softmax: the running maximum grows often
     (4, 128, [0, 5, 0, 128], [0, 0, 0, 2048], 0, True, 1.0),   # requests without any key give zero rows
 ])
-def test_against_oracle(wuda, batch, heads, swa_lens, cmp_lens, holes, with_sink, q_gain):
+@pytest.mark.parametrize("split", [False, True])   # one CTA per request and half / several with a merge launch
+def test_against_oracle(wuda, batch, heads, swa_lens, cmp_lens, holes, with_sink, q_gain, split):
     rng = np.random.default_rng(batch * 1009 + heads * 31 + int(q_gain))
     swa = cmp = None
     if swa_lens is not None:
@@ -111,7 +112,7 @@ def test_against_oracle(wuda, batch, heads, swa_lens, cmp_lens, holes, with_sink
         cmp = (pool, 64, indices(rng, batch, 2048, cmp_lens, 40 * 64, holes), cmp_lens)
     q = oracle.f32_to_bf16((rng.standard_normal((batch, heads, 512)) * q_gain).astype(np.float32))
     sink = rng.standard_normal(heads).astype(np.float32) if with_sink else None
-    got, status = run(wuda, q, swa, cmp, sink)
+    got, status = run(wuda, q, swa, cmp, sink, split=split)
     assert status == 0
     check_close(got, oracle.sparse_mla(q, swa, cmp, sink, SCALE))
 
@@ -130,9 +131,11 @@ def test_rising_logits_rescale_the_accumulator(wuda):
         one = oracle.sparse_mla(q[:, :1], None, (pool, 64, np.array([[t]], np.int32), [1]), None, SCALE)[0, 0]
         logits.append(float(qf @ one.astype(np.float64)))   # one key: the output is the key itself
     order = np.argsort(np.asarray(logits)).astype(np.int32)[None, :]
-    got, status = run(wuda, q, None, (pool, 64, order, [n]), None)
-    assert status == 0
-    check_close(got, oracle.sparse_mla(q, None, (pool, 64, order, [n]), None, SCALE))
+    ref = oracle.sparse_mla(q, None, (pool, 64, order, [n]), None, SCALE)
+    for split in (False, True):
+        got, status = run(wuda, q, None, (pool, 64, order, [n]), None, split=split)
+        assert status == 0
+        check_close(got, ref)
 
 
 def test_reference_call_form(wuda):

@@ -76,7 +76,7 @@ class SparseMlaArgs(ctypes.Structure):
     """wuda_sparse_mla_args"""
     _fields_ = [("q", c_vp), ("swa_pool", c_vp), ("swa_stride", c_i64), ("swa_indices", c_vp), ("swa_lengths", c_vp),
                 ("cmp_pool", c_vp), ("cmp_stride", c_i64), ("cmp_indices", c_vp), ("cmp_lengths", c_vp),
-                ("attn_sink", c_vp), ("out", c_vp),
+                ("attn_sink", c_vp), ("out", c_vp), ("workspace", c_vp), ("workspace_bytes", c_i64),
                 ("swa_pages", ctypes.c_int32), ("swa_entries_per_block", ctypes.c_int32), ("swa_capacity", ctypes.c_int32),
                 ("cmp_pages", ctypes.c_int32), ("cmp_entries_per_block", ctypes.c_int32), ("cmp_capacity", ctypes.c_int32),
                 ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("softmax_scale", c_float)]
@@ -100,6 +100,7 @@ SIGNATURES = {
     "wuda_query_rms_rope": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_int, c_vp, c_int, c_int, c_int, c_float, c_vp]),
     "wuda_csa_decode_step": (c_int, [ctypes.POINTER(CsaWeights), ctypes.POINTER(CsaCaches), ctypes.POINTER(CsaStep),
                                      ctypes.POINTER(CsaWorkspace), c_int, c_vp]),
+    "wuda_sparse_mla_workspace_bytes": (c_i64, [c_int, c_int, c_int]),
     "wuda_sparse_mla_decode": (c_int, [ctypes.POINTER(SparseMlaArgs), c_vp, c_vp]),
     "wuda_mhc_pre_workspace_bytes": (c_i64, [c_int, c_int]),
     "wuda_mhc_pre": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_float, c_float, c_vp, c_vp, c_vp, c_vp, c_vp,

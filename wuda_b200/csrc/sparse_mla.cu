@@ -47,6 +47,8 @@ constexpr int kProducerWarps = 8;
 constexpr int kIssuerWarp = kSoftmaxWarps + kProducerWarps;
 constexpr int kThreads = (kIssuerWarp + 1) * 32;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kAhead = 3;             // blocks whose records are in flight ahead of the one being stored
+constexpr int kMaxSplits = 32;        // CTAs that may share one request's keys (per output half)
 constexpr float kRescaleStep = 8.0f;   // log2 units the block maximum may exceed the reference by
 
 // shared memory, offsets from a 1024-byte aligned base
@@ -85,6 +87,8 @@ struct Params {
     __nv_bfloat16* out;       // [batch, heads, 512]
     int heads;
     int* status;
+    float* part_o;            // [batch, splits, heads, 512] unnormalised sums, when a request is split
+    float* part_ml;           // [batch, splits, heads, 2] reference maximum (log2 units) and sum
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -200,7 +204,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
     const int n_swa = p.swa.capacity > 0 ? min(max(__ldg(p.swa.lengths + b), 0), p.swa.capacity) : 0;
     const int n_cmp = p.cmp.capacity > 0 ? min(max(__ldg(p.cmp.lengths + b), 0), p.cmp.capacity) : 0;
     const int n_total = n_swa + n_cmp;
-    const int blocks = (n_total + kBlock - 1) / kBlock;
+    // the CTAs of a request that share an output half each take a contiguous run of its key blocks
+    const int all_blocks = (n_total + kBlock - 1) / kBlock;
+    const int per_split = (all_blocks + static_cast<int>(gridDim.z) - 1) / static_cast<int>(gridDim.z);
+    const int first = static_cast<int>(blockIdx.z) * per_split;
+    const int blocks = min(max(all_blocks - first, 0), per_split);
 
     // the query rows, zero-padded to 128, in the swizzled K-major operand layout
     for (int i = threadIdx.x; i < kRows * 64; i += kThreads) {
@@ -221,26 +229,33 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         const int pw = warp - kSoftmaxWarps;
         const int row = pw * 4 + (lane >> 3), piece = lane & 7;
         bool bad = false;
-        KeyRegs cur, nxt;
-        fetch_key(p, b, row, n_swa, n_total, piece, cur, &bad);
+        // a block's records are requested kAhead blocks before they are converted: a gather from
+        // random pages takes far longer than one block's turn through the pipeline
+        KeyRegs ring[kAhead + 1];
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) fetch_key(p, b, (first + u) * kBlock + row, n_swa, n_total, piece, ring[u], &bad);
         bool alive = true;
-        for (int j = 0; j < blocks && alive; ++j) {
-            const int s = j & 1;
-            nxt.valid = 0;
-            if (j + 1 < blocks) fetch_key(p, b, (j + 1) * kBlock + row, n_swa, n_total, piece, nxt, &bad);
-            if (j >= 2)
-                alive = mbar_wait_warp(pv_done + s * 8, ((j >> 1) - 1) & 1u, abort_flag, p.status, kDevTimeoutMlaOutput);
-            if (!alive) break;
-            store_key(base + kOffK + s * kStageBytes, row, piece, cur);
-            const uint32_t bits = __ballot_sync(0xffffffffu, cur.valid != 0);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                valid_bytes[s * 8 + pw] = static_cast<uint8_t>((bits & 1u) | ((bits >> 7) & 2u) | ((bits >> 14) & 4u) |
-                                                               ((bits >> 21) & 8u));
-                mbar_arrive(k_full + s * 8);
+        for (int j0 = 0; j0 < blocks && alive; j0 += kAhead + 1) {
+#pragma unroll
+            for (int u = 0; u <= kAhead; ++u) {
+                const int j = j0 + u;
+                if (j >= blocks) break;
+                const int s = j & 1;
+                fetch_key(p, b, (first + j + kAhead) * kBlock + row, n_swa, n_total, piece, ring[(u + kAhead) % (kAhead + 1)],
+                          &bad);
+                if (j >= 2)
+                    alive = mbar_wait_warp(pv_done + s * 8, ((j >> 1) - 1) & 1u, abort_flag, p.status, kDevTimeoutMlaOutput);
+                if (!alive) break;
+                store_key(base + kOffK + s * kStageBytes, row, piece, ring[u]);
+                const uint32_t bits = __ballot_sync(0xffffffffu, ring[u].valid != 0);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    valid_bytes[s * 8 + pw] = static_cast<uint8_t>((bits & 1u) | ((bits >> 7) & 2u) | ((bits >> 14) & 4u) |
+                                                                   ((bits >> 21) & 8u));
+                    mbar_arrive(k_full + s * 8);
+                }
             }
-            cur = nxt;
         }
         if (bad && p.status) atomicCAS(p.status, 0, static_cast<int>(kDevBadPageIndex));
     } else if (warp == kIssuerWarp) {
@@ -369,7 +384,30 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         if (alive && blocks > 0)
             alive = mbar_wait_warp(pv_done + ((blocks - 1) & 1) * 8, ((blocks - 1) >> 1) & 1u, abort_flag, p.status,
                                    kDevTimeoutMlaOutput);
-        if (alive) {
+        if (alive && gridDim.z > 1) {
+            // partial result of this run of blocks: the unnormalised sums with their reference maximum
+            tc_fence_after();
+            const int64_t slot = (static_cast<int64_t>(b) * gridDim.z + blockIdx.z) * p.heads + row;
+            if (row < p.heads && half == 0) {
+                p.part_ml[slot * 2] = blocks > 0 ? m_ref : -INFINITY;
+                p.part_ml[slot * 2 + 1] = blocks > 0 ? l : 0.0f;
+            }
+            if (blocks > 0) {   // the combine step skips partials whose maximum is -inf
+                float* dst = p.part_o + slot * kDim + half * kHalf;
+#pragma unroll 1
+                for (int c = 0; c < kHalf; c += 32) {
+                    uint32_t o[32];
+                    tmem_ld_32x32(lane_addr + kColO + c, o);
+                    tmem_ld_wait();
+                    if (row < p.heads) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+                    }
+                }
+            }
+            tc_fence_before();
+        } else if (alive) {
             tc_fence_after();
             const bool any = blocks > 0 && m_ref != -INFINITY;
             float inv = 0.0f;
@@ -413,6 +451,45 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
     }
 }
 
+// Merges the partial results of a split request: weights 2^(m_z - max m), the sink in the denominator.
+__global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const Params p, int splits) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int64_t first = (static_cast<int64_t>(b) * splits) * p.heads + h;
+    float m = -INFINITY;
+    for (int z = 0; z < splits; ++z) m = fmaxf(m, p.part_ml[(first + static_cast<int64_t>(z) * p.heads) * 2]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.0f;
+    if (m != -INFINITY) {
+        for (int z = 0; z < splits; ++z) {
+            const int64_t slot = first + static_cast<int64_t>(z) * p.heads;
+            const float mz = p.part_ml[slot * 2];
+            if (mz == -INFINITY) continue;
+            const float w = ex2(mz - m);
+            den += w * p.part_ml[slot * 2 + 1];
+            const float4 o = *reinterpret_cast<const float4*>(p.part_o + slot * kDim + threadIdx.x * 4);
+            acc.x += w * o.x, acc.y += w * o.y, acc.z += w * o.z, acc.w += w * o.w;
+        }
+        if (p.sink) den += ex2(__ldg(p.sink + h) * kLog2e - m);
+    }
+    const float inv = m != -INFINITY ? 1.0f / den : 0.0f;
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    uint2 v;
+    v.x = *reinterpret_cast<const uint32_t*>(&lo);
+    v.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p.out + (static_cast<int64_t>(b) * p.heads + h) * kDim + threadIdx.x * 4) = v;
+}
+
+// CTAs per request and output half: enough to give every SM one, at least two key blocks each.
+static int splits_for(int batch, int key_capacity, int num_sms) {
+    const int blocks = (key_capacity + kBlock - 1) / kBlock;
+    int s = num_sms / (2 * batch);
+    if (s > blocks / 2) s = blocks / 2;
+    if (s > kMaxSplits) s = kMaxSplits;
+    return s < 1 ? 1 : s;
+}
+
 static int check_pool(const char* name, const void* data, int64_t stride, int pages, int epb, const int32_t* indices,
                       const int32_t* lengths, int capacity, Pool* out) {
     WUDA_REQUIRE(capacity >= 0, "%s_capacity must be >= 0 (got %d)", name, capacity);
@@ -439,6 +516,17 @@ static int check_pool(const char* name, const void* data, int64_t stride, int pa
 
 }  // namespace mla
 }  // namespace wuda
+
+extern "C" int64_t wuda_sparse_mla_workspace_bytes(int batch, int heads, int key_capacity) {
+    using namespace wuda;
+    using namespace wuda::mla;
+    if (batch < 1 || heads < 1 || heads > kRows || key_capacity < 0) return -1;
+    DeviceInfo dev;
+    if (current_device_info(&dev) != WUDA_OK) return -1;
+    const int splits = splits_for(batch, key_capacity, dev.num_sms);
+    if (splits <= 1) return 0;
+    return static_cast<int64_t>(batch) * splits * heads * (kDim + 2) * 4;
+}
 
 extern "C" int wuda_sparse_mla_decode(const wuda_sparse_mla_args* a, int32_t* status_word, void* stream) {
     using namespace wuda;
@@ -472,8 +560,22 @@ extern "C" int wuda_sparse_mla_decode(const wuda_sparse_mla_args* a, int32_t* st
     if (static_cast<int>(kSmemBytes) > dev.smem_optin)
         return fail(WUDA_ERR_UNSUPPORTED, "device offers %d bytes of shared memory per block; the kernel needs %u",
                     dev.smem_optin, kSmemBytes);
+    int splits = a->workspace ? splits_for(a->batch, a->swa_capacity + a->cmp_capacity, dev.num_sms) : 1;
+    if (splits > 1) {
+        const int64_t need = wuda_sparse_mla_workspace_bytes(a->batch, a->heads, a->swa_capacity + a->cmp_capacity);
+        WUDA_REQUIRE(a->workspace_bytes >= need, "workspace holds %lld bytes; %lld are needed (wuda_sparse_mla_workspace_bytes)",
+                     static_cast<long long>(a->workspace_bytes), static_cast<long long>(need));
+        WUDA_REQUIRE(aligned16(a->workspace), "workspace must be 16-byte aligned");
+        p.part_o = static_cast<float*>(a->workspace);
+        p.part_ml = p.part_o + static_cast<int64_t>(a->batch) * splits * a->heads * kDim;
+    } else {
+        p.part_o = p.part_ml = nullptr;
+    }
     WUDA_CUDA(cudaFuncSetAttribute(sparse_mla_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    WUDA_CUDA(launch_pdl(sparse_mla_kernel, dim3(2, a->batch), dim3(kThreads), kSmemBytes,
+    WUDA_CUDA(launch_pdl(sparse_mla_kernel, dim3(2, a->batch, splits), dim3(kThreads), kSmemBytes,
                          static_cast<cudaStream_t>(stream), p));
+    if (splits > 1)
+        WUDA_CUDA(launch_pdl(sparse_mla_combine_kernel, dim3(a->heads, a->batch), dim3(128), 0,
+                             static_cast<cudaStream_t>(stream), p, splits));
     return WUDA_OK;
 }

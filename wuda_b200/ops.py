@@ -292,6 +292,9 @@ def _ptr(t):
     return t.data_ptr() if t is not None else None
 
 
+_mla_workspace = {}   # per device: partial sums of split requests (grown on demand)
+
+
 def _model1_pool(cache, name):
     """(pointer, page stride, pages, entries) of a MODEL1 pool given either as uint8 [pages, stride]
     with an explicit entry count, or as the strided [pages, entries, 1, 584] view the cache manager hands
@@ -303,7 +306,7 @@ def _model1_pool(cache, name):
 
 
 def sparse_mla_decode(q, swa_cache, swa_indices, swa_lengths, cmp_cache=None, cmp_indices=None, cmp_lengths=None,
-                      attn_sink=None, softmax_scale=None, *, out=None, status_word=None):
+                      attn_sink=None, softmax_scale=None, *, out=None, status_word=None, split=True):
     """Decode attention of q bf16 [batch, heads, 512] over gathered MODEL1 records: swa_lengths[b] entries of
     swa_indices[b] in swa_cache, then cmp_lengths[b] entries of cmp_indices[b] in cmp_cache (pool entry
     indices, negative = skipped), with the attention sink in the denominator.  Returns bf16
@@ -339,6 +342,14 @@ def sparse_mla_decode(q, swa_cache, swa_indices, swa_lengths, cmp_cache=None, cm
     _require(out.is_cuda and out.is_contiguous() and out.dtype == torch.bfloat16 and out.shape == q.shape,
              "out must be contiguous CUDA bf16 shaped like q")
     a.out = out.data_ptr()
+    if split and batch > 0:   # small batches: several CTAs per request, merged by a second launch
+        need = lib.wuda_sparse_mla_workspace_bytes(batch, heads, a.swa_capacity + a.cmp_capacity)
+        _require(need >= 0, "wuda_sparse_mla_workspace_bytes rejected the shape")
+        if need > 0:
+            ws = _mla_workspace.get(q.device)
+            if ws is None or ws.numel() < need:
+                ws = _mla_workspace[q.device] = torch.empty(need, dtype=torch.uint8, device=q.device)
+            a.workspace, a.workspace_bytes = ws.data_ptr(), need
     check(lib.wuda_sparse_mla_decode(ctypes.byref(a), _ptr(status_word), _stream()))
     return out
 
