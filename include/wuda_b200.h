@@ -338,7 +338,10 @@ typedef struct wuda_csa_step {
     const int64_t* idx_dst;
     const int64_t* cmp_dst;
     const int64_t* swa_dst;
-    const int32_t* idx_block_table; /* int32 [m, block_table_stride]                           */
+    const int32_t* idx_block_table; /* int32 [m, block_table_stride]: pages of the indexer pool */
+    const int32_t* cmp_block_table; /* int32 [m, block_table_stride]: pages the top-k positions are
+                                       translated with (the compressed-KV pool the attention reads,
+                                       test/test_e2e_decode.py:655-657); NULL = idx_block_table  */
     const int32_t* n_compressed;    /* int32 [m]                                               */
     int block_table_stride;
     int topk;

@@ -34,6 +34,7 @@ def make_stage(batch, seed):
     weights = CsaWeights(index_heads=INDEX_HEADS, main_heads=MAIN_HEADS, out_heads=OUT_HEADS,
                          **{k: v.cuda() for k, v in host.items()})
     cache = KVCacheManager(batch + 1, 64, 8, device="cuda")
+    cache._pools["cmp"].take()   # the compressed-KV pool numbers its pages one off the indexer pool's
     stage = CsaDecodeStage(weights, cache, batch, topk=TOPK)
     return stage, cache, {k: v.numpy() for k, v in host.items()}, g
 
@@ -97,7 +98,8 @@ def check_step(stage, cache, host, st, m, before):
     # 6 logits over the GPU's pool with the GPU's q, 7 top-k over the GPU's logits
     ncmp = stage.n_compressed[:m].cpu().numpy()
     assert np.array_equal(ncmp, (pos + 1) // 4)
-    bt = stage.block_table[:m].cpu().numpy()
+    bt, cmp_bt = stage.block_table[:m].cpu().numpy(), stage.cmp_block_table[:m].cpu().numpy()
+    assert not np.array_equal(bt, cmp_bt)    # the two pools number their pages differently here
     logits = stage.logits[:m].cpu().numpy()
     ref_l = oracle.mqa_logits_fp8(stage.iq_fp8[:m].cpu().numpy(), got["idx"], stage.w_folded[:m].cpu().numpy(),
                                   ncmp.reshape(m, 1), bt, 1, cache.entries_per_block["idx"], stage.logits_stride)
@@ -106,7 +108,8 @@ def check_step(stage, cache, host, st, m, before):
     rms = np.sqrt(np.mean(ref_l[valid].astype(np.float64) ** 2))
     assert np.all(np.abs(logits[valid] - ref_l[valid]) <= 1e-2 * np.abs(ref_l[valid]) + 1e-4 * rms)
     masked = np.where(valid, logits, -np.inf).astype(np.float32)
-    ref_pages, ref_raw = oracle.topk(masked, ncmp, bt, TOPK, cache.entries_per_block["idx"])
+    # positions are translated with the pages of the compressed-KV pool, which the attention reads
+    ref_pages, ref_raw = oracle.topk(masked, ncmp, cmp_bt, TOPK, cache.entries_per_block["cmp"])
     got_pages, got_raw = stage.topk_indices[:m].cpu().numpy(), stage.topk_raw[:m].cpu().numpy()
     for r in range(m):
         assert sorted(got_raw[r].tolist()) == sorted(ref_raw[r].tolist())

@@ -61,7 +61,7 @@ class CsaStep(ctypes.Structure):
     """wuda_csa_step"""
     _fields_ = [("q_raw", c_vp), ("q_raw_stride", c_i64), ("w64", c_vp), ("win_y2", c_vp), ("pos", c_vp),
                 ("q_pos", c_vp), ("main_state_row", c_vp), ("idx_state_row", c_vp), ("idx_dst", c_vp), ("cmp_dst", c_vp),
-                ("swa_dst", c_vp), ("idx_block_table", c_vp), ("n_compressed", c_vp), ("block_table_stride", c_int),
+                ("swa_dst", c_vp), ("idx_block_table", c_vp), ("cmp_block_table", c_vp), ("n_compressed", c_vp), ("block_table_stride", c_int),
                 ("topk", c_int), ("logits_stride", c_i64), ("logits", c_vp), ("topk_indices", c_vp), ("topk_raw", c_vp),
                 ("q_main_out", c_vp)]
 

@@ -266,7 +266,7 @@ def csa_chain(batch=64, context=32768, topk=2048, reps=30, launches_only=0):
 def attention_half_layer(batch=64, context=32768, topk=2048, reps=30, launches_only=0):
     """Every built stage of the attention half-layer in order, one CUDA graph: mHC pre -> front mixed
     GEMM + FRONT-EMIT -> indexer half-step (q norm/quant, q projection, tails, cache writers, MQA
-    logits, top-k) -> [sparse attention: not built; its output is a constant stand-in tensor] ->
+    logits, top-k) -> sparse MLA attention over the window and the top-k compressed records ->
     inverse RoPE + quant, grouped wo_a, quant, wo_b -> mHC post.  Model geometry (hidden 7168,
     128 heads of 512, 16 output groups), random weights, L2 flushed before every timed replay."""
     from wuda_b200 import o_proj
@@ -306,7 +306,15 @@ def attention_half_layer(batch=64, context=32768, topk=2048, reps=30, launches_o
     ape, idx_ape = torch.randn(4, 1024, generator=g, device=dev), torch.randn(4, 256, generator=g, device=dev)
     oproj = o_proj.OProjWeights(rnd8(16, 1024, 4096), sc(16 * 8, 32), rnd8(hidden, 16384), sc(56, 128))
     x_hidden = torch.randn(batch, 4, hidden, generator=g, device=dev).bfloat16()
-    mla_out = torch.randn(batch, mh, 512, generator=g, device=dev).bfloat16()      # stand-in for the sparse attention
+    mla_out = torch.empty(batch, mh, 512, dtype=torch.bfloat16, device=dev)
+    for name in ("swa", "cmp"):   # attention caches: random finite records instead of the zeros of a fresh pool
+        data = cache._pools[name].data
+        epb_m = cache.entries_per_block[name]
+        data[:, :epb_m * 584] = model1_pool(data.size(0), epb_m, 5)[:, :epb_m * 584]
+    swa_idx, swa_len = cache.swa_indices(slots, [context - 1] * batch, 128)
+    swa_idx = swa_idx.view(batch, 128).contiguous()
+    cmp_len = torch.clamp(stage.n_compressed[:batch], max=topk).contiguous()
+    sink = torch.randn(mh, generator=g, device=dev)
     front_out = torch.empty(batch, 2048, dtype=torch.bfloat16, device=dev)
     y16 = torch.empty(batch, 2624, dtype=torch.float32, device=dev)
     ws = torch.empty(wuda.lib.wuda_mhc_pre_workspace_bytes(batch, hidden), dtype=torch.uint8, device=dev)
@@ -320,6 +328,9 @@ def attention_half_layer(batch=64, context=32768, topk=2048, reps=30, launches_o
                               idx_state=cache.idx_state, idx_state_row=stage.idx_state_row, idx_ape=idx_ape,
                               win_y2=stage.win_y2, w64=stage.w64, y16=y16, status_word=stage.status)
         stage.launch(batch)
+        wuda.sparse_mla_decode(stage.q_main[:batch], cache.model1_cache_view("swa"), swa_idx, swa_len,
+                               cache.model1_cache_view("cmp"), stage.topk_indices[:batch], cmp_len, sink, 512 ** -0.5,
+                               out=mla_out, status_word=stage.status)
         result["out"] = o_proj.run_o_proj_mhc_post(mla_out, stage.pos, cos, sin, x_hidden, pre["post"], pre["comb"], oproj,
                                                    status_word=stage.status)
 
@@ -350,7 +361,7 @@ def attention_half_layer(batch=64, context=32768, topk=2048, reps=30, launches_o
     stage.check_status()
     us = total / reps
     wbytes = 24 * 4 * hidden * 4 + 2048 * hidden + 2624 * hidden * 2 + n_total * q_lora + 16 * 1024 * 4096 + hidden * 16384
-    print("attention half-layer without its sparse attention: batch %d, context %d" % (batch, context))
+    print("attention half-layer: batch %d, context %d, window 128 + top-%d" % (batch, context, topk))
     print("  %.1f us per pass (one graph, L2 flushed before each); weights streamed %.1f MB + %.1f MB of indexer keys"
           % (us, wbytes / 1e6, batch * (context // 4) * 132 / 1e6))
 

@@ -13,7 +13,11 @@
 //
 // One CTA owns one request and one 256-dim half of the output (the 512 fp32 accumulator
 // columns of a full row do not fit beside the scores in tensor memory); both halves compute
-// the full scores.  Roles:
+// the full scores.  The 448 scaled dims of the query live in tensor memory as the A operand of
+// Q K^T (224 columns of bf16 pairs): read from shared memory, the 128 KB query would have to
+// cross the shared-memory port for every key block and the MMAs would wait on it.  Only the 64
+// rotary dims of the query are a shared-memory operand.  Tensor memory: query 224 columns,
+// output half 256, one score block 32.  Roles:
 //   warps 0-3   softmax: thread = head row = tensor-memory lane.  Scores of a 32-key block are
 //               read from tensor memory, scaled, masked, exponentiated against a running
 //               reference maximum and written to shared memory as bf16 probabilities.  The
@@ -23,7 +27,8 @@
 //               2^E to bf16 (exact) and store the block in the 128-byte-swizzled operand layout.
 //               The same bytes serve as the K-major operand of Q K^T and as the MN-major
 //               operand of P V.
-//   warp 12     issues the tcgen05 MMAs: Q K^T of block j ahead of P V of block j-1.
+//   warp 12     issues the tcgen05 MMAs: Q K^T of block j, then P V of block j-1, so that the
+//               tensor pipe works on one while the softmax works on the other.
 // Every wait is bounded; a wait that runs out leaves a code in the status word and the CTA
 // exits normally.
 #include <cuda_bf16.h>
@@ -52,23 +57,23 @@ constexpr int kMaxSplits = 32;        // CTAs that may share one request's keys 
 constexpr float kRescaleStep = 8.0f;   // log2 units the block maximum may exceed the reference by
 
 // shared memory, offsets from a 1024-byte aligned base
-constexpr uint32_t kQBytes = kRows * kDim * 2;          // 8 chunks of [128 rows][128 B]
-constexpr uint32_t kQChunk = kRows * 128;
+constexpr int kStages = 5;                              // key blocks in flight between producers and MMAs
+constexpr uint32_t kQRopeBytes = kRows * 128;           // the query's 64 rotary dims: [128 rows][128 B]
 constexpr uint32_t kStageBytes = kBlock * kDim * 2;     // 8 chunks of [32 keys][128 B]
 constexpr uint32_t kKChunk = kBlock * 128;
 constexpr uint32_t kPBytes = kRows * kBlock * 2;        // 4 pieces of [128 rows][16 B]
 constexpr uint32_t kPPiece = kRows * 16;
 constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffK = kOffQ + kQBytes;
-constexpr uint32_t kOffP = kOffK + 2 * kStageBytes;
-constexpr uint32_t kOffValid = kOffP + 2 * kPBytes;     // 2 x 8 bytes: per producer warp, 4 valid bits
-constexpr uint32_t kOffBars = kOffValid + 16;
-constexpr uint32_t kNumBars = 10;
+constexpr uint32_t kOffK = kOffQ + kQRopeBytes;
+constexpr uint32_t kOffP = kOffK + kStages * kStageBytes;
+constexpr uint32_t kOffValid = kOffP + 2 * kPBytes;     // kStages x 8 bytes: per producer warp, 4 valid bits
+constexpr uint32_t kOffBars = kOffValid + kStages * 8;
+constexpr uint32_t kNumBars = 2 * kStages + 6;
 constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
 
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColO = 0, kColS = 256;
+constexpr uint32_t kColQ = 0, kColO = 224, kColS = 480;   // query pairs | output half | one score block
 
 struct Pool {
     const uint8_t* data;
@@ -172,9 +177,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - raw_addr);
     const uint32_t bars = base + kOffBars;
-    // per buffer b in {0, 1}: key block stored, scores complete, scores read, probabilities stored,
-    // weighted sum complete
-    const uint32_t k_full = bars, s_full = bars + 16, s_empty = bars + 32, p_full = bars + 48, pv_done = bars + 64;
+    // per stage: key block stored / its weighted sum complete; scores complete / read; per
+    // probability buffer: probabilities stored / weighted sum complete
+    const uint32_t k_full = bars, k_free = bars + kStages * 8, s_full = bars + 2 * kStages * 8, s_empty = s_full + 8,
+                   p_full = s_full + 16, pv_done = s_full + 32;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kOffMisc + 4);
     volatile uint8_t* valid_bytes = base_ptr + kOffValid;
@@ -185,10 +191,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kStages; ++i) {
             mbar_init(k_full + i * 8, kProducerWarps);
-            mbar_init(s_full + i * 8, 1);
-            mbar_init(s_empty + i * 8, kSoftmaxWarps);
+            mbar_init(k_free + i * 8, 1);
+        }
+        mbar_init(s_full, 1);
+        mbar_init(s_empty, kSoftmaxWarps);
+        for (int i = 0; i < 2; ++i) {
             mbar_init(p_full + i * 8, kSoftmaxWarps);
             mbar_init(pv_done + i * 8, 1);
         }
@@ -210,19 +219,38 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
     const int first = static_cast<int>(blockIdx.z) * per_split;
     const int blocks = min(max(all_blocks - first, 0), per_split);
 
-    // the query rows, zero-padded to 128, in the swizzled K-major operand layout
-    for (int i = threadIdx.x; i < kRows * 64; i += kThreads) {
-        const int row = i >> 6, piece = i & 63;
+    tc_fence_before();
+    __syncthreads();   // the tensor-memory base address is published
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // the query rows, zero-padded to 128: rotary dims to shared memory in the swizzled K-major operand
+    // layout, scaled dims to tensor memory (row = lane, column = a pair of dims)
+    for (int i = threadIdx.x; i < kRows * 8; i += kThreads) {
+        const int row = i >> 3, piece = i & 7;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < p.heads)
-            v = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim) + piece);
-        st_shared_v4(base + kOffQ + (piece >> 3) * kQChunk + row * 128 + (((piece & 7) ^ (row & 7)) << 4), v);
+            v = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim + kNope) + piece);
+        st_shared_v4(base + kOffQ + row * 128 + ((piece ^ (row & 7)) << 4), v);
+    }
+    if (warp < kSoftmaxWarps) {
+        const int row = warp * 32 + lane;
+        const uint4* src = reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim);
+#pragma unroll 1
+        for (int c = 0; c < 7; ++c) {
+            uint32_t w[32];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint4 v = row < p.heads ? __ldg(src + c * 8 + i) : make_uint4(0, 0, 0, 0);
+                w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
+            }
+            tmem_st_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + kColQ + c * 32, w);
+        }
+        tmem_st_wait();
     }
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
 
     if (warp >= kSoftmaxWarps && warp < kIssuerWarp) {
         // ------------------------------------------------------------ key producers
@@ -240,11 +268,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
             for (int u = 0; u <= kAhead; ++u) {
                 const int j = j0 + u;
                 if (j >= blocks) break;
-                const int s = j & 1;
+                const int s = j % kStages, use = j / kStages;
                 fetch_key(p, b, (first + j + kAhead) * kBlock + row, n_swa, n_total, piece, ring[(u + kAhead) % (kAhead + 1)],
                           &bad);
-                if (j >= 2)
-                    alive = mbar_wait_warp(pv_done + s * 8, ((j >> 1) - 1) & 1u, abort_flag, p.status, kDevTimeoutMlaOutput);
+                if (use >= 1)
+                    alive = mbar_wait_warp(k_free + s * 8, (use - 1) & 1u, abort_flag, p.status, kDevTimeoutMlaOutput);
                 if (!alive) break;
                 store_key(base + kOffK + s * kStageBytes, row, piece, ring[u]);
                 const uint32_t bits = __ballot_sync(0xffffffffu, ring[u].valid != 0);
@@ -265,38 +293,42 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         bool alive = true;
         for (int j = 0; j <= blocks && alive; ++j) {
             if (j < blocks) {
-                const int s = j & 1;
-                alive = mbar_wait_lane0(k_full + s * 8, (j >> 1) & 1u, abort_flag, p.status, kDevTimeoutMlaKeys);
-                if (alive && j >= 2)
-                    alive = mbar_wait_lane0(s_empty + s * 8, ((j >> 1) - 1) & 1u, abort_flag, p.status,
-                                            kDevTimeoutMlaScoresRead);
+                const int s = j % kStages;
+                alive = mbar_wait_lane0(k_full + s * 8, (j / kStages) & 1u, abort_flag, p.status, kDevTimeoutMlaKeys);
+                if (alive && j >= 1)
+                    alive = mbar_wait_lane0(s_empty, (j - 1) & 1u, abort_flag, p.status, kDevTimeoutMlaScoresRead);
                 if (!alive) break;
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t q_addr = base + kOffQ, k_addr = base + kOffK + s * kStageBytes;
+                    const uint32_t k_addr = base + kOffK + s * kStageBytes;
 #pragma unroll
-                    for (int c = 0; c < 8; ++c)
+                    for (int c = 0; c < 7; ++c)
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            umma_f16(tmem_base + kColS + s * kBlock, umma_smem_desc_sw128(q_addr + c * kQChunk + k * 32),
-                                     umma_smem_desc_sw128(k_addr + c * kKChunk + k * 32), idesc_qk, (c | k) != 0);
-                    umma_commit(s_full + s * 8);
+                            umma_f16_ta(tmem_base + kColS, tmem_base + kColQ + c * 32 + k * 8,
+                                        umma_smem_desc_sw128(k_addr + c * kKChunk + k * 32), idesc_qk, (c | k) != 0);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_f16(tmem_base + kColS, umma_smem_desc_sw128(base + kOffQ + k * 32),
+                                 umma_smem_desc_sw128(k_addr + 7 * kKChunk + k * 32), idesc_qk, 1u);
+                    umma_commit(s_full);
                 }
                 __syncwarp();
             }
             if (j >= 1) {
-                const int t = (j - 1) & 1;
+                const int t = (j - 1) & 1, s = (j - 1) % kStages;
                 alive = mbar_wait_lane0(p_full + t * 8, ((j - 1) >> 1) & 1u, abort_flag, p.status, kDevTimeoutMlaProbs);
                 if (!alive) break;
                 tc_fence_after();
                 if (lane == 0) {
                     const uint32_t p_addr = base + kOffP + t * kPBytes;
-                    const uint32_t v_addr = base + kOffK + t * kStageBytes + half * 4 * kKChunk;
+                    const uint32_t v_addr = base + kOffK + s * kStageBytes + half * 4 * kKChunk;
 #pragma unroll
                     for (int k = 0; k < 2; ++k)   // 16 keys each
                         umma_f16(tmem_base + kColO, umma_smem_desc_noswz(p_addr + k * 2 * kPPiece, kPPiece, 128),
                                  umma_smem_desc_mn_sw128(v_addr + k * 16 * 128, kKChunk), idesc_pv, (j - 1 > 0) || k > 0);
-                    umma_commit(pv_done + t * 8);
+                    umma_commit(pv_done + t * 8);   // the probability buffer and the accumulator
+                    umma_commit(k_free + s * 8);    // the key stage
                 }
                 __syncwarp();
             }
@@ -308,19 +340,19 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         float m_ref = -INFINITY, l = 0.0f;
         bool alive = true;
         for (int j = 0; j < blocks && alive; ++j) {
-            const int s = j & 1;
-            alive = mbar_wait_warp(s_full + s * 8, (j >> 1) & 1u, abort_flag, p.status, kDevTimeoutMlaScores);
+            const int s = j & 1, stage = j % kStages;
+            alive = mbar_wait_warp(s_full, j & 1u, abort_flag, p.status, kDevTimeoutMlaScores);
             if (!alive) break;
             tc_fence_after();
             uint32_t v[32];
-            tmem_ld_32x32(lane_addr + kColS + s * kBlock, v);
+            tmem_ld_32x32(lane_addr + kColS, v);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty + s * 8);
+            if (lane == 0) mbar_arrive(s_empty);
             // the block's valid bits were published before its keys were announced, and its stage is
             // not refilled before this block's weighted sum has run
-            const volatile uint32_t* vw = reinterpret_cast<const volatile uint32_t*>(valid_bytes + s * 8);
+            const volatile uint32_t* vw = reinterpret_cast<const volatile uint32_t*>(valid_bytes + stage * 8);
             const uint2 vb = make_uint2(vw[0], vw[1]);
             uint32_t mask = 0;
 #pragma unroll

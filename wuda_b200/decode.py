@@ -61,6 +61,7 @@ class CsaDecodeStage:
         self.main_state_row, self.idx_state_row = i64(m), i64(m)
         self.idx_dst, self.cmp_dst, self.swa_dst = i64(m), i64(m), i64(m)
         self.block_table = i32(m, cache.max_pages)
+        self.cmp_block_table = i32(m, cache.max_pages)
         self.n_compressed = i32(m)
         self.q_raw = torch.zeros(m, weights.q_lora, dtype=torch.bfloat16, device=dev)
         self.w64 = torch.zeros(m, weights.index_heads, dtype=torch.float32, device=dev)
@@ -109,6 +110,7 @@ class CsaDecodeStage:
         for name in ("idx_dst", "cmp_dst", "swa_dst"):
             getattr(self, name)[:m].copy_(st[name], non_blocking=True)
         self.block_table[:m].copy_(self.cache.block_table("idx", slots), non_blocking=True)
+        self.cmp_block_table[:m].copy_(self.cache.block_table("cmp", slots), non_blocking=True)
         self.n_compressed[:m].copy_(self.cache.n_compressed(slots, pos), non_blocking=True)
         return st
 
@@ -118,7 +120,8 @@ class CsaDecodeStage:
             win_y2=self.win_y2.data_ptr(), pos=self.pos.data_ptr(), q_pos=self.q_pos.data_ptr(),
             main_state_row=self.main_state_row.data_ptr(), idx_state_row=self.idx_state_row.data_ptr(),
             idx_dst=self.idx_dst.data_ptr(), cmp_dst=self.cmp_dst.data_ptr(), swa_dst=self.swa_dst.data_ptr(),
-            idx_block_table=self.block_table.data_ptr(), n_compressed=self.n_compressed.data_ptr(),
+            idx_block_table=self.block_table.data_ptr(), cmp_block_table=self.cmp_block_table.data_ptr(),
+            n_compressed=self.n_compressed.data_ptr(),
             block_table_stride=self.block_table.stride(0), topk=self.topk, logits_stride=self.logits_stride,
             logits=self.logits.data_ptr(), topk_indices=self.topk_indices.data_ptr(), topk_raw=self.topk_raw.data_ptr(),
             q_main_out=self.q_main.data_ptr())
