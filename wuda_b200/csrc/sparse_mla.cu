@@ -13,12 +13,11 @@
 //
 // One CTA owns one request and one 256-dim half of the output (the 512 fp32 accumulator
 // columns of a full row do not fit beside the scores in tensor memory); both halves compute
-// the full scores.  The 448 scaled dims of the query live in tensor memory as the A operand of
-// Q K^T (224 columns of bf16 pairs): read from shared memory, the 128 KB query would have to
-// cross the shared-memory port for every key block and the MMAs would wait on it.  Only the 64
-// rotary dims of the query are a shared-memory operand.  Tensor memory: query 224 columns,
-// output half 256, one score block 32.  Roles:
-//   warps 0-3   softmax: thread = head row = tensor-memory lane.  Scores of a 32-key block are
+// the full scores.  An MMA of this shape costs about 70 cycles however few keys it covers, so
+// Q K^T runs over blocks of 64 keys (32 MMAs per block); the tensor memory that leaves beside the
+// output half (256 columns) and one score block (64) holds the first 384 dims of the query as
+// the A operand (192 columns of bf16 pairs), the last 128 dims are a shared-memory operand.  Roles:
+//   warps 0-3   softmax: thread = head row = tensor-memory lane.  Scores of a 64-key block are
 //               read from tensor memory, scaled, masked, exponentiated against a running
 //               reference maximum and written to shared memory as bf16 probabilities.  The
 //               accumulator is rescaled only when the maximum grows by more than 2^8 (the final
@@ -45,35 +44,44 @@ constexpr int kNope = 448;         // e4m3 part
 constexpr int kBody = 576;         // 448 + 64 * 2 bytes
 constexpr int kScaleRec = 8;       // 7 scale bytes + 1 pad
 constexpr int kRows = 128;         // UMMA M: head rows, zero-padded
-constexpr int kBlock = 32;         // keys per block
+constexpr int kBlock = 64;         // keys per block
+constexpr int kPass = 32;          // keys the producer warps convert at a time (4 per warp)
 constexpr int kHalf = 256;         // output dims per CTA
 constexpr int kSoftmaxWarps = 4;
 constexpr int kProducerWarps = 8;
 constexpr int kIssuerWarp = kSoftmaxWarps + kProducerWarps;
 constexpr int kThreads = (kIssuerWarp + 1) * 32;
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kAhead = 3;             // blocks whose records are in flight ahead of the one being stored
+constexpr int kAhead = 3;             // passes whose records are in flight ahead of the one being stored
 constexpr int kMaxSplits = 32;        // CTAs that may share one request's keys (per output half)
 constexpr float kRescaleStep = 8.0f;   // log2 units the block maximum may exceed the reference by
 
 // shared memory, offsets from a 1024-byte aligned base
-constexpr int kStages = 5;                              // key blocks in flight between producers and MMAs
-constexpr uint32_t kQRopeBytes = kRows * 128;           // the query's 64 rotary dims: [128 rows][128 B]
-constexpr uint32_t kStageBytes = kBlock * kDim * 2;     // 8 chunks of [32 keys][128 B]
-constexpr uint32_t kKChunk = kBlock * 128;
-constexpr uint32_t kPBytes = kRows * kBlock * 2;        // 4 pieces of [128 rows][16 B]
+// A key block's own output half (4 of its 8 chunks) is needed until P V of the block has run, its other half
+// only until Q K^T has: two rings of different depth let the producers run a block further ahead than
+// whole-block stages of the same total size would.
+constexpr int kOwnStages = 3;
+constexpr int kOthStages = 2;
+constexpr int kQTmemChunks = 6;                         // 64-dim chunks of the query held in tensor memory
+constexpr uint32_t kQChunk = kRows * 128;               // one 64-dim chunk of the query: [128 rows][128 B]
+constexpr uint32_t kQSmemBytes = (8 - kQTmemChunks) * kQChunk;
+constexpr uint32_t kKChunk = kBlock * 128;              // one 64-dim chunk of a key block: [64 keys][128 B]
+constexpr uint32_t kHalfStageBytes = 4 * kKChunk;
+constexpr uint32_t kPBytes = kRows * kBlock * 2;        // 8 pieces of [128 rows][16 B]
 constexpr uint32_t kPPiece = kRows * 16;
 constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffK = kOffQ + kQRopeBytes;
-constexpr uint32_t kOffP = kOffK + kStages * kStageBytes;
-constexpr uint32_t kOffValid = kOffP + 2 * kPBytes;     // kStages x 8 bytes: per producer warp, 4 valid bits
-constexpr uint32_t kOffBars = kOffValid + kStages * 8;
-constexpr uint32_t kNumBars = 2 * kStages + 6;
+constexpr uint32_t kOffOwn = kOffQ + kQSmemBytes;
+constexpr uint32_t kOffOth = kOffOwn + kOwnStages * kHalfStageBytes;
+constexpr uint32_t kOffP = kOffOth + kOthStages * kHalfStageBytes;
+constexpr uint32_t kOffValid = kOffP + 2 * kPBytes;     // kOwnStages x 16 bytes: per pass and producer warp, 4 valid bits
+constexpr uint32_t kOffBars = kOffValid + kOwnStages * 16;
+constexpr uint32_t kNumBars = 2 * kOwnStages + kOthStages + 6;
 constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
 
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColQ = 0, kColO = 224, kColS = 480;   // query pairs | output half | one score block
+constexpr uint32_t kColQ = 0, kColO = kQTmemChunks * 32, kColS = kColO + kHalf;   // query pairs | output half | scores
+static_assert(kColS + kBlock <= kTmemCols, "tensor memory columns");
 
 struct Pool {
     const uint8_t* data;
@@ -150,11 +158,13 @@ __device__ __forceinline__ void fetch_key(const Params& p, int b, int g, int n_s
     r.valid = 1;
 }
 
-__device__ __forceinline__ void store_key(uint32_t stage_addr, int row, int piece, const KeyRegs& r) {
-    const uint32_t at = stage_addr + row * 128 + ((piece ^ (row & 7)) << 4);
+// `lo_addr` / `hi_addr`: where dims 0-255 / 256-511 of the block go (4 chunks each)
+__device__ __forceinline__ void store_key(uint32_t lo_addr, uint32_t hi_addr, int row, int piece, const KeyRegs& r) {
+    const uint32_t in_chunk = row * 128 + ((piece ^ (row & 7)) << 4);
     if (!r.valid) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) st_shared_v4(at + c * kKChunk, make_uint4(0, 0, 0, 0));
+        for (int c = 0; c < 8; ++c)
+            st_shared_v4((c < 4 ? lo_addr : hi_addr) + (c & 3) * kKChunk + in_chunk, make_uint4(0, 0, 0, 0));
         return;
     }
 #pragma unroll
@@ -166,9 +176,9 @@ __device__ __forceinline__ void store_key(uint32_t stage_addr, int row, int piec
         v.y = e4m3x2_to_bf16x2(r.nope[c].x >> 16, s);
         v.z = e4m3x2_to_bf16x2(r.nope[c].y & 0xffffu, s);
         v.w = e4m3x2_to_bf16x2(r.nope[c].y >> 16, s);
-        st_shared_v4(at + c * kKChunk, v);
+        st_shared_v4((c < 4 ? lo_addr : hi_addr) + (c & 3) * kKChunk + in_chunk, v);
     }
-    st_shared_v4(at + 7 * kKChunk, r.rope);
+    st_shared_v4(hi_addr + 3 * kKChunk + in_chunk, r.rope);
 }
 
 __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p) {
@@ -179,8 +189,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
     const uint32_t bars = base + kOffBars;
     // per stage: key block stored / its weighted sum complete; scores complete / read; per
     // probability buffer: probabilities stored / weighted sum complete
-    const uint32_t k_full = bars, k_free = bars + kStages * 8, s_full = bars + 2 * kStages * 8, s_empty = s_full + 8,
-                   p_full = s_full + 16, pv_done = s_full + 32;
+    const uint32_t k_full = bars, own_free = bars + kOwnStages * 8, oth_free = bars + 2 * kOwnStages * 8,
+                   s_full = oth_free + kOthStages * 8, s_empty = s_full + 8, p_full = s_full + 16, pv_done = s_full + 32;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kOffMisc + 4);
     volatile uint8_t* valid_bytes = base_ptr + kOffValid;
@@ -191,10 +201,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < kStages; ++i) {
-            mbar_init(k_full + i * 8, kProducerWarps);
-            mbar_init(k_free + i * 8, 1);
+        for (int i = 0; i < kOwnStages; ++i) {
+            mbar_init(k_full + i * 8, kProducerWarps * (kBlock / kPass));
+            mbar_init(own_free + i * 8, 1);
         }
+        for (int i = 0; i < kOthStages; ++i) mbar_init(oth_free + i * 8, 1);
         mbar_init(s_full, 1);
         mbar_init(s_empty, kSoftmaxWarps);
         for (int i = 0; i < 2; ++i) {
@@ -225,18 +236,20 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
     const uint32_t tmem_base = *tmem_slot;
     // the query rows, zero-padded to 128: rotary dims to shared memory in the swizzled K-major operand
     // layout, scaled dims to tensor memory (row = lane, column = a pair of dims)
-    for (int i = threadIdx.x; i < kRows * 8; i += kThreads) {
-        const int row = i >> 3, piece = i & 7;
+    constexpr int kQSmemPieces = (8 - kQTmemChunks) * 8;
+    for (int i = threadIdx.x; i < kRows * kQSmemPieces; i += kThreads) {
+        const int row = i / kQSmemPieces, piece = i % kQSmemPieces;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < p.heads)
-            v = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim + kNope) + piece);
-        st_shared_v4(base + kOffQ + row * 128 + ((piece ^ (row & 7)) << 4), v);
+            v = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim +
+                                                     kQTmemChunks * 64) + piece);
+        st_shared_v4(base + kOffQ + (piece >> 3) * kQChunk + row * 128 + (((piece & 7) ^ (row & 7)) << 4), v);
     }
     if (warp < kSoftmaxWarps) {
         const int row = warp * 32 + lane;
         const uint4* src = reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim);
 #pragma unroll 1
-        for (int c = 0; c < 7; ++c) {
+        for (int c = 0; c < kQTmemChunks; ++c) {
             uint32_t w[32];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -260,27 +273,37 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         // a block's records are requested kAhead blocks before they are converted: a gather from
         // random pages takes far longer than one block's turn through the pipeline
         KeyRegs ring[kAhead + 1];
+        constexpr int kPasses = kBlock / kPass;
+        const int passes = blocks * kPasses, first_key = first * kBlock;
 #pragma unroll
-        for (int u = 0; u < kAhead; ++u) fetch_key(p, b, (first + u) * kBlock + row, n_swa, n_total, piece, ring[u], &bad);
+        for (int u = 0; u < kAhead; ++u) fetch_key(p, b, first_key + u * kPass + row, n_swa, n_total, piece, ring[u], &bad);
         bool alive = true;
-        for (int j0 = 0; j0 < blocks && alive; j0 += kAhead + 1) {
+        for (int q0 = 0; q0 < passes && alive; q0 += kAhead + 1) {
 #pragma unroll
             for (int u = 0; u <= kAhead; ++u) {
-                const int j = j0 + u;
-                if (j >= blocks) break;
-                const int s = j % kStages, use = j / kStages;
-                fetch_key(p, b, (first + j + kAhead) * kBlock + row, n_swa, n_total, piece, ring[(u + kAhead) % (kAhead + 1)],
-                          &bad);
-                if (use >= 1)
-                    alive = mbar_wait_warp(k_free + s * 8, (use - 1) & 1u, abort_flag, p.status, kDevTimeoutMlaOutput);
+                const int q = q0 + u;
+                if (q >= passes) break;
+                const int j = q / kPasses, sub = q % kPasses;
+                const int s = j % kOwnStages, t = j % kOthStages;
+                fetch_key(p, b, first_key + (q + kAhead) * kPass + row, n_swa, n_total, piece,
+                          ring[(u + kAhead) % (kAhead + 1)], &bad);
+                if (sub == 0) {
+                    if (j >= kOwnStages)
+                        alive = mbar_wait_warp(own_free + s * 8, (j / kOwnStages - 1) & 1u, abort_flag, p.status,
+                                               kDevTimeoutMlaOutput);
+                    if (alive && j >= kOthStages)
+                        alive = mbar_wait_warp(oth_free + t * 8, (j / kOthStages - 1) & 1u, abort_flag, p.status,
+                                               kDevTimeoutMlaScores);
+                }
                 if (!alive) break;
-                store_key(base + kOffK + s * kStageBytes, row, piece, ring[u]);
+                const uint32_t own_addr = base + kOffOwn + s * kHalfStageBytes, oth_addr = base + kOffOth + t * kHalfStageBytes;
+                store_key(half == 0 ? own_addr : oth_addr, half == 0 ? oth_addr : own_addr, sub * kPass + row, piece, ring[u]);
                 const uint32_t bits = __ballot_sync(0xffffffffu, ring[u].valid != 0);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    valid_bytes[s * 8 + pw] = static_cast<uint8_t>((bits & 1u) | ((bits >> 7) & 2u) | ((bits >> 14) & 4u) |
-                                                                   ((bits >> 21) & 8u));
+                    valid_bytes[s * 16 + sub * 8 + pw] = static_cast<uint8_t>(
+                        (bits & 1u) | ((bits >> 7) & 2u) | ((bits >> 14) & 4u) | ((bits >> 21) & 8u));
                     mbar_arrive(k_full + s * 8);
                 }
             }
@@ -293,42 +316,46 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         bool alive = true;
         for (int j = 0; j <= blocks && alive; ++j) {
             if (j < blocks) {
-                const int s = j % kStages;
-                alive = mbar_wait_lane0(k_full + s * 8, (j / kStages) & 1u, abort_flag, p.status, kDevTimeoutMlaKeys);
+                const int s = j % kOwnStages, t = j % kOthStages;
+                alive = mbar_wait_lane0(k_full + s * 8, (j / kOwnStages) & 1u, abort_flag, p.status, kDevTimeoutMlaKeys);
                 if (alive && j >= 1)
                     alive = mbar_wait_lane0(s_empty, (j - 1) & 1u, abort_flag, p.status, kDevTimeoutMlaScoresRead);
                 if (!alive) break;
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t k_addr = base + kOffK + s * kStageBytes;
+                    const uint32_t own_addr = base + kOffOwn + s * kHalfStageBytes, oth_addr = base + kOffOth + t * kHalfStageBytes;
 #pragma unroll
-                    for (int c = 0; c < 7; ++c)
+                    for (int c = 0; c < 8; ++c)
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            umma_f16_ta(tmem_base + kColS, tmem_base + kColQ + c * 32 + k * 8,
-                                        umma_smem_desc_sw128(k_addr + c * kKChunk + k * 32), idesc_qk, (c | k) != 0);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_f16(tmem_base + kColS, umma_smem_desc_sw128(base + kOffQ + k * 32),
-                                 umma_smem_desc_sw128(k_addr + 7 * kKChunk + k * 32), idesc_qk, 1u);
+                        for (int k = 0; k < 4; ++k) {
+                            const uint64_t k_desc =
+                                umma_smem_desc_sw128(((c >> 2) == half ? own_addr : oth_addr) + (c & 3) * kKChunk + k * 32);
+                            if (c < kQTmemChunks)
+                                umma_f16_ta(tmem_base + kColS, tmem_base + kColQ + c * 32 + k * 8, k_desc, idesc_qk, (c | k) != 0);
+                            else
+                                umma_f16(tmem_base + kColS,
+                                         umma_smem_desc_sw128(base + kOffQ + (c - kQTmemChunks) * kQChunk + k * 32), k_desc,
+                                         idesc_qk, 1u);
+                        }
                     umma_commit(s_full);
+                    umma_commit(oth_free + t * 8);   // the half of the key block only the scores needed
                 }
                 __syncwarp();
             }
             if (j >= 1) {
-                const int t = (j - 1) & 1, s = (j - 1) % kStages;
+                const int t = (j - 1) & 1, s = (j - 1) % kOwnStages;
                 alive = mbar_wait_lane0(p_full + t * 8, ((j - 1) >> 1) & 1u, abort_flag, p.status, kDevTimeoutMlaProbs);
                 if (!alive) break;
                 tc_fence_after();
                 if (lane == 0) {
                     const uint32_t p_addr = base + kOffP + t * kPBytes;
-                    const uint32_t v_addr = base + kOffK + s * kStageBytes + half * 4 * kKChunk;
+                    const uint32_t v_addr = base + kOffOwn + s * kHalfStageBytes;
 #pragma unroll
-                    for (int k = 0; k < 2; ++k)   // 16 keys each
+                    for (int k = 0; k < kBlock / 16; ++k)   // 16 keys each
                         umma_f16(tmem_base + kColO, umma_smem_desc_noswz(p_addr + k * 2 * kPPiece, kPPiece, 128),
                                  umma_smem_desc_mn_sw128(v_addr + k * 16 * 128, kKChunk), idesc_pv, (j - 1 > 0) || k > 0);
                     umma_commit(pv_done + t * 8);   // the probability buffer and the accumulator
-                    umma_commit(k_free + s * 8);    // the key stage
+                    umma_commit(own_free + s * 8);  // this half of the key block
                 }
                 __syncwarp();
             }
@@ -340,32 +367,35 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         float m_ref = -INFINITY, l = 0.0f;
         bool alive = true;
         for (int j = 0; j < blocks && alive; ++j) {
-            const int s = j & 1, stage = j % kStages;
+            const int s = j & 1, stage = j % kOwnStages;
             alive = mbar_wait_warp(s_full, j & 1u, abort_flag, p.status, kDevTimeoutMlaScores);
             if (!alive) break;
             tc_fence_after();
-            uint32_t v[32];
-            tmem_ld_32x32(lane_addr + kColS, v);
-            tmem_ld_wait();
+            // the block's valid bits were published before its keys were announced, and its stage is
+            // not refilled before this block's weighted sum has run
+            const volatile uint32_t* vw = reinterpret_cast<const volatile uint32_t*>(valid_bytes + stage * 16);
+            float x[kBlock], bmax = -INFINITY;
+#pragma unroll
+            for (int h2 = 0; h2 < kBlock / 32; ++h2) {
+                uint32_t v[32];
+                tmem_ld_32x32(lane_addr + kColS + h2 * 32, v);
+                const uint2 vb = make_uint2(vw[2 * h2], vw[2 * h2 + 1]);
+                uint32_t mask = 0;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    mask |= ((vb.x >> (8 * w)) & 0xfu) << (4 * w);
+                    mask |= ((vb.y >> (8 * w)) & 0xfu) << (16 + 4 * w);
+                }
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    x[h2 * 32 + i] = (mask >> i) & 1u ? __uint_as_float(v[i]) * p.scale_log2 : -INFINITY;
+                    bmax = fmaxf(bmax, x[h2 * 32 + i]);
+                }
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty);
-            // the block's valid bits were published before its keys were announced, and its stage is
-            // not refilled before this block's weighted sum has run
-            const volatile uint32_t* vw = reinterpret_cast<const volatile uint32_t*>(valid_bytes + stage * 8);
-            const uint2 vb = make_uint2(vw[0], vw[1]);
-            uint32_t mask = 0;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                mask |= ((vb.x >> (8 * w)) & 0xfu) << (4 * w);
-                mask |= ((vb.y >> (8 * w)) & 0xfu) << (16 + 4 * w);
-            }
-            float x[32], bmax = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                x[i] = (mask >> i) & 1u ? __uint_as_float(v[i]) * p.scale_log2 : -INFINITY;
-                bmax = fmaxf(bmax, x[i]);
-            }
             const bool grow = bmax > m_ref + kRescaleStep;   // also the first finite maximum
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? bmax : m_ref;
@@ -391,9 +421,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
                 m_ref = m_new;
             }
             float sum = 0.0f;
-            uint32_t pk[16];
+            uint32_t pk[kBlock / 2];
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
+            for (int i = 0; i < kBlock; i += 2) {
                 const float e0 = m_ref == -INFINITY ? 0.0f : ex2(x[i] - m_ref);
                 const float e1 = m_ref == -INFINITY ? 0.0f : ex2(x[i + 1] - m_ref);
                 sum += e0 + e1;
@@ -407,7 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
             }
             const uint32_t p_addr = base + kOffP + s * kPBytes + row * 16;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < kBlock / 8; ++c)
                 st_shared_v4(p_addr + c * kPPiece, make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]));
             fence_proxy_async_smem();
             __syncwarp();
