@@ -56,7 +56,8 @@ typedef enum wuda_device_status {
     WUDA_DEV_TIMEOUT_MLA_SCORES = 152,
     WUDA_DEV_TIMEOUT_MLA_SCORES_READ = 153,
     WUDA_DEV_TIMEOUT_MLA_PROBS = 154,
-    WUDA_DEV_TIMEOUT_MLA_OUTPUT = 155
+    WUDA_DEV_TIMEOUT_MLA_OUTPUT = 155,
+    WUDA_DEV_MLA_SCALE_RANGE = 156  /* a key's scale exponent outside [-15, 7] was clamped into that range */
 } wuda_device_status;
 
 /* Library version (major*10000 + minor*100 + patch). */
@@ -376,8 +377,12 @@ int wuda_csa_decode_step(const wuda_csa_weights* weights, const wuda_csa_caches*
  * wuda_cache_writers_fp8 writes.  The value vector of a key is the key itself.
  *   logit[h, t] = softmax_scale * q[h, :] . k[t, :]
  *   out[h, :]   = sum_t exp(logit[h, t]) k[t, :] / (sum_t exp(logit[h, t]) + exp(attn_sink[h]))
- * A request without a valid key gives a zero row.  fp32 logits and sums; the probabilities
- * are rounded to bf16 before they meet the values.
+ * A request without a valid key gives a zero row.  fp32 logits and sums.  The tensor cores run on
+ * fp16 operands: key values e4m3 * 2^E are exact for scale exponents E in [-15, 7] (the cache writers
+ * produce E >= -13; E > 7 would mean activations beyond 57344), a scale byte outside that range is
+ * clamped into it and reported as WUDA_DEV_MLA_SCALE_RANGE; query and rotary bf16 values are exact
+ * in fp16 between 6.1e-5 and 65504 in magnitude; the probabilities are rounded to fp16 before
+ * they meet the values.
  *
  * Replaces the third-party call at test/test_e2e_decode.py:719-728 (flash_mla_with_kvcache
  * with indices / extra_indices_in_kvcache / attn_sink); arithmetic as the torch twin

@@ -2,7 +2,7 @@
 restates the reference's torch twin (ref_flash_attn over deq_model1_row records) with sums in
 double, and against the fixture made with that twin.
 
-Floating point, so a tolerance: the kernel rounds the probabilities to bf16 before they meet the
+Floating point, so a tolerance: the kernel rounds the probabilities to 16 bits before they meet the
 values (as the reference kernels do) and its output to bf16.  Per head row the error must stay
 below 2^-7 of the row's largest output magnitude, and the cosine against the oracle above 0.9999
 (the reference's own end-to-end gate for this stage is cosine > 0.98)."""
@@ -172,6 +172,27 @@ def test_index_outside_the_pool_is_skipped_and_reported(wuda):
     skipped = idx.copy()
     skipped[0, 7] = -1
     check_close(got, oracle.sparse_mla(q, None, (pool, 64, skipped, [40]), None, SCALE))
+
+
+def test_scale_exponent_outside_the_exact_range_is_clamped_and_reported(wuda):
+    """Key values are exact for scale exponents in [-15, 7]; a byte beyond that is clamped and reported."""
+    rng = np.random.default_rng(13)
+    pool = model1_pool(rng, 1, 64)
+    idx = np.arange(40, dtype=np.int32)[None, :]
+    q = oracle.f32_to_bf16(rng.standard_normal((1, 16, 512)).astype(np.float32))
+    edge = pool.copy()
+    edge[0, 64 * 576 + 3 * 8 + 2] = 127 - 15     # the lower edge of the range: still exact
+    edge[0, 64 * 576 + 5 * 8 + 0] = 127 + 7      # the upper edge
+    got, status = run(wuda, q, None, (edge, 64, idx, [40]), None)
+    assert status == 0
+    check_close(got, oracle.sparse_mla(q, None, (edge, 64, idx, [40]), None, SCALE))
+    beyond = pool.copy()
+    beyond[0, 64 * 576 + 3 * 8 + 2] = 127 + 9
+    got, status = run(wuda, q, None, (beyond, 64, idx, [40]), None)
+    assert status == 156   # WUDA_DEV_MLA_SCALE_RANGE
+    clamped = pool.copy()
+    clamped[0, 64 * 576 + 3 * 8 + 2] = 127 + 7
+    check_close(got, oracle.sparse_mla(q, None, (clamped, 64, idx, [40]), None, SCALE))
 
 
 def test_argument_checks(wuda):

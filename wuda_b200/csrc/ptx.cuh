@@ -36,6 +36,7 @@ enum DeviceStatus : int {
     kDevTimeoutMlaScoresRead = 153, // ... the softmax never released a score buffer
     kDevTimeoutMlaProbs = 154,      // ... its probabilities never arrived
     kDevTimeoutMlaOutput = 155,     // ... its weighted sum never completed
+    kDevMlaScaleRange = 156,        // a key's scale exponent outside [-15, 7] was clamped into that range
 };
 
 // Wall-clock limit of one device-side wait.  Generous next to any real pipeline

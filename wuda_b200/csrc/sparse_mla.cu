@@ -16,14 +16,16 @@
 // the full scores.  An MMA of this shape costs about 70 cycles however few keys it covers, so
 // Q K^T runs over blocks of 64 keys (32 MMAs per block); the tensor memory that leaves beside the
 // output half (256 columns) and one score block (64) holds the first 384 dims of the query as
-// the A operand (192 columns of bf16 pairs), the last 128 dims are a shared-memory operand.  Roles:
+// the A operand (192 columns of fp16 pairs), the last 128 dims are a shared-memory operand.  Roles:
 //   warps 0-3   softmax: thread = head row = tensor-memory lane.  Scores of a 64-key block are
 //               read from tensor memory, scaled, masked, exponentiated against a running
-//               reference maximum and written to shared memory as bf16 probabilities.  The
+//               reference maximum and written to shared memory as fp16 probabilities.  The
 //               accumulator is rescaled only when the maximum grows by more than 2^8 (the final
 //               division uses the same reference, so the result does not depend on when).
 //   warps 4-11  key producers: gather records with plain loads (8 lanes per key), expand e4m3 *
-//               2^E to bf16 (exact) and store the block in the 128-byte-swizzled operand layout.
+//               2^E to fp16 (exact for E in [-15, 7], two instructions per pair; the query, the
+//               rotary values and the probabilities are fp16 as well) and store the block in the
+//               128-byte-swizzled operand layout.
 //               The same bytes serve as the K-major operand of Q K^T and as the MN-major
 //               operand of P V.
 //   warp 12     issues the tcgen05 MMAs: Q K^T of block j, then P V of block j-1, so that the
@@ -110,17 +112,39 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// 2^(e - 127) of a scale byte, as torch's float8_e8m0fnu reads it
-__device__ __forceinline__ float ue8m0(uint32_t e) {
-    return __uint_as_float(e == 0 ? 0x00400000u : (e == 255u ? 0x7fc00000u : e << 23));
+// The MMAs run on fp16 operands: e4m3 * 2^E is exact in fp16 for E in [-15, 7] (every value from
+// 2^-9 * 2^-15 = 2^-24 up to 448 * 2^7 < 65504), which costs two instructions per pair of values where
+// the way to bf16 costs six; the cache writers clamp their scales at 1e-4 (E >= -13) and E > 7 would
+// mean activations beyond 57344.  A scale byte outside that range is clamped into it and reported.
+constexpr int kScaleExpLo = -15, kScaleExpHi = 7;
+
+// 2^E as a pair of fp16, E = byte - 127 clamped to the exact range; `*clamped` is raised when it was
+__device__ __forceinline__ uint32_t scale_f16x2(uint32_t byte, bool* clamped) {
+    int e = static_cast<int>(byte) - 127;
+    if (e < kScaleExpLo || e > kScaleExpHi) {
+        *clamped = true;
+        e = e < kScaleExpLo ? kScaleExpLo : kScaleExpHi;
+    }
+    const uint32_t h = e >= -14 ? static_cast<uint32_t>(e + 15) << 10 : 0x0200u;   // 2^-15 is subnormal
+    return h | (h << 16);
 }
 
-__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t pair, float scale) {
-    uint32_t h2;
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t pair, uint32_t scale2) {
+    uint32_t h2, r;
     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<unsigned short>(pair)));
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-    const __nv_bfloat162 b = __floats2bfloat162_rn(f.x * scale, f.y * scale);
-    return *reinterpret_cast<const uint32_t*>(&b);
+    asm("mul.f16x2 %0, %1, %2;" : "=r"(r) : "r"(h2), "r"(scale2));
+    return r;
+}
+
+// two bf16 -> two fp16, saturating at the largest finite fp16 (exact for normal-range values)
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+    const float lo = fminf(fmaxf(__uint_as_float(v << 16), -65504.0f), 65504.0f);
+    const float hi = fminf(fmaxf(__uint_as_float(v & 0xffff0000u), -65504.0f), 65504.0f);
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint4 bf16x8_to_f16x8(uint4 v) {
+    return make_uint4(bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z), bf16x2_to_f16x2(v.w));
 }
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
@@ -159,7 +183,8 @@ __device__ __forceinline__ void fetch_key(const Params& p, int b, int g, int n_s
 }
 
 // `lo_addr` / `hi_addr`: where dims 0-255 / 256-511 of the block go (4 chunks each)
-__device__ __forceinline__ void store_key(uint32_t lo_addr, uint32_t hi_addr, int row, int piece, const KeyRegs& r) {
+__device__ __forceinline__ void store_key(uint32_t lo_addr, uint32_t hi_addr, int row, int piece, const KeyRegs& r,
+                                          bool* clamped) {
     const uint32_t in_chunk = row * 128 + ((piece ^ (row & 7)) << 4);
     if (!r.valid) {
 #pragma unroll
@@ -170,15 +195,15 @@ __device__ __forceinline__ void store_key(uint32_t lo_addr, uint32_t hi_addr, in
 #pragma unroll
     for (int c = 0; c < 7; ++c) {
         const uint32_t byte = ((c < 4 ? r.scales.x : r.scales.y) >> ((c & 3) * 8)) & 0xffu;
-        const float s = ue8m0(byte);
+        const uint32_t s = scale_f16x2(byte, clamped);
         uint4 v;
-        v.x = e4m3x2_to_bf16x2(r.nope[c].x & 0xffffu, s);
-        v.y = e4m3x2_to_bf16x2(r.nope[c].x >> 16, s);
-        v.z = e4m3x2_to_bf16x2(r.nope[c].y & 0xffffu, s);
-        v.w = e4m3x2_to_bf16x2(r.nope[c].y >> 16, s);
+        v.x = e4m3x2_to_f16x2(r.nope[c].x & 0xffffu, s);
+        v.y = e4m3x2_to_f16x2(r.nope[c].x >> 16, s);
+        v.z = e4m3x2_to_f16x2(r.nope[c].y & 0xffffu, s);
+        v.w = e4m3x2_to_f16x2(r.nope[c].y >> 16, s);
         st_shared_v4((c < 4 ? lo_addr : hi_addr) + (c & 3) * kKChunk + in_chunk, v);
     }
-    st_shared_v4(hi_addr + 3 * kKChunk + in_chunk, r.rope);
+    st_shared_v4(hi_addr + 3 * kKChunk + in_chunk, bf16x8_to_f16x8(r.rope));
 }
 
 __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p) {
@@ -243,7 +268,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         if (row < p.heads)
             v = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim +
                                                      kQTmemChunks * 64) + piece);
-        st_shared_v4(base + kOffQ + (piece >> 3) * kQChunk + row * 128 + (((piece & 7) ^ (row & 7)) << 4), v);
+        st_shared_v4(base + kOffQ + (piece >> 3) * kQChunk + row * 128 + (((piece & 7) ^ (row & 7)) << 4), bf16x8_to_f16x8(v));
     }
     if (warp < kSoftmaxWarps) {
         const int row = warp * 32 + lane;
@@ -253,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
             uint32_t w[32];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const uint4 v = row < p.heads ? __ldg(src + c * 8 + i) : make_uint4(0, 0, 0, 0);
+                const uint4 v = bf16x8_to_f16x8(row < p.heads ? __ldg(src + c * 8 + i) : make_uint4(0, 0, 0, 0));
                 w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
             }
             tmem_st_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + kColQ + c * 32, w);
@@ -269,7 +294,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         // ------------------------------------------------------------ key producers
         const int pw = warp - kSoftmaxWarps;
         const int row = pw * 4 + (lane >> 3), piece = lane & 7;
-        bool bad = false;
+        bool bad = false, clamped = false;
         // a block's records are requested kAhead blocks before they are converted: a gather from
         // random pages takes far longer than one block's turn through the pipeline
         KeyRegs ring[kAhead + 1];
@@ -297,7 +322,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
                 }
                 if (!alive) break;
                 const uint32_t own_addr = base + kOffOwn + s * kHalfStageBytes, oth_addr = base + kOffOth + t * kHalfStageBytes;
-                store_key(half == 0 ? own_addr : oth_addr, half == 0 ? oth_addr : own_addr, sub * kPass + row, piece, ring[u]);
+                store_key(half == 0 ? own_addr : oth_addr, half == 0 ? oth_addr : own_addr, sub * kPass + row, piece, ring[u],
+                          &clamped);
                 const uint32_t bits = __ballot_sync(0xffffffffu, ring[u].valid != 0);
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -309,10 +335,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
             }
         }
         if (bad && p.status) atomicCAS(p.status, 0, static_cast<int>(kDevBadPageIndex));
+        if (clamped && p.status) atomicCAS(p.status, 0, static_cast<int>(kDevMlaScaleRange));
     } else if (warp == kIssuerWarp) {
         // ------------------------------------------------------------ MMA issuer
-        constexpr uint32_t idesc_qk = umma_idesc(kRows, kBlock, 1, 1);
-        constexpr uint32_t idesc_pv = umma_idesc_b_mn(kRows, kHalf, 1, 1);
+        constexpr uint32_t idesc_qk = umma_idesc(kRows, kBlock, 0, 0);     // fp16 operands
+        constexpr uint32_t idesc_pv = umma_idesc_b_mn(kRows, kHalf, 0, 0);
         bool alive = true;
         for (int j = 0; j <= blocks && alive; ++j) {
             if (j < blocks) {
@@ -427,7 +454,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
                 const float e0 = m_ref == -INFINITY ? 0.0f : ex2(x[i] - m_ref);
                 const float e1 = m_ref == -INFINITY ? 0.0f : ex2(x[i + 1] - m_ref);
                 sum += e0 + e1;
-                const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+                const __half2 h = __floats2half2_rn(e0, e1);
                 pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
             }
             l += sum;
