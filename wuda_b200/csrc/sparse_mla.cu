@@ -160,14 +160,19 @@ struct KeyRegs {
     int valid;
 };
 
-__device__ __forceinline__ void fetch_key(const Params& p, int b, int g, int n_swa, int n_total, int piece,
-                                          KeyRegs& r, bool* bad) {
-    r.valid = 0;
-    if (g >= n_total) return;
+// The pool entry of key position g of request b (window entries first), -1 past the end.  Loaded one
+// pass before the record loads that depend on it, so that those are not held up by its latency.
+__device__ __forceinline__ int fetch_index(const Params& p, int b, int g, int n_swa, int n_total) {
+    if (g >= n_total) return -1;
     const bool window = g < n_swa;
     const Pool& pool = window ? p.swa : p.cmp;
-    const int idx = __ldg(pool.indices + static_cast<int64_t>(b) * pool.capacity + (window ? g : g - n_swa));
+    return __ldg(pool.indices + static_cast<int64_t>(b) * pool.capacity + (window ? g : g - n_swa));
+}
+
+__device__ __forceinline__ void fetch_key(const Params& p, int g, int n_swa, int idx, int piece, KeyRegs& r, bool* bad) {
+    r.valid = 0;
     if (idx < 0) return;
+    const Pool& pool = g < n_swa ? p.swa : p.cmp;
     const int page = idx / pool.epb, off = idx - page * pool.epb;
     if (page >= pool.pages) {
         *bad = true;
@@ -301,7 +306,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         constexpr int kPasses = kBlock / kPass;
         const int passes = blocks * kPasses, first_key = first * kBlock;
 #pragma unroll
-        for (int u = 0; u < kAhead; ++u) fetch_key(p, b, first_key + u * kPass + row, n_swa, n_total, piece, ring[u], &bad);
+        for (int u = 0; u < kAhead; ++u) {
+            const int g = first_key + u * kPass + row;
+            fetch_key(p, g, n_swa, fetch_index(p, b, g, n_swa, n_total), piece, ring[u], &bad);
+        }
+        int next_idx = fetch_index(p, b, first_key + kAhead * kPass + row, n_swa, n_total);
         bool alive = true;
         for (int q0 = 0; q0 < passes && alive; q0 += kAhead + 1) {
 #pragma unroll
@@ -310,8 +319,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
                 if (q >= passes) break;
                 const int j = q / kPasses, sub = q % kPasses;
                 const int s = j % kOwnStages, t = j % kOthStages;
-                fetch_key(p, b, first_key + (q + kAhead) * kPass + row, n_swa, n_total, piece,
-                          ring[(u + kAhead) % (kAhead + 1)], &bad);
+                const int g_ahead = first_key + (q + kAhead) * kPass + row;
+                fetch_key(p, g_ahead, n_swa, next_idx, piece, ring[(u + kAhead) % (kAhead + 1)], &bad);
+                next_idx = fetch_index(p, b, g_ahead + kPass, n_swa, n_total);
                 if (sub == 0) {
                     if (j >= kOwnStages)
                         alive = mbar_wait_warp(own_free + s * 8, (j / kOwnStages - 1) & 1u, abort_flag, p.status,
@@ -351,17 +361,18 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
                 tc_fence_after();
                 if (lane == 0) {
                     const uint32_t own_addr = base + kOffOwn + s * kHalfStageBytes, oth_addr = base + kOffOth + t * kHalfStageBytes;
+                    // descriptors differ only in their 14-bit address field: one add per MMA
+                    const uint64_t own_desc = umma_smem_desc_sw128(own_addr), oth_desc = umma_smem_desc_sw128(oth_addr);
+                    const uint64_t q_desc = umma_smem_desc_sw128(base + kOffQ);
 #pragma unroll
                     for (int c = 0; c < 8; ++c)
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const uint64_t k_desc =
-                                umma_smem_desc_sw128(((c >> 2) == half ? own_addr : oth_addr) + (c & 3) * kKChunk + k * 32);
+                            const uint64_t k_desc = ((c >> 2) == half ? own_desc : oth_desc) + (((c & 3) * kKChunk + k * 32) >> 4);
                             if (c < kQTmemChunks)
                                 umma_f16_ta(tmem_base + kColS, tmem_base + kColQ + c * 32 + k * 8, k_desc, idesc_qk, (c | k) != 0);
                             else
-                                umma_f16(tmem_base + kColS,
-                                         umma_smem_desc_sw128(base + kOffQ + (c - kQTmemChunks) * kQChunk + k * 32), k_desc,
+                                umma_f16(tmem_base + kColS, q_desc + (((c - kQTmemChunks) * kQChunk + k * 32) >> 4), k_desc,
                                          idesc_qk, 1u);
                         }
                     umma_commit(s_full);
@@ -402,10 +413,17 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
             // not refilled before this block's weighted sum has run
             const volatile uint32_t* vw = reinterpret_cast<const volatile uint32_t*>(valid_bytes + stage * 16);
             float x[kBlock], bmax = -INFINITY;
+            {   // raw scores into registers, then the score buffer goes back to the issuer at once
+                uint32_t* raw = reinterpret_cast<uint32_t*>(x);
+                tmem_ld_32x32(lane_addr + kColS, *reinterpret_cast<uint32_t(*)[32]>(raw));
+                tmem_ld_32x32(lane_addr + kColS + 32, *reinterpret_cast<uint32_t(*)[32]>(raw + 32));
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_empty);
+            }
 #pragma unroll
             for (int h2 = 0; h2 < kBlock / 32; ++h2) {
-                uint32_t v[32];
-                tmem_ld_32x32(lane_addr + kColS + h2 * 32, v);
                 const uint2 vb = make_uint2(vw[2 * h2], vw[2 * h2 + 1]);
                 uint32_t mask = 0;
 #pragma unroll
@@ -413,16 +431,12 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
                     mask |= ((vb.x >> (8 * w)) & 0xfu) << (4 * w);
                     mask |= ((vb.y >> (8 * w)) & 0xfu) << (16 + 4 * w);
                 }
-                tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    x[h2 * 32 + i] = (mask >> i) & 1u ? __uint_as_float(v[i]) * p.scale_log2 : -INFINITY;
+                    x[h2 * 32 + i] = (mask >> i) & 1u ? x[h2 * 32 + i] * p.scale_log2 : -INFINITY;
                     bmax = fmaxf(bmax, x[h2 * 32 + i]);
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty);
             const bool grow = bmax > m_ref + kRescaleStep;   // also the first finite maximum
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? bmax : m_ref;
