@@ -412,7 +412,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
             // the block's valid bits were published before its keys were announced, and its stage is
             // not refilled before this block's weighted sum has run
             const volatile uint32_t* vw = reinterpret_cast<const volatile uint32_t*>(valid_bytes + stage * 16);
-            float x[kBlock], bmax = -INFINITY;
+            float x[kBlock], bm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of 64
             {   // raw scores into registers, then the score buffer goes back to the issuer at once
                 uint32_t* raw = reinterpret_cast<uint32_t*>(x);
                 tmem_ld_32x32(lane_addr + kColS, *reinterpret_cast<uint32_t(*)[32]>(raw));
@@ -434,9 +434,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     x[h2 * 32 + i] = (mask >> i) & 1u ? x[h2 * 32 + i] * p.scale_log2 : -INFINITY;
-                    bmax = fmaxf(bmax, x[h2 * 32 + i]);
+                    bm[i & 3] = fmaxf(bm[i & 3], x[h2 * 32 + i]);
                 }
             }
+            const float bmax = fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3]));
             const bool grow = bmax > m_ref + kRescaleStep;   // also the first finite maximum
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? bmax : m_ref;
@@ -461,17 +462,18 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
                 l *= f;
                 m_ref = m_new;
             }
-            float sum = 0.0f;
+            // while the reference is still -inf every score of the row is -inf too: 2^(-inf - 0) = 0
+            const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+            float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint32_t pk[kBlock / 2];
 #pragma unroll
             for (int i = 0; i < kBlock; i += 2) {
-                const float e0 = m_ref == -INFINITY ? 0.0f : ex2(x[i] - m_ref);
-                const float e1 = m_ref == -INFINITY ? 0.0f : ex2(x[i + 1] - m_ref);
-                sum += e0 + e1;
+                const float e0 = ex2(x[i] - m_use), e1 = ex2(x[i + 1] - m_use);
+                sm[(i >> 1) & 3] += e0 + e1;
                 const __half2 h = __floats2half2_rn(e0, e1);
                 pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
             }
-            l += sum;
+            l += (sm[0] + sm[1]) + (sm[2] + sm[3]);
             if (j >= 2) {   // the weighted sum of block j-2 has read this probability buffer
                 alive = mbar_wait_warp(pv_done + s * 8, ((j >> 1) - 1) & 1u, abort_flag, p.status, kDevTimeoutMlaOutput);
                 if (!alive) break;
