@@ -486,7 +486,7 @@ if __name__ == "__main__":
         one(sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]))
         sys.exit(0)
     {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2,
-     "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(16,), launches_only=3),
+     "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(32,), launches_only=3),
      "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
      "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,
      "moe_experts_launches": lambda: moe_experts(launches_only=2),
