@@ -495,6 +495,12 @@ int wuda_moe_max_groups(int tokens, int k, int experts);
 int wuda_moe_dispatch(const int32_t* indices, const float* weights, int32_t* group_expert, int32_t* num_groups,
                       int32_t* row_token, float* row_weight, int32_t* pair_row, int tokens, int k, int experts,
                       int max_groups, int32_t* status_word, void* stream);
+/* Expert parallelism: this rank holds experts [expert_first, expert_first + experts) of experts_total.
+ * Pairs routed to another rank's expert are skipped (pair_row -1) without a report; an index outside
+ * [0, experts_total) is reported as WUDA_DEV_BAD_EXPERT.  group_expert holds LOCAL expert numbers. */
+int wuda_moe_dispatch_range(const int32_t* indices, const float* weights, int32_t* group_expert, int32_t* num_groups,
+                            int32_t* row_token, float* row_weight, int32_t* pair_row, int tokens, int k, int experts,
+                            int expert_first, int experts_total, int max_groups, int32_t* status_word, void* stream);
 int wuda_moe_gather_quant_nvfp4(const void* x_bf16, const int32_t* row_token, const int32_t* num_groups, void* a_fp4,
                                 void* a_sf_packed, float global_scale, int max_groups, int k, void* stream);
 int wuda_gemm_nvfp4_grouped(const void* a, const void* a_sf_packed, float a_global_scale, const void* w,
@@ -506,6 +512,18 @@ int wuda_moe_swiglu_quant_nvfp4(const void* h_bf16, const int32_t* row_token, co
                                 float swiglu_limit, int max_groups, int inter, void* stream);
 int wuda_moe_combine(const void* expert_out_bf16, const int32_t* pair_row, const void* shared_bf16, void* y_bf16,
                      int tokens, int k, int dim, void* stream);
+/* The combine step of two expert-parallel ranks (each holds half of the experts, the all-reduce site of
+ * origin/model.py:641-642): every rank sums its own experts' rows per token in fp32, pushes the partial
+ * row into the peer GPU's inbox over NVLink peer memory, awaits the peer's row and adds it; y is
+ * bit-identical on both ranks.  Inboxes: wuda_moe_ep2_inbox_bytes(tokens_max, dim) bytes (tokens_max <= 512,
+ * dim <= 8192) from wuda_tp2_alloc, the peer's mapped with wuda_tp2_open; zero-initialised.  `epoch` counts the
+ * calls of the pair from 1 and must advance by one on both ranks; a rank may be one call ahead of its peer.
+ * shared_bf16 is added by the rank that passes it (one of the two).  A peer that does not answer within
+ * peer_wait_ms leaves WUDA_DEV_TIMEOUT_PEER_FLAG in status_word and the local sum in y. */
+int64_t wuda_moe_ep2_inbox_bytes(int tokens_max, int dim);
+int wuda_moe_combine_ep2(const void* expert_out_bf16, const int32_t* pair_row, const void* shared_bf16, void* y_bf16,
+                         int tokens, int k, int dim, void* my_inbox, void* peer_inbox, int tokens_max, int epoch,
+                         int peer_wait_ms, int32_t* status_word, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * mHC post mix, the last op of an attention half-layer:

@@ -113,6 +113,11 @@ SIGNATURES = {
     "wuda_moe_route": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_vp]),
     "wuda_moe_max_groups": (c_int, [c_int, c_int, c_int]),
     "wuda_moe_dispatch": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp, c_vp]),
+    "wuda_moe_dispatch_range": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_vp, c_vp]),
+    "wuda_moe_ep2_inbox_bytes": (c_i64, [c_int, c_int]),
+    "wuda_moe_combine_ep2": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp, c_int, c_int, c_int, c_vp,
+                                     c_vp]),
     "wuda_moe_gather_quant_nvfp4": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_int, c_int, c_vp]),
     "wuda_gemm_nvfp4_grouped": (c_int, [c_vp, c_vp, c_float, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int,
                                         c_int, c_vp, c_i64, c_vp, c_vp]),

@@ -18,6 +18,7 @@
 #include <cuda_bf16.h>
 
 #include "host.h"
+#include "ptx.cuh"
 
 namespace wuda {
 namespace moe {
@@ -34,6 +35,7 @@ struct DispatchParams {
     float* row_weight;        // [max_groups * 16]
     int32_t* pair_row;        // [tokens, k]
     int tokens, k, experts, max_groups;
+    int first, total;         // this rank holds experts [first, first + experts) of `total`
     int32_t* status;
 };
 
@@ -55,9 +57,9 @@ __global__ void __launch_bounds__(kDispatchThreads) moe_dispatch_kernel(Dispatch
     for (int g = threadIdx.x; g < p.max_groups; g += kDispatchThreads) p.group_expert[g] = -1;
     __syncthreads();
     for (int i = threadIdx.x; i < pairs; i += kDispatchThreads) {
-        const int e = p.indices[i];
+        const int global = p.indices[i], e = global - p.first;
         if (e >= 0 && e < p.experts) atomicAdd(&count[e], 1);
-        else if (p.status) atomicCAS(p.status, 0, WUDA_DEV_BAD_EXPERT);
+        else if ((global < 0 || global >= p.total) && p.status) atomicCAS(p.status, 0, WUDA_DEV_BAD_EXPERT);
     }
     __syncthreads();
     if (threadIdx.x == 0) {                 // experts <= 512: a serial scan is a few hundred steps
@@ -78,13 +80,13 @@ __global__ void __launch_bounds__(kDispatchThreads) moe_dispatch_kernel(Dispatch
     }
     // stable placement: the rank of a pair among the earlier pairs of the same expert
     for (int i = threadIdx.x; i < pairs; i += kDispatchThreads) {
-        const int e = p.indices[i];
-        if (e < 0 || e >= p.experts) {
+        const int global = p.indices[i], e = global - p.first;
+        if (e < 0 || e >= p.experts) {   // another rank's expert, or an invalid index
             p.pair_row[i] = -1;
             continue;
         }
         int rank = 0;
-        for (int j = 0; j < i; ++j) rank += (p.indices[j] == e);
+        for (int j = 0; j < i; ++j) rank += (p.indices[j] == global);
         const int row = base[e] * kGroupRows + rank;
         p.pair_row[i] = row;
         p.row_token[row] = i / p.k;
@@ -262,6 +264,118 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
     }
 }
 
+// Expert parallelism over two ranks: each rank sums the outputs of its own experts for every token, pushes
+// the fp32 partial row into the peer GPU's inbox (plain stores through the peer mapping, then a system-scope
+// release of the token's flag), awaits the peer's row in its own inbox and adds it: a + b == b + a in fp32, so
+// both ranks hold bit-identical rows.  Inbox sets alternate with the call's sequence number.  The wait is
+// bounded: a peer that does not answer leaves WUDA_DEV_TIMEOUT_PEER_FLAG and the local sum in y.
+constexpr int64_t kEpFlagBytes = 4096;
+constexpr int kEpMaxTokens = 512;
+constexpr int kEpMaxVec = 4;            // 8-value vectors per thread: dim <= 8192
+
+struct CombineEpParams {
+    CombineParams c;
+    float* my_rows;      // [2 sets][tokens_max][dim] fp32 in this GPU's memory
+    float* peer_rows;    // the same buffer of the peer
+    int32_t* my_flags;   // [2 sets][kEpMaxTokens]
+    int32_t* peer_flags;
+    int tokens_max, epoch;
+    unsigned long long wait_ns;
+    int32_t* status;
+};
+
+__device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_volatile_f32x4(const float* p) {   // written by the peer GPU: bypass L1
+    float4 v;
+    asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(256) moe_combine_ep2_kernel(CombineEpParams q) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const CombineParams& p = q.c;
+    __shared__ int peer_ok;
+    const int t = blockIdx.x;
+    const int set = q.epoch & 1;
+    const int64_t row_off = (static_cast<int64_t>(set) * q.tokens_max + t) * p.dim;
+    float acc[kEpMaxVec][8];
+#pragma unroll
+    for (int v = 0; v < kEpMaxVec; ++v) {
+        const int c = threadIdx.x + v * 256;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[v][i] = 0.f;
+        if (c >= p.dim / 8) continue;
+        for (int j = 0; j < p.k; ++j) {
+            const int row = p.pair_row[t * p.k + j];
+            if (row < 0) continue;
+            const uint4 raw = *(reinterpret_cast<const uint4*>(p.out + static_cast<int64_t>(row) * p.dim) + c);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[v][2 * i] = __fadd_rn(acc[v][2 * i], __uint_as_float(w[i] << 16));
+                acc[v][2 * i + 1] = __fadd_rn(acc[v][2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
+            }
+        }
+        if (p.shared) {
+            const uint4 raw = *(reinterpret_cast<const uint4*>(p.shared + static_cast<int64_t>(t) * p.dim) + c);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[v][2 * i] = __fadd_rn(acc[v][2 * i], __uint_as_float(w[i] << 16));
+                acc[v][2 * i + 1] = __fadd_rn(acc[v][2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
+            }
+        }
+        float4* dst = reinterpret_cast<float4*>(q.peer_rows + row_off + c * 8);
+        dst[0] = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+        dst[1] = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        st_release_sys(q.peer_flags + set * kEpMaxTokens + t, q.epoch);
+        int ok = 1;
+        const unsigned long long start = globaltimer_ns();
+        uint32_t spins = 0;
+        while (ld_acquire_sys(q.my_flags + set * kEpMaxTokens + t) != q.epoch) {
+            if ((++spins & 63u) == 0u && globaltimer_ns() - start > q.wait_ns) {
+                if (q.status) atomicCAS(q.status, 0, static_cast<int>(kDevTimeoutPeerFlag));
+                ok = 0;
+                break;
+            }
+            __nanosleep(100);
+        }
+        peer_ok = ok;
+    }
+    __syncthreads();
+    const bool add = peer_ok != 0;
+#pragma unroll
+    for (int v = 0; v < kEpMaxVec; ++v) {
+        const int c = threadIdx.x + v * 256;
+        if (c >= p.dim / 8) continue;
+        if (add) {
+            const float4 a = ld_volatile_f32x4(q.my_rows + row_off + c * 8), b = ld_volatile_f32x4(q.my_rows + row_off + c * 8 + 4);
+            acc[v][0] += a.x, acc[v][1] += a.y, acc[v][2] += a.z, acc[v][3] += a.w;
+            acc[v][4] += b.x, acc[v][5] += b.y, acc[v][6] += b.z, acc[v][7] += b.w;
+        }
+        uint4 o;
+        uint32_t* ow = &o.x;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(acc[v][2 * i], acc[v][2 * i + 1]);
+            ow[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *(reinterpret_cast<uint4*>(p.y + static_cast<int64_t>(t) * p.dim) + c) = o;
+    }
+}
+
 }  // namespace moe
 }  // namespace wuda
 
@@ -276,10 +390,20 @@ extern "C" int wuda_moe_max_groups(int tokens, int k, int experts) {
 extern "C" int wuda_moe_dispatch(const int32_t* indices, const float* weights, int32_t* group_expert, int32_t* num_groups,
                                  int32_t* row_token, float* row_weight, int32_t* pair_row, int tokens, int k, int experts,
                                  int max_groups, int32_t* status_word, void* stream) {
+    return wuda_moe_dispatch_range(indices, weights, group_expert, num_groups, row_token, row_weight, pair_row, tokens, k,
+                                   experts, 0, experts, max_groups, status_word, stream);
+}
+
+extern "C" int wuda_moe_dispatch_range(const int32_t* indices, const float* weights, int32_t* group_expert,
+                                       int32_t* num_groups, int32_t* row_token, float* row_weight, int32_t* pair_row,
+                                       int tokens, int k, int experts, int expert_first, int experts_total, int max_groups,
+                                       int32_t* status_word, void* stream) {
     using namespace wuda;
     using namespace wuda::moe;
     clear_error();
     WUDA_REQUIRE(tokens >= 1 && k >= 1, "tokens and k must be >= 1");
+    WUDA_REQUIRE(expert_first >= 0 && experts_total >= 1 && expert_first + experts <= experts_total,
+                 "the local experts [%d, %d + %d) must lie inside [0, %d)", expert_first, expert_first, experts, experts_total);
     WUDA_REQUIRE(experts >= 1 && experts <= kMaxExperts, "experts must be in [1, %d] (got %d)", kMaxExperts, experts);
     WUDA_REQUIRE(static_cast<long long>(tokens) * k <= 65536, "at most 65536 (token, expert) pairs per call");
     WUDA_REQUIRE(max_groups >= wuda_moe_max_groups(tokens, k, experts),
@@ -298,6 +422,8 @@ extern "C" int wuda_moe_dispatch(const int32_t* indices, const float* weights, i
     p.tokens = tokens;
     p.k = k;
     p.experts = experts;
+    p.first = expert_first;
+    p.total = experts_total;
     p.max_groups = max_groups;
     p.status = status_word;
     WUDA_CUDA(launch_pdl(moe_dispatch_kernel, dim3(1), dim3(kDispatchThreads), 0, static_cast<cudaStream_t>(stream), p));
@@ -368,5 +494,45 @@ extern "C" int wuda_moe_combine(const void* expert_out_bf16, const int32_t* pair
     p.k = k;
     p.dim = dim;
     WUDA_CUDA(launch_pdl(moe_combine_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream), p));
+    return WUDA_OK;
+}
+
+extern "C" int64_t wuda_moe_ep2_inbox_bytes(int tokens_max, int dim) {
+    using namespace wuda::moe;
+    if (tokens_max < 1 || tokens_max > kEpMaxTokens || dim < 8 || dim % 8 != 0 || dim > kEpMaxVec * 256 * 8) return -1;
+    return kEpFlagBytes + 2ll * tokens_max * dim * 4;
+}
+
+extern "C" int wuda_moe_combine_ep2(const void* expert_out_bf16, const int32_t* pair_row, const void* shared_bf16,
+                                    void* y_bf16, int tokens, int k, int dim, void* my_inbox, void* peer_inbox,
+                                    int tokens_max, int epoch, int peer_wait_ms, int32_t* status_word, void* stream) {
+    using namespace wuda;
+    using namespace wuda::moe;
+    clear_error();
+    WUDA_REQUIRE(tokens >= 1 && k >= 1 && tokens <= tokens_max, "1 <= tokens <= tokens_max and k >= 1");
+    WUDA_REQUIRE(wuda_moe_ep2_inbox_bytes(tokens_max, dim) > 0, "tokens_max must be in [1, %d] and dim a multiple of 8 up to %d",
+                 kEpMaxTokens, kEpMaxVec * 256 * 8);
+    WUDA_REQUIRE(expert_out_bf16 && pair_row && y_bf16 && my_inbox && peer_inbox,
+                 "expert_out, pair_row, y and both inboxes must not be NULL");
+    WUDA_REQUIRE(aligned16(expert_out_bf16) && aligned16(shared_bf16) && aligned16(y_bf16) && aligned16(my_inbox) &&
+                     aligned16(peer_inbox), "rows and inboxes must be 16-byte aligned");
+    WUDA_REQUIRE(epoch >= 1, "epoch counts calls from 1 (got %d)", epoch);
+    WUDA_REQUIRE(peer_wait_ms >= 1 && peer_wait_ms <= 10000, "peer_wait_ms must be in [1, 10000] (got %d)", peer_wait_ms);
+    CombineEpParams q;
+    q.c.out = static_cast<const __nv_bfloat16*>(expert_out_bf16);
+    q.c.pair_row = pair_row;
+    q.c.shared = static_cast<const __nv_bfloat16*>(shared_bf16);
+    q.c.y = static_cast<__nv_bfloat16*>(y_bf16);
+    q.c.k = k;
+    q.c.dim = dim;
+    q.my_flags = static_cast<int32_t*>(my_inbox);
+    q.peer_flags = static_cast<int32_t*>(peer_inbox);
+    q.my_rows = reinterpret_cast<float*>(static_cast<uint8_t*>(my_inbox) + kEpFlagBytes);
+    q.peer_rows = reinterpret_cast<float*>(static_cast<uint8_t*>(peer_inbox) + kEpFlagBytes);
+    q.tokens_max = tokens_max;
+    q.epoch = epoch;
+    q.wait_ns = static_cast<unsigned long long>(peer_wait_ms) * 1000ull * 1000ull;
+    q.status = status_word;
+    WUDA_CUDA(launch_pdl(moe_combine_ep2_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream), q));
     return WUDA_OK;
 }

@@ -5,6 +5,8 @@ allocated once; a forward pass is eight launches with no host synchronisation in
 of row groups stays on the device), so it can be captured into a CUDA graph.
 """
 import numpy as np
+import ctypes
+
 import torch
 
 from . import ops, workloads
@@ -50,9 +52,61 @@ class RandomRoutedExperts:
             w2_gs=torch.full((experts,), 1e-3, device=device))
 
 
+class EP2Link:
+    """Exchange buffers of two expert-parallel ranks for the combine step of the routed experts
+    (the all-reduce site of MoE.forward, origin/model.py:641-642): each rank's inbox receives the peer's
+    fp32 partial rows over NVLink peer memory.  Created like ops.TP2Link (the IPC handles travel over
+    torch.distributed once); `loopback=True` makes the rank its own peer (one GPU: y = local + local),
+    `mute=True` gives a peer that never answers (time-out path)."""
+
+    def __init__(self, max_tokens, dim, group=None, peer_handle=None, loopback=False, mute=False):
+        self.max_tokens, self.dim = max_tokens, dim
+        self.nbytes = lib.wuda_moe_ep2_inbox_bytes(max_tokens, dim)
+        if self.nbytes <= 0:
+            raise ValueError("unsupported (max_tokens, dim) for the exchange buffer")
+        self._local, self._peer, self._mute = ctypes.c_void_p(), ctypes.c_void_p(), None
+        handle = (ctypes.c_ubyte * 64)()
+        check(lib.wuda_tp2_alloc(self.nbytes, ctypes.byref(self._local), handle))
+        self.handle, self.epoch, self._own_peer = bytes(handle), 0, False
+        if mute:
+            self._mute = ctypes.c_void_p()
+            check(lib.wuda_tp2_alloc(self.nbytes, ctypes.byref(self._mute), (ctypes.c_ubyte * 64)()))
+            self._peer = self._mute
+        elif loopback:
+            self._peer = self._local
+        else:
+            if peer_handle is None:
+                peer_handle = ops.exchange_handles(self.handle, group)
+            check(lib.wuda_tp2_open((ctypes.c_ubyte * 64).from_buffer_copy(peer_handle), ctypes.byref(self._peer)))
+            self._own_peer = True
+
+    def close(self):
+        if self._own_peer and self._peer:
+            lib.wuda_tp2_close(self._peer)
+        self._peer, self._own_peer = None, False
+        if self._mute:
+            lib.wuda_tp2_free(self._mute)
+            self._mute = None
+        if self._local:
+            lib.wuda_tp2_free(self._local)
+            self._local = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class MoERunner:
-    def __init__(self, weights, max_tokens, topk, device="cuda"):
+    """Routed experts of one rank.  With expert parallelism the rank holds experts
+    [expert_first, expert_first + weights.experts) of experts_total and `link` joins it to its peer."""
+
+    def __init__(self, weights, max_tokens, topk, device="cuda", expert_first=0, experts_total=None, link=None,
+                 peer_wait_ms=2000):
         self.w, self.max_tokens, self.topk = weights, max_tokens, topk
+        self.expert_first, self.experts_total = expert_first, experts_total or weights.experts
+        self.link, self.peer_wait_ms = link, peer_wait_ms
         self.max_groups = lib.wuda_moe_max_groups(max_tokens, topk, weights.experts)
         rows = self.max_groups * 16
         dev = device
@@ -76,9 +130,10 @@ class MoERunner:
             raise ValueError("batch does not fit this runner")
         s = torch.cuda.current_stream().cuda_stream
         st = self.status.data_ptr()
-        check(lib.wuda_moe_dispatch(indices.data_ptr(), weights.data_ptr(), self.group_expert.data_ptr(),
-                                    self.num_groups.data_ptr(), self.row_token.data_ptr(), self.row_weight.data_ptr(),
-                                    self.pair_row.data_ptr(), m, self.topk, w.experts, self.max_groups, st, s))
+        check(lib.wuda_moe_dispatch_range(indices.data_ptr(), weights.data_ptr(), self.group_expert.data_ptr(),
+                                          self.num_groups.data_ptr(), self.row_token.data_ptr(), self.row_weight.data_ptr(),
+                                          self.pair_row.data_ptr(), m, self.topk, w.experts, self.expert_first,
+                                          self.experts_total, self.max_groups, st, s))
         check(lib.wuda_moe_gather_quant_nvfp4(x.data_ptr(), self.row_token.data_ptr(), self.num_groups.data_ptr(),
                                               self.a1.data_ptr(), self.a1_sf.data_ptr(), w.act_scale_in, self.max_groups,
                                               w.dim, s))
@@ -96,8 +151,15 @@ class MoERunner:
                                           w.dim, w.inter, self.scratch.data_ptr(), self.scratch.numel(), st, s))
         if y is None:
             y = torch.empty(m, w.dim, dtype=torch.bfloat16, device=x.device)
-        check(lib.wuda_moe_combine(self.out.data_ptr(), self.pair_row.data_ptr(), shared.data_ptr() if shared is not None else None,
-                                   y.data_ptr(), m, self.topk, w.dim, s))
+        shared_ptr = shared.data_ptr() if shared is not None else None
+        if self.link is None:
+            check(lib.wuda_moe_combine(self.out.data_ptr(), self.pair_row.data_ptr(), shared_ptr, y.data_ptr(), m, self.topk,
+                                       w.dim, s))
+        else:
+            self.link.epoch += 1
+            check(lib.wuda_moe_combine_ep2(self.out.data_ptr(), self.pair_row.data_ptr(), shared_ptr, y.data_ptr(), m,
+                                           self.topk, w.dim, self.link._local, self.link._peer, self.link.max_tokens,
+                                           self.link.epoch, int(self.peer_wait_ms), st, s))
         return y
 
 
