@@ -16,6 +16,7 @@ because consecutive launches use different weight buffers that together exceed L
     python -m wuda_b200.benchmarks sparse_mla_launches             (three eager launches of a small case, for ncu)
     python -m wuda_b200.benchmarks one gemm_fp8 64 24576 7168      (a few launches of one shape, for ncu)
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks tp2
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks moe_ep2
 """
 import json
 import os
@@ -408,6 +409,63 @@ def moe_experts(tokens=64, topk=8, experts=256, dim=7168, inter=2048, reps=10, l
           (us, wbytes / 1e9, wbytes / us / 1e3, wbytes / us / 1e3 / hbm, kind))
 
 
+def moe_ep2(tokens=64, topk=8, experts=256, dim=7168, inter=2048, iters=20):
+    """Run under torch.distributed.run with two ranks: router + routed experts of one MoE block with the
+    256 experts split over the two ranks and the combine step exchanging fp32 rows over NVLink peer
+    memory; time per block = max over ranks of the device time."""
+    import torch.distributed as dist
+    from wuda_b200 import moe
+    rank = int(os.environ["RANK"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("gloo")
+    hbm, _, kind = peaks()
+    half = experts // 2
+    g = torch.Generator(device="cuda").manual_seed(3)          # the same tokens and gate on both ranks
+    x = torch.randn(tokens, dim, generator=g, device="cuda").bfloat16()
+    gate_w = (torch.randn(experts, dim, generator=g, device="cuda") * 0.05).bfloat16()
+    bias = torch.zeros(experts, device="cuda")
+    logits = torch.empty(tokens, experts, device="cuda")
+    y = torch.empty(tokens, dim, dtype=torch.bfloat16, device="cuda")
+    w = moe.RandomRoutedExperts(half, inter, dim, seed=10 + rank)
+    link = moe.EP2Link(tokens, dim)
+    runner = moe.MoERunner(w, tokens, topk, expert_first=rank * half, experts_total=experts, link=link)
+
+    def step():
+        rw, idx = wuda.moe_gate(x, gate_w, bias, "sqrtsoftplus", 2.5, topk, logits=logits)
+        runner.forward(x, rw, idx, y=y)
+        return idx
+
+    for _ in range(3):
+        idx = step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    mine = (idx >= rank * half) & (idx < (rank + 1) * half)
+    active = torch.tensor([int(torch.unique(idx[mine]).numel())], dtype=torch.float64)
+    both = [torch.zeros(1, dtype=torch.float64) for _ in range(2)]
+    dist.all_gather(both, active)
+    status = int(runner.status.item())
+    if rank == 0:
+        per_expert = 2 * inter * dim // 2 + 2 * inter * dim // 16 + dim * inter // 2 + dim * inter // 16
+        most = max(float(b.item()) for b in both)
+        print("MoE block on two expert-parallel ranks: %d tokens x top-%d of %d experts (%d + %d active), status %d" %
+              (tokens, topk, experts, int(both[0].item()), int(both[1].item()), status))
+        print("  %.1f us per block (eager launches, max over ranks); the busier rank streams %.2f GB -> %.0f GB/s = %.2f of "
+              "%s HBM peak; %.1f MB over the link per rank" %
+              (float(t.item()), most * per_expert / 1e9, most * per_expert / float(t.item()) / 1e3,
+               most * per_expert / float(t.item()) / 1e3 / hbm, kind, tokens * dim * 4 / 1e6))
+    dist.barrier()
+    link.close()
+    dist.destroy_process_group()
+
+
 def model1_pool(pages, epb, seed):
     """uint8 [pages, stride] pool of random MODEL1 records (finite e4m3, exponents near 0, small bf16)."""
     g = torch.Generator(device="cuda").manual_seed(seed)
@@ -485,7 +543,7 @@ if __name__ == "__main__":
     if which == "one":
         one(sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]))
         sys.exit(0)
-    {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2,
+    {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2,
      "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(32,), launches_only=3),
      "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
      "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,
