@@ -218,7 +218,6 @@ def csa_chain(batch=64, context=32768, topk=2048, reps=30, launches_only=0):
                          torch.sin(ang).contiguous(), index_heads=ih, main_heads=mh)
     pages_per_req = (context // 4 + 63) // 64 + 1
     cache = KVCacheManager(batch, batch * pages_per_req + batch, pages_per_req, device=dev)
-    stage = CsaDecodeStage(weights, cache, batch, topk=topk)
     slots = [cache.alloc_request() for _ in range(batch)]
     for s in slots:
         cache.advance(s, context - 1)               # the timed token is the one at position context - 1
@@ -287,7 +286,6 @@ def attention_half_layer(batch=64, context=32768, topk=2048, reps=30, launches_o
                          cos, sin, index_heads=ih, main_heads=mh)
     pages_per_req = (context // 4 + 63) // 64 + 1
     cache = KVCacheManager(batch, batch * pages_per_req + batch, pages_per_req, device=dev)
-    stage = CsaDecodeStage(weights, cache, batch, topk=topk)
     slots = [cache.alloc_request() for _ in range(batch)]
     for s_ in slots:
         cache.advance(s_, context - 1)
@@ -297,43 +295,25 @@ def attention_half_layer(batch=64, context=32768, topk=2048, reps=30, launches_o
     pool[:, epb * 128:epb * 132] = (torch.rand(pool.size(0), epb, generator=g, device=dev) * 0.09 + 0.01).view(torch.uint8)
     cache.main_state.normal_(generator=g)
     cache.idx_state.normal_(generator=g)
-    stage.prepare(slots)
     # weights of the other stages
-    hc_w = torch.randn(24, 4 * hidden, generator=g, device=dev) * 0.01
-    hc_base, hc_scale = torch.zeros(24, device=dev), torch.ones(3, device=dev)
-    gamma = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
-    w8, w8s = rnd8(2048, hidden), sc(16, hidden // 128)
-    w16 = (torch.randn(2624, hidden, generator=g, device=dev) * 0.02).bfloat16()
-    ape, idx_ape = torch.randn(4, 1024, generator=g, device=dev), torch.randn(4, 256, generator=g, device=dev)
-    oproj = o_proj.OProjWeights(rnd8(16, 1024, 4096), sc(16 * 8, 32), rnd8(hidden, 16384), sc(56, 128))
+    from wuda_b200.layer import AttentionHalfLayer, HalfLayerWeights
+    hw = HalfLayerWeights(
+        hc_weight=torch.randn(24, 4 * hidden, generator=g, device=dev) * 0.01, hc_base=torch.zeros(24, device=dev),
+        hc_scale=torch.ones(3, device=dev), attn_norm=torch.ones(hidden, dtype=torch.bfloat16, device=dev),
+        front_w8=rnd8(2048, hidden), front_w8_scales=sc(16, hidden // 128),
+        front_w16=(torch.randn(2624, hidden, generator=g, device=dev) * 0.02).bfloat16(),
+        ape=torch.randn(4, 1024, generator=g, device=dev), idx_ape=torch.randn(4, 256, generator=g, device=dev),
+        o_proj=o_proj.OProjWeights(rnd8(16, 1024, 4096), sc(16 * 8, 32), rnd8(hidden, 16384), sc(56, 128)),
+        attn_sink=torch.randn(mh, generator=g, device=dev))
     x_hidden = torch.randn(batch, 4, hidden, generator=g, device=dev).bfloat16()
-    mla_out = torch.empty(batch, mh, 512, dtype=torch.bfloat16, device=dev)
     for name in ("swa", "cmp"):   # attention caches: random finite records instead of the zeros of a fresh pool
         data = cache._pools[name].data
         epb_m = cache.entries_per_block[name]
         data[:, :epb_m * 584] = model1_pool(data.size(0), epb_m, 5)[:, :epb_m * 584]
-    swa_idx, swa_len = cache.swa_indices(slots, [context - 1] * batch, 128)
-    swa_idx = swa_idx.view(batch, 128).contiguous()
-    cmp_len = torch.clamp(stage.n_compressed[:batch], max=topk).contiguous()
-    sink = torch.randn(mh, generator=g, device=dev)
-    front_out = torch.empty(batch, 2048, dtype=torch.bfloat16, device=dev)
-    y16 = torch.empty(batch, 2624, dtype=torch.float32, device=dev)
-    ws = torch.empty(wuda.lib.wuda_mhc_pre_workspace_bytes(batch, hidden), dtype=torch.uint8, device=dev)
-    stage.q_raw = front_out[:, :q_lora]                                            # read in place by the chain
-    result = {}
-
-    def layer():
-        pre = wuda.mhc_pre(x_hidden, hc_w, hc_base, hc_scale, gamma, workspace=ws)
-        wuda.front_mixed_gemm(pre["normed"], pre["xq"], pre["xsf"], w16, w8, w8s, front_out, pos=stage.pos,
-                              main_state=cache.main_state, ape=ape, main_state_row=stage.main_state_row,
-                              idx_state=cache.idx_state, idx_state_row=stage.idx_state_row, idx_ape=idx_ape,
-                              win_y2=stage.win_y2, w64=stage.w64, y16=y16, status_word=stage.status)
-        stage.launch(batch)
-        wuda.sparse_mla_decode(stage.q_main[:batch], cache.model1_cache_view("swa"), swa_idx, swa_len,
-                               cache.model1_cache_view("cmp"), stage.topk_indices[:batch], cmp_len, sink, 512 ** -0.5,
-                               out=mla_out, status_word=stage.status)
-        result["out"] = o_proj.run_o_proj_mhc_post(mla_out, stage.pos, cos, sin, x_hidden, pre["post"], pre["comb"], oproj,
-                                                   status_word=stage.status)
+    half_layer = AttentionHalfLayer(weights, hw, cache, batch, topk=topk)
+    stage = half_layer.stage
+    half_layer.prepare(slots)
+    layer = lambda: half_layer.launch(x_hidden, batch)
 
     if launches_only:
         for _ in range(launches_only):
