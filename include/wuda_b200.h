@@ -368,6 +368,27 @@ int wuda_csa_decode_step(const wuda_csa_weights* weights, const wuda_csa_caches*
                          const wuda_csa_workspace* workspace, int m, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Paged MQA logits on MXFP4 operands (the FP4 form of the indexer):
+ *   logits[b, t] = sum_h weights[b, h] * relu(q[b, h, :] . k[t, :]),  t < context_lens[b]
+ * q_fp4 uint8 [batch, 64, 64]: 128 e2m1 values per head, two per byte, low nibble first;
+ * q_scales int32 [batch, 64]: four ue8m0 bytes per head, byte g scales values [32g, 32g+32);
+ * kv_pages uint8 [num_blocks, page_stride_bytes]: entries_per_block rows of 64 key bytes, then
+ * entries_per_block scale words of the same form (68 bytes per token); weights fp32 [batch, 64];
+ * context_lens int32 [batch]; block_table int32 [batch, block_table_stride]; logits fp32
+ * [batch, logits_stride], only t < context is written (a -inf pre-fill by the caller persists).
+ * The block scales are applied inside the tensor core (block-scaled MMA); sums in fp32.
+ *
+ * Replaces mqa_logits_fp4_decode_out (kernels/mqa_logits_fp4.cu:474-650); formats as
+ * test/test_mqa_logits_fp4.py:100-115 and :228-256, arithmetic as its twin (:207-218) over the
+ * dequantised values.  A block_table entry outside [0, num_blocks) reads page 0 and is reported
+ * as WUDA_DEV_BAD_PAGE_INDEX.
+ */
+int wuda_mqa_logits_fp4(const void* q_fp4, const void* q_scales, const void* kv_pages, const float* weights,
+                        const int32_t* context_lens, const int32_t* block_table, float* logits, int batch,
+                        int max_context, int num_blocks, int entries_per_block, int64_t page_stride_bytes,
+                        int block_table_stride, int64_t logits_stride, int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Sparse MLA decode attention over gathered FP8 cache records: per request one query token
  * with `heads` heads of 512 dims attends to swa_lengths[b] sliding-window entries and then
  * cmp_lengths[b] top-k compressed entries, each named by a pool entry index

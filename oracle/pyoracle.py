@@ -291,6 +291,43 @@ def sparse_mla(q_bf16, swa, cmp, sink, scale):
     return out
 
 
+E2M1_VALUES = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0])
+
+
+def dequant_mxfp4(packed_u8, scale_words):
+    """packed uint8 [..., 64] (two e2m1 per byte, low nibble first) with uint32 [...] scale words (four ue8m0
+    bytes, byte g scales values [32g, 32g+32)) -> float64 [..., 128], as cast_back_from_fp4 of
+    dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py:103-115."""
+    p = np.asarray(packed_u8, np.uint8)
+    v = np.empty(p.shape[:-1] + (128,), np.float64)
+    v[..., 0::2] = E2M1_VALUES[p & 15]
+    v[..., 1::2] = E2M1_VALUES[p >> 4]
+    w = np.asarray(scale_words).astype(np.uint32)
+    e = np.stack([(w >> (8 * g)) & 255 for g in range(4)], axis=-1).astype(np.int64)      # [..., 4]
+    return v * np.repeat(np.ldexp(1.0, e - 127), 32, axis=-1)
+
+
+def mqa_logits_fp4(q, q_sf, kv_pages, weights, context_lens, block_table, epb, columns):
+    """logits[b, t] = sum_h w[b, h] relu(q[b, h] . k[t]) over dequantised MXFP4 operands (the twin
+    ref_fp8_mqa_logits, test_mqa_logits_fp4.py:207-218), t < context; -inf elsewhere.  Test infrastructure."""
+    q = np.asarray(q).view(np.uint8)
+    batch = q.shape[0]
+    qf = dequant_mxfp4(q, np.asarray(q_sf).view(np.uint32).reshape(batch, 64))
+    out = np.full((batch, columns), -np.inf, np.float32)
+    for b in range(batch):
+        n = int(context_lens[b])
+        if n == 0:
+            continue
+        t = np.arange(n)
+        page, off = np.asarray(block_table)[b, t // epb], t % epb
+        keys = kv_pages[page[:, None], (off * 64)[:, None] + np.arange(64)[None, :]]
+        sw = kv_pages[page[:, None], (epb * 64 + off * 4)[:, None] + np.arange(4)[None, :]].copy().view(np.uint32)[:, 0]
+        kf = dequant_mxfp4(keys, sw)                                         # [n, 128]
+        score = np.maximum(qf[b] @ kf.T, 0.0)                                # [64, n]
+        out[b, :n] = (np.asarray(weights, np.float64)[b][:, None] * score).sum(0)
+    return out
+
+
 def gemm_bf16(a_bf16, w_bf16):
     """a uint16 (bf16) [M,K], w uint16 [N,K] -> float64 [M,N] (products of bf16 values are exact in
     fp32; the sum is taken in double so that any fp32 summation order can be held against it)."""

@@ -6,7 +6,8 @@ neither the checkout nor this script.
     python tests/golden/make_golden.py /path/to/reference
 
 Functions used (paths inside the reference repository):
-  dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py  ref_fp8_mqa_logits (:207-218)
+  dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py  ref_fp8_mqa_logits (:207-218); quantize_fp4 (:222-227),
+                                                           build_paged_cache (:235-262) for the FP4 form
   dsv4_megakernel/megakernel/test/test_topk_v2.py         ref_page_transform (:86-94) and the
                                                            stable-argsort rule (:116)
   dsv4_megakernel/megakernel/test/test_e2e_decode.py      ref_mhc_post (:423-426), ref_flash_attn
@@ -90,6 +91,32 @@ def golden_mqa(ref_mqa, name, **kw):
     np.savez_compressed(os.path.join(HERE, name), expected=expected, next_n=case["next_n"], epb=case["epb"],
                         logits_stride=case["logits_stride"], **arrays)
     print(name, expected.shape, "finite:", int(np.isfinite(expected).sum()))
+
+
+def golden_mqa_fp4(ref_mqa):
+    """MXFP4 indexer scores: the reference's quantiser (quantize_fp4), page builder (build_paged_cache, shuffled
+    pages) and torch twin (ref_fp8_mqa_logits over the dequantised values), all run on the CPU."""
+    torch.manual_seed(31)
+    batch, tokens, epb = 3, 384, 64
+    q = torch.randn(batch, 64, 128).bfloat16()
+    kv = torch.randn(batch, tokens, 128).bfloat16()
+    weights = torch.randn(batch, 64)
+    q_p, q_sf, q_sim = ref_mqa.quantize_fp4(q, 128)
+    kv_p, kv_sf, kv_sim = ref_mqa.quantize_fp4(kv, 128)
+    stride = epb * 68 + 48
+    fused, table = ref_mqa.build_paged_cache(kv_p.view(-1, 64), kv_sf.view(-1), batch, tokens, shuffle=True,
+                                             entries_per_block=epb, block_stride_bytes=stride)
+    ctx = [384, 201, 1]
+    rows = []
+    for b in range(batch):
+        ks, ke = torch.zeros(1, dtype=torch.int32), torch.full((1,), ctx[b], dtype=torch.int32)
+        rows.append(ref_mqa.ref_fp8_mqa_logits(q_sim.view(batch, 64, 128)[b:b + 1], kv_sim.view(batch, tokens, 128)[b],
+                                               weights[b:b + 1], ks, ke)[0])
+    np.savez_compressed(os.path.join(HERE, "mqa_logits_fp4.npz"), q=q_p.view(batch, 64, 64).numpy().view(np.uint8),
+                        q_sf=q_sf.view(batch, 64).numpy(), pages=fused.numpy(), weights=weights.numpy(),
+                        context_lens=np.asarray(ctx, np.int32), block_table=table.numpy(), epb=np.int32(epb),
+                        logits=torch.stack(rows).float().numpy())
+    print("mqa_logits_fp4.npz", batch, tokens)
 
 
 def golden_topk(ref_topk, name, rows, length, k, lens, tie_levels, seed):
@@ -397,6 +424,7 @@ def main():
     golden_mqa(ref_mqa, "mqa_logits_fp8_n1.npz", batch=3, next_n=1, ctx_lo=1, ctx_hi=400, epb=64, seed=11)
     golden_mqa(ref_mqa, "mqa_logits_fp8_n2_epb32.npz", batch=2, next_n=2, ctx_lo=60, ctx_hi=300, epb=32,
                seed=12, page_pad=128)
+    golden_mqa_fp4(ref_mqa)
     ref_topk = _load(ref_root, tdir + "/test_topk_v2.py", "ref_topk")
     golden_topk(ref_topk, "topk_random.npz", 3, 3000, 512, [3000, 2100, 300], 0, 21)
     golden_topk(ref_topk, "topk_ties.npz", 2, 4096, 1024, [4096, 2500], 7, 22)

@@ -287,3 +287,15 @@ def test_sparse_mla_oracle_matches_reference_twin():
     got = oracle.sparse_mla(g["q"], (g["swa_pool"], int(g["swa_epb"]), g["swa_idx"], g["swa_len"]),
                             (g["cmp_pool"], int(g["cmp_epb"]), g["cmp_idx"], g["cmp_len"]), g["sink"], float(g["scale"]))
     assert np.max(np.abs(got - g["out"])) <= 2e-5 * np.max(np.abs(g["out"]))
+
+
+def test_mqa_logits_fp4_oracle_matches_reference_twin():
+    """MXFP4 indexer scores: inputs quantised and paged by the reference's own helpers, expected values from
+    its torch twin over the dequantised operands."""
+    g = load_golden("mqa_logits_fp4.npz")
+    got = oracle.mqa_logits_fp4(g["q"], g["q_sf"], g["pages"], g["weights"], g["context_lens"], g["block_table"],
+                                int(g["epb"]), g["logits"].shape[1])
+    ref = g["logits"]
+    valid = np.isfinite(ref)
+    assert np.array_equal(np.isfinite(got), valid)
+    assert np.max(np.abs(got[valid] - ref[valid])) <= 1e-5 * np.sqrt(np.mean(ref[valid].astype(np.float64) ** 2))

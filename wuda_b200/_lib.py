@@ -100,6 +100,8 @@ SIGNATURES = {
     "wuda_query_rms_rope": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_int, c_vp, c_int, c_int, c_int, c_float, c_vp]),
     "wuda_csa_decode_step": (c_int, [ctypes.POINTER(CsaWeights), ctypes.POINTER(CsaCaches), ctypes.POINTER(CsaStep),
                                      ctypes.POINTER(CsaWorkspace), c_int, c_vp]),
+    "wuda_mqa_logits_fp4": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_i64, c_int,
+                                    c_i64, c_vp, c_vp]),
     "wuda_sparse_mla_workspace_bytes": (c_i64, [c_int, c_int, c_int]),
     "wuda_sparse_mla_decode": (c_int, [ctypes.POINTER(SparseMlaArgs), c_vp, c_vp]),
     "wuda_mhc_pre_workspace_bytes": (c_i64, [c_int, c_int]),

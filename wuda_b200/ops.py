@@ -13,7 +13,7 @@ import torch
 from . import _lib
 from ._lib import WudaError, check, lib
 
-__all__ = ["mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
+__all__ = ["mqa_logits_fp4_decode_out", "mqa_logits_fp4_decode", "mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "sparse_mla_decode", "flash_mla_with_kvcache", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
            "rmsnorm_rope_out", "mhc_post_out", "mhc_pre", "moe_gate", "bf16_gemm", "front_mixed_gemm", "idx_postprocess_fp8", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
 
@@ -101,6 +101,48 @@ def fp8_paged_mqa_logits(q, kv_cache, weights, context_lens, block_table, schedu
                               context_lens, block_table, schedule_meta, logits, kv_entries_per_block,
                               next_n=next_n, status_word=status_word)
     return logits[:, :max_context_len]
+
+
+def mqa_logits_fp4_decode_out(q, sf_q, kv_cache, weights, context_lens, block_table, logits, max_context_len=None,
+                              kv_entries_per_block=64, kv_block_stride_bytes=0, *, status_word=None):
+    """The FP4 indexer scores with the reference's argument order (kernels/mqa_logits_fp4.cu:474-650): q int8
+    [B, 64, 64] packed e2m1, sf_q int32 [B, 64] (four ue8m0 bytes), kv_cache uint8 [num_blocks, stride] of fused
+    pages (keys, then scale words), weights fp32 [B, 64], context_lens int32 [B], block_table int32 [B, pages],
+    logits fp32 [B, >= max_context_len]; only t < context is written."""
+    _require(q.is_cuda and q.is_contiguous() and q.element_size() == 1 and q.dim() == 3 and q.shape[1:] == (64, 64),
+             "q must be contiguous CUDA int8 [B, 64, 64]")
+    b = q.size(0)
+    _require(sf_q.is_cuda and sf_q.is_contiguous() and sf_q.dtype == torch.int32 and sf_q.numel() == b * 64,
+             "sf_q must be contiguous CUDA int32 [B, 64]")
+    _require(kv_cache.is_cuda and kv_cache.is_contiguous() and kv_cache.dtype == torch.uint8 and kv_cache.dim() == 2,
+             "kv_cache must be contiguous CUDA uint8 [num_blocks, stride]")
+    _require(kv_block_stride_bytes in (0, kv_cache.size(1)), "kv_block_stride_bytes must match kv_cache")
+    _f32(weights, "weights")
+    _require(weights.numel() == b * 64, "weights must be [B, 64]")
+    _require(context_lens.is_cuda and context_lens.dtype == torch.int32 and context_lens.numel() == b and
+             context_lens.is_contiguous(), "context_lens must be contiguous CUDA int32 [B]")
+    _require(block_table.is_cuda and block_table.dtype == torch.int32 and block_table.dim() == 2 and
+             block_table.size(0) == b and block_table.stride(1) == 1, "block_table must be CUDA int32 [B, pages]")
+    _require(logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.size(0) >= b and
+             logits.stride(1) == 1, "logits must be CUDA fp32 [>= B, columns]")
+    max_ctx = int(max_context_len) if max_context_len is not None else min(logits.size(1),
+                                                                            block_table.size(1) * kv_entries_per_block)
+    _require(max_ctx <= logits.size(1), "logits has fewer columns than max_context_len")
+    check(lib.wuda_mqa_logits_fp4(q.data_ptr(), sf_q.data_ptr(), kv_cache.data_ptr(), weights.data_ptr(),
+                                  context_lens.data_ptr(), block_table.data_ptr(), logits.data_ptr(), b, max_ctx,
+                                  kv_cache.size(0), int(kv_entries_per_block), kv_cache.size(1), block_table.stride(0),
+                                  logits.stride(0), _ptr(status_word), _stream()))
+    return logits
+
+
+def mqa_logits_fp4_decode(q, sf_q, kv_cache, weights, context_lens, block_table, max_context_len,
+                          out_dtype=torch.float32, kv_entries_per_block=64, kv_block_stride_bytes=0):
+    """The allocating form (kernels/mqa_logits_fp4.cu:652-700): returns fp32 [B, max_context_len] with -inf
+    at and beyond each request's context."""
+    _require(out_dtype == torch.float32, "only fp32 logits are implemented")
+    logits = torch.full((q.size(0), int(max_context_len)), float("-inf"), dtype=torch.float32, device=q.device)
+    return mqa_logits_fp4_decode_out(q, sf_q, kv_cache, weights, context_lens, block_table, logits, max_context_len,
+                                     kv_entries_per_block, kv_block_stride_bytes)
 
 
 def topk_v2_transform(scores, seq_lens, page_table, page_indices, page_size=64, metadata=None,
