@@ -12,6 +12,7 @@ because consecutive launches use different weight buffers that together exceed L
     python -m wuda_b200.benchmarks attention_half_layer_launches   (three eager passes, for an ncu launch list)
     python -m wuda_b200.benchmarks moe_experts                     (router + routed NVFP4 experts of one MoE block)
     python -m wuda_b200.benchmarks moe_experts_launches            (two eager passes, for an ncu launch list)
+    python -m wuda_b200.benchmarks mqa_fp4                         (MXFP4 paged MQA logits)
     python -m wuda_b200.benchmarks sparse_mla                      (sparse MLA decode attention, window 128 + top-2048)
     python -m wuda_b200.benchmarks sparse_mla_launches             (three eager launches of a small case, for ncu)
     python -m wuda_b200.benchmarks one gemm_fp8 64 24576 7168      (a few launches of one shape, for ncu)
@@ -446,6 +447,39 @@ def moe_ep2(tokens=64, topk=8, experts=256, dim=7168, inter=2048, iters=20):
     dist.destroy_process_group()
 
 
+def mqa_fp4(batches=(64,), contexts=(8192, 32768), launches_only=0):
+    """MXFP4 paged MQA logits (68 bytes per token): identity page tables, random codes and scale bytes."""
+    hbm, _, kind = peaks()
+    print("MXFP4 paged MQA logits, 64 heads x 128; HBM peak (%s) %.0f GB/s" % (kind, hbm))
+    for batch in batches:
+        for ctx in contexts:
+            g = torch.Generator(device="cuda").manual_seed(ctx)
+            epb, pages_per = 64, ctx // 64
+            pages = torch.randint(0, 256, (batch * pages_per, epb * 68), generator=g, dtype=torch.uint8, device="cuda")
+            pages[:, epb * 64:] = torch.randint(120, 130, (batch * pages_per, epb * 4), generator=g, dtype=torch.uint8,
+                                                device="cuda")
+            q = torch.randint(0, 256, (batch, 64, 64), generator=g, dtype=torch.uint8, device="cuda").view(torch.int8)
+            q_sf = torch.randint(120, 130, (batch, 64, 4), generator=g, dtype=torch.uint8, device="cuda").view(torch.int32)
+            weights = torch.randn(batch, 64, generator=g, device="cuda")
+            lens = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
+            table = torch.arange(batch * pages_per, dtype=torch.int32, device="cuda").view(batch, pages_per)
+            logits = torch.empty(batch, ctx, device="cuda")
+            status = wuda.device_status_word()
+            fn = lambda: wuda.mqa_logits_fp4_decode_out(q, q_sf.view(batch, 64), pages, weights, lens, table, logits, ctx,
+                                                        status_word=status)
+            if launches_only:
+                for _ in range(launches_only):
+                    fn()
+                torch.cuda.synchronize()
+                print("ran %d launches at batch %d, context %d (status %d)" % (launches_only, batch, ctx, int(status.item())))
+                continue
+            us = time_graph(fn, reps=10, inner=5)
+            assert int(status.item()) == 0
+            by = batch * ctx * 68 + batch * ctx * 4
+            print("batch %3d ctx %6d: %7.1f us  %6.0f GB/s = %.2f of peak (%.0f MB of pages)" %
+                  (batch, ctx, us, by / us / 1e3, by / us / 1e3 / hbm, batch * ctx * 68 / 1e6))
+
+
 def model1_pool(pages, epb, seed):
     """uint8 [pages, stride] pool of random MODEL1 records (finite e4m3, exponents near 0, small bf16)."""
     g = torch.Generator(device="cuda").manual_seed(seed)
@@ -523,7 +557,7 @@ if __name__ == "__main__":
     if which == "one":
         one(sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]))
         sys.exit(0)
-    {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2,
+    {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(contexts=(32768,), launches_only=3),
      "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(32,), launches_only=3),
      "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
      "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,

@@ -8,12 +8,15 @@
 // :228-256 (build_paged_cache), arithmetic as its twin ref_fp8_mqa_logits (:207-218) over the
 // dequantised values.
 //
-// First form of this kernel: one CTA per (request, tile of 128 tokens), no pipeline inside a CTA -
-// several CTAs per SM overlap each other's loads.  A CTA gathers its 128 key rows and the request's
-// 64 query rows with plain loads into the unswizzled K-major operand layout, copies the scale words
-// to tensor memory (tcgen05.cp), issues two block-scaled MMAs (kind::mxf4nvf4, scale_vec::2X, ue8m0:
-// the scales are applied inside the tensor core) and reduces the 64 head columns of each token row
-// with relu and the head weights.
+// A CTA of 128 threads serves one request and walks its tiles of 128 tokens with the grid's stride; four
+// CTAs share an SM (each holds 128 tensor-memory columns) and overlap one another.  The request's 64
+// query rows, their scale words and the head weights are loaded once.  Per tile its 128
+// key rows arrive by cp.async (three tiles ahead) straight in the unswizzled K-major operand
+// layout; the CTA copies the scale words to tensor memory (tcgen05.cp), issues two block-scaled MMAs
+// (kind::mxf4nvf4, scale_vec::2X, ue8m0: the scales are applied inside the tensor core) and reduces the
+// 64 head columns of each token row with relu and the head weights.
+#include <climits>
+
 #include "host.h"
 #include "ptx.cuh"
 
@@ -27,14 +30,15 @@ constexpr int kTile = 128;             // tokens per CTA (UMMA M)
 constexpr int kThreads = 128;
 constexpr uint32_t kTmemCols = 128;    // 64 accumulator columns, 4 + 4 scale columns
 constexpr uint32_t kColSfa = 64, kColSfb = 68;
+constexpr int kStages = 4;             // key tiles in shared memory: three in flight ahead of the one in use
 
 // shared memory (static): operands as [16-byte K chunk][row][16 B], scale images of 512 B
 struct Smem {
-    alignas(128) uint8_t keys[4 * kTile * 16];     // 8 KB
-    alignas(128) uint8_t query[4 * kHeads * 16];   // 4 KB
-    alignas(128) uint32_t key_scales[128];         // [row % 32][row / 32]
+    alignas(128) uint8_t keys[kStages][4 * kTile * 16];   // 8 KB each
+    alignas(128) uint8_t query[4 * kHeads * 16];          // 4 KB
+    alignas(128) uint32_t key_scales[kStages][128];       // [row % 32][row / 32]
     alignas(128) uint32_t query_scales[128];
-    float weights[kHeads];
+    alignas(16) float weights[kHeads];
     alignas(8) uint64_t mma_done;
     uint32_t tmem_slot;
     int abort_flag;
@@ -51,6 +55,7 @@ struct Params {
     int32_t* status;
     int64_t page_stride, logits_stride;
     int num_blocks, epb, bt_stride;
+    int epb_shift;               // log2(epb) when epb is a power of two, else -1
 };
 
 __device__ __forceinline__ void umma_mxf4_2x(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -66,14 +71,54 @@ __device__ __forceinline__ void umma_mxf4_2x(uint32_t d_tmem, uint64_t a_desc, u
         : "memory");
 }
 
+__device__ __forceinline__ void cp_async(uint32_t dst, const void* src, int bytes, int valid_bytes) {
+    if (bytes == 16)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid_bytes) : "memory");
+    else
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+constexpr int kNoToken = INT_MIN;   // fetch_page's answer for a token at or beyond the context
+
+// The block-table entry of token t of request b, unchecked (kNoToken beyond the context).  Requested one
+// tile before the copies that depend on it are started and looked at only then, so nothing waits for it.
+__device__ __forceinline__ int fetch_page(const Params& p, int b, int t, int ctx) {
+    if (t >= ctx) return kNoToken;
+    const int slot = p.epb_shift >= 0 ? t >> p.epb_shift : t / p.epb;
+    return slot < p.bt_stride ? __ldg(p.block_table + static_cast<int64_t>(b) * p.bt_stride + slot) : -1;
+}
+
+// Starts the copies of token row `t` (on page `phys`) into stage `s` (thread = row of the tile); a row at or
+// beyond the context (phys < 0) is zero-filled: zero values, scale bytes 0 - the products are zero either way.
+__device__ __forceinline__ void fetch_row(const Params& p, Smem& sm, int s, int row, int t, int phys) {
+    if (phys != kNoToken && (phys < 0 || phys >= p.num_blocks)) {   // a bad entry reads page 0 and is reported
+        if (p.status) atomicCAS(p.status, 0, static_cast<int>(kDevBadPageIndex));
+        phys = 0;
+    }
+    const int valid = phys >= 0 ? 1 : 0;
+    const int off = valid ? (p.epb_shift >= 0 ? t & (p.epb - 1) : t % p.epb) : 0;
+    const uint8_t* page = p.kv_pages + static_cast<int64_t>(valid ? phys : 0) * p.page_stride;
+    const uint8_t* src = page + static_cast<int64_t>(off) * kRowBytes;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) cp_async(smem_u32(sm.keys[s] + (c * kTile + row) * 16), src + c * 16, 16, valid * 16);
+    cp_async(smem_u32(&sm.key_scales[s][(row & 31) * 4 + (row >> 5)]), page + static_cast<int64_t>(p.epb) * kRowBytes + off * 4,
+             4, valid * 4);
+}
+
 __global__ void __launch_bounds__(kThreads) mqa_logits_fp4_kernel(const Params p) {
     __shared__ Smem sm;
-    const int b = blockIdx.y, tile = blockIdx.x;
+    const int b = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5;
     pdl_launch_dependents();
     pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     const int ctx = __ldg(p.context_lens + b);
-    if (tile * kTile >= ctx) return;   // whole CTA: nothing of this tile is valid
+    const int tiles = (ctx + kTile - 1) / kTile;
+    if (static_cast<int>(blockIdx.x) >= tiles) return;   // whole CTA: no tile of this request is left for it
 
     if (tid == 0) {
         sm.abort_flag = 0;
@@ -84,28 +129,8 @@ __global__ void __launch_bounds__(kThreads) mqa_logits_fp4_kernel(const Params p
         tmem_alloc(smem_u32(&sm.tmem_slot), kTmemCols);
         tmem_relinquish();
     }
-
-    // ---- gather: thread = token row of the tile; threads 0..63 also take one query row
+    // the request's query rows, scale words and head weights, once per CTA
     {
-        const int t = tile * kTile + tid;
-        uint4 k4[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-        uint32_t ks = 0x7f7f7f7fu;   // scale 1.0: a row of zeros stays zero
-        if (t < ctx) {
-            const int slot = t / p.epb, off = t - slot * p.epb;
-            int phys = slot < p.bt_stride ? __ldg(p.block_table + static_cast<int64_t>(b) * p.bt_stride + slot) : -1;
-            if (phys < 0 || phys >= p.num_blocks) {
-                if (p.status) atomicCAS(p.status, 0, static_cast<int>(kDevBadPageIndex));
-                phys = 0;
-            }
-            const uint8_t* page = p.kv_pages + static_cast<int64_t>(phys) * p.page_stride;
-            const uint4* row = reinterpret_cast<const uint4*>(page + static_cast<int64_t>(off) * kRowBytes);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) k4[c] = __ldg(row + c);
-            ks = __ldg(reinterpret_cast<const uint32_t*>(page + static_cast<int64_t>(p.epb) * kRowBytes) + off);
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(sm.keys + (c * kTile + tid) * 16) = k4[c];
-        sm.key_scales[(tid & 31) * 4 + (tid >> 5)] = ks;
         uint32_t qs = 0x7f7f7f7fu;
         if (tid < kHeads) {
             const uint4* row = reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * kHeads + tid) * kRowBytes);
@@ -116,48 +141,78 @@ __global__ void __launch_bounds__(kThreads) mqa_logits_fp4_kernel(const Params p
         }
         sm.query_scales[(tid & 31) * 4 + (tid >> 5)] = qs;
     }
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i) {   // the first tiles of this CTA; one group per tile, empty or not
+        const int t = (blockIdx.x + i * gridDim.x) * kTile + tid;
+        fetch_row(p, sm, i, tid, t, fetch_page(p, b, t, ctx));
+        cp_async_commit();
+    }
+    int page_ahead = fetch_page(p, b, (blockIdx.x + (kStages - 1) * gridDim.x) * kTile + tid, ctx);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = sm.tmem_slot;
-
-    if (warp == 0 && lane_id() == 0) {
-        tmem_cp_32x128b_warpx4(tmem_base + kColSfa, umma_smem_desc_noswz(smem_u32(sm.key_scales), 16, 128));
+    if (warp == 0 && lane_id() == 0)
         tmem_cp_32x128b_warpx4(tmem_base + kColSfb, umma_smem_desc_noswz(smem_u32(sm.query_scales), 16, 128));
-        const uint32_t a_addr = smem_u32(sm.keys), b_addr = smem_u32(sm.query);
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {   // 64 dims each: two 16-byte K chunks, scale bytes 2k and 2k+1 of a row's word
-            const uint32_t idesc = umma_idesc_block_scaled(kTile, kHeads, 1, 1, 1, 2 * k, 2 * k);
-            umma_mxf4_2x(tmem_base, umma_smem_desc_noswz(a_addr + k * 2 * kTile * 16, kTile * 16, 128),
-                         umma_smem_desc_noswz(b_addr + k * 2 * kHeads * 16, kHeads * 16, 128), idesc, tmem_base + kColSfa,
-                         tmem_base + kColSfb, k);
-        }
-        umma_commit(smem_u32(&sm.mma_done));
-    }
-    __syncwarp();
 
-    // ---- epilogue: thread = token row = tensor-memory lane
-    const bool alive = mbar_wait_warp(smem_u32(&sm.mma_done), 0u, &sm.abort_flag, p.status, kDevTimeoutFullTmem);
-    if (alive) {
-        tc_fence_after();
-        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-        float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-        for (int c = 0; c < kHeads; c += 32) {
-            uint32_t v[32];
-            tmem_ld_32x32(lane_addr + c, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                acc0 = fmaf(fmaxf(__uint_as_float(v[i]), 0.f), sm.weights[c + i], acc0);
-                acc1 = fmaf(fmaxf(__uint_as_float(v[i + 1]), 0.f), sm.weights[c + i + 1], acc1);
-            }
+    // A CTA walks the request's tiles with the grid's stride; the rows of its next three tiles are in
+    // flight (cp.async straight into the operand layout) while one tile is multiplied and reduced.
+    bool alive = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++it) {
+        const int s = it % kStages;
+        {   // the stage that tile it-1 used is free: its MMAs were awaited by every thread
+            const int t_ahead = (tile + (kStages - 1) * gridDim.x) * kTile + tid;
+            fetch_row(p, sm, (it + kStages - 1) % kStages, tid, t_ahead, page_ahead);
+            cp_async_commit();
+            page_ahead = fetch_page(p, b, t_ahead + gridDim.x * kTile, ctx);
         }
-        const int t = tile * kTile + tid;
-        if (t < ctx) p.logits[static_cast<int64_t>(b) * p.logits_stride + t] = acc0 + acc1;
-        tc_fence_before();
+        cp_async_wait<kStages - 1>();   // this thread's copies of the current tile have landed
+        fence_proxy_async_smem();
+        tc_fence_before();      // the previous tile's accumulator reads are done
+        __syncthreads();
+        if (warp == 0 && lane_id() == 0) {
+            tc_fence_after();
+            tmem_cp_32x128b_warpx4(tmem_base + kColSfa, umma_smem_desc_noswz(smem_u32(sm.key_scales[s]), 16, 128));
+            const uint32_t a_addr = smem_u32(sm.keys[s]), b_addr = smem_u32(sm.query);
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {   // 64 dims each: two 16-byte K chunks, scale bytes 2k and 2k+1 of a row's word
+                const uint32_t idesc = umma_idesc_block_scaled(kTile, kHeads, 1, 1, 1, 2 * k, 2 * k);
+                umma_mxf4_2x(tmem_base, umma_smem_desc_noswz(a_addr + k * 2 * kTile * 16, kTile * 16, 128),
+                             umma_smem_desc_noswz(b_addr + k * 2 * kHeads * 16, kHeads * 16, 128), idesc,
+                             tmem_base + kColSfa, tmem_base + kColSfb, k);
+            }
+            umma_commit(smem_u32(&sm.mma_done));
+        }
+        __syncwarp();
+
+        // ---- epilogue: thread = token row = tensor-memory lane
+        alive = mbar_wait_warp(smem_u32(&sm.mma_done), it & 1u, &sm.abort_flag, p.status, kDevTimeoutFullTmem);
+        if (alive) {
+            tc_fence_after();
+            const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+            float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < kHeads; c += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32(lane_addr + c, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(sm.weights + c + i);
+                    acc0 = fmaf(fmaxf(__uint_as_float(v[i]), 0.f), w4.x, acc0);
+                    acc1 = fmaf(fmaxf(__uint_as_float(v[i + 1]), 0.f), w4.y, acc1);
+                    acc0 = fmaf(fmaxf(__uint_as_float(v[i + 2]), 0.f), w4.z, acc0);
+                    acc1 = fmaf(fmaxf(__uint_as_float(v[i + 3]), 0.f), w4.w, acc1);
+                }
+            }
+            const int t = tile * kTile + tid;
+            if (t < ctx) p.logits[static_cast<int64_t>(b) * p.logits_stride + t] = acc0 + acc1;
+        }
     }
+    cp_async_wait<0>();
+    tc_fence_before();
     __syncthreads();
     if (sm.abort_flag) abort_drain_sleep();
     __syncthreads();
@@ -201,7 +256,18 @@ extern "C" int wuda_mqa_logits_fp4(const void* q_fp4, const void* q_scales, cons
     p.num_blocks = num_blocks;
     p.epb = entries_per_block;
     p.bt_stride = block_table_stride;
+    p.epb_shift = -1;
+    for (int sft = 0; sft < 20; ++sft)
+        if ((1 << sft) == entries_per_block) p.epb_shift = sft;
+    // enough CTAs to give every SM four (tensor memory allows four of them per SM), each walking its
+    // request's tiles with the grid's stride
+    DeviceInfo dev;
+    const int st = current_device_info(&dev);
+    if (st != WUDA_OK) return st;
     const int tiles = (max_context + kTile - 1) / kTile;
-    WUDA_CUDA(launch_pdl(mqa_logits_fp4_kernel, dim3(tiles, batch), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p));
+    int per_request = 4 * dev.num_sms / batch;      // rounded down: a CTA beyond the resident ones would run as a second wave
+    if (per_request < 1) per_request = 1;
+    if (per_request > tiles) per_request = tiles;
+    WUDA_CUDA(launch_pdl(mqa_logits_fp4_kernel, dim3(per_request, batch), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
