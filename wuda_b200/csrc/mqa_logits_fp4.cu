@@ -30,6 +30,7 @@ constexpr int kTile = 128;             // tokens per CTA (UMMA M)
 constexpr int kThreads = 128;
 constexpr uint32_t kTmemCols = 128;    // 64 accumulator columns, 4 + 4 scale columns
 constexpr uint32_t kColSfa = 64, kColSfb = 68;
+constexpr int kPadBytes = 16 * 1024;     // unused dynamic shared memory: 40 + 16 KB per CTA, four CTAs per SM
 constexpr int kStages = 4;             // key tiles in shared memory: three in flight ahead of the one in use
 
 // shared memory (static): operands as [16-byte K chunk][row][16 B], scale images of 512 B
@@ -268,6 +269,11 @@ extern "C" int wuda_mqa_logits_fp4(const void* q_fp4, const void* q_scales, cons
     int per_request = 4 * dev.num_sms / batch;      // rounded down: a CTA beyond the resident ones would run as a second wave
     if (per_request < 1) per_request = 1;
     if (per_request > tiles) per_request = tiles;
-    WUDA_CUDA(launch_pdl(mqa_logits_fp4_kernel, dim3(per_request, batch), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p));
+    // Tensor memory holds four of these CTAs per SM, but the block scheduler only counts shared memory and
+    // registers and would place a fifth, which then waits in its allocation while other SMs stay empty: an
+    // unused dynamic allocation makes shared memory the limit at four.
+    WUDA_CUDA(cudaFuncSetAttribute(mqa_logits_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPadBytes));
+    WUDA_CUDA(launch_pdl(mqa_logits_fp4_kernel, dim3(per_request, batch), dim3(kThreads), kPadBytes,
+                         static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
