@@ -219,6 +219,7 @@ def csa_chain(batch=64, context=32768, topk=2048, reps=30, launches_only=0):
                          torch.sin(ang).contiguous(), index_heads=ih, main_heads=mh)
     pages_per_req = (context // 4 + 63) // 64 + 1
     cache = KVCacheManager(batch, batch * pages_per_req + batch, pages_per_req, device=dev)
+    stage = CsaDecodeStage(weights, cache, batch, topk=topk)
     slots = [cache.alloc_request() for _ in range(batch)]
     for s in slots:
         cache.advance(s, context - 1)               # the timed token is the one at position context - 1
