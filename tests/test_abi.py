@@ -83,3 +83,12 @@ def test_struct_layouts_match_the_header(tmp_path):
         assert int(out[cname]) == ctypes.sizeof(cls), cname
         for field, _ in cls._fields_:
             assert int(out["%s.%s" % (cname, field)]) == getattr(cls, field).offset, "%s.%s" % (cname, field)
+
+
+def test_benchmark_kinds_are_registered_and_documented():
+    """Every kind the benchmark module documents in its header is registered, and the other way round."""
+    import re
+    from wuda_b200 import benchmarks
+    documented = set(re.findall(r"wuda_b200\.benchmarks (\w+)", benchmarks.__doc__)) - {"one"}
+    assert documented == set(benchmarks.KINDS), documented ^ set(benchmarks.KINDS)
+    assert all(callable(f) for f in benchmarks.KINDS.values())

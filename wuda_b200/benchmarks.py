@@ -13,6 +13,7 @@ because consecutive launches use different weight buffers that together exceed L
     python -m wuda_b200.benchmarks moe_experts                     (router + routed NVFP4 experts of one MoE block)
     python -m wuda_b200.benchmarks moe_experts_launches            (two eager passes, for an ncu launch list)
     python -m wuda_b200.benchmarks mqa_fp4                         (MXFP4 paged MQA logits)
+    python -m wuda_b200.benchmarks mqa_fp4_launches                (three eager launches at batch 64 x 32768, for ncu)
     python -m wuda_b200.benchmarks sparse_mla                      (sparse MLA decode attention, window 128 + top-2048)
     python -m wuda_b200.benchmarks sparse_mla_launches             (three eager launches of a small case, for ncu)
     python -m wuda_b200.benchmarks one gemm_fp8 64 24576 7168      (a few launches of one shape, for ncu)
@@ -553,14 +554,17 @@ def one(kind, m, n, k, launches=5):
     print("ran %d launches of %s M=%d N=%d K=%d" % (launches, kind, m, n, k))
 
 
+KINDS = {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(contexts=(32768,), launches_only=3),
+         "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(32,), launches_only=3),
+         "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
+         "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,
+         "moe_experts_launches": lambda: moe_experts(launches_only=2),
+         "attention_half_layer_launches": lambda: attention_half_layer(launches_only=3)}
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm_fp8"
     if which == "one":
         one(sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]))
         sys.exit(0)
-    {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(contexts=(32768,), launches_only=3),
-     "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(32,), launches_only=3),
-     "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
-     "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,
-     "moe_experts_launches": lambda: moe_experts(launches_only=2),
-     "attention_half_layer_launches": lambda: attention_half_layer(launches_only=3)}[which]()
+    KINDS[which]()
