@@ -10,11 +10,13 @@
 //
 // A CTA of 128 threads serves one request and walks its tiles of 128 tokens with the grid's stride; four
 // CTAs share an SM (each holds 128 tensor-memory columns) and overlap one another.  The request's 64
-// query rows, their scale words and the head weights are loaded once.  Per tile its 128
-// key rows arrive by cp.async (three tiles ahead) straight in the unswizzled K-major operand
-// layout; the CTA copies the scale words to tensor memory (tcgen05.cp), issues two block-scaled MMAs
-// (kind::mxf4nvf4, scale_vec::2X, ue8m0: the scales are applied inside the tensor core) and reduces the
-// 64 head columns of each token row with relu and the head weights.
+// query rows, their scale words and the head weights are loaded once.  A thread owns one token row of a
+// tile: it keeps the rows of the CTA's next two tiles in registers (plain 16-byte loads; per-thread
+// cp.async copies were tried and throttled in the load/store queue), stores the current row into the
+// unswizzled K-major operand layout, and after the MMAs reduces its row of the accumulator.  Per tile
+// the scale words go to tensor memory (tcgen05.cp) and two block-scaled MMAs (kind::mxf4nvf4,
+// scale_vec::2X, ue8m0) apply them inside the tensor core; the epilogue is relu, head weight, sum over
+// the 64 head columns.
 #include <climits>
 
 #include "host.h"
@@ -30,12 +32,12 @@ constexpr int kTile = 128;             // tokens per CTA (UMMA M)
 constexpr int kThreads = 128;
 constexpr uint32_t kTmemCols = 128;    // 64 accumulator columns, 4 + 4 scale columns
 constexpr uint32_t kColSfa = 64, kColSfb = 68;
-constexpr int kPadBytes = 16 * 1024;     // unused dynamic shared memory: 40 + 16 KB per CTA, four CTAs per SM
-constexpr int kStages = 4;             // key tiles in shared memory: three in flight ahead of the one in use
+constexpr int kPadBytes = 40 * 1024;     // unused dynamic shared memory: 14 + 40 KB per CTA, four CTAs per SM
+constexpr int kStages = 1;             // one key tile in shared memory; the next two wait in registers
 
 // shared memory (static): operands as [16-byte K chunk][row][16 B], scale images of 512 B
 struct Smem {
-    alignas(128) uint8_t keys[kStages][4 * kTile * 16];   // 8 KB each
+    alignas(128) uint8_t keys[kStages][4 * kTile * 16];   // 8 KB
     alignas(128) uint8_t query[4 * kHeads * 16];          // 4 KB
     alignas(128) uint32_t key_scales[kStages][128];       // [row % 32][row / 32]
     alignas(128) uint32_t query_scales[128];
@@ -72,18 +74,6 @@ __device__ __forceinline__ void umma_mxf4_2x(uint32_t d_tmem, uint64_t a_desc, u
         : "memory");
 }
 
-__device__ __forceinline__ void cp_async(uint32_t dst, const void* src, int bytes, int valid_bytes) {
-    if (bytes == 16)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid_bytes) : "memory");
-    else
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
 constexpr int kNoToken = INT_MIN;   // fetch_page's answer for a token at or beyond the context
 
 // The block-table entry of token t of request b, unchecked (kNoToken beyond the context).  Requested one
@@ -94,21 +84,29 @@ __device__ __forceinline__ int fetch_page(const Params& p, int b, int t, int ctx
     return slot < p.bt_stride ? __ldg(p.block_table + static_cast<int64_t>(b) * p.bt_stride + slot) : -1;
 }
 
-// Starts the copies of token row `t` (on page `phys`) into stage `s` (thread = row of the tile); a row at or
-// beyond the context (phys < 0) is zero-filled: zero values, scale bytes 0 - the products are zero either way.
-__device__ __forceinline__ void fetch_row(const Params& p, Smem& sm, int s, int row, int t, int phys) {
-    if (phys != kNoToken && (phys < 0 || phys >= p.num_blocks)) {   // a bad entry reads page 0 and is reported
+struct KeyRow {
+    uint4 k[4];
+    uint32_t scale;
+};
+
+// Loads token row `t` (block-table entry `phys`, unchecked) into registers; zeros beyond the context.
+__device__ __forceinline__ KeyRow load_row(const Params& p, int t, int phys) {
+    KeyRow r;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) r.k[c] = make_uint4(0, 0, 0, 0);
+    r.scale = 0;
+    if (phys == kNoToken) return r;
+    if (phys < 0 || phys >= p.num_blocks) {   // a bad entry reads page 0 and is reported
         if (p.status) atomicCAS(p.status, 0, static_cast<int>(kDevBadPageIndex));
         phys = 0;
     }
-    const int valid = phys >= 0 ? 1 : 0;
-    const int off = valid ? (p.epb_shift >= 0 ? t & (p.epb - 1) : t % p.epb) : 0;
-    const uint8_t* page = p.kv_pages + static_cast<int64_t>(valid ? phys : 0) * p.page_stride;
-    const uint8_t* src = page + static_cast<int64_t>(off) * kRowBytes;
+    const int off = p.epb_shift >= 0 ? t & (p.epb - 1) : t % p.epb;
+    const uint8_t* page = p.kv_pages + static_cast<int64_t>(phys) * p.page_stride;
+    const uint4* row = reinterpret_cast<const uint4*>(page + static_cast<int64_t>(off) * kRowBytes);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) cp_async(smem_u32(sm.keys[s] + (c * kTile + row) * 16), src + c * 16, 16, valid * 16);
-    cp_async(smem_u32(&sm.key_scales[s][(row & 31) * 4 + (row >> 5)]), page + static_cast<int64_t>(p.epb) * kRowBytes + off * 4,
-             4, valid * 4);
+    for (int c = 0; c < 4; ++c) r.k[c] = __ldg(row + c);
+    r.scale = __ldg(reinterpret_cast<const uint32_t*>(page + static_cast<int64_t>(p.epb) * kRowBytes) + off);
+    return r;
 }
 
 __global__ void __launch_bounds__(kThreads) mqa_logits_fp4_kernel(const Params p) {
@@ -142,13 +140,11 @@ __global__ void __launch_bounds__(kThreads) mqa_logits_fp4_kernel(const Params p
         }
         sm.query_scales[(tid & 31) * 4 + (tid >> 5)] = qs;
     }
-#pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) {   // the first tiles of this CTA; one group per tile, empty or not
-        const int t = (blockIdx.x + i * gridDim.x) * kTile + tid;
-        fetch_row(p, sm, i, tid, t, fetch_page(p, b, t, ctx));
-        cp_async_commit();
-    }
-    int page_ahead = fetch_page(p, b, (blockIdx.x + (kStages - 1) * gridDim.x) * kTile + tid, ctx);
+    const int stride_tokens = gridDim.x * kTile;
+    const int t0 = blockIdx.x * kTile + tid;
+    KeyRow r0 = load_row(p, t0, fetch_page(p, b, t0, ctx));                                   // this CTA's first tile
+    KeyRow r1 = load_row(p, t0 + stride_tokens, fetch_page(p, b, t0 + stride_tokens, ctx));   // and its second
+    int page_ahead = fetch_page(p, b, t0 + 2 * stride_tokens, ctx);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -157,19 +153,16 @@ __global__ void __launch_bounds__(kThreads) mqa_logits_fp4_kernel(const Params p
     if (warp == 0 && lane_id() == 0)
         tmem_cp_32x128b_warpx4(tmem_base + kColSfb, umma_smem_desc_noswz(smem_u32(sm.query_scales), 16, 128));
 
-    // A CTA walks the request's tiles with the grid's stride; the rows of its next three tiles are in
-    // flight (cp.async straight into the operand layout) while one tile is multiplied and reduced.
+    // A CTA walks the request's tiles with the grid's stride; the rows of its next two tiles are in flight
+    // (in registers) while one tile is multiplied and reduced.
     bool alive = true;
     int it = 0;
     for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++it) {
-        const int s = it % kStages;
-        {   // the stage that tile it-1 used is free: its MMAs were awaited by every thread
-            const int t_ahead = (tile + (kStages - 1) * gridDim.x) * kTile + tid;
-            fetch_row(p, sm, (it + kStages - 1) % kStages, tid, t_ahead, page_ahead);
-            cp_async_commit();
-            page_ahead = fetch_page(p, b, t_ahead + gridDim.x * kTile, ctx);
-        }
-        cp_async_wait<kStages - 1>();   // this thread's copies of the current tile have landed
+        const int s = 0;
+        // the tile's rows go from registers to the operand layout (every thread has awaited the MMAs of the tile before)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(sm.keys[0] + (c * kTile + tid) * 16) = r0.k[c];
+        sm.key_scales[0][(tid & 31) * 4 + (tid >> 5)] = r0.scale;
         fence_proxy_async_smem();
         tc_fence_before();      // the previous tile's accumulator reads are done
         __syncthreads();
@@ -188,6 +181,12 @@ __global__ void __launch_bounds__(kThreads) mqa_logits_fp4_kernel(const Params p
         }
         __syncwarp();
 
+        {   // rows two tiles ahead are requested now; the block-table entry for them was requested a tile ago
+            const int t_ahead = (tile + 2 * static_cast<int>(gridDim.x)) * kTile + tid;
+            r0 = r1;
+            r1 = load_row(p, t_ahead, page_ahead);
+            page_ahead = fetch_page(p, b, t_ahead + stride_tokens, ctx);
+        }
         // ---- epilogue: thread = token row = tensor-memory lane
         alive = mbar_wait_warp(smem_u32(&sm.mma_done), it & 1u, &sm.abort_flag, p.status, kDevTimeoutFullTmem);
         if (alive) {
@@ -212,7 +211,6 @@ __global__ void __launch_bounds__(kThreads) mqa_logits_fp4_kernel(const Params p
             if (t < ctx) p.logits[static_cast<int64_t>(b) * p.logits_stride + t] = acc0 + acc1;
         }
     }
-    cp_async_wait<0>();
     tc_fence_before();
     __syncthreads();
     if (sm.abort_flag) abort_drain_sleep();
