@@ -1,4 +1,4 @@
-"""Benchmark of the indexer step: paged FP8 MQA logits + top-2048 selection.
+"""Benchmark of the indexer step (paged FP8 MQA logits + top-2048 selection) and of the decode layer.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
@@ -14,7 +14,16 @@ of one step (keys and scales read once per request, fp32 logits written once and
 once, q/weights/indices) divided by the device time of the step, inputs resident in HBM.
 `e2e` is the same number through the host-buffer C-ABI call, host<->device copies
 included.  `--impl reference` times the CPU oracle (the reference ships no CPU
-implementation of this path) on a bounded sample of the same workload.
+implementation of this path) on a bounded sample of the same workload, on every host core
+the process may use (one rank only under a multi-rank launcher).
+
+Beside the indexer step the line carries the decode layer (one random-init sparse-attention MoE
+layer, batch 64, context 32768): `layer` = one GPU (N = 1), and for N >= 2 the ranks pair up
+(0,1), (2,3), .. as independent tensor-parallel replicas: `tp2` = the wo_b projection with its
+all-reduce fused into the GEMM epilogue over NVLink peer memory, checked against the CPU oracle;
+`ep2` = the expert-parallel MoE block whose combine step exchanges rows over peer memory, checked
+against the ranks' own partial sums; `layer_tp2` = the whole layer on a pair, decode
+tokens/s/GPU = 64 / (t_layer x 2), checked against the same layer on one GPU.
 """
 import argparse
 import json
@@ -28,6 +37,19 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+# the pair legs exchange through plain peer loads and stores; NCCL (bootstrap and barriers only) stays
+# off the NVLink multicast objects
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+
+
+def load_workloads():
+    """The synthetic-input generators, loaded by path: importing the package would load the CUDA library,
+    which the reference arm must not do."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("wuda_b200_workloads", os.path.join(ROOT, "wuda_b200", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 BATCH, NEXT_N, CTX_LO, CTX_HI, EPB, TOPK = 64, 2, 16384, 65536, 64, 2048
 SEED = 0xB201
@@ -37,7 +59,7 @@ METRIC = "MQA-logits + top-k HBM GB/s"
 
 
 def step_bytes(case):
-    from wuda_b200 import workloads
+    workloads = load_workloads()
     rows = case["batch"] * case["next_n"]
     mqa = workloads.mqa_algorithmic_bytes(case)
     topk = int(case["context_lens"].sum()) * 4 + rows * TOPK * 4
@@ -50,6 +72,16 @@ def measured_hbm_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def measured_traffic(algorithmic_bytes):
+    """DRAM bytes of one MQA launch from the profiler capture recorded under profiles/ (DRAM bytes per
+    algorithmic byte of a smaller batch), or None when no capture is recorded."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "mqa_logits_fp8_traffic.json")) as f:
+            return int(float(json.load(f)["dram_bytes_per_algorithmic_byte"]) * algorithmic_bytes)
+    except Exception:
+        return None
 
 
 class ClockSampler:
@@ -122,6 +154,7 @@ def cpu_step(sub):
 
 def time_cpu(sub, steps, warmup):
     import oracle
+    oracle.set_num_threads()          # a launcher's OMP_NUM_THREADS=1 is for its GPU workers, not for this leg
     for _ in range(warmup):
         cpu_step(sub)
     t0 = time.perf_counter()
@@ -135,7 +168,7 @@ def time_cpu(sub, steps, warmup):
 def run_reference(args, rank):
     if rank != 0:
         return
-    from wuda_b200 import workloads
+    workloads = load_workloads()
     case = workloads.make_mqa_case(SAMPLE_REQUESTS, NEXT_N, CTX_LO, CTX_HI, epb=EPB, seed=SEED)
     gbs, dt, cores = time_cpu(case, args.steps, min(args.warmup, 1))
     sample = "first %d of 64 requests (same seed), every step" % SAMPLE_REQUESTS
@@ -159,7 +192,9 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="requests per rank (default 64 = the benchmark workload; smaller values are for profiler captures)")
     ap.add_argument("--capture", action="store_true",
-                    help="profiler capture mode: no clock pre-warm, no end-to-end leg, no CPU baseline")
+                    help="profiler capture mode: no clock pre-warm, no end-to-end leg, no CPU baseline, no layer legs")
+    ap.add_argument("--no-layer", action="store_true", help="skip the decode-layer legs (indexer step only)")
+    ap.add_argument("--layer-reps", type=int, default=20, help="timed CUDA-graph replays of the layer legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -177,9 +212,15 @@ def main():
     from wuda_b200 import workloads
 
     torch.cuda.set_device(local_rank)
+    host_group = pair_group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # host-side groups (gloo) for the pair legs: IPC handles, barriers and result objects travel over them
+        host_group = dist.new_group(backend="gloo")
+        pairs = [dist.new_group([2 * i, 2 * i + 1], backend="gloo") for i in range(world // 2)]
+        if rank // 2 < len(pairs):
+            pair_group = pairs[rank // 2]
 
     def barrier():
         if world > 1:
@@ -312,9 +353,9 @@ def main():
             "kernels_us": {"mqa_logits_fp8": mqa_ms * 1e3, "topk": topk_ms * 1e3},
             "roofline": {"kernel": "mqa_logits_fp8_kernel<2>", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         # dram read+write per launch: 0.98 x algorithmic bytes, from the ncu capture
-                         # of the batch-24 case scaled by bytes (profiles/mqa_logits_fp8_batch24.md)
-                         "traffic": int(0.98 * mqa_b) if batch == BATCH else None, "algorithmic_bytes": mqa_b},
+                         # DRAM read + write bytes per launch: the profiler's figure for a smaller batch of the
+                         # same workload, scaled by algorithmic bytes (the traffic is the key stream)
+                         "traffic": measured_traffic(mqa_b) if batch == BATCH else None, "algorithmic_bytes": mqa_b},
             "e2e": {"value": world * (mqa_b + topk_b) / e2e_s / 1e9, "unit": "GB/s", "ms_per_step": e2e_s * 1e3,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "matches_device_path": bool(same)},
             "gpu_launches": 2 * args.steps, "launch": "one CUDA graph replay per step",
@@ -325,9 +366,122 @@ def main():
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                                     "sample": "first %d of %d requests, 3 timed passes of the C oracle "
                                               "(OpenMP), %.2f s each" % (min(SAMPLE_REQUESTS, batch), batch, dt)}
+    else:
+        line = None
+
+    # ---- the decode layer: one GPU at N = 1, tensor-parallel pairs (and their exchange kernels) at N >= 2
+    torch.cuda.empty_cache()
+    if not args.no_layer:
+        legs = layer_legs(args, rank, world, host_group, pair_group)
+        if rank == 0:
+            line.update(legs)
+    if rank == 0:
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+def bf16_bits_to_f32(u16):
+    return (u16.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits(x):
+    """Round-to-nearest-even bf16 bits of finite fp32 values."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def layer_legs(args, rank, world, host_group, pair_group):
+    """Runs the layer legs on every rank and returns, on rank 0, the blocks to add to the JSON line."""
+    import torch
+    import torch.distributed as dist
+    from wuda_b200 import benchmarks
+
+    if world == 1:
+        res, _ = benchmarks.layer_leg(reps=args.layer_reps)
+        res["parallelism"] = "1 GPU"
+        return {"layer": res}
+    if pair_group is None:          # an odd rank out: nothing to pair with
+        mine = None
+    else:
+        import oracle
+        pair_rank = rank % 2
+        mine = {}
+        # (1) wo_b with the fused all-reduce: both ranks of a pair must hold bf16(partial_0 + partial_1)
+        res, gcase, got = benchmarks.tp2_gemm_leg(pair_group, pair_rank)
+        both = [None, None]
+        dist.all_gather_object(both, got.tobytes(), group=pair_group)
+        res["ranks_identical"] = both[0] == both[1]
+        if rank == 0:               # the oracle check runs once: every pair gets the same inputs
+            oracle.set_num_threads()
+            k = gcase["a"].shape[1]
+            parts = [oracle.gemm_fp8_blockscaled(gcase["a"][:, sl], gcase["a_s"][:, sb], gcase["w"][:, sl], gcase["w_s"][:, sb],
+                                                 out_bf16=False)
+                     for sl, sb in ((slice(0, k // 2), slice(0, k // 256)), (slice(k // 2, k), slice(k // 256, k // 128)))]
+            ref = parts[0] + parts[1]
+            f = bf16_bits_to_f32(got)
+            rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+            res["matches_oracle"] = bool(np.all(np.abs(f - ref) <= 1e-2 * np.abs(ref) + 1e-3 * rms))
+            res["tolerance"] = "|got - (oracle partial 0 + partial 1)| <= 1e-2 |ref| + 1e-3 rms"
+        res["output_digest"] = int(np.bitwise_xor.reduce(got.reshape(-1).astype(np.uint64) * np.arange(1, got.size + 1, dtype=np.uint64)))
+        mine["tp2"] = res
+        # (2) expert-parallel MoE block: y must be bf16(own partial + peer partial) bit for bit
+        res, got, part = benchmarks.ep2_combine_leg(pair_group, pair_rank)
+        both = [None, None]
+        dist.all_gather_object(both, (got.tobytes(), part.tobytes()), group=pair_group)
+        parts = [np.frombuffer(b[1], np.float32).reshape(part.shape) for b in both]
+        res["ranks_identical"] = both[0][0] == both[1][0]
+        res["equals_sum_of_partials"] = bool(np.array_equal(got, f32_to_bf16_bits(parts[0] + parts[1])))
+        mine["ep2"] = res
+        # (3) the whole layer on the pair
+        res, out = benchmarks.layer_leg(reps=args.layer_reps, group=pair_group, pair_rank=pair_rank)
+        both = [None, None]
+        dist.all_gather_object(both, out.numpy().tobytes(), group=pair_group)
+        res["ranks_identical"] = both[0] == both[1]
+        res["finite"] = bool(torch.isfinite(out).all())
+        if rank == 0:               # the same layer (same seed) on one GPU, one eager pass
+            from wuda_b200.layer_setup import build_random_layer
+            single, slots, x = build_random_layer(64, 32768)
+            single.prepare(slots)
+            ref = single.launch(x, 64).float().cpu()
+            single.check_status()
+            err = float((out - ref).norm() / ref.norm())
+            res["rel_err_vs_one_gpu"] = err
+            res["matches_one_gpu"] = bool(err < 2e-2)
+            del single
+        mine["layer_tp2"] = res
+    gathered = [None] * world
+    dist.all_gather_object(gathered, mine, group=host_group)
+    if rank != 0:
+        return None
+    leaders = [g for i, g in enumerate(gathered) if g is not None and i % 2 == 0]
+    followers = [g for i, g in enumerate(gathered) if g is not None and i % 2 == 1]
+    out = {}
+    for key in ("tp2", "ep2", "layer_tp2"):
+        block = dict(leaders[0][key])
+        block["pairs"] = len(leaders)
+        block["status"] = max(g[key]["status"] for g in leaders + followers)
+        block["ranks_identical"] = all(g[key]["ranks_identical"] for g in leaders)
+        out[key] = block
+    t = out["tp2"]
+    t["gemm_allreduce_us"] = max(g["tp2"]["gemm_allreduce_us"] for g in leaders)
+    t["local_gemm_us"] = max(g["tp2"]["local_gemm_us"] for g in leaders)
+    t["roofline_frac"] = t["roofline_us"] / t["gemm_allreduce_us"]
+    t["pairs_identical"] = all(g["tp2"]["output_digest"] == t["output_digest"] for g in leaders)
+    t["parity_ok"] = bool(t["matches_oracle"] and t["ranks_identical"] and t["pairs_identical"] and t["status"] == 0)
+    e = out["ep2"]
+    e["block_us"] = max(g["ep2"]["block_us"] for g in leaders)
+    e["equals_sum_of_partials"] = all(g["ep2"]["equals_sum_of_partials"] for g in leaders + followers)
+    e["parity_ok"] = bool(e["equals_sum_of_partials"] and e["ranks_identical"] and e["status"] == 0)
+    l = out["layer_tp2"]
+    l["layer_us"] = max(g["layer_tp2"]["layer_us"] for g in leaders)
+    l["tok_s_per_gpu"] = l["batch"] / (l["layer_us"] * 1e-6) / 2
+    l["tok_s_all_gpus"] = l["tok_s_per_gpu"] * 2 * len(leaders)
+    l["finite"] = all(g["layer_tp2"]["finite"] for g in leaders + followers)
+    l["parallelism"] = "tp2 x %d replicas" % len(leaders)
+    l["parity_ok"] = bool(l["matches_one_gpu"] and l["ranks_identical"] and l["finite"] and l["status"] == 0)
+    return out
 
 
 if __name__ == "__main__":

@@ -44,6 +44,8 @@ typedef enum wuda_device_status {
     WUDA_DEV_TIMEOUT_FULL_TMEM = 105,
     WUDA_DEV_TIMEOUT_EMPTY_TMEM = 106,
     WUDA_DEV_BAD_PAGE_INDEX = 110, /* block_table entry outside [0, num_blocks): page 0 was read instead */
+    WUDA_DEV_BAD_CONTEXT_LEN = 111, /* a context length beyond logits_stride or block_table_stride * entries_per_block
+                                       was cut to that limit: nothing is written past a row of the logits */
     WUDA_DEV_TIMEOUT_GEMM_FULL = 121,
     WUDA_DEV_TIMEOUT_GEMM_EMPTY = 122,
     WUDA_DEV_TIMEOUT_GEMM_TMEM_FULL = 123,
@@ -74,7 +76,9 @@ int wuda_num_sms(void);
  *
  * for every row r = b * next_n + j and every token t < context_lens[b, j] of request b,
  * where token t lives in physical page block_table[b, t / entries_per_block] at slot
- * t % entries_per_block.  Positions t >= context_lens[b, j] are NOT written.
+ * t % entries_per_block.  Positions t >= context_lens[b, j] are NOT written.  A negative context
+ * length counts as 0; one beyond min(logits_stride, block_table_stride * entries_per_block) is cut
+ * to that limit and reported as WUDA_DEV_BAD_CONTEXT_LEN (the reference checks neither).
  *
  * Stands in for mqa_logits_fp8_decode_out (kernels/mqa_logits_fp8.cu:388-526) without
  * its optional compressor / query tails, and for deep_gemm.fp8_paged_mqa_logits as
@@ -539,6 +543,8 @@ int wuda_moe_combine(const void* expert_out_bf16, const int32_t* pair_row, const
  * bit-identical on both ranks.  Inboxes: wuda_moe_ep2_inbox_bytes(tokens_max, dim) bytes (tokens_max <= 512,
  * dim <= 8192) from wuda_tp2_alloc, the peer's mapped with wuda_tp2_open; zero-initialised.  `epoch` counts the
  * calls of the pair from 1 and must advance by one on both ranks; a rank may be one call ahead of its peer.
+ * epoch = 0 lets the link number its calls itself (a counter in the inbox that the kernel advances), so that the
+ * same launch can be replayed from a CUDA graph; a link uses one of the two forms for its whole life.
  * shared_bf16 is added by the rank that passes it (one of the two).  A peer that does not answer within
  * peer_wait_ms leaves WUDA_DEV_TIMEOUT_PEER_FLAG in status_word and the local sum in y. */
 int64_t wuda_moe_ep2_inbox_bytes(int tokens_max, int dim);
@@ -689,7 +695,10 @@ int wuda_gemm_nvfp4(const void* a, const void* a_sf_packed, float a_global_scale
  * An inbox is device memory of wuda_tp2_inbox_bytes(m, n) bytes created by wuda_tp2_alloc,
  * which also returns a 64-byte CUDA IPC handle; the peer process maps it with wuda_tp2_open
  * (the handles travel by any host-side channel).  `epoch` is the call's sequence number: it
- * must start at 1 and grow by one per call, identically on both ranks.  A wait for the peer
+ * must start at 1 and grow by one per call, identically on both ranks; epoch = 0 lets the link
+ * number its calls itself (a counter in the inbox that the kernel advances), so that the same
+ * launch can be replayed from a CUDA graph - a link uses one of the two forms for its whole
+ * life.  m <= 128 (larger batches: several calls).  A wait for the peer
  * that exceeds peer_wait_ms ends the kernel with WUDA_DEV_TIMEOUT_PEER_FLAG in status_word
  * (c is then not fully written); nothing traps or hangs.
  */
@@ -728,8 +737,12 @@ int wuda_gemm_fp8_blockscaled_noalloc(const void* a, const float* a_scales, cons
  * max_batch requests; wuda_indexer_topk_host copies the *_host inputs to the device on
  * `stream`, runs both kernels, copies page_indices [batch*next_n, k] (and the logits
  * [batch*next_n, logits_stride] when logits_host != NULL) back, and synchronises the
- * stream.  Host buffers should be page-locked for full copy bandwidth.  A non-zero
- * device status is returned as WUDA_ERR_DEVICE_STATUS.
+ * stream - on every path, also after a refused launch, so the host buffers are free when
+ * the call returns.  Host buffers should be page-locked for full copy bandwidth.
+ * kv_pages_host == NULL skips the upload of the key pool: the pages of the previous call
+ * on this plan stay in place (a decode server changes a few pages per step, not the pool).
+ * The plan belongs to the device that was current when it was created; a call with another
+ * device current is refused.  A non-zero device status is returned as WUDA_ERR_DEVICE_STATUS.
  */
 typedef struct wuda_indexer_plan wuda_indexer_plan;
 int wuda_indexer_plan_create(wuda_indexer_plan** plan, int max_batch, int next_n, int num_blocks,

@@ -786,6 +786,16 @@ int oracle_num_threads(void) {
 #endif
 }
 
+/* Threads for the parallel loops from now on (a launcher may have exported OMP_NUM_THREADS=1 for
+ * its workers; a timed CPU baseline that runs alone on the host takes the cores it is given). */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------ sparse MLA decode attention
  *
  * Softmax attention of one query token per request over gathered cache records, after

@@ -48,6 +48,7 @@ def _declare(l):
     l.oracle_topk.argtypes = [c.c_void_p] * 5 + [c.c_int, c.c_int64, c.c_int64, c.c_int, c.c_int]
     l.oracle_topk.restype = c.c_int
     l.oracle_num_threads.restype = c.c_int
+    l.oracle_set_num_threads.argtypes = [c.c_int]
     l.oracle_rmsnorm_bf16.argtypes = [c.c_void_p, c.c_void_p, c.c_int, c.c_float, c.c_void_p, c.c_int, c.c_int]
     l.oracle_act_quant_fp8.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int]
     l.oracle_rope_bf16.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int,
@@ -84,6 +85,15 @@ def _c(a, dtype):
 
 def num_threads():
     return int(lib().oracle_num_threads())
+
+
+def set_num_threads(n=None):
+    """Use n threads in the oracle's parallel loops (default: every core this process may run on),
+    whatever OMP_NUM_THREADS said when the library was loaded.  Returns the count now in force."""
+    if n is None:
+        n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()
 
 
 def e4m3_decode(u8):

@@ -58,6 +58,32 @@ def test_reference_arm_prints_one_json_line():
     assert res["e2e"]["h2d_bytes_per_step"] == 0
 
 
+def test_reference_arm_takes_all_cores_under_a_launcher_and_never_loads_the_product(tmp_path):
+    """A multi-rank launcher exports OMP_NUM_THREADS=1 to its workers; the CPU arm must still use the cores
+    the process may run on, and it must not map the CUDA library (it times the oracle, not the product)."""
+    probe = tmp_path / "probe.py"
+    probe.write_text(textwrap.dedent("""
+        import json, runpy, sys
+        sys.argv = [%r, "--impl", "reference", "--steps", "1", "--warmup", "1"]
+        runpy.run_path(sys.argv[0], run_name="__main__")
+        print(json.dumps({"mapped": sorted({l.split()[-1].rsplit("/", 1)[-1] for l in open("/proc/self/maps")
+                                            if "libwuda" in l or "liboracle" in l})}))
+    """) % os.path.join(ROOT, "bench.py"))
+    env = dict(os.environ, OMP_NUM_THREADS="1", RANK="0", WORLD_SIZE="2", LOCAL_RANK="0")
+    out = subprocess.run([sys.executable, str(probe)], capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stderr[-2000:]
+    import json
+    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+    cores = len(os.sched_getaffinity(0))
+    assert lines[0]["impl"] == "reference" and lines[0]["cpu_baseline"]["cores"] == cores
+    assert lines[1]["mapped"] == ["liboracle.so"]
+    # every other rank leaves without work and without output
+    env["RANK"] = "1"
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1"],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0 and out.stdout.strip() == ""
+
+
 HANDLE_WORKER = textwrap.dedent("""
     import os, sys, json
     sys.path.insert(0, %r)

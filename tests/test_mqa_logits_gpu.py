@@ -117,6 +117,33 @@ def test_out_of_pool_page_is_reported_not_faulted(wuda):
     assert_close_logits(got[:1], ref, np.isfinite(ref))
 
 
+def test_context_beyond_the_logits_row_is_cut_and_reported(wuda):
+    """A context length larger than logits_stride (or negative) must neither write past the row nor
+    corrupt the tile count: the row is cut at the stride, the cut is reported as code 111, the guard
+    rows behind the logits stay untouched and the other requests are unaffected."""
+    case = workloads.make_mqa_case(3, 1, 0, 0, ctx=[700, 300, 500], seed=41)
+    stride = case["logits_stride"]
+    assert stride == 768
+    d = workloads.to_device(case)
+    lens = d["context_lens"].clone()
+    lens[0] = stride + 1000           # claims more tokens than its row of the logits holds
+    lens[1] = -5000                   # negative: counts as empty
+    logits = torch.full((3 + 2, stride), SENTINEL, dtype=torch.float32, device="cuda")
+    status = wuda.device_status_word()
+    wuda.mqa_logits_fp8_decode_out(d["q"], d["kv_pages"], d["weights"], lens, d["block_table"], None, logits,
+                                   case["epb"], status_word=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 111
+    got = logits.cpu().numpy()
+    ref = oracle.mqa_logits_fp8(case["q"], case["kv_pages"], case["weights"], case["context_lens"],
+                                case["block_table"], 1, 64, stride)
+    assert np.all(got[3:] == SENTINEL) and np.all(got[1] == SENTINEL)       # guard rows, the "negative" request
+    valid = np.isfinite(ref)
+    valid[1] = False
+    assert_close_logits(got[:3], ref, valid)                               # rows 0 (its real 700 tokens) and 2
+    assert np.all(got[2][500:] == SENTINEL)
+
+
 def test_reference_call_shape_allocating_form(wuda):
     case = workloads.make_mqa_case(3, 2, 100, 900, seed=31)
     d = workloads.to_device(case)

@@ -59,6 +59,18 @@ def test_noalloc_entry_matches_regular_entry_on_two_calls_in_a_row(wuda):
         assert np.all(np.abs(f - exact) <= 1e-2 * np.abs(exact) + 1e-3 * np.sqrt(np.mean(exact.astype(np.float64) ** 2)))
 
 
+def test_noalloc_calls_of_different_row_counts_share_the_array(wuda):
+    """5, 20 and 64 rows use partial-tile slots of 16, 32 and 64 columns: consecutive calls lay their slots
+    out differently over the one shared array (the flags stay where they are), and each must still give
+    the regular entry point's bits."""
+    wide = workloads.make_gemm_fp8_case(64, 7168, 2048, seed=43)
+    narrow = workloads.make_gemm_fp8_case(5, 7168, 2048, seed=44)
+    middle = workloads.make_gemm_fp8_case(20, 2112, 4096, seed=45)
+    refs = {id(c): _regular(wuda, c) for c in (wide, narrow, middle)}
+    for case in (wide, narrow, wide, middle, narrow, middle, wide):
+        assert np.array_equal(_noalloc(wuda, case), refs[id(case)])
+
+
 def test_noalloc_entry_refuses_sizes_beyond_its_scratch(wuda):
     fake = ctypes.c_void_p(0x1000)
     st = wuda.lib.wuda_gemm_fp8_blockscaled_noalloc(fake, fake, fake, fake, fake, 65, 4096, 4096, None, None)

@@ -17,6 +17,9 @@ because consecutive launches use different weight buffers that together exceed L
     python -m wuda_b200.benchmarks sparse_mla                      (sparse MLA decode attention, window 128 + top-2048)
     python -m wuda_b200.benchmarks sparse_mla_launches             (three eager launches of a small case, for ncu)
     python -m wuda_b200.benchmarks one gemm_fp8 64 24576 7168      (a few launches of one shape, for ncu)
+    python -m wuda_b200.benchmarks layer                          (the whole decode layer, one graph: tok/s/GPU)
+    python -m wuda_b200.benchmarks layer_launches                 (two eager passes of the layer, for an ncu launch list)
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks layer_tp2
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks tp2
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m wuda_b200.benchmarks moe_ep2
 """
@@ -29,6 +32,7 @@ import torch
 
 import wuda_b200 as wuda
 from wuda_b200 import workloads
+from wuda_b200.layer_setup import model1_pool
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -482,21 +486,6 @@ def mqa_fp4(batches=(64,), contexts=(8192, 32768), launches_only=0):
                   (batch, ctx, us, by / us / 1e3, by / us / 1e3 / hbm, batch * ctx * 68 / 1e6))
 
 
-def model1_pool(pages, epb, seed):
-    """uint8 [pages, stride] pool of random MODEL1 records (finite e4m3, exponents near 0, small bf16)."""
-    g = torch.Generator(device="cuda").manual_seed(seed)
-    stride = -(-epb * 584 // 576) * 576
-    pool = torch.zeros(pages, stride, dtype=torch.uint8, device="cuda")
-    body = torch.randint(0, 256, (pages, epb, 576), generator=g, device="cuda", dtype=torch.int32)
-    body = torch.where((body & 0x7f) == 0x7f, body & 0x80, body)
-    body[..., 449::2] = (body[..., 449::2] & 0x80) | 0x3e | (body[..., 449::2] & 1)   # bf16 high bytes: |x| in [0.1, 0.6)
-    pool[:, :epb * 576] = body.to(torch.uint8).reshape(pages, epb * 576)
-    sb = torch.zeros(pages, epb, 8, dtype=torch.uint8, device="cuda")
-    sb[..., :7] = torch.randint(115, 122, (pages, epb, 7), generator=g, device="cuda").to(torch.uint8)
-    pool[:, epb * 576:epb * 584] = sb.reshape(pages, epb * 8)
-    return pool
-
-
 def sparse_mla(batches=(4, 16, 64, 128), heads=128, window=128, topk=2048, context=32768, launches_only=0):
     """Sparse MLA decode attention: per request `window` sliding-window records and `topk` of the
     context / 4 compressed records, gathered by index from pools that exceed L2."""
@@ -536,6 +525,204 @@ def sparse_mla(batches=(4, 16, 64, 128), heads=128, window=128, topk=2048, conte
                                                          gathered / us / 1e3, gathered / us / 1e3 / hbm * 100))
 
 
+def time_replays(replay, reps, group=None, flush=None):
+    """Mean device time (us) of replay(), timed with CUDA events around each call on the current stream; with a
+    process group, the ranks start each call together (host barrier) and the mean of the per-call MAX over ranks
+    is returned.  `flush` (a buffer larger than L2) is rewritten before every call when given."""
+    import torch.distributed as dist
+    times = []
+    for i in range(reps + 3):
+        if flush is not None:
+            flush.fill_(i & 0xff)
+        if group is not None:
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        replay()
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(e0.elapsed_time(e1) * 1e3)
+    t = torch.tensor(times, dtype=torch.float64)
+    if group is not None:
+        if dist.get_backend(group) == "nccl":
+            t = t.cuda()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t.mean().item())
+
+
+def tp2_gemm_leg(group, pair_rank, m=64, n=7168, k=16384, reps=30, seed=1234):
+    """The wo_b projection of a tensor-parallel pair (K split in two, all-reduce fused into the GEMM epilogue
+    over NVLink peer memory) as CUDA-graph replays, next to the same local GEMM without the exchange.
+    Returns the timings and what the caller needs to check the result: the full synthetic case (identical on
+    both ranks) and this rank's bf16 output as uint16."""
+    hbm, _, kind = peaks()
+    case = workloads.make_gemm_fp8_case(m, n, k, seed=seed)
+    kl = k // 2
+    sl, sb = slice(pair_rank * kl, (pair_rank + 1) * kl), slice(pair_rank * kl // 128, (pair_rank + 1) * kl // 128)
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    a, w = t(case["a"][:, sl]).view(torch.float8_e4m3fn), t(case["w"][:, sl]).view(torch.float8_e4m3fn)
+    a_s, w_s = t(case["a_s"][:, sb]), t(case["w_s"][:, sb])
+    copies = 4                                    # rotate weight buffers: 4 x 59 MB exceed the L2
+    ws = [w] + [w.clone() for _ in range(copies - 1)]
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    link = wuda.TP2Link(m, n, group=group, device_sequence=True)
+    status = wuda.device_status_word()
+
+    def graph_of(fn):
+        fn(ws[0])
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(copies):
+                    fn(ws[i])
+        torch.cuda.synchronize()
+        return g
+
+    g_fused = graph_of(lambda wt: link.fp8_gemm(a, a_s, wt, w_s, out=out, status_word=status))
+    g_local = graph_of(lambda wt: wuda.fp8_gemm(a, a_s, wt, w_s, out=out))
+    t_local = time_replays(g_local.replay, reps, group) / copies
+    t_fused = time_replays(g_fused.replay, reps, group) / copies
+    got = out.cpu().view(torch.int16).numpy().view(np.uint16)       # last replay ends on ws[copies-1] == the same weights
+    by = workloads.gemm_fp8_algorithmic_bytes(m, n, kl)
+    link_bytes = m * n * 4
+    bound_us = max(by / (hbm * 1e3), link_bytes / (770.0 * 1e3))
+    res = dict(shape=[m, n, k], gemm_allreduce_us=t_fused, local_gemm_us=t_local, nvlink_bytes=link_bytes,
+               hbm_bytes=by, roofline_us=bound_us, roofline_frac=bound_us / t_fused, status=int(status.item()),
+               launch="CUDA-graph replays, call sequence numbered on the device")
+    torch.cuda.synchronize()
+    link.close()
+    return res, case, got
+
+
+def ep2_combine_leg(group, pair_rank, tokens=64, topk=8, experts=256, dim=7168, inter=2048, reps=10):
+    """Router + routed experts of one MoE block with the experts split over a pair of ranks and the combine step
+    exchanging fp32 partial rows over NVLink peer memory, as CUDA-graph replays.  Returns timings, this rank's
+    output (uint16 bits of the bf16 rows) and its local fp32 partial sums for the caller's check."""
+    from wuda_b200 import moe
+    hbm, _, kind = peaks()
+    half = experts // 2
+    g = torch.Generator(device="cuda").manual_seed(3)          # the same tokens and gate on both ranks
+    x = torch.randn(tokens, dim, generator=g, device="cuda").bfloat16()
+    gate_w = (torch.randn(experts, dim, generator=g, device="cuda") * 0.05).bfloat16()
+    bias = torch.zeros(experts, device="cuda")
+    logits = torch.empty(tokens, experts, device="cuda")
+    y = torch.empty(tokens, dim, dtype=torch.bfloat16, device="cuda")
+    w = moe.RandomRoutedExperts(half, inter, dim, seed=10 + pair_rank)
+    link = moe.EP2Link(tokens, dim, group=group, device_sequence=True)
+    runner = moe.MoERunner(w, tokens, topk, expert_first=pair_rank * half, experts_total=experts, link=link)
+    state = {}
+
+    def step():
+        rw, idx = wuda.moe_gate(x, gate_w, bias, "sqrtsoftplus", 2.5, topk, logits=logits)
+        runner.forward(x, rw, idx, y=y)
+        state["idx"] = idx
+
+    step()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+    torch.cuda.synchronize()
+    us = time_replays(graph.replay, reps, group)
+    idx = state["idx"]
+    mine = (idx >= pair_rank * half) & (idx < (pair_rank + 1) * half)
+    active = int(torch.unique(idx[mine]).numel())
+    # this rank's partial: fp32 sum of its experts' bf16 rows per token, in the kernel's order (pair order)
+    rows = runner.pair_row[:tokens].long()
+    out = runner.out.float()
+    part = torch.zeros(tokens, dim, device="cuda")
+    for j in range(topk):
+        r = rows[:, j]
+        part = part + torch.where((r >= 0)[:, None], out[r.clamp_min(0)], torch.zeros_like(part))
+    per_expert = 2 * inter * dim // 2 + 2 * inter * dim // 16 + dim * inter // 2 + dim * inter // 16
+    res = dict(tokens=tokens, experts=experts, active_experts=active, block_us=us, expert_bytes=active * per_expert,
+               hbm_frac=active * per_expert / us / 1e3 / hbm, nvlink_bytes=tokens * dim * 4, status=int(runner.status.item()),
+               launch="one CUDA graph per block, call sequence numbered on the device")
+    got = y.cpu().view(torch.int16).numpy().view(np.uint16)
+    part = part.cpu().numpy()
+    torch.cuda.synchronize()
+    link.close()
+    return res, got, part
+
+
+def layer_leg(batch=64, context=32768, topk=2048, reps=20, group=None, pair_rank=0, launches_only=0):
+    """The whole decode layer (attention half + MoE half) of `batch` requests at `context` tokens as one CUDA
+    graph, on one GPU (group None) or on a tensor-parallel pair; decode tokens/s/GPU = batch / (t * ranks).
+    Returns (result dict, output of the last pass as a CPU tensor)."""
+    from wuda_b200 import moe
+    from wuda_b200.layer_setup import build_random_layer, layer_weight_bytes
+    hbm, _, kind = peaks()
+    world = 1 if group is None else 2
+    tp_link = ep_link = None
+    if world == 2:
+        tp_link = wuda.TP2Link(batch, 7168, group=group, device_sequence=True)
+        ep_link = moe.EP2Link(batch, 7168, group=group, device_sequence=True)
+    layer, slots, x = build_random_layer(batch, context, topk=topk, rank=pair_rank, world=world, tp_link=tp_link,
+                                         ep_link=ep_link)
+    layer.prepare(slots)
+    if launches_only:
+        for _ in range(launches_only):
+            layer.launch(x, batch)
+        torch.cuda.synchronize()
+        layer.check_status()
+        print("layer: %d eager passes done" % launches_only)
+        return None, None
+    layer.capture(x, batch)
+    us = time_replays(layer.replay, reps, group)
+    layer.check_status()
+    out = layer.replay()
+    torch.cuda.synchronize()
+    idx = layer.route_indices
+    per = layer.ffn.routed.experts
+    mine = (idx >= layer.ffn.expert_first) & (idx < layer.ffn.expert_first + per)
+    active = int(torch.unique(idx[mine]).numel())
+    ncmp = context // 4
+    wbytes = layer_weight_bytes(world, experts_active=active)
+    cache_bytes = batch * ncmp * 132 + batch * (128 + min(topk, ncmp)) * 584
+    res = dict(batch=batch, context=context, ranks=world, layer_us=us, tok_s_per_gpu=batch / (us * 1e-6) / world,
+               weight_bytes_per_rank=wbytes, cache_bytes_per_rank=cache_bytes, active_experts_this_rank=active,
+               hbm_floor_us=(wbytes + cache_bytes) / (hbm * 1e3), hbm_frac=(wbytes + cache_bytes) / (hbm * 1e3) / us,
+               launch="one CUDA graph per layer pass; weights streamed per pass (%.1f GB) exceed the L2" % (wbytes / 1e9),
+               status=0)
+    result = out.float().cpu()
+    if tp_link is not None:
+        torch.cuda.synchronize()
+        tp_link.close()
+        ep_link.close()
+    return res, result
+
+
+def layer(batch=64, context=32768):
+    res, _ = layer_leg(batch, context)
+    print("decode layer, batch %d, context %d, one GPU: %.1f us per pass = %.0f tokens/s/GPU; %.2f GB of weights + %.0f MB of "
+          "cache records streamed = %.2f of the HBM floor (%.1f us)" %
+          (batch, context, res["layer_us"], res["tok_s_per_gpu"], res["weight_bytes_per_rank"] / 1e9,
+           res["cache_bytes_per_rank"] / 1e6, res["hbm_frac"], res["hbm_floor_us"]))
+
+
+def layer_tp2(batch=64, context=32768):
+    """Run under torch.distributed.run with two ranks."""
+    import torch.distributed as dist
+    rank = int(os.environ["RANK"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("gloo")
+    group = dist.new_group([0, 1])
+    res, _ = layer_leg(batch, context, group=group, pair_rank=rank)
+    if rank == 0:
+        print("decode layer, batch %d, context %d, tensor-parallel pair: %.1f us per pass = %.0f tokens/s/GPU; this rank "
+              "streams %.2f GB of weights = %.2f of its HBM floor (%.1f us)" %
+              (batch, context, res["layer_us"], res["tok_s_per_gpu"], res["weight_bytes_per_rank"] / 1e9, res["hbm_frac"],
+               res["hbm_floor_us"]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def one(kind, m, n, k, launches=5):
     """A few eager launches of one GEMM shape (profiler captures)."""
     t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
@@ -558,6 +745,7 @@ KINDS = {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm
          "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(32,), launches_only=3),
          "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
          "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,
+         "layer": layer, "layer_tp2": layer_tp2, "layer_launches": lambda: layer_leg(launches_only=2),
          "moe_experts_launches": lambda: moe_experts(launches_only=2),
          "attention_half_layer_launches": lambda: attention_half_layer(launches_only=3)}
 

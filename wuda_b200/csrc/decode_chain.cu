@@ -133,8 +133,11 @@ extern "C" int wuda_csa_decode_step(const wuda_csa_weights* w, const wuda_csa_ca
                                      m, 1, c->idx_num_blocks, c->idx_entries_per_block, c->idx_block_stride_bytes,
                                      s->block_table_stride, s->logits_stride, ws->status_word, stream);
     if (status == WUDA_OK)
-        status = wuda_topk(s->logits, s->n_compressed, s->cmp_block_table ? s->cmp_block_table : s->idx_block_table, s->topk_indices, s->topk_raw, m,
-                           s->logits_stride, s->block_table_stride, 1, s->topk, c->idx_entries_per_block, stream);
+        // the selected positions become entries of the pool the attention reads: the compressed-KV pool's page
+        // table and page size when that table is given, else the indexer pool's
+        status = wuda_topk(s->logits, s->n_compressed, s->cmp_block_table ? s->cmp_block_table : s->idx_block_table,
+                           s->topk_indices, s->topk_raw, m, s->logits_stride, s->block_table_stride, 1, s->topk,
+                           s->cmp_block_table ? c->cmp_entries_per_block : c->idx_entries_per_block, stream);
     if (query_forked) WUDA_CUDA(cudaStreamWaitEvent(main_stream, side->query_done, 0));   // join B
     return status;
 }

@@ -73,7 +73,8 @@ struct Params {
     float* tp_peer_inbox = nullptr;    // the same buffer of the peer, mapped into this process
     int32_t* tp_my_flags = nullptr;    // [2 sets][n_tiles]: sequence number of the last tile received
     int32_t* tp_peer_flags = nullptr;
-    int tp_epoch = 0;                  // sequence number of this call (> 0, same on both ranks)
+    int32_t* tp_ctrl = nullptr;        // this rank's control words: [0] last finished call, [1] CTAs done
+    int tp_epoch = 0;                  // sequence number of this call (> 0, same on both ranks); 0: tp_ctrl[0] + 1
     unsigned long long tp_wait_ns = 0; // limit of one wait for the peer
 };
 
@@ -225,6 +226,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     // the prologue above ran while the kernel ahead was still finishing; global memory from here on
     pdl_launch_dependents();
     pdl_wait();
+
+    // two-rank form with the link's own numbering: this call's number is one more than the last
+    // finished call's (the word is rewritten only after every CTA of this call has read it)
+    const int tp_epoch = (p.tp_peer_inbox && p.tp_epoch == 0) ? ld_acquire_gpu(p.tp_ctrl) + 1 : p.tp_epoch;
 
     const long long units = static_cast<long long>(p.n_tiles) * p.kb;
     const long long u0 = range_begin(units, blockIdx.x, gridDim.x);
@@ -516,7 +521,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
                         // in fp32, so both ranks hold bit-identical sums.  Inbox sets alternate
                         // with the call's sequence number: a rank can be one call ahead of its
                         // peer's reads, never two.
-                        const int64_t set = static_cast<int64_t>(p.tp_epoch & 1) * p.n_tiles;
+                        const int64_t set = static_cast<int64_t>(tp_epoch & 1) * p.n_tiles;
                         const int64_t tile_off = (set + tile) * (M_PAD * kTileN) + row_in_tile;
                         if (alive) {
 #pragma unroll
@@ -526,10 +531,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
                         __threadfence_system();
                         epi_bar_sync();
                         if (et == 0 && alive) {
-                            st_release_sys(p.tp_peer_flags + set + tile, p.tp_epoch);
+                            st_release_sys(p.tp_peer_flags + set + tile, tp_epoch);
                             const unsigned long long start = globaltimer_ns();
                             uint32_t spins = 0;
-                            while (ld_acquire_sys(p.tp_my_flags + set + tile) != p.tp_epoch) {
+                            while (ld_acquire_sys(p.tp_my_flags + set + tile) != tp_epoch) {
                                 if ((++spins & 63u) == 0u && (*abort_flag || globaltimer_ns() - start > p.tp_wait_ns)) {
                                     *abort_flag = 1;
                                     if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeerFlag);
@@ -572,6 +577,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     if (warp == kProducers) {
         tc_fence_after();
         tmem_dealloc(tmem_base, L::kTmemCols);
+    }
+    if (p.tp_peer_inbox && p.tp_epoch == 0 && threadIdx.x == 0) {
+        // the last CTA to get here has seen every other CTA finish, hence read the old number
+        __threadfence();
+        if (atomicAdd(p.tp_ctrl + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+            p.tp_ctrl[1] = 0;
+            st_release_gpu(p.tp_ctrl, tp_epoch);
+        }
     }
 }
 
@@ -620,13 +633,107 @@ extern "C" int64_t wuda_gemm_fp8_scratch_bytes(int m, int n) {
     return static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4 + kMaxGrid * 4;
 }
 
-// groups == 1: the plain GEMM.  groups > 1: `n` rows per group, group g multiplies the activations'
-// columns [g * k, (g + 1) * k) by the weight rows [g * n, (g + 1) * n).
-static int gemm_fp8_entry(const void* a, const float* a_scales, const void* w, const float* w_scales, void* c_bf16,
-                          int m, int n, int k, int groups, void* scratch, int64_t scratch_bytes,
-                          int32_t* status_word, void* stream) {
+namespace {
+
+// What every entry point of this file hands to the one set-up routine below.
+struct GemmCall {
+    const void* a = nullptr;
+    const float* a_scales = nullptr;
+    const void* w = nullptr;
+    const float* w_scales = nullptr;
+    void* c = nullptr;
+    int m = 0, n = 0, k = 0;          // n = rows per group
+    int groups = 1;
+    float* slots = nullptr;           // [kMaxGrid][m_pad][128] fp32 partial tiles
+    int32_t* flags = nullptr;         // [kMaxGrid], zero between calls
+    int32_t* status = nullptr;
+    cudaStream_t stream = nullptr;
+    // two-rank form (inboxes == nullptr: none)
+    void* my_inbox = nullptr;
+    void* peer_inbox = nullptr;
+    int epoch = 0;
+    int peer_wait_ms = 0;
+};
+
+constexpr int64_t kTpFlagBytes = 4096;      // 2 sets x n_tiles tile flags, then the control words
+constexpr int64_t kTpCtrlBytes = 64;        // last bytes of the flag block: {call sequence, CTAs done}
+
+int64_t tp_bytes(int m, int n) {
+    if (m < 1 || m > 256 || n < 1) return -1;
+    int m_pad = 16;
+    while (m_pad < m) m_pad *= 2;
+    const int64_t n_tiles = (n + 127) / 128;
+    if (2 * n_tiles * 4 > kTpFlagBytes - kTpCtrlBytes) return -1;
+    return kTpFlagBytes + 2 * n_tiles * m_pad * 128 * 4;
+}
+
+// Parameter block, the two tensor maps and the launch for 1 <= m <= 128 (checked by the callers).
+int gemm_fp8_setup_and_launch(const GemmCall& g) {
     using namespace wuda;
     using namespace wuda::gemm8;
+    DeviceInfo dev;
+    int st = current_device_info(&dev);
+    if (st != WUDA_OK) return st;
+    WUDA_REQUIRE(dev.num_sms <= kMaxGrid, "device has %d SMs; at most %d are supported", dev.num_sms, kMaxGrid);
+    const int n_all = g.n * g.groups;
+    int m_pad = 16;
+    while (m_pad < g.m) m_pad *= 2;
+    Params p;
+    p.a_scales = g.a_scales;
+    p.w_scales = g.w_scales;
+    p.c = static_cast<__nv_bfloat16*>(g.c);
+    p.status = g.status;
+    p.M = g.m;
+    p.N = n_all;
+    p.K = g.k;
+    p.kb = g.k / 128;
+    p.n_tiles = (n_all + 127) / 128;
+    p.group_tiles = g.groups > 1 ? g.n / 128 : 0;
+    p.a_kb_total = g.groups * (g.k / 128);
+    p.scratch = g.slots;
+    p.flags = g.flags;
+    p.stages = 0;
+    if (g.peer_inbox) {
+        p.tp_my_flags = static_cast<int32_t*>(g.my_inbox);
+        p.tp_peer_flags = static_cast<int32_t*>(g.peer_inbox);
+        p.tp_my_inbox = reinterpret_cast<float*>(static_cast<uint8_t*>(g.my_inbox) + kTpFlagBytes);
+        p.tp_peer_inbox = reinterpret_cast<float*>(static_cast<uint8_t*>(g.peer_inbox) + kTpFlagBytes);
+        p.tp_ctrl = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(g.my_inbox) + kTpFlagBytes - kTpCtrlBytes);
+        p.tp_epoch = g.epoch;
+        p.tp_wait_ns = static_cast<unsigned long long>(g.peer_wait_ms) * 1000ull * 1000ull;
+    }
+
+    CUtensorMap w_map, a_map;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(g.k), static_cast<uint64_t>(n_all)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(g.k)};
+        const uint32_t box[2] = {128u, 128u};
+        st = encode_tensor_map(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, g.w, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (st != WUDA_OK) return st;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(g.k) * g.groups, static_cast<uint64_t>(g.m)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(g.k) * g.groups};
+        const uint32_t box[2] = {128u, static_cast<uint32_t>(m_pad)};
+        st = encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, g.a, dims, strides, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+        if (st != WUDA_OK) return st;
+    }
+    switch (m_pad) {
+        case 16: return launch<16>(w_map, a_map, p, dev, g.stream);
+        case 32: return launch<32>(w_map, a_map, p, dev, g.stream);
+        case 64: return launch<64>(w_map, a_map, p, dev, g.stream);
+        default: return launch<128>(w_map, a_map, p, dev, g.stream);
+    }
+}
+
+// groups == 1: the plain GEMM.  groups > 1: `n` rows per group, group g multiplies the activations'
+// columns [g * k, (g + 1) * k) by the weight rows [g * n, (g + 1) * n).
+int gemm_fp8_entry(const void* a, const float* a_scales, const void* w, const float* w_scales, void* c_bf16,
+                   int m, int n, int k, int groups, void* scratch, int64_t scratch_bytes,
+                   int32_t* status_word, void* stream) {
+    using namespace wuda;
     clear_error();
     WUDA_REQUIRE(groups >= 1, "groups must be >= 1 (got %d)", groups);
     WUDA_REQUIRE(groups == 1 || n % 128 == 0, "with groups the rows per group must be a multiple of 128 (got %d)", n);
@@ -653,56 +760,19 @@ static int gemm_fp8_entry(const void* a, const float* a_scales, const void* w, c
                               static_cast<__nv_bfloat16*>(c_bf16) + static_cast<int64_t>(128) * n_all, m - 128, n, k,
                               groups, scratch, scratch_bytes, status_word, stream);
     }
-
-    DeviceInfo dev;
-    int st = current_device_info(&dev);
-    if (st != WUDA_OK) return st;
-
     int m_pad = 16;
     while (m_pad < m) m_pad *= 2;
-    Params p;
-    p.a_scales = a_scales;
-    p.w_scales = w_scales;
-    p.c = static_cast<__nv_bfloat16*>(c_bf16);
-    p.status = status_word;
-    p.M = m;
-    p.N = n_all;
-    p.K = k;
-    p.kb = k / 128;
-    p.n_tiles = (n_all + 127) / 128;
-    p.group_tiles = groups > 1 ? n / 128 : 0;
-    p.a_kb_total = groups * (k / 128);
-    p.scratch = static_cast<float*>(scratch);
-    p.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
-    WUDA_REQUIRE(dev.num_sms <= kMaxGrid, "device has %d SMs; at most %d are supported", dev.num_sms, kMaxGrid);
-    p.stages = 0;
-
-    CUtensorMap w_map, a_map;
-    {
-        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n_all)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(k)};
-        const uint32_t box[2] = {128u, 128u};
-        st = encode_tensor_map(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box,
-                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-        if (st != WUDA_OK) return st;
-    }
-    {
-        const uint64_t dims[2] = {static_cast<uint64_t>(k) * groups, static_cast<uint64_t>(m)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(k) * groups};
-        const uint32_t box[2] = {128u, static_cast<uint32_t>(m_pad)};
-        st = encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box,
-                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
-        if (st != WUDA_OK) return st;
-    }
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    switch (m_pad) {
-        case 16: return launch<16>(w_map, a_map, p, dev, s);
-        case 32: return launch<32>(w_map, a_map, p, dev, s);
-        case 64: return launch<64>(w_map, a_map, p, dev, s);
-        case 128: return launch<128>(w_map, a_map, p, dev, s);
-        default: return launch<256>(w_map, a_map, p, dev, s);
-    }
+    GemmCall g;
+    g.a = a, g.a_scales = a_scales, g.w = w, g.w_scales = w_scales, g.c = c_bf16;
+    g.m = m, g.n = n, g.k = k, g.groups = groups;
+    g.slots = static_cast<float*>(scratch);
+    g.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
+    g.status = status_word;
+    g.stream = static_cast<cudaStream_t>(stream);
+    return gemm_fp8_setup_and_launch(g);
 }
+
+}  // namespace
 
 extern "C" int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* w, const float* w_scales,
                                          void* c_bf16, int m, int n, int k, void* scratch, int64_t scratch_bytes,
@@ -734,7 +804,8 @@ extern "C" int wuda_gemm_fp8_grouped(const void* a, const float* a_scales, const
 // zero; the kernel resets each flag after use, and the entry point clears all of them again
 // before every launch in case an earlier call ended abnormally.  Two calls that overlap on the
 // GPU (different streams) would race on the slots: calls through this entry point must be
-// ordered one after another on the device.
+// ordered one after another on the device.  The flags sit at a fixed offset behind the largest
+// slot area, so calls with different m (different slot sizes) share the array without moving them.
 constexpr int kNoAllocMaxM = 64;
 constexpr int64_t kNoAllocSlotBytes = static_cast<int64_t>(kMaxGrid) * kNoAllocMaxM * 128 * 4;
 constexpr int64_t kNoAllocScratchBytes = kNoAllocSlotBytes + kMaxGrid * 4;   // 6,292,224 bytes
@@ -765,7 +836,6 @@ extern "C" int wuda_gemm_fp8_blockscaled_noalloc(const void* a, const float* a_s
                                                  const float* w_scales, void* c_bf16, int m, int n, int k,
                                                  int32_t* status_word, void* stream) {
     using namespace wuda;
-    using namespace wuda::gemm8;
     clear_error();
     WUDA_REQUIRE(m >= 0, "m must be >= 0 (got %d)", m);
     if (m > kNoAllocMaxM)
@@ -782,52 +852,20 @@ extern "C" int wuda_gemm_fp8_blockscaled_noalloc(const void* a, const float* a_s
     DeviceInfo dev;
     int st = current_device_info(&dev);
     if (st != WUDA_OK) return st;
-    WUDA_REQUIRE(dev.num_sms <= kMaxGrid, "device has %d SMs; at most %d are supported", dev.num_sms, kMaxGrid);
     void* scratch = nullptr;
     st = noalloc_scratch_address(dev.device, &scratch);   // first call on a device: symbol lookup
     if (st != WUDA_OK) return st;
 
-    int m_pad = 16;
-    while (m_pad < m) m_pad *= 2;
-    Params p;
-    p.a_scales = a_scales;
-    p.w_scales = w_scales;
-    p.c = static_cast<__nv_bfloat16*>(c_bf16);
-    p.status = status_word;
-    p.M = m;
-    p.N = n;
-    p.K = k;
-    p.kb = k / 128;
-    p.n_tiles = (n + 127) / 128;
-    p.scratch = static_cast<float*>(scratch);
-    p.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + kNoAllocSlotBytes);
-    p.stages = 0;
-
-    CUtensorMap w_map, a_map;
-    {
-        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(k)};
-        const uint32_t box[2] = {128u, 128u};
-        st = encode_tensor_map(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box,
-                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-        if (st != WUDA_OK) return st;
-    }
-    {
-        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(k)};
-        const uint32_t box[2] = {128u, static_cast<uint32_t>(m_pad)};
-        st = encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box,
-                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
-        if (st != WUDA_OK) return st;
-    }
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    GemmCall g;
+    g.a = a, g.a_scales = a_scales, g.w = w, g.w_scales = w_scales, g.c = c_bf16;
+    g.m = m, g.n = n, g.k = k;
+    g.slots = static_cast<float*>(scratch);
+    g.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + kNoAllocSlotBytes);
+    g.status = status_word;
+    g.stream = static_cast<cudaStream_t>(stream);
     // the flags must start at zero whatever the previous call left behind
-    WUDA_CUDA(cudaMemsetAsync(p.flags, 0, kMaxGrid * sizeof(int32_t), s));
-    switch (m_pad) {
-        case 16: return launch<16>(w_map, a_map, p, dev, s);
-        case 32: return launch<32>(w_map, a_map, p, dev, s);
-        default: return launch<64>(w_map, a_map, p, dev, s);
-    }
+    WUDA_CUDA(cudaMemsetAsync(g.flags, 0, kMaxGrid * sizeof(int32_t), g.stream));
+    return gemm_fp8_setup_and_launch(g);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -838,21 +876,15 @@ extern "C" int wuda_gemm_fp8_blockscaled_noalloc(const void* a, const float* a_s
 // its K slice; the all-reduce happens tile by tile inside the epilogue through peer memory.
 //
 // The exchange buffer of a rank ("inbox") is ordinary device memory made visible to the peer
-// process with CUDA IPC.  Layout: 2 sets x n_tiles flags (int32, padded to 4 KB), then
+// process with CUDA IPC.  Layout: a 4 KB flag block (2 sets x n_tiles int32 tile flags; its last
+// 64 bytes hold the link's own call sequence number and a count of finished CTAs), then
 // 2 sets x n_tiles x [M_PAD][128] fp32 tiles.
-namespace {
-constexpr int64_t kTpFlagBytes = 4096;
-
-int64_t tp_bytes(int m, int n) {
-    if (m < 1 || m > 256 || n < 1) return -1;
-    int m_pad = 16;
-    while (m_pad < m) m_pad *= 2;
-    const int64_t n_tiles = (n + 127) / 128;
-    if (2 * n_tiles * 4 > kTpFlagBytes) return -1;
-    return kTpFlagBytes + 2 * n_tiles * m_pad * 128 * 4;
-}
-}  // namespace
-
+//
+// Call sequence numbers.  A tile's flag carries the number of the call that delivered it, so both
+// ranks must number their calls alike.  epoch >= 1: the host numbers them (1, 2, 3, .. on both
+// ranks).  epoch == 0: the link numbers them itself - every CTA reads the last finished number from
+// the control words and the last CTA to finish stores the new one - so the same launch can be
+// replayed from a CUDA graph.  A link uses one of the two forms for its whole life.
 extern "C" int64_t wuda_tp2_inbox_bytes(int m, int n) { return tp_bytes(m, n); }
 
 extern "C" int wuda_tp2_alloc(int64_t bytes, void** local_base, unsigned char* ipc_handle_64) {
@@ -904,14 +936,15 @@ extern "C" int wuda_gemm_fp8_blockscaled_tp2(const void* a, const float* a_scale
                                              void* scratch, int64_t scratch_bytes, void* my_inbox, void* peer_inbox,
                                              int epoch, int peer_wait_ms, int32_t* status_word, void* stream) {
     using namespace wuda;
-    using namespace wuda::gemm8;
     clear_error();
-    WUDA_REQUIRE(m >= 1 && m <= 256, "m must be in [1, 256] (got %d)", m);
+    // one pass only: a second pass of rows would need a second exchange under its own sequence number
+    WUDA_REQUIRE(m >= 1 && m <= 128, "m must be in [1, 128] (got %d); split larger batches into calls of <= 128 rows", m);
     WUDA_REQUIRE(n >= 1, "n must be >= 1 (got %d)", n);
     WUDA_REQUIRE(k_local >= 128 && k_local % 128 == 0, "k_local must be a positive multiple of 128 (got %d)", k_local);
     WUDA_REQUIRE(a && a_scales && w && w_scales && c_bf16 && scratch && my_inbox && peer_inbox,
                  "a, a_scales, w, w_scales, c, scratch and both inboxes must not be NULL");
-    WUDA_REQUIRE(epoch >= 1, "epoch must be >= 1 and grow by one per call on both ranks (got %d)", epoch);
+    WUDA_REQUIRE(epoch >= 0, "epoch must be >= 1 and grow by one per call on both ranks, or 0 for the link's own "
+                 "numbering (got %d)", epoch);
     WUDA_REQUIRE(peer_wait_ms >= 1 && peer_wait_ms <= 10000, "peer_wait_ms must be in [1, 10000] (got %d)", peer_wait_ms);
     WUDA_REQUIRE(aligned16(a) && aligned16(w), "a and w must be 16-byte aligned");
     WUDA_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "scratch must be 256-byte aligned");
@@ -919,57 +952,15 @@ extern "C" int wuda_gemm_fp8_blockscaled_tp2(const void* a, const float* a_scale
     WUDA_REQUIRE(scratch_bytes >= need, "scratch holds %lld bytes; %lld are needed (wuda_gemm_fp8_scratch_bytes)",
                  static_cast<long long>(scratch_bytes), static_cast<long long>(need));
     WUDA_REQUIRE(tp_bytes(m, n) > 0, "n is too large for the exchange buffer's flag block");
-
-    DeviceInfo dev;
-    int st = current_device_info(&dev);
-    if (st != WUDA_OK) return st;
-    WUDA_REQUIRE(dev.num_sms <= kMaxGrid, "device has %d SMs; at most %d are supported", dev.num_sms, kMaxGrid);
-
     int m_pad = 16;
     while (m_pad < m) m_pad *= 2;
-    Params p;
-    p.a_scales = a_scales;
-    p.w_scales = w_scales;
-    p.c = static_cast<__nv_bfloat16*>(c_bf16);
-    p.status = status_word;
-    p.M = m;
-    p.N = n;
-    p.K = k_local;
-    p.kb = k_local / 128;
-    p.n_tiles = (n + 127) / 128;
-    p.scratch = static_cast<float*>(scratch);
-    p.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
-    p.stages = 0;
-    p.tp_my_flags = static_cast<int32_t*>(my_inbox);
-    p.tp_peer_flags = static_cast<int32_t*>(peer_inbox);
-    p.tp_my_inbox = reinterpret_cast<float*>(static_cast<uint8_t*>(my_inbox) + kTpFlagBytes);
-    p.tp_peer_inbox = reinterpret_cast<float*>(static_cast<uint8_t*>(peer_inbox) + kTpFlagBytes);
-    p.tp_epoch = epoch;
-    p.tp_wait_ns = static_cast<unsigned long long>(peer_wait_ms) * 1000ull * 1000ull;
-
-    CUtensorMap w_map, a_map;
-    {
-        const uint64_t dims[2] = {static_cast<uint64_t>(k_local), static_cast<uint64_t>(n)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(k_local)};
-        const uint32_t box[2] = {128u, 128u};
-        st = encode_tensor_map(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box,
-                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-        if (st != WUDA_OK) return st;
-    }
-    {
-        const uint64_t dims[2] = {static_cast<uint64_t>(k_local), static_cast<uint64_t>(m)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(k_local)};
-        const uint32_t box[2] = {128u, static_cast<uint32_t>(m_pad)};
-        st = encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box,
-                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
-        if (st != WUDA_OK) return st;
-    }
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    switch (m_pad) {
-        case 16: return launch<16>(w_map, a_map, p, dev, s);
-        case 32: return launch<32>(w_map, a_map, p, dev, s);
-        case 64: return launch<64>(w_map, a_map, p, dev, s);
-        case 128: return launch<128>(w_map, a_map, p, dev, s);
-        default: return launch<256>(w_map, a_map, p, dev, s);
-    }
+    GemmCall g;
+    g.a = a, g.a_scales = a_scales, g.w = w, g.w_scales = w_scales, g.c = c_bf16;
+    g.m = m, g.n = n, g.k = k_local;
+    g.slots = static_cast<float*>(scratch);
+    g.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
+    g.status = status_word;
+    g.stream = static_cast<cudaStream_t>(stream);
+    g.my_inbox = my_inbox, g.peer_inbox = peer_inbox, g.epoch = epoch, g.peer_wait_ms = peer_wait_ms;
+    return gemm_fp8_setup_and_launch(g);
 }

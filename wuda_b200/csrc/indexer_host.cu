@@ -80,6 +80,43 @@ extern "C" int wuda_indexer_plan_create(wuda_indexer_plan** out, int max_batch, 
     return WUDA_OK;
 }
 
+namespace {
+
+// Everything between the first enqueue and the final synchronisation; a failure in here must not
+// return to the caller while copies from (or to) its host buffers are still in flight.
+int indexer_topk_enqueue(wuda_indexer_plan* plan, const void* q_host, const void* kv_pages_host,
+                         const float* weights_host, const int32_t* context_lens_host, const int32_t* block_table_host,
+                         int32_t* page_indices_host, float* logits_host, int batch, int32_t* dev_status, cudaStream_t s) {
+    using namespace wuda;
+    const int64_t rows = static_cast<int64_t>(batch) * plan->next_n;
+    WUDA_CUDA(cudaMemsetAsync(plan->status, 0, sizeof(int32_t), s));
+    WUDA_CUDA(cudaMemcpyAsync(plan->q, q_host, rows * 64 * 128, cudaMemcpyHostToDevice, s));
+    if (kv_pages_host)
+        WUDA_CUDA(cudaMemcpyAsync(plan->kv, kv_pages_host, static_cast<size_t>(plan->num_blocks) * plan->page_stride,
+                                  cudaMemcpyHostToDevice, s));
+    WUDA_CUDA(cudaMemcpyAsync(plan->weights, weights_host, rows * 64 * sizeof(float), cudaMemcpyHostToDevice, s));
+    WUDA_CUDA(cudaMemcpyAsync(plan->ctx, context_lens_host, rows * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    WUDA_CUDA(cudaMemcpyAsync(plan->bt, block_table_host,
+                              static_cast<size_t>(batch) * plan->bt_stride * sizeof(int32_t),
+                              cudaMemcpyHostToDevice, s));
+    int st = wuda_mqa_logits_fp8(plan->q, plan->kv, plan->weights, plan->ctx, plan->bt, plan->logits, batch,
+                                 plan->next_n, plan->num_blocks, plan->epb, plan->page_stride, plan->bt_stride,
+                                 plan->logits_stride, plan->status, s);
+    if (st != WUDA_OK) return st;
+    st = wuda_topk(plan->logits, plan->ctx, plan->bt, plan->indices, nullptr, static_cast<int>(rows),
+                   plan->logits_stride, plan->bt_stride, plan->next_n, plan->k, plan->epb, s);
+    if (st != WUDA_OK) return st;
+    WUDA_CUDA(cudaMemcpyAsync(page_indices_host, plan->indices, rows * plan->k * sizeof(int32_t),
+                              cudaMemcpyDeviceToHost, s));
+    if (logits_host)
+        WUDA_CUDA(cudaMemcpyAsync(logits_host, plan->logits, rows * plan->logits_stride * sizeof(float),
+                                  cudaMemcpyDeviceToHost, s));
+    WUDA_CUDA(cudaMemcpyAsync(dev_status, plan->status, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    return WUDA_OK;
+}
+
+}  // namespace
+
 extern "C" int wuda_indexer_topk_host(wuda_indexer_plan* plan, const void* q_host, const void* kv_pages_host,
                                       const float* weights_host, const int32_t* context_lens_host,
                                       const int32_t* block_table_host, int32_t* page_indices_host,
@@ -90,34 +127,19 @@ extern "C" int wuda_indexer_topk_host(wuda_indexer_plan* plan, const void* q_hos
     WUDA_REQUIRE(batch >= 0 && batch <= plan->max_batch, "batch %d exceeds the plan's max_batch %d", batch,
                  plan->max_batch);
     if (batch == 0) return WUDA_OK;
-    WUDA_REQUIRE(q_host && kv_pages_host && weights_host && context_lens_host && block_table_host && page_indices_host,
-                 "host input and output pointers must not be NULL");
+    WUDA_REQUIRE(q_host && weights_host && context_lens_host && block_table_host && page_indices_host,
+                 "host input and output pointers must not be NULL (only kv_pages_host may be: pool unchanged)");
+    int dev = -1;
+    WUDA_CUDA(cudaGetDevice(&dev));
+    WUDA_REQUIRE(dev == plan->device, "the plan was created on device %d but device %d is current", plan->device, dev);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int64_t rows = static_cast<int64_t>(batch) * plan->next_n;
-    WUDA_CUDA(cudaMemsetAsync(plan->status, 0, sizeof(int32_t), s));
-    WUDA_CUDA(cudaMemcpyAsync(plan->q, q_host, rows * 64 * 128, cudaMemcpyHostToDevice, s));
-    WUDA_CUDA(cudaMemcpyAsync(plan->kv, kv_pages_host, static_cast<size_t>(plan->num_blocks) * plan->page_stride,
-                              cudaMemcpyHostToDevice, s));
-    WUDA_CUDA(cudaMemcpyAsync(plan->weights, weights_host, rows * 64 * sizeof(float), cudaMemcpyHostToDevice, s));
-    WUDA_CUDA(cudaMemcpyAsync(plan->ctx, context_lens_host, rows * sizeof(int32_t), cudaMemcpyHostToDevice, s));
-    WUDA_CUDA(cudaMemcpyAsync(plan->bt, block_table_host,
-                              static_cast<size_t>(batch) * plan->bt_stride * sizeof(int32_t),
-                              cudaMemcpyHostToDevice, s));
-    int st = wuda_mqa_logits_fp8(plan->q, plan->kv, plan->weights, plan->ctx, plan->bt, plan->logits, batch,
-                                 plan->next_n, plan->num_blocks, plan->epb, plan->page_stride, plan->bt_stride,
-                                 plan->logits_stride, plan->status, stream);
-    if (st != WUDA_OK) return st;
-    st = wuda_topk(plan->logits, plan->ctx, plan->bt, plan->indices, nullptr, static_cast<int>(rows),
-                   plan->logits_stride, plan->bt_stride, plan->next_n, plan->k, plan->epb, stream);
-    if (st != WUDA_OK) return st;
-    WUDA_CUDA(cudaMemcpyAsync(page_indices_host, plan->indices, rows * plan->k * sizeof(int32_t),
-                              cudaMemcpyDeviceToHost, s));
-    if (logits_host)
-        WUDA_CUDA(cudaMemcpyAsync(logits_host, plan->logits, rows * plan->logits_stride * sizeof(float),
-                                  cudaMemcpyDeviceToHost, s));
     int32_t dev_status = 0;
-    WUDA_CUDA(cudaMemcpyAsync(&dev_status, plan->status, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
-    WUDA_CUDA(cudaStreamSynchronize(s));
+    const int st = indexer_topk_enqueue(plan, q_host, kv_pages_host, weights_host, context_lens_host, block_table_host,
+                                        page_indices_host, logits_host, batch, &dev_status, s);
+    // on every path: no copy may outlive this call, the caller is free to reuse its host buffers
+    const cudaError_t sync = cudaStreamSynchronize(s);
+    if (st != WUDA_OK) return st;      // the message of the first failure stands
+    if (sync != cudaSuccess) return fail(WUDA_ERR_CUDA, "cudaStreamSynchronize failed: %s", cudaGetErrorString(sync));
     if (dev_status != 0) return fail(WUDA_ERR_DEVICE_STATUS, "kernel reported device status %d", dev_status);
     return WUDA_OK;
 }

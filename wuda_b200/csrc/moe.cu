@@ -269,8 +269,9 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
 // release of the token's flag), awaits the peer's row in its own inbox and adds it: a + b == b + a in fp32, so
 // both ranks hold bit-identical rows.  Inbox sets alternate with the call's sequence number.  The wait is
 // bounded: a peer that does not answer leaves WUDA_DEV_TIMEOUT_PEER_FLAG and the local sum in y.
-constexpr int64_t kEpFlagBytes = 4096;
 constexpr int kEpMaxTokens = 512;
+constexpr int64_t kEpCtrlOffset = 2 * kEpMaxTokens * 4;   // behind the flags: {call sequence, CTAs done}
+constexpr int64_t kEpFlagBytes = kEpCtrlOffset + 256;
 constexpr int kEpMaxVec = 4;            // 8-value vectors per thread: dim <= 8192
 
 struct CombineEpParams {
@@ -279,7 +280,8 @@ struct CombineEpParams {
     float* peer_rows;    // the same buffer of the peer
     int32_t* my_flags;   // [2 sets][kEpMaxTokens]
     int32_t* peer_flags;
-    int tokens_max, epoch;
+    int32_t* ctrl;       // this rank's control words: [0] last finished call, [1] CTAs done
+    int tokens_max, epoch;   // epoch 0: the call's number is ctrl[0] + 1 (replayable from a CUDA graph)
     unsigned long long wait_ns;
     int32_t* status;
 };
@@ -304,7 +306,8 @@ __global__ void __launch_bounds__(256) moe_combine_ep2_kernel(CombineEpParams q)
     const CombineParams& p = q.c;
     __shared__ int peer_ok;
     const int t = blockIdx.x;
-    const int set = q.epoch & 1;
+    const int epoch = q.epoch ? q.epoch : ld_acquire_sys(q.ctrl) + 1;
+    const int set = epoch & 1;
     const int64_t row_off = (static_cast<int64_t>(set) * q.tokens_max + t) * p.dim;
     float acc[kEpMaxVec][8];
 #pragma unroll
@@ -340,11 +343,11 @@ __global__ void __launch_bounds__(256) moe_combine_ep2_kernel(CombineEpParams q)
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
-        st_release_sys(q.peer_flags + set * kEpMaxTokens + t, q.epoch);
+        st_release_sys(q.peer_flags + set * kEpMaxTokens + t, epoch);
         int ok = 1;
         const unsigned long long start = globaltimer_ns();
         uint32_t spins = 0;
-        while (ld_acquire_sys(q.my_flags + set * kEpMaxTokens + t) != q.epoch) {
+        while (ld_acquire_sys(q.my_flags + set * kEpMaxTokens + t) != epoch) {
             if ((++spins & 63u) == 0u && globaltimer_ns() - start > q.wait_ns) {
                 if (q.status) atomicCAS(q.status, 0, static_cast<int>(kDevTimeoutPeerFlag));
                 ok = 0;
@@ -373,6 +376,14 @@ __global__ void __launch_bounds__(256) moe_combine_ep2_kernel(CombineEpParams q)
             ow[i] = *reinterpret_cast<uint32_t*>(&h);
         }
         *(reinterpret_cast<uint4*>(p.y + static_cast<int64_t>(t) * p.dim) + c) = o;
+    }
+    if (q.epoch == 0 && threadIdx.x == 0) {
+        // the last CTA to finish has seen every other CTA read the old number; it stores the new one
+        __threadfence();
+        if (atomicAdd(q.ctrl + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+            q.ctrl[1] = 0;
+            st_release_sys(q.ctrl, epoch);
+        }
     }
 }
 
@@ -516,9 +527,10 @@ extern "C" int wuda_moe_combine_ep2(const void* expert_out_bf16, const int32_t* 
                  "expert_out, pair_row, y and both inboxes must not be NULL");
     WUDA_REQUIRE(aligned16(expert_out_bf16) && aligned16(shared_bf16) && aligned16(y_bf16) && aligned16(my_inbox) &&
                      aligned16(peer_inbox), "rows and inboxes must be 16-byte aligned");
-    WUDA_REQUIRE(epoch >= 1, "epoch counts calls from 1 (got %d)", epoch);
+    WUDA_REQUIRE(epoch >= 0, "epoch counts calls from 1, or is 0 for the link's own numbering (got %d)", epoch);
     WUDA_REQUIRE(peer_wait_ms >= 1 && peer_wait_ms <= 10000, "peer_wait_ms must be in [1, 10000] (got %d)", peer_wait_ms);
     CombineEpParams q;
+    q.ctrl = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(my_inbox) + kEpCtrlOffset);
     q.c.out = static_cast<const __nv_bfloat16*>(expert_out_bf16);
     q.c.pair_row = pair_row;
     q.c.shared = static_cast<const __nv_bfloat16*>(shared_bf16);

@@ -27,17 +27,6 @@
 namespace wuda {
 namespace mqa {
 
-#ifndef WUDA_STYLE_PROD
-#define WUDA_STYLE_PROD 1
-#endif
-#ifndef WUDA_STYLE_MMA
-#define WUDA_STYLE_MMA 1
-#endif
-#ifndef WUDA_STYLE_MATH
-#define WUDA_STYLE_MATH 1
-#endif
-
-
 constexpr int kHeads = 64;
 constexpr int kDim = 128;
 constexpr int kTile = 128;          // tokens per work item (UMMA M)
@@ -85,6 +74,8 @@ struct Params {
     int epb;
     int bt_stride;
     int kv_stages;
+    int max_ctx;      // min(logits_stride, bt_stride * epb): no row may claim more tokens than its row of the
+                      // logits and of the block table holds
 };
 
 template <int NEXT_N>
@@ -103,12 +94,16 @@ struct Smem {
     static __host__ __device__ constexpr int total(int stages) { return misc_off(stages) + 16 + 1024; }
 };
 
-// Number of 128-token tiles request b needs (max context over its next_n rows).
+// A context length as the kernel uses it: negative values count as 0, values beyond what a row of the
+// logits / block table holds are cut to that (the math warps report the cut as kDevBadContextLen).
+__device__ __forceinline__ int clamp_ctx(int v, int max_ctx) { return min(max(v, 0), max_ctx); }
+
+// Max context over the next_n rows of request b (its tile count follows from it).
 template <int NEXT_N>
-__device__ __forceinline__ int request_ctx(const int32_t* ctx, int b) {
+__device__ __forceinline__ int request_ctx(const int32_t* ctx, int b, int max_ctx) {
     int m = 0;
 #pragma unroll
-    for (int j = 0; j < NEXT_N; ++j) m = max(m, __ldg(ctx + b * NEXT_N + j));
+    for (int j = 0; j < NEXT_N; ++j) m = max(m, clamp_ctx(__ldg(ctx + b * NEXT_N + j), max_ctx));
     return m;
 }
 
@@ -123,12 +118,12 @@ struct TileCursor {
 };
 
 template <int NEXT_N>
-__device__ __forceinline__ TileCursor make_cursor(const int32_t* ctx, int batch) {
+__device__ __forceinline__ TileCursor make_cursor(const int32_t* ctx, int batch, int max_ctx) {
     const uint32_t lane = lane_id();
     long long total = 0;
     for (int base = 0; base < batch; base += 32) {
         int b = base + lane;
-        int t = (b < batch) ? ((request_ctx<NEXT_N>(ctx, b) + kTile - 1) / kTile) : 0;
+        int t = (b < batch) ? ((request_ctx<NEXT_N>(ctx, b, max_ctx) + kTile - 1) / kTile) : 0;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
         total += t;
@@ -145,7 +140,7 @@ __device__ __forceinline__ TileCursor make_cursor(const int32_t* ctx, int batch)
     long long prefix = 0;
     for (int base = 0; base < batch; base += 32) {
         int b = base + lane;
-        int cx = (b < batch) ? request_ctx<NEXT_N>(ctx, b) : 0;
+        int cx = (b < batch) ? request_ctx<NEXT_N>(ctx, b, max_ctx) : 0;
         int t = (cx + kTile - 1) / kTile;
         int incl = t;
 #pragma unroll
@@ -175,7 +170,8 @@ __device__ __forceinline__ TileCursor make_cursor(const int32_t* ctx, int batch)
 // request entered on the way (requests without tiles are skipped by every role alike),
 // including the one the cursor lands in.  The caller never moves past the CTA's range.
 template <int NEXT_N, typename F>
-__device__ __forceinline__ void advance_by(TileCursor& c, int k, const int32_t* ctx, int batch, F&& on_enter) {
+__device__ __forceinline__ void advance_by(TileCursor& c, int k, const int32_t* ctx, int batch, int max_ctx,
+                                           F&& on_enter) {
     c.j += k;
     while (c.j >= c.tiles_b) {
         c.j -= c.tiles_b;
@@ -186,7 +182,7 @@ __device__ __forceinline__ void advance_by(TileCursor& c, int k, const int32_t* 
                 c.ctx_b = 0;
                 return;
             }
-            c.ctx_b = request_ctx<NEXT_N>(ctx, c.b);
+            c.ctx_b = request_ctx<NEXT_N>(ctx, c.b, max_ctx);
             c.tiles_b = (c.ctx_b + kTile - 1) / kTile;
         } while (c.tiles_b == 0);
         on_enter(c);
@@ -268,7 +264,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
     pdl_launch_dependents();
     pdl_wait();
 
-    TileCursor cur = make_cursor<NEXT_N>(p.context_lens, p.batch);
+    TileCursor cur = make_cursor<NEXT_N>(p.context_lens, p.batch, p.max_ctx);
     const int ntiles = cur.count;
 
     // Every role walks its own tiles n = r, r + R, ... of the CTA's range with a cursor
@@ -300,7 +296,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
         auto on_enter = [&](const TileCursor& c) {
             if (me == 0 && alive) {
                 const int qs = qc & 1;
-                alive = mbar_wait_lane0<WUDA_STYLE_PROD>(empty_q + qs * 8, ((qc >> 1) & 1) ^ 1, abort_flag, p.status,
+                alive = mbar_wait_lane0(empty_q + qs * 8, ((qc >> 1) & 1) ^ 1, abort_flag, p.status,
                                                          kDevTimeoutEmptyQ);
                 if (alive && lane == 0) {
                     mbar_arrive_expect_tx(full_q + qs * 8, L::kQBytes + L::kWBytes);
@@ -319,7 +315,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
         if (ntiles > 0) on_enter(cur);
         ring.step(me, S);       // the host guarantees S >= kProducers
         for (int n = me; n < ntiles && alive; n += kProducers) {
-            advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, on_enter);
+            advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, p.max_ctx, on_enter);
             at = n;
             if (!alive) break;
             const int first_page = cur.j << ppt_shift;
@@ -343,7 +339,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
                 phys = 0;
             }
             const int s = ring.idx;
-            alive = mbar_wait_lane0<WUDA_STYLE_PROD>(empty_kv + s * 8, ring.phase ^ 1u, abort_flag, p.status,
+            alive = mbar_wait_lane0(empty_kv + s * 8, ring.phase ^ 1u, abort_flag, p.status,
                                                      kDevTimeoutEmptyKv);
             if (!alive) break;
             if (lane == 0) mbar_arrive_expect_tx(full_kv + s * 8, valid * (page_bytes + page_scale_bytes));
@@ -353,7 +349,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
             ring.step(kProducers, S);
         }
         if (alive && ntiles > 0 && at < ntiles - 1)
-            advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, on_enter);
+            advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, p.max_ctx, on_enter);
     } else if (warp < kMmaWarp0 + kIssuers) {
         // ------------------------------------------------------------ UMMA issuers
         // One thread per warp runs the whole loop (the other lanes go straight to the
@@ -367,7 +363,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
                 if (qc > 0) umma_commit(empty_q + qs * 8);   // this issuer's UMMAs on the old q stage retired
                 qs = qc & 1;
                 if (alive)
-                    alive = mbar_wait<WUDA_STYLE_MMA>(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status,
+                    alive = mbar_wait(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status,
                                                       kDevTimeoutFullQ);
                 ++qc;
             };
@@ -377,13 +373,13 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
             ring.step(me, S);
             tring.step(me, kTmemStages);
             for (int n = me; n < ntiles && alive; n += kIssuers) {
-                advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, on_enter);
+                advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, p.max_ctx, on_enter);
                 at = n;
                 if (!alive) break;
                 const int s = ring.idx, ts = tring.idx;
-                if (!mbar_wait<WUDA_STYLE_MMA>(full_kv + s * 8, ring.phase, abort_flag, p.status, kDevTimeoutFullKv))
+                if (!mbar_wait(full_kv + s * 8, ring.phase, abort_flag, p.status, kDevTimeoutFullKv))
                     break;
-                if (!mbar_wait<WUDA_STYLE_MMA>(empty_tm + ts * 8, tring.phase ^ 1u, abort_flag, p.status,
+                if (!mbar_wait(empty_tm + ts * 8, tring.phase ^ 1u, abort_flag, p.status,
                                                kDevTimeoutEmptyTmem))
                     break;
                 tc_fence_after();
@@ -400,7 +396,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
                 tring.step(kIssuers, kTmemStages);
             }
             if (alive && ntiles > 0 && at < ntiles - 1)
-                advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, on_enter);
+                advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, p.max_ctx, on_enter);
         }
     } else if (warp >= kFirstMathWarp) {
         // ------------------------------------------------------------ math warps
@@ -422,11 +418,15 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
             }
             qs = qc & 1;
             if (alive)
-                alive = mbar_wait_warp_fast<WUDA_STYLE_MATH>(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status,
+                alive = mbar_wait_warp_fast(full_q + qs * 8, (qc >> 1) & 1, abort_flag, p.status,
                                                              kDevTimeoutFullQ);
             ++qc;
 #pragma unroll
-            for (int i = 0; i < NEXT_N; ++i) ctx_row[i] = __ldg(p.context_lens + c.b * NEXT_N + i);
+            for (int i = 0; i < NEXT_N; ++i) {
+                const int raw = __ldg(p.context_lens + c.b * NEXT_N + i);
+                ctx_row[i] = clamp_ctx(raw, p.max_ctx);
+                if (raw > p.max_ctx && p.status) atomicCAS(p.status, 0, kDevBadContextLen);
+            }
         };
         Ring ring, tring;
         int at = 0;
@@ -434,14 +434,14 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
         ring.step(wg, S);
         tring.step(wg, kTmemStages);
         for (int n = wg; n < ntiles && alive; n += kMathGroups) {
-            advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, on_enter);
+            advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, p.max_ctx, on_enter);
             at = n;
             if (!alive) break;
             const int s = ring.idx, ts = tring.idx;
             // full_tm completes after the UMMAs that read key stage s retired, and those
             // were issued after the stage's copies had landed: one wait covers the
             // accumulator and the stage's scales.
-            alive = mbar_wait_warp_fast<WUDA_STYLE_MATH>(full_tm + ts * 8, tring.phase, abort_flag, p.status,
+            alive = mbar_wait_warp_fast(full_tm + ts * 8, tring.phase, abort_flag, p.status,
                                                          kDevTimeoutFullTmem);
             if (!alive) break;
             tc_fence_after();
@@ -496,7 +496,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
             tring.step(kMathGroups, kTmemStages);
         }
         if (alive && ntiles > 0 && at < ntiles - 1)
-            advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, on_enter);
+            advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, p.max_ctx, on_enter);
     }
 
     __syncthreads();
@@ -596,6 +596,11 @@ extern "C" int wuda_mqa_logits_fp8(const void* q, const void* kv_pages, const fl
     p.num_blocks = num_blocks;
     p.epb = entries_per_block;
     p.bt_stride = block_table_stride;
+    {
+        const int64_t by_table = static_cast<int64_t>(block_table_stride) * entries_per_block;
+        const int64_t cap = logits_stride < by_table ? logits_stride : by_table;
+        p.max_ctx = static_cast<int>(cap < 0x7fffff00 ? cap : 0x7fffff00);
+    }
     // As many key stages as shared memory allows (a stage = 128 tokens = 16.5 KB), in
     // multiples of kStageQuantum: a stage must always be filled by the same producer,
     // read by the same issuer and released by the same math group, because a parity

@@ -11,9 +11,6 @@
 #include <cuda_runtime.h>
 
 namespace wuda {
-#ifdef WUDA_COUNT_POLLS
-__device__ unsigned long long g_polls[64];
-#endif
 
 // ---------------------------------------------------------------- status codes
 // Written (first writer wins) to the int32 status word a kernel is given.
@@ -26,6 +23,7 @@ enum DeviceStatus : int {
     kDevTimeoutFullTmem = 105,
     kDevTimeoutEmptyTmem = 106,
     kDevBadPageIndex = 110,
+    kDevBadContextLen = 111,        // a context length beyond the logits row / block-table row was cut to fit
     kDevTimeoutGemmFull = 121,
     kDevTimeoutGemmEmpty = 122,
     kDevTimeoutGemmTmemFull = 123,
@@ -90,17 +88,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-#if defined(WUDA_TRYWAIT_HINT_NS) && WUDA_TRYWAIT_HINT_NS > 0
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(WUDA_TRYWAIT_HINT_NS))
-        : "memory");
-#else
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
@@ -110,10 +97,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
-#endif
-#ifdef WUDA_COUNT_POLLS
-    if (blockIdx.x == 0) atomicAdd(&g_polls[(threadIdx.x >> 5) * 2 + (ok ? 0 : 1)], 1ull);
-#endif
     return ok != 0;
 }
 
@@ -139,54 +122,29 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
     }
     return true;
 }
-#ifndef WUDA_SLEEP_NS
-#define WUDA_SLEEP_NS 200
-#endif
-template <int STYLE = 1>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status_word, int code) {
-    if (STYLE == 0) {
+#pragma unroll 1
+    for (uint32_t spins = 0; spins < 4096u; ++spins)
         if (mbar_try_wait(bar, parity)) return true;
-        return mbar_wait_slow(bar, parity, abort_flag, status_word, code);
-    } else if (STYLE == 3) {   // one poll, one pause, then poll hot
-        if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(WUDA_SLEEP_NS);
-#pragma unroll 1
-        for (uint32_t spins = 0; spins < 4096u; ++spins)
-            if (mbar_try_wait(bar, parity)) return true;
-        return mbar_wait_slow(bar, parity, abort_flag, status_word, code);
-    } else if (STYLE == 4) {   // pause between all polls
-#pragma unroll 1
-        for (uint32_t spins = 0; spins < 4096u; ++spins) {
-            if (mbar_try_wait(bar, parity)) return true;
-            __nanosleep(WUDA_SLEEP_NS);
-        }
-        return mbar_wait_slow(bar, parity, abort_flag, status_word, code);
-    } else {
-#pragma unroll 1
-        for (uint32_t spins = 0; spins < 4096u; ++spins)
-            if (mbar_try_wait(bar, parity)) return true;
-        return mbar_wait_slow(bar, parity, abort_flag, status_word, code);
-    }
+    return mbar_wait_slow(bar, parity, abort_flag, status_word, code);
 }
 
 // Warp-uniform forms, so that all 32 lanes take the same branch afterwards (callers use
 // full-mask shuffles and __syncwarp).  `_warp`: every lane polls (each lane that later
 // reads data written by the async proxy must observe the barrier itself), then votes.
 // `_lane0`: only lane 0 polls and the result is broadcast.
-template <int STYLE = 1>
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
                                                volatile int* abort_flag, int* status_word,
                                                int code) {
-    const bool ok = mbar_wait<STYLE>(bar, parity, abort_flag, status_word, code);
+    const bool ok = mbar_wait(bar, parity, abort_flag, status_word, code);
     return __all_sync(0xffffffffu, ok);
 }
-template <int STYLE = 1>
 __device__ __forceinline__ bool mbar_wait_lane0(uint32_t bar, uint32_t parity,
                                                 volatile int* abort_flag, int* status_word,
                                                 int code) {
     int ok = 1;
-    if (lane_id() == 0) ok = mbar_wait<STYLE>(bar, parity, abort_flag, status_word, code) ? 1 : 0;
+    if (lane_id() == 0) ok = mbar_wait(bar, parity, abort_flag, status_word, code) ? 1 : 0;
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
@@ -376,12 +334,11 @@ __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
 // Warp-wide wait whose common case (phase already complete) costs one poll and one
 // vote: all lanes test the barrier together; only when that fails does lane 0 take the
 // polling loop and broadcast the outcome.
-template <int STYLE = 1>
 __device__ __forceinline__ bool mbar_wait_warp_fast(uint32_t bar, uint32_t parity,
                                                     volatile int* abort_flag, int* status_word,
                                                     int code) {
     if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
-    return mbar_wait_lane0<STYLE>(bar, parity, abort_flag, status_word, code);
+    return mbar_wait_lane0(bar, parity, abort_flag, status_word, code);
 }
 
 __device__ __forceinline__ void tmem_ld_wait() {

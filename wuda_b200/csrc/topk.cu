@@ -363,17 +363,6 @@ __device__ __forceinline__ void classify_pass(const float* row, int lo, int hi, 
     }
 }
 
-#ifdef WUDA_TOPK_TIMING
-// Development aid, compiled only on request: cycle stamps of the phases of CTA 0's first row.
-__device__ long long g_phase_clock[16];
-#define WUDA_STAMP(i)                                                    \
-    do {                                                                 \
-        if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[i] = clock64(); \
-    } while (0)
-#else
-#define WUDA_STAMP(i) ((void)0)
-#endif
-
 __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
     pdl_launch_dependents();
     pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
@@ -411,7 +400,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
         }
 
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
-        WUDA_STAMP(0);
         zero_hist(s, kBins);
         if (threadIdx.x == 0) {
             s.out_count = 0;
@@ -448,29 +436,24 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
                     }
                 }
             }
-            WUDA_STAMP(1);
 #pragma unroll
             for (int e = 0; e < 8; ++e)
                 if ((valid >> e) & 1u) atomicAdd(&s.hist[key[e] >> 20], 1u);
             __syncthreads();
-            WUDA_STAMP(2);
             find_threshold(s, kBins, static_cast<uint32_t>(k));
             const uint32_t d1 = s.sel_digit;
             const uint32_t need1 = static_cast<uint32_t>(k) - s.sel_above;
             __syncthreads();
-            WUDA_STAMP(3);
             zero_hist(s, kBins);
             __syncthreads();
 #pragma unroll
             for (int e = 0; e < 8; ++e)
                 if (((valid >> e) & 1u) && (key[e] >> 20) == d1) atomicAdd(&s.hist[(key[e] >> 8) & 0xFFFu], 1u);
             __syncthreads();
-            WUDA_STAMP(4);
             find_threshold(s, kBins, need1);
             const uint32_t d2 = s.sel_digit;
             const uint32_t need2 = need1 - s.sel_above;
             __syncthreads();
-            WUDA_STAMP(5);
             zero_hist(s, 256);
             __syncthreads();
             const uint32_t prefix24 = (d1 << 12) | d2;
@@ -478,14 +461,12 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
             for (int e = 0; e < 8; ++e)
                 if (((valid >> e) & 1u) && (key[e] >> 8) == prefix24) atomicAdd(&s.hist[key[e] & 0xFFu], 1u);
             __syncthreads();
-            WUDA_STAMP(6);
             find_threshold(s, 256, need2);
             const uint32_t d3 = s.sel_digit;
             need3 = need2 - s.sel_above;
             thr = (prefix24 << 8) | d3;
             take_all_equal = (s.hist[d3] == need3);
             __syncthreads();
-            WUDA_STAMP(7);
             uint32_t mask = 0;
 #pragma unroll
             for (int e = 0; e < 8; ++e)
@@ -505,7 +486,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
             __syncthreads();
             if (threadIdx.x == 0) s.out_count = total;
             __syncthreads();
-            WUDA_STAMP(8);
             done = true;
         }
         if (sampled) {
@@ -706,7 +686,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
             }
         }
         __syncthreads();
-        WUDA_STAMP(10);
     }
 }
 
@@ -773,9 +752,3 @@ extern "C" int wuda_topk(const float* scores, const int32_t* seq_lens, const int
     WUDA_CUDA(cudaLaunchKernelEx(&cfg, topk_kernel, p));
     return WUDA_OK;
 }
-
-#ifdef WUDA_TOPK_TIMING
-extern "C" int wuda_topk_phase_clocks(long long* out16) {
-    return cudaMemcpyFromSymbol(out16, wuda::topk::g_phase_clock, sizeof(long long) * 16) == cudaSuccess ? 0 : 3;
-}
-#endif

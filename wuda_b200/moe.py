@@ -59,8 +59,8 @@ class EP2Link:
     torch.distributed once); `loopback=True` makes the rank its own peer (one GPU: y = local + local),
     `mute=True` gives a peer that never answers (time-out path)."""
 
-    def __init__(self, max_tokens, dim, group=None, peer_handle=None, loopback=False, mute=False):
-        self.max_tokens, self.dim = max_tokens, dim
+    def __init__(self, max_tokens, dim, group=None, peer_handle=None, loopback=False, mute=False, device_sequence=False):
+        self.max_tokens, self.dim, self.device_sequence = max_tokens, dim, device_sequence
         self.nbytes = lib.wuda_moe_ep2_inbox_bytes(max_tokens, dim)
         if self.nbytes <= 0:
             raise ValueError("unsupported (max_tokens, dim) for the exchange buffer")
@@ -159,7 +159,7 @@ class MoERunner:
             self.link.epoch += 1
             check(lib.wuda_moe_combine_ep2(self.out.data_ptr(), self.pair_row.data_ptr(), shared_ptr, y.data_ptr(), m,
                                            self.topk, w.dim, self.link._local, self.link._peer, self.link.max_tokens,
-                                           self.link.epoch, int(self.peer_wait_ms), st, s))
+                                           0 if self.link.device_sequence else self.link.epoch, int(self.peer_wait_ms), st, s))
         return y
 
 

@@ -698,9 +698,11 @@ class TP2Link:
     y = link.fp8_gemm(a_local, a_s, w_local, w_s)   # == bf16(sum over ranks), on both ranks
     """
 
-    def __init__(self, m, n, group=None, peer_handle=None, loopback=False):
+    def __init__(self, m, n, group=None, peer_handle=None, loopback=False, device_sequence=False):
+        """device_sequence: the link numbers its calls on the device (both ranks must choose alike); needed
+        when the call is captured into a CUDA graph and replayed."""
         import ctypes
-        self.m, self.n = m, n
+        self.m, self.n, self.device_sequence = m, n, device_sequence
         self.nbytes = lib.wuda_tp2_inbox_bytes(m, n)
         _require(self.nbytes > 0, "unsupported (m, n) for the exchange buffer")
         self._local, self._peer = ctypes.c_void_p(), ctypes.c_void_p()
@@ -735,7 +737,8 @@ class TP2Link:
         self.epoch += 1
         check(lib.wuda_gemm_fp8_blockscaled_tp2(a.data_ptr(), a_s.data_ptr(), b.data_ptr(), b_s.data_ptr(),
                                                 out.data_ptr(), m, n, k, scratch.data_ptr(), scratch.numel(),
-                                                self._local, self._peer, self.epoch, int(peer_wait_ms),
+                                                self._local, self._peer, 0 if self.device_sequence else self.epoch,
+                                                int(peer_wait_ms),
                                                 status_word.data_ptr() if status_word is not None else None,
                                                 _stream()))
         return out
