@@ -715,7 +715,7 @@ int wuda_gemm_fp8_blockscaled_tp2(const void* a, const float* a_scales, const vo
 /* The same GEMM for callers that cannot provide scratch memory and must not trigger a device
  * allocation (a process that has handed all device memory to its own pool, a loop in which
  * cudaMalloc would stall the device).  No counterpart in the reference.  The scratch is a fixed
- * 6,292,224-byte array inside the library's device image, present on every GPU that loads the
+ * 6,292,480-byte array inside the library's device image, present on every GPU that loads the
  * library until the process exits; the entry point allocates nothing and frees nothing.
  * Limits and rules: m <= 64 (larger m is refused with WUDA_ERR_UNSUPPORTED); calls on one
  * device share the array, so they must not overlap on the GPU (issue them on one stream, or

@@ -429,6 +429,45 @@ def moe_swiglu(h_bf16, row_weight, limit):
     return f32_to_bf16((np.asarray(row_weight, np.float32)[:, None] * (silu * up).astype(np.float32)).astype(np.float32))
 
 
+def moe_block(x_bf16, gate_w_bf16, gate_bias, w1_bf16, w3_bf16, w2_bf16, k, score_func=2, route_scale=1.0,
+              swiglu_limit=0.0, shared=True):
+    """The structure of the origin's MoE.forward (dsv4_megakernel/origin/model.py:629-644) with Gate.forward
+    (:563-584) and Expert.forward (:596-606) on bf16 weights, in numpy: router on fp32 copies (the bias shifts the
+    selection, not the weights), every selected expert's bf16 projections w1 / w3 -> fp32 SwiGLU (clamped when
+    swiglu_limit > 0) times the routing weight -> bf16 -> w2 -> bf16, summed over a token's experts in fp32 in
+    expert order; the shared expert (last entry of w1 / w3 / w2 when `shared`) is added to that sum and the
+    result is cast to bf16 once.  All tensors are uint16 bf16 bit patterns; w* are [E(+1), out, in].
+    Returns (y uint16 [tokens, dim], routing weights fp32 [tokens, k], indices int32 [tokens, k])."""
+    x = bf16_to_f32(_c(x_bf16, np.uint16))
+    gw = bf16_to_f32(_c(gate_w_bf16, np.uint16))
+    w1, w3, w2 = (bf16_to_f32(_c(w, np.uint16)) for w in (w1_bf16, w3_bf16, w2_bf16))
+    experts = gw.shape[0]
+    logits = (x.astype(np.float64) @ gw.astype(np.float64).T).astype(np.float32)
+    rw, idx = moe_route(logits, gate_bias, k, score_func, route_scale)
+
+    def lin(v, w):      # F.linear on bf16 operands: fp32 (here: double) sum, one rounding to bf16
+        return bf16_to_f32(f32_to_bf16((v.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32)))
+
+    def expert(e, rows, weight):
+        gate, up = lin(x[rows], w1[e]), lin(x[rows], w3[e])
+        if swiglu_limit > 0:
+            up = np.clip(up, -np.float32(swiglu_limit), np.float32(swiglu_limit))
+            gate = np.minimum(gate, np.float32(swiglu_limit))
+        h = (gate / (np.float32(1) + np.exp(-gate, dtype=np.float32))).astype(np.float32) * up
+        if weight is not None:
+            h = weight[:, None] * h
+        return lin(bf16_to_f32(f32_to_bf16(h.astype(np.float32))), w2[e])
+
+    y = np.zeros_like(x)
+    for e in range(experts):
+        rows, slot = np.nonzero(idx == e)
+        if len(rows):
+            y[rows] += expert(e, rows, rw[rows, slot])
+    if shared:
+        y = y + expert(experts, np.arange(x.shape[0]), None)
+    return f32_to_bf16(y.astype(np.float32)), rw, idx
+
+
 def gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=True):
     """a e4m3 bytes [M,K], a_s fp32 [M,K/128], b e4m3 bytes [N,K], b_s fp32 [N/128,K/128].
     Returns uint16 (bf16) or fp32 [M,N]."""

@@ -3,7 +3,7 @@ Python reference functions (imported from a checkout of guluguluhhhh/wuda) on sm
 seeded inputs.  The fixtures store inputs and expected outputs, so the tests need
 neither the checkout nor this script.
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [golden_<name> ...]
 
 Functions used (paths inside the reference repository):
   dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py  ref_fp8_mqa_logits (:207-218); quantize_fp4 (:222-227),
@@ -15,10 +15,16 @@ Functions used (paths inside the reference repository):
   dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py   ref_comp_step (:550-586, fp8 form) and
                                                            ref_win_step (:646-665)
   dsv4_megakernel/megakernel/test/test_hc_fused_tc.py     hc_reference (:115-136)
-  dsv4_megakernel/origin/model.py                         Gate.forward (:563-584)
+  dsv4_megakernel/origin/model.py                         Gate.forward (:563-584); Gate, Expert, MoE (:546-644) for
+                                                           the whole MoE block on bf16 weights
   dsv4_megakernel/megakernel/test/kv_cache_manager.py     KVCacheManager (:53-257), run on the CPU
 The first two are written for device="cuda"; they are run here on the CPU by mapping that one
 keyword to "cpu", which changes no arithmetic.
+
+Two of the reference's twins are not callable: they stand inline in GPU tests.  Their formulas are restated
+here, statement by statement, and run on seeded CPU inputs:
+  dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py:404-413   query RMSNorm + RoPE (golden_query_rms_rope)
+  dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py:772-791   MAIN compressor row (golden_main_compressor)
 """
 import importlib.util
 import os
@@ -341,6 +347,116 @@ def golden_moe_gate(ref_root):
     print("moe_gate_256.npz", tuple(weights.shape))
 
 
+def golden_query_rms_rope():
+    """The inline twin of the fused query tail (test_mqa_logits_fp4.py:404-413): per head row of 512,
+    x * rsqrt(mean x^2 + eps) without a weight, the last 64 dims rotated in interleaved pairs at the token's
+    position, one rounding to bf16 at the end; input_heads 64 repeats the heads to 128 (here 4 -> 8)."""
+    g = torch.Generator().manual_seed(91)
+    batch, eps, max_pos = 5, 1e-6, 64
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float32), 1.0 / (10000.0 ** (torch.arange(32) / 32.0)))
+    cos_tab, sin_tab = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    positions = torch.tensor([0, 1, 17, 40, 63])
+    out = dict(cos=cos_tab.numpy(), sin=sin_tab.numpy(), positions=positions.numpy(), eps=eps)
+    for name, input_heads, out_heads in (("full", 8, 8), ("half", 4, 8)):
+        query_x = (torch.randn(batch, input_heads, 512, generator=g) *
+                   torch.tensor([1.0, 0.02, 30.0, 1.0, 5.0]).view(batch, 1, 1)).bfloat16()
+        source = query_x if input_heads == out_heads else query_x.repeat(1, out_heads // input_heads, 1)
+        source_f = source.float()
+        ref = source_f * torch.rsqrt(source_f.square().mean(-1, keepdim=True) + eps)
+        even, odd = ref[..., 448::2].clone(), ref[..., 449::2].clone()
+        cos = cos_tab[positions, None, :]
+        sin = sin_tab[positions, None, :]
+        ref[..., 448::2] = even * cos - odd * sin
+        ref[..., 449::2] = even * sin + odd * cos
+        out["x_" + name], out["out_" + name] = _u16(query_x), _u16(ref.bfloat16())
+    np.savez_compressed(os.path.join(HERE, "query_rms_rope.npz"), **out)
+    print("query_rms_rope.npz", tuple(out["out_half"].shape))
+
+
+def golden_main_compressor():
+    """The inline twin of the MAIN compressor row (test_mqa_logits_fp4.py:772-791): softmax-weighted sum over
+    the eight ring rows that end at the current one (rows 0..3 of the window read columns [0, 512), rows 4..7
+    columns [512, 1024) of the kv and score halves), bf16, RMSNorm(512) with an fp32 weight, bf16, RoPE of the
+    last 64 dims at position pos + 1 - 4, and the power-of-two scale per 64 of the first 448 values.  Stored:
+    the twin's pre-quantisation values, its scales and its rotary tail."""
+    g = torch.Generator().manual_seed(93)
+    B, S = 10, 64
+    ang = torch.outer(torch.arange(S, dtype=torch.float32), 1.0 / (10000.0 ** (torch.arange(32) / 32.0)))
+    cos_tab, sin_tab = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    pos = torch.tensor([3, 4, 7, 11, 15, 19, 30, 31, 47, 63])
+    comp_state = torch.randn(B, 8, 2048, generator=g)
+    comp_state[2, :, 1024:] *= 6.0                                    # a peaked softmax
+    comp_state[3] *= torch.tensor(0.01)                               # small values: the 1e-4 scale floor
+    comp_norm = torch.rand(512, generator=g) + 0.5
+    state_rows = torch.arange(B) * 8 + pos % 8
+    idx = torch.arange(512)
+    blk_all, scale_all, rope_all = torch.zeros(B, 448), torch.full((B, 7), -1.0), torch.zeros(B, 64)
+    mask = torch.zeros(B, dtype=torch.bool)
+    for m in range(B):
+        p = int(pos[m])
+        if (p + 1) % 4 != 0:
+            continue
+        mask[m] = True
+        current = int(state_rows[m]) % 8
+        perm = [(current - 7 + r) % 8 for r in range(8)]
+        kv0, sc0 = comp_state[m, :, :1024], comp_state[m, :, 1024:]
+        col = torch.stack([idx if r < 4 else idx + 512 for r in range(8)])
+        sc8 = torch.gather(sc0[perm], 1, col)
+        kv8 = torch.gather(kv0[perm], 1, col)
+        e = torch.exp(sc8 - sc8.max(0).values)
+        agg = (e * kv8).sum(0) / e.sum(0)
+        vb = agg.bfloat16().float()
+        rms = torch.rsqrt((vb * vb).sum() / 512.0 + 1e-6)
+        ro = (vb * rms * comp_norm).bfloat16().float()
+        ri = p + 1 - 4
+        ev, ov = ro[448::2].clone(), ro[449::2].clone()
+        ro[448::2] = (ev * cos_tab[ri] - ov * sin_tab[ri]).bfloat16().float()
+        ro[449::2] = (ev * sin_tab[ri] + ov * cos_tab[ri]).bfloat16().float()
+        blk = ro[:448].view(7, 64)
+        scale_ref = torch.pow(2.0, (blk.abs().max(1).values / 448.0).clamp_min(1e-4).log2().ceil())
+        blk_all[m], scale_all[m], rope_all[m] = ro[:448], scale_ref, ro[448:]
+    np.savez_compressed(os.path.join(HERE, "main_compressor_fp8.npz"), state=comp_state.numpy(), pos=pos.numpy(),
+                        state_row=state_rows.numpy(), norm_w=comp_norm.numpy(), cos=cos_tab.numpy(), sin=sin_tab.numpy(),
+                        values=blk_all.numpy(), scale=scale_all.numpy(), rope=_u16(rope_all.bfloat16()),
+                        compress=mask.numpy())
+    print("main_compressor_fp8.npz", int(mask.sum()), "compress rows of", B)
+
+
+def golden_moe_block(ref_root):
+    """The origin's MoE module (Gate + routed Experts + shared Expert, origin/model.py:546-644) on bf16
+    weights, world_size 1, run on the CPU: the block structure (selection with a bias, weights without it,
+    fp32 accumulation over experts, the shared expert added last, one cast at the end) that the NVFP4 / FP8
+    arithmetic of this library is laid over.  The weights are exactly representable in bf16."""
+    import types
+    model = _load(ref_root, "dsv4_megakernel/origin/model.py", "ref_origin_model_moe")
+    model.torch = torch
+    g = torch.Generator().manual_seed(97)
+    tokens, dim, inter, experts, topk = 9, 256, 256, 8, 3
+    out = {}
+    for name, limit in (("plain", 0.0), ("limit", 1.5)):
+        args = types.SimpleNamespace(dim=dim, moe_inter_dim=inter, n_routed_experts=experts, n_shared_experts=1,
+                                     n_activated_experts=topk, score_func="sqrtsoftplus", route_scale=2.5, n_hash_layers=0,
+                                     vocab_size=16, expert_dtype=None, swiglu_limit=limit)
+        with model.set_dtype(torch.bfloat16):
+            block = model.MoE(1, args)
+        bf = lambda *s, scale: (torch.randn(*s, generator=g) * scale).bfloat16()
+        block.gate.weight.data = bf(experts, dim, scale=0.08).float()
+        block.gate.bias.data = torch.randn(experts, generator=g) * 0.05
+        w1, w3, w2 = bf(experts + 1, inter, dim, scale=0.08), bf(experts + 1, inter, dim, scale=0.08), bf(experts + 1, dim, inter, scale=0.08)
+        for e, mod in enumerate(list(block.experts) + [block.shared_experts]):
+            mod.w1.weight.data, mod.w3.weight.data, mod.w2.weight.data = w1[e].clone(), w3[e].clone(), w2[e].clone()
+        x = (torch.randn(tokens, dim, generator=g) * 1.5).bfloat16()
+        with torch.no_grad():
+            y = block(x.view(1, tokens, dim), torch.zeros(1, tokens, dtype=torch.long)).view(tokens, dim)
+            weights, indices = block.gate(x, None)
+        out.update({"x_" + name: _u16(x), "gate_w_" + name: _u16(block.gate.weight.data.bfloat16()),
+                    "gate_bias_" + name: block.gate.bias.data.numpy(), "w1_" + name: _u16(w1), "w3_" + name: _u16(w3),
+                    "w2_" + name: _u16(w2), "y_" + name: _u16(y), "indices_" + name: indices.numpy().astype(np.int32),
+                    "weights_" + name: weights.float().numpy(), "limit_" + name: limit})
+    np.savez_compressed(os.path.join(HERE, "moe_block_origin.npz"), topk=topk, route_scale=2.5, **out)
+    print("moe_block_origin.npz", tuple(y.shape))
+
+
 KV_TRACE_CONFIGS = [
     dict(capacity=5, pages_per_pool=96, max_pages_per_req=12),
     dict(capacity=5, pages_per_pool=96, max_pages_per_req=12, state_ring_entries=16),
@@ -419,6 +535,12 @@ def main():
     if len(sys.argv) < 2 and "WUDA_REFERENCE_ROOT" not in os.environ:
         sys.exit("usage: make_golden.py <path to a checkout of the reference>  (or set WUDA_REFERENCE_ROOT)")
     ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ["WUDA_REFERENCE_ROOT"]
+    only = set(sys.argv[2:])          # optional: names of single generators, e.g. `golden_moe_block`
+    if only:
+        for name in sorted(only):
+            fn = globals()[name]
+            fn(ref_root) if fn.__code__.co_argcount else fn()
+        return
     tdir = "dsv4_megakernel/megakernel/test"
     ref_mqa = _load(ref_root, tdir + "/test_mqa_logits_fp4.py", "ref_mqa")
     golden_mqa(ref_mqa, "mqa_logits_fp8_n1.npz", batch=3, next_n=1, ctx_lo=1, ctx_hi=400, epb=64, seed=11)
@@ -435,6 +557,9 @@ def main():
     golden_mhc_pre(ref_root)
     golden_moe_gate(ref_root)
     golden_sparse_mla(ref_root)
+    golden_query_rms_rope()
+    golden_main_compressor()
+    golden_moe_block(ref_root)
 
 
 if __name__ == "__main__":

@@ -299,3 +299,56 @@ def test_mqa_logits_fp4_oracle_matches_reference_twin():
     valid = np.isfinite(ref)
     assert np.array_equal(np.isfinite(got), valid)
     assert np.max(np.abs(got[valid] - ref[valid])) <= 1e-5 * np.sqrt(np.mean(ref[valid].astype(np.float64) ** 2))
+
+
+def test_query_rms_rope_oracle_matches_the_reference_twin():
+    """Fixture from the reference's inline twin of the fused query tail (test_mqa_logits_fp4.py:404-413,
+    restated in tests/golden/make_golden.py): bit-exact on both head layouts up to the twin's own libm
+    (torch's rsqrt against 1/sqrt: the last bf16 bit of a few values)."""
+    g = load_golden("query_rms_rope.npz")
+    for name, out_heads in (("full", 8), ("half", 8)):
+        got = oracle.query_rms_rope(g["x_" + name], g["positions"], g["cos"], g["sin"], out_heads=out_heads,
+                                    eps=float(g["eps"]))
+        want = g["out_" + name]
+        d = np.abs(got.astype(np.int32) - want.astype(np.int32))
+        assert d.max() <= 1 and np.mean(d == 0) >= 0.999, (name, int(d.max()), float(np.mean(d == 0)))
+
+
+def test_main_compressor_oracle_matches_the_reference_twin():
+    """Fixture from the reference's inline twin of the MAIN compressor row (test_mqa_logits_fp4.py:772-791):
+    scales exact, e4m3 codes those of the twin's values, rotary tail within one bf16 step (the twin's own GPU
+    check allows 1e-2 / 0.15 / 0.05 because its kernel is built with fast-math)."""
+    g = load_golden("main_compressor_fp8.npz")
+    q8, s8, rope = oracle.main_compressor_fp8(g["state"], g["state_row"], g["pos"], g["norm_w"], g["cos"], g["sin"])
+    rows = np.nonzero(g["compress"])[0]
+    assert len(rows) == 8
+    for r in range(len(g["pos"])):
+        if not g["compress"][r]:
+            assert (q8[r] == 0xAB).all() and (s8[r] == -1).all()
+    assert np.array_equal(s8[rows], g["scale"][rows])
+    want_q = oracle.e4m3_encode((g["values"][rows].reshape(-1, 7, 64) / g["scale"][rows][:, :, None]).reshape(-1, 448))
+    same = q8[rows] == want_q
+    assert same.mean() >= 0.995, float(same.mean())
+    deq = oracle.e4m3_decode(q8[rows]).reshape(-1, 7, 64) * s8[rows][:, :, None]
+    assert np.all(np.abs(deq.reshape(-1, 448) - g["values"][rows]) <=
+                  np.abs(g["values"][rows]) * 2.0 ** -3 + np.repeat(s8[rows], 64, axis=1) * 2.0 ** -9)
+    d = np.abs(rope[rows].astype(np.int32) - g["rope"][rows].astype(np.int32))
+    assert d.max() <= 1 and np.mean(d == 0) >= 0.99
+
+
+@pytest.mark.parametrize("name", ["plain", "limit"])
+def test_moe_block_oracle_matches_the_origin_module(name):
+    """Fixture from the origin's MoE module (Gate, Experts, shared Expert, origin/model.py:546-644) on bf16
+    weights: same experts selected, same routing weights, and the block output within two bf16 steps of the
+    largest term (torch sums a projection in fp32, the oracle in double: single roundings differ)."""
+    g = load_golden("moe_block_origin.npz")
+    y, rw, idx = oracle.moe_block(g["x_" + name], g["gate_w_" + name], g["gate_bias_" + name], g["w1_" + name],
+                                  g["w3_" + name], g["w2_" + name], int(g["topk"]), 2, float(g["route_scale"]),
+                                  float(g["limit_" + name]))
+    assert np.array_equal(np.sort(idx, axis=1), np.sort(g["indices_" + name], axis=1))
+    order = np.argsort(idx, axis=1), np.argsort(g["indices_" + name], axis=1)
+    assert np.allclose(np.take_along_axis(rw, order[0], 1), np.take_along_axis(g["weights_" + name], order[1], 1),
+                       rtol=2e-6, atol=1e-7)
+    got, want = oracle.bf16_to_f32(y), oracle.bf16_to_f32(g["y_" + name])
+    assert np.all(np.abs(got - want) <= 2.0 ** -7 * np.abs(want) + 2.0 ** -8 * np.abs(want).max())
+    assert np.mean(y == g["y_" + name]) >= 0.9

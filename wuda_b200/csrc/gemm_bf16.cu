@@ -42,6 +42,7 @@ __host__ __device__ constexpr int first_epi_warp_for(int m_pad) { return (produc
 __host__ __device__ constexpr int threads_for(int m_pad) { return 32 * (first_epi_warp_for(m_pad) + kEpiWarps); }
 constexpr int kWBytes = kTileN * kRowBytes;   // 16 KB
 constexpr int kMaxGrid = 192;
+constexpr int64_t kFlagBytes = 1024;   // the flags lead the scratch: calls of any row count find them in the same place
 
 struct Params {
     void* c;                   // bf16 or fp32 [M, N]
@@ -371,7 +372,7 @@ extern "C" int64_t wuda_gemm_bf16_scratch_bytes(int m, int n) {
     if (m < 1 || n < 1 || m > 128) return -1;
     int m_pad = 16;
     while (m_pad < m) m_pad *= 2;
-    return static_cast<int64_t>(wuda::gemm16::kMaxGrid) * m_pad * 128 * 4 + wuda::gemm16::kMaxGrid * 4;
+    return wuda::gemm16::kFlagBytes + static_cast<int64_t>(wuda::gemm16::kMaxGrid) * m_pad * 128 * 4;
 }
 
 extern "C" int wuda_gemm_bf16(const void* a_bf16, const void* w_bf16, void* c, int c_is_fp32, int m, int n, int k,
@@ -405,8 +406,8 @@ extern "C" int wuda_gemm_bf16(const void* a_bf16, const void* w_bf16, void* c, i
     p.N = n;
     p.kb = k / kBlockK;
     p.n_tiles = (n + 127) / 128;
-    p.scratch = static_cast<float*>(scratch);
-    p.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
+    p.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + kFlagBytes);
+    p.flags = static_cast<int32_t*>(scratch);
     p.stages = 0;
 
     CUtensorMap w_map, a_map;

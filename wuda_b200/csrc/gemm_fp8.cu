@@ -622,15 +622,18 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p,
 }  // namespace gemm8
 }  // namespace wuda
 
-// Scratch = one fp32 partial tile [M_PAD][128] per CTA, then one flag per CTA.  The grid
-// never exceeds kMaxGrid CTAs (one per SM).
+// Scratch = one flag per CTA (the first kFlagBytes bytes), then one fp32 partial tile [M_PAD][128] per CTA.
+// The grid never exceeds kMaxGrid CTAs (one per SM).  The flags come first so that calls with different row
+// counts, which size their slots differently, find them in the same place: one scratch buffer can then serve
+// every GEMM of a stream without a slot of one call ever covering the flags of another.
 constexpr int kMaxGrid = 192;
+constexpr int64_t kFlagBytes = 1024;
 
 extern "C" int64_t wuda_gemm_fp8_scratch_bytes(int m, int n) {
     if (m < 1 || n < 1 || m > 256) return -1;
     int m_pad = 16;
     while (m_pad < m) m_pad *= 2;
-    return static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4 + kMaxGrid * 4;
+    return kFlagBytes + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4;
 }
 
 namespace {
@@ -760,13 +763,11 @@ int gemm_fp8_entry(const void* a, const float* a_scales, const void* w, const fl
                               static_cast<__nv_bfloat16*>(c_bf16) + static_cast<int64_t>(128) * n_all, m - 128, n, k,
                               groups, scratch, scratch_bytes, status_word, stream);
     }
-    int m_pad = 16;
-    while (m_pad < m) m_pad *= 2;
     GemmCall g;
     g.a = a, g.a_scales = a_scales, g.w = w, g.w_scales = w_scales, g.c = c_bf16;
     g.m = m, g.n = n, g.k = k, g.groups = groups;
-    g.slots = static_cast<float*>(scratch);
-    g.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
+    g.flags = static_cast<int32_t*>(scratch);
+    g.slots = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + kFlagBytes);
     g.status = status_word;
     g.stream = static_cast<cudaStream_t>(stream);
     return gemm_fp8_setup_and_launch(g);
@@ -804,11 +805,11 @@ extern "C" int wuda_gemm_fp8_grouped(const void* a, const float* a_scales, const
 // zero; the kernel resets each flag after use, and the entry point clears all of them again
 // before every launch in case an earlier call ended abnormally.  Two calls that overlap on the
 // GPU (different streams) would race on the slots: calls through this entry point must be
-// ordered one after another on the device.  The flags sit at a fixed offset behind the largest
-// slot area, so calls with different m (different slot sizes) share the array without moving them.
+// ordered one after another on the device.  The flags sit at the start of the array, so calls with
+// different m (different slot sizes) share it without moving them.
 constexpr int kNoAllocMaxM = 64;
 constexpr int64_t kNoAllocSlotBytes = static_cast<int64_t>(kMaxGrid) * kNoAllocMaxM * 128 * 4;
-constexpr int64_t kNoAllocScratchBytes = kNoAllocSlotBytes + kMaxGrid * 4;   // 6,292,224 bytes
+constexpr int64_t kNoAllocScratchBytes = kFlagBytes + kNoAllocSlotBytes;   // 6,292,480 bytes
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
@@ -859,8 +860,8 @@ extern "C" int wuda_gemm_fp8_blockscaled_noalloc(const void* a, const float* a_s
     GemmCall g;
     g.a = a, g.a_scales = a_scales, g.w = w, g.w_scales = w_scales, g.c = c_bf16;
     g.m = m, g.n = n, g.k = k;
-    g.slots = static_cast<float*>(scratch);
-    g.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + kNoAllocSlotBytes);
+    g.flags = static_cast<int32_t*>(scratch);
+    g.slots = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + kFlagBytes);
     g.status = status_word;
     g.stream = static_cast<cudaStream_t>(stream);
     // the flags must start at zero whatever the previous call left behind
@@ -952,13 +953,11 @@ extern "C" int wuda_gemm_fp8_blockscaled_tp2(const void* a, const float* a_scale
     WUDA_REQUIRE(scratch_bytes >= need, "scratch holds %lld bytes; %lld are needed (wuda_gemm_fp8_scratch_bytes)",
                  static_cast<long long>(scratch_bytes), static_cast<long long>(need));
     WUDA_REQUIRE(tp_bytes(m, n) > 0, "n is too large for the exchange buffer's flag block");
-    int m_pad = 16;
-    while (m_pad < m) m_pad *= 2;
     GemmCall g;
     g.a = a, g.a_scales = a_scales, g.w = w, g.w_scales = w_scales, g.c = c_bf16;
     g.m = m, g.n = n, g.k = k_local;
-    g.slots = static_cast<float*>(scratch);
-    g.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
+    g.flags = static_cast<int32_t*>(scratch);
+    g.slots = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + kFlagBytes);
     g.status = status_word;
     g.stream = static_cast<cudaStream_t>(stream);
     g.my_inbox = my_inbox, g.peer_inbox = peer_inbox, g.epoch = epoch, g.peer_wait_ms = peer_wait_ms;

@@ -48,6 +48,7 @@ __host__ __device__ constexpr int threads_for(int m_pad) { return 32 * (first_ep
 constexpr int kWBytes = kTileN * kRowBytes;   // 16 KB
 constexpr int kSfBytes = 2048;                // one packed scale block
 constexpr int kMaxGrid = 192;
+constexpr int64_t kFlagBytes = 1024;   // the flags lead the scratch: calls of any row count find them in the same place
 
 struct Params {
     __nv_bfloat16* c;
@@ -201,7 +202,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 const int g_now = tile / p.n_tiles;
                 if (g_now != grp) {
                     grp = g_now;
-                    expert = __ldg(p.group_expert + grp);
+                    expert = __ldcg(p.group_expert + grp);   // written by the dispatch kernel of the same chain
                 }
                 wtile = expert * p.n_tiles + (tile - grp * p.n_tiles);
             } else if (!grouped) {
@@ -375,7 +376,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                         for (int c = blockIdx.x + 1 + et; c <= last; c += 32 * kEpiWarps) p.flags[c] = 0;
                 }
                 if (alive && nrow < p.N) {
-                    const float scale = grouped ? p.out_scale * __ldg(p.expert_scale + __ldg(p.group_expert + grp)) : p.out_scale;
+                    const float scale = grouped ? p.out_scale * __ldg(p.expert_scale + __ldcg(p.group_expert + grp)) : p.out_scale;
                     __nv_bfloat16* c = p.c + static_cast<int64_t>(grp) * M_PAD * p.N;
 #pragma unroll
                     for (int i = 0; i < M_PAD; ++i)
@@ -433,7 +434,7 @@ extern "C" int64_t wuda_gemm_nvfp4_scratch_bytes(int m, int n) {
     if (m < 1 || n < 1 || m > 128) return -1;
     int m_pad = 16;
     while (m_pad < m) m_pad *= 2;
-    return static_cast<int64_t>(wuda::gemm4::kMaxGrid) * m_pad * 128 * 4 + wuda::gemm4::kMaxGrid * 4;
+    return wuda::gemm4::kFlagBytes + static_cast<int64_t>(wuda::gemm4::kMaxGrid) * m_pad * 128 * 4;
 }
 
 extern "C" int wuda_gemm_nvfp4(const void* a, const void* a_sf_packed, float a_global_scale, const void* w,
@@ -470,8 +471,8 @@ extern "C" int wuda_gemm_nvfp4(const void* a, const void* a_sf_packed, float a_g
     p.N = n;
     p.kb = k / 256;
     p.n_tiles = (n + 127) / 128;
-    p.scratch = static_cast<float*>(scratch);
-    p.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
+    p.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + kFlagBytes);
+    p.flags = static_cast<int32_t*>(scratch);
     p.stages = 0;
 
     CUtensorMap w_map, a_map, wsf_map, asf_map;
@@ -552,8 +553,8 @@ extern "C" int wuda_gemm_nvfp4_grouped(const void* a, const void* a_sf_packed, f
     p.N = n;
     p.kb = k / 256;
     p.n_tiles = n / 128;
-    p.scratch = static_cast<float*>(scratch);
-    p.flags = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(scratch) + static_cast<int64_t>(kMaxGrid) * m_pad * 128 * 4);
+    p.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + kFlagBytes);
+    p.flags = static_cast<int32_t*>(scratch);
     p.stages = 0;
     p.group_expert = group_expert;
     p.num_groups = num_groups;

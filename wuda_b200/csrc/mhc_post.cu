@@ -51,11 +51,11 @@ __global__ void __launch_bounds__(kThreads) mhc_post_kernel(Params p) {
     const uint4 xv = __ldcs(p.x + row * p.vectors + vec);
 
     float post[kStreams], comb[kStreams][kStreams];
-    const float4 pv = __ldg(reinterpret_cast<const float4*>(p.post) + row);
+    const float4 pv = __ldcg(reinterpret_cast<const float4*>(p.post) + row);   // written by a kernel of the same chain
     post[0] = pv.x, post[1] = pv.y, post[2] = pv.z, post[3] = pv.w;
 #pragma unroll
     for (int i = 0; i < kStreams; ++i) {
-        const float4 c = __ldg(reinterpret_cast<const float4*>(p.comb) + row * kStreams + i);
+        const float4 c = __ldcg(reinterpret_cast<const float4*>(p.comb) + row * kStreams + i);
         comb[i][0] = c.x, comb[i][1] = c.y, comb[i][2] = c.z, comb[i][3] = c.w;
     }
 

@@ -77,7 +77,8 @@ __global__ void __launch_bounds__(kMixThreads) mhc_pre_mix_kernel(Params p) {
     uint2 raw[kTokensPerCta];
 #pragma unroll
     for (int i = 0; i < kTokensPerCta; ++i)
-        raw[i] = (in && t0 + i < p.m) ? __ldg(reinterpret_cast<const uint2*>(p.x + static_cast<int64_t>(t0 + i) * K + k0))
+        // (coherent load: the streams come from the kernel ahead, which may still be running when this one is launched)
+        raw[i] = (in && t0 + i < p.m) ? __ldcg(reinterpret_cast<const uint2*>(p.x + static_cast<int64_t>(t0 + i) * K + k0))
                                       : make_uint2(0u, 0u);
 #pragma unroll
     for (int i = 0; i < kTokensPerCta; ++i) {

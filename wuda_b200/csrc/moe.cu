@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(256) moe_gather_quant_kernel(GatherParams p) {
         uint32_t packed[2] = {0u, 0u}, sf = 0u;
         if (tok >= 0) {
             const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(tok) * p.K + b * 16);
-            const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+            const uint4 lo = __ldcg(src), hi = __ldcg(src + 1);   // activations of a kernel of the same chain
             const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
             float v[16];
 #pragma unroll

@@ -104,8 +104,8 @@ __device__ __forceinline__ KeyRow load_row(const Params& p, int t, int phys) {
     const uint8_t* page = p.kv_pages + static_cast<int64_t>(phys) * p.page_stride;
     const uint4* row = reinterpret_cast<const uint4*>(page + static_cast<int64_t>(off) * kRowBytes);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) r.k[c] = __ldg(row + c);
-    r.scale = __ldg(reinterpret_cast<const uint32_t*>(page + static_cast<int64_t>(p.epb) * kRowBytes) + off);
+    for (int c = 0; c < 4; ++c) r.k[c] = __ldcg(row + c);   // pool pages may have been written by a kernel of the same chain
+    r.scale = __ldcg(reinterpret_cast<const uint32_t*>(page + static_cast<int64_t>(p.epb) * kRowBytes) + off);
     return r;
 }
 
@@ -134,9 +134,9 @@ __global__ void __launch_bounds__(kThreads) mqa_logits_fp4_kernel(const Params p
         if (tid < kHeads) {
             const uint4* row = reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * kHeads + tid) * kRowBytes);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(sm.query + (c * kHeads + tid) * 16) = __ldg(row + c);
-            qs = __ldg(p.q_scales + static_cast<int64_t>(b) * kHeads + tid);
-            sm.weights[tid] = __ldg(p.weights + static_cast<int64_t>(b) * kHeads + tid);
+            for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(sm.query + (c * kHeads + tid) * 16) = __ldcg(row + c);
+            qs = __ldcg(p.q_scales + static_cast<int64_t>(b) * kHeads + tid);
+            sm.weights[tid] = __ldcg(p.weights + static_cast<int64_t>(b) * kHeads + tid);
         }
         sm.query_scales[(tid & 31) * 4 + (tid >> 5)] = qs;
     }

@@ -166,7 +166,9 @@ __device__ __forceinline__ int fetch_index(const Params& p, int b, int g, int n_
     if (g >= n_total) return -1;
     const bool window = g < n_swa;
     const Pool& pool = window ? p.swa : p.cmp;
-    return __ldg(pool.indices + static_cast<int64_t>(b) * pool.capacity + (window ? g : g - n_swa));
+    // coherent loads here and for the records: the top-k entries, this step's cache records and the query come from
+    // kernels of the same chain, which may still be running when this kernel is launched
+    return __ldcg(pool.indices + static_cast<int64_t>(b) * pool.capacity + (window ? g : g - n_swa));
 }
 
 __device__ __forceinline__ void fetch_key(const Params& p, int g, int n_swa, int idx, int piece, KeyRegs& r, bool* bad) {
@@ -181,9 +183,9 @@ __device__ __forceinline__ void fetch_key(const Params& p, int g, int n_swa, int
     const uint8_t* base = pool.data + static_cast<int64_t>(page) * pool.stride;
     const uint8_t* rec = base + static_cast<int64_t>(off) * kBody;
 #pragma unroll
-    for (int c = 0; c < 7; ++c) r.nope[c] = __ldg(reinterpret_cast<const uint2*>(rec + c * 64) + piece);
-    r.rope = __ldg(reinterpret_cast<const uint4*>(rec + kNope) + piece);
-    r.scales = __ldg(reinterpret_cast<const uint2*>(base + static_cast<int64_t>(pool.epb) * kBody + off * kScaleRec));
+    for (int c = 0; c < 7; ++c) r.nope[c] = __ldcg(reinterpret_cast<const uint2*>(rec + c * 64) + piece);
+    r.rope = __ldcg(reinterpret_cast<const uint4*>(rec + kNope) + piece);
+    r.scales = __ldcg(reinterpret_cast<const uint2*>(base + static_cast<int64_t>(pool.epb) * kBody + off * kScaleRec));
     r.valid = 1;
 }
 
@@ -251,8 +253,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
     pdl_launch_dependents();
     pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
 
-    const int n_swa = p.swa.capacity > 0 ? min(max(__ldg(p.swa.lengths + b), 0), p.swa.capacity) : 0;
-    const int n_cmp = p.cmp.capacity > 0 ? min(max(__ldg(p.cmp.lengths + b), 0), p.cmp.capacity) : 0;
+    const int n_swa = p.swa.capacity > 0 ? min(max(__ldcg(p.swa.lengths + b), 0), p.swa.capacity) : 0;
+    const int n_cmp = p.cmp.capacity > 0 ? min(max(__ldcg(p.cmp.lengths + b), 0), p.cmp.capacity) : 0;
     const int n_total = n_swa + n_cmp;
     // the CTAs of a request that share an output half each take a contiguous run of its key blocks
     const int all_blocks = (n_total + kBlock - 1) / kBlock;
@@ -271,7 +273,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         const int row = i / kQSmemPieces, piece = i % kQSmemPieces;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < p.heads)
-            v = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim +
+            v = __ldcg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim +
                                                      kQTmemChunks * 64) + piece);
         st_shared_v4(base + kOffQ + (piece >> 3) * kQChunk + row * 128 + (((piece & 7) ^ (row & 7)) << 4), bf16x8_to_f16x8(v));
     }
@@ -283,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
             uint32_t w[32];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const uint4 v = bf16x8_to_f16x8(row < p.heads ? __ldg(src + c * 8 + i) : make_uint4(0, 0, 0, 0));
+                const uint4 v = bf16x8_to_f16x8(row < p.heads ? __ldcg(src + c * 8 + i) : make_uint4(0, 0, 0, 0));
                 w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
             }
             tmem_st_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + kColQ + c * 32, w);
