@@ -670,7 +670,7 @@ int wuda_front_emit(const void* y8_bf16, const float* y16_f32, const int64_t* po
  * reference has no NVFP4 GEMM: its fp4_gemm (origin/kernel.py:441-536) is FP8-activation x
  * FP4-weight with 1x32 e8m0 scales; this entry is the 16-element-ue4m3 + per-tensor-fp32 form.
  *
- *   a  uint8 [m, k/2];  w  uint8 [n, k/2];  1 <= m <= 128, k % 256 == 0; 16-byte aligned
+ *   a  uint8 [m, k/2];  w  uint8 [n, k/2];  1 <= m <= 256 (above 128 rows: two passes over the weights), k % 256 == 0; 16-byte aligned
  *   a_sf_packed, w_sf_packed: the ue4m3 scale bytes in tensor-core order: per 128 rows x 256 K one
  *      2048-byte block [K/64 step (4)][row % 32 (32)][row / 32 (4)][scale of the step (4)],
  *      blocks ordered [row tile][k / 256]; rows beyond m / n are zero-padded to a multiple of 128

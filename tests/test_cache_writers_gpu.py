@@ -58,6 +58,31 @@ def test_indexer_compressor_golden(wuda):
     assert np.mean(s == os_) >= 0.9
 
 
+def test_main_compressor_golden(wuda):
+    """The MAIN compressor against the fixture made from the reference's inline twin of the row
+    (test/test_mqa_logits_fp4.py:772-791): state read-only, rows that do not compress untouched, scales equal,
+    e4m3 codes those of the twin's values, rotary tail within one bf16 step.  The twin's own GPU gate is far
+    looser (scale 1e-2, values 0.15, rope 0.05) because its kernel is built with fast-math."""
+    g = load_golden("main_compressor_fp8.npz")
+    rows = len(g["pos"])
+    q8 = torch.full((rows, 448), 0xAB, dtype=torch.uint8, device="cuda")
+    s8 = torch.full((rows, 7), -1.0, device="cuda")
+    rope = torch.zeros((rows, 64), dtype=torch.bfloat16, device="cuda")
+    state = cu(g["state"])
+    before = state.clone()
+    wuda.mqa_compressor_fp8_standalone(cu(g["pos"]), cu(g["norm_w"]), cu(g["cos"]), cu(g["sin"]), state,
+                                       cu(g["state_row"]), 8, q8, s8, rope, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(state, before)
+    m = g["compress"]
+    q, s, r = q8.cpu().numpy(), s8.cpu().numpy(), u16(rope)
+    assert (q[~m] == 0xAB).all() and (s[~m] == -1).all() and (r[~m] == 0).all()
+    assert np.array_equal(s[m], g["scale"][m])
+    want = oracle.e4m3_encode((g["values"][m].reshape(-1, 7, 64) / g["scale"][m][:, :, None]).reshape(-1, 448))
+    close_bytes(q[m], want)
+    close_bf16(r[m], g["rope"][m])
+
+
 def test_window_kv_golden(wuda):
     g = load_golden("window_kv_fp8.npz")
     rows = len(g["pos"])

@@ -44,9 +44,38 @@ def test_ragged_shapes_and_partial_tiles(wuda, m, n, k):
     check(wuda, m, n, k, seed=m + n + k)
 
 
-@pytest.mark.parametrize("n,k", [(24576, 7168), (7168, 16384), (2112, 7168), (4096, 7168)])
-def test_config2_shapes_m64(wuda, n, k):
-    check(wuda, 64, n, k, seed=n % 97)
+CONFIG2_SHAPES = [(24576, 7168), (7168, 16384), (2112, 7168), (4096, 7168)]
+_config2_cases = {}
+
+
+def _config2_case(n, k):
+    """One seeded case per shape, 256 activation rows; smaller M take the first rows."""
+    if (n, k) not in _config2_cases:
+        _config2_cases.clear()                       # one shape at a time: the largest case holds 180 MB
+        _config2_cases[(n, k)] = workloads.make_gemm_fp8_case(256, n, k, seed=n % 101)
+    return _config2_cases[(n, k)]
+
+
+@pytest.mark.parametrize("m", [1, 8, 32, 64, 128, 256])
+@pytest.mark.parametrize("n,k", CONFIG2_SHAPES)
+def test_config2_sweep_every_m_on_every_shape(wuda, n, k, m):
+    """The whole (N, K) x M sweep of the block-scaled decode GEMM: the GPU computes
+    the full product; the oracle checks every row on a sample of 128-column blocks - the first, the last (ragged
+    for N = 2112), and four seeded ones - which is where the stream-K splits, the resident-activation switch and
+    the two-pass path above 128 rows differ between M."""
+    full = _config2_case(n, k)
+    case = dict(a=full["a"][:m], a_s=full["a_s"][:m], w=full["w"], w_s=full["w_s"])
+    got = oracle.bf16_to_f32(run(wuda, case)).astype(np.float64)
+    tiles = (n + 127) // 128
+    rng = np.random.default_rng(n + m)
+    blocks = sorted({0, tiles - 1} | set(rng.integers(0, tiles, size=4).tolist()))
+    for t in blocks:
+        lo, hi = t * 128, min(n, t * 128 + 128)
+        ref = oracle.gemm_fp8_blockscaled(case["a"], case["a_s"], full["w"][lo:hi], full["w_s"][t:t + 1],
+                                          out_bf16=False).astype(np.float64)
+        rms = np.sqrt(np.mean(ref ** 2))
+        err = np.abs(got[:, lo:hi] - ref)
+        assert np.all(err <= 1e-2 * np.abs(ref) + 1e-3 * rms), "block %d: max err %g at rms %g" % (t, err.max(), rms)
 
 
 def test_scratch_is_left_clean_and_results_repeat(wuda):
@@ -60,6 +89,39 @@ def test_scratch_is_left_clean_and_results_repeat(wuda):
     # same scratch reused: a dirty scratch would show up as a changed result
     assert np.mean(first == second) > 0.999 and np.mean(first == third) > 0.999
     assert np.max(np.abs(oracle.bf16_to_f32(second) - f)) <= np.max(np.abs(f)) * 2 ** -7
+
+
+def test_gemm_launched_while_another_kernel_holds_the_sms(wuda):
+    """The stream-K fix-up makes a tile's first CTA wait for the CTAs that hold the rest of its K range, which
+    is only sound while those can become resident.  Here every SM is held by another stream's persistent
+    kernel (the paged MQA logits, one 170 KB CTA per SM, launched back to back) while the GEMMs are launched:
+    their CTAs trickle onto SMs as that kernel's CTAs leave.  Every GEMM must finish with status 0 and the
+    bits of an undisturbed run (the partial sums are added in CTA order whatever the arrival order)."""
+    case = workloads.make_gemm_fp8_case(64, 7168, 4096, seed=77)      # 56 tiles over 148 SMs: most tiles are split
+    a = torch.from_numpy(case["a"]).cuda().view(torch.float8_e4m3fn)
+    w = torch.from_numpy(case["w"]).cuda().view(torch.float8_e4m3fn)
+    a_s, w_s = torch.from_numpy(case["a_s"]).cuda(), torch.from_numpy(case["w_s"]).cuda()
+    status = wuda.device_status_word()
+    quiet = wuda.fp8_gemm(a, a_s, w, w_s, status_word=status).clone()
+    torch.cuda.synchronize()
+    mqa = workloads.make_mqa_case(24, 2, 30000, 60000, seed=5)
+    d = workloads.to_device(mqa)
+    logits = torch.empty((48, mqa["logits_stride"]), dtype=torch.float32, device="cuda")
+    mqa_status = wuda.device_status_word()
+    busy, side = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = [torch.empty_like(quiet) for _ in range(12)]
+    torch.cuda.synchronize()
+    with torch.cuda.stream(busy):
+        for _ in range(40):
+            wuda.mqa_logits_fp8_decode_out(d["q"], d["kv_pages"], d["weights"], d["context_lens"], d["block_table"], None,
+                                           logits, 64, next_n=2, status_word=mqa_status)
+    with torch.cuda.stream(side):
+        for out in outs:
+            wuda.fp8_gemm(a, a_s, w, w_s, out=out, status_word=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(mqa_status.item()) == 0
+    for out in outs:
+        assert torch.equal(out, quiet)
 
 
 def test_exactly_representable_products_are_bit_exact(wuda):

@@ -76,7 +76,7 @@ def test_scale_layout_is_pinned_by_power_of_two_scales(wuda):
     assert np.array_equal(got, ref)
 
 
-@pytest.mark.parametrize("m", [1, 8, 32, 64, 128])
+@pytest.mark.parametrize("m", [1, 8, 32, 64, 128, 200, 256])
 def test_random_every_m(wuda, m):
     check(wuda, m, 512, 1024, seed=m)
 
@@ -86,9 +86,37 @@ def test_ragged_shapes(wuda, m, n, k):
     check(wuda, m, n, k, seed=m + n)
 
 
-@pytest.mark.parametrize("n,k", [(24576, 7168), (7168, 16384), (4096, 7168)])
-def test_config2_shapes_m64(wuda, n, k):
-    check(wuda, 64, n, k, seed=n % 89)
+CONFIG2_SHAPES = [(24576, 7168), (7168, 16384), (2112, 7168), (4096, 7168)]
+_config2_cases = {}
+
+
+def _config2_case(n, k):
+    if (n, k) not in _config2_cases:
+        _config2_cases.clear()
+        _config2_cases[(n, k)] = workloads.make_gemm_nvfp4_case(256, n, k, seed=n % 103)
+    return _config2_cases[(n, k)]
+
+
+@pytest.mark.parametrize("m", [1, 8, 32, 64, 128, 256])
+@pytest.mark.parametrize("n,k", CONFIG2_SHAPES)
+def test_config2_sweep_every_m_on_every_shape(wuda, n, k, m):
+    """Every M of the decode sweep on every (N, K) pair, (2112, 7168) and the two-pass M = 256 included.  The GPU
+    computes the full product; the oracle checks every row on the first, the last and four seeded 128-column
+    blocks."""
+    full = _config2_case(n, k)
+    case = dict(full, a=np.ascontiguousarray(full["a"][:m]), a_sf=full["a_sf"][:m],
+                a_sf_packed=workloads.pack_nvfp4_scales(full["a_sf"][:m]))
+    got = oracle.bf16_to_f32(run(wuda, case)).astype(np.float64)
+    assert got.shape == (m, n)
+    tiles = (n + 127) // 128
+    rng = np.random.default_rng(n + m)
+    for t in sorted({0, tiles - 1} | set(rng.integers(0, tiles, size=4).tolist())):
+        lo, hi = t * 128, min(n, t * 128 + 128)
+        ref = oracle.gemm_nvfp4(case["a"], case["a_sf"], case["a_gs"], np.ascontiguousarray(full["w"][lo:hi]),
+                                np.ascontiguousarray(full["w_sf"][lo:hi]), full["w_gs"], False).astype(np.float64)
+        rms = np.sqrt(np.mean(ref ** 2))
+        err = np.abs(got[:, lo:hi] - ref)
+        assert np.all(err <= 1e-2 * np.abs(ref) + 1e-3 * rms), "block %d: max err %g at rms %g" % (t, err.max(), rms)
 
 
 def test_bad_arguments(wuda):

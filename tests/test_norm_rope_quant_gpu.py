@@ -148,6 +148,20 @@ def test_query_rmsnorm_rope_reference_signature(wuda):
     assert np.allclose(oracle.bf16_to_f32(u16(out)), oracle.bf16_to_f32(two_pass), rtol=2 ** -6, atol=3e-2)
 
 
+@pytest.mark.parametrize("name,input_heads", [("full", 8), ("half", 4)])
+def test_query_rmsnorm_rope_golden(wuda, name, input_heads):
+    """Fixture from the reference's inline twin of the fused query tail (test/test_mqa_logits_fp4.py:404-413):
+    the twin's own gate is max_abs == 0 against its kernel; torch's rsqrt and this kernel's 1 / sqrt may
+    differ in the last bit of a few values, so: within one bf16 step, >= 99.9 % identical."""
+    g = load_golden("query_rms_rope.npz")
+    x = torch.from_numpy(g["x_" + name].view(np.int16)).view(torch.bfloat16).cuda()
+    out = torch.empty(x.size(0), 8, 512, dtype=torch.bfloat16, device="cuda")
+    wuda.rmsnorm_rope_out(x, torch.from_numpy(g["positions"]).cuda(), torch.from_numpy(g["cos"]).cuda(),
+                          torch.from_numpy(g["sin"]).cuda(), out, input_heads, float(g["eps"]))
+    torch.cuda.synchronize()
+    bf16_close(u16(out), g["out_" + name], min_equal=0.999)
+
+
 def test_query_rmsnorm_rope_strided_input_and_head_duplication(wuda):
     """x is read in place from a wider projection output; out head h reads head h % heads."""
     gen = torch.Generator().manual_seed(8)

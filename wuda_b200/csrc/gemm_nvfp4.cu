@@ -431,9 +431,9 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, const CUte
 }  // namespace wuda
 
 extern "C" int64_t wuda_gemm_nvfp4_scratch_bytes(int m, int n) {
-    if (m < 1 || n < 1 || m > 128) return -1;
+    if (m < 1 || n < 1 || m > 256) return -1;
     int m_pad = 16;
-    while (m_pad < m) m_pad *= 2;
+    while (m_pad < m && m_pad < 128) m_pad *= 2;      // above 128 rows: passes of <= 128 rows
     return wuda::gemm4::kFlagBytes + static_cast<int64_t>(wuda::gemm4::kMaxGrid) * m_pad * 128 * 4;
 }
 
@@ -443,12 +443,24 @@ extern "C" int wuda_gemm_nvfp4(const void* a, const void* a_sf_packed, float a_g
     using namespace wuda;
     using namespace wuda::gemm4;
     clear_error();
-    WUDA_REQUIRE(m >= 0 && m <= 128, "m must be in [0, 128] (got %d)", m);
+    WUDA_REQUIRE(m >= 0 && m <= 256, "m must be in [0, 256] (got %d)", m);
     WUDA_REQUIRE(n >= 1, "n must be >= 1 (got %d)", n);
     WUDA_REQUIRE(k >= 256 && k % 256 == 0, "k must be a positive multiple of 256 (got %d)", k);
     if (m == 0) return WUDA_OK;
     WUDA_REQUIRE(a && a_sf_packed && w && w_sf_packed && c_bf16 && scratch,
                  "a, a_sf_packed, w, w_sf_packed, c and scratch must not be NULL");
+    if (m > 128) {
+        // A tile holds at most 128 activation rows (the accumulator's columns): two passes over the weights,
+        // one per 128-row tile of the activations and of their packed scales ([row tile][k / 256][2048 bytes]).
+        int st2 = wuda_gemm_nvfp4(a, a_sf_packed, a_global_scale, w, w_sf_packed, w_global_scale, c_bf16, 128, n, k, scratch,
+                                  scratch_bytes, status_word, stream);
+        if (st2 != WUDA_OK) return st2;
+        return wuda_gemm_nvfp4(static_cast<const uint8_t*>(a) + static_cast<int64_t>(128) * (k / 2),
+                               static_cast<const uint8_t*>(a_sf_packed) + static_cast<int64_t>(k / 256) * 2048, a_global_scale,
+                               w, w_sf_packed, w_global_scale,
+                               static_cast<__nv_bfloat16*>(c_bf16) + static_cast<int64_t>(128) * n, m - 128, n, k, scratch,
+                               scratch_bytes, status_word, stream);
+    }
     WUDA_REQUIRE(aligned16(a) && aligned16(w) && aligned16(a_sf_packed) && aligned16(w_sf_packed),
                  "operands and packed scales must be 16-byte aligned");
     WUDA_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "scratch must be 256-byte aligned");

@@ -777,7 +777,7 @@ def nvfp4_gemm(a, a_sf_packed, a_global_scale, w, w_sf_packed, w_global_scale, *
     if out is None:
         out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
     need = lib.wuda_gemm_nvfp4_scratch_bytes(m, n)
-    _require(need >= 0, "m must be in [1, 128]")
+    _require(need >= 0, "m must be in [1, 256]")
     scratch = _scratch_for(a.device, need)
     check(lib.wuda_gemm_nvfp4(a.data_ptr(), a_sf_packed.data_ptr(), float(a_global_scale), w.data_ptr(),
                               w_sf_packed.data_ptr(), float(w_global_scale), out.data_ptr(), m, n, k,
