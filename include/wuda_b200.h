@@ -472,6 +472,23 @@ int wuda_mhc_pre(const void* hidden_states, const float* weight, const float* ba
                  const void* attn_norm_gamma, float hc_eps, float rms_eps, float norm_eps, float* pre, float* post,
                  float* comb, void* collapsed_bf16, void* normed_bf16, void* x_fp8, float* x_scales,
                  void* workspace, int64_t workspace_bytes, int m, int hidden, void* stream);
+/* The same operation in the pieces the reference calls one by one (test/test_e2e_decode.py:441-470):
+ * wuda_mhc_pre_mix = the split-K mix projection alone (the role of the third-party tf32_hc_prenorm_gemm):
+ *   partial sums fp32 [splits][m][25] (24 dot products and the sum of squares) into `workspace`,
+ *   splits = ceil(4 * hidden / 512);
+ * wuda_mhc_pre_finish = everything behind it (hc_reduce_fuse_out, kernels/hc_fused_kernel_tc.cu:420-520) on
+ *   partial sums of ANY split count in that layout, plus mix_out fp32 [m, 24] = the mixes times r (nullable),
+ *   which is what the reference's front projection computes post and comb from in its tail;
+ * wuda_mhc_tail = that tail alone (include/front_mixed_gemm.cuh:438-489): post fp32 [m, 4] and comb
+ *   fp32 [m, 16] from mix_out. */
+int wuda_mhc_pre_mix(const void* hidden_states, const float* weight, void* workspace, int64_t workspace_bytes, int m,
+                     int hidden, void* stream);
+int wuda_mhc_pre_finish(const void* hidden_states, const float* partials, int splits, const float* base,
+                        const float* scale, const void* attn_norm_gamma, float hc_eps, float rms_eps, float norm_eps,
+                        float* pre, float* post, float* comb, float* mix_out, void* collapsed_bf16, void* normed_bf16,
+                        void* x_fp8, float* x_scales, int m, int hidden, void* stream);
+int wuda_mhc_tail(const float* mix, const float* base, const float* scale, float hc_eps, float* post, float* comb, int m,
+                  void* stream);
 
 /* ------------------------------------------------------------------------------------
  * MoE router: expert logits -> top-k experts and routing weights.
@@ -726,6 +743,123 @@ int wuda_gemm_fp8_blockscaled_tp2(const void* a, const float* a_scales, const vo
 int wuda_gemm_fp8_blockscaled_noalloc(const void* a, const float* a_scales, const void* w,
                                       const float* w_scales, void* c_bf16, int m, int n, int k,
                                       int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * The whole decode layer as one call: the origin's Block.forward (origin/model.py:688-700) for one token
+ * per request.  The attention half is the reference's decode_step (test/test_e2e_decode.py:475-800: mHC
+ * pre, front projection with its scatter into the state rings, the indexer half-step of
+ * wuda_csa_decode_step, sparse MLA attention, the output projection chain of test/o_proj_csa.py:319-494,
+ * mHC post); the feed-forward half (mHC pre with the ffn weights, ffn RMSNorm, router, shared expert, routed
+ * NVFP4 experts, mHC post; origin/model.py:546-644) has no counterpart in the reference's megakernel.
+ * Every stage is one of the entry points above, enqueued in order on `stream`: no allocation, no host
+ * synchronisation, capturable into a CUDA graph (one call outside a capture first: kernel attributes are
+ * set on first use).
+ *
+ * Tensor-parallel pair: give every rank its share - csa.wq_b with its main heads only, wo_a with its
+ * groups, wo_b with its K columns, attn_sink of its heads, its routed experts (expert_first,
+ * experts_local), its half of the shared expert's intermediate columns - and the two exchange buffers
+ * (wuda_tp2_inbox_bytes(m_max, hidden) and wuda_moe_ep2_inbox_bytes(m_max, hidden) bytes from wuda_tp2_alloc,
+ * the peer's opened with wuda_tp2_open).  wo_b then sums over the pair inside its epilogue and the combine
+ * step exchanges the partial rows, both over NVLink peer memory with the call numbering kept on the device
+ * (epoch 0 of those entry points); both ranks must make the same calls.  NULL inboxes: one GPU.
+ *
+ * workspace: wuda_layer_workspace_bytes(weights, m_max, topk, logits_stride, window) bytes, 256-byte
+ * aligned, zeroed once before the first call (it holds the GEMMs' stream-K flags); its layout depends on
+ * m_max only.  wuda_layer_workspace_offset names where the stages' results lie in it ("logits",
+ * "topk_indices", "topk_raw", "q_main", "mla_out", "attn_out", "gate_logits", "route_indices",
+ * "route_weights", "moe_out", "front_out", "q_proj", "iq_fp8", "w_folded", "win_y2", "w64"), for callers that
+ * read them.
+ */
+typedef struct wuda_layer_weights {
+    wuda_csa_weights csa;           /* q projection, norm weights, rotary tables                            */
+    const float* attn_hc_weight;    /* fp32 [24, 4 * hidden]                                                */
+    const float* attn_hc_base;      /* fp32 [24]                                                            */
+    const float* attn_hc_scale;     /* fp32 [3]                                                             */
+    const void* attn_norm;          /* bf16 [hidden]                                                        */
+    const void* front_w8;           /* e4m3 [2048, hidden], fp32 128x128 scales                             */
+    const float* front_w8_scales;
+    const void* front_w16;          /* bf16 [2624, hidden]                                                  */
+    const float* ape;               /* fp32 [4, 1024]                                                       */
+    const float* idx_ape;           /* fp32 [4, 256]                                                        */
+    const void* wo_a;               /* e4m3 [o_groups, 1024, heads / o_groups * 512]                        */
+    const float* wo_a_scales;
+    const void* wo_b;               /* e4m3 [hidden, o_groups * 1024]                                       */
+    const float* wo_b_scales;
+    const float* attn_sink;         /* fp32 [csa.out_heads]                                                 */
+    const float* ffn_hc_weight;     /* as the attention-side three                                          */
+    const float* ffn_hc_base;
+    const float* ffn_hc_scale;
+    const void* ffn_norm;           /* bf16 [hidden]                                                        */
+    const void* gate_weight;        /* bf16 [experts_total, hidden]                                         */
+    const float* gate_bias;         /* fp32 [experts_total] or NULL                                         */
+    const void* w13;                /* packed e2m1 [experts_local, 2 * inter, hidden / 2]  (w1 rows, then w3) */
+    const void* w13_sf;             /* their ue4m3 scales in tensor-core order, per expert                  */
+    const float* w13_gs;            /* fp32 [experts_local] tensor scales                                   */
+    const void* w2;                 /* packed e2m1 [experts_local, hidden, inter / 2]                       */
+    const void* w2_sf;
+    const float* w2_gs;
+    const void* shared_w13;         /* e4m3 [2 * shared_inter, hidden] or NULL: no shared expert            */
+    const float* shared_w13_scales;
+    const void* shared_w2;          /* e4m3 [hidden, shared_inter]                                          */
+    const float* shared_w2_scales;
+    int hidden;
+    int o_groups;
+    int experts_total, expert_first, experts_local;
+    int moe_topk;
+    int score_func;                 /* 0 softmax, 1 sigmoid, 2 sqrt(softplus)                               */
+    int inter;
+    int shared_inter;
+    float route_scale;
+    float swiglu_limit;
+    float act_scale_in, act_scale_mid;  /* tensor scales of the NVFP4 activations                           */
+    float softmax_scale;
+    float hc_eps, rms_eps, norm_eps;
+} wuda_layer_weights;
+
+typedef struct wuda_layer_state {
+    wuda_csa_caches caches;
+    void* workspace;
+    int64_t workspace_bytes;
+    void* tp_my_inbox;              /* wo_b exchange of a tensor-parallel pair, or NULL                     */
+    void* tp_peer_inbox;
+    void* ep_my_inbox;              /* combine exchange of the pair, or NULL                                */
+    void* ep_peer_inbox;
+    int ep_tokens_max;              /* the row count the combine inboxes were sized for                     */
+    int peer_wait_ms;               /* limit of one wait for the peer, [1, 10000]                           */
+    int m_max;                      /* rows the workspace was laid out for, <= 128                          */
+    int reserved;
+    int32_t* status_word;
+} wuda_layer_state;
+
+typedef struct wuda_layer_step {
+    const void* hidden_in;          /* bf16 [m, 4, hidden] residual streams                                 */
+    void* hidden_out;               /* bf16 [m, 4, hidden]                                                  */
+    const int64_t* pos;             /* per-request arrays as in wuda_csa_step                               */
+    const int32_t* q_pos;
+    const int64_t* main_state_row;
+    const int64_t* idx_state_row;
+    const int64_t* idx_dst;
+    const int64_t* cmp_dst;
+    const int64_t* swa_dst;
+    const int32_t* idx_block_table;
+    const int32_t* cmp_block_table;
+    const int32_t* n_compressed;
+    const int32_t* swa_indices;     /* int32 [m, window] entries of the window pool                         */
+    const int32_t* swa_lengths;     /* int32 [m]                                                            */
+    const int32_t* cmp_lengths;     /* int32 [m]: min(n_compressed, topk)                                   */
+    int block_table_stride;
+    int topk;
+    int window;
+    int reserved;
+    int64_t logits_stride;
+} wuda_layer_step;
+
+int64_t wuda_layer_workspace_bytes(const wuda_layer_weights* weights, int m_max, int topk, int64_t logits_stride,
+                                   int window);
+int64_t wuda_layer_workspace_offset(const wuda_layer_weights* weights, int m_max, int topk, int64_t logits_stride,
+                                    int window, const char* name);
+int wuda_layer_decode(const wuda_layer_weights* weights, const wuda_layer_state* state, const wuda_layer_step* step,
+                      int m, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * Host-buffer form of the indexer step: paged MQA logits, then top-k with the request's

@@ -67,7 +67,8 @@ def test_struct_layouts_match_the_header(tmp_path):
     structs = {"wuda_compressor_bundle": L.CompressorBundle, "wuda_window_bundle": L.WindowBundle,
                "wuda_cache_writers": L.CacheWriters, "wuda_csa_weights": L.CsaWeights, "wuda_csa_caches": L.CsaCaches,
                "wuda_csa_step": L.CsaStep, "wuda_csa_workspace": L.CsaWorkspace,
-               "wuda_sparse_mla_args": L.SparseMlaArgs}
+               "wuda_sparse_mla_args": L.SparseMlaArgs, "wuda_layer_weights": L.LayerWeights,
+               "wuda_layer_state": L.LayerState, "wuda_layer_step": L.LayerStep}
     lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "%s"' % HEADER, 'int main(void) {']
     for cname, cls in structs.items():
         lines.append('printf("%s %%zu\\n", sizeof(%s));' % (cname, cname))

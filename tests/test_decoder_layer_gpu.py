@@ -25,7 +25,7 @@ SMALL = dict(topk=512, experts=32, inter=512, moe_topk=4)
 
 def test_feed_forward_half_is_wired_like_block_forward():
     batch = 6
-    layer, slots, x = build_random_layer(batch, 1500, seed=5, **SMALL)
+    layer, slots, x = build_random_layer(batch, 1500, seed=5, native=False, **SMALL)     # sequenced from Python
     layer.prepare(slots)
     out = layer.launch(x, batch).clone()
     torch.cuda.synchronize()
@@ -50,12 +50,30 @@ def test_feed_forward_half_is_wired_like_block_forward():
     torch.cuda.synchronize()
     layer.check_status()
     assert torch.equal(out, again)
+    # the library's own C++ sequence (one call per step) gives the same bits from the same state
+    native, slots_n, x_n = build_random_layer(batch, 1500, seed=5, native=True, **SMALL)
+    native.prepare(slots_n)
+    out_n = native.launch(x_n, batch)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert torch.equal(x, x_n) and torch.equal(out, out_n)
+    assert torch.equal(native.view("mla_out", torch.bfloat16, batch, 128, 512), layer.attn.mla_out[:batch])
+    assert torch.equal(native.route_indices, layer.route_indices)
+    for pool in ("idx_pool", "cmp_pool", "swa_pool", "main_state", "idx_state"):
+        assert torch.equal(getattr(native.attn.cache, pool), getattr(layer.attn.cache, pool))
+    native.capture(x_n, batch)
+    again = native.replay()
+    torch.cuda.synchronize()
+    native.check_status()
+    assert torch.equal(out, again)
 
 
 def _snapshot(layer):
-    c = layer.attn.cache
-    return [t.clone() for t in (c.idx_pool, c.cmp_pool, c.swa_pool, c.main_state, c.idx_state, layer.attn.stage.logits,
-                                layer.attn.stage.topk_indices, layer.attn.mla_out, layer.out)]
+    c, b = layer.attn.cache, layer.max_batch
+    stride = layer.attn.stage.logits_stride
+    return [t.clone() for t in (c.idx_pool, c.cmp_pool, c.swa_pool, c.main_state, c.idx_state,
+                                layer.view("logits", torch.float32, b, stride), layer.view("topk_raw", torch.int32, b, layer.attn.topk).sort(-1).values,
+                                layer.view("mla_out", torch.bfloat16, b, 128, 512), layer.out)]
 
 
 def test_two_runs_from_the_same_state_agree_bit_for_bit():

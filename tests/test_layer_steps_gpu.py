@@ -65,8 +65,8 @@ def check_step(layer, st, m):
     assert np.all(np.abs(out - ref) <= np.abs(ref).max(axis=-1, keepdims=True) * 2.0 ** -7 + 1e-6)
 
 
-def run_sim(check):
-    layer, slots, _ = build_random_layer(BATCH, 1, seed=17, **SMALL)       # every request at position 0 next
+def run_sim(check, native):
+    layer, slots, _ = build_random_layer(BATCH, 1, seed=17, native=native, **SMALL)       # every request at position 0 next
     cache = layer.attn.cache
     g = torch.Generator(device="cuda").manual_seed(42)
     finals = []
@@ -89,9 +89,18 @@ def run_sim(check):
         if check:
             check_step(layer, st, BATCH)
         finals.append(out.clone())
+    stage, b = layer.attn.stage, BATCH
+    if native:
+        mid = [layer.view("logits", torch.float32, b, stage.logits_stride), layer.view("q_main", torch.bfloat16, b, 128, 512),
+               layer.view("mla_out", torch.bfloat16, b, 128, 512), layer.view("q_proj", torch.bfloat16, b, stage.w.n_total),
+               layer.view("front_out", torch.bfloat16, b, 2048)]
+    else:
+        mid = [stage.logits, stage.q_main, layer.attn.mla_out, stage.y, layer.attn.front_out]
+    # only the scored positions of a logits row are defined (the rest keeps whatever the buffer held)
+    scored = torch.arange(stage.logits_stride, device="cuda")[None, :] < stage.n_compressed[:b, None]
+    mid[0] = torch.where(scored, mid[0][:b], torch.zeros_like(mid[0][:b]))
     snap = finals + [cache.swa_pool.clone(), cache.cmp_pool.clone(), cache.idx_pool.clone(), cache.main_state.clone(),
-                     cache.idx_state.clone(), layer.attn.stage.logits.clone(), layer.attn.stage.q_main.clone(),
-                     layer.attn.mla_out.clone(), layer.attn.stage.y.clone(), layer.attn.front_out.clone()]
+                     cache.idx_state.clone()] + [t.clone() for t in mid]
     # the last step once more as a graph replay: same inputs, same rows and destinations, same bits
     layer.capture(hidden, BATCH)
     again = layer.replay()
@@ -101,7 +110,10 @@ def run_sim(check):
 
 
 def test_eight_steps_with_slot_reuse_and_a_zero_row_then_the_same_again():
-    first = run_sim(check=True)
-    second = run_sim(check=False)
+    first = run_sim(check=True, native=False)      # sequenced from Python, stage tensors held against the oracle
+    second = run_sim(check=False, native=True)     # the library's own C++ sequence, one call per step
+    third = run_sim(check=False, native=True)
+    for a, b, c in zip(first, second, third):
+        assert torch.equal(b.contiguous().view(torch.uint8), c.contiguous().view(torch.uint8))
     for a, b in zip(first, second):
         assert torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8))   # byte view: NaN-safe

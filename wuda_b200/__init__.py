@@ -7,3 +7,4 @@ streams.  Importing the package requires the built library (python -m wuda_b200.
 """
 from ._lib import WudaError, lib, LIB_PATH  # noqa: F401
 from .ops import *  # noqa: F401,F403
+from .shims import *  # noqa: F401,F403

@@ -82,6 +82,36 @@ class SparseMlaArgs(ctypes.Structure):
                 ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("softmax_scale", c_float)]
 
 
+class LayerWeights(ctypes.Structure):
+    """wuda_layer_weights"""
+    _fields_ = ([("csa", CsaWeights)] +
+                [(n, c_vp) for n in ("attn_hc_weight", "attn_hc_base", "attn_hc_scale", "attn_norm", "front_w8",
+                                     "front_w8_scales", "front_w16", "ape", "idx_ape", "wo_a", "wo_a_scales", "wo_b",
+                                     "wo_b_scales", "attn_sink", "ffn_hc_weight", "ffn_hc_base", "ffn_hc_scale", "ffn_norm",
+                                     "gate_weight", "gate_bias", "w13", "w13_sf", "w13_gs", "w2", "w2_sf", "w2_gs",
+                                     "shared_w13", "shared_w13_scales", "shared_w2", "shared_w2_scales")] +
+                [(n, c_int) for n in ("hidden", "o_groups", "experts_total", "expert_first", "experts_local", "moe_topk",
+                                      "score_func", "inter", "shared_inter")] +
+                [(n, c_float) for n in ("route_scale", "swiglu_limit", "act_scale_in", "act_scale_mid", "softmax_scale",
+                                        "hc_eps", "rms_eps", "norm_eps")])
+
+
+class LayerState(ctypes.Structure):
+    """wuda_layer_state"""
+    _fields_ = [("caches", CsaCaches), ("workspace", c_vp), ("workspace_bytes", c_i64), ("tp_my_inbox", c_vp),
+                ("tp_peer_inbox", c_vp), ("ep_my_inbox", c_vp), ("ep_peer_inbox", c_vp), ("ep_tokens_max", c_int),
+                ("peer_wait_ms", c_int), ("m_max", c_int), ("reserved", c_int), ("status_word", c_vp)]
+
+
+class LayerStep(ctypes.Structure):
+    """wuda_layer_step"""
+    _fields_ = ([(n, c_vp) for n in ("hidden_in", "hidden_out", "pos", "q_pos", "main_state_row", "idx_state_row", "idx_dst",
+                                     "cmp_dst", "swa_dst", "idx_block_table", "cmp_block_table", "n_compressed",
+                                     "swa_indices", "swa_lengths", "cmp_lengths")] +
+                [("block_table_stride", c_int), ("topk", c_int), ("window", c_int), ("reserved", c_int),
+                 ("logits_stride", c_i64)])
+
+
 # name -> (restype, argtypes); mirrors include/wuda_b200.h one to one.
 SIGNATURES = {
     "wuda_version": (c_int, []),
@@ -107,6 +137,10 @@ SIGNATURES = {
     "wuda_mhc_pre_workspace_bytes": (c_i64, [c_int, c_int]),
     "wuda_mhc_pre": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_float, c_float, c_vp, c_vp, c_vp, c_vp, c_vp,
                              c_vp, c_vp, c_vp, c_i64, c_int, c_int, c_vp]),
+    "wuda_mhc_pre_mix": (c_int, [c_vp, c_vp, c_vp, c_i64, c_int, c_int, c_vp]),
+    "wuda_mhc_pre_finish": (c_int, [c_vp, c_vp, c_int, c_vp, c_vp, c_vp, c_float, c_float, c_float, c_vp, c_vp, c_vp, c_vp,
+                                    c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
+    "wuda_mhc_tail": (c_int, [c_vp, c_vp, c_vp, c_float, c_vp, c_vp, c_int, c_vp]),
     "wuda_gemm_bf16_scratch_bytes": (c_i64, [c_int, c_int]),
     "wuda_gemm_bf16": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
     "wuda_front_emit": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_int, c_vp,
@@ -141,6 +175,10 @@ SIGNATURES = {
     "wuda_gemm_nvfp4": (c_int, [c_vp, c_vp, c_float, c_vp, c_vp, c_float, c_vp, c_int, c_int, c_int, c_vp, c_i64,
                                 c_vp, c_vp]),
     "wuda_topk": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_int, c_int, c_int, c_vp]),
+    "wuda_layer_workspace_bytes": (c_i64, [ctypes.POINTER(LayerWeights), c_int, c_int, c_i64, c_int]),
+    "wuda_layer_workspace_offset": (c_i64, [ctypes.POINTER(LayerWeights), c_int, c_int, c_i64, c_int, ctypes.c_char_p]),
+    "wuda_layer_decode": (c_int, [ctypes.POINTER(LayerWeights), ctypes.POINTER(LayerState), ctypes.POINTER(LayerStep),
+                                  c_int, c_vp]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

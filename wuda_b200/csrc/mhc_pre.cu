@@ -44,6 +44,7 @@ struct Params {
     float* pre;                    // [m, 4] or nullptr
     float* post;                   // [m, 4]
     float* comb;                   // [m, 4, 4]
+    float* mix_out;                // [m, 24] or nullptr: the mixes times r (what the post / comb gates are made of)
     __nv_bfloat16* collapsed;      // [m, hidden] or nullptr
     __nv_bfloat16* normed;         // [m, hidden] or nullptr
     uint8_t* x_fp8;                // [m, hidden] or nullptr
@@ -118,6 +119,54 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
     return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
 }
 
+// The post gates and the Sinkhorn-normalised comb matrix of one token, by one warp.  `folded` is lane j's mix
+// value times r for j < 24 (pre 0..3 | post 4..7 | comb 8..23); lanes 0..3 write post, lanes 0..15 comb
+// (row = lane / 4, column = lane % 4): row sums by xor 1, 2; column sums by xor 4, 8.
+__device__ __forceinline__ void post_and_comb(float folded, int lane, const float* scale, const float* base, float hc_eps,
+                                              float* post, float* comb) {
+    const float post_mix = __shfl_sync(0xffffffffu, folded, (lane + kStreams) & 31);
+    if (post && lane < kStreams) post[lane] = 2.0f * sigmoid(post_mix * scale[1] + base[kStreams + lane]);
+    const float comb_mix = __shfl_sync(0xffffffffu, folded, (lane + 2 * kStreams) & 31);
+    const bool live = lane < kStreams * kStreams;
+    float v = live ? comb_mix * scale[2] + base[2 * kStreams + lane] : 0.f;
+    float mx = v;
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float e = expf(v - mx);
+    float rs = e;
+    rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+    rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+    v = __fdiv_rn(e, rs) + hc_eps;
+    float cs = v;
+    cs += __shfl_xor_sync(0xffffffffu, cs, 4);
+    cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+    v = __fdiv_rn(v, cs + hc_eps);
+    for (int it = 0; it < kSinkhornIters - 1; ++it) {
+        rs = v;
+        rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+        rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+        v = __fdiv_rn(v, rs + hc_eps);
+        cs = v;
+        cs += __shfl_xor_sync(0xffffffffu, cs, 4);
+        cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+        v = __fdiv_rn(v, cs + hc_eps);
+    }
+    if (live && comb) comb[lane] = v;
+}
+
+// The tail alone: post and comb from exported mixes (one warp per token), for callers that run it behind
+// another kernel as the reference does (include/front_mixed_gemm.cuh:438-489).
+__global__ void __launch_bounds__(128) mhc_tail_kernel(const float* mix, const float* base, const float* scale, float hc_eps,
+                                                       float* post, float* comb, int m) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (t >= m) return;
+    const float folded = lane < kMix ? __ldcg(mix + t * kMix + lane) : 0.f;
+    post_and_comb(folded, lane, scale, base, hc_eps, post + t * kStreams, comb + t * kStreams * kStreams);
+}
+
 __global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p) {
     pdl_launch_dependents();
     pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
@@ -163,36 +212,10 @@ __global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p
             const float v = sigmoid(mix[lane] * r * p.scale[0] + p.base[lane]) + p.hc_eps;
             pre_s[lane] = v;
             if (p.pre) p.pre[t * kStreams + lane] = v;
-            if (p.post)
-                p.post[t * kStreams + lane] = 2.0f * sigmoid(mix[kStreams + lane] * r * p.scale[1] + p.base[kStreams + lane]);
         }
-        // Sinkhorn on the 4 x 4 comb in lanes 0..15 (row = lane / 4, column = lane % 4): row sums by
-        // xor 1, 2; column sums by xor 4, 8.  Lanes 16..31 compute on zeros and are ignored.
-        const bool live = lane < kStreams * kStreams;
-        float v = live ? mix[2 * kStreams + lane] * r * p.scale[2] + p.base[2 * kStreams + lane] : 0.f;
-        float mx = v;
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float e = expf(v - mx);
-        float rs = e;
-        rs += __shfl_xor_sync(0xffffffffu, rs, 1);
-        rs += __shfl_xor_sync(0xffffffffu, rs, 2);
-        v = __fdiv_rn(e, rs) + p.hc_eps;
-        float cs = v;
-        cs += __shfl_xor_sync(0xffffffffu, cs, 4);
-        cs += __shfl_xor_sync(0xffffffffu, cs, 8);
-        v = __fdiv_rn(v, cs + p.hc_eps);
-        for (int it = 0; it < kSinkhornIters - 1; ++it) {
-            rs = v;
-            rs += __shfl_xor_sync(0xffffffffu, rs, 1);
-            rs += __shfl_xor_sync(0xffffffffu, rs, 2);
-            v = __fdiv_rn(v, rs + p.hc_eps);
-            cs = v;
-            cs += __shfl_xor_sync(0xffffffffu, cs, 4);
-            cs += __shfl_xor_sync(0xffffffffu, cs, 8);
-            v = __fdiv_rn(v, cs + p.hc_eps);
-        }
-        if (live && p.comb) p.comb[t * kStreams * kStreams + lane] = v;
+        if (p.mix_out && lane < kMix) p.mix_out[t * kMix + lane] = mix[lane] * r;
+        post_and_comb(lane < kMix ? mix[lane] * r : 0.f, lane, p.scale, p.base, p.hc_eps, p.post ? p.post + t * kStreams : nullptr,
+                      p.comb ? p.comb + t * kStreams * kStreams : nullptr);
     }
     __syncthreads();
     if (!p.collapsed && !p.normed && !p.x_fp8) return;
@@ -293,36 +316,33 @@ extern "C" int64_t wuda_mhc_pre_workspace_bytes(int m, int hidden) {
     return slices * m * wuda::mhcpre::kPart * 4;
 }
 
-extern "C" int wuda_mhc_pre(const void* hidden_states, const float* weight, const float* base, const float* scale,
-                            const void* attn_norm_gamma, float hc_eps, float rms_eps, float norm_eps, float* pre,
-                            float* post, float* comb, void* collapsed_bf16, void* normed_bf16, void* x_fp8,
-                            float* x_scales, void* workspace, int64_t workspace_bytes, int m, int hidden,
-                            void* stream) {
+namespace {
+
+int fill_params(wuda::mhcpre::Params& p, const void* hidden_states, const float* weight, const float* base, const float* scale,
+                const void* gamma, float hc_eps, float rms_eps, float norm_eps, float* pre, float* post, float* comb,
+                float* mix_out, void* collapsed_bf16, void* normed_bf16, void* x_fp8, float* x_scales, void* workspace, int m,
+                int hidden) {
     using namespace wuda;
     using namespace wuda::mhcpre;
-    clear_error();
     WUDA_REQUIRE(m >= 1, "m must be >= 1 (got %d)", m);
     WUDA_REQUIRE(hidden >= 128 && hidden % 128 == 0 && hidden <= 8192,
                  "hidden must be a multiple of 128 in [128, 8192] (got %d)", hidden);
-    WUDA_REQUIRE(hidden_states && weight && base && scale && workspace, "hidden, weight, base, scale and workspace are required");
-    WUDA_REQUIRE((!normed_bf16 && !x_fp8) || attn_norm_gamma, "the norm weight is required with normed or x_fp8");
+    WUDA_REQUIRE(hidden_states && workspace, "hidden and workspace are required");
+    WUDA_REQUIRE((!normed_bf16 && !x_fp8) || gamma, "the norm weight is required with normed or x_fp8");
     WUDA_REQUIRE(!x_fp8 || x_scales, "x_scales is required with x_fp8");
-    WUDA_REQUIRE(aligned16(hidden_states) && aligned16(weight) && aligned16(attn_norm_gamma) && aligned16(collapsed_bf16) &&
+    WUDA_REQUIRE(aligned16(hidden_states) && aligned16(weight) && aligned16(gamma) && aligned16(collapsed_bf16) &&
                      aligned16(normed_bf16) && aligned16(x_fp8),
                  "hidden, weight, gamma and the row outputs must be 16-byte aligned");
-    const int64_t need = wuda_mhc_pre_workspace_bytes(m, hidden);
-    WUDA_REQUIRE(workspace_bytes >= need, "workspace holds %lld bytes; %lld are needed (wuda_mhc_pre_workspace_bytes)",
-                 static_cast<long long>(workspace_bytes), static_cast<long long>(need));
-    Params p;
     p.x = static_cast<const __nv_bfloat16*>(hidden_states);
     p.weight = weight;
     p.base = base;
     p.scale = scale;
-    p.gamma = static_cast<const __nv_bfloat16*>(attn_norm_gamma);
+    p.gamma = static_cast<const __nv_bfloat16*>(gamma);
     p.ws = static_cast<float*>(workspace);
     p.pre = pre;
     p.post = post;
     p.comb = comb;
+    p.mix_out = mix_out;
     p.collapsed = static_cast<__nv_bfloat16*>(collapsed_bf16);
     p.normed = static_cast<__nv_bfloat16*>(normed_bf16);
     p.x_fp8 = static_cast<uint8_t*>(x_fp8);
@@ -333,8 +353,77 @@ extern "C" int wuda_mhc_pre(const void* hidden_states, const float* weight, cons
     p.hc_eps = hc_eps;
     p.rms_eps = rms_eps;
     p.norm_eps = norm_eps;
+    return WUDA_OK;
+}
+
+}  // namespace
+
+extern "C" int wuda_mhc_pre(const void* hidden_states, const float* weight, const float* base, const float* scale,
+                            const void* attn_norm_gamma, float hc_eps, float rms_eps, float norm_eps, float* pre,
+                            float* post, float* comb, void* collapsed_bf16, void* normed_bf16, void* x_fp8,
+                            float* x_scales, void* workspace, int64_t workspace_bytes, int m, int hidden,
+                            void* stream) {
+    using namespace wuda;
+    using namespace wuda::mhcpre;
+    clear_error();
+    WUDA_REQUIRE(weight && base && scale, "weight, base and scale are required");
+    Params p;
+    int st = fill_params(p, hidden_states, weight, base, scale, attn_norm_gamma, hc_eps, rms_eps, norm_eps, pre, post, comb,
+                         nullptr, collapsed_bf16, normed_bf16, x_fp8, x_scales, workspace, m, hidden);
+    if (st != WUDA_OK) return st;
+    const int64_t need = wuda_mhc_pre_workspace_bytes(m, hidden);
+    WUDA_REQUIRE(workspace_bytes >= need, "workspace holds %lld bytes; %lld are needed (wuda_mhc_pre_workspace_bytes)",
+                 static_cast<long long>(workspace_bytes), static_cast<long long>(need));
     const dim3 grid_mix(p.slices, (m + kTokensPerCta - 1) / kTokensPerCta);
     WUDA_CUDA(launch_pdl(mhc_pre_mix_kernel, dim3(grid_mix), dim3(kMixThreads), 0, static_cast<cudaStream_t>(stream), p));
     WUDA_CUDA(launch_pdl(mhc_pre_finish_kernel, dim3(m), dim3(kFinishThreads), 0, static_cast<cudaStream_t>(stream), p));
+    return WUDA_OK;
+}
+
+extern "C" int wuda_mhc_pre_mix(const void* hidden_states, const float* weight, void* workspace, int64_t workspace_bytes,
+                                int m, int hidden, void* stream) {
+    using namespace wuda;
+    using namespace wuda::mhcpre;
+    clear_error();
+    WUDA_REQUIRE(weight, "weight is required");
+    Params p;
+    int st = fill_params(p, hidden_states, weight, nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, nullptr, nullptr, nullptr, nullptr,
+                         nullptr, nullptr, nullptr, nullptr, workspace, m, hidden);
+    if (st != WUDA_OK) return st;
+    const int64_t need = wuda_mhc_pre_workspace_bytes(m, hidden);
+    WUDA_REQUIRE(workspace_bytes >= need, "workspace holds %lld bytes; %lld are needed (wuda_mhc_pre_workspace_bytes)",
+                 static_cast<long long>(workspace_bytes), static_cast<long long>(need));
+    const dim3 grid_mix(p.slices, (m + kTokensPerCta - 1) / kTokensPerCta);
+    WUDA_CUDA(launch_pdl(mhc_pre_mix_kernel, dim3(grid_mix), dim3(kMixThreads), 0, static_cast<cudaStream_t>(stream), p));
+    return WUDA_OK;
+}
+
+extern "C" int wuda_mhc_pre_finish(const void* hidden_states, const float* partials, int splits, const float* base,
+                                   const float* scale, const void* attn_norm_gamma, float hc_eps, float rms_eps,
+                                   float norm_eps, float* pre, float* post, float* comb, float* mix_out,
+                                   void* collapsed_bf16, void* normed_bf16, void* x_fp8, float* x_scales, int m, int hidden,
+                                   void* stream) {
+    using namespace wuda;
+    using namespace wuda::mhcpre;
+    clear_error();
+    WUDA_REQUIRE(base && scale, "base and scale are required");
+    WUDA_REQUIRE(splits >= 1, "splits must be >= 1 (got %d)", splits);
+    Params p;
+    int st = fill_params(p, hidden_states, nullptr, base, scale, attn_norm_gamma, hc_eps, rms_eps, norm_eps, pre, post, comb,
+                         mix_out, collapsed_bf16, normed_bf16, x_fp8, x_scales, const_cast<float*>(partials), m, hidden);
+    if (st != WUDA_OK) return st;
+    p.slices = splits;
+    WUDA_CUDA(launch_pdl(mhc_pre_finish_kernel, dim3(m), dim3(kFinishThreads), 0, static_cast<cudaStream_t>(stream), p));
+    return WUDA_OK;
+}
+
+extern "C" int wuda_mhc_tail(const float* mix, const float* base, const float* scale, float hc_eps, float* post, float* comb,
+                             int m, void* stream) {
+    using namespace wuda;
+    using namespace wuda::mhcpre;
+    clear_error();
+    WUDA_REQUIRE(m >= 1 && mix && base && scale && post && comb, "m >= 1 and every pointer are required");
+    WUDA_CUDA(launch_pdl(mhc_tail_kernel, dim3((m + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream), mix, base, scale,
+                         hc_eps, post, comb, m));
     return WUDA_OK;
 }

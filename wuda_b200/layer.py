@@ -27,8 +27,10 @@ from typing import Optional
 
 import torch
 
-from . import moe, o_proj, ops
-from ._lib import lib
+import ctypes
+
+from . import _lib, moe, o_proj, ops
+from ._lib import check, lib
 from .decode import CsaDecodeStage
 
 WINDOW = 128
@@ -141,27 +143,110 @@ class FfnWeights:
 
 
 class DecoderLayer:
-    """Block.forward for one decode token per request: hidden bf16 [m, 4, hidden] -> bf16 [m, 4, hidden]."""
+    """Block.forward for one decode token per request: hidden bf16 [m, 4, hidden] -> bf16 [m, 4, hidden].
 
-    def __init__(self, attention, ffn, max_batch, ep_link=None, peer_wait_ms=2000):
-        self.attn, self.ffn, self.max_batch = attention, ffn, max_batch
+    native=True (default): the launch sequence is the library's own C++ (wuda_layer_decode: one call per step,
+    every intermediate tensor in one workspace).  native=False: the same entry points called one by one from
+    Python, each stage's tensors at hand - the form the stage-level tests read.  Both give the same bits."""
+
+    def __init__(self, attention, ffn, max_batch, ep_link=None, peer_wait_ms=2000, native=True):
+        self.attn, self.ffn, self.max_batch, self.native = attention, ffn, max_batch, native
+        self.ep_link, self.peer_wait_ms = ep_link, peer_wait_ms
         dev = ffn.hc_weight.device
         hidden = ffn.ffn_norm.numel()
         self.hidden = hidden
-        self.runner = moe.MoERunner(ffn.routed, max_batch, ffn.topk, device=dev, expert_first=ffn.expert_first,
-                                    experts_total=ffn.experts_total, link=ep_link, peer_wait_ms=peer_wait_ms)
-        self.pre_ws = torch.empty(lib.wuda_mhc_pre_workspace_bytes(max_batch, hidden), dtype=torch.uint8, device=dev)
-        self.gate_logits = torch.empty(max_batch, ffn.experts_total, dtype=torch.float32, device=dev)
-        self.y = torch.empty(max_batch, hidden, dtype=torch.bfloat16, device=dev)
         self.out = torch.empty(max_batch, 4, hidden, dtype=torch.bfloat16, device=dev)
         self.route_indices = None
         self._graph = None
+        if native:
+            self._init_native(dev)
+        else:
+            self.runner = moe.MoERunner(ffn.routed, max_batch, ffn.topk, device=dev, expert_first=ffn.expert_first,
+                                        experts_total=ffn.experts_total, link=ep_link, peer_wait_ms=peer_wait_ms)
+            self.pre_ws = torch.empty(lib.wuda_mhc_pre_workspace_bytes(max_batch, hidden), dtype=torch.uint8, device=dev)
+            self.gate_logits = torch.empty(max_batch, ffn.experts_total, dtype=torch.float32, device=dev)
+            self.y = torch.empty(max_batch, hidden, dtype=torch.bfloat16, device=dev)
+
+    # ---- the C++ launch sequence
+    def _init_native(self, dev):
+        a, f, st = self.attn, self.ffn, self.attn.stage
+        hw, routed, shared = a.w, f.routed, f.shared
+        if shared is not None and float(shared.limit) != float(routed.swiglu_limit):
+            raise ValueError("the shared and the routed experts must use one swiglu_limit")
+        p = lambda t: t.data_ptr() if t is not None else None
+        w = _lib.LayerWeights()
+        w.csa = st.w.c
+        w.attn_hc_weight, w.attn_hc_base, w.attn_hc_scale, w.attn_norm = p(hw.hc_weight), p(hw.hc_base), p(hw.hc_scale), p(hw.attn_norm)
+        w.front_w8, w.front_w8_scales, w.front_w16 = p(hw.front_w8), p(hw.front_w8_scales), p(hw.front_w16)
+        w.ape, w.idx_ape = p(hw.ape), p(hw.idx_ape)
+        w.wo_a, w.wo_a_scales, w.wo_b, w.wo_b_scales = p(hw.o_proj.wo_a), p(hw.o_proj.wo_a_scale), p(hw.o_proj.wo_b), p(hw.o_proj.wo_b_scale)
+        w.attn_sink = p(hw.attn_sink)
+        w.ffn_hc_weight, w.ffn_hc_base, w.ffn_hc_scale, w.ffn_norm = p(f.hc_weight), p(f.hc_base), p(f.hc_scale), p(f.ffn_norm)
+        w.gate_weight, w.gate_bias = p(f.gate_weight), p(f.gate_bias)
+        d = routed.dev
+        w.w13, w.w13_sf, w.w13_gs, w.w2, w.w2_sf, w.w2_gs = (p(d[k]) for k in ("w13", "w13_sf", "w13_gs", "w2", "w2_sf", "w2_gs"))
+        if shared is not None:
+            w.shared_w13, w.shared_w13_scales, w.shared_w2, w.shared_w2_scales = p(shared.w13), p(shared.w13_scale), p(shared.w2), p(shared.w2_scale)
+            w.shared_inter = shared.inter
+        w.hidden, w.o_groups = self.hidden, hw.o_proj.wo_a.size(0)
+        w.experts_total, w.expert_first, w.experts_local = f.experts_total, f.expert_first, routed.experts
+        w.moe_topk, w.score_func, w.inter = f.topk, ops.SCORE_FUNCS[f.score_func], routed.inter
+        w.route_scale, w.swiglu_limit = float(f.route_scale), float(routed.swiglu_limit)
+        w.act_scale_in, w.act_scale_mid = float(routed.act_scale_in), float(routed.act_scale_mid)
+        w.softmax_scale = float(a.softmax_scale)
+        w.hc_eps = w.rms_eps = w.norm_eps = 1e-6
+        self._w = w
+        self._geometry = (self.max_batch, a.topk, st.logits_stride, a.swa_idx.size(1))
+        need = lib.wuda_layer_workspace_bytes(ctypes.byref(w), *self._geometry)
+        if need <= 0:
+            raise ValueError("wuda_layer_workspace_bytes refused the layer geometry")
+        self.workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
+        s = _lib.LayerState()
+        s.caches = st._caches
+        s.workspace, s.workspace_bytes = self.workspace.data_ptr(), need
+        if a.tp_link is not None:
+            if not a.tp_link.device_sequence:
+                raise ValueError("the tensor-parallel link must number its calls on the device (device_sequence=True)")
+            s.tp_my_inbox, s.tp_peer_inbox = a.tp_link._local, a.tp_link._peer
+        if self.ep_link is not None:
+            if not self.ep_link.device_sequence:
+                raise ValueError("the expert-parallel link must number its calls on the device (device_sequence=True)")
+            s.ep_my_inbox, s.ep_peer_inbox, s.ep_tokens_max = self.ep_link._local, self.ep_link._peer, self.ep_link.max_tokens
+        s.peer_wait_ms, s.m_max, s.status_word = int(self.peer_wait_ms), self.max_batch, st.status.data_ptr()
+        self._s = s
+
+    def view(self, name, dtype, *shape):
+        """A stage's result inside the workspace of the native form (names: wuda_layer_workspace_offset)."""
+        off = lib.wuda_layer_workspace_offset(ctypes.byref(self._w), *self._geometry, name.encode())
+        if off < 0:
+            raise KeyError(name)
+        n = 1
+        for d in shape:
+            n *= d
+        return self.workspace[off:off + n * torch.empty(0, dtype=dtype).element_size()].view(dtype).view(*shape)
+
+    def _launch_native(self, hidden_states, m):
+        a, st = self.attn, self.attn.stage
+        if not (hidden_states.is_cuda and hidden_states.is_contiguous() and hidden_states.dtype == torch.bfloat16
+                and tuple(hidden_states.shape) == (m, 4, self.hidden)):
+            raise ValueError("hidden_states must be contiguous CUDA bf16 [m, 4, hidden]")
+        t = _lib.LayerStep(
+            hidden_in=hidden_states.data_ptr(), hidden_out=self.out.data_ptr(), pos=st.pos.data_ptr(), q_pos=st.q_pos.data_ptr(),
+            main_state_row=st.main_state_row.data_ptr(), idx_state_row=st.idx_state_row.data_ptr(), idx_dst=st.idx_dst.data_ptr(),
+            cmp_dst=st.cmp_dst.data_ptr(), swa_dst=st.swa_dst.data_ptr(), idx_block_table=st.block_table.data_ptr(),
+            cmp_block_table=st.cmp_block_table.data_ptr(), n_compressed=st.n_compressed.data_ptr(),
+            swa_indices=a.swa_idx.data_ptr(), swa_lengths=a.swa_len.data_ptr(), cmp_lengths=a.cmp_len.data_ptr(),
+            block_table_stride=st.block_table.stride(0), topk=a.topk, window=a.swa_idx.size(1), logits_stride=st.logits_stride)
+        check(lib.wuda_layer_decode(ctypes.byref(self._w), ctypes.byref(self._s), ctypes.byref(t), m,
+                                    torch.cuda.current_stream().cuda_stream))
+        self.route_indices = self.view("route_indices", torch.int32, self.max_batch, self.ffn.topk)[:m]
+        return self.out[:m]
 
     def prepare(self, slots):
         return self.attn.prepare(slots)
 
     def launch_ffn(self, x, m):
-        """The feed-forward half on the residual streams x bf16 [m, 4, hidden]."""
+        """The feed-forward half on the residual streams x bf16 [m, 4, hidden] (Python-sequenced form)."""
         f = self.ffn
         pre = ops.mhc_pre(x, f.hc_weight, f.hc_base, f.hc_scale, f.ffn_norm, quant=False, workspace=self.pre_ws)
         normed = pre["normed"]
@@ -173,6 +258,8 @@ class DecoderLayer:
         return ops.mhc_post_out(y, x, pre["post"], pre["comb"], self.out[:m])
 
     def launch(self, hidden_states, m):
+        if self.native:
+            return self._launch_native(hidden_states, m)
         return self.launch_ffn(self.attn.launch(hidden_states, m), m)
 
     def capture(self, hidden_states, m):
@@ -194,7 +281,7 @@ class DecoderLayer:
 
     def check_status(self):
         self.attn.check_status()
-        code = int(self.runner.status.item())
-        if code:
-            from ._lib import WudaError
-            raise WudaError(5, "device status %d in the MoE block" % code)
+        if not self.native:
+            code = int(self.runner.status.item())
+            if code:
+                raise _lib.WudaError(5, "device status %d in the MoE block" % code)

@@ -40,7 +40,7 @@ def _fp8_weight(g, n, k, device):
 
 
 def build_random_layer(batch, context, topk=2048, rank=0, world=1, tp_link=None, ep_link=None, seed=11,
-                       experts=256, inter=2048, moe_topk=8, device="cuda", peer_wait_ms=2000):
+                       experts=256, inter=2048, moe_topk=8, device="cuda", peer_wait_ms=2000, native=True):
     """Returns (layer, slots, hidden_states): a DecoderLayer whose requests all stand at position context - 1
     (the timed token), the request slots, and bf16 [batch, 4, hidden] residual streams.  world = 2 builds what
     rank `rank` of a tensor-parallel pair holds and needs both links."""
@@ -123,7 +123,7 @@ def build_random_layer(batch, context, topk=2048, rank=0, world=1, tp_link=None,
                      gate_weight=gate_w, gate_bias=torch.zeros(experts, device=dev), routed=all_experts,
                      shared=moe.SharedExpert(w13, w13_s, w2, w2_s), experts_total=experts, expert_first=first,
                      topk=moe_topk, route_scale=2.5)
-    layer = DecoderLayer(attention, ffn, batch, ep_link=ep_link, peer_wait_ms=peer_wait_ms)
+    layer = DecoderLayer(attention, ffn, batch, ep_link=ep_link, peer_wait_ms=peer_wait_ms, native=native)
     x = rnd(batch, 4, hidden).bfloat16()
     return layer, slots, x
 
