@@ -12,6 +12,7 @@ because consecutive launches use different weight buffers that together exceed L
     python -m wuda_b200.benchmarks attention_half_layer_launches   (three eager passes, for an ncu launch list)
     python -m wuda_b200.benchmarks moe_experts                     (router + routed NVFP4 experts of one MoE block)
     python -m wuda_b200.benchmarks moe_experts_launches            (two eager passes, for an ncu launch list)
+    python -m wuda_b200.benchmarks topk                            (top-2048 over L2-resident rows: the layer's and the bench's shapes)
     python -m wuda_b200.benchmarks mqa_fp4                         (MXFP4 paged MQA logits)
     python -m wuda_b200.benchmarks mqa_fp4_launches                (three eager launches at batch 64 x 32768, for ncu)
     python -m wuda_b200.benchmarks sparse_mla                      (sparse MLA decode attention, window 128 + top-2048)
@@ -453,6 +454,24 @@ def moe_ep2(tokens=64, topk=8, experts=256, dim=7168, inter=2048, iters=20):
     dist.destroy_process_group()
 
 
+def topk(k=2048):
+    """Top-k selection + page transform over rows that were just written (L2-resident), CUDA-graph replays:
+    64 rows of 8192 scores (the layer at 32 K context), 64 rows of 16384, and 128 rows of 16384..65536 scores
+    (the benchmark step's shape)."""
+    hbm, _, kind = peaks()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for rows, lo, hi in ((64, 8192, 8192), (64, 16384, 16384), (128, 16384, 65536)):
+        lens = torch.randint(lo, hi + 1, (rows,), generator=g, device="cuda", dtype=torch.int32)
+        stride = (hi + 255) // 256 * 256
+        scores = torch.randn(rows, stride, generator=g, device="cuda")
+        table = torch.arange(rows * (stride // 64), device="cuda", dtype=torch.int32).view(rows, -1)
+        out = torch.empty(rows, k, dtype=torch.int32, device="cuda")
+        us = time_graph(lambda: wuda.topk_v2_transform(scores, lens, table, out, 64), reps=20, inner=10)
+        by = int(lens.sum()) * 4 + rows * k * 4
+        print("top-%d of %3d rows x %5d..%5d scores: %6.2f us  (%.1f MB read once -> %.0f GB/s, %.2f of %s HBM peak; "
+              "the rows are L2-resident)" % (k, rows, lo, hi, us, by / 1e6, by / us / 1e3, by / us / 1e3 / hbm, kind))
+
+
 def mqa_fp4(batches=(64,), contexts=(8192, 32768), launches_only=0):
     """MXFP4 paged MQA logits (68 bytes per token): identity page tables, random codes and scale bytes."""
     hbm, _, kind = peaks()
@@ -741,7 +760,7 @@ def one(kind, m, n, k, launches=5):
     print("ran %d launches of %s M=%d N=%d K=%d" % (launches, kind, m, n, k))
 
 
-KINDS = {"gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(contexts=(32768,), launches_only=3),
+KINDS = {"topk": topk, "gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(contexts=(32768,), launches_only=3),
          "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(32,), launches_only=3),
          "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
          "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,

@@ -6,27 +6,30 @@
 // scores[r, 0:seq_len[r]], in no particular order; rows with seq_len <= k give
 // [0..n) followed by -1; page_indices = (page_table[r, i >> bits] << bits) | (i & mask).
 // Equal values are resolved towards the LOWER index, so the selected set is exactly
-// torch.argsort(-scores, stable=True)[:k] — stricter than the reference, which leaves the
-// choice among exact duplicates unspecified.
+// torch.argsort(-scores, stable=True)[:k] - stricter than the reference, which leaves the
+// choice among exact duplicates unspecified.  The order of a row's output is a function of
+// the row alone (no atomics decide a position), so a rerun writes the same bytes.
 //
-// One CTA of 1024 threads per row.  The selection is a most-significant-digit radix
-// select on an order-preserving 32-bit key (digits of 12 + 12 + 8 bits) over a
-// CANDIDATE list held in shared memory.  The candidate list is built in one of two ways:
+// A row is the work of one CTA of 512 threads, or of a cluster of two (rows beyond 16 K
+// scores while the device has room: two CTAs fit an SM, so 128 rows keep all 148 SMs busy
+// and the longest row's scan is halved).
 //
-//   sampled path (long rows, n >= 4k): 2048 evenly spaced samples give a 12-bit digit
-//     that, with overwhelming probability, bounds the k-th value from below; ONE pass
-//     over the row then parks every element at or above that digit (a few thousand
-//     entries).  If the sample misled (fewer than k parked, or more than fit) the row
-//     falls back to the exact path.
-//   exact path: pass 1 histograms the top digit over the row, pass 2 emits everything
-//     above the threshold digit and parks the threshold digit's members; when they do
-//     not fit in shared memory (heavily duplicated scores) the two lower levels re-read
-//     the row instead.
+// Fast path (n >= 4k): 2048 evenly spaced samples give a 12-bit key digit that bounds the
+// k-th value from below with a 5-sigma margin.  ONE pass over the row then parks every
+// element at or above it - a few hundred more than k - as (key, index) pairs in the lead
+// CTA's shared memory: every warp owns a segment of the candidate list and compacts into
+// it with one ballot per 32 elements, no atomics and no scans; the second CTA of a cluster
+// writes its segments through distributed shared memory.  Among the candidates one
+// 4096-bin histogram of (key - key_lo) >> 12 resolves 20 key bits; the handful of
+// candidates in the threshold bin are then ranked exactly by (key, lower index first), which
+// also settles ties: the first of them take the last output positions, the candidates above the bin the
+// positions before, from per-segment prefix sums.  The row's page-table entries wait in shared memory.
 //
-// If more values equal the final threshold than are still needed, one ordered pass over
-// the row takes the lowest indices among them.  Shared-memory counters are bumped once
-// per warp (ballot + popcount), not once per element.  No global scratch memory is used
-// and nothing is allocated.
+// Exact path (short rows, a sample that misled, duplicates by the thousand): a three-level
+// radix select (12 + 12 + 8 key bits) with one pass over the row per level and an ordered
+// emit pass, by the lead CTA alone.
+//
+// No global scratch memory is used and nothing is allocated.
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
 
@@ -35,12 +38,16 @@
 namespace wuda {
 namespace topk {
 
-constexpr int kThreads = 1024;
+constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
 constexpr int kBins = 4096;
 constexpr int kCandCap = 8192;
 constexpr int kSamples = 2048;
-constexpr int kMaxCluster = 4;  // CTAs that may share one row's scan (thread-block cluster, distributed shared memory)
+constexpr int kTieCap = 2048;       // candidates of the threshold bin that are ranked pairwise
+constexpr int kMaxCluster = 2;
+constexpr int kMaxSeg = kMaxCluster * kWarps;
+constexpr int kLoadBatch = 4;       // 16-byte loads in flight per thread in the scan (more only queue up in the L2)
+constexpr int kPageCache = 1024;    // page-table entries of a row kept in shared memory (64 K scores at 64 per page)
 
 struct Params {
     const float* scores;
@@ -66,90 +73,48 @@ __device__ __forceinline__ float float_of_key(uint32_t key) {   // inverse of ke
     return __uint_as_float((key & 0x80000000u) ? (key & 0x7FFFFFFFu) : ~key);
 }
 
+// Bin i of the histogram lives at word i + (i >> 5): a thread's run of 8 consecutive bins and the runs of the
+// 31 other lanes then fall into 32 different banks (unpadded, every fourth lane would collide).
+__device__ __forceinline__ int hslot(uint32_t bin) { return static_cast<int>(bin + (bin >> 5)); }
+
 struct Shared {
-    uint32_t hist[kBins];
-    uint32_t cand_key[kCandCap];
-    int32_t cand_idx[kCandCap];
+    uint32_t hist[kBins + kBins / 32];
+    uint2 cand[kCandCap];            // (key, index)
+    uint32_t tie_key[kTieCap];
+    int32_t tie_idx[kTieCap];
+    int32_t pages[kPageCache];       // the row's page-table entries
+    uint32_t seg_cnt[kMaxSeg];
+    uint32_t seg_off[kMaxSeg];
     uint32_t warp_tot[kWarps];
     uint32_t warp_excl[kWarps];
-    uint32_t sel_digit, sel_above;
-    uint32_t out_count, cand_count;
+    uint32_t sel_digit, sel_above, sel_count;
+    uint32_t tie_count;
+    uint32_t total;
+    int pages_cached;
 };
 
-// f(index, value, valid) for every element of the row.  Every thread of the CTA makes
-// the same number of calls (valid = false past the end), so f may use full-warp votes.
-// Loads are issued kBatch at a time before any is consumed: the row comes from L2 (the
-// logits kernel has just written it) and a dependent load-use chain per 16 bytes would
-// leave the pass bound by L2 latency.
-constexpr int kBatch = 4;
-template <typename F>
-__device__ __forceinline__ void for_each_elem(const float* row, int n, bool vec_ok, F f) {
-    if (vec_ok) {
-        const int n4 = n >> 2;
-        const float4* row4 = reinterpret_cast<const float4*>(row);
-        for (int base = 0; base < n4; base += kThreads * kBatch) {
-            float4 v[kBatch];
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int i = base + u * kThreads + threadIdx.x;
-                v[u] = i < n4 ? __ldcg(row4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int i = base + u * kThreads + threadIdx.x;
-                const bool valid = i < n4;
-                f(4 * i + 0, v[u].x, valid);
-                f(4 * i + 1, v[u].y, valid);
-                f(4 * i + 2, v[u].z, valid);
-                f(4 * i + 3, v[u].w, valid);
-            }
-        }
-        const int i = (n4 << 2) + threadIdx.x;   // at most 3 leftover elements
-        if ((n & 3) != 0) f(i, i < n ? row[i] : 0.f, i < n);
-    } else {
-        for (int base = 0; base < n; base += kThreads * kBatch) {
-            float v[kBatch];
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int i = base + u * kThreads + threadIdx.x;
-                v[u] = i < n ? row[i] : 0.f;
-            }
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const int i = base + u * kThreads + threadIdx.x;
-                f(i, v[u], i < n);
-            }
-        }
-    }
-}
-
-// Reserves one slot per lane with `pred` set by bumping `counter` once per warp.
-// Must be called by all 32 lanes of the warp.
-__device__ __forceinline__ uint32_t warp_reserve(bool pred, uint32_t* counter) {
-    const uint32_t mask = __ballot_sync(0xffffffffu, pred);
-    if (mask == 0) return 0;
-    const uint32_t lane = threadIdx.x & 31;
-    uint32_t base = 0;
-    if (lane == (__ffs(mask) - 1)) base = atomicAdd(counter, __popc(mask));
-    base = __shfl_sync(0xffffffffu, base, __ffs(mask) - 1);
-    return base + __popc(mask & ((1u << lane) - 1u));
-}
-
 __device__ __forceinline__ void zero_hist(Shared& s, int nbins) {
-    for (int i = threadIdx.x; i < nbins; i += kThreads) s.hist[i] = 0;
+    for (int i = threadIdx.x; i < nbins + nbins / 32; i += kThreads) s.hist[i] = 0;
 }
 
-// Finds the digit T with  count(digit > T) < need <= count(digit >= T)  and leaves
-// T in s.sel_digit and count(digit > T) in s.sel_above.  Needs 1 <= need <= total.
+// Finds the digit T with  count(digit > T) < need <= count(digit >= T)  and leaves T in
+// s.sel_digit, count(digit > T) in s.sel_above and count(digit == T) in s.sel_count.
+// Needs 1 <= need <= total and nbins a multiple of 32 * kWarps or at most 256.  Two barriers: every
+// warp sums its run of bins (thread = a few consecutive bins), all warps then read the 16 warp totals,
+// and the one warp whose run holds the threshold locates it with a shuffle scan.  The histogram must be
+// complete on entry (caller's barrier) and is unchanged on exit.
 __device__ __forceinline__ void find_threshold(Shared& s, int nbins, uint32_t need) {
-    const int per = nbins >= kThreads ? nbins / kThreads : 1;
-    const int lo = threadIdx.x * per;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int per = nbins >= kThreads ? nbins / kThreads : 1;     // bins per thread
+    const int lo = threadIdx.x * per;
+    uint32_t h[kBins / kThreads];
     uint32_t local = 0;
-    if (lo < nbins)
-        for (int b = 0; b < per; ++b) local += s.hist[lo + b];
-    // suffix sums: v = sum of `local` over threads >= this one
-    uint32_t v = local;
+#pragma unroll
+    for (int b = 0; b < kBins / kThreads; ++b) {
+        h[b] = (b < per && lo + b < nbins) ? s.hist[hslot(lo + b)] : 0u;
+        local += h[b];
+    }
+    uint32_t v = local;   // suffix sums inside the warp: v = sum of `local` over lanes >= this one
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         const uint32_t t = __shfl_down_sync(0xffffffffu, v, o);
@@ -157,29 +122,48 @@ __device__ __forceinline__ void find_threshold(Shared& s, int nbins, uint32_t ne
     }
     if (lane == 0) s.warp_tot[warp] = v;
     __syncthreads();
+    uint32_t above = 0;   // count in the bins of the warps behind this one (higher digits)
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) above += w > warp ? s.warp_tot[w] : 0u;
+    uint32_t running = above + v - local;   // count in digits above this thread's bins
+#pragma unroll
+    for (int b = kBins / kThreads - 1; b >= 0; --b) {
+        if (running < need && need <= running + h[b]) {      // true for exactly one (thread, b)
+            s.sel_digit = lo + b;
+            s.sel_above = running;
+            s.sel_count = h[b];
+        }
+        running += h[b];
+    }
+    __syncthreads();
+}
+
+// Exclusive prefix sum of `count` over the CTA's threads (thread order) and the CTA total.  Three barriers.
+__device__ __forceinline__ uint32_t block_exclusive_scan(Shared& s, uint32_t count, uint32_t* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t v = count;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+    }
+    __syncthreads();                                  // the arrays below may still be read from an earlier scan
+    if (lane == 31) s.warp_tot[warp] = v;
+    __syncthreads();
     if (warp == 0) {
-        const uint32_t mine = s.warp_tot[lane];
-        uint32_t w = mine;
+        const uint32_t tot = lane < kWarps ? s.warp_tot[lane] : 0u;
+        uint32_t w = tot;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t t = __shfl_down_sync(0xffffffffu, w, o);
-            if (lane + o < 32) w += t;
+            const uint32_t t = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += t;
         }
-        s.warp_excl[lane] = w - mine;
+        if (lane < kWarps) s.warp_excl[lane] = w - tot;
+        if (lane == 31) s.total = w;
     }
     __syncthreads();
-    uint32_t running = v - local + s.warp_excl[warp];  // count in digits above this thread's range
-    if (lo < nbins) {
-        for (int b = per - 1; b >= 0; --b) {
-            const uint32_t h = s.hist[lo + b];
-            if (running < need && need <= running + h) {
-                s.sel_digit = lo + b;
-                s.sel_above = running;
-            }
-            running += h;
-        }
-    }
-    __syncthreads();
+    *total = s.total;
+    return v - count + s.warp_excl[warp];
 }
 
 __device__ __forceinline__ int32_t page_of(const Params& p, int r, int idx) {
@@ -190,502 +174,390 @@ __device__ __forceinline__ int32_t page_of(const Params& p, int r, int idx) {
                                 static_cast<uint32_t>(idx & ((1 << p.page_bits) - 1)));
 }
 
-// Writes index `idx` to the next output slot of row r if `pred`; all 32 lanes call it.
-__device__ __forceinline__ void emit(const Params& p, Shared& s, int r, int idx, bool pred) {
-    const uint32_t pos = warp_reserve(pred, &s.out_count);
-    if (pred && pos < static_cast<uint32_t>(p.k)) {
+__device__ __forceinline__ void put(const Params& p, int r, uint32_t pos, int idx) {
+    if (pos < static_cast<uint32_t>(p.k)) {
         const int64_t o = static_cast<int64_t>(r) * p.k + pos;
         if (p.raw) p.raw[o] = idx;
         p.page_indices[o] = page_of(p, r, idx);
     }
 }
 
-// Exclusive prefix sum of `count` over the CTA's threads (thread order) and the CTA total.
-// Two barriers; uses warp_tot / warp_excl.
-__device__ __forceinline__ uint32_t block_exclusive_scan(Shared& s, uint32_t count, uint32_t* total) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    uint32_t v = count;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t t = __shfl_up_sync(0xffffffffu, v, o);
-        if (lane >= o) v += t;
-    }
-    if (lane == 31) s.warp_tot[warp] = v;
-    __syncthreads();
-    if (warp == 0) {
-        const uint32_t tot = s.warp_tot[lane];
-        uint32_t w = tot;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t t = __shfl_up_sync(0xffffffffu, w, o);
-            if (lane >= o) w += t;
-        }
-        s.warp_excl[lane] = w - tot;
-        if (lane == 31) s.sel_above = w;             // the total (sel_above is free between selections)
-    }
-    __syncthreads();
-    *total = s.sel_above;
-    return v - count + s.warp_excl[warp];
-}
-
-// Writes the selected candidates (sel(key) true) to the row's output, after the `s.out_count` already
-// written, without atomics: every thread counts its candidates c = tid, tid + 1024, .. (at most 8),
-// one block scan hands out the positions.  All threads must call it; ends with a barrier.
-template <typename Sel>
-__device__ __forceinline__ void emit_candidates(const Params& p, Shared& s, int r, int ncand, Sel sel) {
-    uint32_t mask = 0;
-#pragma unroll
-    for (int j = 0; j < kCandCap / kThreads; ++j) {
-        const int c = threadIdx.x + j * kThreads;
-        if (c < ncand && sel(s.cand_key[c])) mask |= 1u << j;
-    }
-    uint32_t total;
-    const uint32_t base = s.out_count;               // stable: the caller's last barrier is behind us
-    uint32_t pos = base + block_exclusive_scan(s, __popc(mask), &total);
-#pragma unroll
-    for (int j = 0; j < kCandCap / kThreads; ++j) {
-        if ((mask >> j) & 1u) {
-            if (pos < static_cast<uint32_t>(p.k)) {
-                const int idx = s.cand_idx[threadIdx.x + j * kThreads];
-                const int64_t o = static_cast<int64_t>(r) * p.k + pos;
-                if (p.raw) p.raw[o] = idx;
-                p.page_indices[o] = page_of(p, r, idx);
-            }
-            ++pos;
-        }
-    }
-    __syncthreads();                                 // everybody has read out_count and sel_above
-    if (threadIdx.x == 0) s.out_count = base + total;
-    __syncthreads();
-}
-
-// One pass over the row that sorts every element into "emit now", "park as candidate"
-// or "drop" (cls(key) = 2 / 1 / 0).  A thread classifies a whole batch of its elements
-// into two bit masks first; slots in the output and in the candidate list are then
-// reserved once per warp and batch (a warp scan of the per-thread counts and ONE counter
-// bump), instead of a vote and a shared-memory atomic round trip per element.
-constexpr int kClsBatch = 4;   // 16 elements per thread and batch: fits the 64 registers a thread of a 1024-thread CTA can have
-// The pass covers elements [lo, hi) of the row (lo a multiple of 4); candidates go to
-// `dst`, which may be another CTA's shared memory within the cluster; emitted indices
-// are counted in `dst` as well.
-template <typename Cls>
-__device__ __forceinline__ void classify_pass(const float* row, int lo, int hi, bool vec_ok, const Params& p,
-                                              Shared& dst, int r, Cls cls) {
-    Shared& s = dst;
-    const int n = hi;
-    const uint32_t lane = threadIdx.x & 31;
-    auto reserve = [&](uint32_t count, uint32_t* counter) -> uint32_t {   // exclusive offset for this lane
-        uint32_t incl = count;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= static_cast<uint32_t>(o)) incl += t;
-        }
-        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-        uint32_t base = 0;
-        if (total != 0) {
-            if (lane == 31) base = atomicAdd(counter, total);
-            base = __shfl_sync(0xffffffffu, base, 31);
-        }
-        return base + incl - count;
-    };
-    auto put_emit = [&](uint32_t pos, int idx) {
-        if (pos < static_cast<uint32_t>(p.k)) {
-            const int64_t o = static_cast<int64_t>(r) * p.k + pos;
-            if (p.raw) p.raw[o] = idx;
-            p.page_indices[o] = page_of(p, r, idx);
-        }
-    };
-    auto put_park = [&](uint32_t slot, int idx, uint32_t key) {
-        if (slot < static_cast<uint32_t>(kCandCap)) {
-            s.cand_key[slot] = key;
-            s.cand_idx[slot] = idx;
-        }
-    };
+// f(index, value, valid) for every element of the row, every thread making the same number of calls.
+template <typename F>
+__device__ __forceinline__ void for_each_elem(const float* row, int n, bool vec_ok, F f) {
     if (vec_ok) {
         const int n4 = n >> 2;
         const float4* row4 = reinterpret_cast<const float4*>(row);
-        for (int base = lo >> 2; base < n4; base += kThreads * kClsBatch) {
-            float4 v[kClsBatch];
+        for (int base = 0; base < n4; base += kThreads * 4) {
+            float4 v[4];
 #pragma unroll
-            for (int u = 0; u < kClsBatch; ++u) {
+            for (int u = 0; u < 4; ++u) {
                 const int i = base + u * kThreads + threadIdx.x;
                 v[u] = i < n4 ? __ldcg(row4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            uint32_t park = 0, emit_m = 0;
 #pragma unroll
-            for (int u = 0; u < kClsBatch; ++u) {
-                const bool valid = base + u * kThreads + static_cast<int>(threadIdx.x) < n4;
-                const float x[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int cl = valid ? cls(x[c]) : 0;
-                    park |= static_cast<uint32_t>(cl == 1) << (u * 4 + c);
-                    emit_m |= static_cast<uint32_t>(cl == 2) << (u * 4 + c);
-                }
-            }
-            uint32_t park_at = reserve(__popc(park), &s.cand_count);
-            uint32_t emit_at = reserve(__popc(emit_m), &s.out_count);
-            if ((park | emit_m) != 0) {
-#pragma unroll
-                for (int u = 0; u < kClsBatch; ++u) {
-                    const int i = base + u * kThreads + threadIdx.x;
-                    const float x[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        if ((park >> (u * 4 + c)) & 1u) put_park(park_at++, 4 * i + c, key_of(x[c]));
-                        if ((emit_m >> (u * 4 + c)) & 1u) put_emit(emit_at++, 4 * i + c);
-                    }
-                }
+            for (int u = 0; u < 4; ++u) {
+                const int i = base + u * kThreads + threadIdx.x;
+                const bool valid = i < n4;
+                f(4 * i + 0, v[u].x, valid);
+                f(4 * i + 1, v[u].y, valid);
+                f(4 * i + 2, v[u].z, valid);
+                f(4 * i + 3, v[u].w, valid);
             }
         }
-        if ((n & 3) != 0) {   // at most 3 leftover elements
-            const int i = (n4 << 2) + threadIdx.x;
-            const float x = i < n ? row[i] : 0.f;
-            const uint32_t key = key_of(x);
-            const int cl = (i < n && lo < hi) ? cls(x) : 0;
-            const uint32_t slot = warp_reserve(cl == 1, &s.cand_count);
-            if (cl == 1) put_park(slot, i, key);
-            const uint32_t pos = warp_reserve(cl == 2, &s.out_count);
-            if (cl == 2) put_emit(pos, i);
-        }
+        const int i = (n4 << 2) + threadIdx.x;   // at most 3 leftover elements
+        if ((n & 3) != 0) f(i, i < n ? __ldcg(row + i) : 0.f, i < n);
     } else {
-        for (int base = lo; base < n; base += kThreads) {
+        for (int base = 0; base < n; base += kThreads) {
             const int i = base + threadIdx.x;
-            const float x = i < n ? row[i] : 0.f;
-            const uint32_t key = key_of(x);
-            const int cl = i < n ? cls(x) : 0;
-            const uint32_t slot = warp_reserve(cl == 1, &s.cand_count);
-            if (cl == 1) put_park(slot, i, key);
-            const uint32_t pos = warp_reserve(cl == 2, &s.out_count);
-            if (cl == 2) put_emit(pos, i);
+            f(i, i < n ? __ldcg(row + i) : 0.f, i < n);
         }
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) topk_kernel(const Params p) {
-    pdl_launch_dependents();
-    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
+// ---------------------------------------------------------------------------------------------
+// Exact path: three histogram levels over the whole row, then one ordered pass that writes the
+// values above the threshold and the lowest-indexed `need3` of those equal to it.  One CTA.
+__device__ void exact_select(const Params& p, Shared& s, const float* row, int n, int r, bool vec_ok) {
+    const int k = p.k;
+    zero_hist(s, kBins);
+    __syncthreads();
+    for_each_elem(row, n, vec_ok, [&](int, float x, bool valid) {
+        if (valid) atomicAdd(&s.hist[hslot(key_of(x) >> 20)], 1u);
+    });
+    __syncthreads();
+    find_threshold(s, kBins, static_cast<uint32_t>(k));
+    const uint32_t d1 = s.sel_digit;
+    const uint32_t need1 = static_cast<uint32_t>(k) - s.sel_above;
+    __syncthreads();
+    zero_hist(s, kBins);
+    __syncthreads();
+    for_each_elem(row, n, vec_ok, [&](int, float x, bool valid) {
+        const uint32_t key = key_of(x);
+        if (valid && (key >> 20) == d1) atomicAdd(&s.hist[hslot((key >> 8) & 0xFFFu)], 1u);
+    });
+    __syncthreads();
+    find_threshold(s, kBins, need1);
+    const uint32_t prefix24 = (d1 << 12) | s.sel_digit;
+    const uint32_t need2 = need1 - s.sel_above;
+    __syncthreads();
+    zero_hist(s, 256);
+    __syncthreads();
+    for_each_elem(row, n, vec_ok, [&](int, float x, bool valid) {
+        const uint32_t key = key_of(x);
+        if (valid && (key >> 8) == prefix24) atomicAdd(&s.hist[hslot(key & 0xFFu)], 1u);
+    });
+    __syncthreads();
+    find_threshold(s, 256, need2);
+    const uint32_t thr = (prefix24 << 8) | s.sel_digit;
+    const uint32_t need3 = need2 - s.sel_above;      // values equal to thr still taken: the lowest indices
+    __syncthreads();
+    // ordered emit: thread t owns the contiguous chunk [beg, end)
+    const int chunk = (n + kThreads - 1) / kThreads;
+    const int beg = min(n, static_cast<int>(threadIdx.x) * chunk), end = min(n, beg + chunk);
+    uint32_t gt = 0, eq = 0;
+    for (int i = beg; i < end; ++i) {
+        const uint32_t key = key_of(__ldcg(row + i));
+        gt += key > thr;
+        eq += key == thr;
+    }
+    uint32_t total_gt, total_eq;
+    uint32_t at_gt = block_exclusive_scan(s, gt, &total_gt);
+    uint32_t at_eq = block_exclusive_scan(s, eq, &total_eq);
+    for (int i = beg; i < end; ++i) {
+        const uint32_t key = key_of(__ldcg(row + i));
+        if (key > thr) put(p, r, at_gt++, i);
+        else if (key == thr) {
+            if (at_eq < need3) put(p, r, total_gt + at_eq, i);
+            ++at_eq;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// One ballot per 32 elements: the lanes whose value is a candidate store (key, index) at the warp's
+// running count plus their rank among the lanes below them.
+__device__ __forceinline__ void park(bool pred, float x, int idx, uint2* seg, uint32_t segcap, uint32_t lane_lt,
+                                     uint32_t& cnt) {
+    const uint32_t b = __ballot_sync(0xffffffffu, pred);
+    if (pred) {
+        const uint32_t pos = cnt + __popc(b & lane_lt);
+        if (pos < segcap) seg[pos] = make_uint2(key_of(x), static_cast<uint32_t>(idx));
+    }
+    cnt += __popc(b);
+}
+
+// Four elements per lane: the four ballots and their counts are independent of each other, so they overlap;
+// only the running count links one call to the next.
+__device__ __forceinline__ void park4(bool valid, const float4& v, int i4, float x_lo, uint2* seg, uint32_t segcap,
+                                      uint32_t lane_lt, uint32_t& cnt) {
+    const bool p0 = valid && v.x >= x_lo, p1 = valid && v.y >= x_lo, p2 = valid && v.z >= x_lo, p3 = valid && v.w >= x_lo;
+    const uint32_t b0 = __ballot_sync(0xffffffffu, p0), b1 = __ballot_sync(0xffffffffu, p1);
+    const uint32_t b2 = __ballot_sync(0xffffffffu, p2), b3 = __ballot_sync(0xffffffffu, p3);
+    const uint32_t at0 = cnt, at1 = at0 + __popc(b0), at2 = at1 + __popc(b1), at3 = at2 + __popc(b2);
+    cnt = at3 + __popc(b3);
+    const uint32_t idx = 4u * static_cast<uint32_t>(i4);
+    if (p0) {
+        const uint32_t pos = at0 + __popc(b0 & lane_lt);
+        if (pos < segcap) seg[pos] = make_uint2(key_of(v.x), idx);
+    }
+    if (p1) {
+        const uint32_t pos = at1 + __popc(b1 & lane_lt);
+        if (pos < segcap) seg[pos] = make_uint2(key_of(v.y), idx + 1);
+    }
+    if (p2) {
+        const uint32_t pos = at2 + __popc(b2 & lane_lt);
+        if (pos < segcap) seg[pos] = make_uint2(key_of(v.z), idx + 2);
+    }
+    if (p3) {
+        const uint32_t pos = at3 + __popc(b3 & lane_lt);
+        if (pos < segcap) seg[pos] = make_uint2(key_of(v.w), idx + 3);
+    }
+}
+
+// Output position `pos` of row r gets index idx, translated with the row's page table: from the copy in shared
+// memory when the row's pages fit it (s.pages_cached), else from global memory.
+__device__ __forceinline__ void put_cached(const Params& p, const Shared& s, int r, uint32_t pos, int idx) {
+    if (pos >= static_cast<uint32_t>(p.k)) return;
+    const int64_t o = static_cast<int64_t>(r) * p.k + pos;
+    if (p.raw) p.raw[o] = idx;
+    int32_t out = idx;
+    if (p.page_table) {
+        const int pg = idx >> p.page_bits;
+        const int32_t page = pg < s.pages_cached
+                                 ? s.pages[pg]
+                                 : __ldg(p.page_table + static_cast<int64_t>(r / p.rows_per_table_row) * p.pt_stride + pg);
+        out = static_cast<int32_t>((static_cast<uint32_t>(page) << p.page_bits) |
+                                   static_cast<uint32_t>(idx & ((1 << p.page_bits) - 1)));
+    }
+    p.page_indices[o] = out;
+}
+
+__global__ void __launch_bounds__(kThreads, 2) topk_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     Shared& s = *reinterpret_cast<Shared*>(smem_raw);
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const int crank = static_cast<int>(cluster.block_rank());
     const int csize = static_cast<int>(cluster.num_blocks());
-    Shared& lead = *cluster.map_shared_rank(&s, 0);   // the cluster leader's shared memory
+    Shared& lead = *cluster.map_shared_rank(&s, 0);   // the lead CTA's shared memory
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t lane_lt = (1u << lane) - 1u;
+    const int k = p.k;
+    // shared memory only, so it may run while the kernel ahead is still finishing
+    zero_hist(s, kBins);
+    if (threadIdx.x == 0) s.tie_count = 0;
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
+    bool clean = true;   // the histogram and the tie counter are zero
 
-    // A cluster of csize CTAs (1, 2 or 4: the host uses the SMs that rows alone would leave
-    // idle) takes one row at a time.  Only the scan of a long row
-    // is shared (every CTA classifies its slice and parks candidates in the leader's
-    // shared memory); the selection among the candidates runs in the leader alone.
     for (int r = blockIdx.x / csize; r < p.rows; r += gridDim.x / csize) {
         const float* row = p.scores + static_cast<int64_t>(r) * p.score_stride;
         int n = p.seq_lens[r];
         n = n < 0 ? 0 : n;
         if (static_cast<int64_t>(n) > p.score_stride) n = static_cast<int>(p.score_stride);
-        const int k = p.k;
 
-        // A row that fits the candidate list whole needs neither sampling nor classification.
-        const bool small = n <= kCandCap;
-        const bool sampled = !small && n >= 4 * k && k <= kCandCap / 2;
-        if (crank != 0 && !sampled) continue;   // short rows are the leader's alone
         if (n <= k) {  // everything is selected: [0..n) then -1
-            for (int i = threadIdx.x; i < k; i += kThreads) {
-                const int64_t o = static_cast<int64_t>(r) * k + i;
-                const int idx = i < n ? i : -1;
-                if (p.raw) p.raw[o] = idx;
-                p.page_indices[o] = idx >= 0 ? page_of(p, r, idx) : -1;
-            }
-            continue;
-        }
-
-        const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
-        zero_hist(s, kBins);
-        if (threadIdx.x == 0) {
-            s.out_count = 0;
-            s.cand_count = 0;
-        }
-        __syncthreads();
-
-        // ------------------------------------------------ sampled path: build the candidate list
-        bool have_all = false;      // candidate list holds EVERY element at or above some digit
-        int ncand = 0;
-        uint32_t key_lo = 0;        // lower bound of the sampled scan's candidate keys
-        uint32_t thr = 0, need3 = 0;   // threshold key; how many values equal to it are still taken
-        bool take_all_equal = true;
-        bool done = false;
-        if (small) {
-            // ---------------------------------------------------------- short rows: keys stay in registers
-            // Thread t holds elements 4 (t + 1024 j) + c, j < 2, c < 4.  Three histogram levels
-            // (12 + 12 + 8 key bits) find the threshold, one scan hands out the output positions.
-            uint32_t key[8];
-            uint32_t valid = 0;
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int e0 = 4 * (threadIdx.x + j * kThreads);
-                if (vec_ok && e0 + 3 < n) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(row + e0));
-                    key[4 * j] = key_of(v.x), key[4 * j + 1] = key_of(v.y), key[4 * j + 2] = key_of(v.z), key[4 * j + 3] = key_of(v.w);
-                    valid |= 0xFu << (4 * j);
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const bool in = e0 + c < n;
-                        key[4 * j + c] = in ? key_of(row[e0 + c]) : 0u;
-                        valid |= static_cast<uint32_t>(in) << (4 * j + c);
-                    }
-                }
-            }
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-                if ((valid >> e) & 1u) atomicAdd(&s.hist[key[e] >> 20], 1u);
-            __syncthreads();
-            find_threshold(s, kBins, static_cast<uint32_t>(k));
-            const uint32_t d1 = s.sel_digit;
-            const uint32_t need1 = static_cast<uint32_t>(k) - s.sel_above;
-            __syncthreads();
-            zero_hist(s, kBins);
-            __syncthreads();
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-                if (((valid >> e) & 1u) && (key[e] >> 20) == d1) atomicAdd(&s.hist[(key[e] >> 8) & 0xFFFu], 1u);
-            __syncthreads();
-            find_threshold(s, kBins, need1);
-            const uint32_t d2 = s.sel_digit;
-            const uint32_t need2 = need1 - s.sel_above;
-            __syncthreads();
-            zero_hist(s, 256);
-            __syncthreads();
-            const uint32_t prefix24 = (d1 << 12) | d2;
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-                if (((valid >> e) & 1u) && (key[e] >> 8) == prefix24) atomicAdd(&s.hist[key[e] & 0xFFu], 1u);
-            __syncthreads();
-            find_threshold(s, 256, need2);
-            const uint32_t d3 = s.sel_digit;
-            need3 = need2 - s.sel_above;
-            thr = (prefix24 << 8) | d3;
-            take_all_equal = (s.hist[d3] == need3);
-            __syncthreads();
-            uint32_t mask = 0;
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-                if (((valid >> e) & 1u) && (key[e] > thr || (key[e] == thr && take_all_equal))) mask |= 1u << e;
-            uint32_t total;
-            uint32_t pos = block_exclusive_scan(s, __popc(mask), &total);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                if ((mask >> e) & 1u) {
-                    const int idx = 4 * (threadIdx.x + (e >> 2) * kThreads) + (e & 3);
-                    const int64_t o = static_cast<int64_t>(r) * k + pos;
+            if (crank == 0)
+                for (int i = threadIdx.x; i < k; i += kThreads) {
+                    const int64_t o = static_cast<int64_t>(r) * k + i;
+                    const int idx = i < n ? i : -1;
                     if (p.raw) p.raw[o] = idx;
-                    p.page_indices[o] = page_of(p, r, idx);
-                    ++pos;
+                    p.page_indices[o] = idx >= 0 ? page_of(p, r, idx) : -1;
+                }
+            continue;   // (no shared memory was touched: no cluster barrier needed)
+        }
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
+        bool done = false;
+
+        if (n >= 4 * k && 2 * k <= kCandCap) {
+            // ---------------------------------------------------------------- fast path
+            if (!clean) {
+                zero_hist(s, kBins);
+                if (threadIdx.x == 0) s.tie_count = 0;
+            }
+            // every CTA of the cluster takes the same samples and finds the same bound; the lead CTA also
+            // fetches the row's page-table entries, which the emit at the end then finds in shared memory
+            // (an aligned row is sampled in 512 evenly spaced groups of four neighbours - one 16-byte load per
+            // thread; neighbours that move together only widen the margin's miss rate, and a miss is caught)
+            float v[kSamples / kThreads];
+            if (vec_ok) {
+                const int at = static_cast<int>(static_cast<long long>(threadIdx.x) * (n >> 2) / kThreads);
+                const float4 q = __ldcg(reinterpret_cast<const float4*>(row) + at);
+                v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+            } else {
+#pragma unroll
+                for (int j = 0; j < kSamples / kThreads; ++j) {
+                    const int t = threadIdx.x + j * kThreads;
+                    v[j] = __ldcg(row + static_cast<int>(static_cast<long long>(t) * n / kSamples));
                 }
             }
-            __syncthreads();
-            if (threadIdx.x == 0) s.out_count = total;
-            __syncthreads();
-            done = true;
-        }
-        if (sampled) {
-            cluster.sync();   // the leader's counters are zeroed before anyone parks into them
-            for (int t = threadIdx.x; t < kSamples; t += kThreads) {
-                const int i = static_cast<int>(static_cast<long long>(t) * n / kSamples);
-                atomicAdd(&s.hist[key_of(row[i]) >> 20], 1u);
+            if (crank == 0 && p.page_table) {
+                const int pages = min(kPageCache, ((n - 1) >> p.page_bits) + 1);
+                const int32_t* table = p.page_table + static_cast<int64_t>(r / p.rows_per_table_row) * p.pt_stride;
+                for (int i = threadIdx.x; i < pages; i += kThreads) s.pages[i] = __ldg(table + i);
+                if (threadIdx.x == 0) s.pages_cached = pages;
             }
+            __syncthreads();                          // the zeroes are in place
+#pragma unroll
+            for (int j = 0; j < kSamples / kThreads; ++j) atomicAdd(&s.hist[hslot(key_of(v[j]) >> 20)], 1u);
             __syncthreads();
             // expected sample rank of the k-th value, plus a 5-sigma margin
             const float expect = static_cast<float>(kSamples) * static_cast<float>(k) / static_cast<float>(n);
             uint32_t rank = static_cast<uint32_t>(expect + 5.f * sqrtf(expect) + 8.f);
             if (rank > static_cast<uint32_t>(kSamples)) rank = kSamples;
             find_threshold(s, kBins, rank);
-            const uint32_t d_lo = s.sel_digit;
-            __syncthreads();
-            // every CTA of the cluster found the same d_lo (same samples); each scans a slice
+            const uint32_t key_lo = s.sel_digit << 20;
+            // digit >= d_lo  <=>  key >= key_lo  <=>  x >= the float with that key: one compare per element
+            // (an unordered bound selects nothing and the row falls back to the exact path)
+            const float x_lo = float_of_key(key_lo);
+            zero_hist(s, kBins);                    // level A's histogram (the lead CTA's is the one used); the
+                                                    // barrier at the end of the scan covers it
+            // ---- the scan: this CTA's slice of the row, candidates into this warp's segment of the lead's list
+            const int nseg = csize * kWarps;
+            const uint32_t segcap = kCandCap / nseg;
+            const int seg = crank * kWarps + warp;
+            uint2* seg_ptr = lead.cand + seg * segcap;
+            uint32_t cnt = 0;
             const int slice = ((n + csize - 1) / csize + 3) & ~3;
             const int lo = min(n, crank * slice), hi = min(n, lo + slice);
-            // digit >= d_lo  <=>  key >= d_lo << 20  <=>  x >= the float with that key: one
-            // compare per element (an unordered bound selects nothing and the row falls back)
-            key_lo = d_lo << 20;
-            const float x_lo = float_of_key(key_lo);
-            classify_pass(row, lo, hi, vec_ok, p, lead, r, [&](float x) { return x >= x_lo ? 1 : 0; });
-            zero_hist(s, kBins);
-            cluster.sync();   // all slices are parked
-            if (crank != 0) continue;
-            const uint32_t total = s.cand_count;
-            have_all = total >= static_cast<uint32_t>(k) && total <= static_cast<uint32_t>(kCandCap);
-            ncand = have_all ? static_cast<int>(total) : 0;
-            __syncthreads();
-            if (!have_all && threadIdx.x == 0) s.cand_count = 0;
-            __syncthreads();
-        }
-
-        const int ncand_pad = (ncand + kThreads - 1) / kThreads * kThreads;
-        if (have_all && !small) {
-            // ------------------------------------------------ candidates from the sampled scan
-            // Their keys start at key_lo = d_lo << 20.  A 4096-bin histogram of
-            // (key - key_lo) >> 12 resolves 20 key bits at once with little contention (the
-            // candidates spread over many bins); one more level on the low 12 bits finishes.
-            // Keys beyond the window share the last bin; if the threshold lands there
-            // (never for ordinary data) the generic three-level path below takes over.
-            for (int c = threadIdx.x; c < ncand; c += kThreads)
-                atomicAdd(&s.hist[min((s.cand_key[c] - key_lo) >> 12, static_cast<uint32_t>(kBins - 1))], 1u);
-            __syncthreads();
-            find_threshold(s, kBins, static_cast<uint32_t>(k));
-            const uint32_t bin_a = s.sel_digit;
-            const uint32_t need_a = static_cast<uint32_t>(k) - s.sel_above;
-            __syncthreads();
-            zero_hist(s, kBins);
-            __syncthreads();
-            if (bin_a != static_cast<uint32_t>(kBins - 1)) {
-                const uint32_t prefix20 = (key_lo >> 12) + bin_a;
-                for (int c = threadIdx.x; c < ncand; c += kThreads) {
-                    const uint32_t key = s.cand_key[c];
-                    if ((key >> 12) == prefix20) atomicAdd(&s.hist[key & 0xFFFu], 1u);
+            if (vec_ok) {
+                // two half-batches of loads are always in flight: the next is issued before the current is used
+                const int hi4 = hi >> 2;             // full 16-byte groups end here (hi is a multiple of 4, or n)
+                const float4* row4 = reinterpret_cast<const float4*>(row);
+                constexpr int kHalf = kLoadBatch / 2;
+                const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 a[kHalf], b[kHalf];
+                int base = (lo >> 2) + threadIdx.x;
+#pragma unroll
+                for (int u = 0; u < kHalf; ++u) a[u] = base + u * kThreads < hi4 ? __ldcg(row4 + base + u * kThreads) : zero4;
+                while (base - static_cast<int>(threadIdx.x) < hi4) {
+                    const int next = base + kHalf * kThreads;
+#pragma unroll
+                    for (int u = 0; u < kHalf; ++u) b[u] = next + u * kThreads < hi4 ? __ldcg(row4 + next + u * kThreads) : zero4;
+#pragma unroll
+                    for (int u = 0; u < kHalf; ++u) {
+                        const int i = base + u * kThreads;
+                        park4(i < hi4, a[u], i, x_lo, seg_ptr, segcap, lane_lt, cnt);
+                    }
+                    const int next2 = next + kHalf * kThreads;
+#pragma unroll
+                    for (int u = 0; u < kHalf; ++u) a[u] = next2 + u * kThreads < hi4 ? __ldcg(row4 + next2 + u * kThreads) : zero4;
+#pragma unroll
+                    for (int u = 0; u < kHalf; ++u) {
+                        const int i = next + u * kThreads;
+                        park4(i < hi4, b[u], i, x_lo, seg_ptr, segcap, lane_lt, cnt);
+                    }
+                    base = next2;
                 }
-                __syncthreads();
-                find_threshold(s, kBins, need_a);
-                const uint32_t d_b = s.sel_digit;
-                need3 = need_a - s.sel_above;
-                take_all_equal = (s.hist[d_b] == need3);
-                thr = (prefix20 << 12) | d_b;
-                __syncthreads();
-                {
-                    const uint32_t t = thr;
-                    const bool eq = take_all_equal;
-                    emit_candidates(p, s, r, ncand, [&](uint32_t key) { return key > t || (key == t && eq); });
-                }
-                done = true;
-            }
-        }
-        if (!done) {
-        // ------------------------------------------------ level 1: the top 12 bits
-        uint32_t d1, need1;
-        bool parked;                // the threshold digit's members are in the candidate list
-        if (have_all) {
-            for (int c = threadIdx.x; c < ncand; c += kThreads) atomicAdd(&s.hist[s.cand_key[c] >> 20], 1u);
-            __syncthreads();
-            find_threshold(s, kBins, static_cast<uint32_t>(k));
-            d1 = s.sel_digit;
-            need1 = static_cast<uint32_t>(k) - s.sel_above;
-            parked = true;
-            __syncthreads();
-            emit_candidates(p, s, r, ncand, [&](uint32_t key) { return (key >> 20) > d1; });
-            zero_hist(s, kBins);
-            __syncthreads();
-        } else {
-            for_each_elem(row, n, vec_ok, [&](int, float x, bool valid) {
-                if (valid) atomicAdd(&s.hist[key_of(x) >> 20], 1u);
-            });
-            __syncthreads();
-            find_threshold(s, kBins, static_cast<uint32_t>(k));
-            d1 = s.sel_digit;
-            need1 = static_cast<uint32_t>(k) - s.sel_above;   // still needed from digit d1
-            parked = s.hist[d1] <= static_cast<uint32_t>(kCandCap);
-            __syncthreads();
-            // pass 2: emit everything above the digit, park the digit's members
-            classify_pass(row, 0, n, vec_ok, p, s, r, [&](float x) {
-                const uint32_t d = key_of(x) >> 20;
-                return d > d1 ? 2 : ((d == d1 && parked) ? 1 : 0);
-            });
-            zero_hist(s, kBins);
-            __syncthreads();
-            ncand = parked ? static_cast<int>(min(s.cand_count, static_cast<uint32_t>(kCandCap))) : 0;
-        }
-        const int nmem_pad = (ncand + kThreads - 1) / kThreads * kThreads;
-
-        // f(index, key, is_member) over the members of digit d1, with a uniform call
-        // count across the CTA (is_member = false on padding calls)
-        auto for_each_member = [&](auto f) {
-            if (parked) {
-                for (int c = threadIdx.x; c < nmem_pad; c += kThreads) {
-                    const bool in = c < ncand;
-                    const uint32_t key = in ? s.cand_key[c] : 0u;
-                    f(in ? s.cand_idx[c] : 0, key, in && (key >> 20) == d1);
+                if (hi == n && lo < hi && (n & 3) != 0 && warp == 0) {   // at most 3 leftover elements, by the last slice's warp 0
+                    const int i = (hi4 << 2) + lane;
+                    const float x = i < n ? __ldcg(row + i) : 0.f;
+                    park(i < n && x >= x_lo, x, i, seg_ptr, segcap, lane_lt, cnt);
                 }
             } else {
-                for_each_elem(row, n, vec_ok, [&](int i, float x, bool valid) {
-                    const uint32_t key = key_of(x);
-                    f(i, key, valid && (key >> 20) == d1);
-                });
-            }
-        };
-
-        // ------------------------------------------------ level 2: the next 12 bits
-        for_each_member([&](int, uint32_t key, bool in) {
-            if (in) atomicAdd(&s.hist[(key >> 8) & 0xFFFu], 1u);
-        });
-        __syncthreads();
-        find_threshold(s, kBins, need1);
-        const uint32_t d2 = s.sel_digit;
-        const uint32_t need2 = need1 - s.sel_above;
-        __syncthreads();
-        zero_hist(s, 256);
-        __syncthreads();
-
-        // ------------------------------------------------ level 3: the last 8 bits
-        const uint32_t prefix24 = (d1 << 12) | d2;
-        for_each_member([&](int, uint32_t key, bool in) {
-            if (in && (key >> 8) == prefix24) atomicAdd(&s.hist[key & 0xFFu], 1u);
-        });
-        __syncthreads();
-        find_threshold(s, 256, need2);
-        const uint32_t d3 = s.sel_digit;
-        need3 = need2 - s.sel_above;
-        const uint32_t ceq = s.hist[d3];
-        thr = (prefix24 << 8) | d3;
-        take_all_equal = (ceq == need3);
-        __syncthreads();
-
-        for_each_member([&](int i, uint32_t key, bool in) {
-            emit(p, s, r, i, in && (key > thr || (key == thr && take_all_equal)));
-        });
-        }
-
-        if (!take_all_equal) {
-            // More duplicates of the threshold value than needed: take the lowest indices.
-            const int chunk = (n + kThreads - 1) / kThreads;
-            const int beg = min(n, static_cast<int>(threadIdx.x) * chunk);
-            const int end = min(n, beg + chunk);
-            uint32_t mine = 0;
-            for (int i = beg; i < end; ++i) mine += (key_of(row[i]) == thr);
-            // exclusive prefix over threads
-            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-            uint32_t v = mine;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t t = __shfl_up_sync(0xffffffffu, v, o);
-                if (lane >= o) v += t;
-            }
-            __syncthreads();
-            if (lane == 31) s.warp_tot[warp] = v;
-            __syncthreads();
-            if (warp == 0) {
-                const uint32_t tot = s.warp_tot[lane];
-                uint32_t w = tot;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t t = __shfl_up_sync(0xffffffffu, w, o);
-                    if (lane >= o) w += t;
+                for (int base = lo; base < hi; base += kThreads) {
+                    const int i = base + threadIdx.x;
+                    const float x = i < hi ? __ldcg(row + i) : 0.f;
+                    park(i < hi && x >= x_lo, x, i, seg_ptr, segcap, lane_lt, cnt);
                 }
-                s.warp_excl[lane] = w - tot;
             }
-            __syncthreads();
-            uint32_t rank = v - mine + s.warp_excl[warp];
-            for (int i = beg; i < end && rank < need3; ++i) {
-                if (key_of(row[i]) == thr) {   // few and scattered: one counter bump each
-                    const uint32_t pos = atomicAdd(&s.out_count, 1u);
-                    if (pos < static_cast<uint32_t>(k)) {
-                        const int64_t o = static_cast<int64_t>(r) * k + pos;
-                        if (p.raw) p.raw[o] = i;
-                        p.page_indices[o] = page_of(p, r, i);
+            if (lane == 0) lead.seg_cnt[seg] = cnt;
+            if (csize > 1) cluster.sync();           // every slice is parked, every count is in
+            else __syncthreads();
+            clean = false;
+
+            if (crank == 0) {
+                // ---- the selection among the candidates, by the lead CTA
+                const uint32_t mine = lane < nseg ? s.seg_cnt[lane] : 0u;     // every warp adds the counts up by itself
+                uint32_t total = mine;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+                bool ok = __all_sync(0xffffffffu, mine <= segcap) && total >= static_cast<uint32_t>(k);
+                if (ok) {
+                    // level A: 20 key bits at once over the candidates' window
+                    for (int g = warp; g < nseg; g += kWarps) {
+                        const uint32_t c = s.seg_cnt[g];
+                        const uint2* cands = s.cand + g * segcap;
+                        for (uint32_t j = lane; j < c; j += 32)
+                            atomicAdd(&s.hist[hslot(min((cands[j].x - key_lo) >> 12, static_cast<uint32_t>(kBins - 1)))], 1u);
                     }
-                    ++rank;
+                    __syncthreads();
+                    find_threshold(s, kBins, static_cast<uint32_t>(k));
+                    const uint32_t bin_a = s.sel_digit;
+                    const uint32_t above_a = s.sel_above;
+                    const uint32_t need_a = static_cast<uint32_t>(k) - above_a;
+                    const uint32_t c_a = s.sel_count;
+                    // keys beyond the window share the last bin, and a bin with thousands of members is a row of
+                    // duplicates: both go to the exact path
+                    ok = bin_a != static_cast<uint32_t>(kBins - 1) && c_a <= static_cast<uint32_t>(kTieCap);
+                    if (ok) {
+                        // One walk over the candidates: those above the threshold bin are counted per segment,
+                        // the bin's own members go to the tie list.
+                        for (int g = warp; g < nseg; g += kWarps) {
+                            const uint32_t c = s.seg_cnt[g];
+                            uint32_t sel = 0;
+                            for (uint32_t j0 = 0; j0 < c; j0 += 32) {
+                                const uint32_t j = j0 + lane;
+                                const uint2 cand = j < c ? s.cand[g * segcap + j] : make_uint2(key_lo, 0u);
+                                const uint32_t key = cand.x;
+                                const uint32_t bin = (key - key_lo) >> 12;
+                                sel += __popc(__ballot_sync(0xffffffffu, j < c && bin > bin_a));
+                                const bool in = j < c && bin == bin_a;
+                                const uint32_t b = __ballot_sync(0xffffffffu, in);
+                                if (b != 0) {
+                                    uint32_t at = 0;
+                                    if (lane == __ffs(b) - 1) at = atomicAdd(&s.tie_count, __popc(b));
+                                    at = __shfl_sync(0xffffffffu, at, __ffs(b) - 1) + __popc(b & lane_lt);
+                                    if (in) {
+                                        s.tie_key[at] = key;
+                                        s.tie_idx[at] = static_cast<int32_t>(cand.y);
+                                    }
+                                }
+                            }
+                            if (lane == 0) s.seg_off[g] = sel;
+                        }
+                        __syncthreads();
+                        // The bin's members ranked exactly - larger key first, lower index first among equals: the
+                        // first need_a of them take the last output positions.  Meanwhile every warp turns the
+                        // segment counts into its segments' first positions.
+                        for (uint32_t t = threadIdx.x; t < c_a; t += kThreads) {
+                            const uint32_t kt = s.tie_key[t];
+                            const int it = s.tie_idx[t];
+                            uint32_t ahead = 0;
+                            for (uint32_t j = 0; j < c_a; ++j) {
+                                const uint32_t kj = s.tie_key[j];
+                                ahead += (kj > kt) || (kj == kt && s.tie_idx[j] < it);
+                            }
+                            if (ahead < need_a) put_cached(p, s, r, above_a + ahead, it);
+                        }
+                        for (int g = warp; g < nseg; g += kWarps) {
+                            uint32_t at = lane < g ? s.seg_off[lane] : 0u;       // positions taken by the segments before
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) at += __shfl_xor_sync(0xffffffffu, at, o);
+                            const uint32_t c = s.seg_cnt[g];
+                            for (uint32_t j0 = 0; j0 < c; j0 += 32) {
+                                const uint32_t j = j0 + lane;
+                                const uint2 cand = j < c ? s.cand[g * segcap + j] : make_uint2(key_lo, 0u);
+                                const bool in = j < c && ((cand.x - key_lo) >> 12) > bin_a;
+                                const uint32_t b = __ballot_sync(0xffffffffu, in);
+                                if (in) put_cached(p, s, r, at + __popc(b & lane_lt), static_cast<int>(cand.y));
+                                at += __popc(b);
+                            }
+                        }
+                        done = true;
+                    }
                 }
+                __syncthreads();
             }
         }
-        __syncthreads();
+        if (!done && crank == 0) {
+            exact_select(p, s, row, n, r, vec_ok);
+            clean = false;
+        }
+        // the next row's candidates must not land in the lead's list while it is still being read
+        if (csize > 1) cluster.sync();
+        else __syncthreads();
     }
 }
 
@@ -729,20 +601,19 @@ extern "C" int wuda_topk(const float* scores, const int32_t* seq_lens, const int
 
     const int smem = static_cast<int>(sizeof(Shared));
     WUDA_CUDA(cudaFuncSetAttribute(topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    // One 1024-thread CTA fills an SM; when there are fewer rows than SMs the spare SMs
-    // join the rows' clusters.
-    // (rows of at most 16 K scores are not worth a cluster barrier: one CTA scans them in a few passes)
-    int kCluster = 1;
-    while (score_stride > 16384 && kCluster < kMaxCluster && rows * kCluster * 2 <= dev.num_sms) kCluster *= 2;
-    const int clusters = rows * kCluster <= dev.num_sms ? rows : dev.num_sms / kCluster;
+    // Two CTAs fit an SM.  Rows beyond 16 K scores are scanned by a cluster of two while every cluster can be
+    // resident at once; otherwise one CTA per row, and a grid-stride loop when there are more rows than places.
+    const int places = 2 * dev.num_sms;
+    const int csize = (score_stride > 16384 && rows * kMaxCluster <= places) ? kMaxCluster : 1;
+    const int clusters = rows * csize <= places ? rows : places / csize;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(clusters * kCluster), 1, 1);
+    cfg.gridDim = dim3(static_cast<unsigned>(clusters * csize), 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = kCluster;
+    attr[0].val.clusterDim.x = csize;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
