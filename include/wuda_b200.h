@@ -512,8 +512,11 @@ int wuda_moe_route(const float* logits, const float* bias, float* weights, int32
  *
  *   wuda_moe_dispatch            (token, expert) pairs -> rows sorted by expert, each expert's rows
  *                                padded to groups of 16 (a GEMM row tile), stable in token order
- *   wuda_moe_gather_quant_nvfp4  row r <- activation of row_token[r], quantised to NVFP4
- *   wuda_gemm_nvfp4_grouped      c[group rows] = a[group rows] . w[expert of the group]^T
+ *   wuda_moe_gather_quant_nvfp4  row pair_row[t, j] <- activation of token t, quantised to NVFP4
+ *   wuda_gemm_nvfp4_grouped      c[group rows] = a[group rows] . w[expert of the group]^T; with row_token given
+ *                                the rows without a token are not stored (their inputs were never written);
+ *                                with row_token NULL every row is stored and padding rows hold whatever
+ *                                their unwritten inputs give
  *   wuda_moe_swiglu_quant_nvfp4  silu(min(gate, L)) * clamp(up, +-L) * routing weight -> bf16 -> NVFP4
  *   wuda_moe_combine             y[t] = bf16(sum_j out[pair_row[t, j]] (+ shared[t])), slot order
  * The reference has no kernel for this block (its MoE runs through the origin's TileLang GEMMs,
@@ -524,7 +527,8 @@ int wuda_moe_route(const float* logits, const float* bias, float* weights, int32
  *   group_expert int32 [max_groups] (-1 = unused);  num_groups int32 [1]
  *   row_token int32 [max_groups*16] (-1 = padding);  row_weight fp32 [max_groups*16]
  *   pair_row int32 [tokens, k] (row of each pair; -1 for an invalid expert index)
- *   a_fp4 uint8 [max_groups*16, K/2] (two e2m1 per byte, low nibble first)
+ *   a_fp4 uint8 [max_groups*16, K/2] (two e2m1 per byte, low nibble first); padding rows (row_token < 0)
+ *       are never written, neither values nor scales: 16-row groups of a decode batch are mostly padding
  *   a_sf_packed uint8 [max_groups, K/256, 2048]: scale of row r, values [16j, 16j+16) of K block kb at
  *       ((g*K/256 + kb)*2048) + ((j/4)%4)*512 + (r%16)*16 + j%4, g = r/16; ZERO before the first call
  *       (only rows 0..15 of each 128-row image are ever written)
@@ -543,15 +547,17 @@ int wuda_moe_dispatch(const int32_t* indices, const float* weights, int32_t* gro
 int wuda_moe_dispatch_range(const int32_t* indices, const float* weights, int32_t* group_expert, int32_t* num_groups,
                             int32_t* row_token, float* row_weight, int32_t* pair_row, int tokens, int k, int experts,
                             int expert_first, int experts_total, int max_groups, int32_t* status_word, void* stream);
-int wuda_moe_gather_quant_nvfp4(const void* x_bf16, const int32_t* row_token, const int32_t* num_groups, void* a_fp4,
-                                void* a_sf_packed, float global_scale, int max_groups, int k, void* stream);
+int wuda_moe_gather_quant_nvfp4(const void* x_bf16, const int32_t* pair_row, void* a_fp4, void* a_sf_packed,
+                                float global_scale, int tokens, int topk, int k, void* stream);
 int wuda_gemm_nvfp4_grouped(const void* a, const void* a_sf_packed, float a_global_scale, const void* w,
                             const void* w_sf_packed, const float* w_global_scales, const int32_t* group_expert,
-                            const int32_t* num_groups, void* c_bf16, int max_groups, int experts, int n, int k,
-                            void* scratch, int64_t scratch_bytes, int32_t* status_word, void* stream);
-int wuda_moe_swiglu_quant_nvfp4(const void* h_bf16, const int32_t* row_token, const float* row_weight,
-                                const int32_t* num_groups, void* a_fp4, void* a_sf_packed, float global_scale,
-                                float swiglu_limit, int max_groups, int inter, void* stream);
+                            const int32_t* num_groups, const int32_t* row_token, void* c_bf16, int max_groups,
+                            int experts, int n, int k, void* scratch, int64_t scratch_bytes, int32_t* status_word,
+                            void* stream);
+/* pair_weight fp32 [tokens, topk]: the routing weights the dispatch was given. */
+int wuda_moe_swiglu_quant_nvfp4(const void* h_bf16, const int32_t* pair_row, const float* pair_weight, void* a_fp4,
+                                void* a_sf_packed, float global_scale, float swiglu_limit, int tokens, int topk,
+                                int inter, void* stream);
 int wuda_moe_combine(const void* expert_out_bf16, const int32_t* pair_row, const void* shared_bf16, void* y_bf16,
                      int tokens, int k, int dim, void* stream);
 /* The combine step of two expert-parallel ranks (each holds half of the experts, the all-reduce site of

@@ -63,34 +63,35 @@ def test_routed_experts_stagewise(wuda, tokens, experts, k, dim, inter, limit):
     row_w = np.zeros(rows, np.float32)
     row_w[pr.reshape(-1)] = rw.numpy().reshape(-1)
     assert np.array_equal(runner.row_weight.cpu().numpy()[:rows], row_w)
-    # 2 gather + quantise: bit-exact
+    # 2 gather + quantise: bit-exact on the rows that hold a token.  Padding rows are never written (neither values
+    # nor scales): the grouped GEMM does not store their outputs and nothing reads them.
     xr = np.zeros((rows, dim), np.float32)
     xr[live] = oracle.bf16_to_f32(u16(x))[rt[live]]
     q, sf = oracle.quantize_nvfp4_rows(xr, weights.act_scale_in)
-    assert np.array_equal(runner.a1.cpu().numpy()[:rows], q)
+    assert np.array_equal(runner.a1.cpu().numpy()[:rows][live], q[live])
     a1_sf = unpack_sf(runner.a1_sf.cpu().numpy()[:groups], groups, dim // 256)
-    assert np.array_equal(a1_sf, sf)
+    assert np.array_equal(a1_sf[live], sf[live])
     # 3 grouped w1|w3 GEMM on the GPU's own quantised rows
     h = u16(runner.h)[:rows]
     for gi, e in enumerate(ge):
         sl = slice(gi * 16, gi * 16 + 16)
         ref = oracle.gemm_nvfp4(q[sl], sf[sl], weights.act_scale_in, weights.host["w13"][e], weights.raw_scales["w13"][e],
                                 weights.host["w13_gs"][e])
-        close_bf16(h[sl], ref)
+        close_bf16(h[sl][live[sl]], ref[live[sl]])
     # 4 SwiGLU + routing weight + quantise, from the GPU's h
     act = oracle.moe_swiglu(h, row_w, limit)
     act[~live] = 0
     q2, sf2 = oracle.quantize_nvfp4_rows(oracle.bf16_to_f32(act), weights.act_scale_mid)
     a2 = runner.a2.cpu().numpy()[:rows]
     a2_sf = unpack_sf(runner.a2_sf.cpu().numpy()[:groups], groups, inter // 256)
-    assert np.mean(a2 == q2) >= 0.995 and np.mean(a2_sf == sf2) >= 0.995     # expf differs in the last bit
+    assert np.mean(a2[live] == q2[live]) >= 0.995 and np.mean(a2_sf[live] == sf2[live]) >= 0.995     # expf differs in the last bit
     # 5 grouped w2 GEMM on the GPU's own a2
     out = u16(runner.out)[:rows]
     for gi, e in enumerate(ge):
         sl = slice(gi * 16, gi * 16 + 16)
         ref = oracle.gemm_nvfp4(a2[sl], a2_sf[sl], weights.act_scale_mid, weights.host["w2"][e],
                                 weights.raw_scales["w2"][e], weights.host["w2_gs"][e])
-        close_bf16(out[sl], ref)
+        close_bf16(out[sl][live[sl]], ref[live[sl]])
     # 6 combine: exact, pairs in slot order, then the shared expert's row
     of = oracle.bf16_to_f32(out)
     acc = np.zeros((tokens, dim), np.float32)

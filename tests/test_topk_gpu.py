@@ -76,6 +76,60 @@ def test_duplicate_heavy_rows_take_lowest_indices(wuda, tie_levels):
     check(wuda, *make(4, 65536, lens, tie_levels=tie_levels, seed=tie_levels + 100), 512)
 
 
+@pytest.mark.parametrize("crowd,step", [(1500, 1.0 / 64), (300, 1.0 / 64), (2000, 1.0 / 1024), (1100, 0.0)])
+def test_threshold_inside_a_crowded_bin(wuda, crowd, step):
+    """Scores crowded into a narrow band around the k-th value (hundreds of candidates share the threshold's
+    histogram bin, many of them equal): the band's members must still be ranked exactly - larger first, lower
+    index first among equals.  Projection outputs of real layers look like this: tens of thousands in magnitude,
+    a few binades wide, runs of exact zeros behind a ReLU."""
+    rng = np.random.default_rng(crowd)
+    rows, length, k = 6, 8192, 2048
+    scores = (rng.normal(size=(rows, length)) * 3000.0).astype(np.float32)
+    for r in range(rows):
+        scores[r, rng.permutation(length)[:1000]] += 60000.0                  # 1000 clear winners
+        where = rng.permutation(length)[:crowd + 600]
+        band = 30000.0 + rng.integers(0, 256, size=where.size) * step          # the k-th value lies in here
+        scores[r, where] = band.astype(np.float32)
+    lens = [length] * rows
+    pages = length // PAGE
+    page_table = rng.integers(0, 1 << 20, size=(rows, pages), dtype=np.int32)
+    check(wuda, scores, np.asarray(lens, np.int32), page_table, k)
+
+
+def test_crowded_rows_cost_about_what_spread_rows_cost(wuda):
+    """A selection whose cost grew with the square of the threshold bin's size would take twenty times longer on
+    crowded rows than on normal ones; the bound here is loose (a factor of 4) and relative, so it holds at any clock."""
+    rng = np.random.default_rng(5)
+    rows, length, k = 64, 8192, 2048
+    spread = rng.normal(size=(rows, length)).astype(np.float32)
+    crowded = np.maximum(rng.normal(size=(rows, length)) - 0.4, 0).astype(np.float32)    # the k-th value is an exact zero
+    crowded[:, ::3] = (30000.0 + rng.integers(0, 200, size=crowded[:, ::3].shape) / 64.0).astype(np.float32)
+    seq = torch.full((rows,), length, dtype=torch.int32, device="cuda")
+    table = torch.arange(rows * (length // PAGE), dtype=torch.int32, device="cuda").reshape(rows, -1)
+    out = torch.empty(rows, k, dtype=torch.int32, device="cuda")
+
+    def device_time(scores):
+        d = torch.from_numpy(scores).cuda()
+        graph = torch.cuda.CUDAGraph()
+        wuda.topk_v2_transform(d, seq, table, out, PAGE)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph):
+            for _ in range(10):
+                wuda.topk_v2_transform(d, seq, table, out, PAGE)
+        best = 1e9
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return best
+
+    t_spread, t_crowded = device_time(spread), device_time(crowded)
+    assert t_crowded < 4.0 * t_spread, (t_crowded, t_spread)
+
+
 def test_special_values(wuda):
     rng = np.random.default_rng(9)
     scores = rng.normal(size=(3, 8192)).astype(np.float32)

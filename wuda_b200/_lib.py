@@ -154,10 +154,10 @@ SIGNATURES = {
     "wuda_moe_ep2_inbox_bytes": (c_i64, [c_int, c_int]),
     "wuda_moe_combine_ep2": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp, c_int, c_int, c_int, c_vp,
                                      c_vp]),
-    "wuda_moe_gather_quant_nvfp4": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_int, c_int, c_vp]),
-    "wuda_gemm_nvfp4_grouped": (c_int, [c_vp, c_vp, c_float, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int,
+    "wuda_moe_gather_quant_nvfp4": (c_int, [c_vp, c_vp, c_vp, c_vp, c_float, c_int, c_int, c_int, c_vp]),
+    "wuda_gemm_nvfp4_grouped": (c_int, [c_vp, c_vp, c_float, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int,
                                         c_int, c_vp, c_i64, c_vp, c_vp]),
-    "wuda_moe_swiglu_quant_nvfp4": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_float, c_int, c_int, c_vp]),
+    "wuda_moe_swiglu_quant_nvfp4": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_float, c_int, c_int, c_int, c_vp]),
     "wuda_moe_combine": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp]),
     "wuda_swiglu_quant_fp8": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_float, c_int, c_vp]),
     "wuda_mhc_post": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),

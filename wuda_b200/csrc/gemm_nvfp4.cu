@@ -63,6 +63,7 @@ struct Params {
     // group_expert[g]; flat tile T = g * n_tiles + tile of the expert's N rows.  The number of groups
     // is read on the device, so nothing is synchronised with the host between routing and the GEMM.
     const int32_t* group_expert = nullptr;   // [num_groups]
+    const int32_t* row_token = nullptr;      // [num_groups * 16] or nullptr: rows without a token (< 0) are not stored
     const int32_t* num_groups = nullptr;     // [1]
     const float* expert_scale = nullptr;     // [experts] per-expert weight tensor scale (times out_scale)
 };
@@ -378,9 +379,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 if (alive && nrow < p.N) {
                     const float scale = grouped ? p.out_scale * __ldg(p.expert_scale + __ldcg(p.group_expert + grp)) : p.out_scale;
                     __nv_bfloat16* c = p.c + static_cast<int64_t>(grp) * M_PAD * p.N;
+                    uint32_t stored = 0xffffffffu;   // grouped rows without a token are padding: nobody reads them
+                    if (M_PAD <= 32 && grouped && p.row_token) {
+                        const int tok = lane < M_PAD ? __ldcg(p.row_token + grp * M_PAD + lane) : -1;
+                        stored = __ballot_sync(0xffffffffu, tok >= 0);
+                    }
 #pragma unroll
                     for (int i = 0; i < M_PAD; ++i)
-                        if (i < p.M) c[static_cast<int64_t>(i) * p.N + nrow] = __float2bfloat16_rn(acc[i] * scale);
+                        if (i < p.M && (M_PAD > 32 || ((stored >> i) & 1u)))
+                            c[static_cast<int64_t>(i) * p.N + nrow] = __float2bfloat16_rn(acc[i] * scale);
                 }
             }
             n += seg_len;
@@ -534,8 +541,8 @@ extern "C" int wuda_gemm_nvfp4(const void* a, const void* a_sf_packed, float a_g
 // moe.cu), expert weights stacked [experts * n, k / 2] with their packed scales stacked per expert.
 extern "C" int wuda_gemm_nvfp4_grouped(const void* a, const void* a_sf_packed, float a_global_scale, const void* w,
                                        const void* w_sf_packed, const float* w_global_scales,
-                                       const int32_t* group_expert, const int32_t* num_groups, void* c_bf16,
-                                       int max_groups, int experts, int n, int k, void* scratch, int64_t scratch_bytes,
+                                       const int32_t* group_expert, const int32_t* num_groups, const int32_t* row_token,
+                                       void* c_bf16, int max_groups, int experts, int n, int k, void* scratch, int64_t scratch_bytes,
                                        int32_t* status_word, void* stream) {
     using namespace wuda;
     using namespace wuda::gemm4;
@@ -570,6 +577,7 @@ extern "C" int wuda_gemm_nvfp4_grouped(const void* a, const void* a_sf_packed, f
     p.stages = 0;
     p.group_expert = group_expert;
     p.num_groups = num_groups;
+    p.row_token = row_token;
     p.expert_scale = w_global_scales;
 
     CUtensorMap w_map, a_map, wsf_map, asf_map;

@@ -302,15 +302,14 @@ extern "C" int wuda_layer_decode(const wuda_layer_weights* w, const wuda_layer_s
     }
     WUDA_STAGE(wuda_moe_dispatch_range(b.route_idx, b.route_w, b.group_expert, b.num_groups, b.row_token, b.row_weight, b.pair_row, m,
                                        w->moe_topk, w->experts_local, w->expert_first, w->experts_total, b.max_groups, status, stream));
-    WUDA_STAGE(wuda_moe_gather_quant_nvfp4(b.f_normed, b.row_token, b.num_groups, b.a1, b.a1_sf, w->act_scale_in, b.max_groups, hidden,
-                                           stream));
-    WUDA_STAGE(wuda_gemm_nvfp4_grouped(b.a1, b.a1_sf, w->act_scale_in, w->w13, w->w13_sf, w->w13_gs, b.group_expert, b.num_groups, b.h,
+    WUDA_STAGE(wuda_moe_gather_quant_nvfp4(b.f_normed, b.pair_row, b.a1, b.a1_sf, w->act_scale_in, m, w->moe_topk, hidden, stream));
+    WUDA_STAGE(wuda_gemm_nvfp4_grouped(b.a1, b.a1_sf, w->act_scale_in, w->w13, w->w13_sf, w->w13_gs, b.group_expert, b.num_groups, b.row_token, b.h,
                                        b.max_groups, w->experts_local, 2 * w->inter, hidden, b.nvfp4_scratch, b.nvfp4_scratch_bytes,
                                        status, stream));
-    WUDA_STAGE(wuda_moe_swiglu_quant_nvfp4(b.h, b.row_token, b.row_weight, b.num_groups, b.a2, b.a2_sf, w->act_scale_mid,
-                                           w->swiglu_limit, b.max_groups, w->inter, stream));
+    WUDA_STAGE(wuda_moe_swiglu_quant_nvfp4(b.h, b.pair_row, b.route_w, b.a2, b.a2_sf, w->act_scale_mid, w->swiglu_limit, m, w->moe_topk,
+                                           w->inter, stream));
     WUDA_STAGE(wuda_gemm_nvfp4_grouped(b.a2, b.a2_sf, w->act_scale_mid, w->w2, w->w2_sf, w->w2_gs, b.group_expert, b.num_groups,
-                                       b.r_out, b.max_groups, w->experts_local, hidden, w->inter, b.nvfp4_scratch,
+                                       b.row_token, b.r_out, b.max_groups, w->experts_local, hidden, w->inter, b.nvfp4_scratch,
                                        b.nvfp4_scratch_bytes, status, stream));
     if (s->ep_peer_inbox)
         WUDA_STAGE(wuda_moe_combine_ep2(b.r_out, b.pair_row, shared_rows, b.y_moe, m, w->moe_topk, hidden, s->ep_my_inbox,

@@ -12,15 +12,21 @@
 // of a third-party library plus kernels/hc_fused_kernel_tc.cu:420-520 (hc_reduce_fuse_out, fused
 // norm + quant at :300-340) and the Sinkhorn tail include/front_mixed_gemm.cuh:438-489.
 //
-// Two kernels.  (1) The 24 dot products are 1.4 MFLOP per token against 2.75 MB of weights: CUDA
-// cores in fp32 (exact products, unlike TF32), K cut into 56 slices of 512 so that 56 x ceil(M/4)
-// CTAs share the work; a thread keeps its 24 x 4 weights in registers across the CTA's 4 tokens.
+// Two kernels.  (1) The mix, a [m, K] x [24, K]^T contraction with K = 4 * hidden, on the tensor cores with
+// fp32-grade products: W is cut into three bf16 terms (hi + mid + lo carry its 24 mantissa bits, so
+// x * hi, x * mid, x * lo are exact in fp32) stacked as 72 operand rows, and one tcgen05.mma kind::f16
+// chain per CTA multiplies a 128-token tile of x by them; the three column groups are added in the
+// epilogue.  K is cut into slices of 512: one CTA per (slice, 128-token tile) brings its x tile in with
+// TMA (128-byte swizzle, rows beyond m filled with zeros), splits its 24 x 512 weights into shared memory
+// in the same layout, and while the MMAs run sums the squares of its x rows from shared memory.
 // Partials go to a workspace [slice][token][25] (24 dots + the sum of squares).  (2) One CTA per
 // token adds the slices in order (deterministic), runs the gates and the Sinkhorn in one warp, and
 // streams the 4 residual rows once for collapse + norm + quantisation.
+#include <cuda.h>
 #include <cuda_bf16.h>
 
 #include "host.h"
+#include "ptx.cuh"
 
 namespace wuda {
 namespace mhcpre {
@@ -29,8 +35,13 @@ constexpr int kStreams = 4;
 constexpr int kMix = 24;                 // pre 4 | post 4 | comb 16
 constexpr int kPart = kMix + 1;          // + sum of squares
 constexpr int kSlice = 512;              // K elements per slice
-constexpr int kMixThreads = 128;         // 4 elements per thread
-constexpr int kTokensPerCta = 4;
+constexpr int kMixThreads = 128;         // thread = token row of the tile = tensor-memory lane
+constexpr int kMixTile = 128;            // tokens per CTA (UMMA M)
+constexpr int kMixN = 80;                // 3 x 24 operand rows, padded to a multiple of 16 (UMMA N)
+constexpr int kKBlocks = kSlice / 64;    // 128-byte K blocks per slice
+constexpr int kXBlockBytes = kMixTile * 128, kWBlockBytes = kMixN * 128;
+constexpr int kMixSmemBytes = kKBlocks * (kXBlockBytes + kWBlockBytes) + 64 + 1024;
+constexpr int kMixTmemCols = 128;
 constexpr int kFinishThreads = 256;
 constexpr int kSinkhornIters = 20;
 
@@ -59,54 +70,161 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-__global__ void __launch_bounds__(kMixThreads) mhc_pre_mix_kernel(Params p) {
-    pdl_launch_dependents();
-    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
-    __shared__ float warp_part[2][kMixThreads / 32][kPart];   // two buffers: one barrier per token
-    const int slice = blockIdx.x;
-    const int k0 = slice * kSlice + threadIdx.x * 4;
+__device__ __forceinline__ uint32_t bf16_bits_rn(float v) {
+    return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(v)));
+}
+
+__global__ void __launch_bounds__(kMixThreads, 1) mhc_pre_mix_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw_addr);
+    const uint32_t x_addr = base, w_addr = base + kKBlocks * kXBlockBytes;
+    uint8_t* x_ptr = base_ptr;
+    uint8_t* w_ptr = base_ptr + kKBlocks * kXBlockBytes;
+    const uint32_t bars = w_addr + kKBlocks * kWBlockBytes;
+    const uint32_t x_full = bars, mma_done = bars + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + kKBlocks * (kXBlockBytes + kWBlockBytes) + 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kKBlocks * (kXBlockBytes + kWBlockBytes) + 20);
+    const int warp = threadIdx.x >> 5;
+    const uint32_t lane = lane_id();
+    const int slice = blockIdx.x, tile = blockIdx.y;
     const int K = kStreams * p.hidden;
-    const bool in = k0 < K;                         // the last slice may be ragged (K % 512 != 0)
-    float4 w[kMix];
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(x_full, 1);
+        mbar_init(mma_done, 1);
+        fence_mbar_init();
+        prefetch_tmap(&x_map);
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(tmem_slot), kMixTmemCols);
+        tmem_relinquish();
+    }
+    // the 24 x 512 weights of the slice (constants: they may be read before the kernel ahead has finished):
+    // item = (row j, 8 consecutive K) -> two 16-byte loads, twelve items per thread
+    constexpr int kItems = kMix * (kSlice / 8) / kMixThreads;
+    float4 wraw[kItems][2];
 #pragma unroll
-    for (int j = 0; j < kMix; ++j)
-        w[j] = in ? __ldg(reinterpret_cast<const float4*>(p.weight + static_cast<int64_t>(j) * K + k0))
-                  : make_float4(0.f, 0.f, 0.f, 0.f);
-    const int t0 = blockIdx.y * kTokensPerCta;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // all of the CTA's activation loads go out before the first is used
-    uint2 raw[kTokensPerCta];
+    for (int i = 0; i < kItems; ++i) {
+        const int item = threadIdx.x + i * kMixThreads, j = item / (kSlice / 8), c = item % (kSlice / 8);
+        const float4* src = reinterpret_cast<const float4*>(p.weight + static_cast<int64_t>(j) * K + slice * kSlice + c * 8);
+        wraw[i][0] = __ldg(src);
+        wraw[i][1] = __ldg(src + 1);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();   // the residual streams come from the kernel ahead
+
+    if (threadIdx.x == 0) {
+        mbar_arrive_expect_tx(x_full, kKBlocks * kXBlockBytes);
 #pragma unroll
-    for (int i = 0; i < kTokensPerCta; ++i)
-        // (coherent load: the streams come from the kernel ahead, which may still be running when this one is launched)
-        raw[i] = (in && t0 + i < p.m) ? __ldcg(reinterpret_cast<const uint2*>(p.x + static_cast<int64_t>(t0 + i) * K + k0))
-                                      : make_uint2(0u, 0u);
+        for (int kb = 0; kb < kKBlocks; ++kb)
+            tma_load_2d(x_addr + kb * kXBlockBytes, &x_map, x_full, slice * kSlice + kb * 64, tile * kMixTile);
+    }
+    // w = hi + mid + lo in bf16, rows j, 24 + j, 48 + j of the operand, 128-byte swizzle (16-byte chunk c of row
+    // r sits at chunk c ^ (r & 7)); rows 72..79 are zero
 #pragma unroll
-    for (int i = 0; i < kTokensPerCta; ++i) {
-        const int t = t0 + i;
-        if (t >= p.m) break;                        // uniform over the CTA
-        float x[4];
-        x[0] = __uint_as_float(raw[i].x << 16);
-        x[1] = __uint_as_float(raw[i].x & 0xffff0000u);
-        x[2] = __uint_as_float(raw[i].y << 16);
-        x[3] = __uint_as_float(raw[i].y & 0xffff0000u);
-        float part[kPart];
+    for (int i = 0; i < kItems; ++i) {
+        const int item = threadIdx.x + i * kMixThreads, j = item / (kSlice / 8), c = item % (kSlice / 8);
+        const float w[8] = {wraw[i][0].x, wraw[i][0].y, wraw[i][0].z, wraw[i][0].w, wraw[i][1].x, wraw[i][1].y, wraw[i][1].z, wraw[i][1].w};
+        uint32_t term[3][4];
 #pragma unroll
-        for (int j = 0; j < kMix; ++j)
-            part[j] = fmaf(x[3], w[j].w, fmaf(x[2], w[j].z, fmaf(x[1], w[j].y, x[0] * w[j].x)));
-        part[kMix] = fmaf(x[3], x[3], fmaf(x[2], x[2], fmaf(x[1], x[1], x[0] * x[0])));
+        for (int e = 0; e < 8; e += 2) {
+            uint32_t pair[3] = {0u, 0u, 0u};
 #pragma unroll
-        for (int j = 0; j < kPart; ++j) part[j] = warp_sum(part[j]);
-        float (*buf)[kPart] = warp_part[i & 1];
-        if (lane == 0) {
+            for (int h = 0; h < 2; ++h) {
+                float r = w[e + h];
 #pragma unroll
-            for (int j = 0; j < kPart; ++j) buf[warp][j] = part[j];
+                for (int t = 0; t < 3; ++t) {
+                    const uint32_t bits = bf16_bits_rn(r);
+                    pair[t] |= bits << (16 * h);
+                    r = __fsub_rn(r, __uint_as_float(bits << 16));   // exact: the difference fits fp32
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < 3; ++t) term[t][e >> 1] = pair[t];
         }
-        __syncthreads();                            // (buffer i & 1 is next written two tokens later, after another barrier)
-        if (threadIdx.x < kPart) {
-            const int j = threadIdx.x;
-            p.ws[(static_cast<int64_t>(slice) * p.m + t) * kPart + j] = ((buf[0][j] + buf[1][j]) + buf[2][j]) + buf[3][j];
+        const int kb = c >> 3, cc = c & 7;
+#pragma unroll
+        for (int t = 0; t < 3; ++t) {
+            const int r = t * kMix + j;
+            *reinterpret_cast<uint4*>(w_ptr + kb * kWBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4)) =
+                make_uint4(term[t][0], term[t][1], term[t][2], term[t][3]);
         }
+    }
+    for (int z = threadIdx.x; z < kKBlocks * (kMixN - 3 * kMix) * 8; z += kMixThreads) {
+        const int kb = z / ((kMixN - 3 * kMix) * 8), rest = z % ((kMixN - 3 * kMix) * 8);
+        *reinterpret_cast<uint4*>(w_ptr + kb * kWBlockBytes + (3 * kMix) * 128 + rest * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async_smem();   // the generic-proxy stores above are read by the tensor core
+    __syncthreads();
+
+    bool alive = mbar_wait(x_full, 0, abort_flag, nullptr, 0);
+    if (threadIdx.x == 0 && alive) {
+        tc_fence_after();
+        constexpr uint32_t idesc = umma_idesc(kMixTile, kMixN, 1, 1);   // bf16 x bf16 -> fp32, both K-major
+        uint32_t accumulate = 0;
+#pragma unroll
+        for (int kb = 0; kb < kKBlocks; ++kb)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                umma_f16(tmem_base, umma_smem_desc_sw128(x_addr + kb * kXBlockBytes + k * 32),
+                         umma_smem_desc_sw128(w_addr + kb * kWBlockBytes + k * 32), idesc, accumulate);
+                accumulate = 1;
+            }
+        umma_commit(mma_done);
+    }
+    // sum of squares of this thread's token row, from the tile in shared memory, while the MMAs run
+    float ss = 0.f;
+    if (alive) {
+        const int r = threadIdx.x;
+#pragma unroll 2
+        for (int kb = 0; kb < kKBlocks; ++kb)
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(x_ptr + kb * kXBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4));
+                const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float lo = __uint_as_float(wv[i] << 16), hi = __uint_as_float(wv[i] & 0xffff0000u);
+                    ss = fmaf(hi, hi, fmaf(lo, lo, ss));
+                }
+            }
+    }
+    alive = alive && mbar_wait(mma_done, 0, abort_flag, nullptr, 0);
+    const int t = tile * kMixTile + threadIdx.x;
+    if (alive) {
+        tc_fence_after();
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        uint32_t c[kMixN];
+#pragma unroll
+        for (int q = 0; q < kMixN / 16; ++q) {
+            uint32_t v[16];
+            tmem_ld_32x16(tmem_base + lane_base + q * 16, v);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) c[q * 16 + i] = v[i];
+        }
+        tmem_ld_wait();
+        tc_fence_before();
+        if (t < p.m) {
+            float* out = p.ws + (static_cast<int64_t>(slice) * p.m + t) * kPart;
+#pragma unroll
+            for (int j = 0; j < kMix; ++j)
+                out[j] = __uint_as_float(c[j]) + (__uint_as_float(c[kMix + j]) + __uint_as_float(c[2 * kMix + j]));
+            out[kMix] = ss;
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) abort_drain_sleep();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kMixTmemCols);
     }
 }
 
@@ -356,6 +474,26 @@ int fill_params(wuda::mhcpre::Params& p, const void* hidden_states, const float*
     return WUDA_OK;
 }
 
+// The mix kernel: the residual streams as a [m, 4 * hidden] bf16 tensor map with 64 x 128 boxes in the 128-byte
+// swizzle; a tile's rows beyond m read as zeros.
+int launch_mix(const wuda::mhcpre::Params& p, cudaStream_t stream) {
+    using namespace wuda;
+    using namespace wuda::mhcpre;
+    WUDA_REQUIRE(static_cast<int64_t>(p.m) <= 65535ll * kMixTile, "m is too large (got %d)", p.m);
+    CUtensorMap x_map;
+    const uint64_t K = static_cast<uint64_t>(kStreams) * p.hidden;
+    const uint64_t dims[2] = {K, static_cast<uint64_t>(p.m)};
+    const uint64_t strides[1] = {K * 2};
+    const uint32_t box[2] = {64u, static_cast<uint32_t>(kMixTile)};
+    int st = encode_tensor_map(&x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    if (st != WUDA_OK) return st;
+    WUDA_CUDA(cudaFuncSetAttribute(mhc_pre_mix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMixSmemBytes));
+    const dim3 grid(p.slices, (p.m + kMixTile - 1) / kMixTile);
+    WUDA_CUDA(launch_pdl(mhc_pre_mix_kernel, grid, dim3(kMixThreads), kMixSmemBytes, stream, x_map, p));
+    return WUDA_OK;
+}
+
 }  // namespace
 
 extern "C" int wuda_mhc_pre(const void* hidden_states, const float* weight, const float* base, const float* scale,
@@ -374,8 +512,8 @@ extern "C" int wuda_mhc_pre(const void* hidden_states, const float* weight, cons
     const int64_t need = wuda_mhc_pre_workspace_bytes(m, hidden);
     WUDA_REQUIRE(workspace_bytes >= need, "workspace holds %lld bytes; %lld are needed (wuda_mhc_pre_workspace_bytes)",
                  static_cast<long long>(workspace_bytes), static_cast<long long>(need));
-    const dim3 grid_mix(p.slices, (m + kTokensPerCta - 1) / kTokensPerCta);
-    WUDA_CUDA(launch_pdl(mhc_pre_mix_kernel, dim3(grid_mix), dim3(kMixThreads), 0, static_cast<cudaStream_t>(stream), p));
+    st = launch_mix(p, static_cast<cudaStream_t>(stream));
+    if (st != WUDA_OK) return st;
     WUDA_CUDA(launch_pdl(mhc_pre_finish_kernel, dim3(m), dim3(kFinishThreads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
@@ -393,8 +531,8 @@ extern "C" int wuda_mhc_pre_mix(const void* hidden_states, const float* weight, 
     const int64_t need = wuda_mhc_pre_workspace_bytes(m, hidden);
     WUDA_REQUIRE(workspace_bytes >= need, "workspace holds %lld bytes; %lld are needed (wuda_mhc_pre_workspace_bytes)",
                  static_cast<long long>(workspace_bytes), static_cast<long long>(need));
-    const dim3 grid_mix(p.slices, (m + kTokensPerCta - 1) / kTokensPerCta);
-    WUDA_CUDA(launch_pdl(mhc_pre_mix_kernel, dim3(grid_mix), dim3(kMixThreads), 0, static_cast<cudaStream_t>(stream), p));
+    st = launch_mix(p, static_cast<cudaStream_t>(stream));
+    if (st != WUDA_OK) return st;
     return WUDA_OK;
 }
 

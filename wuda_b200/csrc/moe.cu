@@ -41,36 +41,51 @@ struct DispatchParams {
 
 constexpr int kDispatchThreads = 1024;
 constexpr int kMaxExperts = 512;
+constexpr int kPairsInShared = 4096;   // up to this many pairs the ranking reads them from shared memory
 
 __global__ void __launch_bounds__(kDispatchThreads) moe_dispatch_kernel(DispatchParams p) {
     pdl_launch_dependents();
     pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     __shared__ int count[kMaxExperts];
     __shared__ int base[kMaxExperts];       // first group of the expert
+    __shared__ int pair_expert[kPairsInShared];
     __shared__ int total_groups;
     const int pairs = p.tokens * p.k;
+    const bool staged = pairs <= kPairsInShared;
     for (int e = threadIdx.x; e < p.experts; e += kDispatchThreads) count[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += kDispatchThreads) {
+        const int global = __ldcg(p.indices + i), e = global - p.first;   // written by the router of the same chain
+        if (staged) pair_expert[i] = global;
+        if (e >= 0 && e < p.experts) atomicAdd(&count[e], 1);
+        else if ((global < 0 || global >= p.total) && p.status) atomicCAS(p.status, 0, WUDA_DEV_BAD_EXPERT);
+    }
     for (int r = threadIdx.x; r < p.max_groups * kGroupRows; r += kDispatchThreads) {
         p.row_token[r] = -1;
         p.row_weight[r] = 0.f;
     }
     for (int g = threadIdx.x; g < p.max_groups; g += kDispatchThreads) p.group_expert[g] = -1;
     __syncthreads();
-    for (int i = threadIdx.x; i < pairs; i += kDispatchThreads) {
-        const int global = p.indices[i], e = global - p.first;
-        if (e >= 0 && e < p.experts) atomicAdd(&count[e], 1);
-        else if ((global < 0 || global >= p.total) && p.status) atomicCAS(p.status, 0, WUDA_DEV_BAD_EXPERT);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {                 // experts <= 512: a serial scan is a few hundred steps
-        int g = 0;
-        for (int e = 0; e < p.experts; ++e) {
+    if (threadIdx.x < 32) {                 // exclusive scan of the experts' group counts by one warp
+        const int per = (p.experts + 31) / 32, e0 = threadIdx.x * per, e1 = min(e0 + per, p.experts);
+        int mine = 0;
+        for (int e = e0; e < e1; ++e) mine += (count[e] + kGroupRows - 1) / kGroupRows;
+        int incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (threadIdx.x >= d) incl += up;
+        }
+        int g = incl - mine;
+        for (int e = e0; e < e1; ++e) {
             base[e] = g;
             g += (count[e] + kGroupRows - 1) / kGroupRows;
         }
-        total_groups = g;
-        *p.num_groups = g <= p.max_groups ? g : 0;
-        if (g > p.max_groups && p.status) atomicCAS(p.status, 0, WUDA_DEV_BAD_DESTINATION);
+        if (threadIdx.x == 31) {
+            total_groups = incl;
+            *p.num_groups = incl <= p.max_groups ? incl : 0;
+            if (incl > p.max_groups && p.status) atomicCAS(p.status, 0, WUDA_DEV_BAD_DESTINATION);
+        }
     }
     __syncthreads();
     if (total_groups > p.max_groups) return;
@@ -80,17 +95,22 @@ __global__ void __launch_bounds__(kDispatchThreads) moe_dispatch_kernel(Dispatch
     }
     // stable placement: the rank of a pair among the earlier pairs of the same expert
     for (int i = threadIdx.x; i < pairs; i += kDispatchThreads) {
-        const int global = p.indices[i], e = global - p.first;
+        const int global = staged ? pair_expert[i] : __ldcg(p.indices + i), e = global - p.first;
         if (e < 0 || e >= p.experts) {   // another rank's expert, or an invalid index
             p.pair_row[i] = -1;
             continue;
         }
         int rank = 0;
-        for (int j = 0; j < i; ++j) rank += (p.indices[j] == global);
+        if (staged) {
+#pragma unroll 8
+            for (int j = 0; j < i; ++j) rank += (pair_expert[j] == global);
+        } else {
+            for (int j = 0; j < i; ++j) rank += (__ldcg(p.indices + j) == global);
+        }
         const int row = base[e] * kGroupRows + rank;
         p.pair_row[i] = row;
         p.row_token[row] = i / p.k;
-        p.row_weight[row] = p.weights[i];
+        p.row_weight[row] = __ldcg(p.weights + i);
     }
 }
 
@@ -134,88 +154,107 @@ __device__ __forceinline__ int64_t sf_offset(int row, int k16, int kb_per_row) {
     return (static_cast<int64_t>(group) * kb_per_row + kb) * 2048 + (within >> 2) * 512 + r * 16 + (within & 3);
 }
 
+// A thread of the two quantisation kernels owns one block of 16 values of one (token, expert) pair's row; the
+// four scale bytes of a 64-value step are collected by the first of its four lanes and stored as one word.
+// Rows without a token are not touched at all: the grouped GEMM, given row_token, does not store their
+// outputs, and nothing else reads them.
+__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* v) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+__device__ __forceinline__ void store_block(uint8_t* a4, uint8_t* a_sf, int row, int b, int row_blocks, const uint32_t (&packed)[2],
+                                            uint32_t sf, bool live) {
+    // (every lane of the warp takes part in the shuffles; blocks of a row never straddle a group of four lanes
+    // because row_blocks is a multiple of 16)
+    uint32_t word = sf;
+    word |= __shfl_down_sync(0xffffffffu, sf, 1) << 8;
+    word |= __shfl_down_sync(0xffffffffu, sf, 2) << 16;
+    word |= __shfl_down_sync(0xffffffffu, sf, 3) << 24;
+    if (!live) return;
+    *reinterpret_cast<uint2*>(a4 + static_cast<int64_t>(row) * (row_blocks * 8) + b * 8) = make_uint2(packed[0], packed[1]);
+    if ((b & 3) == 0) *reinterpret_cast<uint32_t*>(a_sf + sf_offset(row, b, row_blocks / 16)) = word;
+}
+
+constexpr int kQuantThreads = 256;
+
 // ---------------------------------------------------------------- gather + quantise
 struct GatherParams {
     const __nv_bfloat16* x;      // [tokens, K]
-    const int32_t* row_token;
-    const int32_t* num_groups;
+    const int32_t* pair_row;     // [tokens, topk]: row of the pair, or -1
     uint8_t* a4;                 // [rows, K / 2]
     uint8_t* a_sf;               // packed scales
     float gs;
-    int K;
+    int K, pairs, topk;
 };
 
-__global__ void __launch_bounds__(256) moe_gather_quant_kernel(GatherParams p) {
+__global__ void __launch_bounds__(kQuantThreads) moe_gather_quant_kernel(GatherParams p) {
     pdl_launch_dependents();
     pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
-    const int row = blockIdx.x;
-    if (row >= *p.num_groups * kGroupRows) return;
-    const int tok = p.row_token[row];
     const int blocks = p.K / 16;
-    for (int b = threadIdx.x; b < blocks; b += blockDim.x) {
-        uint32_t packed[2] = {0u, 0u}, sf = 0u;
-        if (tok >= 0) {
-            const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(tok) * p.K + b * 16);
-            const uint4 lo = __ldcg(src), hi = __ldcg(src + 1);   // activations of a kernel of the same chain
-            const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-            float v[16];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                v[2 * i] = __uint_as_float(w[i] << 16);
-                v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-            }
-            quant16(v, p.gs, packed, &sf);
-        }
-        *reinterpret_cast<uint2*>(p.a4 + static_cast<int64_t>(row) * (p.K / 2) + b * 8) = make_uint2(packed[0], packed[1]);
-        p.a_sf[sf_offset(row, b, p.K / 256)] = static_cast<uint8_t>(sf);
+    const int item = blockIdx.x * kQuantThreads + threadIdx.x;
+    const int pair = item / blocks, b = item - pair * blocks;
+    const int row = pair < p.pairs ? __ldcg(p.pair_row + pair) : -1;
+    const bool live = row >= 0;
+    uint32_t packed[2] = {0u, 0u}, sf = 0u;
+    if (live) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(pair / p.topk) * p.K + b * 16);
+        const uint4 lo = __ldcg(src), hi = __ldcg(src + 1);   // activations of a kernel of the same chain
+        float v[16];
+        unpack_bf16x8(lo, v);
+        unpack_bf16x8(hi, v + 8);
+        quant16(v, p.gs, packed, &sf);
     }
+    store_block(p.a4, p.a_sf, row, b, blocks, packed, sf, live);
 }
 
 // ---------------------------------------------------------------- SwiGLU + routing weight + quantise
 struct SwigluParams {
     const __nv_bfloat16* h;      // [rows, 2 * I]: gate | up
-    const int32_t* row_token;
-    const float* row_weight;
-    const int32_t* num_groups;
+    const int32_t* pair_row;     // [tokens, topk]
+    const float* pair_weight;    // [tokens, topk] routing weights
     uint8_t* a4;                 // [rows, I / 2]
     uint8_t* a_sf;
     float gs, limit;
-    int I;
+    int I, pairs;
 };
 
-__global__ void __launch_bounds__(128) moe_swiglu_quant_kernel(SwigluParams p) {
+__global__ void __launch_bounds__(kQuantThreads) moe_swiglu_quant_kernel(SwigluParams p) {
     pdl_launch_dependents();
     pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
-    const int row = blockIdx.x;
-    if (row >= *p.num_groups * kGroupRows) return;
-    const bool live = p.row_token[row] >= 0;
-    const float rw = p.row_weight[row];
     const int blocks = p.I / 16;
-    for (int b = threadIdx.x; b < blocks; b += blockDim.x) {
-        uint32_t packed[2] = {0u, 0u}, sf = 0u;
-        if (live) {
-            const __nv_bfloat16* g = p.h + static_cast<int64_t>(row) * (2 * p.I) + b * 16;
-            const uint4 g0 = *reinterpret_cast<const uint4*>(g), g1 = *reinterpret_cast<const uint4*>(g + 8);
-            const uint4 u0 = *reinterpret_cast<const uint4*>(g + p.I), u1 = *reinterpret_cast<const uint4*>(g + p.I + 8);
-            const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-            const uint32_t uw[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-            float v[16];
+    const int item = blockIdx.x * kQuantThreads + threadIdx.x;
+    const int pair = item / blocks, b = item - pair * blocks;
+    const int row = pair < p.pairs ? __ldcg(p.pair_row + pair) : -1;
+    const bool live = row >= 0;
+    uint32_t packed[2] = {0u, 0u}, sf = 0u;
+    if (live) {
+        const float rw = __ldcg(p.pair_weight + pair);
+        const uint4* g = reinterpret_cast<const uint4*>(p.h + static_cast<int64_t>(row) * (2 * p.I) + b * 16);
+        const uint4* u = reinterpret_cast<const uint4*>(p.h + static_cast<int64_t>(row) * (2 * p.I) + p.I + b * 16);
+        const uint4 g0 = __ldcg(g), g1 = __ldcg(g + 1), u0 = __ldcg(u), u1 = __ldcg(u + 1);
+        float gate[16], up[16], v[16];
+        unpack_bf16x8(g0, gate);
+        unpack_bf16x8(g1, gate + 8);
+        unpack_bf16x8(u0, up);
+        unpack_bf16x8(u1, up + 8);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                float gate = __uint_as_float((i & 1) ? (gw[i >> 1] & 0xffff0000u) : (gw[i >> 1] << 16));
-                float up = __uint_as_float((i & 1) ? (uw[i >> 1] & 0xffff0000u) : (uw[i >> 1] << 16));
-                if (p.limit > 0.f) {
-                    up = fminf(fmaxf(up, -p.limit), p.limit);
-                    gate = fminf(gate, p.limit);
-                }
-                const float silu = __fdiv_rn(gate, 1.0f + expf(-gate));
-                v[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(rw, __fmul_rn(silu, up))));
+        for (int i = 0; i < 16; ++i) {
+            float gt = gate[i], uu = up[i];
+            if (p.limit > 0.f) {
+                uu = fminf(fmaxf(uu, -p.limit), p.limit);
+                gt = fminf(gt, p.limit);
             }
-            quant16(v, p.gs, packed, &sf);
+            const float silu = __fdiv_rn(gt, 1.0f + expf(-gt));
+            v[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(rw, __fmul_rn(silu, uu))));
         }
-        *reinterpret_cast<uint2*>(p.a4 + static_cast<int64_t>(row) * (p.I / 2) + b * 8) = make_uint2(packed[0], packed[1]);
-        p.a_sf[sf_offset(row, b, p.I / 256)] = static_cast<uint8_t>(sf);
+        quant16(v, p.gs, packed, &sf);
     }
+    store_block(p.a4, p.a_sf, row, b, blocks, packed, sf, live);
 }
 
 // ---------------------------------------------------------------- combine
@@ -227,41 +266,60 @@ struct CombineParams {
     int k, dim;
 };
 
-__global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
+constexpr int kCombineSlots = 8;   // expert rows whose loads are in flight together
+
+// The fp32 sum of a token's expert rows (in slot order) and its shared-expert row over 8 dims: all row numbers
+// first, then up to eight rows' loads at once, then the additions in order.
+__device__ __forceinline__ void combine_sum8(const CombineParams& p, int t, int c, float (&acc)[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int j0 = 0; j0 < p.k; j0 += kCombineSlots) {
+        int row[kCombineSlots];
+        uint4 raw[kCombineSlots];
+#pragma unroll
+        for (int j = 0; j < kCombineSlots; ++j) row[j] = j0 + j < p.k ? __ldcg(p.pair_row + t * p.k + j0 + j) : -1;
+#pragma unroll
+        for (int j = 0; j < kCombineSlots; ++j)
+            if (row[j] >= 0) raw[j] = __ldcg(reinterpret_cast<const uint4*>(p.out + static_cast<int64_t>(row[j]) * p.dim) + c);
+#pragma unroll
+        for (int j = 0; j < kCombineSlots; ++j) {
+            if (row[j] < 0) continue;
+            float v[8];
+            unpack_bf16x8(raw[j], v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+        }
+    }
+    if (p.shared) {
+        float v[8];
+        unpack_bf16x8(__ldcg(reinterpret_cast<const uint4*>(p.shared + static_cast<int64_t>(t) * p.dim) + c), v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+    }
+}
+
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&acc)[8]) {
+    uint4 o;
+    uint32_t* ow = &o.x;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        ow[i] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    return o;
+}
+
+constexpr int kCombineThreads = 128;
+
+// grid (ceil(dim / 8 / 128), tokens): one 8-dim vector per thread
+__global__ void __launch_bounds__(kCombineThreads) moe_combine_kernel(CombineParams p) {
     pdl_launch_dependents();
     pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
-    const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < p.dim / 8; c += blockDim.x) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < p.k; ++j) {
-            const int row = p.pair_row[t * p.k + j];
-            if (row < 0) continue;
-            const uint4 raw = *(reinterpret_cast<const uint4*>(p.out + static_cast<int64_t>(row) * p.dim) + c);
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                acc[2 * i] = __fadd_rn(acc[2 * i], __uint_as_float(w[i] << 16));
-                acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
-            }
-        }
-        if (p.shared) {
-            const uint4 raw = *(reinterpret_cast<const uint4*>(p.shared + static_cast<int64_t>(t) * p.dim) + c);
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                acc[2 * i] = __fadd_rn(acc[2 * i], __uint_as_float(w[i] << 16));
-                acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
-            }
-        }
-        uint4 o;
-        uint32_t* ow = &o.x;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-            ow[i] = *reinterpret_cast<uint32_t*>(&b);
-        }
-        *(reinterpret_cast<uint4*>(p.y + static_cast<int64_t>(t) * p.dim) + c) = o;
-    }
+    const int t = blockIdx.y, c = blockIdx.x * kCombineThreads + threadIdx.x;
+    if (c >= p.dim / 8) return;
+    float acc[8];
+    combine_sum8(p, t, c, acc);
+    *(reinterpret_cast<uint4*>(p.y + static_cast<int64_t>(t) * p.dim) + c) = pack_bf16x8(acc);
 }
 
 // Expert parallelism over two ranks: each rank sums the outputs of its own experts for every token, pushes
@@ -272,7 +330,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
 constexpr int kEpMaxTokens = 512;
 constexpr int64_t kEpCtrlOffset = 2 * kEpMaxTokens * 4;   // behind the flags: {call sequence, CTAs done}
 constexpr int64_t kEpFlagBytes = kEpCtrlOffset + 256;
-constexpr int kEpMaxVec = 4;            // 8-value vectors per thread: dim <= 8192
+constexpr int kEpMaxDim = 8192;         // one 8-value vector per thread of a 1024-thread CTA
 
 struct CombineEpParams {
     CombineParams c;
@@ -300,45 +358,23 @@ __device__ __forceinline__ float4 ld_volatile_f32x4(const float* p) {   // writt
     return v;
 }
 
-__global__ void __launch_bounds__(256) moe_combine_ep2_kernel(CombineEpParams q) {
+// one CTA per token, one 8-dim vector per thread (dim <= 8192)
+__global__ void __launch_bounds__(1024) moe_combine_ep2_kernel(CombineEpParams q) {
     pdl_launch_dependents();
     pdl_wait();
     const CombineParams& p = q.c;
     __shared__ int peer_ok;
-    const int t = blockIdx.x;
+    const int t = blockIdx.x, c = threadIdx.x;
+    const bool mine = c < p.dim / 8;
     const int epoch = q.epoch ? q.epoch : ld_acquire_sys(q.ctrl) + 1;
     const int set = epoch & 1;
     const int64_t row_off = (static_cast<int64_t>(set) * q.tokens_max + t) * p.dim;
-    float acc[kEpMaxVec][8];
-#pragma unroll
-    for (int v = 0; v < kEpMaxVec; ++v) {
-        const int c = threadIdx.x + v * 256;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[v][i] = 0.f;
-        if (c >= p.dim / 8) continue;
-        for (int j = 0; j < p.k; ++j) {
-            const int row = p.pair_row[t * p.k + j];
-            if (row < 0) continue;
-            const uint4 raw = *(reinterpret_cast<const uint4*>(p.out + static_cast<int64_t>(row) * p.dim) + c);
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                acc[v][2 * i] = __fadd_rn(acc[v][2 * i], __uint_as_float(w[i] << 16));
-                acc[v][2 * i + 1] = __fadd_rn(acc[v][2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
-            }
-        }
-        if (p.shared) {
-            const uint4 raw = *(reinterpret_cast<const uint4*>(p.shared + static_cast<int64_t>(t) * p.dim) + c);
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                acc[v][2 * i] = __fadd_rn(acc[v][2 * i], __uint_as_float(w[i] << 16));
-                acc[v][2 * i + 1] = __fadd_rn(acc[v][2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
-            }
-        }
+    float acc[8];
+    if (mine) {
+        combine_sum8(p, t, c, acc);
         float4* dst = reinterpret_cast<float4*>(q.peer_rows + row_off + c * 8);
-        dst[0] = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
-        dst[1] = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+        dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
     __threadfence_system();
     __syncthreads();
@@ -358,24 +394,13 @@ __global__ void __launch_bounds__(256) moe_combine_ep2_kernel(CombineEpParams q)
         peer_ok = ok;
     }
     __syncthreads();
-    const bool add = peer_ok != 0;
-#pragma unroll
-    for (int v = 0; v < kEpMaxVec; ++v) {
-        const int c = threadIdx.x + v * 256;
-        if (c >= p.dim / 8) continue;
-        if (add) {
+    if (mine) {
+        if (peer_ok != 0) {
             const float4 a = ld_volatile_f32x4(q.my_rows + row_off + c * 8), b = ld_volatile_f32x4(q.my_rows + row_off + c * 8 + 4);
-            acc[v][0] += a.x, acc[v][1] += a.y, acc[v][2] += a.z, acc[v][3] += a.w;
-            acc[v][4] += b.x, acc[v][5] += b.y, acc[v][6] += b.z, acc[v][7] += b.w;
+            acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
+            acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
         }
-        uint4 o;
-        uint32_t* ow = &o.x;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(acc[v][2 * i], acc[v][2 * i + 1]);
-            ow[i] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        *(reinterpret_cast<uint4*>(p.y + static_cast<int64_t>(t) * p.dim) + c) = o;
+        *(reinterpret_cast<uint4*>(p.y + static_cast<int64_t>(t) * p.dim) + c) = pack_bf16x8(acc);
     }
     if (q.epoch == 0 && threadIdx.x == 0) {
         // the last CTA to finish has seen every other CTA read the old number; it stores the new one
@@ -441,51 +466,57 @@ extern "C" int wuda_moe_dispatch_range(const int32_t* indices, const float* weig
     return WUDA_OK;
 }
 
-extern "C" int wuda_moe_gather_quant_nvfp4(const void* x_bf16, const int32_t* row_token, const int32_t* num_groups,
-                                           void* a_fp4, void* a_sf_packed, float global_scale, int max_groups, int k,
-                                           void* stream) {
+extern "C" int wuda_moe_gather_quant_nvfp4(const void* x_bf16, const int32_t* pair_row, void* a_fp4, void* a_sf_packed,
+                                           float global_scale, int tokens, int topk, int k, void* stream) {
     using namespace wuda;
     using namespace wuda::moe;
     clear_error();
-    WUDA_REQUIRE(max_groups >= 1, "max_groups must be >= 1");
+    WUDA_REQUIRE(tokens >= 1 && topk >= 1 && static_cast<long long>(tokens) * topk <= 65536, "tokens, topk >= 1 and at most 65536 pairs");
     WUDA_REQUIRE(k >= 256 && k % 256 == 0, "k must be a positive multiple of 256 (got %d)", k);
     WUDA_REQUIRE(global_scale > 0.f, "global_scale must be positive");
-    WUDA_REQUIRE(x_bf16 && row_token && num_groups && a_fp4 && a_sf_packed, "no array may be NULL");
+    WUDA_REQUIRE(x_bf16 && pair_row && a_fp4 && a_sf_packed, "no array may be NULL");
     WUDA_REQUIRE(aligned16(x_bf16) && aligned16(a_fp4) && aligned16(a_sf_packed), "x, a_fp4 and a_sf must be 16-byte aligned");
     GatherParams p;
     p.x = static_cast<const __nv_bfloat16*>(x_bf16);
-    p.row_token = row_token;
-    p.num_groups = num_groups;
+    p.pair_row = pair_row;
     p.a4 = static_cast<uint8_t*>(a_fp4);
     p.a_sf = static_cast<uint8_t*>(a_sf_packed);
     p.gs = global_scale;
     p.K = k;
-    WUDA_CUDA(launch_pdl(moe_gather_quant_kernel, dim3(max_groups * kGroupRows), dim3(256), 0, static_cast<cudaStream_t>(stream), p));
+    p.pairs = tokens * topk;
+    p.topk = topk;
+    const long long items = static_cast<long long>(p.pairs) * (k / 16);
+    WUDA_REQUIRE(items < (1ll << 31), "tokens * topk * k / 16 must stay below 2^31");
+    WUDA_CUDA(launch_pdl(moe_gather_quant_kernel, dim3(static_cast<unsigned>((items + kQuantThreads - 1) / kQuantThreads)),
+                         dim3(kQuantThreads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 
-extern "C" int wuda_moe_swiglu_quant_nvfp4(const void* h_bf16, const int32_t* row_token, const float* row_weight,
-                                           const int32_t* num_groups, void* a_fp4, void* a_sf_packed, float global_scale,
-                                           float swiglu_limit, int max_groups, int inter, void* stream) {
+extern "C" int wuda_moe_swiglu_quant_nvfp4(const void* h_bf16, const int32_t* pair_row, const float* pair_weight, void* a_fp4,
+                                           void* a_sf_packed, float global_scale, float swiglu_limit, int tokens, int topk,
+                                           int inter, void* stream) {
     using namespace wuda;
     using namespace wuda::moe;
     clear_error();
-    WUDA_REQUIRE(max_groups >= 1, "max_groups must be >= 1");
+    WUDA_REQUIRE(tokens >= 1 && topk >= 1 && static_cast<long long>(tokens) * topk <= 65536, "tokens, topk >= 1 and at most 65536 pairs");
     WUDA_REQUIRE(inter >= 256 && inter % 256 == 0, "inter must be a positive multiple of 256 (got %d)", inter);
     WUDA_REQUIRE(global_scale > 0.f, "global_scale must be positive");
-    WUDA_REQUIRE(h_bf16 && row_token && row_weight && num_groups && a_fp4 && a_sf_packed, "no array may be NULL");
+    WUDA_REQUIRE(h_bf16 && pair_row && pair_weight && a_fp4 && a_sf_packed, "no array may be NULL");
     WUDA_REQUIRE(aligned16(h_bf16) && aligned16(a_fp4) && aligned16(a_sf_packed), "h, a_fp4 and a_sf must be 16-byte aligned");
     SwigluParams p;
     p.h = static_cast<const __nv_bfloat16*>(h_bf16);
-    p.row_token = row_token;
-    p.row_weight = row_weight;
-    p.num_groups = num_groups;
+    p.pair_row = pair_row;
+    p.pair_weight = pair_weight;
     p.a4 = static_cast<uint8_t*>(a_fp4);
     p.a_sf = static_cast<uint8_t*>(a_sf_packed);
     p.gs = global_scale;
     p.limit = swiglu_limit;
     p.I = inter;
-    WUDA_CUDA(launch_pdl(moe_swiglu_quant_kernel, dim3(max_groups * kGroupRows), dim3(128), 0, static_cast<cudaStream_t>(stream), p));
+    p.pairs = tokens * topk;
+    const long long items = static_cast<long long>(p.pairs) * (inter / 16);
+    WUDA_REQUIRE(items < (1ll << 31), "tokens * topk * inter / 16 must stay below 2^31");
+    WUDA_CUDA(launch_pdl(moe_swiglu_quant_kernel, dim3(static_cast<unsigned>((items + kQuantThreads - 1) / kQuantThreads)),
+                         dim3(kQuantThreads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 
@@ -494,7 +525,8 @@ extern "C" int wuda_moe_combine(const void* expert_out_bf16, const int32_t* pair
     using namespace wuda;
     using namespace wuda::moe;
     clear_error();
-    WUDA_REQUIRE(tokens >= 1 && k >= 1 && dim >= 8 && dim % 8 == 0, "tokens, k >= 1 and dim a positive multiple of 8");
+    WUDA_REQUIRE(tokens >= 1 && tokens <= 65535 && k >= 1 && dim >= 8 && dim % 8 == 0,
+                 "tokens in [1, 65535], k >= 1 and dim a positive multiple of 8");
     WUDA_REQUIRE(expert_out_bf16 && pair_row && y_bf16, "expert_out, pair_row and y must not be NULL");
     WUDA_REQUIRE(aligned16(expert_out_bf16) && aligned16(shared_bf16) && aligned16(y_bf16), "rows must be 16-byte aligned");
     CombineParams p;
@@ -504,13 +536,14 @@ extern "C" int wuda_moe_combine(const void* expert_out_bf16, const int32_t* pair
     p.y = static_cast<__nv_bfloat16*>(y_bf16);
     p.k = k;
     p.dim = dim;
-    WUDA_CUDA(launch_pdl(moe_combine_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream), p));
+    WUDA_CUDA(launch_pdl(moe_combine_kernel, dim3((dim / 8 + kCombineThreads - 1) / kCombineThreads, tokens), dim3(kCombineThreads), 0,
+                         static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 
 extern "C" int64_t wuda_moe_ep2_inbox_bytes(int tokens_max, int dim) {
     using namespace wuda::moe;
-    if (tokens_max < 1 || tokens_max > kEpMaxTokens || dim < 8 || dim % 8 != 0 || dim > kEpMaxVec * 256 * 8) return -1;
+    if (tokens_max < 1 || tokens_max > kEpMaxTokens || dim < 8 || dim % 8 != 0 || dim > kEpMaxDim) return -1;
     return kEpFlagBytes + 2ll * tokens_max * dim * 4;
 }
 
@@ -522,7 +555,7 @@ extern "C" int wuda_moe_combine_ep2(const void* expert_out_bf16, const int32_t* 
     clear_error();
     WUDA_REQUIRE(tokens >= 1 && k >= 1 && tokens <= tokens_max, "1 <= tokens <= tokens_max and k >= 1");
     WUDA_REQUIRE(wuda_moe_ep2_inbox_bytes(tokens_max, dim) > 0, "tokens_max must be in [1, %d] and dim a multiple of 8 up to %d",
-                 kEpMaxTokens, kEpMaxVec * 256 * 8);
+                 kEpMaxTokens, kEpMaxDim);
     WUDA_REQUIRE(expert_out_bf16 && pair_row && y_bf16 && my_inbox && peer_inbox,
                  "expert_out, pair_row, y and both inboxes must not be NULL");
     WUDA_REQUIRE(aligned16(expert_out_bf16) && aligned16(shared_bf16) && aligned16(y_bf16) && aligned16(my_inbox) &&
@@ -545,6 +578,6 @@ extern "C" int wuda_moe_combine_ep2(const void* expert_out_bf16, const int32_t* 
     q.epoch = epoch;
     q.wait_ns = static_cast<unsigned long long>(peer_wait_ms) * 1000ull * 1000ull;
     q.status = status_word;
-    WUDA_CUDA(launch_pdl(moe_combine_ep2_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream), q));
+    WUDA_CUDA(launch_pdl(moe_combine_ep2_kernel, dim3(tokens), dim3((dim / 8 + 31) / 32 * 32), 0, static_cast<cudaStream_t>(stream), q));
     return WUDA_OK;
 }

@@ -43,7 +43,8 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kBins = 4096;
 constexpr int kCandCap = 8192;
 constexpr int kSamples = 2048;
-constexpr int kTieCap = 2048;       // candidates of the threshold bin that are ranked pairwise
+constexpr int kTieCap = 2048;       // candidates of the threshold bin that are ranked exactly in shared memory
+constexpr int kPairwiseMax = 128;   // up to this many they are ranked by counting (quadratic); more are sorted
 constexpr int kMaxCluster = 2;
 constexpr int kMaxSeg = kMaxCluster * kWarps;
 constexpr int kLoadBatch = 4;       // 16-byte loads in flight per thread in the scan (more only queue up in the L2)
@@ -80,8 +81,7 @@ __device__ __forceinline__ int hslot(uint32_t bin) { return static_cast<int>(bin
 struct Shared {
     uint32_t hist[kBins + kBins / 32];
     uint2 cand[kCandCap];            // (key, index)
-    uint32_t tie_key[kTieCap];
-    int32_t tie_idx[kTieCap];
+    unsigned long long tie[kTieCap];   // (key << 32) | ~index: larger = larger key, then lower index; all distinct
     int32_t pages[kPageCache];       // the row's page-table entries
     uint32_t seg_cnt[kMaxSeg];
     uint32_t seg_off[kMaxSeg];
@@ -509,27 +509,43 @@ __global__ void __launch_bounds__(kThreads, 2) topk_kernel(const Params p) {
                                     uint32_t at = 0;
                                     if (lane == __ffs(b) - 1) at = atomicAdd(&s.tie_count, __popc(b));
                                     at = __shfl_sync(0xffffffffu, at, __ffs(b) - 1) + __popc(b & lane_lt);
-                                    if (in) {
-                                        s.tie_key[at] = key;
-                                        s.tie_idx[at] = static_cast<int32_t>(cand.y);
-                                    }
+                                    if (in) s.tie[at] = (static_cast<unsigned long long>(key) << 32) | (~cand.y);
                                 }
                             }
                             if (lane == 0) s.seg_off[g] = sel;
                         }
                         __syncthreads();
                         // The bin's members ranked exactly - larger key first, lower index first among equals: the
-                        // first need_a of them take the last output positions.  Meanwhile every warp turns the
-                        // segment counts into its segments' first positions.
-                        for (uint32_t t = threadIdx.x; t < c_a; t += kThreads) {
-                            const uint32_t kt = s.tie_key[t];
-                            const int it = s.tie_idx[t];
-                            uint32_t ahead = 0;
-                            for (uint32_t j = 0; j < c_a; ++j) {
-                                const uint32_t kj = s.tie_key[j];
-                                ahead += (kj > kt) || (kj == kt && s.tie_idx[j] < it);
+                        // first need_a of them take the last output positions.  A few dozen (the usual case) are
+                        // ranked by counting, each against all; a bin with hundreds of members (values crowded into
+                        // a few binades, runs of equal scores) is sorted instead: counting is quadratic.
+                        if (c_a <= static_cast<uint32_t>(kPairwiseMax)) {
+                            for (uint32_t t = threadIdx.x; t < c_a; t += kThreads) {
+                                const unsigned long long mine_t = s.tie[t];
+                                uint32_t ahead = 0;
+                                for (uint32_t j = 0; j < c_a; ++j) ahead += s.tie[j] > mine_t;
+                                if (ahead < need_a) put_cached(p, s, r, above_a + ahead, static_cast<int>(~static_cast<uint32_t>(mine_t)));
                             }
-                            if (ahead < need_a) put_cached(p, s, r, above_a + ahead, it);
+                        } else {
+                            uint32_t pow2 = 2u * kPairwiseMax;
+                            while (pow2 < c_a) pow2 <<= 1;
+                            for (uint32_t t = c_a + threadIdx.x; t < pow2; t += kThreads) s.tie[t] = 0ull;   // below every real entry
+                            __syncthreads();
+                            for (uint32_t size = 2; size <= pow2; size <<= 1)
+                                for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+                                    for (uint32_t t = threadIdx.x; t < pow2 / 2; t += kThreads) {
+                                        const uint32_t a = 2u * t - (t & (stride - 1u)), b = a + stride;   // bitonic network, descending
+                                        const unsigned long long va = s.tie[a], vb = s.tie[b];
+                                        const bool descending = (a & size) == 0u;
+                                        if ((va < vb) == descending) {
+                                            s.tie[a] = vb;
+                                            s.tie[b] = va;
+                                        }
+                                    }
+                                    __syncthreads();
+                                }
+                            for (uint32_t t = threadIdx.x; t < need_a; t += kThreads)
+                                put_cached(p, s, r, above_a + t, static_cast<int>(~static_cast<uint32_t>(s.tie[t])));
                         }
                         for (int g = warp; g < nseg; g += kWarps) {
                             uint32_t at = lane < g ? s.seg_off[lane] : 0u;       // positions taken by the segments before

@@ -134,20 +134,18 @@ class MoERunner:
                                           self.num_groups.data_ptr(), self.row_token.data_ptr(), self.row_weight.data_ptr(),
                                           self.pair_row.data_ptr(), m, self.topk, w.experts, self.expert_first,
                                           self.experts_total, self.max_groups, st, s))
-        check(lib.wuda_moe_gather_quant_nvfp4(x.data_ptr(), self.row_token.data_ptr(), self.num_groups.data_ptr(),
-                                              self.a1.data_ptr(), self.a1_sf.data_ptr(), w.act_scale_in, self.max_groups,
-                                              w.dim, s))
+        check(lib.wuda_moe_gather_quant_nvfp4(x.data_ptr(), self.pair_row.data_ptr(), self.a1.data_ptr(), self.a1_sf.data_ptr(),
+                                              w.act_scale_in, m, self.topk, w.dim, s))
         d = w.dev
         check(lib.wuda_gemm_nvfp4_grouped(self.a1.data_ptr(), self.a1_sf.data_ptr(), w.act_scale_in, d["w13"].data_ptr(),
                                           d["w13_sf"].data_ptr(), d["w13_gs"].data_ptr(), self.group_expert.data_ptr(),
-                                          self.num_groups.data_ptr(), self.h.data_ptr(), self.max_groups, w.experts,
+                                          self.num_groups.data_ptr(), self.row_token.data_ptr(), self.h.data_ptr(), self.max_groups, w.experts,
                                           2 * w.inter, w.dim, self.scratch.data_ptr(), self.scratch.numel(), st, s))
-        check(lib.wuda_moe_swiglu_quant_nvfp4(self.h.data_ptr(), self.row_token.data_ptr(), self.row_weight.data_ptr(),
-                                              self.num_groups.data_ptr(), self.a2.data_ptr(), self.a2_sf.data_ptr(),
-                                              w.act_scale_mid, w.swiglu_limit, self.max_groups, w.inter, s))
+        check(lib.wuda_moe_swiglu_quant_nvfp4(self.h.data_ptr(), self.pair_row.data_ptr(), weights.data_ptr(), self.a2.data_ptr(),
+                                              self.a2_sf.data_ptr(), w.act_scale_mid, w.swiglu_limit, m, self.topk, w.inter, s))
         check(lib.wuda_gemm_nvfp4_grouped(self.a2.data_ptr(), self.a2_sf.data_ptr(), w.act_scale_mid, d["w2"].data_ptr(),
                                           d["w2_sf"].data_ptr(), d["w2_gs"].data_ptr(), self.group_expert.data_ptr(),
-                                          self.num_groups.data_ptr(), self.out.data_ptr(), self.max_groups, w.experts,
+                                          self.num_groups.data_ptr(), self.row_token.data_ptr(), self.out.data_ptr(), self.max_groups, w.experts,
                                           w.dim, w.inter, self.scratch.data_ptr(), self.scratch.numel(), st, s))
         if y is None:
             y = torch.empty(m, w.dim, dtype=torch.bfloat16, device=x.device)
