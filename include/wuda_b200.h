@@ -50,6 +50,7 @@ typedef enum wuda_device_status {
     WUDA_DEV_TIMEOUT_GEMM_EMPTY = 122,
     WUDA_DEV_TIMEOUT_GEMM_TMEM_FULL = 123,
     WUDA_DEV_TIMEOUT_GEMM_TMEM_EMPTY = 124,
+    WUDA_DEV_SCALE_NOT_POW2 = 125, /* a scale given to a *_pow2 GEMM was not a power of two: it was truncated to one */
     WUDA_DEV_TIMEOUT_PEER_FLAG = 131,
     WUDA_DEV_BAD_DESTINATION = 141, /* cache destination outside the pool: that record was not written */
     WUDA_DEV_BAD_STATE_ROW = 142,   /* state_row outside the state rings: that row was skipped         */
@@ -315,6 +316,8 @@ typedef struct wuda_csa_weights {
     int main_heads;            /* heads of 512 in the weight                                  */
     int out_heads;             /* heads of q_main_out (a multiple of main_heads)              */
     float eps;
+    int scales_pow2;           /* non-zero: every wq_b scale is a power of two (the reference's UE8M0 scales) and the
+                                  projection takes wuda_gemm_fp8_blockscaled_pow2                                  */
 } wuda_csa_weights;
 
 typedef struct wuda_csa_caches {
@@ -644,6 +647,24 @@ int wuda_gemm_fp8_grouped(const void* a, const float* a_scales, const void* w, c
                           int32_t* status_word, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * The same two GEMMs for scales that are exact powers of two (what the reference's checkpoints and its
+ * quantisers hold: UE8M0 scales, kernels/wq_b_fp8_gemm.cu:139-183, include/cluster_mma_fp8.cuh:144-301).
+ * The scales are then applied inside the tensor core (tcgen05.mma kind::mxf8f6f4.block_scale, exponent
+ * bytes in tensor memory), a weight tile accumulates over its whole K range there, and the per-block
+ * promotion on CUDA cores that bounds the general entry points from 64 rows up is gone.  Arguments,
+ * layouts, scratch (wuda_gemm_fp8_scratch_bytes) and results as for wuda_gemm_fp8_blockscaled /
+ * wuda_gemm_fp8_grouped, with the products added in fp32 inside the tensor core instead of block by block.
+ * A scale that is not a power of two is truncated to the one below and reported as
+ * WUDA_DEV_SCALE_NOT_POW2; a zero scale reads as 2^-127.
+ */
+int wuda_gemm_fp8_blockscaled_pow2(const void* a, const float* a_scales, const void* w, const float* w_scales,
+                                   void* c_bf16, int m, int n, int k, void* scratch, int64_t scratch_bytes,
+                                   int32_t* status_word, void* stream);
+int wuda_gemm_fp8_grouped_pow2(const void* a, const float* a_scales, const void* w, const float* w_scales, void* c_bf16,
+                               int m, int n_per_group, int k, int groups, void* scratch, int64_t scratch_bytes,
+                               int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * BF16 GEMM for decode-sized M:  c[m, n] = sum_k a[m, k] * w[n, k], fp32 accumulation, written
  * as bf16 or (c_is_fp32 != 0) as fp32.
  *
@@ -820,6 +841,8 @@ typedef struct wuda_layer_weights {
     float act_scale_in, act_scale_mid;  /* tensor scales of the NVFP4 activations                           */
     float softmax_scale;
     float hc_eps, rms_eps, norm_eps;
+    int fp8_scales_pow2;            /* non-zero: the FP8 weights' scales are powers of two; projections whose shape gains
+                                       from it (wo_a) take the *_pow2 GEMMs                                        */
 } wuda_layer_weights;
 
 typedef struct wuda_layer_state {

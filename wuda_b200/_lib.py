@@ -45,7 +45,7 @@ class CsaWeights(ctypes.Structure):
     """wuda_csa_weights"""
     _fields_ = [("wq_b", c_vp), ("wq_b_scales", c_vp), ("q_norm", c_vp), ("idx_norm", c_vp), ("main_norm", c_vp),
                 ("win_norm", c_vp), ("cos_table", c_vp), ("sin_table", c_vp), ("max_pos", c_int), ("q_lora", c_int),
-                ("index_heads", c_int), ("main_heads", c_int), ("out_heads", c_int), ("eps", c_float)]
+                ("index_heads", c_int), ("main_heads", c_int), ("out_heads", c_int), ("eps", c_float), ("scales_pow2", c_int)]
 
 
 class CsaCaches(ctypes.Structure):
@@ -93,7 +93,8 @@ class LayerWeights(ctypes.Structure):
                 [(n, c_int) for n in ("hidden", "o_groups", "experts_total", "expert_first", "experts_local", "moe_topk",
                                       "score_func", "inter", "shared_inter")] +
                 [(n, c_float) for n in ("route_scale", "swiglu_limit", "act_scale_in", "act_scale_mid", "softmax_scale",
-                                        "hc_eps", "rms_eps", "norm_eps")])
+                                        "hc_eps", "rms_eps", "norm_eps")] +
+                [("fp8_scales_pow2", c_int)])
 
 
 class LayerState(ctypes.Structure):
@@ -146,6 +147,8 @@ SIGNATURES = {
     "wuda_front_emit": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_int, c_vp,
                                 c_vp]),
     "wuda_gemm_fp8_grouped": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
+    "wuda_gemm_fp8_grouped_pow2": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
+    "wuda_gemm_fp8_blockscaled_pow2": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
     "wuda_moe_route": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_vp]),
     "wuda_moe_max_groups": (c_int, [c_int, c_int, c_int]),
     "wuda_moe_dispatch": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp, c_vp]),

@@ -4,6 +4,7 @@ between launches is not forced: weights (>= 15 MB) are re-streamed from HBM ever
 because consecutive launches use different weight buffers that together exceed L2.
 
     python -m wuda_b200.benchmarks gemm_fp8
+    python -m wuda_b200.benchmarks gemm_fp8_pow2                   (power-of-two scales applied inside the tensor core)
     python -m wuda_b200.benchmarks gemm_nvfp4
     python -m wuda_b200.benchmarks norm_rope_quant
     python -m wuda_b200.benchmarks csa_chain                       (layer launch of the indexer half-step)
@@ -70,11 +71,13 @@ def time_graph(fn, reps=20, inner=10):
     return e0.elapsed_time(e1) * 1e3 / (reps * inner)
 
 
-def gemm_fp8():
+def gemm_fp8(pow2=False):
     hbm, tf, kind = peaks()
-    print("block-scaled FP8 GEMM, bf16 out; peaks (%s): %.0f GB/s HBM, %.0f TFLOP/s dense bf16 (fp8 nominal = 2x)" % (kind, hbm, tf))
+    print("block-scaled FP8 GEMM%s, bf16 out; peaks (%s): %.0f GB/s HBM, %.0f TFLOP/s dense bf16 (fp8 nominal = 2x)"
+          % (" with power-of-two scales applied in the tensor core" if pow2 else "", kind, hbm, tf))
     print("%6s %6s %6s %9s %9s %8s %9s %8s" % ("M", "N", "K", "us", "GB/s", "of HBM", "TFLOP/s", "of 2xbf16"))
-    for n, k in ((24576, 7168), (7168, 16384), (2112, 7168), (4096, 7168)):
+    shapes = ((24576, 7168), (7168, 16384), (2112, 7168), (4096, 7168)) + (((73728, 1536),) if pow2 else ())
+    for n, k in shapes:
         for m in (1, 8, 32, 64, 128, 256):
             # enough distinct weight buffers that a launch never finds its weights in the 126 MB L2
             copies = max(2, int(300e6 // (n * k)) + 1)
@@ -84,11 +87,13 @@ def gemm_fp8():
             w0 = torch.from_numpy(cases[0]["w"]).cuda()
             ws = [w0.clone().view(torch.float8_e4m3fn) for _ in range(copies)]
             w_s = torch.from_numpy(cases[0]["w_s"]).cuda()
+            if pow2:
+                a_s, w_s = torch.exp2(torch.log2(a_s).round()), torch.exp2(torch.log2(w_s).round())
             out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
             state = {"i": 0}
 
             def fn():
-                wuda.fp8_gemm(a, a_s, ws[state["i"] % copies], w_s, out=out)
+                wuda.fp8_gemm(a, a_s, ws[state["i"] % copies], w_s, out=out, pow2_scales=pow2)
                 state["i"] += 1
 
             us = time_graph(fn, reps=10, inner=copies * 2)
@@ -544,6 +549,15 @@ def sparse_mla(batches=(4, 16, 64, 128), heads=128, window=128, topk=2048, conte
                                                          gathered / us / 1e3, gathered / us / 1e3 / hbm * 100))
 
 
+def pair_sync(group):
+    """Both ranks of a pair have finished their set-up before either starts a call that waits for the other:
+    the exchange kernels bound their waits, and set-up times differ by more than that bound."""
+    import torch.distributed as dist
+    torch.cuda.synchronize()
+    if group is not None:
+        dist.barrier(group=group)
+
+
 def time_replays(replay, reps, group=None, flush=None):
     """Mean device time (us) of replay(), timed with CUDA events around each call on the current stream; with a
     process group, the ranks start each call together (host barrier) and the mean of the per-call MAX over ranks
@@ -590,6 +604,7 @@ def tp2_gemm_leg(group, pair_rank, m=64, n=7168, k=16384, reps=30, seed=1234):
     status = wuda.device_status_word()
 
     def graph_of(fn):
+        pair_sync(group)
         fn(ws[0])
         torch.cuda.synchronize()
         side = torch.cuda.Stream()
@@ -640,6 +655,7 @@ def ep2_combine_leg(group, pair_rank, tokens=64, topk=8, experts=256, dim=7168, 
         runner.forward(x, rw, idx, y=y)
         state["idx"] = idx
 
+    pair_sync(group)
     step()
     torch.cuda.synchronize()
     side = torch.cuda.Stream()
@@ -692,9 +708,11 @@ def layer_leg(batch=64, context=32768, topk=2048, reps=20, group=None, pair_rank
         layer.check_status()
         print("layer: %d eager passes done" % launches_only)
         return None, None
+    pair_sync(group)
     layer.capture(x, batch)
     us = time_replays(layer.replay, reps, group)
     layer.check_status()
+    pair_sync(group)
     out = layer.replay()
     torch.cuda.synchronize()
     idx = layer.route_indices
@@ -745,11 +763,13 @@ def layer_tp2(batch=64, context=32768):
 def one(kind, m, n, k, launches=5):
     """A few eager launches of one GEMM shape (profiler captures)."""
     t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
-    if kind == "gemm_fp8":
+    if kind in ("gemm_fp8", "gemm_fp8_pow2"):
         c = workloads.make_gemm_fp8_case(m, n, k, seed=7)
         a, w = t(c["a"]).view(torch.float8_e4m3fn), t(c["w"]).view(torch.float8_e4m3fn)
         a_s, w_s = t(c["a_s"]), t(c["w_s"])
-        fn = lambda: wuda.fp8_gemm(a, a_s, w, w_s)
+        if kind == "gemm_fp8_pow2":
+            a_s, w_s = torch.exp2(torch.log2(a_s).round()), torch.exp2(torch.log2(w_s).round())
+        fn = lambda: wuda.fp8_gemm(a, a_s, w, w_s, pow2_scales=kind == "gemm_fp8_pow2")
     else:
         c = workloads.make_gemm_nvfp4_case(m, n, k, seed=7)
         a, w, a_sf, w_sf = t(c["a"]), t(c["w"]), t(c["a_sf_packed"]), t(c["w_sf_packed"])
@@ -760,7 +780,7 @@ def one(kind, m, n, k, launches=5):
     print("ran %d launches of %s M=%d N=%d K=%d" % (launches, kind, m, n, k))
 
 
-KINDS = {"topk": topk, "gemm_fp8": gemm_fp8, "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(contexts=(32768,), launches_only=3),
+KINDS = {"topk": topk, "gemm_fp8": gemm_fp8, "gemm_fp8_pow2": lambda: gemm_fp8(pow2=True), "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(contexts=(32768,), launches_only=3),
          "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(32,), launches_only=3),
          "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
          "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,

@@ -112,8 +112,9 @@ extern "C" int wuda_csa_decode_step(const wuda_csa_weights* w, const wuda_csa_ca
         status = wuda_rmsnorm_quant_fp8(s->q_raw, s->q_raw_stride, w->q_norm, 0, w->eps, nullptr, ws->q_fp8, ws->q_scales,
                                         m, w->q_lora, 1, stream);
     if (status == WUDA_OK)
-        status = wuda_gemm_fp8_blockscaled(ws->q_fp8, ws->q_scales, w->wq_b, w->wq_b_scales, ws->y, m, n_total, w->q_lora,
-                                           ws->gemm_scratch, ws->gemm_scratch_bytes, ws->status_word, stream);
+        status = (w->scales_pow2 ? wuda_gemm_fp8_blockscaled_pow2 : wuda_gemm_fp8_blockscaled)(
+            ws->q_fp8, ws->q_scales, w->wq_b, w->wq_b_scales, ws->y, m, n_total, w->q_lora, ws->gemm_scratch, ws->gemm_scratch_bytes,
+            ws->status_word, stream);
     // ---- branch B (side stream): the main heads' query tail, needed only by the attention that follows
     bool query_forked = false;
     if (status == WUDA_OK && s->q_main_out) {

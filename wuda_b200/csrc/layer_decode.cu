@@ -269,8 +269,9 @@ extern "C" int wuda_layer_decode(const wuda_layer_weights* w, const wuda_layer_s
     const int o_width = heads * kHeadDim, z_width = w->o_groups * kORank;
     WUDA_STAGE(wuda_rope_quant_fp8(b.mla_out, t->pos, w->csa.cos_table, w->csa.sin_table, nullptr, b.o_fp8, b.o_scale, m, heads,
                                    kHeadDim, kRopeDim, w->csa.max_pos, 1, 1, stream));
-    WUDA_STAGE(wuda_gemm_fp8_grouped(b.o_fp8, b.o_scale, w->wo_a, w->wo_a_scales, b.z, m, kORank, o_width / w->o_groups, w->o_groups,
-                                     b.gemm_scratch, b.gemm_scratch_bytes, status, stream));
+    WUDA_STAGE((w->fp8_scales_pow2 ? wuda_gemm_fp8_grouped_pow2 : wuda_gemm_fp8_grouped)(
+        b.o_fp8, b.o_scale, w->wo_a, w->wo_a_scales, b.z, m, kORank, o_width / w->o_groups, w->o_groups, b.gemm_scratch,
+        b.gemm_scratch_bytes, status, stream));
     WUDA_STAGE(wuda_rmsnorm_quant_fp8(b.z, z_width, nullptr, 0, 0.0f, nullptr, b.z_fp8, b.z_scale, m, z_width, 1, stream));
     if (s->tp_peer_inbox)
         WUDA_STAGE(wuda_gemm_fp8_blockscaled_tp2(b.z_fp8, b.z_scale, w->wo_b, w->wo_b_scales, b.projected, m, hidden, z_width,

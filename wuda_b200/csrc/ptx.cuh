@@ -28,6 +28,7 @@ enum DeviceStatus : int {
     kDevTimeoutGemmEmpty = 122,
     kDevTimeoutGemmTmemFull = 123,
     kDevTimeoutGemmTmemEmpty = 124,
+    kDevScaleNotPow2 = 125,         // a scale given to the power-of-two GEMM was not one: the power of two below it was used
     kDevTimeoutPeerFlag = 131,
     kDevTimeoutMlaKeys = 151,       // sparse attention: a key block never arrived
     kDevTimeoutMlaScores = 152,     // ... its scores never completed

@@ -25,7 +25,9 @@ class CsaWeights:
     fp32 128x128 block scales; the norm weights are fp32; the tables fp32 [max_pos, 32]."""
 
     def __init__(self, wq_b, wq_b_scales, q_norm, idx_norm, main_norm, win_norm, cos_table, sin_table,
-                 index_heads=64, main_heads=128, out_heads=None, eps=1e-6):
+                 index_heads=64, main_heads=128, out_heads=None, eps=1e-6, scales_pow2=False):
+        """scales_pow2: every wq_b scale is a power of two (the reference's UE8M0 scales); the projection then runs on
+        the GEMM that applies the scales inside the tensor core."""
         self.q_lora = wq_b.size(1)
         self.index_heads, self.main_heads = index_heads, main_heads
         self.out_heads = out_heads or main_heads
@@ -39,7 +41,7 @@ class CsaWeights:
             if not (t.is_cuda and t.is_contiguous()) or (name != "wq_b" and t.dtype != torch.float32):
                 raise ValueError(name + " must be a contiguous CUDA tensor (fp32 unless wq_b)")
         self.c = _lib.CsaWeights(max_pos=cos_table.size(0), q_lora=self.q_lora, index_heads=index_heads,
-                                 main_heads=main_heads, out_heads=self.out_heads, eps=eps,
+                                 main_heads=main_heads, out_heads=self.out_heads, eps=eps, scales_pow2=int(bool(scales_pow2)),
                                  **{k: t.data_ptr() for k, t in self.tensors.items()})
 
 

@@ -195,6 +195,7 @@ class DecoderLayer:
         w.act_scale_in, w.act_scale_mid = float(routed.act_scale_in), float(routed.act_scale_mid)
         w.softmax_scale = float(a.softmax_scale)
         w.hc_eps = w.rms_eps = w.norm_eps = 1e-6
+        w.fp8_scales_pow2 = int(bool(hw.o_proj.scales_pow2))
         self._w = w
         self._geometry = (self.max_batch, a.topk, st.logits_stride, a.swa_idx.size(1))
         need = lib.wuda_layer_workspace_bytes(ctypes.byref(w), *self._geometry)

@@ -30,20 +30,24 @@ def model1_pool(pages, epb, seed, device="cuda"):
     return pool
 
 
-def _fp8_weight(g, n, k, device):
+def _fp8_weight(g, n, k, device, pow2=True):
     """Random e4m3 bytes of moderate magnitude (exponent field <= 8: |w| <= 3.75) with both signs, and
-    128x128 block scales around 1e-2, so that a K = 7168 product stays O(1)."""
+    128x128 block scales around 1e-2, so that a K = 7168 product stays O(1); with pow2 the scales are rounded to
+    powers of two, the form the reference's checkpoints hold (UE8M0)."""
     b = torch.randint(0, 0x48, (n, k), generator=g, dtype=torch.uint8, device=device)
     sign = torch.randint(0, 2, (n, k), generator=g, dtype=torch.uint8, device=device) << 7
     scales = torch.rand(((n + 127) // 128, k // 128), generator=g, device=device) * 1e-2 + 5e-3
+    if pow2:
+        scales = torch.exp2(torch.log2(scales).round())
     return (b | sign).view(torch.float8_e4m3fn), scales
 
 
 def build_random_layer(batch, context, topk=2048, rank=0, world=1, tp_link=None, ep_link=None, seed=11,
-                       experts=256, inter=2048, moe_topk=8, device="cuda", peer_wait_ms=2000, native=True):
+                       experts=256, inter=2048, moe_topk=8, device="cuda", peer_wait_ms=2000, native=True, pow2_scales=True):
     """Returns (layer, slots, hidden_states): a DecoderLayer whose requests all stand at position context - 1
     (the timed token), the request slots, and bf16 [batch, 4, hidden] residual streams.  world = 2 builds what
-    rank `rank` of a tensor-parallel pair holds and needs both links."""
+    rank `rank` of a tensor-parallel pair holds and needs both links.  pow2_scales: FP8 weight scales are powers
+    of two (as in the reference's checkpoints) and the projections that gain from it apply them in the tensor core."""
     if world not in (1, 2) or (world == 2 and (tp_link is None or ep_link is None)):
         raise ValueError("world must be 1, or 2 with both links")
     dev = device
@@ -53,7 +57,7 @@ def build_random_layer(batch, context, topk=2048, rank=0, world=1, tp_link=None,
     rnd = lambda *s, scale=1.0: torch.randn(*s, generator=g, device=dev) * scale
     n_index = INDEX_HEADS * 128
     # ---- attention half
-    wq_b, wq_b_s = _fp8_weight(g, n_index + MAIN_HEADS * 512, Q_LORA, dev)
+    wq_b, wq_b_s = _fp8_weight(g, n_index + MAIN_HEADS * 512, Q_LORA, dev, pow2_scales)
     ang = torch.outer(torch.arange(65536, dtype=torch.float32), 1.0 / (10000.0 ** (torch.arange(32) / 32.0))).to(dev)
     cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
     norms = [torch.rand(n, generator=g, device=dev) + 0.5 for n in (Q_LORA, 128, 512, 512)]
@@ -63,10 +67,10 @@ def build_random_layer(batch, context, topk=2048, rank=0, world=1, tp_link=None,
         wq_b = wq_b.view(torch.uint8)[rows].contiguous().view(torch.float8_e4m3fn)
         wq_b_s = wq_b_s[torch.cat([torch.arange(n_index // 128, device=dev),
                                    torch.arange(lo // 128, (lo + heads * 512) // 128, device=dev)])].contiguous()
-    csa = CsaWeights(wq_b, wq_b_s, *norms, cos, sin, index_heads=INDEX_HEADS, main_heads=heads)
-    front_w8, front_w8_s = _fp8_weight(g, 2048, hidden, dev)
-    wo_a, wo_a_s = _fp8_weight(g, GROUPS * 1024, 4096, dev)
-    wo_b, wo_b_s = _fp8_weight(g, hidden, GROUPS * 1024, dev)
+    csa = CsaWeights(wq_b, wq_b_s, *norms, cos, sin, index_heads=INDEX_HEADS, main_heads=heads, scales_pow2=pow2_scales)
+    front_w8, front_w8_s = _fp8_weight(g, 2048, hidden, dev, pow2_scales)
+    wo_a, wo_a_s = _fp8_weight(g, GROUPS * 1024, 4096, dev, pow2_scales)
+    wo_b, wo_b_s = _fp8_weight(g, hidden, GROUPS * 1024, dev, pow2_scales)
     sink = rnd(MAIN_HEADS)
     if world == 2:
         gpr = GROUPS // 2
@@ -80,7 +84,8 @@ def build_random_layer(batch, context, topk=2048, rank=0, world=1, tp_link=None,
         hc_weight=rnd(24, 4 * hidden, scale=0.01), hc_base=torch.zeros(24, device=dev), hc_scale=torch.ones(3, device=dev),
         attn_norm=(rnd(hidden, scale=0.1) + 1.0).bfloat16(), front_w8=front_w8, front_w8_scales=front_w8_s,
         front_w16=rnd(2624, hidden, scale=0.02).bfloat16(), ape=rnd(4, 1024), idx_ape=rnd(4, 256),
-        o_proj=o_proj.OProjWeights(wo_a.view(GROUPS // world, 1024, 4096), wo_a_s, wo_b, wo_b_s), attn_sink=sink)
+        o_proj=o_proj.OProjWeights(wo_a.view(GROUPS // world, 1024, 4096), wo_a_s, wo_b, wo_b_s, scales_pow2=pow2_scales),
+        attn_sink=sink)
     # ---- caches: every request stands one token before `context`
     pages_per_req = (context // 4 + 63) // 64 + 1
     cache = KVCacheManager(batch, batch * pages_per_req + batch, pages_per_req, device=dev)
@@ -100,8 +105,8 @@ def build_random_layer(batch, context, topk=2048, rank=0, world=1, tp_link=None,
     attention = AttentionHalfLayer(csa, hw, cache, batch, topk=topk, tp_link=tp_link)
     # ---- feed-forward half
     gate_w = rnd(experts, hidden, scale=0.05).bfloat16()
-    w13, w13_s = _fp8_weight(g, 2 * inter, hidden, dev)      # rows [0, inter) = w1 (gate), [inter, 2*inter) = w3 (up)
-    w2, w2_s = _fp8_weight(g, hidden, inter, dev)
+    w13, w13_s = _fp8_weight(g, 2 * inter, hidden, dev, pow2_scales)      # rows [0, inter) = w1 (gate), [inter, 2*inter) = w3 (up)
+    w2, w2_s = _fp8_weight(g, hidden, inter, dev, pow2_scales)
     all_experts = moe.RandomRoutedExperts(experts, inter, hidden, device=dev, seed=seed + 1)
     first = 0
     if world == 2:

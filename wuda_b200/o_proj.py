@@ -25,6 +25,7 @@ class OProjWeights:
     wo_a_scale: torch.Tensor   # fp32 [groups * n_per_group / 128, heads_per_group * 4]
     wo_b: torch.Tensor         # e4m3 [hidden, groups * n_per_group]  (or this rank's K slice)
     wo_b_scale: torch.Tensor   # fp32 [ceil(hidden / 128), K / 128]
+    scales_pow2: bool = False  # every scale is a power of two: wo_a runs on the GEMM that applies them in the tensor core
 
 
 def _pow2_block_quant(w):
@@ -45,11 +46,12 @@ def quantize_o_proj_weights(wo_a, wo_b):
         raise ValueError("wo_a must be [groups, 128*i, 128*j] and wo_b [128*h, groups * n_per_group]")
     qa, sa = _pow2_block_quant(wo_a.reshape(groups * npg, ka))
     qb, sb = _pow2_block_quant(wo_b)
-    return OProjWeights(qa.view(groups, npg, ka), sa, qb, sb)
+    return OProjWeights(qa.view(groups, npg, ka), sa, qb, sb, scales_pow2=True)
 
 
-def fp8_gemm_grouped(a, a_s, w, w_s, *, out=None, status_word=None):
-    """c[m, g, :] = a[m, g, :] @ w[g]^T for every group g in one launch (wuda_gemm_fp8_grouped).
+def fp8_gemm_grouped(a, a_s, w, w_s, *, out=None, status_word=None, pow2_scales=False):
+    """c[m, g, :] = a[m, g, :] @ w[g]^T for every group g in one launch (wuda_gemm_fp8_grouped, or with
+    pow2_scales=True - every scale a power of two - wuda_gemm_fp8_grouped_pow2).
     a e4m3 [M, groups * K] with fp32 scales [M, groups * K / 128]; w e4m3 [groups, N, K] with fp32
     scales [groups * N / 128, K / 128]; returns bf16 [M, groups * N]."""
     groups, n, k = w.shape
@@ -64,10 +66,10 @@ def fp8_gemm_grouped(a, a_s, w, w_s, *, out=None, status_word=None):
         out = torch.empty(m, groups * n, dtype=torch.bfloat16, device=a.device)
     need = lib.wuda_gemm_fp8_scratch_bytes(m, groups * n)
     scratch = ops._scratch_for(a.device, need)
-    check(lib.wuda_gemm_fp8_grouped(a.data_ptr(), a_s.data_ptr(), w.data_ptr(), w_s.data_ptr(), out.data_ptr(), m, n, k,
-                                    groups, scratch.data_ptr(), scratch.numel(),
-                                    status_word.data_ptr() if status_word is not None else None,
-                                    torch.cuda.current_stream().cuda_stream))
+    entry = lib.wuda_gemm_fp8_grouped_pow2 if pow2_scales else lib.wuda_gemm_fp8_grouped
+    check(entry(a.data_ptr(), a_s.data_ptr(), w.data_ptr(), w_s.data_ptr(), out.data_ptr(), m, n, k, groups, scratch.data_ptr(),
+                scratch.numel(), status_word.data_ptr() if status_word is not None else None,
+                torch.cuda.current_stream().cuda_stream))
     return out
 
 
@@ -87,7 +89,8 @@ def run_o_proj_mhc_post(mla_out, positions, cos_table, sin_table, residual, post
         raise ValueError("heads do not match wo_a's groups")
     _, o_fp8, o_scale = ops.rope_quant(mla_out, positions, cos_table, sin_table, ROPE_DIM, inverse=True, quant=True,
                                        scale_fmt="ue8m0")
-    z = fp8_gemm_grouped(o_fp8, o_scale, weights.wo_a, weights.wo_a_scale, status_word=status_word)
+    z = fp8_gemm_grouped(o_fp8, o_scale, weights.wo_a, weights.wo_a_scale, status_word=status_word,
+                         pow2_scales=weights.scales_pow2)
     z_fp8, z_scale = ops.act_quant(z, 128, "ue8m0")
     if tp_link is None:
         projected = ops.fp8_gemm(z_fp8, z_scale, weights.wo_b, weights.wo_b_scale, status_word=status_word)

@@ -566,9 +566,11 @@ def _scratch_for(device, nbytes):
     return buf
 
 
-def fp8_gemm(a, a_s, b, b_s, scale_dtype=torch.float32, *, out=None, status_word=None):
+def fp8_gemm(a, a_s, b, b_s, scale_dtype=torch.float32, *, out=None, status_word=None, pow2_scales=False):
     """C[M,N] = A[M,K] @ B[N,K]^T with 1x128 (A) and 128x128 (B) fp32 block scales, bf16
-    output: the origin's fp8_gemm(a, a_s, b, b_s) (origin/kernel.py:257-273)."""
+    output: the origin's fp8_gemm(a, a_s, b, b_s) (origin/kernel.py:257-273).  pow2_scales=True promises that
+    every scale is a power of two (the reference's UE8M0 scales) and takes the kernel that applies them inside
+    the tensor core."""
     _require(scale_dtype == torch.float32, "only fp32 scales are implemented")
     _require(a.is_cuda and a.is_contiguous() and a.dtype == torch.float8_e4m3fn, "a must be contiguous CUDA e4m3")
     _require(b.is_cuda and b.is_contiguous() and b.dtype == torch.float8_e4m3fn and b.dim() == 2,
@@ -586,9 +588,9 @@ def fp8_gemm(a, a_s, b, b_s, scale_dtype=torch.float32, *, out=None, status_word
     need = lib.wuda_gemm_fp8_scratch_bytes(m, n)
     _require(need >= 0, "m must be in [1, 256]")
     scratch = _scratch_for(a.device, need)
-    check(lib.wuda_gemm_fp8_blockscaled(a.data_ptr(), a_s.data_ptr(), b.data_ptr(), b_s.data_ptr(), out.data_ptr(),
-                                        m, n, k, scratch.data_ptr(), scratch.numel(),
-                                        status_word.data_ptr() if status_word is not None else None, _stream()))
+    entry = lib.wuda_gemm_fp8_blockscaled_pow2 if pow2_scales else lib.wuda_gemm_fp8_blockscaled
+    check(entry(a.data_ptr(), a_s.data_ptr(), b.data_ptr(), b_s.data_ptr(), out.data_ptr(), m, n, k, scratch.data_ptr(),
+                scratch.numel(), status_word.data_ptr() if status_word is not None else None, _stream()))
     return out
 
 
