@@ -625,6 +625,13 @@ int wuda_swiglu_quant_fp8(const void* h_bf16, void* y_bf16, void* y_fp8, float* 
  *             on the GPU).  It holds the fp32 partial tiles of weight tiles whose K range is
  *             split across SMs.
  */
+/* The GEMM launches the CALLING THREAD makes from now on (FP8, BF16, NVFP4) cover at most max_sms SMs; 0 gives
+ * them the whole device again.  Returns the previous setting.  For callers that run two launches side by side on
+ * two streams: a GEMM of a few dozen MB is bound by its fixed latencies rather than by bandwidth, so two of them
+ * on disjoint halves of the device finish sooner than one after the other (a GEMM launched on every SM leaves no
+ * room for anything beside it).  The number of CTAs decides how a weight tile's K range is cut and therefore the
+ * order of the fp32 additions: results are reproducible for a given setting, not across settings. */
+int wuda_gemm_sm_limit(int max_sms);
 int64_t wuda_gemm_fp8_scratch_bytes(int m, int n);
 int wuda_gemm_fp8_blockscaled(const void* a, const float* a_scales, const void* w, const float* w_scales,
                               void* c_bf16, int m, int n, int k, void* scratch, int64_t scratch_bytes,

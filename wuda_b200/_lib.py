@@ -166,6 +166,7 @@ SIGNATURES = {
     "wuda_mhc_post": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
     "wuda_gemm_fp8_scratch_bytes": (c_i64, [c_int, c_int]),
     "wuda_gemm_fp8_blockscaled": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
+    "wuda_gemm_sm_limit": (c_int, [c_int]),
     "wuda_gemm_fp8_blockscaled_noalloc": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp]),
     "wuda_tp2_inbox_bytes": (c_i64, [c_int, c_int]),
     "wuda_tp2_alloc": (c_int, [c_i64, ctypes.POINTER(c_vp), c_vp]),

@@ -359,7 +359,8 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p,
     // the other, which costs more than it saves when a few tiles are cut into a hundred pieces
     // (adding one partial costs the owner about as much as streaming M_PAD / 64 units, so wide tiles split less)
     constexpr int kMaxSplit = M_PAD <= 16 ? 16 : (M_PAD == 32 ? 12 : (M_PAD == 64 ? 8 : 6));
-    int grid = units < dev.num_sms ? static_cast<int>(units) : dev.num_sms;
+    const int sms = gemm_sms(dev);
+    int grid = units < sms ? static_cast<int>(units) : sms;
     if (static_cast<long long>(p.n_tiles) * kMaxSplit < grid) grid = p.n_tiles * kMaxSplit;
     WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(threads_for(M_PAD)), L::total(stages), stream, w_map, a_map, p));
     return WUDA_OK;

@@ -428,7 +428,8 @@ static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, const CUte
     // CTAs that may share one weight tile: the owner adds their partials serially, which costs about as much
     // per partial as streaming M_PAD / 64 units
     constexpr int kMaxSplit = M_PAD <= 16 ? 16 : (M_PAD == 32 ? 12 : (M_PAD == 64 ? 8 : 6));
-    int grid = (!p.group_expert && units < dev.num_sms) ? static_cast<int>(units) : dev.num_sms;
+    const int sms = gemm_sms(dev);
+    int grid = (!p.group_expert && units < sms) ? static_cast<int>(units) : sms;
     if (!p.group_expert && static_cast<long long>(p.n_tiles) * kMaxSplit < grid) grid = p.n_tiles * kMaxSplit;
     WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(threads_for(M_PAD)), L::total(stages), stream, w_map, a_map, wsf_map, asf_map, p));
     return WUDA_OK;

@@ -17,6 +17,11 @@ int fail(int status, const char* fmt, ...) {
 }
 void clear_error() { g_error[0] = '\0'; }
 
+static thread_local int g_gemm_sm_limit = 0;
+int gemm_sms(const DeviceInfo& dev) {
+    return g_gemm_sm_limit > 0 && g_gemm_sm_limit < dev.num_sms ? g_gemm_sm_limit : dev.num_sms;
+}
+
 int current_device_info(DeviceInfo* out) {
     static std::mutex mu;
     static DeviceInfo cache[64];
@@ -101,3 +106,9 @@ int wuda_num_sms(void) {
 }
 
 }  // extern "C"
+
+extern "C" int wuda_gemm_sm_limit(int max_sms) {
+    const int before = wuda::g_gemm_sm_limit;
+    wuda::g_gemm_sm_limit = max_sms > 0 ? max_sms : 0;
+    return before;
+}

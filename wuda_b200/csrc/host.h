@@ -37,6 +37,8 @@ struct DeviceInfo {
     int cc_major = 0;
 };
 int current_device_info(DeviceInfo* out);
+// SMs the GEMM launches of the calling thread may cover: all of the device's, or fewer after wuda_gemm_sm_limit
+int gemm_sms(const DeviceInfo& dev);
 
 // rank-`rank` tiled tensor map. dims/box are innermost-first; strides_bytes has rank-1
 // entries (stride of dims 1..rank-1). Returns a wuda_status.

@@ -16,7 +16,8 @@
 //       partial rows over peer memory), mHC post
 //
 // Host code only: every stage is one of the library's own entry points, called in order on the caller's
-// stream; nothing is allocated and nothing synchronises, so the call can be captured into a CUDA graph.
+// stream (two stretches of independent work on a side stream forked from it and joined back, see Side below);
+// nothing is allocated and nothing synchronises, so the call can be captured into a CUDA graph.
 // All intermediate tensors live in one caller-provided workspace that this file lays out.
 #include <cuda_runtime.h>
 
@@ -84,12 +85,46 @@ struct Buffers {
     float* row_weight;
     uint8_t *a1, *a1_sf, *a2, *a2_sf;
     uint16_t *h, *r_out, *y_moe;
-    uint8_t *gemm_scratch, *nvfp4_scratch;
+    uint8_t *gemm_scratch, *side_scratch, *nvfp4_scratch;
     int64_t gemm_scratch_bytes, nvfp4_scratch_bytes;
     int max_groups;
 };
 
 int64_t max64(int64_t a, int64_t b) { return a > b ? a : b; }
+
+// Two places of the layer hold independent work whose GEMMs are bound by their fixed latencies (15-40 MB of
+// weights each): the FP8 and the BF16 segment of the front projection, and the shared expert beside router
+// projection / routing / dispatch / gather.  Each pair runs side by side - one part on a side stream forked from
+// the caller's and joined back (under stream capture: parallel branches of the graph) - with the GEMMs kept to
+// disjoint shares of the SMs (wuda_gemm_sm_limit); a GEMM launched on every SM would leave no room beside it.
+// Stream and events are created once per device and never destroyed.
+struct Side {
+    bool ready = false;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork[2] = {nullptr, nullptr}, done[2] = {nullptr, nullptr};
+};
+
+int side_of_current_device(Side** out) {
+    static Side sides[16];
+    int dev = 0;
+    WUDA_CUDA(cudaGetDevice(&dev));
+    WUDA_REQUIRE(dev >= 0 && dev < 16, "device ordinal %d is outside the 16 this library keeps state for", dev);
+    Side& s = sides[dev];
+    if (!s.ready) {
+        WUDA_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+        for (cudaEvent_t* e : {&s.fork[0], &s.fork[1], &s.done[0], &s.done[1]})
+            WUDA_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+        s.ready = true;
+    }
+    *out = &s;
+    return WUDA_OK;
+}
+
+// SM shares (of the device's n): FP8 front segment 5/16 (its weights are 14.7 MB against the BF16 segment's
+// 37.6 MB), BF16 segment the rest; the shared expert all but 32, which the router's small kernels keep.
+int front8_sms(int n) { return n * 5 / 16 > 8 ? n * 5 / 16 : n; }
+int front16_sms(int n) { return n * 5 / 16 > 8 ? n - n * 5 / 16 : n; }
+int shared_sms(int n) { return n > 64 ? n - 32 : n; }
 
 // Lays the buffers out for up to m rows; returns the bytes used, or -1 for a geometry an entry point refuses.
 int64_t carve(const wuda_layer_weights* w, int m, int topk, int64_t logits_stride, int window, void* base, Buffers* b) {
@@ -163,6 +198,7 @@ int64_t carve(const wuda_layer_weights* w, int m, int topk, int64_t logits_strid
     if (need < 0) return -1;
     b->gemm_scratch_bytes = need;
     b->gemm_scratch = c.take<uint8_t>(need);
+    b->side_scratch = c.take<uint8_t>(need);   // for the GEMMs that run beside others on the side stream
     b->nvfp4_scratch_bytes = wuda_gemm_nvfp4_scratch_bytes(16, 128);
     b->nvfp4_scratch = c.take<uint8_t>(b->nvfp4_scratch_bytes);
     return c.used;
@@ -211,10 +247,25 @@ extern "C" int wuda_layer_decode(const wuda_layer_weights* w, const wuda_layer_s
     WUDA_STAGE(wuda_mhc_pre(t->hidden_in, w->attn_hc_weight, w->attn_hc_base, w->attn_hc_scale, w->attn_norm, w->hc_eps, w->rms_eps,
                             w->norm_eps, b.a_pre, b.a_post, b.a_comb, nullptr, b.a_normed, b.a_xq, b.a_xsf, b.pre_ws,
                             wuda_mhc_pre_workspace_bytes(s->m_max, hidden), m, hidden, stream));
-    WUDA_STAGE(wuda_gemm_fp8_blockscaled(b.a_xq, b.a_xsf, w->front_w8, w->front_w8_scales, b.front_out, m, kFront8, hidden,
-                                         b.gemm_scratch, b.gemm_scratch_bytes, status, stream));
-    WUDA_STAGE(wuda_gemm_bf16(b.a_normed, w->front_w16, b.y16, 1, m, kFront16, hidden, b.gemm_scratch, b.gemm_scratch_bytes, status,
-                              stream));
+    Side* side = nullptr;
+    WUDA_STAGE(side_of_current_device(&side));
+    cudaStream_t main_stream = static_cast<cudaStream_t>(stream);
+    const int sms = wuda_num_sms();
+    {   // the two segments of the front projection side by side; the fork is joined on every path
+        WUDA_CUDA(cudaEventRecord(side->fork[0], main_stream));
+        WUDA_CUDA(cudaStreamWaitEvent(side->stream, side->fork[0], 0));
+        wuda_gemm_sm_limit(front16_sms(sms));
+        int st = wuda_gemm_bf16(b.a_normed, w->front_w16, b.y16, 1, m, kFront16, hidden, b.side_scratch, b.gemm_scratch_bytes, status,
+                                side->stream);
+        WUDA_CUDA(cudaEventRecord(side->done[0], side->stream));
+        wuda_gemm_sm_limit(front8_sms(sms));
+        if (st == WUDA_OK)
+            st = wuda_gemm_fp8_blockscaled(b.a_xq, b.a_xsf, w->front_w8, w->front_w8_scales, b.front_out, m, kFront8, hidden,
+                                           b.gemm_scratch, b.gemm_scratch_bytes, status, stream);
+        wuda_gemm_sm_limit(0);
+        WUDA_CUDA(cudaStreamWaitEvent(main_stream, side->done[0], 0));
+        if (st != WUDA_OK) return st;
+    }
     WUDA_STAGE(wuda_front_emit(b.front_out, b.y16, t->pos, c.main_state, w->ape, t->main_state_row, c.idx_state, w->idx_ape,
                                t->idx_state_row, b.win_y2, b.w64, c.state_rows_total, m, status, stream));
     wuda_csa_step step = {};
@@ -286,24 +337,42 @@ extern "C" int wuda_layer_decode(const wuda_layer_weights* w, const wuda_layer_s
     WUDA_STAGE(wuda_mhc_pre(b.attn_out, w->ffn_hc_weight, w->ffn_hc_base, w->ffn_hc_scale, w->ffn_norm, w->hc_eps, w->rms_eps,
                             w->norm_eps, b.f_pre, b.f_post, b.f_comb, nullptr, b.f_normed, nullptr, nullptr, b.pre_ws,
                             wuda_mhc_pre_workspace_bytes(s->m_max, hidden), m, hidden, stream));
-    WUDA_STAGE(wuda_gemm_bf16(b.f_normed, w->gate_weight, b.gate_logits, 1, m, w->experts_total, hidden, b.gemm_scratch,
-                              b.gemm_scratch_bytes, status, stream));
-    WUDA_STAGE(wuda_moe_route(b.gate_logits, w->gate_bias, b.route_w, b.route_idx, m, w->experts_total, w->moe_topk, w->score_func,
-                              w->route_scale, stream));
+    // the shared expert on the side stream, beside router projection, routing, dispatch and gather
     const void* shared_rows = nullptr;
     if (w->shared_w13) {
         const int si = w->shared_inter;
-        WUDA_STAGE(wuda_rmsnorm_quant_fp8(b.f_normed, hidden, nullptr, 0, 0.0f, nullptr, b.s_x8, b.s_xs, m, hidden, 1, stream));
-        WUDA_STAGE(wuda_gemm_fp8_blockscaled(b.s_x8, b.s_xs, w->shared_w13, w->shared_w13_scales, b.s_h, m, 2 * si, hidden,
-                                             b.gemm_scratch, b.gemm_scratch_bytes, status, stream));
-        WUDA_STAGE(wuda_swiglu_quant_fp8(b.s_h, nullptr, b.s_a8, b.s_as, m, si, w->swiglu_limit, 1, stream));
-        WUDA_STAGE(wuda_gemm_fp8_blockscaled(b.s_a8, b.s_as, w->shared_w2, w->shared_w2_scales, b.s_out, m, hidden, si, b.gemm_scratch,
-                                             b.gemm_scratch_bytes, status, stream));
+        WUDA_CUDA(cudaEventRecord(side->fork[1], main_stream));
+        WUDA_CUDA(cudaStreamWaitEvent(side->stream, side->fork[1], 0));
+        wuda_gemm_sm_limit(shared_sms(sms));
+        int st = wuda_rmsnorm_quant_fp8(b.f_normed, hidden, nullptr, 0, 0.0f, nullptr, b.s_x8, b.s_xs, m, hidden, 1, side->stream);
+        if (st == WUDA_OK)
+            st = wuda_gemm_fp8_blockscaled(b.s_x8, b.s_xs, w->shared_w13, w->shared_w13_scales, b.s_h, m, 2 * si, hidden,
+                                           b.side_scratch, b.gemm_scratch_bytes, status, side->stream);
+        if (st == WUDA_OK) st = wuda_swiglu_quant_fp8(b.s_h, nullptr, b.s_a8, b.s_as, m, si, w->swiglu_limit, 1, side->stream);
+        if (st == WUDA_OK)
+            st = wuda_gemm_fp8_blockscaled(b.s_a8, b.s_as, w->shared_w2, w->shared_w2_scales, b.s_out, m, hidden, si, b.side_scratch,
+                                           b.gemm_scratch_bytes, status, side->stream);
+        wuda_gemm_sm_limit(0);
+        WUDA_CUDA(cudaEventRecord(side->done[1], side->stream));
+        if (st != WUDA_OK) {
+            WUDA_CUDA(cudaStreamWaitEvent(main_stream, side->done[1], 0));
+            return st;
+        }
         shared_rows = b.s_out;
     }
-    WUDA_STAGE(wuda_moe_dispatch_range(b.route_idx, b.route_w, b.group_expert, b.num_groups, b.row_token, b.row_weight, b.pair_row, m,
-                                       w->moe_topk, w->experts_local, w->expert_first, w->experts_total, b.max_groups, status, stream));
-    WUDA_STAGE(wuda_moe_gather_quant_nvfp4(b.f_normed, b.pair_row, b.a1, b.a1_sf, w->act_scale_in, m, w->moe_topk, hidden, stream));
+    int routed = wuda_gemm_bf16(b.f_normed, w->gate_weight, b.gate_logits, 1, m, w->experts_total, hidden, b.gemm_scratch,
+                                b.gemm_scratch_bytes, status, stream);
+    if (routed == WUDA_OK)
+        routed = wuda_moe_route(b.gate_logits, w->gate_bias, b.route_w, b.route_idx, m, w->experts_total, w->moe_topk, w->score_func,
+                                w->route_scale, stream);
+    if (routed == WUDA_OK)
+        routed = wuda_moe_dispatch_range(b.route_idx, b.route_w, b.group_expert, b.num_groups, b.row_token, b.row_weight, b.pair_row, m,
+                                         w->moe_topk, w->experts_local, w->expert_first, w->experts_total, b.max_groups, status,
+                                         stream);
+    if (routed == WUDA_OK)
+        routed = wuda_moe_gather_quant_nvfp4(b.f_normed, b.pair_row, b.a1, b.a1_sf, w->act_scale_in, m, w->moe_topk, hidden, stream);
+    if (w->shared_w13) WUDA_CUDA(cudaStreamWaitEvent(main_stream, side->done[1], 0));   // join
+    if (routed != WUDA_OK) return routed;
     WUDA_STAGE(wuda_gemm_nvfp4_grouped(b.a1, b.a1_sf, w->act_scale_in, w->w13, w->w13_sf, w->w13_gs, b.group_expert, b.num_groups, b.row_token, b.h,
                                        b.max_groups, w->experts_local, 2 * w->inter, hidden, b.nvfp4_scratch, b.nvfp4_scratch_bytes,
                                        status, stream));

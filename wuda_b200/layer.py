@@ -56,6 +56,7 @@ class AttentionHalfLayer:
     def __init__(self, csa_weights, weights, cache, max_batch, topk=2048, softmax_scale=512 ** -0.5, tp_link=None):
         """tp_link (ops.TP2Link): this rank holds half of the heads - csa_weights projects only its main
         heads, weights.o_proj holds its wo_a groups and its K slice of wo_b - and wo_b sums over the pair."""
+        self.sm_split = None      # (FP8, BF16) SM shares of the front projection, set by a DecoderLayer that mirrors the C++ call
         self.w, self.cache, self.max_batch, self.topk = weights, cache, max_batch, topk
         self.softmax_scale, self.tp_link = softmax_scale, tp_link
         self.stage = CsaDecodeStage(csa_weights, cache, max_batch, topk=topk)
@@ -94,7 +95,7 @@ class AttentionHalfLayer:
                              self.front_out[:m], pos=st.pos[:m], main_state=cache.main_state, ape=w.ape,
                              main_state_row=st.main_state_row[:m], idx_state=cache.idx_state,
                              idx_state_row=st.idx_state_row[:m], idx_ape=w.idx_ape, win_y2=st.win_y2[:m], w64=st.w64[:m],
-                             y16=self.y16[:m], status_word=self.status)
+                             y16=self.y16[:m], status_word=self.status, sm_split=self.sm_split)
         st.launch(m)
         ops.sparse_mla_decode(st.q_main[:m], cache.model1_cache_view("swa"), self.swa_idx[:m], self.swa_len[:m],
                               cache.model1_cache_view("cmp"), st.topk_indices[:m], self.cmp_len[:m], w.attn_sink,
@@ -166,6 +167,12 @@ class DecoderLayer:
             self.pre_ws = torch.empty(lib.wuda_mhc_pre_workspace_bytes(max_batch, hidden), dtype=torch.uint8, device=dev)
             self.gate_logits = torch.empty(max_batch, ffn.experts_total, dtype=torch.float32, device=dev)
             self.y = torch.empty(max_batch, hidden, dtype=torch.bfloat16, device=dev)
+            # the SM shares the C++ sequence gives the GEMMs it runs side by side (wuda_b200/csrc/layer_decode.cu): with
+            # them this Python-sequenced form adds in the same order and is bit-identical to it
+            n = lib.wuda_num_sms()
+            first = n * 5 // 16
+            attention.sm_split = (first, n - first) if first > 8 else (n, n)
+            self._shared_sms = n - 32 if n > 64 else n
 
     # ---- the C++ launch sequence
     def _init_native(self, dev):
@@ -254,7 +261,13 @@ class DecoderLayer:
         rw, idx = ops.moe_gate(normed, f.gate_weight, f.gate_bias, f.score_func, f.route_scale, f.topk,
                                logits=self.gate_logits[:m])
         self.route_indices = idx
-        shared = f.shared.forward(normed) if f.shared is not None else None
+        shared = None
+        if f.shared is not None:   # on the SM share wuda_layer_decode gives the shared expert beside the router
+            lib.wuda_gemm_sm_limit(self._shared_sms)
+            try:
+                shared = f.shared.forward(normed)
+            finally:
+                lib.wuda_gemm_sm_limit(0)
         y = self.runner.forward(normed, rw, idx, shared=shared, y=self.y[:m])
         return ops.mhc_post_out(y, x, pre["post"], pre["comb"], self.out[:m])
 

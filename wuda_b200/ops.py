@@ -617,22 +617,32 @@ def bf16_gemm(a, w, *, out=None, out_dtype=torch.bfloat16, status_word=None):
 
 def front_mixed_gemm(x, x_fp8, x_sf, w_bf16, w_fp8, w_sf, out, *, pos=None, main_state=None, ape=None,
                      main_state_row=None, idx_state=None, idx_state_row=None, idx_ape=None, win_y2=None, w64=None,
-                     y16=None, status_word=None):
+                     y16=None, status_word=None, sm_split=None):
     """The front projection of a decode step with its side-channel outputs, after the reference's
     front_mixed_gemm_csa_swapab (kernels/front_mixed_gemm_csa_swapab.cu:262-279):
     y[M, 4672] = x . [W8 (2048 rows, FP8 1x128 / 128x128 scales) | W16 (2624 rows, BF16)]^T.
     `out` bf16 [M, 2048] receives the FP8 segment (q_raw | win); the BF16 segment is produced in fp32
     (`y16` [M, 2624], allocated if not given) and scattered into the state rings, win_y2 and w64 when
-    those are passed (all-or-none with pos).  Three launches: two GEMMs and the scatter."""
+    those are passed (all-or-none with pos).  Three launches: two GEMMs and the scatter.  sm_split = (SMs of the
+    FP8 GEMM, SMs of the BF16 GEMM) launches them with the shares wuda_layer_decode gives them when it runs the two
+    side by side, which makes the sums bit-identical to that call's."""
     m = x.size(0)
     _require(tuple(w_fp8.shape) == (2048, x.size(1)) and tuple(w_bf16.shape) == (2624, x.size(1)),
              "w_fp8 must be [2048, K] and w_bf16 [2624, K]")
     _require(out.is_cuda and out.is_contiguous() and out.dtype == torch.bfloat16 and tuple(out.shape) == (m, 2048),
              "out must be contiguous CUDA bf16 [M, 2048]")
-    fp8_gemm(x_fp8, x_sf, w_fp8, w_sf, out=out, status_word=status_word)
     if y16 is None:
         y16 = torch.empty(m, 2624, dtype=torch.float32, device=x.device)
-    bf16_gemm(x, w_bf16, out=y16, status_word=status_word)
+    try:
+        if sm_split is not None:
+            lib.wuda_gemm_sm_limit(int(sm_split[0]))
+        fp8_gemm(x_fp8, x_sf, w_fp8, w_sf, out=out, status_word=status_word)
+        if sm_split is not None:
+            lib.wuda_gemm_sm_limit(int(sm_split[1]))
+        bf16_gemm(x, w_bf16, out=y16, status_word=status_word)
+    finally:
+        if sm_split is not None:
+            lib.wuda_gemm_sm_limit(0)
     if pos is not None:
         _require(pos.is_cuda and pos.is_contiguous() and pos.dtype == torch.int64 and pos.numel() == m,
                  "pos must be contiguous CUDA int64 [M]")
