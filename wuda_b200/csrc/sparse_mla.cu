@@ -166,9 +166,10 @@ __device__ __forceinline__ int fetch_index(const Params& p, int b, int g, int n_
     if (g >= n_total) return -1;
     const bool window = g < n_swa;
     const Pool& pool = window ? p.swa : p.cmp;
-    // coherent loads here and for the records: the top-k entries, this step's cache records and the query come from
-    // kernels of the same chain, which may still be running when this kernel is launched
-    return __ldcg(pool.indices + static_cast<int64_t>(b) * pool.capacity + (window ? g : g - n_swa));
+    // (read-only loads are sound here although the top-k entries, this step's cache records and the query come from
+    // kernels of the same chain: this kernel is launched without the programmatic-launch attribute, i.e. only
+    // after those kernels have finished)
+    return __ldg(pool.indices + static_cast<int64_t>(b) * pool.capacity + (window ? g : g - n_swa));
 }
 
 __device__ __forceinline__ void fetch_key(const Params& p, int g, int n_swa, int idx, int piece, KeyRegs& r, bool* bad) {
@@ -183,9 +184,9 @@ __device__ __forceinline__ void fetch_key(const Params& p, int g, int n_swa, int
     const uint8_t* base = pool.data + static_cast<int64_t>(page) * pool.stride;
     const uint8_t* rec = base + static_cast<int64_t>(off) * kBody;
 #pragma unroll
-    for (int c = 0; c < 7; ++c) r.nope[c] = __ldcg(reinterpret_cast<const uint2*>(rec + c * 64) + piece);
-    r.rope = __ldcg(reinterpret_cast<const uint4*>(rec + kNope) + piece);
-    r.scales = __ldcg(reinterpret_cast<const uint2*>(base + static_cast<int64_t>(pool.epb) * kBody + off * kScaleRec));
+    for (int c = 0; c < 7; ++c) r.nope[c] = __ldg(reinterpret_cast<const uint2*>(rec + c * 64) + piece);
+    r.rope = __ldg(reinterpret_cast<const uint4*>(rec + kNope) + piece);
+    r.scales = __ldg(reinterpret_cast<const uint2*>(base + static_cast<int64_t>(pool.epb) * kBody + off * kScaleRec));
     r.valid = 1;
 }
 
@@ -250,11 +251,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         tmem_alloc(smem_u32(tmem_slot), kTmemCols);
         tmem_relinquish();
     }
-    pdl_launch_dependents();
-    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
+    pdl_launch_dependents();   // the kernel behind this one may set itself up early; this one was launched in order
 
-    const int n_swa = p.swa.capacity > 0 ? min(max(__ldcg(p.swa.lengths + b), 0), p.swa.capacity) : 0;
-    const int n_cmp = p.cmp.capacity > 0 ? min(max(__ldcg(p.cmp.lengths + b), 0), p.cmp.capacity) : 0;
+    const int n_swa = p.swa.capacity > 0 ? min(max(__ldg(p.swa.lengths + b), 0), p.swa.capacity) : 0;
+    const int n_cmp = p.cmp.capacity > 0 ? min(max(__ldg(p.cmp.lengths + b), 0), p.cmp.capacity) : 0;
     const int n_total = n_swa + n_cmp;
     // the CTAs of a request that share an output half each take a contiguous run of its key blocks
     const int all_blocks = (n_total + kBlock - 1) / kBlock;
@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         const int row = i / kQSmemPieces, piece = i % kQSmemPieces;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < p.heads)
-            v = __ldcg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim +
+            v = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(b) * p.heads + row) * kDim +
                                                      kQTmemChunks * 64) + piece);
         st_shared_v4(base + kOffQ + (piece >> 3) * kQChunk + row * 128 + (((piece & 7) ^ (row & 7)) << 4), bf16x8_to_f16x8(v));
     }
@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
             uint32_t w[32];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const uint4 v = bf16x8_to_f16x8(row < p.heads ? __ldcg(src + c * 8 + i) : make_uint4(0, 0, 0, 0));
+                const uint4 v = bf16x8_to_f16x8(row < p.heads ? __ldg(src + c * 8 + i) : make_uint4(0, 0, 0, 0));
                 w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
             }
             tmem_st_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + kColQ + c * 32, w);
@@ -424,19 +424,32 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s_empty);
             }
+            // A block whose 64 keys all exist (every block but a request's last) needs no masks: the maximum is taken
+            // over the raw scores and the scale rides in the exponent's multiply-add.  Otherwise missing keys become
+            // -inf and the scores are scaled in place.
+            const bool all_valid = (vw[0] & vw[1] & vw[2] & vw[3]) == 0x0f0f0f0fu;   // the same word for every thread
+            float sc = p.scale_log2;
+            if (all_valid) {
 #pragma unroll
-            for (int h2 = 0; h2 < kBlock / 32; ++h2) {
-                const uint2 vb = make_uint2(vw[2 * h2], vw[2 * h2 + 1]);
-                uint32_t mask = 0;
+                for (int i = 0; i < kBlock; ++i) bm[i & 3] = fmaxf(bm[i & 3], x[i]);
 #pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    mask |= ((vb.x >> (8 * w)) & 0xfu) << (4 * w);
-                    mask |= ((vb.y >> (8 * w)) & 0xfu) << (16 + 4 * w);
-                }
+                for (int c = 0; c < 4; ++c) bm[c] *= p.scale_log2;
+            } else {
+                sc = 1.0f;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    x[h2 * 32 + i] = (mask >> i) & 1u ? x[h2 * 32 + i] * p.scale_log2 : -INFINITY;
-                    bm[i & 3] = fmaxf(bm[i & 3], x[h2 * 32 + i]);
+                for (int h2 = 0; h2 < kBlock / 32; ++h2) {
+                    const uint2 vb = make_uint2(vw[2 * h2], vw[2 * h2 + 1]);
+                    uint32_t mask = 0;
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        mask |= ((vb.x >> (8 * w)) & 0xfu) << (4 * w);
+                        mask |= ((vb.y >> (8 * w)) & 0xfu) << (16 + 4 * w);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        x[h2 * 32 + i] = (mask >> i) & 1u ? x[h2 * 32 + i] * p.scale_log2 : -INFINITY;
+                        bm[i & 3] = fmaxf(bm[i & 3], x[h2 * 32 + i]);
+                    }
                 }
             }
             const float bmax = fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3]));
@@ -470,7 +483,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
             uint32_t pk[kBlock / 2];
 #pragma unroll
             for (int i = 0; i < kBlock; i += 2) {
-                const float e0 = ex2(x[i] - m_use), e1 = ex2(x[i + 1] - m_use);
+                const float e0 = ex2(fmaf(x[i], sc, -m_use)), e1 = ex2(fmaf(x[i + 1], sc, -m_use));
                 sm[(i >> 1) & 3] += e0 + e1;
                 const __half2 h = __floats2half2_rn(e0, e1);
                 pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
@@ -679,8 +692,12 @@ extern "C" int wuda_sparse_mla_decode(const wuda_sparse_mla_args* a, int32_t* st
         p.part_o = p.part_ml = nullptr;
     }
     WUDA_CUDA(cudaFuncSetAttribute(sparse_mla_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    WUDA_CUDA(launch_pdl(sparse_mla_kernel, dim3(2, a->batch, splits), dim3(kThreads), kSmemBytes,
-                         static_cast<cudaStream_t>(stream), p));
+    // An ordinary launch, not a programmatic one: the kernel gathers its records through the read-only path, which
+    // is only sound for data that nobody writes while the kernel is resident - and the cache writers and the query
+    // tail of the same step could still be running under an early launch.  (Coherent loads instead cost 10 % of
+    // the kernel's time; the early launch it gives up is worth 2-3 us.)
+    sparse_mla_kernel<<<dim3(2, a->batch, splits), dim3(kThreads), kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
+    WUDA_CUDA(cudaGetLastError());
     if (splits > 1)
         WUDA_CUDA(launch_pdl(sparse_mla_combine_kernel, dim3(a->heads, a->batch), dim3(128), 0,
                              static_cast<cudaStream_t>(stream), p, splits));
