@@ -96,6 +96,31 @@ def test_threshold_inside_a_crowded_bin(wuda, crowd, step):
     check(wuda, scores, np.asarray(lens, np.int32), page_table, k)
 
 
+@pytest.mark.parametrize("shape", ["log_uniform", "across_zero", "tiny_and_huge"])
+def test_kth_value_binades_above_the_sampled_bound(wuda, shape):
+    """Keys are sparse near zero: when the scores around the k-th value are spread over many binades, or the k-th
+    value is a small positive number with negative scores right below it, the candidate bound found from the
+    samples lies far from the k-th value in key space.  The selection among the candidates must not depend on
+    that distance."""
+    rng = np.random.default_rng(len(shape))
+    rows, length, k = 5, 8192, 2048
+    scores = np.empty((rows, length), np.float32)
+    for r in range(rows):
+        big = rng.uniform(100.0, 1000.0, size=2000)
+        if shape == "log_uniform":
+            rest = 10.0 ** rng.uniform(-6.0, 0.0, size=length - 2000) * rng.choice([-1.0, 1.0], size=length - 2000)
+        elif shape == "across_zero":
+            rest = rng.normal(-2.0, 1.0, size=length - 2000)
+        else:
+            rest = np.where(rng.random(length - 2000) < 0.02, rng.uniform(1e-30, 1e-20, size=length - 2000),
+                            -rng.uniform(1e-3, 1e3, size=length - 2000))
+        row = np.concatenate([big, rest]).astype(np.float32)
+        scores[r] = row[rng.permutation(length)]
+    pages = length // PAGE
+    page_table = rng.integers(0, 1 << 20, size=(rows, pages), dtype=np.int32)
+    check(wuda, scores, np.full(rows, length, np.int32), page_table, k)
+
+
 def test_crowded_rows_cost_about_what_spread_rows_cost(wuda):
     """A selection whose cost grew with the square of the threshold bin's size would take twenty times longer on
     crowded rows than on normal ones; the bound here is loose (a factor of 4) and relative, so it holds at any clock."""
@@ -126,8 +151,11 @@ def test_crowded_rows_cost_about_what_spread_rows_cost(wuda):
             best = min(best, e0.elapsed_time(e1))
         return best
 
-    t_spread, t_crowded = device_time(spread), device_time(crowded)
+    far = (10.0 ** rng.uniform(-6.0, 0.0, size=(rows, length)) * rng.choice([-1.0, 1.0], size=(rows, length))).astype(np.float32)
+    far[:, :2000] = rng.uniform(100.0, 1000.0, size=(rows, 2000)).astype(np.float32)   # the bound falls binades below the k-th value
+    t_spread, t_crowded, t_far = device_time(spread), device_time(crowded), device_time(far)
     assert t_crowded < 4.0 * t_spread, (t_crowded, t_spread)
+    assert t_far < 2.5 * t_spread, (t_far, t_spread)
 
 
 def test_special_values(wuda):

@@ -484,13 +484,48 @@ __global__ void __launch_bounds__(kThreads, 2) topk_kernel(const Params p) {
                     }
                     __syncthreads();
                     find_threshold(s, kBins, static_cast<uint32_t>(k));
-                    const uint32_t bin_a = s.sel_digit;
-                    const uint32_t above_a = s.sel_above;
+                    // A candidate's class is (key - sub) >> shift compared with thr: the window's bin, or - when the
+                    // threshold lies beyond the window - the key's upper 24 bits.
+                    uint32_t sub = key_lo, shift = 12;
+                    uint32_t bin_a = s.sel_digit;
+                    uint32_t above_a = s.sel_above;
+                    uint32_t c_a = s.sel_count;
+                    if (bin_a == static_cast<uint32_t>(kBins - 1)) {
+                        // The window (2^24 keys above the bound: two binades of one sign) does not reach the k-th value:
+                        // the sample's bound lies several binades below it, or on the other side of zero, where keys
+                        // are sparse.  Two exact levels over the candidates instead of the whole row: the key's upper 12
+                        // bits (counted from the bound's), then the next 12 inside that digit.
+                        const uint32_t d_lo = key_lo >> 20;
+                        __syncthreads();
+                        zero_hist(s, kBins);
+                        __syncthreads();
+                        for (int g = warp; g < nseg; g += kWarps) {
+                            const uint32_t c = s.seg_cnt[g];
+                            const uint2* cands = s.cand + g * segcap;
+                            for (uint32_t j = lane; j < c; j += 32) atomicAdd(&s.hist[hslot((cands[j].x >> 20) - d_lo)], 1u);
+                        }
+                        __syncthreads();
+                        find_threshold(s, kBins, static_cast<uint32_t>(k));
+                        const uint32_t digit = d_lo + s.sel_digit, above_1 = s.sel_above;
+                        __syncthreads();
+                        zero_hist(s, kBins);
+                        __syncthreads();
+                        for (int g = warp; g < nseg; g += kWarps) {
+                            const uint32_t c = s.seg_cnt[g];
+                            const uint2* cands = s.cand + g * segcap;
+                            for (uint32_t j = lane; j < c; j += 32)
+                                if ((cands[j].x >> 20) == digit) atomicAdd(&s.hist[hslot((cands[j].x >> 8) & 0xFFFu)], 1u);
+                        }
+                        __syncthreads();
+                        find_threshold(s, kBins, static_cast<uint32_t>(k) - above_1);
+                        sub = 0, shift = 8;
+                        bin_a = (digit << 12) | s.sel_digit;
+                        above_a = above_1 + s.sel_above;
+                        c_a = s.sel_count;
+                    }
                     const uint32_t need_a = static_cast<uint32_t>(k) - above_a;
-                    const uint32_t c_a = s.sel_count;
-                    // keys beyond the window share the last bin, and a bin with thousands of members is a row of
-                    // duplicates: both go to the exact path
-                    ok = bin_a != static_cast<uint32_t>(kBins - 1) && c_a <= static_cast<uint32_t>(kTieCap);
+                    // a class with thousands of members is a row of duplicates: the exact path
+                    ok = c_a <= static_cast<uint32_t>(kTieCap);
                     if (ok) {
                         // One walk over the candidates: those above the threshold bin are counted per segment,
                         // the bin's own members go to the tie list.
@@ -501,7 +536,7 @@ __global__ void __launch_bounds__(kThreads, 2) topk_kernel(const Params p) {
                                 const uint32_t j = j0 + lane;
                                 const uint2 cand = j < c ? s.cand[g * segcap + j] : make_uint2(key_lo, 0u);
                                 const uint32_t key = cand.x;
-                                const uint32_t bin = (key - key_lo) >> 12;
+                                const uint32_t bin = (key - sub) >> shift;
                                 sel += __popc(__ballot_sync(0xffffffffu, j < c && bin > bin_a));
                                 const bool in = j < c && bin == bin_a;
                                 const uint32_t b = __ballot_sync(0xffffffffu, in);
@@ -555,7 +590,7 @@ __global__ void __launch_bounds__(kThreads, 2) topk_kernel(const Params p) {
                             for (uint32_t j0 = 0; j0 < c; j0 += 32) {
                                 const uint32_t j = j0 + lane;
                                 const uint2 cand = j < c ? s.cand[g * segcap + j] : make_uint2(key_lo, 0u);
-                                const bool in = j < c && ((cand.x - key_lo) >> 12) > bin_a;
+                                const bool in = j < c && ((cand.x - sub) >> shift) > bin_a;
                                 const uint32_t b = __ballot_sync(0xffffffffu, in);
                                 if (in) put_cached(p, s, r, at + __popc(b & lane_lt), static_cast<int>(cand.y));
                                 at += __popc(b);
