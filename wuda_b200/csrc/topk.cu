@@ -370,7 +370,12 @@ __global__ void __launch_bounds__(kThreads, 2) topk_kernel(const Params p) {
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
         bool done = false;
 
-        if (n >= 4 * k && 2 * k <= kCandCap) {
+        // expected sample rank of the k-th value, plus a 5-sigma margin, and the candidates that bound would let through
+        const float expect = static_cast<float>(kSamples) * static_cast<float>(k) / static_cast<float>(n);
+        uint32_t rank = static_cast<uint32_t>(expect + 5.f * sqrtf(expect) + 8.f);
+        if (rank > static_cast<uint32_t>(kSamples)) rank = kSamples;
+        const float expected_candidates = static_cast<float>(rank) * static_cast<float>(n) / static_cast<float>(kSamples);
+        if (2 * k <= kCandCap && expected_candidates <= 0.75f * kCandCap) {
             // ---------------------------------------------------------------- fast path
             if (!clean) {
                 zero_hist(s, kBins);
@@ -402,10 +407,6 @@ __global__ void __launch_bounds__(kThreads, 2) topk_kernel(const Params p) {
 #pragma unroll
             for (int j = 0; j < kSamples / kThreads; ++j) atomicAdd(&s.hist[hslot(key_of(v[j]) >> 20)], 1u);
             __syncthreads();
-            // expected sample rank of the k-th value, plus a 5-sigma margin
-            const float expect = static_cast<float>(kSamples) * static_cast<float>(k) / static_cast<float>(n);
-            uint32_t rank = static_cast<uint32_t>(expect + 5.f * sqrtf(expect) + 8.f);
-            if (rank > static_cast<uint32_t>(kSamples)) rank = kSamples;
             find_threshold(s, kBins, rank);
             const uint32_t key_lo = s.sel_digit << 20;
             // digit >= d_lo  <=>  key >= key_lo  <=>  x >= the float with that key: one compare per element
