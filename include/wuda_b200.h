@@ -923,6 +923,15 @@ int wuda_indexer_topk_host(wuda_indexer_plan* plan, const void* q_host, const vo
                            const float* weights_host, const int32_t* context_lens_host,
                            const int32_t* block_table_host, int32_t* page_indices_host,
                            float* logits_host, int batch, void* stream);
+/* The same call for a pool that lives on the device between steps: only the pages listed in dirty_pages_host
+ * (n_dirty page numbers; runs of consecutive numbers travel as one copy) are taken from kv_pages_host, the rest of
+ * the pool is what earlier calls on this plan left there.  A decode step appends a token or two per request, i.e.
+ * touches one page per request.  With a list (even an empty one) nothing else of the pool is uploaded; with
+ * dirty_pages_host == NULL the call is wuda_indexer_topk_host. */
+int wuda_indexer_topk_host_pages(wuda_indexer_plan* plan, const void* q_host, const void* kv_pages_host,
+                                 const int32_t* dirty_pages_host, int n_dirty, const float* weights_host,
+                                 const int32_t* context_lens_host, const int32_t* block_table_host,
+                                 int32_t* page_indices_host, float* logits_host, int batch, void* stream);
 
 #ifdef __cplusplus
 }

@@ -123,6 +123,7 @@ SIGNATURES = {
     "wuda_indexer_plan_create": (c_int, [ctypes.POINTER(c_vp), c_int, c_int, c_int, c_int, c_i64, c_int, c_i64, c_int]),
     "wuda_indexer_plan_destroy": (c_int, [c_vp]),
     "wuda_indexer_topk_host": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_vp]),
+    "wuda_indexer_topk_host_pages": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_vp]),
     "wuda_rmsnorm_quant_fp8": (c_int, [c_vp, c_i64, c_vp, c_int, c_float, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp]),
     "wuda_rope_quant_fp8": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_vp]),

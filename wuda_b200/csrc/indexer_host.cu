@@ -85,15 +85,26 @@ namespace {
 // Everything between the first enqueue and the final synchronisation; a failure in here must not
 // return to the caller while copies from (or to) its host buffers are still in flight.
 int indexer_topk_enqueue(wuda_indexer_plan* plan, const void* q_host, const void* kv_pages_host,
-                         const float* weights_host, const int32_t* context_lens_host, const int32_t* block_table_host,
+                         const int32_t* dirty_pages_host, int n_dirty, const float* weights_host, const int32_t* context_lens_host, const int32_t* block_table_host,
                          int32_t* page_indices_host, float* logits_host, int batch, int32_t* dev_status, cudaStream_t s) {
     using namespace wuda;
     const int64_t rows = static_cast<int64_t>(batch) * plan->next_n;
     WUDA_CUDA(cudaMemsetAsync(plan->status, 0, sizeof(int32_t), s));
     WUDA_CUDA(cudaMemcpyAsync(plan->q, q_host, rows * 64 * 128, cudaMemcpyHostToDevice, s));
-    if (kv_pages_host)
+    if (kv_pages_host && dirty_pages_host) {
+        // only the pages the host names, one copy per run of consecutive page numbers
+        for (int i = 0; i < n_dirty;) {
+            int j = i + 1;
+            while (j < n_dirty && dirty_pages_host[j] == dirty_pages_host[j - 1] + 1) ++j;
+            const size_t at = static_cast<size_t>(dirty_pages_host[i]) * plan->page_stride;
+            WUDA_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(plan->kv) + at, static_cast<const uint8_t*>(kv_pages_host) + at,
+                                      static_cast<size_t>(j - i) * plan->page_stride, cudaMemcpyHostToDevice, s));
+            i = j;
+        }
+    } else if (kv_pages_host) {
         WUDA_CUDA(cudaMemcpyAsync(plan->kv, kv_pages_host, static_cast<size_t>(plan->num_blocks) * plan->page_stride,
                                   cudaMemcpyHostToDevice, s));
+    }
     WUDA_CUDA(cudaMemcpyAsync(plan->weights, weights_host, rows * 64 * sizeof(float), cudaMemcpyHostToDevice, s));
     WUDA_CUDA(cudaMemcpyAsync(plan->ctx, context_lens_host, rows * sizeof(int32_t), cudaMemcpyHostToDevice, s));
     WUDA_CUDA(cudaMemcpyAsync(plan->bt, block_table_host,
@@ -117,12 +128,18 @@ int indexer_topk_enqueue(wuda_indexer_plan* plan, const void* q_host, const void
 
 }  // namespace
 
-extern "C" int wuda_indexer_topk_host(wuda_indexer_plan* plan, const void* q_host, const void* kv_pages_host,
-                                      const float* weights_host, const int32_t* context_lens_host,
-                                      const int32_t* block_table_host, int32_t* page_indices_host,
-                                      float* logits_host, int batch, void* stream) {
+extern "C" int wuda_indexer_topk_host_pages(wuda_indexer_plan* plan, const void* q_host, const void* kv_pages_host,
+                                            const int32_t* dirty_pages_host, int n_dirty, const float* weights_host,
+                                            const int32_t* context_lens_host, const int32_t* block_table_host,
+                                            int32_t* page_indices_host, float* logits_host, int batch, void* stream) {
     using namespace wuda;
     clear_error();
+    WUDA_REQUIRE(n_dirty >= 0 && (n_dirty == 0 || (dirty_pages_host && kv_pages_host)),
+                 "n_dirty must be >= 0, and a list of pages needs both the list and the host pool");
+    if (plan)
+        for (int i = 0; i < n_dirty; ++i)
+            WUDA_REQUIRE(dirty_pages_host[i] >= 0 && dirty_pages_host[i] < plan->num_blocks, "dirty page %d is outside the pool of %d",
+                         dirty_pages_host[i], plan->num_blocks);
     WUDA_REQUIRE(plan, "plan must not be NULL");
     WUDA_REQUIRE(batch >= 0 && batch <= plan->max_batch, "batch %d exceeds the plan's max_batch %d", batch,
                  plan->max_batch);
@@ -134,7 +151,7 @@ extern "C" int wuda_indexer_topk_host(wuda_indexer_plan* plan, const void* q_hos
     WUDA_REQUIRE(dev == plan->device, "the plan was created on device %d but device %d is current", plan->device, dev);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int32_t dev_status = 0;
-    const int st = indexer_topk_enqueue(plan, q_host, kv_pages_host, weights_host, context_lens_host, block_table_host,
+    const int st = indexer_topk_enqueue(plan, q_host, kv_pages_host, dirty_pages_host, n_dirty, weights_host, context_lens_host, block_table_host,
                                         page_indices_host, logits_host, batch, &dev_status, s);
     // on every path: no copy may outlive this call, the caller is free to reuse its host buffers
     const cudaError_t sync = cudaStreamSynchronize(s);
@@ -142,4 +159,12 @@ extern "C" int wuda_indexer_topk_host(wuda_indexer_plan* plan, const void* q_hos
     if (sync != cudaSuccess) return fail(WUDA_ERR_CUDA, "cudaStreamSynchronize failed: %s", cudaGetErrorString(sync));
     if (dev_status != 0) return fail(WUDA_ERR_DEVICE_STATUS, "kernel reported device status %d", dev_status);
     return WUDA_OK;
+}
+
+extern "C" int wuda_indexer_topk_host(wuda_indexer_plan* plan, const void* q_host, const void* kv_pages_host,
+                                      const float* weights_host, const int32_t* context_lens_host,
+                                      const int32_t* block_table_host, int32_t* page_indices_host,
+                                      float* logits_host, int batch, void* stream) {
+    return wuda_indexer_topk_host_pages(plan, q_host, kv_pages_host, nullptr, 0, weights_host, context_lens_host, block_table_host,
+                                        page_indices_host, logits_host, batch, stream);
 }

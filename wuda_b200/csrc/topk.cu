@@ -103,7 +103,7 @@ __device__ __forceinline__ void zero_hist(Shared& s, int nbins) {
 // warp sums its run of bins (thread = a few consecutive bins), all warps then read the 16 warp totals,
 // and the one warp whose run holds the threshold locates it with a shuffle scan.  The histogram must be
 // complete on entry (caller's barrier) and is unchanged on exit.
-__device__ __noinline__ void find_threshold(Shared& s, int nbins, uint32_t need) {
+__device__ __forceinline__ void find_threshold(Shared& s, int nbins, uint32_t need) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int per = nbins >= kThreads ? nbins / kThreads : 1;     // bins per thread
     const int lo = threadIdx.x * per;
@@ -139,7 +139,7 @@ __device__ __noinline__ void find_threshold(Shared& s, int nbins, uint32_t need)
 }
 
 // Exclusive prefix sum of `count` over the CTA's threads (thread order) and the CTA total.  Three barriers.
-__device__ __noinline__ uint32_t block_exclusive_scan(Shared& s, uint32_t count, uint32_t* total) {
+__device__ __forceinline__ uint32_t block_exclusive_scan(Shared& s, uint32_t count, uint32_t* total) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint32_t v = count;
 #pragma unroll
@@ -218,7 +218,7 @@ __device__ __forceinline__ void for_each_elem(const float* row, int n, bool vec_
 // ---------------------------------------------------------------------------------------------
 // Exact path: three histogram levels over the whole row, then one ordered pass that writes the
 // values above the threshold and the lowest-indexed `need3` of those equal to it.  One CTA.
-__device__ __noinline__ void exact_select(const Params& p, Shared& s, const float* row, int n, int r, bool vec_ok) {
+__device__ void exact_select(const Params& p, Shared& s, const float* row, int n, int r, bool vec_ok) {
     const int k = p.k;
     zero_hist(s, kBins);
     __syncthreads();

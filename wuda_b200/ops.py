@@ -201,11 +201,19 @@ class IndexerHostPlan:
         return a.data_ptr() if isinstance(a, torch.Tensor) else a.ctypes.data
 
     def run(self, q, kv_pages, weights, context_lens, block_table, page_indices_out, batch, logits_out=None,
-            stream=None):
-        check(lib.wuda_indexer_topk_host(self._h, self._ptr(q), self._ptr(kv_pages), self._ptr(weights),
-                                         self._ptr(context_lens), self._ptr(block_table),
-                                         self._ptr(page_indices_out), self._ptr(logits_out), batch,
-                                         _stream() if stream is None else stream))
+            stream=None, dirty_pages=None):
+        """dirty_pages (host int32 array of page numbers, or None): with a list only those pages of kv_pages are
+        uploaded, the rest of the pool is what earlier calls left on the device; None uploads the whole pool."""
+        s = _stream() if stream is None else stream
+        if dirty_pages is None:
+            check(lib.wuda_indexer_topk_host(self._h, self._ptr(q), self._ptr(kv_pages), self._ptr(weights),
+                                             self._ptr(context_lens), self._ptr(block_table),
+                                             self._ptr(page_indices_out), self._ptr(logits_out), batch, s))
+        else:
+            n = int(dirty_pages.numel() if isinstance(dirty_pages, torch.Tensor) else dirty_pages.size)
+            check(lib.wuda_indexer_topk_host_pages(self._h, self._ptr(q), self._ptr(kv_pages), self._ptr(dirty_pages), n,
+                                                   self._ptr(weights), self._ptr(context_lens), self._ptr(block_table),
+                                                   self._ptr(page_indices_out), self._ptr(logits_out), batch, s))
         return page_indices_out
 
     def close(self):
