@@ -21,7 +21,7 @@ def u16(t):
     return t.cpu().view(torch.int16).numpy().view(np.uint16)
 
 
-def make_stage(batch, seed):
+def make_stage(batch, seed, cmp_epb=None, max_pages=8):
     g = torch.Generator().manual_seed(seed)
     n_total = INDEX_HEADS * 128 + MAIN_HEADS * 512
     w = torch.randn(n_total, Q_LORA, generator=g) * 0.05
@@ -33,7 +33,8 @@ def make_stage(batch, seed):
                 sin_table=torch.sin(ang).contiguous())
     weights = CsaWeights(index_heads=INDEX_HEADS, main_heads=MAIN_HEADS, out_heads=OUT_HEADS,
                          **{k: v.cuda() for k, v in host.items()})
-    cache = KVCacheManager(batch + 1, 64, 8, device="cuda")
+    extra = {} if cmp_epb is None else dict(cmp_entries_per_block=cmp_epb)
+    cache = KVCacheManager(batch + 1, 64, max_pages, device="cuda", **extra)
     cache._pools["cmp"].take()   # the compressed-KV pool numbers its pages one off the indexer pool's
     stage = CsaDecodeStage(weights, cache, batch, topk=TOPK)
     return stage, cache, {k: v.numpy() for k, v in host.items()}, g
@@ -116,9 +117,15 @@ def check_step(stage, cache, host, st, m, before):
         assert sorted(got_pages[r].tolist()) == sorted(ref_pages[r].tolist())
 
 
-def test_steps_eager_then_graph(wuda):
+@pytest.mark.parametrize("cmp_epb,max_pages", [(None, 8), (32, 16)])
+def test_steps_eager_then_graph(wuda, cmp_epb, max_pages):
+    """The second case gives the compressed-KV pool pages half the size of the indexer pool's: the
+    top-k positions must be translated with the compressed pool's page size, the logits read with
+    the indexer pool's."""
     batch = 5
-    stage, cache, host, gen = make_stage(batch, 1234)
+    stage, cache, host, gen = make_stage(batch, 1234, cmp_epb, max_pages)
+    if cmp_epb is not None:
+        assert cache.entries_per_block["cmp"] == cmp_epb != cache.entries_per_block["idx"]
     slots = [cache.alloc_request() for _ in range(batch)]
     fast_forward(cache, slots, [397, 802, 1, 530, 1199], gen)
     graph = None
