@@ -48,10 +48,10 @@ def build_case(rng, batch, contexts, epb, pad=0, spread=1.0):
         n = contexts[b]
         scale = np.exp(rng.standard_normal((n, 1)) * spread)                     # rows of very different magnitude
         k_p, k_w = quantize_mxfp4(rng.standard_normal((n, 128)) * scale)
-        for t in range(n):
-            pg, off = table[b, t // epb], t % epb
-            pages[pg, off * 64:(off + 1) * 64] = k_p[t]
-            pages[pg, epb * 64 + off * 4:epb * 64 + off * 4 + 4] = np.frombuffer(k_w[t].tobytes(), np.uint8)
+        t = np.arange(n)
+        pg, off = table[b, t // epb], t % epb
+        pages[pg[:, None], (off * 64)[:, None] + np.arange(64)[None, :]] = k_p
+        pages[pg[:, None], (epb * 64 + off * 4)[:, None] + np.arange(4)[None, :]] = k_w.view(np.uint8).reshape(n, 4)
     weights = rng.standard_normal((batch, 64)).astype(np.float32)
     return dict(q=q_p.reshape(batch, 64, 64), q_sf=q_w.reshape(batch, 64).view(np.int32), pages=pages, weights=weights,
                 context_lens=np.asarray(contexts, np.int32), block_table=table, epb=epb)
@@ -90,6 +90,10 @@ def test_golden(wuda):
     (2, [700, 0], 32, 16),                   # a request without context; 32-entry pages with padded stride
     (3, [513, 129, 640], 128, 0),            # 128-entry pages, tile boundaries + 1
     (1, [4096], 64, 48),
+    (2, [1025, 300], 256, 0),                # 256-entry pages: one page per item of the paged kernel
+    (3, [257, 256, 255], 64, 0),             # around the paged kernel's item of 256 tokens
+    (2, [333, 50], 16, 0),                   # page sizes the paged kernel does not take: the gather kernel
+    (2, [500, 97], 48, 16),
 ])
 def test_against_oracle(wuda, batch, contexts, epb, pad):
     rng = np.random.default_rng(batch * 101 + epb)
@@ -99,6 +103,37 @@ def test_against_oracle(wuda, batch, contexts, epb, pad):
     assert status == 0
     check(got, oracle.mqa_logits_fp4(c["q"], c["q_sf"], c["pages"], c["weights"], c["context_lens"], c["block_table"],
                                      epb, columns))
+
+
+def test_many_items_per_sm(wuda):
+    """Half a million tokens: every CTA of the persistent grid walks more items than it has key stages, crosses
+    requests inside its range, and the ring's phases flip."""
+    rng = np.random.default_rng(77)
+    contexts = [40000, 33333, 50001, 256, 47000, 1, 65536, 30000, 52000, 44444, 61000, 38000, 0, 45678]
+    c = build_case(rng, len(contexts), contexts, 64)
+    columns = 65536
+    got, status = run(wuda, c, columns)
+    assert status == 0
+    check(got, oracle.mqa_logits_fp4(c["q"], c["q_sf"], c["pages"], c["weights"], c["context_lens"], c["block_table"],
+                                     64, columns))
+
+
+def test_context_beyond_the_logits_row_is_cut_and_reported(wuda):
+    rng = np.random.default_rng(10)
+    c = build_case(rng, 2, [700, 300], 64)
+    ref = oracle.mqa_logits_fp4(c["q"], c["q_sf"], c["pages"], c["weights"], c["context_lens"], c["block_table"], 64,
+                                768)[:, :512]            # the first request's 700 tokens are cut to the 512 of a logits row
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    logits = torch.full((3, 512), float("-inf"), dtype=torch.float32, device="cuda")   # a guard row behind
+    status = wuda.device_status_word()
+    status.zero_()
+    wuda.mqa_logits_fp4_decode_out(t(c["q"]).view(torch.int8), t(c["q_sf"]), t(c["pages"]), t(c["weights"]),
+                                   t(c["context_lens"]), t(c["block_table"]), logits[:2], 512, 64, status_word=status)
+    torch.cuda.synchronize()
+    got = logits.cpu().numpy()
+    assert int(status.item()) == 111
+    assert np.all(got[2] == -np.inf)                      # nothing behind the last row
+    check(got[:2], ref)
 
 
 def test_reference_call_form_fills_the_tail(wuda):

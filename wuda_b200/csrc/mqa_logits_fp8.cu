@@ -23,6 +23,7 @@
 
 #include "host.h"
 #include "ptx.cuh"
+#include "tile_cursor.cuh"
 
 namespace wuda {
 namespace mqa {
@@ -94,113 +95,7 @@ struct Smem {
     static __host__ __device__ constexpr int total(int stages) { return misc_off(stages) + 16 + 1024; }
 };
 
-// A context length as the kernel uses it: negative values count as 0, values beyond what a row of the
-// logits / block table holds are cut to that (the math warps report the cut as kDevBadContextLen).
-__device__ __forceinline__ int clamp_ctx(int v, int max_ctx) { return min(max(v, 0), max_ctx); }
-
-// Max context over the next_n rows of request b (its tile count follows from it).
-template <int NEXT_N>
-__device__ __forceinline__ int request_ctx(const int32_t* ctx, int b, int max_ctx) {
-    int m = 0;
-#pragma unroll
-    for (int j = 0; j < NEXT_N; ++j) m = max(m, clamp_ctx(__ldg(ctx + b * NEXT_N + j), max_ctx));
-    return m;
-}
-
-// The position of one CTA in the flat tile list. Every warp keeps its own copy and
-// advances it identically, so no shared-memory broadcast is needed.
-struct TileCursor {
-    int b;         // request
-    int j;         // tile inside the request
-    int tiles_b;   // tiles of request b
-    int ctx_b;     // max context of request b
-    int count;     // tiles this CTA owns
-};
-
-template <int NEXT_N>
-__device__ __forceinline__ TileCursor make_cursor(const int32_t* ctx, int batch, int max_ctx) {
-    const uint32_t lane = lane_id();
-    long long total = 0;
-    for (int base = 0; base < batch; base += 32) {
-        int b = base + lane;
-        int t = (b < batch) ? ((request_ctx<NEXT_N>(ctx, b, max_ctx) + kTile - 1) / kTile) : 0;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        total += t;
-    }
-    const long long start = total * blockIdx.x / gridDim.x;
-    const long long end = total * (blockIdx.x + 1) / gridDim.x;
-    TileCursor c;
-    c.count = static_cast<int>(end - start);
-    c.b = batch;
-    c.j = 0;
-    c.tiles_b = 0;
-    c.ctx_b = 0;
-    if (c.count == 0) return c;
-    long long prefix = 0;
-    for (int base = 0; base < batch; base += 32) {
-        int b = base + lane;
-        int cx = (b < batch) ? request_ctx<NEXT_N>(ctx, b, max_ctx) : 0;
-        int t = (cx + kTile - 1) / kTile;
-        int incl = t;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            int v = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += v;
-        }
-        const long long incl_g = prefix + incl;
-        const unsigned hit = __ballot_sync(0xffffffffu, incl_g > start);
-        if (hit) {
-            const int src = __ffs(hit) - 1;
-            const long long incl_src = __shfl_sync(0xffffffffu, incl_g, src);
-            const int t_src = __shfl_sync(0xffffffffu, t, src);
-            c.b = base + src;
-            c.tiles_b = t_src;
-            c.ctx_b = __shfl_sync(0xffffffffu, cx, src);
-            c.j = static_cast<int>(start - (incl_src - t_src));
-            return c;
-        }
-        prefix += __shfl_sync(0xffffffffu, incl, 31);
-    }
-    c.count = 0;  // unreachable when the two passes see the same lengths
-    return c;
-}
-
-// Moves the cursor forward by k tiles.  on_enter(cursor) is called once for every
-// request entered on the way (requests without tiles are skipped by every role alike),
-// including the one the cursor lands in.  The caller never moves past the CTA's range.
-template <int NEXT_N, typename F>
-__device__ __forceinline__ void advance_by(TileCursor& c, int k, const int32_t* ctx, int batch, int max_ctx,
-                                           F&& on_enter) {
-    c.j += k;
-    while (c.j >= c.tiles_b) {
-        c.j -= c.tiles_b;
-        do {
-            ++c.b;
-            if (c.b >= batch) {      // cannot happen inside the range; keeps the loop finite
-                c.tiles_b = 0x3fffffff;
-                c.ctx_b = 0;
-                return;
-            }
-            c.ctx_b = request_ctx<NEXT_N>(ctx, c.b, max_ctx);
-            c.tiles_b = (c.ctx_b + kTile - 1) / kTile;
-        } while (c.tiles_b == 0);
-        on_enter(c);
-    }
-}
-
-// Ring position that advances without integer division.
-struct Ring {
-    int idx = 0;
-    uint32_t phase = 0;
-    __device__ __forceinline__ void step(int n, int size) {   // n <= size
-        idx += n;
-        if (idx >= size) {
-            idx -= size;
-            phase ^= 1u;
-        }
-    }
-};
+using namespace tiles;
 
 template <int NEXT_N>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -264,7 +159,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
     pdl_launch_dependents();
     pdl_wait();
 
-    TileCursor cur = make_cursor<NEXT_N>(p.context_lens, p.batch, p.max_ctx);
+    TileCursor cur = make_cursor<NEXT_N, kTile>(p.context_lens, p.batch, p.max_ctx);
     const int ntiles = cur.count;
 
     // Every role walks its own tiles n = r, r + R, ... of the CTA's range with a cursor
@@ -315,7 +210,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
         if (ntiles > 0) on_enter(cur);
         ring.step(me, S);       // the host guarantees S >= kProducers
         for (int n = me; n < ntiles && alive; n += kProducers) {
-            advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, p.max_ctx, on_enter);
+            advance_by<NEXT_N, kTile>(cur, n - at, p.context_lens, p.batch, p.max_ctx, on_enter);
             at = n;
             if (!alive) break;
             const int first_page = cur.j << ppt_shift;
@@ -349,7 +244,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
             ring.step(kProducers, S);
         }
         if (alive && ntiles > 0 && at < ntiles - 1)
-            advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, p.max_ctx, on_enter);
+            advance_by<NEXT_N, kTile>(cur, ntiles - 1 - at, p.context_lens, p.batch, p.max_ctx, on_enter);
     } else if (warp < kMmaWarp0 + kIssuers) {
         // ------------------------------------------------------------ UMMA issuers
         // One thread per warp runs the whole loop (the other lanes go straight to the
@@ -373,7 +268,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
             ring.step(me, S);
             tring.step(me, kTmemStages);
             for (int n = me; n < ntiles && alive; n += kIssuers) {
-                advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, p.max_ctx, on_enter);
+                advance_by<NEXT_N, kTile>(cur, n - at, p.context_lens, p.batch, p.max_ctx, on_enter);
                 at = n;
                 if (!alive) break;
                 const int s = ring.idx, ts = tring.idx;
@@ -396,7 +291,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
                 tring.step(kIssuers, kTmemStages);
             }
             if (alive && ntiles > 0 && at < ntiles - 1)
-                advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, p.max_ctx, on_enter);
+                advance_by<NEXT_N, kTile>(cur, ntiles - 1 - at, p.context_lens, p.batch, p.max_ctx, on_enter);
         }
     } else if (warp >= kFirstMathWarp) {
         // ------------------------------------------------------------ math warps
@@ -434,7 +329,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
         ring.step(wg, S);
         tring.step(wg, kTmemStages);
         for (int n = wg; n < ntiles && alive; n += kMathGroups) {
-            advance_by<NEXT_N>(cur, n - at, p.context_lens, p.batch, p.max_ctx, on_enter);
+            advance_by<NEXT_N, kTile>(cur, n - at, p.context_lens, p.batch, p.max_ctx, on_enter);
             at = n;
             if (!alive) break;
             const int s = ring.idx, ts = tring.idx;
@@ -496,7 +391,7 @@ mqa_logits_fp8_kernel(const __grid_constant__ CUtensorMap q_map,
             tring.step(kMathGroups, kTmemStages);
         }
         if (alive && ntiles > 0 && at < ntiles - 1)
-            advance_by<NEXT_N>(cur, ntiles - 1 - at, p.context_lens, p.batch, p.max_ctx, on_enter);
+            advance_by<NEXT_N, kTile>(cur, ntiles - 1 - at, p.context_lens, p.batch, p.max_ctx, on_enter);
     }
 
     __syncthreads();
