@@ -388,7 +388,10 @@ int wuda_csa_decode_step(const wuda_csa_weights* weights, const wuda_csa_caches*
  * Replaces mqa_logits_fp4_decode_out (kernels/mqa_logits_fp4.cu:474-650); formats as
  * test/test_mqa_logits_fp4.py:100-115 and :228-256, arithmetic as its twin (:207-218) over the
  * dequantised values.  A block_table entry outside [0, num_blocks) reads page 0 and is reported
- * as WUDA_DEV_BAD_PAGE_INDEX.
+ * as WUDA_DEV_BAD_PAGE_INDEX; a context length beyond logits_stride (or, with pages of 32, 64, 128
+ * or 256 entries, beyond block_table_stride * entries_per_block) is cut to that and reported as
+ * WUDA_DEV_BAD_CONTEXT_LEN.  Pages of 32, 64, 128 or 256 entries are brought in whole by tensor
+ * copies (the fast kernel); any other entries_per_block >= 1 takes a slower gather kernel.
  */
 int wuda_mqa_logits_fp4(const void* q_fp4, const void* q_scales, const void* kv_pages, const float* weights,
                         const int32_t* context_lens, const int32_t* block_table, float* logits, int batch,

@@ -477,7 +477,7 @@ def topk(k=2048):
               "the rows are L2-resident)" % (k, rows, lo, hi, us, by / 1e6, by / us / 1e3, by / us / 1e3 / hbm, kind))
 
 
-def mqa_fp4(batches=(64,), contexts=(8192, 32768), launches_only=0):
+def mqa_fp4(batches=(64, 128), contexts=(8192, 32768), launches_only=0):
     """MXFP4 paged MQA logits (68 bytes per token): identity page tables, random codes and scale bytes."""
     hbm, _, kind = peaks()
     print("MXFP4 paged MQA logits, 64 heads x 128; HBM peak (%s) %.0f GB/s" % (kind, hbm))
@@ -780,7 +780,7 @@ def one(kind, m, n, k, launches=5):
     print("ran %d launches of %s M=%d N=%d K=%d" % (launches, kind, m, n, k))
 
 
-KINDS = {"topk": topk, "gemm_fp8": gemm_fp8, "gemm_fp8_pow2": lambda: gemm_fp8(pow2=True), "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(contexts=(32768,), launches_only=3),
+KINDS = {"topk": topk, "gemm_fp8": gemm_fp8, "gemm_fp8_pow2": lambda: gemm_fp8(pow2=True), "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(batches=(64,), contexts=(32768,), launches_only=3),
          "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(32,), launches_only=3),
          "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
          "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,
