@@ -190,6 +190,27 @@ int wuda_index_q_post_fp8(const void* iq_bf16, int64_t row_stride, const int32_t
                           float* weights_out, int tokens, int heads, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Indexer-q post (FP4 form): every (token, index head) row of 128 bf16 values gets RoPE on its
+ * last 64 dims (rounded to bf16), a Hadamard transform of the 128 values (fp32 butterflies with
+ * strides 1, 2, ... 64 in that order, times 128^-1/2, one rounding to bf16) and MXFP4
+ * quantisation: per 32 values the scale 2^ceil(log2(amax / 6)) as a biased exponent byte, e2m1
+ * codes rounded to nearest even - what wuda_mqa_logits_fp4 takes as q_fp4 and q_scales.  The
+ * head weights are not touched in this form.
+ *
+ * Replaces idx_postprocess (kernels/idx_post_fp4.cu) and the FP4 idx-post tail of
+ * wq_b_proj_gemm_merged (include/idx_post_fp4.cuh:79-224: same order of the butterflies, same
+ * constants, so the bytes are the kernel's); torch twin test/test_wq_b_fp8_gemm.py:161-182
+ * (ref_idx_chain), which multiplies by the Hadamard matrix and rounds e2m1 ties down instead.
+ *
+ *   iq_bf16, row_stride, q_pos, tables: as wuda_index_q_post_fp8
+ *   q_fp4     uint8 [tokens, heads, 64], two codes per byte, the lower index in the low nibble
+ *   q_scales  int32 [tokens, heads], byte g = exponent byte of values [32g, 32g + 32)
+ */
+int wuda_index_q_post_fp4(const void* iq_bf16, int64_t row_stride, const int32_t* q_pos, const float* cos_table,
+                          const float* sin_table, int max_pos, void* q_fp4, void* q_scales, int tokens, int heads,
+                          void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Query RMSNorm (no weight) + RoPE on the last 64 of every 512-wide head, bf16 -> bf16, in
  * one pass with one rounding.  Output head h reads input head h % input_heads.
  *
@@ -282,6 +303,17 @@ typedef struct wuda_cache_writers {
 
 int wuda_cache_writers_fp8(const wuda_cache_writers* args, int rows, int32_t* status_word, void* stream);
 
+/* The same launch with the indexer compressor in its FP4 form (idx_comp::process_row<false>,
+ * include/idx_comp_fp4.cuh:203-274; torch twin ref_comp_step with fp8=False,
+ * test/test_wq_b_fp8_gemm.py:550-586): behind the rotation a Hadamard transform of the 128 values
+ * (fp32 butterflies, strides 1, 2, ... 64, times 128^-1/2, one rounding to bf16) and per 32 values
+ * the scale 2^ceil(log2(amax / 6)) with e2m1 codes (nearest even).  The indexer record is 64 code
+ * bytes at page + off*64 and 4 exponent bytes at page + entries_per_block*64 + off*4 (the kv_pages
+ * format of wuda_mqa_logits_fp4); the indexer bundle's compact outputs are q8 = codes uint8
+ * [rows, 64] and s8 = exponent bytes uint8 [rows, 4] (the pointer is taken as bytes).  MAIN and
+ * window writers are unchanged. */
+int wuda_cache_writers_fp4(const wuda_cache_writers* args, int rows, int32_t* status_word, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Layer launch of the indexer half of one decode step: q RMSNorm + quantisation, the merged
  * q projection, query RMSNorm + RoPE of the main heads, indexer-q post, the three cache
@@ -327,7 +359,10 @@ typedef struct wuda_csa_caches {
     int ring_entries;
     int idx_entries_per_block, cmp_entries_per_block, swa_entries_per_block;
     int idx_num_blocks, cmp_num_blocks, swa_num_blocks;
-    int reserved;
+    int idx_fp4;               /* non-zero: the indexer pool holds MXFP4 records (68 bytes per entry) and the step takes
+                                  the FP4 forms: wuda_index_q_post_fp4, wuda_cache_writers_fp4, wuda_mqa_logits_fp4
+                                  (index_heads must be 64; workspace.iq_fp8 receives the codes, workspace.w_folded the
+                                  query's scale words, and the logits take step.w64 as head weights)              */
     int64_t idx_block_stride_bytes, cmp_block_stride_bytes, swa_block_stride_bytes;
     uint8_t* idx_pool;
     uint8_t* cmp_pool;

@@ -502,6 +502,105 @@ void oracle_index_q_post_fp8(const uint16_t* x, int64_t row_stride, const int32_
     }
 }
 
+/* ------------------------------------------------------------------ the MXFP4 producers
+ *
+ * What the reference's FP4 form of the indexer puts behind the rotation (include/idx_post_fp4.cuh:79-224 for the
+ * query, include/idx_comp_fp4.cuh:239-274 for the compressed key; torch twins ref_idx_chain and ref_comp_step with
+ * fp8=False, test/test_wq_b_fp8_gemm.py:161-182, :550-586): a Hadamard transform of the 128 values as butterflies
+ * in fp32, strides 1, 2, 4, ... 64 in that order (every output of a stage is one fp32 addition or subtraction, so
+ * the order of the stages fixes every bit), times 128^-1/2, one rounding to bf16; per 32 values a power-of-two scale
+ * 2^ceil(log2(amax / 6)) with amax at least about 6 * 2^-126 and the division done as a multiplication by the fp32 1/6,
+ * stored as a biased exponent byte; values / scale (exact) to e2m1, round to nearest even, the sign kept on a zero.
+ * Two codes per byte, the lower index in the low nibble; the four exponent bytes of a row form one little-endian word.
+ */
+static void hadamard128_bf16(float* v) {
+    for (int s = 1; s < 128; s <<= 1)
+        for (int i = 0; i < 128; ++i)
+            if ((i & s) == 0) {
+                const float a = v[i], b = v[i + s];
+                v[i] = a + b;
+                v[i + s] = a - b;
+            }
+    for (int i = 0; i < 128; ++i) v[i] = bf16_round(v[i] * 0.08838834764831845f);
+}
+
+static uint8_t e2m1_rne(float x) {   /* |x| <= 6 after scaling; ties to the even code */
+    static const float grid[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+    const float a = fabsf(x);
+    int code = 7;
+    for (int i = 0; i < 7; ++i) {
+        const float mid = 0.5f * (grid[i] + grid[i + 1]);
+        if (a < mid || (a == mid && (i & 1) == 0)) {
+            code = i;
+            break;
+        }
+    }
+    return (uint8_t)(code | (signbit(x) ? 8 : 0));
+}
+
+__attribute__((optimize("fp-contract=off")))
+static void quant_mxfp4_row(const float* v, float amax_floor, uint8_t* packed64, uint8_t* sf4) {
+    for (int b = 0; b < 4; ++b) {
+        float amax = 0.0f;
+        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[b * 32 + i]));
+        amax = fmaxf(amax, amax_floor);
+        const int e = log2_ceil_f32(amax * (1.0f / 6.0f));
+        const float inv = ldexpf(1.0f, -e);
+        sf4[b] = (uint8_t)(e + 127);
+        for (int i = 0; i < 32; i += 2) {
+            const uint8_t lo = e2m1_rne(v[b * 32 + i] * inv), hi = e2m1_rne(v[b * 32 + i + 1] * inv);
+            packed64[(b * 32 + i) / 2] = (uint8_t)(lo | (hi << 4));
+        }
+    }
+}
+
+__attribute__((optimize("fp-contract=off")))
+void oracle_index_q_post_fp4(const uint16_t* x, int64_t row_stride, const int32_t* q_pos, const float* cos_t,
+                             const float* sin_t, int max_pos, uint8_t* q4, uint32_t* sf_words, int tokens, int heads) {
+    for (int t = 0; t < tokens; ++t) {
+        int pos = q_pos[t] < 0 ? 0 : (q_pos[t] >= max_pos ? max_pos - 1 : q_pos[t]);
+        for (int h = 0; h < heads; ++h) {
+            float v[128];
+            for (int i = 0; i < 128; ++i) v[i] = bf16_to_f32(x[t * row_stride + h * 128 + i]);
+            rotate_tail(v + 64, cos_t + (int64_t)pos * 32, sin_t + (int64_t)pos * 32, 1);
+            hadamard128_bf16(v);
+            const int64_t g = (int64_t)t * heads + h;
+            uint8_t sf[4];
+            /* the query kernel's floor is the decimal 6 * 1.1754944e-38, one ulp above 6 * 2^-126: an all-zero row
+               gets the exponent byte 2 (include/idx_post_fp4.cuh:147) */
+            quant_mxfp4_row(v, 7.052966400779935e-38f, q4 + g * 64, sf);
+            sf_words[g] = (uint32_t)sf[0] | ((uint32_t)sf[1] << 8) | ((uint32_t)sf[2] << 16) | ((uint32_t)sf[3] << 24);
+        }
+    }
+}
+
+/* The indexer compressor's FP4 form: record = 64 code bytes at off * 64 of the page, its four exponent bytes at
+ * entries_per_block * 64 + off * 4 (the page layout the MXFP4 logits read). */
+__attribute__((optimize("fp-contract=off")))
+void oracle_indexer_compressor_fp4(const float* state, const int64_t* state_row, int ring, const int64_t* pos,
+                                   const float* norm_w, const float* cos_t, const float* sin_t, int max_pos,
+                                   float eps, uint8_t* pool, const int64_t* dst, int epb, int64_t stride, uint8_t* q4,
+                                   uint8_t* s4, int rows) {
+    for (int r = 0; r < rows; ++r) {
+        if ((pos[r] + 1) % 4 != 0 || state_row[r] < 0) continue;
+        float v[128];
+        compress_row(state, state_row[r], ring, 128, norm_w, cos_t, sin_t, max_pos, pos[r], eps, v);
+        hadamard128_bf16(v);
+        uint8_t q[64], sf[4];
+        /* the compressor's floor is the product 6 * FLT_MIN, exact: an all-zero row gets the exponent byte 1
+           (include/idx_comp_fp4.cuh:248) */
+        quant_mxfp4_row(v, 6.0f * 1.1754944e-38f, q, sf);
+        if (q4) memcpy(q4 + (int64_t)r * 64, q, 64);
+        if (s4) memcpy(s4 + (int64_t)r * 4, sf, 4);
+        if (pool && dst && dst[r] >= 0) {
+            uint8_t* page = pool + dst[r] / epb * stride;
+            const int off = (int)(dst[r] % epb);
+            memcpy(page + (int64_t)off * 64, q, 64);
+            memcpy(page + (int64_t)epb * 64 + off * 4, sf, 4);
+        }
+    }
+}
+
 /* Query RMSNorm (no weight) + RoPE on the last 64 of 512, one rounding to bf16, after
  * dsv4_megakernel/megakernel/include/query_rms_rope.cuh:20-61: the sum of squares runs as fused
  * multiply-adds over the 16 values a lane holds (columns [8l, 8l+8) then [256+8l, 256+8l+8)) and a

@@ -62,6 +62,9 @@ def _declare(l):
     l.oracle_window_kv_fp8.argtypes = [vp, vp, vp, vp, vp, c.c_int, c.c_float, vp, vp, c.c_int, i64, vp, vp, vp,
                                        c.c_int]
     l.oracle_index_q_post_fp8.argtypes = [vp, i64, vp, vp, vp, c.c_int, vp, vp, vp, c.c_int, c.c_int]
+    l.oracle_index_q_post_fp4.argtypes = [vp, i64, vp, vp, vp, c.c_int, vp, vp, c.c_int, c.c_int]
+    l.oracle_indexer_compressor_fp4.argtypes = [vp, vp, c.c_int, vp, vp, vp, vp, c.c_int, c.c_float, vp, vp, c.c_int,
+                                                i64, vp, vp, c.c_int]
     l.oracle_query_rms_rope.argtypes = [vp, i64, vp, vp, vp, c.c_int, vp, c.c_int, c.c_int, c.c_int, c.c_float]
     l.oracle_mhc_pre.argtypes = [vp, vp, vp, vp, vp, c.c_float, c.c_float, c.c_float, vp, vp, vp, vp, vp, vp, vp,
                                  c.c_int, c.c_int]
@@ -245,6 +248,33 @@ def index_q_post_fp8(x_bf16, q_pos, cos_t, sin_t, weights=None):
     lib().oracle_index_q_post_fp8(_p(x), heads * 128, _p(_c(q_pos, np.int32)), _p(ct), _p(st), ct.shape[0], _p(wt),
                                   _p(q8), _p(w), tokens, heads)
     return q8, w
+
+
+def index_q_post_fp4(x_bf16, q_pos, cos_t, sin_t):
+    """x uint16 (bf16) [tokens, heads, 128] -> (packed e2m1 uint8 [tokens, heads, 64], scale words uint32
+    [tokens, heads]): RoPE on the last 64, Hadamard-128, one power-of-two scale per 32 values."""
+    x = _c(x_bf16, np.uint16)
+    tokens, heads = x.shape[0], x.shape[1]
+    ct, st = _c(cos_t, np.float32), _c(sin_t, np.float32)
+    q4, sf = np.empty((tokens, heads, 64), np.uint8), np.empty((tokens, heads), np.uint32)
+    lib().oracle_index_q_post_fp4(_p(x), heads * 128, _p(_c(q_pos, np.int32)), _p(ct), _p(st), ct.shape[0], _p(q4),
+                                  _p(sf), tokens, heads)
+    return q4, sf
+
+
+def indexer_compressor_fp4(state, state_row, pos, norm_w, cos_t, sin_t, eps=1e-6, pool=None, dst=None, epb=64):
+    """The FP4 form of the indexer compressor.  Returns (packed e2m1 [rows, 64] uint8, exponent bytes [rows, 4]
+    uint8); rows that do not compress keep the fill (0xAB).  `pool` (uint8 [pages, stride], 68 bytes per entry)
+    is written in place."""
+    state = _c(state, np.float32)
+    rows = len(pos)
+    q4, s4 = np.full((rows, 64), 0xAB, np.uint8), np.full((rows, 4), 0xAB, np.uint8)
+    pool, dst, epb, stride = _pool_args(pool, dst, epb)
+    sr, ps = _c(state_row, np.int64), _c(pos, np.int64)
+    nw, ct, st = _c(norm_w, np.float32), _c(cos_t, np.float32), _c(sin_t, np.float32)
+    lib().oracle_indexer_compressor_fp4(_p(state), _p(sr), state.shape[1], _p(ps), _p(nw), _p(ct), _p(st), ct.shape[0],
+                                        eps, _p(pool), _p(dst), epb, stride, _p(q4), _p(s4), rows)
+    return q4, s4
 
 
 def query_rms_rope(x_bf16, positions, cos_t, sin_t, out_heads=None, eps=1e-6):

@@ -12,8 +12,9 @@ Functions used (paths inside the reference repository):
                                                            stable-argsort rule (:116)
   dsv4_megakernel/megakernel/test/test_e2e_decode.py      ref_mhc_post (:423-426), ref_flash_attn
                                                            (:377-392) over deq_model1_row (:346-356)
-  dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py   ref_comp_step (:550-586, fp8 form) and
-                                                           ref_win_step (:646-665)
+  dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py   ref_comp_step (:550-586, both forms), ref_win_step
+                                                           (:646-665), ref_idx_fp8_chain (:184-196) and
+                                                           ref_idx_chain (:161-182, the FP4 form)
   dsv4_megakernel/megakernel/test/test_hc_fused_tc.py     hc_reference (:115-136)
   dsv4_megakernel/origin/model.py                         Gate.forward (:563-584); Gate, Expert, MoE (:546-644) for
                                                            the whole MoE block on bf16 weights
@@ -301,6 +302,39 @@ def golden_cache_writers(ref_root):
     print("window_kv_fp8.npz", tuple(q8.shape))
 
 
+def golden_fp4_producers(ref_root):
+    """The FP4 form of the indexer's producers: the torch twins ref_idx_chain (query: RoPE, Hadamard-128, MXFP4) and
+    ref_comp_step with fp8=False (compressed key).  The twins return the dequantised values and the scales."""
+    wqb = _load(ref_root, "dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py", "ref_wqb")
+    wqb.torch = torch
+    g = torch.Generator().manual_seed(67)
+    max_pos = 64
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float32), 1.0 / (10000.0 ** (torch.arange(32) / 32.0)))
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+
+    tokens, heads = 6, 64
+    iq = (torch.randn(tokens, heads, 128, generator=g) * torch.rand(tokens, heads, 1, generator=g) * 4).bfloat16()
+    iq[0, 0] = 0                                                      # an all-zero head: the scale's lower clamp
+    qpos = torch.tensor([0, 1, 13, 40, 62, 63], dtype=torch.int32)
+    deq, sf = wqb.ref_idx_chain(iq.float().view(tokens, -1), qpos.long(), cos, sin)
+    np.savez_compressed(os.path.join(HERE, "index_q_post_fp4.npz"), iq=_u16(iq), q_pos=qpos.numpy(), cos=cos.numpy(),
+                        sin=sin.numpy(), deq=deq.numpy(), sf=sf.numpy())
+    print("index_q_post_fp4.npz", tuple(deq.shape))
+
+    rows = 12
+    pos = torch.tensor([3, 7, 11, 12, 15, 19, 23, 30, 31, 35, 47, 59])
+    state = torch.randn(rows, 8, 512, generator=g)
+    state[0, 4:, :256], state[0, 4:, 256:] = 0.0, float("-inf")     # a fresh request: entries 4..7 never written
+    state[1, :, 256:] *= 8.0                                        # peaked softmax
+    state_row = torch.arange(rows) * 8 + pos % 8
+    norm_w = torch.rand(128, generator=g) + 0.5
+    deq, s4, mask = wqb.ref_comp_step(state, state_row, pos, norm_w, cos, sin, fp8=False)
+    np.savez_compressed(os.path.join(HERE, "indexer_compressor_fp4.npz"), state=state.numpy(), pos=pos.numpy(),
+                        state_row=state_row.numpy(), norm_w=norm_w.numpy(), cos=cos.numpy(), sin=sin.numpy(),
+                        deq=deq.numpy(), s4=s4.numpy(), compress=mask.numpy())
+    print("indexer_compressor_fp4.npz", int(mask.sum()), "compress rows of", rows)
+
+
 def mhc_pre_inputs(seed=71, m=3, hidden=7168):
     """Seeded inputs of the mHC-pre fixture (regenerated by the tests: 2.75 MB of weights are not
     stored).  numpy's PCG64 stream is stable across versions; the fixture carries a checksum."""
@@ -554,6 +588,7 @@ def main():
     golden_mhc_post(ref_root)
     golden_kv_cache(ref_root)
     golden_cache_writers(ref_root)
+    golden_fp4_producers(ref_root)
     golden_mhc_pre(ref_root)
     golden_moe_gate(ref_root)
     golden_sparse_mla(ref_root)

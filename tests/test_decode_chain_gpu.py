@@ -21,7 +21,7 @@ def u16(t):
     return t.cpu().view(torch.int16).numpy().view(np.uint16)
 
 
-def make_stage(batch, seed, cmp_epb=None, max_pages=8):
+def make_stage(batch, seed, cmp_epb=None, max_pages=8, fp4=False):
     g = torch.Generator().manual_seed(seed)
     n_total = INDEX_HEADS * 128 + MAIN_HEADS * 512
     w = torch.randn(n_total, Q_LORA, generator=g) * 0.05
@@ -34,6 +34,8 @@ def make_stage(batch, seed, cmp_epb=None, max_pages=8):
     weights = CsaWeights(index_heads=INDEX_HEADS, main_heads=MAIN_HEADS, out_heads=OUT_HEADS,
                          **{k: v.cuda() for k, v in host.items()})
     extra = {} if cmp_epb is None else dict(cmp_entries_per_block=cmp_epb)
+    if fp4:
+        extra["indexer_fp8"] = False      # the indexer pool holds MXFP4 records: the step takes its FP4 forms
     cache = KVCacheManager(batch + 1, 64, max_pages, device="cuda", **extra)
     cache._pools["cmp"].take()   # the compressed-KV pool numbers its pages one off the indexer pool's
     stage = CsaDecodeStage(weights, cache, batch, topk=TOPK)
@@ -48,6 +50,10 @@ def fast_forward(cache, slots, tokens, gen):
             cache.step_begin([s])
     pool = cache.idx_pool
     epb = cache.entries_per_block["idx"]
+    if not cache.indexer_fp8:             # MXFP4 records: any codes, exponent bytes around one
+        pool[:, :epb * 64] = torch.randint(0, 256, (pool.size(0), epb * 64), generator=gen, dtype=torch.uint8).cuda()
+        pool[:, epb * 64:epb * 68] = torch.randint(120, 131, (pool.size(0), epb * 4), generator=gen, dtype=torch.uint8).cuda()
+        return
     keys = torch.randint(0, 0x7E, (pool.size(0), epb * 128), generator=gen, dtype=torch.uint8)
     keys |= (torch.randint(0, 2, keys.shape, generator=gen, dtype=torch.uint8) << 7)
     scales = torch.rand(pool.size(0), epb, generator=gen) * 0.09 + 0.01
@@ -74,17 +80,24 @@ def check_step(stage, cache, host, st, m, before):
     # 3 query RMSNorm + RoPE, 4 indexer-q post: exact on the GPU's y
     ref_qm = oracle.query_rms_rope(y[:, n_index:].reshape(m, MAIN_HEADS, 512), pos, cos, sin, out_heads=OUT_HEADS)
     assert np.array_equal(u16(stage.q_main[:m]), ref_qm)
-    ref_iq, ref_w = oracle.index_q_post_fp8(y[:, :n_index].reshape(m, INDEX_HEADS, 128), pos.astype(np.int32), cos, sin,
-                                            stage.w64[:m].cpu().numpy())
-    assert np.array_equal(stage.iq_fp8[:m].cpu().numpy(), ref_iq)
-    assert np.array_equal(stage.w_folded[:m].cpu().numpy(), ref_w)
+    fp4 = stage.indexer_fp4
+    if fp4:    # codes at the start of the iq buffer, the scale words where the folded weights would be
+        q4 = stage.iq_fp8.view(-1)[:m * INDEX_HEADS * 64].view(m, INDEX_HEADS, 64).cpu().numpy()
+        q_sf = stage.w_folded.view(torch.int32)[:m].cpu().numpy().view(np.uint32)
+        ref_q4, ref_sf = oracle.index_q_post_fp4(y[:, :n_index].reshape(m, INDEX_HEADS, 128), pos.astype(np.int32), cos, sin)
+        assert np.array_equal(q4, ref_q4) and np.array_equal(q_sf, ref_sf)
+    else:
+        ref_iq, ref_w = oracle.index_q_post_fp8(y[:, :n_index].reshape(m, INDEX_HEADS, 128), pos.astype(np.int32), cos,
+                                                sin, stage.w64[:m].cpu().numpy())
+        assert np.array_equal(stage.iq_fp8[:m].cpu().numpy(), ref_iq)
+        assert np.array_equal(stage.w_folded[:m].cpu().numpy(), ref_w)
     # 5 cache writers
     ring = cache.state_ring_entries
     pools = {k: v.copy() for k, v in before.items()}
     rows = st["main_state_row"].cpu().numpy()
-    oracle.indexer_compressor_fp8(cache.idx_state.cpu().numpy().reshape(-1, ring, 512), rows, pos, host["idx_norm"], cos,
-                                  sin, pool=pools["idx"], dst=st["idx_dst"].cpu().numpy(),
-                                  epb=cache.entries_per_block["idx"])
+    (oracle.indexer_compressor_fp4 if fp4 else oracle.indexer_compressor_fp8)(
+        cache.idx_state.cpu().numpy().reshape(-1, ring, 512), rows, pos, host["idx_norm"], cos, sin, pool=pools["idx"],
+        dst=st["idx_dst"].cpu().numpy(), epb=cache.entries_per_block["idx"])
     oracle.main_compressor_fp8(cache.main_state.cpu().numpy().reshape(-1, ring, 2048), rows, pos, host["main_norm"], cos,
                                sin, pool=pools["cmp"], dst=st["cmp_dst"].cpu().numpy(),
                                epb=cache.entries_per_block["cmp"])
@@ -102,12 +115,18 @@ def check_step(stage, cache, host, st, m, before):
     bt, cmp_bt = stage.block_table[:m].cpu().numpy(), stage.cmp_block_table[:m].cpu().numpy()
     assert not np.array_equal(bt, cmp_bt)    # the two pools number their pages differently here
     logits = stage.logits[:m].cpu().numpy()
-    ref_l = oracle.mqa_logits_fp8(stage.iq_fp8[:m].cpu().numpy(), got["idx"], stage.w_folded[:m].cpu().numpy(),
-                                  ncmp.reshape(m, 1), bt, 1, cache.entries_per_block["idx"], stage.logits_stride)
     valid = np.arange(stage.logits_stride)[None, :] < ncmp[:, None]
     assert np.all(np.isfinite(logits[valid]))
-    rms = np.sqrt(np.mean(ref_l[valid].astype(np.float64) ** 2))
-    assert np.all(np.abs(logits[valid] - ref_l[valid]) <= 1e-2 * np.abs(ref_l[valid]) + 1e-4 * rms)
+    if fp4:
+        ref_l = oracle.mqa_logits_fp4(q4, q_sf, got["idx"], stage.w64[:m].cpu().numpy(), ncmp, bt,
+                                      cache.entries_per_block["idx"], stage.logits_stride)
+        rms = np.sqrt(np.mean(ref_l[valid].astype(np.float64) ** 2))
+        assert np.all(np.abs(logits[valid] - ref_l[valid]) <= 1e-4 * np.abs(ref_l[valid]) + 1e-5 * rms)
+    else:
+        ref_l = oracle.mqa_logits_fp8(stage.iq_fp8[:m].cpu().numpy(), got["idx"], stage.w_folded[:m].cpu().numpy(),
+                                      ncmp.reshape(m, 1), bt, 1, cache.entries_per_block["idx"], stage.logits_stride)
+        rms = np.sqrt(np.mean(ref_l[valid].astype(np.float64) ** 2))
+        assert np.all(np.abs(logits[valid] - ref_l[valid]) <= 1e-2 * np.abs(ref_l[valid]) + 1e-4 * rms)
     masked = np.where(valid, logits, -np.inf).astype(np.float32)
     # positions are translated with the pages of the compressed-KV pool, which the attention reads
     ref_pages, ref_raw = oracle.topk(masked, ncmp, cmp_bt, TOPK, cache.entries_per_block["cmp"])
@@ -117,13 +136,14 @@ def check_step(stage, cache, host, st, m, before):
         assert sorted(got_pages[r].tolist()) == sorted(ref_pages[r].tolist())
 
 
-@pytest.mark.parametrize("cmp_epb,max_pages", [(None, 8), (32, 16)])
-def test_steps_eager_then_graph(wuda, cmp_epb, max_pages):
+@pytest.mark.parametrize("cmp_epb,max_pages,fp4", [(None, 8, False), (32, 16, False), (None, 8, True)])
+def test_steps_eager_then_graph(wuda, cmp_epb, max_pages, fp4):
     """The second case gives the compressed-KV pool pages half the size of the indexer pool's: the
     top-k positions must be translated with the compressed pool's page size, the logits read with
-    the indexer pool's."""
+    the indexer pool's.  The third runs the FP4 form of the indexer (Hadamard + MXFP4 query and keys)."""
     batch = 5
-    stage, cache, host, gen = make_stage(batch, 1234, cmp_epb, max_pages)
+    stage, cache, host, gen = make_stage(batch, 1234, cmp_epb, max_pages, fp4)
+    assert stage.indexer_fp4 == fp4
     if cmp_epb is not None:
         assert cache.entries_per_block["cmp"] == cmp_epb != cache.entries_per_block["idx"]
     slots = [cache.alloc_request() for _ in range(batch)]

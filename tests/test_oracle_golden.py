@@ -215,6 +215,42 @@ def test_index_q_post_oracle_matches_reference_twin():
     assert (q8[0, 0] == 0).all() and w[0, 0] == g["weights"][0, 0] * np.float32(1e-12)
 
 
+def _cosine(a, b):
+    a, b = a.astype(np.float64).ravel(), b.astype(np.float64).ravel()
+    return float(a @ b / np.sqrt((a @ a) * (b @ b)))
+
+
+def test_index_q_post_fp4_oracle_matches_reference_twin():
+    """The twin multiplies by the Hadamard matrix and rounds e2m1 ties down; the reference kernel (and the oracle)
+    run fp32 butterflies and round ties to even, so the twin's own acceptance is the bar (cosine > 0.999, scales equal
+    in > 98 % of the blocks: test/test_idx_post_fp4.py:40-66)."""
+    g = load_golden("index_q_post_fp4.npz")
+    q4, sf = oracle.index_q_post_fp4(g["iq"], g["q_pos"], g["cos"], g["sin"])
+    tokens, heads = sf.shape
+    deq = oracle.dequant_mxfp4(q4.reshape(-1, 64), sf.reshape(-1)).reshape(tokens, heads, 128)
+    scale = np.ldexp(1.0, sf.view(np.uint8).reshape(tokens, heads, 4).astype(np.int32) - 127)
+    assert np.mean(scale == g["sf"]) >= 0.99          # a bf16 rounding of the transform's output can tip a block's amax
+    assert _cosine(deq, g["deq"]) > 0.999
+    same_scale = np.repeat(scale == g["sf"], 32, axis=-1)
+    assert np.mean(deq[same_scale] == g["deq"][same_scale]) >= 0.99       # the rest: ties and the bf16 rounding
+    step = np.abs(deq - g["deq"]) / np.repeat(scale, 32, axis=-1)         # ... and never more than one code apart
+    assert step[same_scale].max() <= 1.0
+    assert (q4[0, 0] & 0x77 == 0).all() and sf[0, 0] == 0x02020202    # the all-zero head: zero codes; the kernel's floor
+    # constant lies one ulp above 6 * 2^-126, so the exponent byte is 2 where the twin's clamp gives 1
+
+
+def test_indexer_compressor_fp4_oracle_matches_reference_twin():
+    g = load_golden("indexer_compressor_fp4.npz")
+    q4, s4 = oracle.indexer_compressor_fp4(g["state"], g["state_row"], g["pos"], g["norm_w"], g["cos"], g["sin"])
+    m = g["compress"]
+    assert np.array_equal(m, (g["pos"] + 1) % 4 == 0) and m.sum() >= 8
+    assert (q4[~m] == 0xAB).all() and (s4[~m] == 0xAB).all()           # other rows are not touched
+    words = s4[m].astype(np.uint32) @ (1 << (8 * np.arange(4, dtype=np.uint32)))
+    deq = oracle.dequant_mxfp4(q4[m], words.astype(np.uint32))
+    assert np.mean(s4[m] == g["s4"][m]) >= 0.95
+    assert _cosine(deq, g["deq"][m]) > 0.999
+
+
 def test_query_rms_rope_oracle_against_the_two_pass_fixtures():
     """No twin of the fused query tail exists in the reference's tests; the oracle is held against
     the origin model's RMSNorm (fixture rmsnorm_7168) re-used on 512-wide rows: unit weight, so

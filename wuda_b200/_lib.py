@@ -52,7 +52,7 @@ class CsaCaches(ctypes.Structure):
     """wuda_csa_caches"""
     _fields_ = [("idx_state", c_vp), ("main_state", c_vp), ("state_rows_total", c_i64), ("ring_entries", c_int),
                 ("idx_entries_per_block", c_int), ("cmp_entries_per_block", c_int), ("swa_entries_per_block", c_int),
-                ("idx_num_blocks", c_int), ("cmp_num_blocks", c_int), ("swa_num_blocks", c_int), ("reserved", c_int),
+                ("idx_num_blocks", c_int), ("cmp_num_blocks", c_int), ("swa_num_blocks", c_int), ("idx_fp4", c_int),
                 ("idx_block_stride_bytes", c_i64), ("cmp_block_stride_bytes", c_i64), ("swa_block_stride_bytes", c_i64),
                 ("idx_pool", c_vp), ("cmp_pool", c_vp), ("swa_pool", c_vp)]
 
@@ -128,6 +128,8 @@ SIGNATURES = {
     "wuda_rope_quant_fp8": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_vp]),
     "wuda_cache_writers_fp8": (c_int, [ctypes.POINTER(CacheWriters), c_int, c_vp, c_vp]),
+    "wuda_cache_writers_fp4": (c_int, [ctypes.POINTER(CacheWriters), c_int, c_vp, c_vp]),
+    "wuda_index_q_post_fp4": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_int, c_vp, c_vp, c_int, c_int, c_vp]),
     "wuda_index_q_post_fp8": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
     "wuda_query_rms_rope": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, c_int, c_vp, c_int, c_int, c_int, c_float, c_vp]),
     "wuda_csa_decode_step": (c_int, [ctypes.POINTER(CsaWeights), ctypes.POINTER(CsaCaches), ctypes.POINTER(CsaStep),

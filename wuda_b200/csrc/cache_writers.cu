@@ -35,6 +35,7 @@ constexpr int kM1Body = 576, kM1Nope = 448, kM1ScaleBytes = 8;
 struct Params {
     wuda_cache_writers a;
     int rows;
+    int idx_fp4;      // the indexer entry is an MXFP4 record (64 code bytes + 4 exponent bytes) instead of 128 e4m3 + fp32
     int32_t* status;
 };
 
@@ -45,6 +46,19 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
     return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+// two fp32 values -> two e2m1 codes in one byte, `lo` in the low nibble; round to nearest even, saturating
+__device__ __forceinline__ uint32_t pack_e2m1x2(float lo, float hi) {
+    uint32_t out;
+    asm("{\n\t"
+        ".reg .b8 b;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b, %2, %1;\n\t"
+        "cvt.u32.u8 %0, b;\n\t"
+        "}\n"
+        : "=r"(out)
+        : "f"(lo), "f"(hi));
+    return out;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -208,6 +222,49 @@ __device__ void indexer_rows(const Params& P) {
         const int64_t rp = clamp_pos(p + 1 - kRatio, P.a.max_pos);
         rotate4(v, P.a.cos_table + rp * (kRopeDim / 2), P.a.sin_table + rp * (kRopeDim / 2), (col - 64) / 2, true);
     }
+    if (P.idx_fp4) {
+        // The FP4 form (include/idx_comp_fp4.cuh:239-274): Hadamard transform as fp32 butterflies with strides 1, 2
+        // (inside the lane's 4 values), then 4 .. 64 (lanes l ^ 1 .. l ^ 16), times 128^-1/2, one rounding to bf16;
+        // per 32 values (8 lanes) the scale 2^ceil(log2(amax / 6)) and e2m1 codes.
+        const float t0 = __fadd_rn(v[0], v[1]), t1 = __fsub_rn(v[0], v[1]);
+        const float t2 = __fadd_rn(v[2], v[3]), t3 = __fsub_rn(v[2], v[3]);
+        v[0] = __fadd_rn(t0, t2), v[1] = __fadd_rn(t1, t3), v[2] = __fsub_rn(t0, t2), v[3] = __fsub_rn(t1, t3);
+#pragma unroll
+        for (int x = 1; x < 32; x <<= 1) {
+            const bool upper = (lane & x) != 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[e], x);
+                v[e] = upper ? __fsub_rn(other, v[e]) : __fadd_rn(v[e], other);
+            }
+        }
+        float amax4 = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            v[e] = bf16_round(__fmul_rn(v[e], 0.088388347648318447f));
+            amax4 = fmaxf(amax4, fabsf(v[e]));
+        }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) amax4 = fmaxf(amax4, __shfl_xor_sync(0xffffffffu, amax4, o));
+        amax4 = fmaxf(amax4, 6.0f * 1.1754944e-38f);
+        const int se = log2_ceil(__fmul_rn(amax4, 1.0f / 6.0f));
+        const float inv = __uint_as_float(static_cast<uint32_t>(127 - se) << 23);   // 2^-se, exact
+        const uint16_t codes = static_cast<uint16_t>(pack_e2m1x2(v[0] * inv, v[1] * inv) |
+                                                     (pack_e2m1x2(v[2] * inv, v[3] * inv) << 8));
+        uint8_t* q4 = b.q8;                                   // compact outputs: [rows, 64] codes, [rows, 4] exponent bytes
+        uint8_t* s4 = reinterpret_cast<uint8_t*>(b.s8);
+        if (q4) *reinterpret_cast<uint16_t*>(q4 + static_cast<int64_t>(row) * 64 + lane * 2) = codes;
+        if (s4 && (lane & 7) == 0) s4[static_cast<int64_t>(row) * 4 + (lane >> 3)] = static_cast<uint8_t>(se + 127);
+        int off4 = 0;
+        uint8_t* page4 = locate(b.pool, b.dst, row, b.entries_per_block, b.block_stride_bytes, b.num_blocks,
+                                lane == 0 ? P.status : nullptr, &off4);
+        if (page4) {
+            *reinterpret_cast<uint16_t*>(page4 + off4 * 64 + lane * 2) = codes;
+            if ((lane & 7) == 0)
+                page4[static_cast<int64_t>(b.entries_per_block) * 64 + off4 * 4 + (lane >> 3)] = static_cast<uint8_t>(se + 127);
+        }
+        return;
+    }
     float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -341,17 +398,32 @@ int check_compressor(const char* who, const wuda_compressor_bundle& b, int recor
 }  // namespace cw
 }  // namespace wuda
 
+namespace wuda {
+namespace cw {
+int launch_writers(const wuda_cache_writers* args, int rows, int idx_fp4, int32_t* status_word, void* stream);
+}
+}  // namespace wuda
+
 extern "C" int wuda_cache_writers_fp8(const wuda_cache_writers* args, int rows, int32_t* status_word, void* stream) {
+    wuda::clear_error();
+    return wuda::cw::launch_writers(args, rows, 0, status_word, stream);
+}
+
+extern "C" int wuda_cache_writers_fp4(const wuda_cache_writers* args, int rows, int32_t* status_word, void* stream) {
+    wuda::clear_error();
+    return wuda::cw::launch_writers(args, rows, 1, status_word, stream);
+}
+
+int wuda::cw::launch_writers(const wuda_cache_writers* args, int rows, int idx_fp4, int32_t* status_word, void* stream) {
     using namespace wuda;
     using namespace wuda::cw;
-    clear_error();
     WUDA_REQUIRE(args, "args must not be NULL");
     WUDA_REQUIRE(rows >= 0, "rows must be >= 0 (got %d)", rows);
     if (rows == 0) return WUDA_OK;
     WUDA_REQUIRE(args->indexer.state || args->main.state || args->window.y, "no writer is enabled");
     WUDA_REQUIRE(args->pos && args->cos_table && args->sin_table && args->max_pos >= 1,
                  "pos, the cos/sin tables and max_pos >= 1 are required");
-    int st = check_compressor("indexer", args->indexer, 128, 4);
+    int st = check_compressor("indexer", args->indexer, idx_fp4 ? 64 : 128, 4);
     if (st != WUDA_OK) return st;
     st = check_compressor("main", args->main, kM1Body, kM1ScaleBytes);
     if (st != WUDA_OK) return st;
@@ -366,6 +438,7 @@ extern "C" int wuda_cache_writers_fp8(const wuda_cache_writers* args, int rows, 
     Params p;
     p.a = *args;
     p.rows = rows;
+    p.idx_fp4 = idx_fp4;
     p.status = status_word;
     const dim3 grid(rows, 3);
     WUDA_CUDA(launch_pdl(cache_writers_kernel, dim3(grid), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p));

@@ -10,9 +10,9 @@
 //   1 q RMSNorm + power-of-two 1x128 FP8 quantisation of q_raw
 //   2 block-scaled FP8 GEMM with the merged [indexer heads | main heads] weight
 //   3 query RMSNorm + RoPE of the main heads (reads the GEMM output in place)
-//   4 indexer-q post (reads the GEMM output in place) -> FP8 q + folded head weights
+//   4 indexer-q post (reads the GEMM output in place) -> FP8 q + folded head weights (FP4 form: Hadamard + MXFP4 q)
 //   5 cache writers: the indexer entry of this step must be in the pool before 6 scores it
-//   6 paged MQA logits over the indexer pool
+//   6 paged MQA logits over the indexer pool (FP8 records, or MXFP4 records with caches.idx_fp4)
 //   7 top-k + page transform
 // Only 1 -> 2 -> 4 -> 6 -> 7 is a chain.  5 needs nothing from 1-4 and 3 feeds nothing in 4-7, so
 // they run on two side streams forked from and joined back into the caller's stream with events
@@ -60,6 +60,8 @@ extern "C" int wuda_csa_decode_step(const wuda_csa_weights* w, const wuda_csa_ca
                  "index_heads, main_heads >= 1 and out_heads >= main_heads are required");
     WUDA_REQUIRE(ws->q_fp8 && ws->q_scales && ws->y && ws->iq_fp8 && ws->w_folded && ws->gemm_scratch,
                  "every workspace buffer is required");
+    WUDA_REQUIRE(!c->idx_fp4 || w->index_heads == 64, "the FP4 form of the indexer has 64 index heads (got %d)",
+                 w->index_heads);
     const int n_index = w->index_heads * 128, n_main = w->main_heads * 512;
     const int n_total = n_index + n_main;
     const char* y = static_cast<const char*>(ws->y);
@@ -103,7 +105,8 @@ extern "C" int wuda_csa_decode_step(const wuda_csa_weights* w, const wuda_csa_ca
     cw.window.block_stride_bytes = c->swa_block_stride_bytes;
     cw.window.pool = c->swa_pool;
     cw.window.dst = s->swa_dst;
-    int status = wuda_cache_writers_fp8(&cw, m, ws->status_word, side->writers);
+    const bool fp4 = c->idx_fp4 != 0;   // the indexer's FP4 form: Hadamard + MXFP4 query and keys, block-scaled logits
+    int status = (fp4 ? wuda_cache_writers_fp4 : wuda_cache_writers_fp8)(&cw, m, ws->status_word, side->writers);
     WUDA_CUDA(cudaEventRecord(side->writers_done, side->writers));
 
     // ---- the chain on the caller's stream.  Every fork is joined on every path out of this function,
@@ -126,13 +129,26 @@ extern "C" int wuda_csa_decode_step(const wuda_csa_weights* w, const wuda_csa_ca
         WUDA_CUDA(cudaEventRecord(side->query_done, side->query));
     }
     if (status == WUDA_OK)
-        status = wuda_index_q_post_fp8(y, n_total, s->q_pos, w->cos_table, w->sin_table, w->max_pos, s->w64, ws->iq_fp8,
-                                       ws->w_folded, m, w->index_heads, stream);
+        status = fp4 ? wuda_index_q_post_fp4(y, n_total, s->q_pos, w->cos_table, w->sin_table, w->max_pos, ws->iq_fp8,
+                                             ws->w_folded, m, w->index_heads, stream)
+                     : wuda_index_q_post_fp8(y, n_total, s->q_pos, w->cos_table, w->sin_table, w->max_pos, s->w64,
+                                             ws->iq_fp8, ws->w_folded, m, w->index_heads, stream);
     WUDA_CUDA(cudaStreamWaitEvent(main_stream, side->writers_done, 0));     // join A: the pool is written
-    if (status == WUDA_OK)
-        status = wuda_mqa_logits_fp8(ws->iq_fp8, c->idx_pool, ws->w_folded, s->n_compressed, s->idx_block_table, s->logits,
-                                     m, 1, c->idx_num_blocks, c->idx_entries_per_block, c->idx_block_stride_bytes,
-                                     s->block_table_stride, s->logits_stride, ws->status_word, stream);
+    if (status == WUDA_OK) {
+        if (fp4) {
+            const int64_t by_table = static_cast<int64_t>(s->block_table_stride) * c->idx_entries_per_block;
+            const int64_t cap = s->logits_stride < by_table ? s->logits_stride : by_table;
+            status = wuda_mqa_logits_fp4(ws->iq_fp8, ws->w_folded, c->idx_pool, s->w64, s->n_compressed, s->idx_block_table,
+                                         s->logits, m, static_cast<int>(cap < 0x7fffff00 ? cap : 0x7fffff00),
+                                         c->idx_num_blocks, c->idx_entries_per_block, c->idx_block_stride_bytes,
+                                         s->block_table_stride, s->logits_stride, ws->status_word, stream);
+        } else {
+            status = wuda_mqa_logits_fp8(ws->iq_fp8, c->idx_pool, ws->w_folded, s->n_compressed, s->idx_block_table,
+                                         s->logits, m, 1, c->idx_num_blocks, c->idx_entries_per_block,
+                                         c->idx_block_stride_bytes, s->block_table_stride, s->logits_stride,
+                                         ws->status_word, stream);
+        }
+    }
     if (status == WUDA_OK)
         // the selected positions become entries of the pool the attention reads: the compressed-KV pool's page
         // table and page size when that table is given, else the indexer pool's

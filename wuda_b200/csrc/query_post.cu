@@ -4,6 +4,12 @@
 //   bf16) -> one scale per head, scale = max(amax / 448, 1e-12) -> e4m3, and the head weight folded
 //   with that scale.  Torch twin: dsv4_megakernel/megakernel/test/test_wq_b_fp8_gemm.py:184-196
 //   (ref_idx_fp8_chain); device counterpart include/idx_post_fp4.cuh:229-283.
+// index_q_post_fp4: the FP4 form of the same tail: RoPE on the last 64 dims (rounded to bf16) -> Hadamard
+//   transform of the 128 values (fp32 butterflies, strides 1, 2, ... 64 in that order; times 128^-1/2; one
+//   rounding to bf16) -> per 32 values a power-of-two scale 2^ceil(log2(amax / 6)) as a biased exponent byte and
+//   e2m1 codes (round to nearest even), two per byte, the four exponent bytes of a head as one word: the q / q_scales
+//   operands of the MXFP4 MQA logits.  Device counterpart include/idx_post_fp4.cuh:79-224 (same order of the
+//   butterflies, same constants), torch twin test/test_wq_b_fp8_gemm.py:161-182 (ref_idx_chain).
 // query_rms_rope: per (token, head) row of 512 bf16 -> x * 1/sqrt(mean x^2 + eps) (no weight) ->
 //   RoPE on the last 64 dims in fp32 -> one rounding to bf16.  Output head h reads input head
 //   h % input_heads, which duplicates heads for a tensor-parallel consumer.  Counterpart:
@@ -104,6 +110,95 @@ __global__ void __launch_bounds__(kThreads) index_q_post_kernel(IndexParams p) {
     if (sub == 0) p.w_out[g] = p.weights ? __fmul_rn(p.weights[g], scale) : scale;
 }
 
+// two fp32 values (already divided by the block's power-of-two scale) -> two e2m1 codes in one byte, `lo` in the
+// low nibble; round to nearest even, saturating
+__device__ __forceinline__ uint32_t pack_e2m1x2(float lo, float hi) {
+    uint32_t out;
+    asm("{\n\t"
+        ".reg .b8 b;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b, %2, %1;\n\t"
+        "cvt.u32.u8 %0, b;\n\t"
+        "}\n"
+        : "=r"(out)
+        : "f"(lo), "f"(hi));
+    return out;
+}
+
+struct IndexFp4Params {
+    const __nv_bfloat16* x;
+    int64_t row_stride;
+    const int32_t* q_pos;
+    const float* cos_t;
+    const float* sin_t;
+    int max_pos;
+    uint8_t* q4;          // [tokens, heads, 64]
+    uint32_t* sf_words;   // [tokens, heads]
+    int64_t groups;       // tokens * heads
+    int heads;
+};
+
+// 16 lanes own a head, 8 consecutive values each: butterflies of strides 1, 2, 4 stay inside a lane, strides 8..64
+// pair lanes sub ^ 1, 2, 4, 8; a block of 32 values is 4 lanes.
+__global__ void __launch_bounds__(kThreads) index_q_post_fp4_kernel(IndexFp4Params p) {
+    pdl_launch_dependents();
+    pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
+    const int64_t g = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 4;   // (token, head)
+    const int sub = threadIdx.x & 15;
+    const bool live = g < p.groups;            // whole 16-lane groups are live or not
+    const int64_t gg = live ? g : 0;
+    const int64_t tok = gg / p.heads;
+    const int head = static_cast<int>(gg - tok * p.heads);
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(p.x + tok * p.row_stride + head * 128 + sub * 8), v);
+    if (sub >= 8) {
+        int pos = p.q_pos[tok];
+        pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+        rotate8(v, p.cos_t + static_cast<int64_t>(pos) * 32, p.sin_t + static_cast<int64_t>(pos) * 32, (sub - 8) * 4);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = bf16_round(v[i]);
+    }
+#pragma unroll
+    for (int s = 1; s < 8; s <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if ((i & s) == 0) {
+                const float a = v[i], b = v[i + s];
+                v[i] = __fadd_rn(a, b);
+                v[i + s] = __fsub_rn(a, b);
+            }
+#pragma unroll
+    for (int x = 1; x < 16; x <<= 1) {
+        const bool upper = (sub & x) != 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], x);
+            v[i] = upper ? __fsub_rn(other, v[i]) : __fadd_rn(v[i], other);
+        }
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        v[i] = bf16_round(__fmul_rn(v[i], 0.08838834764831845f));
+        amax = fmaxf(amax, fabsf(v[i]));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    // the floor is the decimal 6 * 1.1754944e-38 of the reference kernel (one ulp above 6 * 2^-126)
+    amax = fmaxf(amax, 7.052966400779935e-38f);
+    const uint32_t rbits = __float_as_uint(__fmul_rn(amax, 1.0f / 6.0f));
+    const int e = static_cast<int>((rbits >> 23) & 0xffu) - 127 + ((rbits & 0x7fffffu) ? 1 : 0);
+    const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);   // 2^-e, exact; e <= 127 - 3 for bf16 input
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) packed |= pack_e2m1x2(v[2 * i] * inv, v[2 * i + 1] * inv) << (8 * i);
+    uint32_t word = (sub & 3) == 0 ? static_cast<uint32_t>(e + 127) << (8 * (sub >> 2)) : 0u;
+    word |= __shfl_xor_sync(0xffffffffu, word, 4);
+    word |= __shfl_xor_sync(0xffffffffu, word, 8);
+    if (!live) return;
+    *reinterpret_cast<uint32_t*>(p.q4 + g * 64 + sub * 4) = packed;
+    if (sub == 0) p.sf_words[g] = word;
+}
+
 struct QueryParams {
     const __nv_bfloat16* x;
     int64_t row_stride;
@@ -186,6 +281,39 @@ extern "C" int wuda_index_q_post_fp8(const void* iq_bf16, int64_t row_stride, co
     p.heads = heads;
     const int64_t blocks = (p.groups * 16 + kThreads - 1) / kThreads;
     WUDA_CUDA(launch_pdl(index_q_post_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p));
+    return WUDA_OK;
+}
+
+extern "C" int wuda_index_q_post_fp4(const void* iq_bf16, int64_t row_stride, const int32_t* q_pos,
+                                     const float* cos_table, const float* sin_table, int max_pos, void* q_fp4,
+                                     void* q_scales, int tokens, int heads, void* stream) {
+    using namespace wuda;
+    using namespace wuda::qp;
+    clear_error();
+    WUDA_REQUIRE(tokens >= 0 && heads >= 1, "tokens must be >= 0 and heads >= 1");
+    WUDA_REQUIRE(row_stride >= static_cast<int64_t>(heads) * 128 && row_stride % 8 == 0,
+                 "row_stride must be >= heads * 128 and a multiple of 8 elements");
+    WUDA_REQUIRE(max_pos >= 1, "max_pos must be >= 1");
+    if (tokens == 0) return WUDA_OK;
+    WUDA_REQUIRE(iq_bf16 && q_pos && cos_table && sin_table && q_fp4 && q_scales,
+                 "iq, q_pos, the tables and both outputs must not be NULL");
+    WUDA_REQUIRE(aligned16(iq_bf16) && aligned16(q_fp4) && aligned16(cos_table) && aligned16(sin_table) &&
+                     (reinterpret_cast<uintptr_t>(q_scales) & 3u) == 0,
+                 "iq, q_fp4 and the tables must be 16-byte aligned, q_scales 4-byte aligned");
+    IndexFp4Params p;
+    p.x = static_cast<const __nv_bfloat16*>(iq_bf16);
+    p.row_stride = row_stride;
+    p.q_pos = q_pos;
+    p.cos_t = cos_table;
+    p.sin_t = sin_table;
+    p.max_pos = max_pos;
+    p.q4 = static_cast<uint8_t*>(q_fp4);
+    p.sf_words = static_cast<uint32_t*>(q_scales);
+    p.groups = static_cast<int64_t>(tokens) * heads;
+    p.heads = heads;
+    const int64_t blocks = (p.groups * 16 + kThreads - 1) / kThreads;
+    WUDA_CUDA(launch_pdl(index_q_post_fp4_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 0,
+                         static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 

@@ -52,6 +52,12 @@ class CsaDecodeStage:
         if not 1 <= max_batch <= 128:
             raise ValueError("max_batch must be in [1, 128]")
         self.w, self.cache, self.max_batch, self.topk = weights, cache, max_batch, topk
+        # A cache whose indexer pool holds MXFP4 records (KVCacheManager(indexer_fp8=False)) selects the FP4 form of
+        # the step: Hadamard + MXFP4 indexer-q post and compressor, block-scaled logits.  iq_fp8 then receives the
+        # packed codes and w_folded (viewed as int32) the query's scale words.
+        self.indexer_fp4 = not cache.indexer_fp8
+        if self.indexer_fp4 and weights.index_heads != 64:
+            raise ValueError("the FP4 form of the indexer has 64 index heads")
         epb = cache.entries_per_block["idx"]
         max_compressed = max_compressed or cache.max_pages * epb
         self.logits_stride = (max_compressed + 255) // 256 * 256
@@ -89,7 +95,8 @@ class CsaDecodeStage:
             swa_entries_per_block=cache.entries_per_block["swa"], idx_num_blocks=cache.idx_pool.size(0),
             cmp_num_blocks=cache.cmp_pool.size(0), swa_num_blocks=cache.swa_pool.size(0),
             idx_block_stride_bytes=cache.block_stride_bytes["idx"], cmp_block_stride_bytes=cache.block_stride_bytes["cmp"],
-            swa_block_stride_bytes=cache.block_stride_bytes["swa"], idx_pool=cache.idx_pool.data_ptr(),
+            swa_block_stride_bytes=cache.block_stride_bytes["swa"], idx_fp4=int(self.indexer_fp4),
+            idx_pool=cache.idx_pool.data_ptr(),
             cmp_pool=cache.cmp_pool.data_ptr(), swa_pool=cache.swa_pool.data_ptr())
         self._ws = _lib.CsaWorkspace(q_fp8=self.q_fp8.data_ptr(), q_scales=self.q_scales.data_ptr(), y=self.y.data_ptr(),
                                      iq_fp8=self.iq_fp8.data_ptr(), w_folded=self.w_folded.data_ptr(),

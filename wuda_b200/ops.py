@@ -15,7 +15,7 @@ from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp4_decode_out", "mqa_logits_fp4_decode", "mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "sparse_mla_decode", "flash_mla_with_kvcache", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
-           "rmsnorm_rope_out", "mhc_post_out", "mhc_pre", "moe_gate", "bf16_gemm", "front_mixed_gemm", "idx_postprocess_fp8", "cache_writers_fp8", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
+           "rmsnorm_rope_out", "mhc_post_out", "mhc_pre", "moe_gate", "bf16_gemm", "front_mixed_gemm", "idx_postprocess_fp8", "idx_postprocess", "cache_writers_fp8", "cache_writers_fp4", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -130,8 +130,9 @@ def mqa_logits_fp4_decode_out(q, sf_q, kv_cache, weights, context_lens, block_ta
     _require(max_ctx <= logits.size(1), "logits has fewer columns than max_context_len")
     check(lib.wuda_mqa_logits_fp4(q.data_ptr(), sf_q.data_ptr(), kv_cache.data_ptr(), weights.data_ptr(),
                                   context_lens.data_ptr(), block_table.data_ptr(), logits.data_ptr(), b, max_ctx,
-                                  kv_cache.size(0), int(kv_entries_per_block), kv_cache.size(1), block_table.stride(0),
-                                  logits.stride(0), _ptr(status_word), _stream()))
+                                  kv_cache.size(0), int(kv_entries_per_block), kv_cache.size(1),
+                                  block_table.stride(0) if b > 1 else block_table.size(1),    # (one row: any stride)
+                                  logits.stride(0) if logits.size(0) > 1 else logits.size(1), _ptr(status_word), _stream()))
     return logits
 
 
@@ -445,21 +446,21 @@ def _pool_fields(bundle, rows, name):
                 block_stride_bytes=pool.stride(0), pool=pool.data_ptr(), dst=dst.data_ptr())
 
 
-def _compact_fields(bundle, rows, name, nq, ns, with_rope):
+def _compact_fields(bundle, rows, name, nq, ns, with_rope, scale_dtype=torch.float32):
     q8, s8, rope = bundle.get("q8"), bundle.get("s8"), bundle.get("rope")
     if q8 is not None:
         _require(q8.is_cuda and q8.is_contiguous() and q8.element_size() == 1 and q8.numel() == rows * nq,
                  f"{name}: q8 must be contiguous CUDA 1-byte [rows, {nq}]")
     if s8 is not None:
-        _require(s8.is_cuda and s8.is_contiguous() and s8.dtype == torch.float32 and s8.numel() == rows * ns,
-                 f"{name}: s8 must be contiguous CUDA fp32 with {ns} per row")
+        _require(s8.is_cuda and s8.is_contiguous() and s8.dtype == scale_dtype and s8.numel() == rows * ns,
+                 f"{name}: s8 must be contiguous CUDA {scale_dtype} with {ns} per row")
     if rope is not None:
         _require(with_rope and rope.is_cuda and rope.is_contiguous() and rope.dtype == torch.bfloat16
                  and rope.numel() == rows * 64, f"{name}: rope must be contiguous CUDA bf16 [rows, 64]")
     return dict(q8=_ptr(q8), s8=_ptr(s8), rope=_ptr(rope))
 
 
-def _compressor_bundle(bundle, rows, name, half):
+def _compressor_bundle(bundle, rows, name, half, fp4=False):
     if bundle is None:
         return _lib.CompressorBundle()
     state = _f32(bundle["state"], name + ".state", 4 * half)
@@ -471,13 +472,19 @@ def _compressor_bundle(bundle, rows, name, half):
     fields = dict(state=state.data_ptr(), state_row=row.data_ptr(), norm_w=norm.data_ptr(),
                   state_rows_total=state.numel() // (4 * half), ring_entries=ring)
     fields.update(_pool_fields(bundle, rows, name))
-    fields.update(_compact_fields(bundle, rows, name, 128 if half == 128 else 448, 1 if half == 128 else 7, half == 512))
+    if fp4:
+        fields.update(_compact_fields(bundle, rows, name, 64, 4, False, torch.uint8))
+    else:
+        fields.update(_compact_fields(bundle, rows, name, 128 if half == 128 else 448, 1 if half == 128 else 7, half == 512))
     return _lib.CompressorBundle(**fields)
 
 
-def cache_writers_fp8(pos, cos_table, sin_table, *, indexer=None, main=None, window=None, eps=1e-6, status_word=None):
+def cache_writers_fp8(pos, cos_table, sin_table, *, indexer=None, main=None, window=None, eps=1e-6, status_word=None,
+                      indexer_fp4=False):
     """The indexer compressor, the MAIN compressor and the window-KV writer of one decode step in one
-    launch (wuda_cache_writers_fp8).  Each writer is a dict or None:
+    launch (wuda_cache_writers_fp8; with indexer_fp4=True wuda_cache_writers_fp4: the indexer entry is an MXFP4
+    record - Hadamard transform, 64 code bytes + 4 exponent bytes -, its compact outputs q8 uint8 [rows, 64] and
+    s8 uint8 [rows, 4]).  Each writer is a dict or None:
       indexer / main: state fp32 [blocks, ring, 512 | 2048], state_row int64 [rows], norm_w fp32 [128 | 512],
                       optional pool uint8 [pages, stride] + dst int64 [rows] + entries_per_block,
                       optional compact outputs q8, s8 (and rope bf16 [rows,64] for main)
@@ -491,7 +498,7 @@ def cache_writers_fp8(pos, cos_table, sin_table, *, indexer=None, main=None, win
     _require(cos_table.shape == sin_table.shape and cos_table.dim() == 2, "cos/sin tables must both be [max_pos, 32]")
     args = _lib.CacheWriters(pos=pos.data_ptr(), cos_table=cos_table.data_ptr(), sin_table=sin_table.data_ptr(),
                              max_pos=cos_table.size(0), eps=float(eps))
-    args.indexer = _compressor_bundle(indexer, rows, "indexer", 128)
+    args.indexer = _compressor_bundle(indexer, rows, "indexer", 128, fp4=indexer_fp4)
     args.main = _compressor_bundle(main, rows, "main", 512)
     if window is not None:
         y = _f32(window["y"], "window.y", 512)
@@ -500,7 +507,13 @@ def cache_writers_fp8(pos, cos_table, sin_table, *, indexer=None, main=None, win
         fields.update(_pool_fields(window, rows, "window"))
         fields.update(_compact_fields(window, rows, "window", 448, 7, True))
         args.window = _lib.WindowBundle(**fields)
-    check(lib.wuda_cache_writers_fp8(ctypes.byref(args), rows, _ptr(status_word), _stream()))
+    entry = lib.wuda_cache_writers_fp4 if indexer_fp4 else lib.wuda_cache_writers_fp8
+    check(entry(ctypes.byref(args), rows, _ptr(status_word), _stream()))
+
+
+def cache_writers_fp4(pos, cos_table, sin_table, **kw):
+    """cache_writers_fp8 with the indexer compressor in its FP4 form."""
+    cache_writers_fp8(pos, cos_table, sin_table, indexer_fp4=True, **kw)
 
 
 def mqa_compressor_fp8_standalone(cmp_pos, comp_norm, cos_tab, sin_tab, comp_state, comp_state_row,
@@ -560,6 +573,31 @@ def idx_postprocess_fp8(iq, weights, q_pos, rope_cos, rope_sin, q_fp8=None, weig
                                     rope_sin.data_ptr(), rope_cos.size(0), _ptr(weights), q_fp8.data_ptr(),
                                     weights_out.data_ptr(), m, heads, _stream()))
     return q_fp8, weights_out
+
+
+def idx_postprocess(iq, q_pos, rope_cos, rope_sin, iq_fp4=None, iq_sf=None):
+    """Indexer-q post, FP4 form (the reference's idx_postprocess, kernels/idx_post_fp4.cu; device chain
+    include/idx_post_fp4.cuh:79-224): iq bf16 [M, heads, 128] (may be a column slice of the projection output),
+    q_pos int32 [M].  RoPE on the last 64 dims, Hadamard-128, MXFP4.  Returns (iq_fp4 int8 [M, heads, 64] packed
+    e2m1, iq_sf int32 [M, heads] of four exponent bytes): the q / sf_q operands of mqa_logits_fp4_decode."""
+    _require(iq.is_cuda and iq.dtype == torch.bfloat16 and iq.dim() == 3 and iq.size(2) == 128
+             and iq.stride(2) == 1 and iq.stride(1) == 128, "iq must be CUDA bf16 [M, heads, 128] with dense heads")
+    m, heads, _ = iq.shape
+    _require(q_pos.is_cuda and q_pos.is_contiguous() and q_pos.dtype == torch.int32 and q_pos.numel() == m,
+             "q_pos must be contiguous CUDA int32 [M]")
+    _f32(rope_cos, "rope_cos", 32)
+    _f32(rope_sin, "rope_sin", 32)
+    if iq_fp4 is None:
+        iq_fp4 = torch.empty((m, heads, 64), dtype=torch.int8, device=iq.device)
+    if iq_sf is None:
+        iq_sf = torch.empty((m, heads), dtype=torch.int32, device=iq.device)
+    _require(iq_fp4.is_contiguous() and iq_fp4.element_size() == 1 and iq_fp4.numel() == m * heads * 64
+             and iq_sf.is_contiguous() and iq_sf.element_size() == 4 and iq_sf.numel() == m * heads,
+             "outputs must be contiguous 1-byte [M, heads, 64] / 4-byte [M, heads]")
+    check(lib.wuda_index_q_post_fp4(iq.data_ptr(), iq.stride(0), q_pos.data_ptr(), rope_cos.data_ptr(),
+                                    rope_sin.data_ptr(), rope_cos.size(0), iq_fp4.data_ptr(), iq_sf.data_ptr(), m, heads,
+                                    _stream()))
+    return iq_fp4, iq_sf
 
 
 _gemm_scratch = {}
