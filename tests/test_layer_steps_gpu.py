@@ -31,8 +31,10 @@ def check_step(layer, st, m):
     got = dict(idx=cache.idx_pool.cpu().numpy(), cmp=cache.cmp_pool.cpu().numpy(), swa=cache.swa_pool.cpu().numpy())
     # cache writers: the records this step wrote, recomputed from the rings the front GEMM's epilogue filled
     want = {k: v.copy() for k, v in got.items()}
-    oracle.indexer_compressor_fp8(cache.idx_state.cpu().numpy().reshape(-1, ring, 512), rows, pos, w["idx_norm"], w["cos_table"],
-                                  w["sin_table"], pool=want["idx"], dst=st["idx_dst"].cpu().numpy(), epb=cache.entries_per_block["idx"])
+    fp4 = stage.indexer_fp4
+    (oracle.indexer_compressor_fp4 if fp4 else oracle.indexer_compressor_fp8)(
+        cache.idx_state.cpu().numpy().reshape(-1, ring, 512), rows, pos, w["idx_norm"], w["cos_table"], w["sin_table"],
+        pool=want["idx"], dst=st["idx_dst"].cpu().numpy(), epb=cache.entries_per_block["idx"])
     oracle.main_compressor_fp8(cache.main_state.cpu().numpy().reshape(-1, ring, 2048), rows, pos, w["main_norm"], w["cos_table"],
                                w["sin_table"], pool=want["cmp"], dst=st["cmp_dst"].cpu().numpy(), epb=cache.entries_per_block["cmp"])
     oracle.window_kv_fp8(stage.win_y2[:m].cpu().numpy(), pos, w["win_norm"], w["cos_table"], w["sin_table"], pool=want["swa"],
@@ -45,12 +47,21 @@ def check_step(layer, st, m):
     assert np.array_equal(ncmp, (pos + 1) // 4)
     bt, cmp_bt = stage.block_table[:m].cpu().numpy(), stage.cmp_block_table[:m].cpu().numpy()
     logits = stage.logits[:m].cpu().numpy()
-    ref_l = oracle.mqa_logits_fp8(stage.iq_fp8[:m].cpu().numpy(), got["idx"], stage.w_folded[:m].cpu().numpy(), ncmp.reshape(m, 1),
-                                  bt, 1, cache.entries_per_block["idx"], stage.logits_stride)
     valid = np.arange(stage.logits_stride)[None, :] < ncmp[:, None]
+    if fp4:    # codes at the start of the iq buffer, the query's scale words where the folded weights would be
+        heads = stage.w.index_heads
+        q4 = stage.iq_fp8.view(-1)[:m * heads * 64].view(m, heads, 64).cpu().numpy()
+        q_sf = stage.w_folded.view(torch.int32)[:m].cpu().numpy().view(np.uint32)
+        ref_l = oracle.mqa_logits_fp4(q4, q_sf, got["idx"], stage.w64[:m].cpu().numpy(), ncmp, bt, cache.entries_per_block["idx"],
+                                      stage.logits_stride)
+        rel, floor = 1e-4, 1e-5
+    else:
+        ref_l = oracle.mqa_logits_fp8(stage.iq_fp8[:m].cpu().numpy(), got["idx"], stage.w_folded[:m].cpu().numpy(),
+                                      ncmp.reshape(m, 1), bt, 1, cache.entries_per_block["idx"], stage.logits_stride)
+        rel, floor = 1e-2, 1e-4
     if valid.any():
         rms = np.sqrt(np.mean(ref_l[valid].astype(np.float64) ** 2))
-        assert np.all(np.abs(logits[valid] - ref_l[valid]) <= 1e-2 * np.abs(ref_l[valid]) + 1e-4 * rms + 1e-30)
+        assert np.all(np.abs(logits[valid] - ref_l[valid]) <= rel * np.abs(ref_l[valid]) + floor * rms + 1e-30)
     masked = np.where(valid, logits, -np.inf).astype(np.float32)
     ref_pages, _ = oracle.topk(masked, ncmp, cmp_bt, layer.attn.topk, cache.entries_per_block["cmp"])
     got_pages = stage.topk_indices[:m].cpu().numpy()
@@ -65,8 +76,9 @@ def check_step(layer, st, m):
     assert np.all(np.abs(out - ref) <= np.abs(ref).max(axis=-1, keepdims=True) * 2.0 ** -7 + 1e-6)
 
 
-def run_sim(check, native):
-    layer, slots, _ = build_random_layer(BATCH, 1, seed=17, native=native, **SMALL)       # every request at position 0 next
+def run_sim(check, native, indexer_fp4=False):
+    layer, slots, _ = build_random_layer(BATCH, 1, seed=17, native=native, indexer_fp4=indexer_fp4, **SMALL)   # every request at position 0 next
+    assert layer.attn.stage.indexer_fp4 == indexer_fp4
     cache = layer.attn.cache
     g = torch.Generator(device="cuda").manual_seed(42)
     finals = []
@@ -117,3 +129,12 @@ def test_eight_steps_with_slot_reuse_and_a_zero_row_then_the_same_again():
         assert torch.equal(b.contiguous().view(torch.uint8), c.contiguous().view(torch.uint8))
     for a, b in zip(first, second):
         assert torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8))   # byte view: NaN-safe
+
+
+def test_the_same_simulation_with_the_fp4_indexer():
+    """The indexer in its FP4 form (Hadamard + MXFP4 query and keys, block-scaled logits) inside the whole layer: the
+    Python sequence with the stage checks, then the library's own sequence, bit for bit the same."""
+    first = run_sim(check=True, native=False, indexer_fp4=True)
+    second = run_sim(check=False, native=True, indexer_fp4=True)
+    for a, b in zip(first, second):
+        assert torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8))

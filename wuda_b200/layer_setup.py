@@ -43,11 +43,13 @@ def _fp8_weight(g, n, k, device, pow2=True):
 
 
 def build_random_layer(batch, context, topk=2048, rank=0, world=1, tp_link=None, ep_link=None, seed=11,
-                       experts=256, inter=2048, moe_topk=8, device="cuda", peer_wait_ms=2000, native=True, pow2_scales=True):
+                       experts=256, inter=2048, moe_topk=8, device="cuda", peer_wait_ms=2000, native=True, pow2_scales=True,
+                       indexer_fp4=False):
     """Returns (layer, slots, hidden_states): a DecoderLayer whose requests all stand at position context - 1
     (the timed token), the request slots, and bf16 [batch, 4, hidden] residual streams.  world = 2 builds what
     rank `rank` of a tensor-parallel pair holds and needs both links.  pow2_scales: FP8 weight scales are powers
-    of two (as in the reference's checkpoints) and the projections that gain from it apply them in the tensor core."""
+    of two (as in the reference's checkpoints) and the projections that gain from it apply them in the tensor core.
+    indexer_fp4: the indexer pool holds MXFP4 records and the step takes the FP4 forms of the indexer's kernels."""
     if world not in (1, 2) or (world == 2 and (tp_link is None or ep_link is None)):
         raise ValueError("world must be 1, or 2 with both links")
     dev = device
@@ -88,14 +90,18 @@ def build_random_layer(batch, context, topk=2048, rank=0, world=1, tp_link=None,
         attn_sink=sink)
     # ---- caches: every request stands one token before `context`
     pages_per_req = (context // 4 + 63) // 64 + 1
-    cache = KVCacheManager(batch, batch * pages_per_req + batch, pages_per_req, device=dev)
+    cache = KVCacheManager(batch, batch * pages_per_req + batch, pages_per_req, device=dev, indexer_fp8=not indexer_fp4)
     slots = [cache.alloc_request() for _ in range(batch)]
     for s_ in slots:
         cache.advance(s_, context - 1)
     epb = cache.entries_per_block["idx"]
     pool = cache.idx_pool
-    pool[:, :epb * 128] = torch.randint(0, 0x7E, (pool.size(0), epb * 128), generator=g, dtype=torch.uint8, device=dev)
-    pool[:, epb * 128:epb * 132] = (torch.rand(pool.size(0), epb, generator=g, device=dev) * 0.09 + 0.01).view(torch.uint8)
+    if indexer_fp4:   # any e2m1 codes, exponent bytes around one
+        pool[:, :epb * 64] = torch.randint(0, 256, (pool.size(0), epb * 64), generator=g, dtype=torch.uint8, device=dev)
+        pool[:, epb * 64:epb * 68] = torch.randint(120, 131, (pool.size(0), epb * 4), generator=g, dtype=torch.uint8, device=dev)
+    else:
+        pool[:, :epb * 128] = torch.randint(0, 0x7E, (pool.size(0), epb * 128), generator=g, dtype=torch.uint8, device=dev)
+        pool[:, epb * 128:epb * 132] = (torch.rand(pool.size(0), epb, generator=g, device=dev) * 0.09 + 0.01).view(torch.uint8)
     cache.main_state.normal_(generator=g)
     cache.idx_state.normal_(generator=g)
     for i, name in enumerate(("swa", "cmp")):   # attention caches: random finite records instead of a fresh pool's zeros
