@@ -140,3 +140,23 @@ def test_merged_q_projection_call_of_decode_step(wuda):
                                           sin.cpu().numpy())
     assert np.array_equal(win_q8.cpu().numpy(), oq) and np.array_equal(win_s8.cpu().numpy(), os_)
     assert np.array_equal(win_rope.cpu().view(torch.int16).numpy().view(np.uint16), orope)
+    # the same call in the indexer's FP4 form: Hadamard + MXFP4 query, FP4 compressor records into a pool
+    epb = 64
+    pool = torch.full((2, epb * 68), 0xA5, dtype=torch.uint8, device="cuda")
+    dst = torch.where((pos + 1) % 4 == 0, torch.arange(m, device="cuda") * 3, torch.full_like(pos, -1))
+    rets4 = shims.wq_b_proj_gemm_merged(
+        xq, xq_sf, w8, w_sf, q_pos, cos, sin, head_ssq=None, enable_ssq=False, mock_post=False, cmp_pos=pos, idx_norm=idx_norm,
+        cos_tab=cos, sin_tab=sin, idx_state=idx_state, idx_state_row=state_row, state_ring_entries=8, idx_cache=pool,
+        idx_dst=dst, idx_entries_per_block=epb, indexer_fp8=False, pdl=True)
+    torch.cuda.synchronize()
+    iq4, iq4_sf = rets4[1], rets4[2]
+    assert iq4.dtype == torch.int8 and tuple(iq4.shape) == (m, 64, 64) and iq4_sf.dtype == torch.int32
+    y_idx = y_all[:, :8192].cpu().view(torch.int16).numpy().view(np.uint16).reshape(m, 64, 128)
+    oq4, osf = oracle.index_q_post_fp4(y_idx, q_pos.cpu().numpy(), cos.cpu().numpy(), sin.cpu().numpy())
+    assert np.array_equal(iq4.view(torch.uint8).cpu().numpy(), oq4)
+    assert np.array_equal(iq4_sf.cpu().numpy().view(np.uint32), osf)
+    want = np.full((2, epb * 68), 0xA5, np.uint8)
+    oracle.indexer_compressor_fp4(idx_state.cpu().numpy(), state_row.cpu().numpy(), pos.cpu().numpy(), idx_norm.cpu().numpy(),
+                                  cos.cpu().numpy(), sin.cpu().numpy(), pool=want, dst=dst.cpu().numpy(), epb=epb)
+    got_pool = pool.cpu().numpy()
+    assert (want != 0xA5).any() and np.mean(got_pool == want) >= 0.999

@@ -8,6 +8,7 @@ because consecutive launches use different weight buffers that together exceed L
     python -m wuda_b200.benchmarks gemm_nvfp4
     python -m wuda_b200.benchmarks norm_rope_quant
     python -m wuda_b200.benchmarks csa_chain                       (layer launch of the indexer half-step)
+    python -m wuda_b200.benchmarks csa_chain_fp4                   (the same with the indexer in its FP4 form)
     python -m wuda_b200.benchmarks csa_chain_launches              (three eager steps, for an ncu launch list)
     python -m wuda_b200.benchmarks attention_half_layer            (every built stage of the half-layer, one graph)
     python -m wuda_b200.benchmarks attention_half_layer_launches   (three eager passes, for an ncu launch list)
@@ -210,10 +211,11 @@ def tp2():
     dist.destroy_process_group()
 
 
-def csa_chain(batch=64, context=32768, topk=2048, reps=30, launches_only=0):
+def csa_chain(batch=64, context=32768, topk=2048, reps=30, launches_only=0, indexer_fp4=False):
     """The layer launch of the indexer half of a decode step (wuda_csa_decode_step, seven kernels in
     one CUDA graph) at the model's geometry: q_lora 1536, 64 index heads, 128 main heads, `batch`
-    requests at `context` tokens.  L2 is flushed before every timed replay."""
+    requests at `context` tokens.  L2 is flushed before every timed replay.  indexer_fp4: the indexer
+    in its FP4 form (Hadamard + MXFP4 query and keys, 68-byte records)."""
     from wuda_b200.decode import CsaDecodeStage, CsaWeights
     from wuda_b200.kv_cache import KVCacheManager
     hbm, tf, kind = peaks()
@@ -229,15 +231,19 @@ def csa_chain(batch=64, context=32768, topk=2048, reps=30, launches_only=0):
                          torch.rand(512, generator=g, device=dev) + 0.5, torch.cos(ang).contiguous(),
                          torch.sin(ang).contiguous(), index_heads=ih, main_heads=mh)
     pages_per_req = (context // 4 + 63) // 64 + 1
-    cache = KVCacheManager(batch, batch * pages_per_req + batch, pages_per_req, device=dev)
+    cache = KVCacheManager(batch, batch * pages_per_req + batch, pages_per_req, device=dev, indexer_fp8=not indexer_fp4)
     stage = CsaDecodeStage(weights, cache, batch, topk=topk)
     slots = [cache.alloc_request() for _ in range(batch)]
     for s in slots:
         cache.advance(s, context - 1)               # the timed token is the one at position context - 1
     epb = cache.entries_per_block["idx"]
     pool = cache.idx_pool
-    pool[:, :epb * 128] = torch.randint(0, 0x7E, (pool.size(0), epb * 128), generator=g, dtype=torch.uint8, device=dev)
-    pool[:, epb * 128:epb * 132] = (torch.rand(pool.size(0), epb, generator=g, device=dev) * 0.09 + 0.01).view(torch.uint8)
+    if indexer_fp4:
+        pool[:, :epb * 64] = torch.randint(0, 256, (pool.size(0), epb * 64), generator=g, dtype=torch.uint8, device=dev)
+        pool[:, epb * 64:epb * 68] = torch.randint(120, 131, (pool.size(0), epb * 4), generator=g, dtype=torch.uint8, device=dev)
+    else:
+        pool[:, :epb * 128] = torch.randint(0, 0x7E, (pool.size(0), epb * 128), generator=g, dtype=torch.uint8, device=dev)
+        pool[:, epb * 128:epb * 132] = (torch.rand(pool.size(0), epb, generator=g, device=dev) * 0.09 + 0.01).view(torch.uint8)
     cache.main_state.normal_(generator=g)
     cache.idx_state.normal_(generator=g)
     st = stage.prepare(slots)
@@ -267,10 +273,10 @@ def csa_chain(batch=64, context=32768, topk=2048, reps=30, launches_only=0):
     stage.check_status()
     us = total / reps
     ncmp = int(stage.n_compressed[0])
-    bytes_step = (n_total * q_lora + batch * ncmp * 132 + 2 * batch * ncmp * 4 + batch * n_total * 2 * 2
+    bytes_step = (n_total * q_lora + batch * ncmp * (68 if indexer_fp4 else 132) + 2 * batch * ncmp * 4 + batch * n_total * 2 * 2
                   + batch * mh * 512 * 2)
-    print("indexer half of a decode step: batch %d, context %d (%d indexer entries / request), top-%d" %
-          (batch, context, ncmp, topk))
+    print("indexer half of a decode step%s: batch %d, context %d (%d indexer entries / request), top-%d" %
+          (" (FP4 indexer)" if indexer_fp4 else "", batch, context, ncmp, topk))
     print("  %.1f us per step (L2 flushed before each) = %.0f tokens/s for this stage chain; %.1f MB algorithmic "
           "-> %.0f GB/s = %.2f of %s HBM peak" % (us, batch / us * 1e6, bytes_step / 1e6, bytes_step / us / 1e3,
                                                    bytes_step / us / 1e3 / hbm, kind))
@@ -782,7 +788,8 @@ def one(kind, m, n, k, launches=5):
 
 KINDS = {"topk": topk, "gemm_fp8": gemm_fp8, "gemm_fp8_pow2": lambda: gemm_fp8(pow2=True), "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(batches=(64,), contexts=(32768,), launches_only=3),
          "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(32,), launches_only=3),
-         "csa_chain": csa_chain, "csa_chain_launches": lambda: csa_chain(launches_only=3),
+         "csa_chain": csa_chain, "csa_chain_fp4": lambda: csa_chain(indexer_fp4=True),
+         "csa_chain_launches": lambda: csa_chain(launches_only=3),
          "attention_half_layer": attention_half_layer, "moe_experts": moe_experts,
          "layer": layer, "layer_tp2": layer_tp2, "layer_launches": lambda: layer_leg(launches_only=2),
          "moe_experts_launches": lambda: moe_experts(launches_only=2),

@@ -160,10 +160,11 @@ def wq_b_proj_gemm_merged(x_fp8, x_sf, w_fp8, w_sf, q_pos, rope_cos, rope_sin, h
     the q RMSNorm + quantisation producer (q_y bf16 [M, 1536] strided, q_norm_w fp32 -> fills x_fp8 / x_sf), the FP8
     indexer-q post (indexer_fp8=True: e4m3 [M, 64, 128] and iq_weights times the row scale), the indexer compressor
     and the window-KV writer into their pools.  Returns [y bf16 [M, n_main] (a column view of the projection output),
-    iq, iq_weights_folded] (+ [win_q8, win_s8, win_rope] when the window writer ran without a pool).  Only the FP8
-    indexer form is implemented (indexer_fp8=True); head_ssq / enable_ssq / mock_post select parts of the reference's
-    FP4 path and are accepted and ignored.  Up to five launches where the reference has one."""
-    ops._require(indexer_fp8, "only the FP8 indexer form (indexer_fp8=True) is implemented")
+    iq, iq_weights_folded] (+ [win_q8, win_s8, win_rope] when the window writer ran without a pool).  With
+    indexer_fp8=False the indexer takes its FP4 form: the indexer-q post runs the Hadamard transform and emits packed
+    e2m1 codes int8 [M, 64, 64] with their scale words int32 [M, 64] (returned in the place of iq and the folded
+    weights; iq_weights is not used), and the compressor writes 68-byte MXFP4 records.  head_ssq / enable_ssq /
+    mock_post are accepted and ignored.  Up to five launches where the reference has one."""
     m = x_fp8.size(0)
     dev = x_fp8.device
     if q_y is not None:      # producer: RMSNorm(q_norm_w) + power-of-two quantisation into the caller's x_fp8 / x_sf
@@ -176,8 +177,12 @@ def wq_b_proj_gemm_merged(x_fp8, x_sf, w_fp8, w_sf, q_pos, rope_cos, rope_sin, h
     ws = _cached_weight_scales(w_sf)
     y_all = ops.fp8_gemm(x_fp8.view(torch.float8_e4m3fn), xs, w_fp8.view(torch.float8_e4m3fn), ws)
     n_total = y_all.size(1)
-    iq, wf = ops.idx_postprocess_fp8(y_all[:, :N_INDEX].unflatten(-1, (64, 128)), iq_weights, q_pos, rope_cos, rope_sin,
-                                     q_fp8=iq_dst, weights_out=iq_dst_sf)
+    if indexer_fp8:
+        iq, wf = ops.idx_postprocess_fp8(y_all[:, :N_INDEX].unflatten(-1, (64, 128)), iq_weights, q_pos, rope_cos, rope_sin,
+                                         q_fp8=iq_dst, weights_out=iq_dst_sf)
+    else:
+        iq, wf = ops.idx_postprocess(y_all[:, :N_INDEX].unflatten(-1, (64, 128)), q_pos, rope_cos, rope_sin, iq_fp4=iq_dst,
+                                     iq_sf=iq_dst_sf)
     rets = [y_all[:, N_INDEX:], iq, wf]
     indexer = window = None
     if idx_state is not None:
@@ -193,6 +198,6 @@ def wq_b_proj_gemm_merged(x_fp8, x_sf, w_fp8, w_sf, q_pos, rope_cos, rope_sin, h
                           rope=torch.empty(m, 64, dtype=torch.bfloat16, device=dev))
             rets += [window["q8"], window["s8"], window["rope"]]
     if indexer is not None or window is not None:
-        ops.cache_writers_fp8(cmp_pos, cos_tab, sin_tab, indexer=indexer, window=window)
+        ops.cache_writers_fp8(cmp_pos, cos_tab, sin_tab, indexer=indexer, window=window, indexer_fp4=not indexer_fp8)
     del n_total
     return rets
