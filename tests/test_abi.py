@@ -93,3 +93,18 @@ def test_benchmark_kinds_are_registered_and_documented():
     documented = set(re.findall(r"wuda_b200\.benchmarks (\w+)", benchmarks.__doc__)) - {"one"}
     assert documented == set(benchmarks.KINDS), documented ^ set(benchmarks.KINDS)
     assert all(callable(f) for f in benchmarks.KINDS.values())
+
+
+def test_the_documented_build_command_does_not_need_the_library():
+    """`python -m wuda_b200.build` must be runnable on a tree whose library is missing or older than the ctypes table:
+    the package's __init__ leaves the library alone for that one command (here: an up-to-date tree, so nothing is
+    compiled; with the library's path pointed at a file that does not exist the import itself must still succeed)."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import sys; sys.orig_argv = ['python', '-m', 'wuda_b200.build']; import wuda_b200; "
+            "assert not hasattr(wuda_b200, 'lib'); print('ok')")
+    out = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and out.stdout.strip() == "ok", out.stderr
+    out = subprocess.run([sys.executable, "-m", "wuda_b200.build"], cwd=root, capture_output=True, text=True, timeout=1500)
+    assert out.returncode == 0, out.stderr
