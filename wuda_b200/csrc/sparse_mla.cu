@@ -51,8 +51,9 @@ constexpr int kPass = 32;          // keys the producer warps convert at a time 
 constexpr int kHalf = 256;         // output dims per CTA
 constexpr int kSoftmaxWarps = 4;
 constexpr int kProducerWarps = 8;
-constexpr int kIssuerWarp = kSoftmaxWarps + kProducerWarps;
-constexpr int kThreads = (kIssuerWarp + 1) * 32;
+constexpr int kIssuerWarp = kSoftmaxWarps + kProducerWarps;   // two warps issue Q K^T, of the even and of the odd blocks
+constexpr int kIssuerWarpPV = kIssuerWarp + 2;                 // issues P V
+constexpr int kThreads = (kIssuerWarpPV + 1) * 32;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kAhead = 3;             // passes whose records are in flight ahead of the one being stored
 constexpr int kMaxSplits = 32;        // CTAs that may share one request's keys (per output half)
@@ -77,7 +78,7 @@ constexpr uint32_t kOffOth = kOffOwn + kOwnStages * kHalfStageBytes;
 constexpr uint32_t kOffP = kOffOth + kOthStages * kHalfStageBytes;
 constexpr uint32_t kOffValid = kOffP + 2 * kPBytes;     // kOwnStages x 16 bytes: per pass and producer warp, 4 valid bits
 constexpr uint32_t kOffBars = kOffValid + kOwnStages * 16;
-constexpr uint32_t kNumBars = 2 * kOwnStages + kOthStages + 6;
+constexpr uint32_t kNumBars = 2 * kOwnStages + kOthStages + 8;
 constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
 
@@ -223,7 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
     // per stage: key block stored / its weighted sum complete; scores complete / read; per
     // probability buffer: probabilities stored / weighted sum complete
     const uint32_t k_full = bars, own_free = bars + kOwnStages * 8, oth_free = bars + 2 * kOwnStages * 8,
-                   s_full = oth_free + kOthStages * 8, s_empty = s_full + 8, p_full = s_full + 16, pv_done = s_full + 32;
+                   s_full = oth_free + kOthStages * 8, s_empty = s_full + 16, p_full = s_full + 32, pv_done = s_full + 48;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + kOffMisc + 4);
     volatile uint8_t* valid_bytes = base_ptr + kOffValid;
@@ -239,8 +240,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
             mbar_init(own_free + i * 8, 1);
         }
         for (int i = 0; i < kOthStages; ++i) mbar_init(oth_free + i * 8, 1);
-        mbar_init(s_full, 1);
-        mbar_init(s_empty, kSoftmaxWarps);
+        for (int i = 0; i < 2; ++i) {   // one pair per score issuer (blocks of even / odd number)
+            mbar_init(s_full + i * 8, 1);
+            mbar_init(s_empty + i * 8, kSoftmaxWarps);
+        }
         for (int i = 0; i < 2; ++i) {
             mbar_init(p_full + i * 8, kSoftmaxWarps);
             mbar_init(pv_done + i * 8, 1);
@@ -348,17 +351,23 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         }
         if (bad && p.status) atomicCAS(p.status, 0, static_cast<int>(kDevBadPageIndex));
         if (clamped && p.status) atomicCAS(p.status, 0, static_cast<int>(kDevMlaScaleRange));
-    } else if (warp == kIssuerWarp) {
-        // ------------------------------------------------------------ MMA issuer
+    } else if (warp == kIssuerWarp || warp == kIssuerWarp + 1) {
+        // ------------------------------------------------------------ score issuers
+        // A block's 32 MMAs keep their issuing thread busy for longer than they keep the tensor pipe, and the commit,
+        // the loop and the two waits behind them cost that thread as much again while the other warps of its scheduler
+        // compute; so two threads take the blocks alternately: one is already waiting for the score tile to be read
+        // when the other's MMAs retire.  Each has its own pair of barriers, so that it sees every phase of the ones it
+        // waits on.
+        const int me = warp - kIssuerWarp;
         constexpr uint32_t idesc_qk = umma_idesc(kRows, kBlock, 0, 0);     // fp16 operands
-        constexpr uint32_t idesc_pv = umma_idesc_b_mn(kRows, kHalf, 0, 0);
         bool alive = true;
-        for (int j = 0; j <= blocks && alive; ++j) {
-            if (j < blocks) {
+        for (int j = me; j < blocks && alive; j += 2) {
+            {
                 const int s = j % kOwnStages, t = j % kOthStages;
                 alive = mbar_wait_lane0(k_full + s * 8, (j / kOwnStages) & 1u, abort_flag, p.status, kDevTimeoutMlaKeys);
                 if (alive && j >= 1)
-                    alive = mbar_wait_lane0(s_empty, (j - 1) & 1u, abort_flag, p.status, kDevTimeoutMlaScoresRead);
+                    alive = mbar_wait_lane0(s_empty + (me ^ 1) * 8, ((j - 1) >> 1) & 1u, abort_flag, p.status,
+                                            kDevTimeoutMlaScoresRead);   // the block before, the other issuer's
                 if (!alive) break;
                 tc_fence_after();
                 if (lane == 0) {
@@ -377,28 +386,33 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
                                 umma_f16(tmem_base + kColS, q_desc + (((c - kQTmemChunks) * kQChunk + k * 32) >> 4), k_desc,
                                          idesc_qk, 1u);
                         }
-                    umma_commit(s_full);
-                    umma_commit(oth_free + t * 8);   // the half of the key block only the scores needed
+                    umma_commit(s_full + me * 8);   // (the other half's ring stage is released by the softmax, which sees this commit)
                 }
                 __syncwarp();
             }
-            if (j >= 1) {
-                const int t = (j - 1) & 1, s = (j - 1) % kOwnStages;
-                alive = mbar_wait_lane0(p_full + t * 8, ((j - 1) >> 1) & 1u, abort_flag, p.status, kDevTimeoutMlaProbs);
-                if (!alive) break;
-                tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t p_addr = base + kOffP + t * kPBytes;
-                    const uint32_t v_addr = base + kOffOwn + s * kHalfStageBytes;
+        }
+    } else if (warp == kIssuerWarpPV) {
+        // ------------------------------------------------------------ weighted-sum issuer
+        // A thread issues an MMA about every hundred cycles whatever its size; with the weighted sums on a thread of
+        // their own the score issuer goes straight on to the next block.
+        constexpr uint32_t idesc_pv = umma_idesc_b_mn(kRows, kHalf, 0, 0);
+        bool alive = true;
+        for (int j = 0; j < blocks && alive; ++j) {
+            const int t = j & 1, s = j % kOwnStages;
+            alive = mbar_wait_lane0(p_full + t * 8, (j >> 1) & 1u, abort_flag, p.status, kDevTimeoutMlaProbs);
+            if (!alive) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t p_addr = base + kOffP + t * kPBytes;
+                const uint32_t v_addr = base + kOffOwn + s * kHalfStageBytes;
 #pragma unroll
-                    for (int k = 0; k < kBlock / 16; ++k)   // 16 keys each
-                        umma_f16(tmem_base + kColO, umma_smem_desc_noswz(p_addr + k * 2 * kPPiece, kPPiece, 128),
-                                 umma_smem_desc_mn_sw128(v_addr + k * 16 * 128, kKChunk), idesc_pv, (j - 1 > 0) || k > 0);
-                    umma_commit(pv_done + t * 8);   // the probability buffer and the accumulator
-                    umma_commit(own_free + s * 8);  // this half of the key block
-                }
-                __syncwarp();
+                for (int k = 0; k < kBlock / 16; ++k)   // 16 keys each
+                    umma_f16(tmem_base + kColO, umma_smem_desc_noswz(p_addr + k * 2 * kPPiece, kPPiece, 128),
+                             umma_smem_desc_mn_sw128(v_addr + k * 16 * 128, kKChunk), idesc_pv, j > 0 || k > 0);
+                umma_commit(pv_done + t * 8);   // the probability buffer and the accumulator
+                umma_commit(own_free + s * 8);  // this half of the key block
             }
+            __syncwarp();
         }
     } else {
         // ------------------------------------------------------------ softmax and output
@@ -408,7 +422,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
         bool alive = true;
         for (int j = 0; j < blocks && alive; ++j) {
             const int s = j & 1, stage = j % kOwnStages;
-            alive = mbar_wait_warp(s_full, j & 1u, abort_flag, p.status, kDevTimeoutMlaScores);
+            alive = mbar_wait_warp(s_full + (j & 1) * 8, (j >> 1) & 1u, abort_flag, p.status, kDevTimeoutMlaScores);
+            // the scores are complete: the half of the key block that only they needed may be refilled (a second
+            // tcgen05.commit would hold the issuing thread for several hundred cycles)
+            if (alive && warp == 0 && lane == 0) mbar_arrive(oth_free + (j % kOthStages) * 8);
             if (!alive) break;
             tc_fence_after();
             // the block's valid bits were published before its keys were announced, and its stage is
@@ -422,7 +439,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(s_empty);
+                if (lane == 0) mbar_arrive(s_empty + (j & 1) * 8);
             }
             // A block whose 64 keys all exist (every block but a request's last) needs no masks: the maximum is taken
             // over the raw scores and the scale rides in the exponent's multiply-add.  Otherwise missing keys become
