@@ -28,8 +28,10 @@
 //               128-byte-swizzled operand layout.
 //               The same bytes serve as the K-major operand of Q K^T and as the MN-major
 //               operand of P V.
-//   warp 12     issues the tcgen05 MMAs: Q K^T of block j, then P V of block j-1, so that the
-//               tensor pipe works on one while the softmax works on the other.
+//   warps 12-13 issue Q K^T, of the even and of the odd blocks: a thread gets one MMA out about every hundred
+//               cycles and spends as long again on the commit, the loop and its waits, so one of the two is
+//               already waiting for the score tile when the other's MMAs retire;
+//   warp 14     issues P V of a block as soon as its probabilities are stored.
 // Every wait is bounded; a wait that runs out leaves a code in the status word and the CTA
 // exits normally.
 #include <cuda_bf16.h>
@@ -90,6 +92,7 @@ struct Pool {
     const uint8_t* data;
     int64_t stride;
     int pages, epb;
+    int epb_shift;            // log2(epb) when epb is a power of two, else -1
     const int32_t* indices;   // [batch, capacity]
     const int32_t* lengths;   // [batch]
     int capacity;
@@ -121,11 +124,9 @@ constexpr int kScaleExpLo = -15, kScaleExpHi = 7;
 
 // 2^E as a pair of fp16, E = byte - 127 clamped to the exact range; `*clamped` is raised when it was
 __device__ __forceinline__ uint32_t scale_f16x2(uint32_t byte, bool* clamped) {
-    int e = static_cast<int>(byte) - 127;
-    if (e < kScaleExpLo || e > kScaleExpHi) {
-        *clamped = true;
-        e = e < kScaleExpLo ? kScaleExpLo : kScaleExpHi;
-    }
+    const int raw = static_cast<int>(byte) - 127;
+    const int e = min(max(raw, kScaleExpLo), kScaleExpHi);
+    *clamped |= e != raw;
     const uint32_t h = e >= -14 ? static_cast<uint32_t>(e + 15) << 10 : 0x0200u;   // 2^-15 is subnormal
     return h | (h << 16);
 }
@@ -177,7 +178,7 @@ __device__ __forceinline__ void fetch_key(const Params& p, int g, int n_swa, int
     r.valid = 0;
     if (idx < 0) return;
     const Pool& pool = g < n_swa ? p.swa : p.cmp;
-    const int page = idx / pool.epb, off = idx - page * pool.epb;
+    const int page = pool.epb_shift >= 0 ? idx >> pool.epb_shift : idx / pool.epb, off = idx - page * pool.epb;
     if (page >= pool.pages) {
         *bad = true;
         return;
@@ -236,7 +237,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int i = 0; i < kOwnStages; ++i) {
-            mbar_init(k_full + i * 8, kProducerWarps * (kBlock / kPass));
+            mbar_init(k_full + i * 8, kProducerWarps);   // every producer warp, once per block
             mbar_init(own_free + i * 8, 1);
         }
         for (int i = 0; i < kOthStages; ++i) mbar_init(oth_free + i * 8, 1);
@@ -340,12 +341,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_kernel(const Params p)
                 store_key(half == 0 ? own_addr : oth_addr, half == 0 ? oth_addr : own_addr, sub * kPass + row, piece, ring[u],
                           &clamped);
                 const uint32_t bits = __ballot_sync(0xffffffffu, ring[u].valid != 0);
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
+                if (lane == 0)
                     valid_bytes[s * 16 + sub * 8 + pw] = static_cast<uint8_t>(
                         (bits & 1u) | ((bits >> 7) & 2u) | ((bits >> 14) & 4u) | ((bits >> 21) & 8u));
-                    mbar_arrive(k_full + s * 8);
+                if (sub == kPasses - 1) {   // the block's last pass: one fence and one arrival cover both passes' stores
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(k_full + s * 8);
                 }
             }
         }
@@ -633,7 +635,7 @@ static int check_pool(const char* name, const void* data, int64_t stride, int pa
     out->capacity = capacity;
     if (capacity == 0) {
         out->data = nullptr, out->indices = nullptr, out->lengths = nullptr;
-        out->stride = 0, out->pages = 0, out->epb = 1;
+        out->stride = 0, out->pages = 0, out->epb = 1, out->epb_shift = 0;
         return WUDA_OK;
     }
     WUDA_REQUIRE(data && indices && lengths, "%s pool, indices and lengths must not be NULL when its capacity is > 0", name);
@@ -646,6 +648,9 @@ static int check_pool(const char* name, const void* data, int64_t stride, int pa
     out->stride = stride;
     out->pages = pages;
     out->epb = epb;
+    out->epb_shift = -1;
+    for (int sft = 0; sft < 24; ++sft)
+        if ((1 << sft) == epb) out->epb_shift = sft;
     out->indices = indices;
     out->lengths = lengths;
     return WUDA_OK;
