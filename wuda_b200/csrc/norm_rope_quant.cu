@@ -166,7 +166,7 @@ struct RopeParams {
     int tokens, heads, head_dim, rope_dim, max_pos, inverse, pow2;
 };
 
-__global__ void __launch_bounds__(1024, 1) rope_quant_kernel(const RopeParams p) {
+__global__ void __launch_bounds__(1024) rope_quant_kernel(const RopeParams p) {
     pdl_launch_dependents();
     pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     const int t = blockIdx.x;
@@ -181,28 +181,39 @@ __global__ void __launch_bounds__(1024, 1) rope_quant_kernel(const RopeParams p)
     // every thread of a 16-thread quantisation group runs the same number of iterations
     // (width is a multiple of 128), so the shuffles inside quant_store8 are convergent
     // (blockIdx.y splits a token's chunks over several CTAs when there are few tokens)
-    for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < chunks; ch += blockDim.x * gridDim.y) {
-        float v[8];
-        unpack8(*reinterpret_cast<const uint4*>(x + 8 * ch), v);
-        const int in_head = (8 * ch) % p.head_dim;
-        if (in_head >= nope) {
-            const int pair0 = (in_head - nope) >> 1;
+    // four 16-byte loads of a thread are in flight before the first is used: the kernel is a few MB of latency
+    const int stride = blockDim.x * gridDim.y;
+    for (int ch0 = blockIdx.y * blockDim.x + threadIdx.x; ch0 < chunks; ch0 += 4 * stride) {
+        uint4 raw[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float c = cs[pair0 + i];
-                const float s = p.inverse ? -sn[pair0 + i] : sn[pair0 + i];
-                const float re = v[2 * i], im = v[2 * i + 1];
-                // unfused, as a complex multiply in fp32 (no FMA contraction)
-                v[2 * i] = bf16_round(__fsub_rn(__fmul_rn(re, c), __fmul_rn(im, s)));
-                v[2 * i + 1] = bf16_round(__fadd_rn(__fmul_rn(re, s), __fmul_rn(im, c)));
+        for (int u = 0; u < 4; ++u)
+            raw[u] = ch0 + u * stride < chunks ? *reinterpret_cast<const uint4*>(x + 8 * (ch0 + u * stride)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int ch = ch0 + u * stride;
+            if (ch >= chunks) break;                 // uniform over a 16-thread group
+            float v[8];
+            unpack8(raw[u], v);
+            const int in_head = (8 * ch) % p.head_dim;
+            if (in_head >= nope) {
+                const int pair0 = (in_head - nope) >> 1;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float c = cs[pair0 + i];
+                    const float s = p.inverse ? -sn[pair0 + i] : sn[pair0 + i];
+                    const float re = v[2 * i], im = v[2 * i + 1];
+                    // unfused, as a complex multiply in fp32 (no FMA contraction)
+                    v[2 * i] = bf16_round(__fsub_rn(__fmul_rn(re, c), __fmul_rn(im, s)));
+                    v[2 * i + 1] = bf16_round(__fadd_rn(__fmul_rn(re, s), __fmul_rn(im, c)));
+                }
             }
+            const int64_t o = static_cast<int64_t>(t) * width + 8 * ch;
+            if (p.y_bf16) *reinterpret_cast<uint4*>(p.y_bf16 + o) = pack8(v);
+            if (p.y_fp8)
+                quant_store8(v, p.pow2, p.y_fp8 + o,
+                             p.y_scales ? p.y_scales + static_cast<int64_t>(t) * (width >> 7) + (ch >> 4) : nullptr,
+                             (ch & 15) == 0);
         }
-        const int64_t o = static_cast<int64_t>(t) * width + 8 * ch;
-        if (p.y_bf16) *reinterpret_cast<uint4*>(p.y_bf16 + o) = pack8(v);
-        if (p.y_fp8)
-            quant_store8(v, p.pow2, p.y_fp8 + o,
-                         p.y_scales ? p.y_scales + static_cast<int64_t>(t) * (width >> 7) + (ch >> 4) : nullptr,
-                         (ch & 15) == 0);
     }
 }
 
@@ -318,13 +329,13 @@ extern "C" int wuda_rope_quant_fp8(const void* x_bf16, const int64_t* positions,
     p.inverse = inverse;
     p.pow2 = scale_mode;
     const int chunks = heads * head_dim / 8;
-    int threads = chunks < 1024 ? (chunks + 31) / 32 * 32 : 1024;
-    // keep whole 16-thread groups in step: the per-thread iteration count must be equal inside a group
-    // few tokens: cut each token's row over several CTAs (a quantisation group is 16 consecutive threads, so any
-    // multiple of the block size is a valid cut)
+    // CTAs of 256 threads, each thread four 16-byte chunks per round; a token's row is cut over as many CTAs as keep
+    // the whole launch within one resident wave (a quantisation group is 16 consecutive threads, so any multiple of
+    // the block size is a valid cut, and whole 16-thread groups stay in step)
+    const int threads = chunks < 256 ? (chunks + 31) / 32 * 32 : 256;
     int splits = 1;
-    const int passes = (chunks + threads - 1) / threads;
-    while (splits < passes && tokens * splits < 296) splits *= 2;
+    const int rounds = (chunks + 4 * threads - 1) / (4 * threads);
+    while (splits < rounds && tokens * splits * 2 <= 5 * 148) splits *= 2;
     WUDA_CUDA(launch_pdl(rope_quant_kernel, dim3(dim3(tokens, splits)), dim3(threads), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
