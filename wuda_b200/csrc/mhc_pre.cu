@@ -42,7 +42,8 @@ constexpr int kKBlocks = kSlice / 64;    // 128-byte K blocks per slice
 constexpr int kXBlockBytes = kMixTile * 128, kWBlockBytes = kMixN * 128;
 constexpr int kMixSmemBytes = kKBlocks * (kXBlockBytes + kWBlockBytes) + 64 + 1024;
 constexpr int kMixTmemCols = 128;
-constexpr int kFinishThreads = 256;
+constexpr int kFinishThreads = 256;              // the eight warps that collapse, normalise and quantise a token's row
+constexpr int kFinishLaunch = kFinishThreads + 32;   // plus one warp for the post gates and the Sinkhorn iterations
 constexpr int kSinkhornIters = 20;
 
 struct Params {
@@ -285,7 +286,10 @@ __global__ void __launch_bounds__(128) mhc_tail_kernel(const float* mix, const f
     post_and_comb(folded, lane, scale, base, hc_eps, post + t * kStreams, comb + t * kStreams * kStreams);
 }
 
-__global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p) {
+// barrier of the eight row warps alone (the ninth warp is busy with the Sinkhorn iterations or gone)
+__device__ __forceinline__ void row_warps_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kFinishThreads) : "memory"); }
+
+__global__ void __launch_bounds__(kFinishLaunch) mhc_pre_finish_kernel(Params p) {
     pdl_launch_dependents();
     pdl_wait();   // nothing of global memory is touched before the kernel ahead has finished
     __shared__ float mix[kPart];
@@ -294,7 +298,8 @@ __global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int kMaxVec = 4;                       // hidden <= 4 * 256 * 8 = 8192
-    const int vectors = (p.collapsed || p.normed || p.x_fp8) ? p.hidden / 8 : 0;
+    const bool row_warp = threadIdx.x < kFinishThreads;
+    const int vectors = (row_warp && (p.collapsed || p.normed || p.x_fp8)) ? p.hidden / 8 : 0;
     // the token's four rows are requested first: their latency hides behind the slice sums, the gates and the
     // Sinkhorn iterations, none of which needs them
     uint4 raw[kMaxVec][kStreams];
@@ -324,18 +329,24 @@ __global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p
         mix[threadIdx.x] = s;
     }
     __syncthreads();
-    if (warp == 0) {
+    // The collapse needs the four pre gates only; the post gates and the Sinkhorn-normalised comb matrix - twenty
+    // rounds of shuffles and divisions that nothing in this kernel reads - are the ninth warp's, beside the row work.
+    if (warp == 0 || !row_warp) {
         const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(mix[kMix], static_cast<float>(kStreams * p.hidden)) + p.rms_eps));
-        if (lane < kStreams) {
-            const float v = sigmoid(mix[lane] * r * p.scale[0] + p.base[lane]) + p.hc_eps;
-            pre_s[lane] = v;
-            if (p.pre) p.pre[t * kStreams + lane] = v;
+        if (row_warp) {
+            if (lane < kStreams) {
+                const float v = sigmoid(mix[lane] * r * p.scale[0] + p.base[lane]) + p.hc_eps;
+                pre_s[lane] = v;
+                if (p.pre) p.pre[t * kStreams + lane] = v;
+            }
+            if (p.mix_out && lane < kMix) p.mix_out[t * kMix + lane] = mix[lane] * r;
+        } else {
+            post_and_comb(lane < kMix ? mix[lane] * r : 0.f, lane, p.scale, p.base, p.hc_eps,
+                          p.post ? p.post + t * kStreams : nullptr, p.comb ? p.comb + t * kStreams * kStreams : nullptr);
         }
-        if (p.mix_out && lane < kMix) p.mix_out[t * kMix + lane] = mix[lane] * r;
-        post_and_comb(lane < kMix ? mix[lane] * r : 0.f, lane, p.scale, p.base, p.hc_eps, p.post ? p.post + t * kStreams : nullptr,
-                      p.comb ? p.comb + t * kStreams * kStreams : nullptr);
     }
-    __syncthreads();
+    if (!row_warp) return;
+    row_warps_sync();
     if (!p.collapsed && !p.normed && !p.x_fp8) return;
 
     // collapse: a thread owns the 8-value vectors tid, tid + 256, ..; a 128-block of the row is 16
@@ -379,7 +390,7 @@ __global__ void __launch_bounds__(kFinishThreads) mhc_pre_finish_kernel(Params p
     if (!p.normed && !p.x_fp8) return;
     ss = warp_sum(ss);
     if (lane == 0) warp_ss[warp] = ss;
-    __syncthreads();
+    row_warps_sync();
     float total = 0.f;
 #pragma unroll
     for (int i = 0; i < kFinishThreads / 32; ++i) total += warp_ss[i];
@@ -514,7 +525,7 @@ extern "C" int wuda_mhc_pre(const void* hidden_states, const float* weight, cons
                  static_cast<long long>(workspace_bytes), static_cast<long long>(need));
     st = launch_mix(p, static_cast<cudaStream_t>(stream));
     if (st != WUDA_OK) return st;
-    WUDA_CUDA(launch_pdl(mhc_pre_finish_kernel, dim3(m), dim3(kFinishThreads), 0, static_cast<cudaStream_t>(stream), p));
+    WUDA_CUDA(launch_pdl(mhc_pre_finish_kernel, dim3(m), dim3(kFinishLaunch), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 
@@ -551,7 +562,7 @@ extern "C" int wuda_mhc_pre_finish(const void* hidden_states, const float* parti
                          mix_out, collapsed_bf16, normed_bf16, x_fp8, x_scales, const_cast<float*>(partials), m, hidden);
     if (st != WUDA_OK) return st;
     p.slices = splits;
-    WUDA_CUDA(launch_pdl(mhc_pre_finish_kernel, dim3(m), dim3(kFinishThreads), 0, static_cast<cudaStream_t>(stream), p));
+    WUDA_CUDA(launch_pdl(mhc_pre_finish_kernel, dim3(m), dim3(kFinishLaunch), 0, static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
 
