@@ -565,9 +565,11 @@ def pair_sync(group):
 
 
 def time_replays(replay, reps, group=None, flush=None):
-    """Mean device time (us) of replay(), timed with CUDA events around each call on the current stream; with a
-    process group, the ranks start each call together (host barrier) and the mean of the per-call MAX over ranks
-    is returned.  `flush` (a buffer larger than L2) is rewritten before every call when given."""
+    """Device time (us) of replay(), timed with CUDA events around each call on the current stream; with a
+    process group, the ranks start each call together (host barrier) and the MEDIAN over the calls of the per-call
+    MAX over ranks is returned (a call in which one rank's host leaves the barrier late makes its peer's kernel wait
+    for it: with eight processes on one host such calls happen, and a mean would report the host, not the GPUs).
+    Without a group: the mean.  `flush` (a buffer larger than L2) is rewritten before every call when given."""
     import torch.distributed as dist
     times = []
     for i in range(reps + 3):
@@ -588,6 +590,7 @@ def time_replays(replay, reps, group=None, flush=None):
         if dist.get_backend(group) == "nccl":
             t = t.cuda()
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return float(t.median().item())
     return float(t.mean().item())
 
 
