@@ -43,9 +43,12 @@ constexpr int kRowBytes = 128;       // K elements (bytes) per unit
 constexpr int kProducers = 4;
 constexpr int kIssuers = 2;
 constexpr int kEpiWarps = 4;
-__host__ __device__ constexpr int producers_for(int m_pad) { return m_pad >= 128 ? 2 : kProducers; }
-__host__ __device__ constexpr int first_epi_warp_for(int m_pad) { return (producers_for(m_pad) + kIssuers + 3) / 4 * 4; }
-__host__ __device__ constexpr int threads_for(int m_pad) { return 32 * (first_epi_warp_for(m_pad) + kEpiWarps); }
+// RES ("resident"): the whole activation matrix [M_PAD, K] stays in shared memory for the kernel's lifetime (short K:
+// the q projection's 1536), so a unit's copy is the weight tile alone - at 64 rows a third less for the SM to take
+// in - and two producers are enough (which also lets the stage count be any even number).
+__host__ __device__ constexpr int producers_for(int m_pad, bool res = false) { return (m_pad >= 128 || res) ? 2 : kProducers; }
+__host__ __device__ constexpr int first_epi_warp_for(int m_pad, bool res = false) { return (producers_for(m_pad, res) + kIssuers + 3) / 4 * 4; }
+__host__ __device__ constexpr int threads_for(int m_pad, bool res = false) { return 32 * (first_epi_warp_for(m_pad, res) + kEpiWarps); }
 __host__ __device__ constexpr int acc_buffers_for(int m_pad) { return m_pad <= 64 ? 2 : 1; }
 constexpr int kWBytes = kTileN * kRowBytes;   // 16 KB
 constexpr int kSfBytes = 512;                 // one scale image: 32 rows x 16 bytes
@@ -67,19 +70,22 @@ struct Params {
     int stages;
 };
 
-template <int M_PAD>
+template <int M_PAD, bool RES = false>
 struct Smem {
     static constexpr int kABytes = M_PAD * kRowBytes;
-    static constexpr int kStageBytes = kWBytes + kABytes + 2 * kSfBytes;
+    static constexpr int kStageBytes = kWBytes + (RES ? 0 : kABytes) + 2 * kSfBytes;   // W | [A] | two scale images
+    static constexpr int kSfOff = kWBytes + (RES ? 0 : kABytes);
     static constexpr int kBuffers = acc_buffers_for(M_PAD);
     // TMEM columns: per buffer one accumulator tile per issuer, then per issuer 4 + 4 scale columns (16 reserved)
     static constexpr int kAccCols = kBuffers * kIssuers * M_PAD;
     static constexpr int kUsedCols = kAccCols + kIssuers * 16;
     static constexpr int kTmemCols = kUsedCols <= 64 ? 64 : (kUsedCols <= 128 ? 128 : (kUsedCols <= 256 ? 256 : 512));
-    static __host__ __device__ constexpr int bar_off(int stages) { return stages * kStageBytes; }
-    // barriers: full[16] empty[16] full_tm[2] empty_tm[2]
-    static __host__ __device__ constexpr int misc_off(int stages) { return bar_off(stages) + 36 * 8; }
-    static __host__ __device__ constexpr int total(int stages) { return misc_off(stages) + 32 + 1024; }
+    // behind the stages: the resident activations, kb tiles of kABytes (RES only)
+    static __host__ __device__ constexpr int res_off(int stages) { return stages * kStageBytes; }
+    static __host__ __device__ constexpr int bar_off(int stages, int kb) { return res_off(stages) + (RES ? kb * kABytes : 0); }
+    // barriers: full[16] empty[16] full_tm[2] empty_tm[2] a_full
+    static __host__ __device__ constexpr int misc_off(int stages, int kb) { return bar_off(stages, kb) + 38 * 8; }
+    static __host__ __device__ constexpr int total(int stages, int kb) { return misc_off(stages, kb) + 32 + 1024; }
 };
 
 struct Ring {
@@ -133,26 +139,27 @@ __device__ __forceinline__ uint32_t exponent_byte(float scale, int32_t* status) 
     return e == 0xffu ? 0xfeu : e;
 }
 
-template <int M_PAD>
-__global__ void __launch_bounds__(threads_for(M_PAD), 1)
+template <int M_PAD, bool RES>
+__global__ void __launch_bounds__(threads_for(M_PAD, RES), 1)
 gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap a_map, const Params p) {
-    using L = Smem<M_PAD>;
+    using L = Smem<M_PAD, RES>;
     constexpr int kBuffers = L::kBuffers;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - raw_addr);
     const int S = p.stages;
-    const uint32_t bars = base + L::bar_off(S);
-    const uint32_t full = bars, empty = bars + 16 * 8, full_tm = bars + 32 * 8, empty_tm = bars + 34 * 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + L::misc_off(S));
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::misc_off(S) + 4);
+    const uint32_t bars = base + L::bar_off(S, p.kb);
+    const uint32_t full = bars, empty = bars + 16 * 8, full_tm = bars + 32 * 8, empty_tm = bars + 34 * 8, a_full = bars + 36 * 8;
+    const uint32_t a_res = base + L::res_off(S);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + L::misc_off(S, p.kb));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::misc_off(S, p.kb) + 4);
 
     const int warp = threadIdx.x >> 5;
     const uint32_t lane = lane_id();
-    constexpr int kProd = producers_for(M_PAD);
+    constexpr int kProd = producers_for(M_PAD, RES);
     constexpr int kIssuer0 = kProd;
-    constexpr int kEpi0 = first_epi_warp_for(M_PAD);
+    constexpr int kEpi0 = first_epi_warp_for(M_PAD, RES);
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -164,6 +171,7 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
             mbar_init(full_tm + b * 8, kIssuers);      // both issuers' accumulators of a segment are complete
             mbar_init(empty_tm + b * 8, kEpiWarps);    // the epilogue has read them
         }
+        mbar_init(a_full, 1);
         fence_mbar_init();
     }
     if (warp == kIssuer0) {
@@ -216,6 +224,12 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
         };
         float a_now[kRowsPerLane], a_next[kRowsPerLane];
         load_scales(tile, kb, a_now);
+        if (RES && me == 0 && count > 0) {   // the whole activation matrix, once (plain form: one group)
+            if (lane == 0) mbar_arrive_expect_tx(a_full, p.kb * L::kABytes);
+            __syncwarp();
+            for (int k = static_cast<int>(lane); k < p.kb; k += 32)
+                tma_load_2d_hint(a_res + k * L::kABytes, &a_map, a_full, k * kRowBytes, 0, keep_policy);
+        }
         for (int n = me; n < count && alive; n += kProd) {
             const int s = ring.idx;
             int tile_next = tile, kb_next = kb + kProd;
@@ -226,7 +240,7 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
             load_scales(tile_next, kb_next, a_next);
             alive = mbar_wait_lane0(empty + s * 8, ring.phase ^ 1u, abort_flag, p.status, kDevTimeoutGemmEmpty);
             if (!alive) break;
-            if (lane == 0) mbar_arrive_expect_tx(full + s * 8, kWBytes + L::kABytes);
+            if (lane == 0) mbar_arrive_expect_tx(full + s * 8, kWBytes + (RES ? 0 : L::kABytes));
             __syncwarp();
             // one instruction, two lanes: lane 0 fetches the weight tile, lane 1 the activations of the tile's group
             const uint32_t stage = base + s * L::kStageBytes;
@@ -234,7 +248,7 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
             const int group = tile / p.tiles_per_group;
             const uint32_t dst = stage + (lane == 1 ? kWBytes : 0);
             const void* map = lane == 1 ? static_cast<const void*>(&a_map) : static_cast<const void*>(&w_map);
-            if (lane < 2)
+            if (lane < (RES ? 1u : 2u))
                 tma_load_2d_hint(dst, map, full + s * 8, (lane == 1 ? group * p.kb + kb : kb) * kRowBytes, lane == 1 ? 0 : tile * kTileN,
                                  lane == 1 ? keep_policy : stream_policy);
             // scale images: lane l writes row l of each (16 bytes: the words of rows l, l + 32, l + 64, l + 96)
@@ -245,11 +259,11 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
             }
             const float w_scale = __shfl_sync(0xffffffffu, w_now, (n - batch_first) / kProd);
             const uint32_t ew = exponent_byte(w_scale, p.status) * 0x01010101u;
-            *reinterpret_cast<uint4*>(stage_ptr + kWBytes + L::kABytes + lane * 16) = make_uint4(ew, ew, ew, ew);
+            *reinterpret_cast<uint4*>(stage_ptr + L::kSfOff + lane * 16) = make_uint4(ew, ew, ew, ew);
             uint32_t aw[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
             for (int q = 0; q < kRowsPerLane; ++q) aw[q] = exponent_byte(a_now[q], p.status) * 0x01010101u;
-            *reinterpret_cast<uint4*>(stage_ptr + kWBytes + L::kABytes + kSfBytes + lane * 16) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+            *reinterpret_cast<uint4*>(stage_ptr + L::kSfOff + kSfBytes + lane * 16) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
             fence_proxy_async_smem();       // the images are read by tcgen05.cp
             __syncwarp();
             if (lane == 0) mbar_arrive(full + s * 8);
@@ -272,6 +286,7 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
             int kb = static_cast<int>(u0 % p.kb);
             uint32_t seg = 0;
             bool alive = true;
+            if (RES && count > 0) alive = mbar_wait(a_full, 0, abort_flag, p.status, kDevTimeoutGemmFull);
             for (int n = 0; n < count && alive;) {
                 const int seg_len = min(p.kb - kb, count - n);
                 const uint32_t buf = kBuffers == 2 ? (seg & 1u) : 0u;
@@ -290,8 +305,8 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
                     }
                     tc_fence_after();
                     const uint32_t stage = base + s * L::kStageBytes;
-                    const uint32_t w_addr = stage, a_addr = stage + kWBytes;
-                    const uint32_t wsf_addr = stage + kWBytes + L::kABytes, asf_addr = wsf_addr + kSfBytes;
+                    const uint32_t w_addr = stage, a_addr = RES ? a_res + (kb + (u - n)) * L::kABytes : stage + kWBytes;
+                    const uint32_t wsf_addr = stage + L::kSfOff, asf_addr = wsf_addr + kSfBytes;
                     // 32 rows x 16 bytes; 8-row groups 128 bytes apart
                     tmem_cp_32x128b_warpx4(sfw_t, umma_smem_desc_noswz(wsf_addr, 16, 128));
                     tmem_cp_32x128b_warpx4(sfa_t, umma_smem_desc_noswz(asf_addr, 16, 128));
@@ -419,26 +434,40 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     }
 }
 
-template <int M_PAD>
-static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p, const DeviceInfo& dev, cudaStream_t stream) {
-    using L = Smem<M_PAD>;
-    int stages = 16;
-    constexpr int kStep = M_PAD >= 128 ? 2 : 4;   // lcm of the producer and issuer counts
-    while (stages > kStep && L::total(stages) > dev.smem_optin) stages -= kStep;
-    if (L::total(stages) > dev.smem_optin)
-        return fail(WUDA_ERR_UNSUPPORTED, "device offers %d bytes of shared memory per block; the kernel needs more",
-                    dev.smem_optin);
+template <int M_PAD, bool RES>
+static int launch_as(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p, const DeviceInfo& dev, int stages,
+                     cudaStream_t stream) {
+    using L = Smem<M_PAD, RES>;
     p.stages = stages;
-    auto kernel = gemm_fp8_mx_kernel<M_PAD>;
-    WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total(stages)));
+    auto kernel = gemm_fp8_mx_kernel<M_PAD, RES>;
+    WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total(stages, p.kb)));
     const long long units = static_cast<long long>(p.n_tiles) * p.kb;
     // CTAs that may share one weight tile: the owner adds their partials one after the other
     constexpr int kMaxSplit = M_PAD <= 16 ? 16 : (M_PAD == 32 ? 12 : (M_PAD == 64 ? 8 : 6));
     const int sms = gemm_sms(dev);
     int grid = units < sms ? static_cast<int>(units) : sms;
     if (static_cast<long long>(p.n_tiles) * kMaxSplit < grid) grid = p.n_tiles * kMaxSplit;
-    WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(threads_for(M_PAD)), L::total(stages), stream, w_map, a_map, p));
+    WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(threads_for(M_PAD, RES)), L::total(stages, p.kb), stream, w_map, a_map, p));
     return WUDA_OK;
+}
+
+template <int M_PAD>
+static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p, const DeviceInfo& dev, cudaStream_t stream) {
+    // Short K, one group, 32 or 64 rows: the activations stay resident if at least six weight stages fit beside them.
+    if (M_PAD >= 32 && M_PAD <= 64 && p.tiles_per_group == p.n_tiles && p.kb * Smem<M_PAD>::kABytes <= 96 * 1024) {
+        using R = Smem<M_PAD, true>;
+        int stages = 16;
+        while (stages > 2 && R::total(stages, p.kb) > dev.smem_optin) stages -= 2;
+        if (stages >= 6 && R::total(stages, p.kb) <= dev.smem_optin) return launch_as<M_PAD, true>(w_map, a_map, p, dev, stages, stream);
+    }
+    using L = Smem<M_PAD, false>;
+    int stages = 16;
+    constexpr int kStep = M_PAD >= 128 ? 2 : 4;   // lcm of the producer and issuer counts
+    while (stages > kStep && L::total(stages, p.kb) > dev.smem_optin) stages -= kStep;
+    if (L::total(stages, p.kb) > dev.smem_optin)
+        return fail(WUDA_ERR_UNSUPPORTED, "device offers %d bytes of shared memory per block; the kernel needs more",
+                    dev.smem_optin);
+    return launch_as<M_PAD, false>(w_map, a_map, p, dev, stages, stream);
 }
 
 // One pass of at most 128 rows.  groups = 1 is the plain GEMM.
