@@ -530,6 +530,13 @@ int wuda_mhc_pre_finish(const void* hidden_states, const float* partials, int sp
                         void* x_fp8, float* x_scales, int m, int hidden, void* stream);
 int wuda_mhc_tail(const float* mix, const float* base, const float* scale, float hc_eps, float* post, float* comb, int m,
                   void* stream);
+/* The origin's hc_split_sinkhorn (origin/kernel.py:355-436) with hc_mult = 4 and 20 iterations: from mixes fp32
+ * [tokens, 24] (pre 0..3 | post 4..7 | comb 8..23), scale fp32 [3] and base fp32 [24]:
+ *   pre = sigmoid(mix * scale[0] + base) + eps;  post = 2 sigmoid(mix * scale[1] + base);
+ *   comb = softmax over each row of (mix * scale[2] + base) + eps, columns normalised, then 19 x (rows, columns),
+ *   every division by (sum + eps).  pre, post fp32 [tokens, 4]; comb fp32 [tokens, 4, 4]. */
+int wuda_hc_split_sinkhorn(const float* mixes, const float* scale, const float* base, float hc_eps, float* pre, float* post,
+                           float* comb, int64_t tokens, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * MoE router: expert logits -> top-k experts and routing weights.
@@ -708,6 +715,46 @@ int wuda_gemm_fp8_blockscaled_pow2(const void* a, const float* a_scales, const v
 int wuda_gemm_fp8_grouped_pow2(const void* a, const float* a_scales, const void* w, const float* w_scales, void* c_bf16,
                                int m, int n_per_group, int k, int groups, void* scratch, int64_t scratch_bytes,
                                int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * FP8 activations x 4-bit weights, C = A . W^T (origin/kernel.py:441-536, fp4_gemm: the format of the origin's
+ * routed experts, origin/model.py:108-135,623).
+ *
+ *   a        e4m3 [m, k], a_scales fp32 [m, k/128]: one POWER-OF-TWO scale per row and 128 K-elements
+ *            (act_quant with scale_fmt "ue8m0"; a float8_e8m0fnu tensor converts exactly)
+ *   w_packed e2m1 [n, k/2] bytes, the element of the lower K index in the low nibble (torch.float4_e2m1fn_x2);
+ *            32-byte aligned
+ *   w_sf     [n, k/32] exponent bytes (torch.float8_e8m0fnu): weight (row, j) = code * 2^(w_sf[row, j/32] - 127)
+ *   c_bf16   bf16 [m, n];  0 <= m <= 256 (above 128 rows: two passes), k % 128 == 0
+ *   scratch  as for wuda_gemm_fp8_blockscaled (wuda_gemm_fp8_scratch_bytes(m, n))
+ *
+ * The kernel of wuda_gemm_fp8_blockscaled_pow2 with the weight operand read as e2m1 (the tile is 8 KB of global
+ * memory, expanded by the copy engine to the padded form the tensor core wants) and one exponent byte per weight
+ * row and 32 K-elements in tensor memory.  The products are added in fp32 inside the tensor core; the origin adds
+ * them 32-block by 32-block on CUDA cores: same value up to fp32 summation order.
+ */
+int wuda_gemm_fp8_fp4_pow2(const void* a, const float* a_scales, const void* w_packed, const void* w_sf, void* c_bf16,
+                           int m, int n, int k, void* scratch, int64_t scratch_bytes, int32_t* status_word,
+                           void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Block-wise FP4 quantisation of bf16 rows (origin/kernel.py:126-200, fp4_act_quant): per 32 values
+ * amax = max(max|x|, 6 * 2^-126), scale = 2^ceil(log2(amax / 6)), code = e2m1(x / scale) rounded to nearest even.
+ *
+ *   x_bf16  bf16 [rows, cols] with row_stride elements between rows (row_stride % 8 == 0), cols % 32 == 0
+ *   inplace == 0:  codes u8 [rows, cols/2] (lower index in the low nibble), scales u8 [rows, cols/32] (exponent
+ *                  bytes, float8_e8m0fnu)
+ *   inplace != 0:  x is overwritten with code * scale as bf16 (the quantise-dequantise of origin/model.py:370,416);
+ *                  codes and scales may be NULL
+ */
+int wuda_fp4_act_quant(const void* x_bf16, int64_t row_stride, void* codes, void* scales, int inplace, int64_t rows,
+                       int cols, void* stream);
+
+/* Sum of squares of every 512-value head of bf16 rows (head_ssq_standalone, kernels/wq_b_fp8_gemm.cu:101-123,
+ * 1548-1566): y bf16 [rows, heads * 512] with row_stride elements between rows -> ssq fp32 [rows, heads].  Lane l of
+ * a warp chains fused multiply-adds over values [16 l, 16 l + 16) of a head; a butterfly over lane distances
+ * 16, 8, 4, 2, 1 adds the lanes: the reference kernel's order, so the sums are identical bit for bit. */
+int wuda_head_ssq(const void* y_bf16, int64_t row_stride, float* ssq, int64_t rows, int heads, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * BF16 GEMM for decode-sized M:  c[m, n] = sum_k a[m, k] * w[n, k], fp32 accumulation, written

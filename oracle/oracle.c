@@ -831,6 +831,105 @@ void oracle_gemm_fp8_blockscaled(const uint8_t* a, const float* a_s, const uint8
     free(af);
 }
 
+/* ------------------------------------------------------------------ FP8 activations x FP4 weights
+ *
+ * C[M,N] = A[M,K] @ B[N,K]^T after dsv4_megakernel/origin/kernel.py:441-536 (fp4_gemm_kernel): A e4m3 with one
+ * fp32 scale per row and 128 K-elements (a_s [M, K/128]); B e2m1, two codes per byte with the lower K index in the low
+ * nibble ([N, K/2]), one e8m0 exponent byte per row and 32 K-elements (b_sf [N, K/32]).  Each 32-wide K block is
+ * summed in fp32 and added, times a_s[m, k/128] * 2^(b_sf[n, k/32] - 127), into a second fp32 accumulator (kernel.py
+ * lines 497-512).  Output bf16 (out_bf16) or fp32.
+ */
+static inline float e2m1_code_value(uint8_t code) {
+    static const float grid[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+    const float v = grid[code & 7];
+    return (code & 8) ? -v : v;
+}
+
+__attribute__((optimize("fp-contract=off")))
+void oracle_gemm_fp8_fp4(const uint8_t* a, const float* a_s, const uint8_t* b, const uint8_t* b_sf, void* c, int M, int N,
+                         int K, int out_bf16) {
+    float lut[256];
+    for (int i = 0; i < 256; ++i) lut[i] = oracle_e4m3_to_f32((uint8_t)i);
+    float* af = (float*)malloc((size_t)M * K * sizeof(float));
+    for (int64_t i = 0; i < (int64_t)M * K; ++i) af[i] = lut[a[i]];
+#pragma omp parallel for schedule(dynamic, 16)
+    for (int n = 0; n < N; ++n) {
+        float bf[32];
+        float* acc = (float*)calloc((size_t)M, sizeof(float));
+        for (int kb = 0; kb < K / 32; ++kb) {
+            for (int k = 0; k < 32; ++k) {
+                const uint8_t byte = b[(int64_t)n * (K / 2) + (kb * 32 + k) / 2];
+                bf[k] = e2m1_code_value((k & 1) ? (byte >> 4) : (byte & 15));
+            }
+            const float sb = ldexpf(1.0f, (int)b_sf[(int64_t)n * (K / 32) + kb] - 127);
+            for (int m = 0; m < M; ++m) {
+                const float* am = af + (int64_t)m * K + kb * 32;
+                float part = 0.0f;
+                for (int k = 0; k < 32; ++k) part += am[k] * bf[k];
+                acc[m] += part * a_s[(int64_t)m * (K / 128) + kb / 4] * sb;
+            }
+        }
+        for (int m = 0; m < M; ++m) {
+            if (out_bf16) ((uint16_t*)c)[(int64_t)m * N + n] = f32_to_bf16(acc[m]);
+            else ((float*)c)[(int64_t)m * N + n] = acc[m];
+        }
+        free(acc);
+    }
+    free(af);
+}
+
+/* Block-wise FP4 quantisation after dsv4_megakernel/origin/kernel.py:126-200 (fp4_quant_kernel): per 32 values
+ * amax = max(max|x|, 6 * 2^-126), scale = 2^ceil(log2(amax * (1/6))) taken from the fp32 product's exponent and
+ * mantissa bits (fast_round_scale, kernel.py:22-37), code = e2m1(clamp(x / scale, -6, 6)) to nearest even.  Writes
+ * the packed codes and exponent bytes and, if `deq` is given, code * scale rounded to bf16 (the inplace form).
+ */
+__attribute__((optimize("fp-contract=off")))
+void oracle_fp4_act_quant(const uint16_t* x, int64_t rows, int cols, uint8_t* codes, uint8_t* scales, uint16_t* deq) {
+    for (int64_t r = 0; r < rows; ++r)
+        for (int b = 0; b < cols / 32; ++b) {
+            float v[32], amax = 0.0f;
+            for (int i = 0; i < 32; ++i) {
+                v[i] = bf16_to_f32(x[r * cols + b * 32 + i]);
+                amax = fmaxf(amax, fabsf(v[i]));
+            }
+            amax = fmaxf(amax, 6.0f * 1.1754944e-38f);
+            const int e = log2_ceil_f32(amax * (1.0f / 6.0f));
+            const float inv = ldexpf(1.0f, -e), sc = ldexpf(1.0f, e);
+            if (scales) scales[r * (cols / 32) + b] = (uint8_t)(e + 127);
+            for (int i = 0; i < 32; i += 2) {
+                const uint8_t lo = e2m1_rne(v[i] * inv), hi = e2m1_rne(v[i + 1] * inv);
+                if (codes) codes[(r * cols + b * 32 + i) / 2] = (uint8_t)(lo | (hi << 4));
+                if (deq) {
+                    deq[r * cols + b * 32 + i] = f32_to_bf16(e2m1_code_value(lo) * sc);
+                    deq[r * cols + b * 32 + i + 1] = f32_to_bf16(e2m1_code_value(hi) * sc);
+                }
+            }
+        }
+}
+
+/* Sum of squares per 512-value head in the order of dsv4_megakernel/megakernel/kernels/wq_b_fp8_gemm.cu:101-123:
+ * lane l chains fused multiply-adds over values [16 l, 16 l + 16); a butterfly over distances 16, 8, 4, 2, 1. */
+__attribute__((optimize("fp-contract=off")))
+void oracle_head_ssq(const uint16_t* y, int64_t heads_total, float* ssq) {
+    for (int64_t h = 0; h < heads_total; ++h) {
+        float lane[32];
+        for (int l = 0; l < 32; ++l) {
+            float s = 0.0f;
+            for (int k = 0; k < 16; ++k) {
+                const float v = bf16_to_f32(y[h * 512 + l * 16 + k]);
+                s = fmaf(v, v, s);
+            }
+            lane[l] = s;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            float next[32];
+            for (int l = 0; l < 32; ++l) next[l] = lane[l] + lane[l ^ o];
+            memcpy(lane, next, sizeof lane);
+        }
+        ssq[h] = lane[0];
+    }
+}
+
 /* ------------------------------------------------------------------ NVFP4 block-scaled GEMM
  *
  * C[M,N] = gs_a * gs_w * sum_k (e2m1(a[m,k]) * ue4m3(a_sf[m,k/16])) * (e2m1(w[n,k]) * ue4m3(w_sf[n,k/16]))

@@ -75,6 +75,9 @@ def _declare(l):
                                     c.c_int, c.c_int, c.c_int, c.c_int]
     l.oracle_gemm_fp8_blockscaled.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
                                               c.c_int, c.c_int, c.c_int, c.c_int]
+    l.oracle_gemm_fp8_fp4.argtypes = [vp, vp, vp, vp, vp, c.c_int, c.c_int, c.c_int, c.c_int]
+    l.oracle_fp4_act_quant.argtypes = [vp, i64, c.c_int, vp, vp, vp]
+    l.oracle_head_ssq.argtypes = [vp, i64, vp]
 
 
 def _p(a):
@@ -508,6 +511,56 @@ def gemm_fp8_blockscaled(a, a_s, b, b_s, out_bf16=True):
     c = np.empty((m, n), np.uint16 if out_bf16 else np.float32)
     lib().oracle_gemm_fp8_blockscaled(_p(a), _p(a_s), _p(b), _p(b_s), _p(c), m, n, k, int(out_bf16))
     return c
+
+
+def gemm_fp8_fp4(a, a_s, b_packed, b_sf, out_bf16=True):
+    """a e4m3 bytes [M,K], a_s fp32 [M,K/128], b_packed e2m1 pairs [N,K/2] (lower index in the low nibble), b_sf
+    exponent bytes [N,K/32].  Returns uint16 (bf16) or fp32 [M,N]: the origin's fp4_gemm (origin/kernel.py:441-536)."""
+    a, b, b_sf = _c(a, np.uint8), _c(b_packed, np.uint8), _c(b_sf, np.uint8)
+    a_s = _c(a_s, np.float32)
+    m, k = a.shape
+    n = b.shape[0]
+    c = np.empty((m, n), np.uint16 if out_bf16 else np.float32)
+    lib().oracle_gemm_fp8_fp4(_p(a), _p(a_s), _p(b), _p(b_sf), _p(c), m, n, k, int(out_bf16))
+    return c
+
+
+def fp4_act_quant(x_bf16):
+    """x uint16 (bf16) [rows, cols] -> (packed e2m1 uint8 [rows, cols/2], exponent bytes uint8 [rows, cols/32],
+    dequantised bf16 uint16 [rows, cols]): the origin's fp4_act_quant in both forms (origin/kernel.py:126-200)."""
+    x = _c(x_bf16, np.uint16)
+    rows, cols = x.shape
+    codes, scales = np.empty((rows, cols // 2), np.uint8), np.empty((rows, cols // 32), np.uint8)
+    deq = np.empty((rows, cols), np.uint16)
+    lib().oracle_fp4_act_quant(_p(x), rows, cols, _p(codes), _p(scales), _p(deq))
+    return codes, scales, deq
+
+
+def head_ssq(y_bf16):
+    """y uint16 (bf16) [..., heads, 512] -> fp32 [..., heads] sums of squares in the reference kernel's order."""
+    y = _c(y_bf16, np.uint16)
+    out = np.empty(y.shape[:-1], np.float32)
+    lib().oracle_head_ssq(_p(y), out.size, _p(out))
+    return out
+
+
+def hc_split_sinkhorn(mixes, hc_scale, hc_base, iters=20, eps=1e-6):
+    """The origin's hc_split_sinkhorn (origin/kernel.py:355-436) in fp32 numpy, hc_mult = 4: mixes [n, 24] ->
+    (pre [n, 4], post [n, 4], comb [n, 4, 4])."""
+    f = np.float32
+    mixes, sc, base = _c(mixes, f).reshape(-1, 24), _c(hc_scale, f), _c(hc_base, f)
+    eps = f(eps)
+    sig = lambda v: (f(1) / (f(1) + np.exp(-v, dtype=f))).astype(f)
+    pre = sig(mixes[:, :4] * sc[0] + base[:4]) + eps
+    post = f(2) * sig(mixes[:, 4:8] * sc[1] + base[4:8])
+    c = (mixes[:, 8:] * sc[2] + base[8:]).reshape(-1, 4, 4).astype(f)
+    c = np.exp(c - c.max(-1, keepdims=True), dtype=f)
+    c = (c / c.sum(-1, keepdims=True, dtype=f) + eps).astype(f)
+    c = (c / (c.sum(-2, keepdims=True, dtype=f) + eps)).astype(f)
+    for _ in range(iters - 1):
+        c = (c / (c.sum(-1, keepdims=True, dtype=f) + eps)).astype(f)
+        c = (c / (c.sum(-2, keepdims=True, dtype=f) + eps)).astype(f)
+    return pre.astype(f), post.astype(f), c
 
 
 def bf16_to_f32(u16):

@@ -152,6 +152,10 @@ SIGNATURES = {
     "wuda_gemm_fp8_grouped": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
     "wuda_gemm_fp8_grouped_pow2": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
     "wuda_gemm_fp8_blockscaled_pow2": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
+    "wuda_gemm_fp8_fp4_pow2": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp]),
+    "wuda_fp4_act_quant": (c_int, [c_vp, c_i64, c_vp, c_vp, c_int, c_i64, c_int, c_vp]),
+    "wuda_head_ssq": (c_int, [c_vp, c_i64, c_vp, c_i64, c_int, c_vp]),
+    "wuda_hc_split_sinkhorn": (c_int, [c_vp, c_vp, c_vp, c_float, c_vp, c_vp, c_vp, c_i64, c_vp]),
     "wuda_moe_route": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_vp]),
     "wuda_moe_max_groups": (c_int, [c_int, c_int, c_int]),
     "wuda_moe_dispatch": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp, c_vp]),

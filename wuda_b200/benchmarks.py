@@ -5,6 +5,7 @@ because consecutive launches use different weight buffers that together exceed L
 
     python -m wuda_b200.benchmarks gemm_fp8
     python -m wuda_b200.benchmarks gemm_fp8_pow2                   (power-of-two scales applied inside the tensor core)
+    python -m wuda_b200.benchmarks gemm_fp8_fp4                    (FP8 activations x FP4 weights: the origin's fp4_gemm)
     python -m wuda_b200.benchmarks gemm_nvfp4
     python -m wuda_b200.benchmarks norm_rope_quant
     python -m wuda_b200.benchmarks csa_chain                       (layer launch of the indexer half-step)
@@ -103,6 +104,34 @@ def gemm_fp8(pow2=False):
             tfl = 2.0 * m * n * k / us / 1e6
             print("%6d %6d %6d %9.1f %9.0f %7.1f%% %9.1f %7.1f%%" % (m, n, k, us, gbs, 100 * gbs / hbm, tfl, 100 * tfl / (2 * tf)))
             del ws
+
+
+def gemm_fp8_fp4():
+    """FP8 activations x FP4 weights (the origin's fp4_gemm).  Operands are random bytes made on the device (every
+    byte pattern is a valid e2m1 pair; e4m3 bytes avoid the two NaN codes); results are checked by the tests."""
+    hbm, tf, kind = peaks()
+    print("FP8 x FP4 GEMM (e8m0 scales per 32 weights), bf16 out; peaks (%s): %.0f GB/s HBM, %.0f TFLOP/s dense bf16" % (kind, hbm, tf))
+    print("%6s %6s %6s %9s %9s %8s" % ("M", "N", "K", "us", "GB/s", "of HBM"))
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    for n, k in ((24576, 7168), (7168, 16384), (4096, 7168), (7168, 2048)):
+        copies = max(2, int(300e6 // (n * k // 2)) + 1)
+        ws = [torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda", generator=gen) for _ in range(copies)]
+        w_sf = torch.randint(118, 126, (n, k // 32), dtype=torch.uint8, device="cuda", generator=gen)
+        for m in (1, 8, 32, 64, 128, 256):
+            a = torch.randint(0, 0x78, (m, k), dtype=torch.uint8, device="cuda", generator=gen).view(torch.float8_e4m3fn)
+            a_s = torch.exp2(torch.randint(-4, 4, (m, k // 128), device="cuda", generator=gen).float())
+            out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            state = {"i": 0}
+
+            def fn():
+                wuda.fp4_gemm(a, a_s, ws[state["i"] % copies], w_sf, out=out)
+                state["i"] += 1
+
+            us = time_graph(fn, reps=10, inner=copies * 2)
+            by = n * k // 2 + n * k // 32 + m * k + m * (k // 128) * 4 + m * n * 2
+            gbs = by / us / 1e3
+            print("%6d %6d %6d %9.1f %9.0f %7.1f%%" % (m, n, k, us, gbs, 100 * gbs / hbm))
+        del ws
 
 
 def gemm_nvfp4():
@@ -789,7 +818,7 @@ def one(kind, m, n, k, launches=5):
     print("ran %d launches of %s M=%d N=%d K=%d" % (launches, kind, m, n, k))
 
 
-KINDS = {"topk": topk, "gemm_fp8": gemm_fp8, "gemm_fp8_pow2": lambda: gemm_fp8(pow2=True), "gemm_nvfp4": gemm_nvfp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(batches=(64,), contexts=(32768,), launches_only=3),
+KINDS = {"topk": topk, "gemm_fp8": gemm_fp8, "gemm_fp8_pow2": lambda: gemm_fp8(pow2=True), "gemm_nvfp4": gemm_nvfp4, "gemm_fp8_fp4": gemm_fp8_fp4, "norm_rope_quant": norm_rope_quant, "tp2": tp2, "moe_ep2": moe_ep2, "mqa_fp4": mqa_fp4, "mqa_fp4_launches": lambda: mqa_fp4(batches=(64,), contexts=(32768,), launches_only=3),
          "sparse_mla": sparse_mla, "sparse_mla_launches": lambda: sparse_mla(batches=(32,), launches_only=3),
          "csa_chain": csa_chain, "csa_chain_fp4": lambda: csa_chain(indexer_fp4=True),
          "csa_chain_launches": lambda: csa_chain(launches_only=3),

@@ -52,13 +52,16 @@ __host__ __device__ constexpr int threads_for(int m_pad, bool res = false) { ret
 __host__ __device__ constexpr int acc_buffers_for(int m_pad) { return m_pad <= 64 ? 2 : 1; }
 constexpr int kWBytes = kTileN * kRowBytes;   // 16 KB
 constexpr int kSfBytes = 512;                 // one scale image: 32 rows x 16 bytes
+constexpr int kSfDepth = 4;                   // W4: units a producer requests its weight scales ahead
 constexpr int kMaxGrid = 192;
 constexpr int64_t kFlagBytes = 1024;          // as in gemm_fp8.cu: the two kernels share a scratch
 
 struct Params {
     __nv_bfloat16* c;
     const float* a_scales;     // [M, scale_cols]
-    const float* w_scales;     // [tiles, kb] = flat unit order
+    const float* w_scales;     // [tiles, kb] = flat unit order (FP8 weights)
+    const uint8_t* w_sf;       // W4: [N, K/32] exponent bytes, one per weight row and 32 K-elements
+    int sf_stride;             // W4: bytes between the rows of w_sf
     float* scratch;            // [grid][M_PAD][128] fp32 partial-tile slots
     int32_t* flags;            // [grid]
     int32_t* status;
@@ -85,7 +88,12 @@ struct Smem {
     static __host__ __device__ constexpr int bar_off(int stages, int kb) { return res_off(stages) + (RES ? kb * kABytes : 0); }
     // barriers: full[16] empty[16] full_tm[2] empty_tm[2] a_full
     static __host__ __device__ constexpr int misc_off(int stages, int kb) { return bar_off(stages, kb) + 38 * 8; }
-    static __host__ __device__ constexpr int total(int stages, int kb) { return misc_off(stages, kb) + 32 + 1024; }
+    // W4: behind the 32 bytes of odds and ends, per producer warp a ring of kSfDepth weight-scale images (512 B each)
+    // that cp.async fills kSfDepth units ahead
+    static __host__ __device__ constexpr int sf_ring_off(int stages, int kb) { return misc_off(stages, kb) + 32; }
+    static __host__ __device__ constexpr int total(int stages, int kb, bool w4 = false) {
+        return sf_ring_off(stages, kb) + (w4 ? kProducers * kSfDepth * kSfBytes : 0) + 1024;
+    }
 };
 
 struct Ring {
@@ -130,6 +138,14 @@ __device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint
         : "memory");
 }
 
+// 4 bytes global -> shared without a register in between (src_bytes = 0: zeros); groups are counted per thread
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // Exponent byte of a power-of-two fp32 scale; anything else is reported and truncated to the power of two below.
 __device__ __forceinline__ uint32_t exponent_byte(float scale, int32_t* status) {
     const uint32_t bits = __float_as_uint(scale);
@@ -139,7 +155,13 @@ __device__ __forceinline__ uint32_t exponent_byte(float scale, int32_t* status) 
     return e == 0xffu ? 0xfeu : e;
 }
 
-template <int M_PAD, bool RES>
+// W4: the weights are e2m1, two to a byte ([N, K/2], low nibble first), with one exponent byte per row and 32 K-elements
+// (origin/kernel.py:441-536, fp4_gemm).  The tensor core reads 4-bit operands of this kind from shared memory in the
+// padded form - 16 values in 8 bytes, then 8 bytes of nothing - which is what a tensor map of type 16U4_ALIGN16B makes
+// of the packed rows: a unit's weight tile still fills 16 KB of the stage but is 8 KB of global memory, and the
+// barrier counts those 8 KB.  Its scale image is no longer one byte repeated: word (row) = the row's four exponent
+// bytes of this K block, read straight from w_sf a unit ahead.
+template <int M_PAD, bool RES, bool W4>
 __global__ void __launch_bounds__(threads_for(M_PAD, RES), 1)
 gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap a_map, const Params p) {
     using L = Smem<M_PAD, RES>;
@@ -210,7 +232,34 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
             const long long u = u0 + first + kProd * static_cast<int>(lane);
             return u < u1 ? __ldg(p.w_scales + u) : 1.0f;
         };
-        float w_now = load_batch(batch_first), w_next = load_batch(batch_first + 32 * kProd);
+        float w_now = 1.0f, w_next = 1.0f;
+        if constexpr (!W4) {
+            w_now = load_batch(batch_first);
+            w_next = load_batch(batch_first + 32 * kProd);
+        }
+        // W4: lane l fetches the exponent words of weight rows l, l + 32, l + 64, l + 96 of a unit - its 16 bytes of the
+        // unit's image - into this warp's ring, kSfDepth of the warp's units ahead: a register prefetch would let one
+        // request per iteration be in flight, and the words come from DRAM (every row's sector, every eighth K block).
+        // Rows beyond N read as zeros (2^-127 times an operand row of zeros).
+        const uint32_t sf_ring = base + L::sf_ring_off(S, p.kb) + me * (kSfDepth * kSfBytes) + lane * 16;
+        auto request_wsf = [&](int slot, long long u) {
+            if (u < u1) {
+                const int t = static_cast<int>(u / p.kb), k = static_cast<int>(u - static_cast<long long>(t) * p.kb);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int row = t * kTileN + q * 32 + static_cast<int>(lane);
+                    const int safe = row < p.N ? row : 0;
+                    cp_async_4(sf_ring + slot * kSfBytes + q * 4, p.w_sf + static_cast<int64_t>(safe) * p.sf_stride + k * 4,
+                               row < p.N ? 4u : 0u);
+                }
+            }
+            cp_async_commit();
+        };
+        int sf_slot = 0;
+        if constexpr (W4) {
+#pragma unroll
+            for (int d = 0; d < kSfDepth; ++d) request_wsf(d, u0 + me + d * kProd);
+        }
         // activation scales of a unit: lane l holds those of rows l, l + 32, .. (rows beyond M: 2^0, their operand rows
         // are zeros); the next unit's are requested before this unit's copies are started
         constexpr int kRowsPerLane = (M_PAD + 31) / 32;
@@ -240,7 +289,7 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
             load_scales(tile_next, kb_next, a_next);
             alive = mbar_wait_lane0(empty + s * 8, ring.phase ^ 1u, abort_flag, p.status, kDevTimeoutGemmEmpty);
             if (!alive) break;
-            if (lane == 0) mbar_arrive_expect_tx(full + s * 8, kWBytes + (RES ? 0 : L::kABytes));
+            if (lane == 0) mbar_arrive_expect_tx(full + s * 8, (W4 ? kWBytes / 2 : kWBytes) + (RES ? 0 : L::kABytes));
             __syncwarp();
             // one instruction, two lanes: lane 0 fetches the weight tile, lane 1 the activations of the tile's group
             const uint32_t stage = base + s * L::kStageBytes;
@@ -252,14 +301,25 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
                 tma_load_2d_hint(dst, map, full + s * 8, (lane == 1 ? group * p.kb + kb : kb) * kRowBytes, lane == 1 ? 0 : tile * kTileN,
                                  lane == 1 ? keep_policy : stream_policy);
             // scale images: lane l writes row l of each (16 bytes: the words of rows l, l + 32, l + 64, l + 96)
-            if (n >= batch_first + 32 * kProd) {
-                batch_first += 32 * kProd;
-                w_now = w_next;
-                w_next = load_batch(batch_first + 32 * kProd);
+            if constexpr (W4) {
+                cp_async_wait<kSfDepth - 1>();      // this unit's words have landed (a lane reads only what it fetched)
+                uint4 words;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(words.x), "=r"(words.y), "=r"(words.z), "=r"(words.w)
+                             : "r"(sf_ring + sf_slot * kSfBytes));
+                *reinterpret_cast<uint4*>(stage_ptr + L::kSfOff + lane * 16) = words;
+                request_wsf(sf_slot, u0 + n + static_cast<long long>(kSfDepth) * kProd);   // the slot is read: refill it
+                sf_slot = sf_slot + 1 == kSfDepth ? 0 : sf_slot + 1;
+            } else {
+                if (n >= batch_first + 32 * kProd) {
+                    batch_first += 32 * kProd;
+                    w_now = w_next;
+                    w_next = load_batch(batch_first + 32 * kProd);
+                }
+                const float w_scale = __shfl_sync(0xffffffffu, w_now, (n - batch_first) / kProd);
+                const uint32_t ew = exponent_byte(w_scale, p.status) * 0x01010101u;
+                *reinterpret_cast<uint4*>(stage_ptr + L::kSfOff + lane * 16) = make_uint4(ew, ew, ew, ew);
             }
-            const float w_scale = __shfl_sync(0xffffffffu, w_now, (n - batch_first) / kProd);
-            const uint32_t ew = exponent_byte(w_scale, p.status) * 0x01010101u;
-            *reinterpret_cast<uint4*>(stage_ptr + L::kSfOff + lane * 16) = make_uint4(ew, ew, ew, ew);
             uint32_t aw[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
             for (int q = 0; q < kRowsPerLane; ++q) aw[q] = exponent_byte(a_now[q], p.status) * 0x01010101u;
@@ -312,8 +372,8 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
                     tmem_cp_32x128b_warpx4(sfa_t, umma_smem_desc_noswz(asf_addr, 16, 128));
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        // e4m3 x e4m3 (format 0), ue8m0 scales (1), the k-th scale byte of both operands
-                        const uint32_t idesc = umma_idesc_block_scaled(kTileN, M_PAD, 0, 0, 1, k, k);
+                        // weights e4m3 (format 0) or e2m1 (5) x e4m3, ue8m0 scales (1), the k-th scale byte of both operands
+                        const uint32_t idesc = umma_idesc_block_scaled(kTileN, M_PAD, W4 ? 5 : 0, 0, 1, k, k);
                         umma_mxf8(d_addr, umma_smem_desc_sw128(w_addr + k * 32), umma_smem_desc_sw128(a_addr + k * 32), idesc, sfw_t,
                                   sfa_t, accumulate);
                         accumulate = 1;
@@ -434,47 +494,50 @@ gemm_fp8_mx_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     }
 }
 
-template <int M_PAD, bool RES>
+template <int M_PAD, bool RES, bool W4>
 static int launch_as(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p, const DeviceInfo& dev, int stages,
                      cudaStream_t stream) {
     using L = Smem<M_PAD, RES>;
     p.stages = stages;
-    auto kernel = gemm_fp8_mx_kernel<M_PAD, RES>;
-    WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total(stages, p.kb)));
+    auto kernel = gemm_fp8_mx_kernel<M_PAD, RES, W4>;
+    WUDA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total(stages, p.kb, W4)));
     const long long units = static_cast<long long>(p.n_tiles) * p.kb;
     // CTAs that may share one weight tile: the owner adds their partials one after the other
     constexpr int kMaxSplit = M_PAD <= 16 ? 16 : (M_PAD == 32 ? 12 : (M_PAD == 64 ? 8 : 6));
     const int sms = gemm_sms(dev);
     int grid = units < sms ? static_cast<int>(units) : sms;
     if (static_cast<long long>(p.n_tiles) * kMaxSplit < grid) grid = p.n_tiles * kMaxSplit;
-    WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(threads_for(M_PAD, RES)), L::total(stages, p.kb), stream, w_map, a_map, p));
+    WUDA_CUDA(launch_pdl(kernel, dim3(grid), dim3(threads_for(M_PAD, RES)), L::total(stages, p.kb, W4), stream, w_map, a_map, p));
     return WUDA_OK;
 }
 
-template <int M_PAD>
+template <int M_PAD, bool W4>
 static int launch(const CUtensorMap& w_map, const CUtensorMap& a_map, Params& p, const DeviceInfo& dev, cudaStream_t stream) {
     // Short K, one group, 32 or 64 rows: the activations stay resident if at least six weight stages fit beside them.
     if (M_PAD >= 32 && M_PAD <= 64 && p.tiles_per_group == p.n_tiles && p.kb * Smem<M_PAD>::kABytes <= 96 * 1024) {
         using R = Smem<M_PAD, true>;
         int stages = 16;
-        while (stages > 2 && R::total(stages, p.kb) > dev.smem_optin) stages -= 2;
-        if (stages >= 6 && R::total(stages, p.kb) <= dev.smem_optin) return launch_as<M_PAD, true>(w_map, a_map, p, dev, stages, stream);
+        while (stages > 2 && R::total(stages, p.kb, W4) > dev.smem_optin) stages -= 2;
+        if (stages >= 6 && R::total(stages, p.kb, W4) <= dev.smem_optin) return launch_as<M_PAD, true, W4>(w_map, a_map, p, dev, stages, stream);
     }
     using L = Smem<M_PAD, false>;
     int stages = 16;
     constexpr int kStep = M_PAD >= 128 ? 2 : 4;   // lcm of the producer and issuer counts
-    while (stages > kStep && L::total(stages, p.kb) > dev.smem_optin) stages -= kStep;
-    if (L::total(stages, p.kb) > dev.smem_optin)
+    while (stages > kStep && L::total(stages, p.kb, W4) > dev.smem_optin) stages -= kStep;
+    if (L::total(stages, p.kb, W4) > dev.smem_optin)
         return fail(WUDA_ERR_UNSUPPORTED, "device offers %d bytes of shared memory per block; the kernel needs more",
                     dev.smem_optin);
-    return launch_as<M_PAD, false>(w_map, a_map, p, dev, stages, stream);
+    return launch_as<M_PAD, false, W4>(w_map, a_map, p, dev, stages, stream);
 }
 
-// One pass of at most 128 rows.  groups = 1 is the plain GEMM.
-static int run(const void* a, const float* a_scales, const void* w, const float* w_scales, void* c_bf16, int m, int n_per_group,
-               int k, int groups, void* scratch, int64_t scratch_bytes, int32_t* status_word, void* stream) {
+// One pass of at most 128 rows.  groups = 1 is the plain GEMM.  w_sf != NULL: 4-bit weights (plain form only).
+static int run(const void* a, const float* a_scales, const void* w, const float* w_scales, const uint8_t* w_sf, void* c_bf16, int m,
+               int n_per_group, int k, int groups, void* scratch, int64_t scratch_bytes, int32_t* status_word, void* stream) {
     const int n = n_per_group * groups;
+    const bool w4 = w_sf != nullptr;
     WUDA_REQUIRE(aligned16(a) && aligned16(w), "a and w must be 16-byte aligned");
+    WUDA_REQUIRE(!w4 || ((reinterpret_cast<uintptr_t>(w) & 31u) == 0 && (reinterpret_cast<uintptr_t>(w_sf) & 3u) == 0),
+                 "packed 4-bit weights must be 32-byte aligned and their scale bytes 4-byte aligned");
     WUDA_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "scratch must be 256-byte aligned");
     const int64_t need = wuda_gemm_fp8_scratch_bytes(m, n);
     WUDA_REQUIRE(scratch_bytes >= need, "scratch holds %lld bytes; %lld are needed (wuda_gemm_fp8_scratch_bytes)",
@@ -489,6 +552,8 @@ static int run(const void* a, const float* a_scales, const void* w, const float*
     p.c = static_cast<__nv_bfloat16*>(c_bf16);
     p.a_scales = a_scales;
     p.w_scales = w_scales;
+    p.w_sf = w_sf;
+    p.sf_stride = k / 32;
     p.status = status_word;
     p.M = m;
     p.N = n;
@@ -502,11 +567,12 @@ static int run(const void* a, const float* a_scales, const void* w, const float*
 
     CUtensorMap w_map, a_map;
     {
+        // 4-bit weights: dimensions and box in elements, the row stride in bytes; shared memory gets the padded form
         const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(w4 ? k / 2 : k)};
         const uint32_t box[2] = {128u, 128u};
-        st = encode_tensor_map(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
-                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        st = encode_tensor_map(&w_map, w4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims, strides,
+                               box, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
         if (st != WUDA_OK) return st;
     }
     {
@@ -519,11 +585,19 @@ static int run(const void* a, const float* a_scales, const void* w, const float*
         if (st != WUDA_OK) return st;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (w4) {
+        switch (m_pad) {
+            case 16: return launch<16, true>(w_map, a_map, p, dev, s);
+            case 32: return launch<32, true>(w_map, a_map, p, dev, s);
+            case 64: return launch<64, true>(w_map, a_map, p, dev, s);
+            default: return launch<128, true>(w_map, a_map, p, dev, s);
+        }
+    }
     switch (m_pad) {
-        case 16: return launch<16>(w_map, a_map, p, dev, s);
-        case 32: return launch<32>(w_map, a_map, p, dev, s);
-        case 64: return launch<64>(w_map, a_map, p, dev, s);
-        default: return launch<128>(w_map, a_map, p, dev, s);
+        case 16: return launch<16, false>(w_map, a_map, p, dev, s);
+        case 32: return launch<32, false>(w_map, a_map, p, dev, s);
+        case 64: return launch<64, false>(w_map, a_map, p, dev, s);
+        default: return launch<128, false>(w_map, a_map, p, dev, s);
     }
 }
 
@@ -546,7 +620,7 @@ extern "C" int wuda_gemm_fp8_grouped_pow2(const void* a, const float* a_scales, 
     const int64_t row = static_cast<int64_t>(k) * groups;
     for (int m0 = 0; m0 < m; m0 += 128) {   // a tile holds at most 128 activation rows: passes over the weights
         const int rows = m - m0 < 128 ? m - m0 : 128;
-        const int st = gemm8mx::run(static_cast<const uint8_t*>(a) + m0 * row, a_scales + m0 * (row / 128), w, w_scales,
+        const int st = gemm8mx::run(static_cast<const uint8_t*>(a) + m0 * row, a_scales + m0 * (row / 128), w, w_scales, nullptr,
                                     static_cast<__nv_bfloat16*>(c_bf16) + m0 * n, rows, n_per_group, k, groups, scratch, scratch_bytes,
                                     status_word, stream);
         if (st != WUDA_OK) return st;
@@ -558,4 +632,28 @@ extern "C" int wuda_gemm_fp8_blockscaled_pow2(const void* a, const float* a_scal
                                               int m, int n, int k, void* scratch, int64_t scratch_bytes, int32_t* status_word,
                                               void* stream) {
     return wuda_gemm_fp8_grouped_pow2(a, a_scales, w, w_scales, c_bf16, m, n, k, 1, scratch, scratch_bytes, status_word, stream);
+}
+
+// FP8 activations x 4-bit weights (origin/kernel.py:441-536, fp4_gemm): a e4m3 [m, k] with one power-of-two fp32 scale per
+// row and 128 K-elements; w e2m1 [n, k/2] bytes, the element of the lower K index in the low nibble (torch.float4_e2m1fn_x2),
+// with one exponent byte (float8_e8m0fnu) per row and 32 K-elements, [n, k/32]; c bf16 [m, n].
+extern "C" int wuda_gemm_fp8_fp4_pow2(const void* a, const float* a_scales, const void* w_packed, const void* w_sf, void* c_bf16,
+                                      int m, int n, int k, void* scratch, int64_t scratch_bytes, int32_t* status_word,
+                                      void* stream) {
+    using namespace wuda;
+    clear_error();
+    WUDA_REQUIRE(m >= 0 && m <= 256, "m must be in [0, 256] (got %d)", m);
+    WUDA_REQUIRE(n >= 1, "n must be >= 1 (got %d)", n);
+    WUDA_REQUIRE(k >= 128 && k % 128 == 0, "k must be a positive multiple of 128 (got %d)", k);
+    if (m == 0) return WUDA_OK;
+    WUDA_REQUIRE(a && a_scales && w_packed && w_sf && c_bf16 && scratch, "a, a_scales, w_packed, w_sf, c and scratch must not be NULL");
+    for (int m0 = 0; m0 < m; m0 += 128) {   // a tile holds at most 128 activation rows: passes over the weights
+        const int rows = m - m0 < 128 ? m - m0 : 128;
+        const int st = gemm8mx::run(static_cast<const uint8_t*>(a) + static_cast<int64_t>(m0) * k, a_scales + static_cast<int64_t>(m0) * (k / 128),
+                                    w_packed, nullptr, static_cast<const uint8_t*>(w_sf),
+                                    static_cast<__nv_bfloat16*>(c_bf16) + static_cast<int64_t>(m0) * n, rows, n, k, 1, scratch,
+                                    scratch_bytes, status_word, stream);
+        if (st != WUDA_OK) return st;
+    }
+    return WUDA_OK;
 }

@@ -276,13 +276,14 @@ __device__ __forceinline__ void post_and_comb(float folded, int lane, const floa
 // The tail alone: post and comb from exported mixes (one warp per token), for callers that run it behind
 // another kernel as the reference does (include/front_mixed_gemm.cuh:438-489).
 __global__ void __launch_bounds__(128) mhc_tail_kernel(const float* mix, const float* base, const float* scale, float hc_eps,
-                                                       float* post, float* comb, int m) {
+                                                       float* pre, float* post, float* comb, int m) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (t >= m) return;
     const float folded = lane < kMix ? __ldcg(mix + t * kMix + lane) : 0.f;
+    if (pre && lane < kStreams) pre[t * kStreams + lane] = sigmoid(folded * scale[0] + base[lane]) + hc_eps;
     post_and_comb(folded, lane, scale, base, hc_eps, post + t * kStreams, comb + t * kStreams * kStreams);
 }
 
@@ -573,6 +574,20 @@ extern "C" int wuda_mhc_tail(const float* mix, const float* base, const float* s
     clear_error();
     WUDA_REQUIRE(m >= 1 && mix && base && scale && post && comb, "m >= 1 and every pointer are required");
     WUDA_CUDA(launch_pdl(mhc_tail_kernel, dim3((m + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream), mix, base, scale,
-                         hc_eps, post, comb, m));
+                         hc_eps, static_cast<float*>(nullptr), post, comb, m));
+    return WUDA_OK;
+}
+
+extern "C" int wuda_hc_split_sinkhorn(const float* mixes, const float* scale, const float* base, float hc_eps, float* pre, float* post,
+                                      float* comb, int64_t tokens, void* stream) {
+    using namespace wuda;
+    using namespace wuda::mhcpre;
+    clear_error();
+    WUDA_REQUIRE(tokens >= 0 && tokens <= 0x7fffffff / 32, "tokens out of range");
+    if (tokens == 0) return WUDA_OK;
+    WUDA_REQUIRE(mixes && base && scale && pre && post && comb, "every pointer is required");
+    const int m = static_cast<int>(tokens);
+    WUDA_CUDA(launch_pdl(mhc_tail_kernel, dim3((m + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream), mixes, base, scale,
+                         hc_eps, pre, post, comb, m));
     return WUDA_OK;
 }

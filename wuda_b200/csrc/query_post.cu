@@ -317,6 +317,50 @@ extern "C" int wuda_index_q_post_fp4(const void* iq_bf16, int64_t row_stride, co
     return WUDA_OK;
 }
 
+namespace wuda {
+namespace qp {
+// Sum of squares of every 512-value head of bf16 rows, one warp per head (kernels/wq_b_fp8_gemm.cu:101-123): lane l
+// chains fused multiply-adds over values [16 l, 16 l + 16), then a butterfly over lane distances 16, 8, 4, 2, 1.
+__global__ void __launch_bounds__(256) head_ssq_kernel(const __nv_bfloat16* y, int64_t row_stride, float* ssq, int64_t total, int heads) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t h = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (h >= total) return;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = h / heads;
+    const __nv_bfloat16* src = y + row * row_stride + (h - row * heads) * 512 + lane * 16;
+    const uint4 a = *reinterpret_cast<const uint4*>(src), b = *reinterpret_cast<const uint4*>(src + 8);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xffff0000u);
+        s = __fmaf_rn(lo, lo, s);
+        s = __fmaf_rn(hi, hi, s);
+    }
+#pragma unroll
+    for (int x = 16; x >= 1; x >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, x));
+    if (lane == 0) ssq[h] = s;
+}
+}  // namespace qp
+}  // namespace wuda
+
+extern "C" int wuda_head_ssq(const void* y_bf16, int64_t row_stride, float* ssq, int64_t rows, int heads, void* stream) {
+    using namespace wuda;
+    using namespace wuda::qp;
+    clear_error();
+    WUDA_REQUIRE(rows >= 0 && heads >= 1, "rows must be >= 0 and heads >= 1");
+    WUDA_REQUIRE(row_stride >= static_cast<int64_t>(heads) * 512 && row_stride % 8 == 0,
+                 "row_stride must be >= heads * 512 and a multiple of 8 elements");
+    if (rows == 0) return WUDA_OK;
+    WUDA_REQUIRE(y_bf16 && ssq && aligned16(y_bf16), "y (16-byte aligned) and ssq must not be NULL");
+    const int64_t total = rows * heads;
+    WUDA_REQUIRE((total + 7) / 8 <= 0x7fffffff, "too many heads for one launch");
+    WUDA_CUDA(launch_pdl(head_ssq_kernel, dim3(static_cast<unsigned>((total + 7) / 8)), dim3(256), 0,
+                         static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(y_bf16), row_stride, ssq, total, heads));
+    return WUDA_OK;
+}
+
 extern "C" int wuda_query_rms_rope(const void* x_bf16, int64_t row_stride, const int64_t* positions,
                                    const float* cos_table, const float* sin_table, int max_pos, void* out_bf16,
                                    int tokens, int input_heads, int output_heads, float eps, void* stream) {

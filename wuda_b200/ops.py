@@ -15,7 +15,9 @@ from ._lib import WudaError, check, lib
 
 __all__ = ["mqa_logits_fp4_decode_out", "mqa_logits_fp4_decode", "mqa_logits_fp8_decode_out", "fp8_paged_mqa_logits", "topk_v2", "topk_v2_transform",
            "IndexerHostPlan", "sparse_mla_decode", "flash_mla_with_kvcache", "device_status_word", "num_sms", "rmsnorm_quant", "act_quant", "rope_quant",
-           "rmsnorm_rope_out", "mhc_post_out", "mhc_pre", "moe_gate", "bf16_gemm", "front_mixed_gemm", "idx_postprocess_fp8", "idx_postprocess", "cache_writers_fp8", "cache_writers_fp4", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm"]
+           "rmsnorm_rope_out", "mhc_post_out", "mhc_pre", "moe_gate", "bf16_gemm", "front_mixed_gemm", "idx_postprocess_fp8", "idx_postprocess", "cache_writers_fp8", "cache_writers_fp4", "mqa_compressor_fp8_standalone", "fp8_gemm", "TP2Link", "exchange_handles", "nvfp4_gemm",
+           "fp4_gemm", "fp4_act_quant", "hc_split_sinkhorn", "head_ssq_standalone", "idx_postprocess_standalone",
+           "idx_postprocess_fp8_standalone", "mqa_compressor_standalone", "mqa_compressor_paged", "topk_v2_plan"]
 
 NUM_INDEX_HEADS = 64
 INDEX_HEAD_DIM = 128
@@ -172,6 +174,16 @@ def topk_v2_transform(scores, seq_lens, page_table, page_indices, page_size=64, 
                         raw_indices.data_ptr() if raw_indices is not None else None, rows, scores.stride(0),
                         page_table.stride(0), int(rows_per_table_row), k, int(page_size), _stream()))
     return page_indices
+
+
+def topk_v2_plan(seq_lens, metadata, static_cluster_threshold=0):
+    """The reference's plan call (kernels/topk_v2.cu:329-345) checks its arguments and fills `metadata` int32
+    [B + 1, 2] with the rows it gives to clusters.  The kernel of this library decides that per row at launch and
+    needs no plan: the arguments are checked the same way and `metadata` is left as it is."""
+    _require(seq_lens.is_cuda and seq_lens.is_contiguous() and seq_lens.dtype == torch.int32,
+             "seq_lens must be CUDA i32 [B]")
+    _require(metadata.is_cuda and metadata.is_contiguous() and metadata.dtype == torch.int32
+             and metadata.numel() == 2 * (seq_lens.numel() + 1), "metadata must be CUDA i32 [B+1, 2]")
 
 
 def topk_v2(scores, seq_lens, page_table, topk, page_size=64, raw_indices=None, *, rows_per_table_row=1):
@@ -525,6 +537,34 @@ def mqa_compressor_fp8_standalone(cmp_pos, comp_norm, cos_tab, sin_tab, comp_sta
                                 ring_entries=comp_state_ring_entries, q8=comp_q8, s8=comp_s8, rope=comp_rope))
 
 
+def mqa_compressor_standalone(cmp_pos, comp_norm, cos_tab, sin_tab, comp_state, comp_state_row, comp_state_ring_entries,
+                              comp_q8, comp_s8, comp_rope, eps=1e-6):
+    """The same call under the name the FP4 logits module exports (kernels/mqa_logits_fp4.cu:653-680)."""
+    rows = cmp_pos.numel()      # the reference takes int32 row numbers here; the writers take int64
+    mqa_compressor_fp8_standalone(cmp_pos, comp_norm, cos_tab, sin_tab, comp_state,
+                                  comp_state_row.reshape(-1)[:rows].to(torch.int64), comp_state_ring_entries, comp_q8,
+                                  comp_s8, comp_rope, eps)
+
+
+def mqa_compressor_paged(cmp_pos, comp_norm, cos_tab, sin_tab, comp_state, comp_state_row, comp_state_ring_entries,
+                         cmp_cache, cmp_dst, cmp_entries_per_block, cmp_block_stride_bytes, eps=1e-6):
+    """The MAIN compressor writing its 584-byte records straight into the pool's pages, with the reference's
+    argument list and checks (kernels/mqa_logits_fp4.cu:681-750): cmp_cache uint8 pages of cmp_block_stride_bytes,
+    cmp_dst[r] = the physical entry row r goes to (negative: nowhere)."""
+    _require(cmp_entries_per_block > 0 and cmp_block_stride_bytes >= cmp_entries_per_block * 584
+             and cmp_cache.is_cuda and cmp_cache.is_contiguous() and cmp_cache.dtype == torch.uint8
+             and cmp_cache.numel() % cmp_block_stride_bytes == 0, "cmp_cache physical page geometry is invalid")
+    _require(cmp_dst.is_cuda and cmp_dst.is_contiguous() and cmp_dst.numel() >= cmp_pos.numel(),
+             "cmp_dst must be a contiguous CUDA integer tensor [>=B]")
+    rows = cmp_pos.numel()      # the reference takes int32 row numbers and destinations; the writers take int64
+    cache_writers_fp8(cmp_pos, cos_tab, sin_tab, eps=eps,
+                      main=dict(state=comp_state, state_row=comp_state_row.reshape(-1)[:rows].to(torch.int64),
+                                norm_w=comp_norm, ring_entries=comp_state_ring_entries,
+                                pool=cmp_cache.view(-1, cmp_block_stride_bytes),
+                                dst=cmp_dst.reshape(-1)[:rows].to(torch.int64),
+                                entries_per_block=int(cmp_entries_per_block)))
+
+
 def rmsnorm_rope_out(x, positions, cos_table, sin_table, out, input_heads=None, eps=1e-6, pdl=False, max_blocks=0):
     """Per-head RMSNorm (no gamma) + RoPE on the last 64 dims, bf16 -> bf16 in one pass with one
     rounding, with the reference's signature (kernels/rmsnorm_prod.cu:160-167).  `x` is
@@ -600,6 +640,104 @@ def idx_postprocess(iq, q_pos, rope_cos, rope_sin, iq_fp4=None, iq_sf=None):
     return iq_fp4, iq_sf
 
 
+def idx_postprocess_standalone(iq_f32, q_pos, rope_cos, rope_sin):
+    """idx_postprocess under the name the q-projection module exports (kernels/wq_b_fp8_gemm.cu:1474-1507): iq bf16
+    [M, 64, 128] (an fp32 tensor is rounded to bf16 first, which is what the projection's epilogue would have
+    stored).  Returns (iq_fp4 int8 [M, 64, 64], iq_sf int32 [M, 64])."""
+    return idx_postprocess(iq_f32 if iq_f32.dtype == torch.bfloat16 else iq_f32.bfloat16(), q_pos, rope_cos, rope_sin)
+
+
+def idx_postprocess_fp8_standalone(iq, weights, q_pos, rope_cos, rope_sin):
+    """idx_postprocess_fp8 under the reference's export name (kernels/wq_b_fp8_gemm.cu:1509-1546).  Returns
+    (q e4m3 [M, 64, 128], weights * scale fp32 [M, 64])."""
+    return idx_postprocess_fp8(iq if iq.dtype == torch.bfloat16 else iq.bfloat16(), weights, q_pos, rope_cos, rope_sin)
+
+
+def head_ssq_standalone(y, num_heads=None):
+    """Per (row, head) sum of squares over the bf16 main q [M, heads * 512] -> fp32 [M, heads]
+    (kernels/wq_b_fp8_gemm.cu:101-123, 1548-1566), in the reference kernel's summation order."""
+    _require(y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.stride(1) == 1 and y.size(1) % 512 == 0,
+             "y must be CUDA bf16 [M, heads * 512] with unit inner stride")
+    heads = y.size(1) // 512 if num_heads is None else int(num_heads)
+    _require(heads * 512 <= y.size(1), "y has fewer than num_heads heads")
+    ssq = torch.empty((y.size(0), heads), dtype=torch.float32, device=y.device)
+    check(lib.wuda_head_ssq(y.data_ptr(), y.stride(0), ssq.data_ptr(), y.size(0), heads, _stream()))
+    return ssq
+
+
+def hc_split_sinkhorn(mixes, hc_scale, hc_base, hc_mult=4, sinkhorn_iters=20, eps=1e-6):
+    """The origin's hc_split_sinkhorn (origin/kernel.py:430-436): mixes fp32 [b, s, 24] -> (pre [b, s, 4], post
+    [b, s, 4], comb [b, s, 4, 4])."""
+    _require(hc_mult == 4 and sinkhorn_iters == 20, "hc_mult 4 and 20 Sinkhorn iterations are what is built")
+    _require(mixes.is_cuda and mixes.is_contiguous() and mixes.dtype == torch.float32 and mixes.size(-1) == 24,
+             "mixes must be contiguous CUDA fp32 [..., 24]")
+    _require(hc_scale.is_cuda and hc_scale.is_contiguous() and hc_scale.dtype == torch.float32 and hc_scale.numel() == 3
+             and hc_base.is_cuda and hc_base.is_contiguous() and hc_base.dtype == torch.float32 and hc_base.numel() == 24,
+             "hc_scale fp32 [3] and hc_base fp32 [24] must be contiguous CUDA tensors")
+    lead = mixes.shape[:-1]
+    pre, post = mixes.new_empty(*lead, 4), mixes.new_empty(*lead, 4)
+    comb = mixes.new_empty(*lead, 4, 4)
+    check(lib.wuda_hc_split_sinkhorn(mixes.data_ptr(), hc_scale.data_ptr(), hc_base.data_ptr(), float(eps), pre.data_ptr(),
+                                     post.data_ptr(), comb.data_ptr(), mixes.numel() // 24, _stream()))
+    return pre, post, comb
+
+
+def fp4_act_quant(x, block_size=32, inplace=False):
+    """Block-wise FP4 quantisation with the origin's signature (origin/kernel.py:186-200): returns (y
+    float4_e2m1fn_x2 [..., N/2], scales float8_e8m0fnu [..., N/32]); inplace=True overwrites x with the
+    dequantised values and returns it."""
+    _require(block_size == 32, "block_size must be 32")
+    _require(x.is_cuda and x.dtype == torch.bfloat16 and x.size(-1) % 32 == 0, "x must be CUDA bf16 [..., N], N % 32 == 0")
+    n = x.size(-1)
+    z = x if (inplace and x.is_contiguous()) else x.contiguous()
+    rows = z.numel() // n
+    if inplace:
+        check(lib.wuda_fp4_act_quant(z.data_ptr(), n, None, None, 1, rows, n, _stream()))
+        if z.data_ptr() != x.data_ptr():
+            x.copy_(z)
+        return x
+    y = torch.empty(*z.shape[:-1], n // 2, dtype=torch.uint8, device=x.device)
+    sc = torch.empty(*z.shape[:-1], n // 32, dtype=torch.uint8, device=x.device)
+    check(lib.wuda_fp4_act_quant(z.data_ptr(), n, y.data_ptr(), sc.data_ptr(), 0, rows, n, _stream()))
+    fp4 = getattr(torch, "float4_e2m1fn_x2", None)
+    e8 = getattr(torch, "float8_e8m0fnu", None)
+    return (y.view(fp4) if fp4 is not None else y), (sc.view(e8) if e8 is not None else sc)
+
+
+def _scales_as_fp32(t, name):
+    """fp32 scales as they are; float8_e8m0fnu (or raw exponent bytes) -> the fp32 power of two, exactly."""
+    if t.dtype == torch.float32:
+        return t
+    _require(t.element_size() == 1, name + " must be fp32 or one exponent byte per scale")
+    return (t.view(torch.uint8).to(torch.int32) << 23).view(torch.float32)
+
+
+def fp4_gemm(a, a_s, b, b_s, scale_dtype=torch.float32, *, out=None, status_word=None):
+    """C[M,N] = A_fp8[M,K] @ B_fp4[N,K]^T with the origin's signature (origin/kernel.py:518-536): a e4m3, a_s one
+    POWER-OF-TWO scale per row and 128 K-elements (fp32 or float8_e8m0fnu: act_quant with scale_fmt "ue8m0"), b
+    float4_e2m1fn_x2 [N, K/2], b_s float8_e8m0fnu [N, K/32].  bf16 output."""
+    _require(a.is_cuda and a.is_contiguous() and a.dtype == torch.float8_e4m3fn, "a must be contiguous CUDA e4m3")
+    _require(b.is_cuda and b.is_contiguous() and b.element_size() == 1 and b.dim() == 2,
+             "b must be contiguous CUDA float4_e2m1fn_x2 (or bytes) [N, K/2]")
+    k = a.size(-1)
+    m = a.numel() // k
+    n = b.size(0)
+    _require(b.size(1) * 2 == k and k % 128 == 0, "a and b disagree on K, or K is not a multiple of 128")
+    _require(a_s.is_cuda and a_s.is_contiguous() and a_s.numel() == m * (k // 128), "a_s must be contiguous CUDA [M, K/128]")
+    _require(b_s.is_cuda and b_s.is_contiguous() and b_s.element_size() == 1 and tuple(b_s.shape) == (n, k // 32),
+             "b_s must be contiguous CUDA float8_e8m0fnu (or bytes) [N, K/32]")
+    a_sf = _scales_as_fp32(a_s, "a_s")
+    if out is None:
+        out = torch.empty(*a.shape[:-1], n, dtype=torch.bfloat16, device=a.device)
+    need = lib.wuda_gemm_fp8_scratch_bytes(m, n)
+    _require(need >= 0, "m must be in [1, 256]")
+    scratch = _scratch_for(a.device, need)
+    check(lib.wuda_gemm_fp8_fp4_pow2(a.data_ptr(), a_sf.data_ptr(), b.data_ptr(), b_s.data_ptr(), out.data_ptr(), m, n, k,
+                                     scratch.data_ptr(), scratch.numel(),
+                                     status_word.data_ptr() if status_word is not None else None, _stream()))
+    return out
+
+
 _gemm_scratch = {}
 
 
@@ -617,7 +755,8 @@ def fp8_gemm(a, a_s, b, b_s, scale_dtype=torch.float32, *, out=None, status_word
     output: the origin's fp8_gemm(a, a_s, b, b_s) (origin/kernel.py:257-273).  pow2_scales=True promises that
     every scale is a power of two (the reference's UE8M0 scales) and takes the kernel that applies them inside
     the tensor core."""
-    _require(scale_dtype == torch.float32, "only fp32 scales are implemented")
+    if a_s.dtype != torch.float32 or b_s.dtype != torch.float32:     # float8_e8m0fnu scales: powers of two by type
+        a_s, b_s, pow2_scales = _scales_as_fp32(a_s, "a_s"), _scales_as_fp32(b_s, "b_s"), True
     _require(a.is_cuda and a.is_contiguous() and a.dtype == torch.float8_e4m3fn, "a must be contiguous CUDA e4m3")
     _require(b.is_cuda and b.is_contiguous() and b.dtype == torch.float8_e4m3fn and b.dim() == 2,
              "b must be contiguous CUDA e4m3 [N, K]")
