@@ -551,6 +551,37 @@ def kv_script(seed, capacity, steps):
     return ops
 
 
+def golden_fp4_gemm(ref_root):
+    """FP8 activations x FP4 weights.  The weights are quantised by the reference test's per_token_cast_to_fp4 (e2m1,
+    one ue8m0 scale per 32), turned into the origin's lossless e4m3 form with 128x128 scales by its own
+    cast_e2m1fn_to_e4m3fn (origin/convert.py:20-52: this is what fixes the nibble order, the code table and the
+    meaning of the scale bytes), and dequantised by the test's cast_back_from_fp4; the activations by quant_act_fp8
+    with power-of-two scales.  Expected output: the double-precision product of the dequantised operands."""
+    ref_mqa = _load(ref_root, "dsv4_megakernel/megakernel/test/test_mqa_logits_fp4.py", "ref_mqa_fp4gemm")
+    conv = _load(ref_root, "dsv4_megakernel/origin/convert.py", "ref_origin_convert")
+    conv.torch = torch
+    g = torch.Generator().manual_seed(97)
+    m, n, k = 24, 256, 512
+    w = (torch.randn(n, k, generator=g) * 0.05 * torch.exp(torch.randn(n, 1, generator=g) * 0.7)).bfloat16().float()
+    packed, sf_words = ref_mqa.per_token_cast_to_fp4(w.float(), use_ue8m0=True, gran_k=32, use_packed_ue8m0=True)
+    sf_bytes = sf_words.contiguous().view(torch.uint8).view(n, k // 32)
+    w_deq = ref_mqa.cast_back_from_fp4(packed, sf_words)
+    scale_f = (sf_bytes.to(torch.int32) << 23).view(torch.float32)
+    w8, w8_scale = conv.cast_e2m1fn_to_e4m3fn(packed.contiguous(), scale_f)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    xb = x.view(m, k // 128, 128).float()
+    amax = xb.abs().amax(-1).clamp_min(1e-4)
+    a_s = torch.exp2(torch.ceil(torch.log2(amax / 448.0)))
+    a8 = (xb / a_s[..., None]).to(torch.float8_e4m3fn)
+    a_deq = (a8.float() * a_s[..., None]).view(m, k)
+    c = a_deq.double() @ w_deq.double().T
+    np.savez_compressed(os.path.join(HERE, "fp4_gemm.npz"), a=a8.view(m, k).view(torch.uint8).numpy(), a_s=a_s.numpy(),
+                        w4=packed.view(torch.uint8).numpy(), w_sf=sf_bytes.numpy(),
+                        w8=w8.view(torch.uint8).numpy(), w8_scale=w8_scale.float().numpy(), w_deq=w_deq.numpy(), w=w.numpy(),
+                        c=c.float().numpy())
+    print("fp4_gemm.npz", m, n, k)
+
+
 def golden_kv_cache(ref_root):
     import gzip
     import json
@@ -595,6 +626,7 @@ def main():
     golden_query_rms_rope()
     golden_main_compressor()
     golden_moe_block(ref_root)
+    golden_fp4_gemm(ref_root)
 
 
 if __name__ == "__main__":

@@ -388,3 +388,32 @@ def test_moe_block_oracle_matches_the_origin_module(name):
     got, want = oracle.bf16_to_f32(y), oracle.bf16_to_f32(g["y_" + name])
     assert np.all(np.abs(got - want) <= 2.0 ** -7 * np.abs(want) + 2.0 ** -8 * np.abs(want).max())
     assert np.mean(y == g["y_" + name]) >= 0.9
+
+
+def test_fp4_gemm_oracle_matches_the_origin_lossless_cast_and_the_reference_dequantiser():
+    """Fixture: weights quantised by the reference test's per_token_cast_to_fp4, dequantised by its
+    cast_back_from_fp4, and cast to e4m3 with 128x128 scales by the origin's cast_e2m1fn_to_e4m3fn
+    (origin/convert.py:20-52).  The oracle's FP8 x FP4 product must equal the product of the dequantised operands,
+    and so must its FP8 product over the origin's lossless cast: nibble order, code table and the meaning of the
+    scale bytes are the reference's."""
+    g = load_golden("fp4_gemm.npz")
+    ref = g["c"]
+    rms = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+    c4 = oracle.gemm_fp8_fp4(g["a"], g["a_s"], g["w4"], g["w_sf"], out_bf16=False)
+    c8 = oracle.gemm_fp8_blockscaled(g["a"], g["a_s"], g["w8"], g["w8_scale"], out_bf16=False)
+    assert np.all(np.abs(c4 - ref) <= 1e-6 * rms) and np.all(np.abs(c8 - ref) <= 1e-6 * rms)
+    # the dequantised weights themselves: code table and scale bytes
+    codes = np.stack([g["w4"] & 15, g["w4"] >> 4], -1).reshape(g["w_deq"].shape)
+    table = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, 0, -.5, -1, -1.5, -2, -3, -4, -6], np.float32)
+    assert np.array_equal(table[codes] * np.repeat(np.exp2(g["w_sf"].astype(np.float32) - 127), 32, 1), g["w_deq"])
+    # the oracle's quantiser on the values the reference's quantiser saw (bf16-representable): the same scale bytes
+    # (2^ceil(log2(amax / 6))); the same codes except at exact rounding ties, which the test's bucketize sends down
+    # and the hardware conversion the oracle follows to the even code
+    oc, osf, _ = oracle.fp4_act_quant(oracle.f32_to_bf16(g["w"]))
+    assert np.array_equal(osf, g["w_sf"])
+    mine = np.stack([oc & 15, oc >> 4], -1).reshape(g["w"].shape)
+    scaled = np.abs(g["w"]) / np.repeat(np.exp2(g["w_sf"].astype(np.float32) - 127), 32, 1)
+    tie = np.isin(scaled, [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+    mine = np.where((mine & 7) == 0, 0, mine)        # the hardware conversion keeps the sign of a zero, the test drops it
+    assert np.array_equal(mine[~tie], codes[~tie]) and np.mean(mine == codes) > 0.98
+    assert np.all((mine[tie] & 7).astype(int) - (codes[tie] & 7).astype(int) >= 0)

@@ -11,6 +11,7 @@ import pytest
 import torch
 
 import oracle
+from conftest import load_golden
 
 pytestmark = pytest.mark.gpu
 
@@ -46,6 +47,28 @@ def check_fp4_gemm(wuda, m, n, k, seed):
     err = np.abs(got - ref)
     assert np.all(err <= 2.0 ** -7 * np.abs(ref) + 2e-3 * rms), (m, n, k, float(err.max()), float(rms))
     return out
+
+
+def test_fp4_gemm_golden(wuda):
+    """The fixture made with the reference's FP4 quantiser / dequantiser and the origin's lossless cast to e4m3
+    (origin/convert.py:20-52): the FP4 GEMM, and the FP8 GEMM over the cast weights, against the product of the
+    dequantised operands; the GPU quantiser against the reference's scale bytes."""
+    g = load_golden("fp4_gemm.npz")
+    a = cu(g["a"]).view(torch.float8_e4m3fn)
+    status = wuda.device_status_word()
+    c4 = wuda.fp4_gemm(a, cu(g["a_s"]), cu(g["w4"]), cu(g["w_sf"]), status_word=status)
+    c8 = wuda.fp8_gemm(a, cu(g["a_s"]), cu(g["w8"]).view(torch.float8_e4m3fn), cu(g["w8_scale"]), pow2_scales=True,
+                       status_word=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = g["c"]
+    rms = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+    for got in (c4, c8):
+        assert np.all(np.abs(got.float().cpu().numpy() - ref) <= 2.0 ** -8 * np.abs(ref) + 1e-5 * rms)   # one bf16 rounding
+    assert torch.equal(c4, c8)
+    codes, sf = wuda.fp4_act_quant(torch.from_numpy(g["w"]).bfloat16().cuda())
+    assert np.array_equal(sf.view(torch.uint8).cpu().numpy(), g["w_sf"])
+    assert np.mean(codes.view(torch.uint8).cpu().numpy() == g["w4"]) > 0.9     # signs of zeros and ties differ
 
 
 @pytest.mark.parametrize("m", [1, 8, 32, 64, 128, 256])
