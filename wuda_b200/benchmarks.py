@@ -808,6 +808,18 @@ def one(kind, m, n, k, launches=5):
         if kind == "gemm_fp8_pow2":
             a_s, w_s = torch.exp2(torch.log2(a_s).round()), torch.exp2(torch.log2(w_s).round())
         fn = lambda: wuda.fp8_gemm(a, a_s, w, w_s, pow2_scales=kind == "gemm_fp8_pow2")
+    elif kind == "gemm_fp8_fp4":
+        gen = torch.Generator(device="cuda").manual_seed(7)
+        a = torch.randint(0, 0x78, (m, k), dtype=torch.uint8, device="cuda", generator=gen).view(torch.float8_e4m3fn)
+        a_s = torch.exp2(torch.randint(-4, 4, (m, k // 128), device="cuda", generator=gen).float())
+        # a different weight buffer per launch, together larger than L2
+        ws = [torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda", generator=gen) for _ in range(launches)]
+        w_sf = torch.randint(118, 126, (n, k // 32), dtype=torch.uint8, device="cuda", generator=gen)
+        state = {"i": 0}
+
+        def fn():
+            wuda.fp4_gemm(a, a_s, ws[state["i"] % launches], w_sf)
+            state["i"] += 1
     else:
         c = workloads.make_gemm_nvfp4_case(m, n, k, seed=7)
         a, w, a_sf, w_sf = t(c["a"]), t(c["w"]), t(c["a_sf_packed"]), t(c["w_sf_packed"])
