@@ -83,8 +83,7 @@ def test_fp4_gemm_small_every_row_count(wuda, m):
                                    (64, 384, 128), (8, 512, 640), (64, 256, 1920), (256, 2048, 2048)])
 def test_fp4_gemm_shapes(wuda, m, n, k):
     """The origin's expert shapes (w1/w3: 2048 x 7168 pairs, w2: 7168 x 2048), ragged N, short K (activations resident
-    in shared memory), one K block, an odd number of K blocks (the weights then arrive in the copy engine's padded
-    form instead of packed pairs), two passes of 128 rows."""
+    in shared memory), one K block, an odd number of K blocks, two passes of 128 rows."""
     check_fp4_gemm(wuda, m, n, k, m * 7 + n)
 
 
