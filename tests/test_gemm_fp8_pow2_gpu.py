@@ -137,3 +137,21 @@ def test_repeated_calls_share_a_scratch_with_the_general_kernel(wuda):
         out = wuda.fp8_gemm(a, torch.from_numpy(case["a_s"]).cuda(), w, torch.from_numpy(case["w_s"]).cuda())
         torch.cuda.synchronize()
         close(out.cpu().view(torch.int16).numpy().view(np.uint16), ref[m])
+
+
+def test_exponent_byte_scales_take_the_same_path(wuda):
+    """The origin passes float8_e8m0fnu scales (origin/kernel.py:257-273, scale_dtype): fp8_gemm converts the bytes to
+    the fp32 powers of two they stand for and applies them in the tensor core; same bytes out as with fp32 scales."""
+    case = make(33, 640, 1024, 17)
+    a = torch.from_numpy(case["a"]).cuda().view(torch.float8_e4m3fn)
+    w = torch.from_numpy(case["w"]).cuda().view(torch.float8_e4m3fn)
+    a_s, w_s = torch.from_numpy(case["a_s"]).cuda(), torch.from_numpy(case["w_s"]).cuda()
+    want = wuda.fp8_gemm(a, a_s, w, w_s, pow2_scales=True)
+    exps = lambda t: ((t.view(torch.int32) >> 23) & 0xFF).to(torch.uint8)
+    e8 = getattr(torch, "float8_e8m0fnu", None)
+    a_e, w_e = exps(a_s), exps(w_s)
+    if e8 is not None:
+        a_e, w_e = a_e.view(e8), w_e.view(e8)
+    got = wuda.fp8_gemm(a, a_e, w, w_e, e8 if e8 is not None else torch.float32)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
