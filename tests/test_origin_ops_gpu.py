@@ -116,7 +116,7 @@ def test_fp4_gemm_reports_a_scale_that_is_no_power_of_two(wuda):
         wuda.fp4_gemm(cu(a8).view(torch.float8_e4m3fn), cu(a_s), cu(codes[:, :64]), cu(sf))
 
 
-@pytest.mark.parametrize("rows,cols,seed", [(1, 32, 1), (7, 128, 2), (64, 7168, 3), (300, 512, 4)])
+@pytest.mark.parametrize("rows,cols,seed", [(1, 32, 1), (7, 128, 2), (64, 7168, 3), (300, 512, 4), (2049, 7168, 5)])
 def test_fp4_act_quant_against_oracle(wuda, rows, cols, seed):
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((rows, cols)) * np.exp(rng.standard_normal((rows, 1)) * 4)

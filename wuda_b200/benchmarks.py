@@ -180,6 +180,20 @@ def norm_rope_quant():
         us = time_graph(lambda: wuda.rope_quant(proj, pos, cos, sin, 64))
         by = tokens * 24576 * 2 + tokens * 8 + tokens * 24576 + tokens * 192 * 4
         print("rope_quant    tokens %4d: %7.2f us %7.0f GB/s" % (tokens, us, by / us / 1e3))
+    # FP4 quantisation (the origin's fp4_act_quant): the indexer's keys in place, and a weight matrix larger than L2
+    for rows, cols, inplace in ((64, 7168, False), (64 * 128, 128, True), (24576, 7168, False)):
+        copies = 1 if rows * cols < (1 << 24) else 3
+        xs = [torch.randn(rows, cols, device="cuda").bfloat16() for _ in range(copies)]
+        state = {"i": 0}
+
+        def fn():
+            wuda.fp4_act_quant(xs[state["i"] % copies], 32, inplace)
+            state["i"] += 1
+
+        us = time_graph(fn, inner=copies * 2)
+        by = rows * cols * (4 if inplace else 2) + (0 if inplace else rows * cols * 17 // 32)
+        print("fp4_act_quant %6d x %5d%s: %7.2f us %7.0f GB/s = %.2f of HBM" %
+              (rows, cols, " in place" if inplace else "         ", us, by / us / 1e3, by / us / 1e3 / hbm))
 
 
 def tp2():

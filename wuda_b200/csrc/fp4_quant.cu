@@ -7,8 +7,8 @@
 // scale's exponent byte (torch.float8_e8m0fnu), or - `inplace` - writes code * scale back over x as bf16 (the
 // quantise-dequantise the origin applies to the indexer's keys and queries, origin/model.py:370,416).
 //
-// Four lanes share a block (8 values = one 16-byte load each); a row is walked by as many lanes as it has blocks
-// times four.  Pure streaming: 2 bytes in, 17/32 byte out per value (or 2 in, 2 out in place).
+// Four lanes share a block (8 values = one 16-byte load each); a thread has four such loads of different blocks in
+// flight.  Pure streaming: 2 bytes in, 17/32 byte out per value (or 2 in, 2 out in place).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -50,56 +50,69 @@ struct Params {
     int blocks_per_row;
 };
 
+// kPieces: 16-byte pieces (of kPieces different blocks) a thread has in flight: four for inputs that fill the device
+// several times over, one for the small ones, where more CTAs matter more
+template <int kPieces>
 __global__ void __launch_bounds__(kThreads) fp4_act_quant_kernel(Params p) {
     pdl_launch_dependents();
     pdl_wait();
+    // piece = 8 values = a quarter of a block; thread t of the grid takes pieces t, t + T, t + 2 T, .. (T = all
+    // threads), so a warp's loads are contiguous and the four lanes of a block stay neighbours
+    const int64_t threads = static_cast<int64_t>(gridDim.x) * kThreads;
     const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-    const int64_t blk = t >> 2;
     const int sub = static_cast<int>(t & 3);
-    const bool live = blk < p.blocks;
-    float v[8];
-    int64_t row = 0;
-    int col = 0;
-    if (live) {
-        row = blk / p.blocks_per_row;
-        col = static_cast<int>(blk - row * p.blocks_per_row) * 32 + sub * 8;
-        const uint4 raw = *reinterpret_cast<const uint4*>(p.x + row * p.row_stride + col);
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint4 raw[kPieces];
+    int64_t blk[kPieces], row[kPieces];
+    int col[kPieces];
+#pragma unroll
+    for (int j = 0; j < kPieces; ++j) {
+        blk[j] = (t + j * threads) >> 2;
+        raw[j] = make_uint4(0u, 0u, 0u, 0u);
+        row[j] = 0;
+        col[j] = 0;
+        if (blk[j] < p.blocks) {
+            row[j] = blk[j] / p.blocks_per_row;
+            col[j] = static_cast<int>(blk[j] - row[j] * p.blocks_per_row) * 32 + sub * 8;
+            raw[j] = *reinterpret_cast<const uint4*>(p.x + row[j] * p.row_stride + col[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kPieces; ++j) {
+        const bool live = blk[j] < p.blocks;      // the same for the four lanes of a block
+        const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+        float v[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             v[2 * i] = __uint_as_float(w[i] << 16);
             v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
         }
-    } else {
+        float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 0.f;
-    }
-    float amax = 0.f;
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, 6.0f * 1.1754944e-38f);
+        const uint32_t rbits = __float_as_uint(__fmul_rn(amax, 1.0f / 6.0f));
+        const int e = static_cast<int>((rbits >> 23) & 0xffu) - 127 + ((rbits & 0x7fffffu) ? 1 : 0);
+        const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);   // 2^-e: e <= 126 for bf16 input
+        uint32_t packed = 0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    amax = fmaxf(amax, 6.0f * 1.1754944e-38f);
-    const uint32_t rbits = __float_as_uint(__fmul_rn(amax, 1.0f / 6.0f));
-    const int e = static_cast<int>((rbits >> 23) & 0xffu) - 127 + ((rbits & 0x7fffffu) ? 1 : 0);
-    const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);   // 2^-e: e <= 126 for bf16 input
-    uint32_t packed = 0;
+        for (int i = 0; i < 4; ++i) packed |= pack_e2m1x2(v[2 * i] * inv, v[2 * i + 1] * inv) << (8 * i);
+        if (!live) continue;
+        if (p.y_inplace) {
+            const float scale = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
+            uint32_t o[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) packed |= pack_e2m1x2(v[2 * i] * inv, v[2 * i + 1] * inv) << (8 * i);
-    if (!live) return;
-    if (p.y_inplace) {
-        const float scale = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t byte = (packed >> (8 * i)) & 0xffu;
-            const __nv_bfloat162 pair = __floats2bfloat162_rn(e2m1_value(byte & 15u) * scale, e2m1_value(byte >> 4) * scale);
-            w[i] = *reinterpret_cast<const uint32_t*>(&pair);
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t byte = (packed >> (8 * i)) & 0xffu;
+                const __nv_bfloat162 pair = __floats2bfloat162_rn(e2m1_value(byte & 15u) * scale, e2m1_value(byte >> 4) * scale);
+                o[i] = *reinterpret_cast<const uint32_t*>(&pair);
+            }
+            *reinterpret_cast<uint4*>(p.y_inplace + row[j] * p.row_stride + col[j]) = make_uint4(o[0], o[1], o[2], o[3]);
+        } else {
+            *reinterpret_cast<uint32_t*>(p.codes + blk[j] * 16 + sub * 4) = packed;
+            if (sub == 0) p.scales[blk[j]] = static_cast<uint8_t>(e + 127);
         }
-        *reinterpret_cast<uint4*>(p.y_inplace + row * p.row_stride + col) = make_uint4(w[0], w[1], w[2], w[3]);
-    } else {
-        *reinterpret_cast<uint32_t*>(p.codes + blk * 16 + sub * 4) = packed;
-        if (sub == 0) p.scales[blk] = static_cast<uint8_t>(e + 127);
     }
 }
 
@@ -125,9 +138,14 @@ extern "C" int wuda_fp4_act_quant(const void* x_bf16, int64_t row_stride, void* 
     p.row_stride = row_stride;
     p.blocks_per_row = cols / 32;
     p.blocks = rows * p.blocks_per_row;
-    const int64_t grid = (p.blocks * 4 + kThreads - 1) / kThreads;
+    const int pieces = p.blocks * 4 >= static_cast<int64_t>(kThreads) * 4 * 148 * 8 ? 4 : 1;
+    const int64_t grid = (p.blocks * 4 + kThreads * pieces - 1) / (kThreads * pieces);
     WUDA_REQUIRE(grid <= 0x7fffffff, "too many blocks for one launch");
-    WUDA_CUDA(launch_pdl(fp4_act_quant_kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0,
-                         static_cast<cudaStream_t>(stream), p));
+    if (pieces == 4)
+        WUDA_CUDA(launch_pdl(fp4_act_quant_kernel<4>, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0,
+                             static_cast<cudaStream_t>(stream), p));
+    else
+        WUDA_CUDA(launch_pdl(fp4_act_quant_kernel<1>, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0,
+                             static_cast<cudaStream_t>(stream), p));
     return WUDA_OK;
 }
