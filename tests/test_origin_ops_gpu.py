@@ -135,6 +135,15 @@ def test_fp4_act_quant_against_oracle(wuda, rows, cols, seed):
     torch.cuda.synchronize()
     assert back.data_ptr() == z.data_ptr()
     assert np.array_equal(bf16_bits(z), odeq)
+    # a column slice of a wider matrix is read, and in place written, where it lies
+    wide = torch.full((rows, cols + 64), 7.0, dtype=torch.bfloat16, device="cuda")
+    wide[:, 32:32 + cols] = xb
+    ys, ss = wuda.fp4_act_quant(wide[:, 32:32 + cols])
+    assert torch.equal(ys.view(torch.uint8), y.view(torch.uint8)) and torch.equal(ss.view(torch.uint8), s.view(torch.uint8))
+    wuda.fp4_act_quant(wide[:, 32:32 + cols], 32, True)
+    torch.cuda.synchronize()
+    assert np.array_equal(bf16_bits(wide[:, 32:32 + cols]), odeq)
+    assert (wide[:, :32] == 7.0).all() and (wide[:, 32 + cols:] == 7.0).all()
     # a view of a wider tensor (3-D, last dimension dense) quantises row by row like the origin's .view(-1, N)
     y3, s3 = wuda.fp4_act_quant(xb.view(rows, 1, cols))
     torch.cuda.synchronize()

@@ -822,6 +822,13 @@ def one(kind, m, n, k, launches=5):
         if kind == "gemm_fp8_pow2":
             a_s, w_s = torch.exp2(torch.log2(a_s).round()), torch.exp2(torch.log2(w_s).round())
         fn = lambda: wuda.fp8_gemm(a, a_s, w, w_s, pow2_scales=kind == "gemm_fp8_pow2")
+    elif kind == "fp4_act_quant":          # m rows of n values (k unused)
+        xs = [torch.randn(m, n, device="cuda").bfloat16() for _ in range(launches)]
+        state = {"i": 0}
+
+        def fn():
+            wuda.fp4_act_quant(xs[state["i"] % launches])
+            state["i"] += 1
     elif kind == "gemm_fp8_fp4":
         gen = torch.Generator(device="cuda").manual_seed(7)
         a = torch.randint(0, 0x78, (m, k), dtype=torch.uint8, device="cuda", generator=gen).view(torch.float8_e4m3fn)

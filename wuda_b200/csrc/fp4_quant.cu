@@ -62,18 +62,21 @@ __global__ void __launch_bounds__(kThreads) fp4_act_quant_kernel(Params p) {
     const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
     const int sub = static_cast<int>(t & 3);
     uint4 raw[kPieces];
-    int64_t blk[kPieces], row[kPieces];
-    int col[kPieces];
+    int64_t blk[kPieces], at[kPieces];     // block number; element offset of the thread's piece in x
+    const bool dense = p.row_stride == static_cast<int64_t>(p.blocks_per_row) * 32;   // no division needed
 #pragma unroll
     for (int j = 0; j < kPieces; ++j) {
         blk[j] = (t + j * threads) >> 2;
         raw[j] = make_uint4(0u, 0u, 0u, 0u);
-        row[j] = 0;
-        col[j] = 0;
+        at[j] = 0;
         if (blk[j] < p.blocks) {
-            row[j] = blk[j] / p.blocks_per_row;
-            col[j] = static_cast<int>(blk[j] - row[j] * p.blocks_per_row) * 32 + sub * 8;
-            raw[j] = *reinterpret_cast<const uint4*>(p.x + row[j] * p.row_stride + col[j]);
+            if (dense) {
+                at[j] = blk[j] * 32 + sub * 8;
+            } else {
+                const int64_t row = blk[j] / p.blocks_per_row;
+                at[j] = row * p.row_stride + (blk[j] - row * p.blocks_per_row) * 32 + sub * 8;
+            }
+            raw[j] = *reinterpret_cast<const uint4*>(p.x + at[j]);
         }
     }
 #pragma unroll
@@ -108,7 +111,7 @@ __global__ void __launch_bounds__(kThreads) fp4_act_quant_kernel(Params p) {
                 const __nv_bfloat162 pair = __floats2bfloat162_rn(e2m1_value(byte & 15u) * scale, e2m1_value(byte >> 4) * scale);
                 o[i] = *reinterpret_cast<const uint32_t*>(&pair);
             }
-            *reinterpret_cast<uint4*>(p.y_inplace + row[j] * p.row_stride + col[j]) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(p.y_inplace + at[j]) = make_uint4(o[0], o[1], o[2], o[3]);
         } else {
             *reinterpret_cast<uint32_t*>(p.codes + blk[j] * 16 + sub * 4) = packed;
             if (sub == 0) p.scales[blk[j]] = static_cast<uint8_t>(e + 127);

@@ -689,16 +689,19 @@ def fp4_act_quant(x, block_size=32, inplace=False):
     _require(block_size == 32, "block_size must be 32")
     _require(x.is_cuda and x.dtype == torch.bfloat16 and x.size(-1) % 32 == 0, "x must be CUDA bf16 [..., N], N % 32 == 0")
     n = x.size(-1)
-    z = x if (inplace and x.is_contiguous()) else x.contiguous()
+    # rows of a wider matrix (a column slice with 16-byte aligned rows) are read and written where they are
+    strided = x.dim() == 2 and x.stride(1) == 1 and x.stride(0) >= n and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+    z = x if (strided or x.is_contiguous()) else x.contiguous()
     rows = z.numel() // n
+    stride = z.stride(0) if strided else n
     if inplace:
-        check(lib.wuda_fp4_act_quant(z.data_ptr(), n, None, None, 1, rows, n, _stream()))
+        check(lib.wuda_fp4_act_quant(z.data_ptr(), stride, None, None, 1, rows, n, _stream()))
         if z.data_ptr() != x.data_ptr():
             x.copy_(z)
         return x
     y = torch.empty(*z.shape[:-1], n // 2, dtype=torch.uint8, device=x.device)
     sc = torch.empty(*z.shape[:-1], n // 32, dtype=torch.uint8, device=x.device)
-    check(lib.wuda_fp4_act_quant(z.data_ptr(), n, y.data_ptr(), sc.data_ptr(), 0, rows, n, _stream()))
+    check(lib.wuda_fp4_act_quant(z.data_ptr(), stride, y.data_ptr(), sc.data_ptr(), 0, rows, n, _stream()))
     fp4 = getattr(torch, "float4_e2m1fn_x2", None)
     e8 = getattr(torch, "float8_e8m0fnu", None)
     return (y.view(fp4) if fp4 is not None else y), (sc.view(e8) if e8 is not None else sc)
