@@ -758,8 +758,9 @@ def fp8_gemm(a, a_s, b, b_s, scale_dtype=torch.float32, *, out=None, status_word
     output: the origin's fp8_gemm(a, a_s, b, b_s) (origin/kernel.py:257-273).  pow2_scales=True promises that
     every scale is a power of two (the reference's UE8M0 scales) and takes the kernel that applies them inside
     the tensor core."""
-    if a_s.dtype != torch.float32 or b_s.dtype != torch.float32:     # float8_e8m0fnu scales: powers of two by type
-        a_s, b_s, pow2_scales = _scales_as_fp32(a_s, "a_s"), _scales_as_fp32(b_s, "b_s"), True
+    if a_s.dtype != torch.float32 and b_s.dtype != torch.float32:    # float8_e8m0fnu scales: powers of two by type
+        pow2_scales = True
+    a_s, b_s = _scales_as_fp32(a_s, "a_s"), _scales_as_fp32(b_s, "b_s")
     _require(a.is_cuda and a.is_contiguous() and a.dtype == torch.float8_e4m3fn, "a must be contiguous CUDA e4m3")
     _require(b.is_cuda and b.is_contiguous() and b.dtype == torch.float8_e4m3fn and b.dim() == 2,
              "b must be contiguous CUDA e4m3 [N, K]")
